@@ -1,0 +1,115 @@
+/* tilejax_b200 — C ABI of the sm_100a step-loop kernels.
+ *
+ * Every entry point takes plain pointers and sizes, enqueues work on the CUDA stream it is given and returns
+ * without synchronising: 0 on success, a negative TJX_E_* code otherwise (tjx_last_error() has the text).
+ * Unless stated otherwise every data pointer is DEVICE memory that the callee borrows for the duration of
+ * the enqueued work; nothing is allocated per call. The library never falls back to the CPU: on a device
+ * that is not compute capability 10.x every compute entry point returns TJX_E_DEVICE.
+ *
+ * Each declaration cites the part of the reference (RKKatakam/tilejax, package `autokernel`) it stands in
+ * for, by path within that project.
+ */
+#ifndef TILEJAX_B200_H_
+#define TILEJAX_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* tjx_stream_t; /* a cudaStream_t */
+
+#define TJX_E_ARG (-1)    /* bad argument: shape, alignment, null pointer */
+#define TJX_E_CUDA (-2)   /* a CUDA call failed */
+#define TJX_E_DEVICE (-3) /* not an sm_100 device */
+#define TJX_E_LIMIT (-4)  /* a size exceeds what the entry point supports */
+#define TJX_E_KERNEL (-5) /* a kernel reported an error through its status word */
+
+/* Library version: major * 10000 + minor * 100 + patch. */
+int tjx_version(void);
+
+/* Text of the calling thread's last error ("" if none). */
+const char* tjx_last_error(void);
+
+/* Synchronises `stream`, then reads and clears the current device's kernel status word: *code is 0, or the
+ * code of the first bounded wait that ran out inside a kernel (1xx). Returns 0, or TJX_E_KERNEL if *code != 0.
+ * Replaces nothing in the reference: its kernels cannot report errors; here every device-side wait is bounded
+ * and gives up through this word instead of hanging. */
+int tjx_device_status(tjx_stream_t stream, int* code);
+
+/* The device step-table builder for runtime masks of the form `value(k) >= lengths[tile_value[t]]: continue`
+ * with value(k) = value0 + k * value_step — `paged_gqa_decode` (examples/decode.py:214, value = p * page_size)
+ * and `gqa_decode` (examples/decode.py:188, value = j).
+ * Stands in for the generated `<kernel>_steps` / `_phase_steps` (src/autokernel/codegen.py:376-451).
+ *   lengths      int32[n_lengths]   index array the mask reads
+ *   tile_values  int32[tiles] or NULL (NULL = 0..tiles-1): which length each tile reads (Schedule.tile_values,
+ *                src/autokernel/schedule.py:267)
+ *   step_tile    int32[tiles * blocks]  OUT  each step's tile
+ *   step_code    int32[tiles * blocks]  OUT  block << 3 | empty << 2 | first << 1 | last
+ *   step_count   int32[1]               OUT  steps that run (they come first, in order; the others follow in
+ *                                            their original order, as the reference's stable argsort leaves them)
+ *   tile_first   int32[tiles + 1] or NULL  OUT  extra: index of each tile's first step among those that run
+ */
+int tjx_build_steps(const int32_t* lengths, int n_lengths, const int32_t* tile_values, int tiles, int blocks,
+                    int value0, int value_step, int32_t* step_tile, int32_t* step_code, int32_t* step_count,
+                    int32_t* tile_first, tjx_stream_t stream);
+
+/* The same compaction for an arbitrary mask already evaluated: run[t * blocks + k] != 0 where block k of tile t
+ * runs (uint8). Follows src/autokernel/codegen.py:386-431 for any pattern of skipped blocks. */
+int tjx_build_steps_from_runs(const uint8_t* run, int tiles, int blocks, int32_t* step_tile, int32_t* step_code,
+                              int32_t* step_count, int32_t* tile_first, tjx_stream_t stream);
+
+/* The step loop of `matmul` (examples/matmul.py:22-35), `causal_matmul` (examples/causal_matmul.py:23-40) and
+ * the compute half of `all_gather_matmul` (examples/collective_matmul.py:44-59): out = x @ y with bf16
+ * operands, f32 accumulation (src/autokernel/mxu.py:21-43) and a bf16 or f32 result, one output tile of
+ * (tm, tn) after another, each summing K in blocks. Replaces the generated kernel's loop
+ * (src/autokernel/codegen.py:1433-1538) with a persistent TMA + tcgen05 kernel.
+ *   x [M, K] bf16 row-major; y [K, N] bf16 row-major, or [N, K] if y_transposed (x @ y.T, mxu.py:38-43)
+ *   out [M, N] bf16, or f32 if out_f32
+ *   tile_i, tile_j  int32[n_tiles] or NULL: block indices (i / tm, j / tn) of the tiles that run, in order
+ *                   (Schedule.tables "tile_i"/"tile_j", src/autokernel/schedule.py:349-358); NULL = every tile,
+ *                   row-major
+ *   fill_i, fill_j  int32[n_fills] or NULL: tiles the mask skips, written with zeros (the output's fill)
+ *   causal          != 0: entries above the diagonal of a computed tile are zero (`jnp.where(cols <= rows, ..)`)
+ *   tk              the reduction block: reported only; the kernel sums K in its own blocks of 64
+ *   stages          depth of the shared-memory ring (2..6; 0 = default)
+ * Constraints: K % 8 == 0, N % 8 == 0; tm % 128 == 0 or tm == M; tn % 128 == 0 or tn == N. */
+int tjx_gemm_bf16(const void* x, const void* y, void* out, int M, int N, int K, int y_transposed, int tm, int tn,
+                  int tk, int stages, int out_f32, int causal, const int32_t* tile_i, const int32_t* tile_j,
+                  int n_tiles, const int32_t* fill_i, const int32_t* fill_j, int n_fills, tjx_stream_t stream);
+
+/* Flash-style causal attention, the step loop of `causal_attention` (examples/causal_attention.py:37-63):
+ * q (pre-scaled), k, v, out [B, H, S, D] bf16, D == 128; online softmax in f32, P rounded to bf16 before P @ v.
+ *   step_tile, step_code  int32[pattern_steps]: one (b, h)'s steps (Schedule.tables "step_tile"/"step_code",
+ *                         src/autokernel/schedule.py:196-211): tile = query block, code = kv block << 3 | flags
+ *   pattern_tiles         query blocks per (b, h) = S / block_q */
+int tjx_causal_attention_bf16(const void* q, const void* k, const void* v, void* out, int B, int H, int S, int D,
+                              int block_q, int block_kv, const int32_t* step_tile, const int32_t* step_code,
+                              int pattern_steps, int pattern_tiles, tjx_stream_t stream);
+
+/* Bytes of scratch tjx_paged_gqa_decode_bf16 needs for these sizes. */
+size_t tjx_paged_gqa_decode_workspace_bytes(int B, int H, int D, int pages_per_seq);
+
+/* Ragged paged GQA decode attention, `paged_gqa_decode` (examples/decode.py:199-223) for one new token:
+ * builds the step tables on the device from `lengths` (as the generated entry does before its kernel,
+ * src/autokernel/codegen.py:465-467), then walks only the pages that hold valid positions.
+ *   q [B, 1, H, D] bf16 (pre-scaled); k_pages, v_pages [num_pages, page_size, Hkv * D] bf16
+ *   block_tables int32[B, pages_per_seq] (entries clamped to [0, num_pages - 1], codegen.py:1045-1048)
+ *   lengths int32[B] (0 = empty slot: its output is 0); out [B, 1, H, D] bf16
+ *   step_tile, step_code int32[B * pages_per_seq], step_count int32[1], tile_first int32[B + 1]: OUT, the
+ *   tables this call built and walked (bit-exact with the reference's)
+ *   workspace: scratch of at least tjx_paged_gqa_decode_workspace_bytes(...) bytes, 256-byte aligned
+ * Constraints: D == 128; H / Hkv in {1, 2, 4, 8}; page_size a multiple of 16. */
+int tjx_paged_gqa_decode_bf16(const void* q, const void* k_pages, const void* v_pages, const int32_t* block_tables,
+                              const int32_t* lengths, void* out, int B, int H, int Hkv, int D, int page_size,
+                              int pages_per_seq, int num_pages, int32_t* step_tile, int32_t* step_code,
+                              int32_t* step_count, int32_t* tile_first, void* workspace, size_t workspace_bytes,
+                              tjx_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* TILEJAX_B200_H_ */

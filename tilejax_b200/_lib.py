@@ -1,0 +1,63 @@
+"""Loads libtilejax_b200.so (built in-tree by `tilejax_b200.csrc.build`) and declares its C ABI for ctypes.
+
+There is no fallback: if the library is missing or a call fails, an exception says so.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import threading
+from ctypes import c_char_p, c_int, c_size_t, c_void_p
+from pathlib import Path
+
+LIBRARY = Path(__file__).resolve().parent / "libtilejax_b200.so"
+
+# Every symbol include/tilejax_b200.h declares: name -> (restype, argtypes).
+_P = c_void_p
+SYMBOLS: dict[str, tuple] = {
+    "tjx_version": (c_int, []),
+    "tjx_last_error": (c_char_p, []),
+    "tjx_device_status": (c_int, [_P, ctypes.POINTER(c_int)]),
+    "tjx_build_steps": (c_int, [_P, c_int, _P, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P]),
+    "tjx_build_steps_from_runs": (c_int, [_P, c_int, c_int, _P, _P, _P, _P, _P]),
+    "tjx_gemm_bf16": (c_int, [_P, _P, _P] + [c_int] * 10 + [_P, _P, c_int, _P, _P, c_int, _P]),
+    "tjx_causal_attention_bf16": (c_int, [_P, _P, _P, _P] + [c_int] * 6 + [_P, _P, c_int, c_int, _P]),
+    "tjx_paged_gqa_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "tjx_paged_gqa_decode_bf16": (c_int, [_P] * 6 + [c_int] * 7 + [_P] * 5 + [c_size_t, _P]),
+}
+
+_lock = threading.Lock()
+_lib: ctypes.CDLL | None = None
+
+
+class NativeError(RuntimeError):
+    """A call into libtilejax_b200.so failed; `code` is its TJX_E_* return value."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"tilejax_b200: {message} (code {code})")
+        self.code = code
+
+
+def library() -> ctypes.CDLL:
+    """The loaded library with argument types set. Raises if it has not been built."""
+    global _lib
+    with _lock:
+        if _lib is None:
+            if not LIBRARY.exists():
+                raise RuntimeError(
+                    f"{LIBRARY} is missing: build it with `python -m tilejax_b200.csrc.build` "
+                    "(there is no CPU or PyTorch fallback for these kernels)"
+                )
+            lib = ctypes.CDLL(str(LIBRARY))
+            for name, (restype, argtypes) in SYMBOLS.items():
+                fn = getattr(lib, name)  # AttributeError if the library lacks a declared symbol
+                fn.restype = restype
+                fn.argtypes = argtypes
+            _lib = lib
+        return _lib
+
+
+def check(code: int) -> None:
+    """Raise NativeError for a non-zero return code."""
+    if code != 0:
+        raise NativeError(code, library().tjx_last_error().decode() or "unknown error")

@@ -1,0 +1,79 @@
+"""Builds libtilejax_b200.so (the CUDA kernels and their C ABI) in-tree with nvcc, for sm_100a only.
+
+    python -m tilejax_b200.csrc.build [--force] [--verbose]
+
+nvcc cross-compiles without a GPU. The CUDA runtime is linked statically and the driver API is reached
+through cudaGetDriverEntryPoint, so the library has no load-time dependency on libcuda and also loads (for
+symbol checks) on a machine without a driver.
+"""
+
+from __future__ import annotations
+
+import argparse
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+CSRC = Path(__file__).resolve().parent
+PACKAGE = CSRC.parent
+LIBRARY = PACKAGE / "libtilejax_b200.so"
+SOURCES = ["tjx_host.cu", "tjx_steps.cu", "tjx_gemm.cu", "tjx_decode.cu", "tjx_attention.cu"]
+HEADERS = ["tjx_host.cuh", "tjx_ptx.cuh", "../../include/tilejax_b200.h"]
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
+
+
+def nvcc() -> str:
+    found = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not Path(found).exists():
+        raise RuntimeError("nvcc not found: the CUDA kernels cannot be built")
+    return found
+
+
+def _stale(target: Path, deps: list[Path]) -> bool:
+    if not target.exists():
+        return True
+    built = target.stat().st_mtime
+    return any(d.stat().st_mtime > built for d in deps)
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compile every source that changed and link the shared library; returns its path."""
+    objdir = CSRC / "build"
+    objdir.mkdir(exist_ok=True)
+    headers = [(CSRC / h).resolve() for h in HEADERS] + [Path(__file__).resolve()]
+    sources = [CSRC / s for s in SOURCES if (CSRC / s).exists()]
+    objects = []
+    jobs = []
+    for src in sources:
+        obj = objdir / (src.stem + ".o")
+        objects.append(obj)
+        if force or _stale(obj, [src, *headers]):
+            cmd = [nvcc(), *ARCH_FLAGS, *COMMON_FLAGS, "-c", str(src), "-o", str(obj)]
+            if verbose:
+                cmd.insert(1, "-Xptxas=-v")
+            jobs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    failed = []
+    for src, proc in jobs:
+        out, _ = proc.communicate()
+        if proc.returncode != 0:
+            failed.append(f"{src.name}:\n{out}")
+        elif verbose or out.strip():
+            print(f"--- {src.name}\n{out}", file=sys.stderr)
+    if failed:
+        raise RuntimeError("nvcc failed:\n" + "\n".join(failed))
+    if force or jobs or _stale(LIBRARY, objects):
+        cmd = [nvcc(), *ARCH_FLAGS, "-shared", "-Xcompiler", "-fPIC", "-o", str(LIBRARY), *map(str, objects)]
+        subprocess.run(cmd, check=True)
+    return LIBRARY
+
+
+if __name__ == "__main__":
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--force", action="store_true")
+    parser.add_argument("--verbose", action="store_true", help="print ptxas resource usage (registers, spills, smem)")
+    args = parser.parse_args()
+    os.chdir(CSRC)
+    print(build(args.force, args.verbose))

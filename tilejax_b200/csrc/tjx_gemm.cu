@@ -1,0 +1,434 @@
+// The matmul step loop on sm_100a: out = x @ y (bf16 operands, f32 accumulation in TMEM), optionally causal
+// (tril) with skipped tiles written as zeros, walking a table of the output tiles that run.
+//
+// One persistent CTA per SM. A user tile (tm, tn) — the unit the tile tables and the skip sets are expressed
+// in — is cut into CTA tiles of 128 x BN; work item w = (user tile, sub-tile) and CTA c takes items
+// c, c + grid, c + 2 grid, ... All roles derive the same item sequence, so nothing is communicated.
+//
+//   warp 0   producer: TMA loads of the x tile [128 x 64] and the y tile [64 x BN] into a ring of STAGES
+//            shared-memory slots (128-byte swizzle), one mbarrier pair (full / empty) per slot
+//   warp 1   MMA issuer: one thread issues tcgen05.mma (M 128, N BN, K 16) four times per slot, accumulating
+//            in one of two TMEM accumulators; tcgen05.commit frees the slot and, after the last K block,
+//            hands the accumulator to the epilogue
+//   warps 2-5 epilogue: tcgen05.ld the accumulator (each warp its 32 lanes), apply the causal mask, convert,
+//            stage the tile in shared memory and TMA-store it; they also write the zero fills
+//
+// y [K, N] row-major is the MN-major B operand: a slot holds BN / 64 boxes of [64 n x 64 k], each row of a
+// box one k with 64 consecutive n (128 bytes). y [N, K] (x @ y.T) is the K-major operand, one box [64 k x BN].
+#include "tjx_host.cuh"
+#include "tjx_ptx.cuh"
+
+#include "../../include/tilejax_b200.h"
+
+namespace tjx {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int GEMM_THREADS = 192;
+constexpr int EPI_THREADS = 128;
+
+struct GemmParams {
+  int M, N, K;
+  int tm, tn;            // the user tile
+  int tiles_n;           // user tiles along N (arithmetic order when there is no table)
+  int sub_m, sub_n;      // CTA tiles per user tile
+  int n_tiles, n_fills;  // user tiles that run / that are filled
+  const int32_t* tile_i;
+  const int32_t* tile_j;
+  const int32_t* fill_i;
+  const int32_t* fill_j;
+  int causal, out_f32, b_kmajor;
+  int num_kb;
+  void* out;
+  int* status;
+};
+
+struct Item {
+  int m0, n0;
+  bool compute;  // runs the MMA pipeline; otherwise the epilogue writes zeros
+  bool valid;    // false: a table entry out of range, nothing is written
+};
+
+template <int BN>
+__device__ __forceinline__ Item decode_item(const GemmParams& p, int w) {
+  const int per = p.sub_m * p.sub_n;
+  const int t = w / per, r = w - t * per;
+  const int sm = r / p.sub_n, sn = r - sm * p.sub_n;
+  int ti, tj;
+  bool fill = false;
+  if (t < p.n_tiles) {
+    if (p.tile_i != nullptr) {
+      ti = p.tile_i[t];
+      tj = p.tile_j[t];
+    } else {
+      ti = t / p.tiles_n;
+      tj = t - ti * p.tiles_n;
+    }
+  } else {
+    fill = true;
+    ti = p.fill_i[t - p.n_tiles];
+    tj = p.fill_j[t - p.n_tiles];
+  }
+  Item it;
+  it.valid = ti >= 0 && tj >= 0 && static_cast<long long>(ti) * p.tm < p.M && static_cast<long long>(tj) * p.tn < p.N;
+  it.m0 = ti * p.tm + sm * BM;
+  it.n0 = tj * p.tn + sn * BN;
+  if (it.m0 >= p.M || it.n0 >= p.N) it.valid = false;  // a sub-tile wholly past the edge of a clipped tile
+  // A sub-tile wholly above the diagonal of a causal tile is all zeros: no loads, no MMA.
+  it.compute = it.valid && !fill && !(p.causal && it.n0 > it.m0 + BM - 1);
+  return it;
+}
+
+template <int BN, int STAGES>
+struct GemmSmem {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int C_BYTES = 4 * 32 * 64 * 2 * 2;  // per epilogue warp: two buffers of 32 rows x 128 bytes
+  static constexpr int RING_OFF = 0;
+  static constexpr int C_OFF = STAGES * STAGE_BYTES;
+  static constexpr int BAR_OFF = C_OFF + C_BYTES;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;  // barriers + slack for 1024-byte alignment
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+    gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
+  using L = GemmSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bar_base = base + L::BAR_OFF;
+  // barrier layout (8 bytes each): full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
+  auto tempty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 2 + s); };
+  volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(base_ptr + L::BAR_OFF + 8 * (2 * STAGES + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + L::BAR_OFF + 8 * (2 * STAGES + 4) + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int per = p.sub_m * p.sub_n;
+  const int total_items = (p.n_tiles + p.n_fills) * per;
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(tfull_bar(s), 1);
+      mbar_init(tempty_bar(s), 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+    tma_prefetch_desc(&map_c);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_holder)), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_items && ok; w += gridDim.x) {
+        const Item it = decode_item<BN>(p, w);
+        if (!it.compute) continue;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, TJX_ERR_WAIT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = base + L::RING_OFF + stage * L::STAGE_BYTES;
+          const uint32_t b_dst = a_dst + L::A_BYTES;
+          mbar_expect_tx(full_bar(stage), L::STAGE_BYTES);
+          tma_load_2d(a_dst, &map_a, kb * BK, it.m0, full_bar(stage));
+          if (p.b_kmajor) {
+            tma_load_2d(b_dst, &map_b, kb * BK, it.n0, full_bar(stage));
+          } else {
+#pragma unroll
+            for (int nb = 0; nb < BN / 64; ++nb)
+              tma_load_2d(b_dst + nb * (64 * BK * 2), &map_b, it.n0 + nb * 64, kb * BK, full_bar(stage));
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = idesc_bf16_f32(BM, BN, 0, p.b_kmajor ? 0 : 1);
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_items && ok; w += gridDim.x) {
+        const Item it = decode_item<BN>(p, w);
+        if (!it.compute) continue;
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, TJX_ERR_WAIT_TMEM_EMPTY)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, TJX_ERR_WAIT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = base + L::RING_OFF + stage * L::STAGE_BYTES;
+          const uint32_t b_addr = a_addr + L::A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            const uint64_t a_desc = smem_desc_sw128(a_addr + kk * 32, 16, 1024);
+            const uint64_t b_desc = p.b_kmajor ? smem_desc_sw128(b_addr + kk * 32, 16, 1024)
+                                               : smem_desc_sw128(b_addr + kk * (16 * 128), 64 * BK * 2, 1024);
+            mma_ss(d_tmem, a_desc, b_desc, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          mma_commit(empty_bar(stage));  // the slot is free once these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        mma_commit(tfull_bar(acc));  // the accumulator is complete once every MMA above has finished
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;  // the TMEM lane quarter this warp may read: lanes 32 q .. 32 q + 31
+    const int ew = warp - 2;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const int out_elt = p.out_f32 ? 4 : 2;
+    // Per warp: two staging buffers of 32 rows x 128 bytes (128-byte swizzled), alternated so a TMA store
+    // can still be reading one while the warp fills the other.
+    const uint32_t c_smem = base + L::C_OFF + ew * (2 * 32 * 128);
+    uint8_t* c_ptr = base_ptr + L::C_OFF + ew * (2 * 32 * 128);
+    int c_buf = 0;
+    for (int w = blockIdx.x; w < total_items; w += gridDim.x) {
+      const Item it = decode_item<BN>(p, w);
+      if (!it.valid) {
+        if (lane == 0 && p.status != nullptr) atomicCAS(p.status, 0, TJX_ERR_BAD_TABLE);
+        continue;
+      }
+      if (!it.compute) {
+        // Zeros: rows m0 + 32 q .. + 31, each BN * out_elt bytes, 16 bytes per lane per pass.
+        const int row_bytes = BN * out_elt;
+        for (int r = 0; r < 32; ++r) {
+          const int row = it.m0 + q * 32 + r;
+          if (row >= p.M) break;
+          uint8_t* dst = static_cast<uint8_t*>(p.out) + (static_cast<size_t>(row) * p.N + it.n0) * out_elt;
+          const int valid_bytes = min(row_bytes, (p.N - it.n0) * out_elt);
+          for (int b = lane * 16; b < valid_bytes; b += 32 * 16)
+            *reinterpret_cast<uint4*>(dst + b) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        continue;
+      }
+      const bool got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, TJX_ERR_WAIT_TMEM_FULL);
+      if (!__all_sync(0xFFFFFFFFu, got)) break;
+      tc_fence_after_sync();
+      const int row = it.m0 + q * 32 + lane;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      // Chunks of 32 accumulator columns. bf16: two chunks fill one 32 x 64 staging buffer (128 bytes per
+      // row); f32: one chunk does.
+      constexpr int CHUNKS = BN / 32;
+#pragma unroll 1
+      for (int c = 0; c < CHUNKS; ++c) {
+        uint32_t v[32];
+        tmem_ld32(t_row + c * 32, v);
+        tmem_wait_ld();
+        if (p.causal) {
+          const int col0 = it.n0 + c * 32;
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j > row) v[j] = 0u;
+        }
+        const bool new_buf = p.out_f32 || (c & 1) == 0;
+        if (new_buf) {
+          // The TMA store issued two buffers ago has finished reading this buffer.
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+        }
+        uint8_t* buf = c_ptr + c_buf * (32 * 128);
+        // Row `lane` of the buffer is 128 bytes = eight 16-byte units; unit u is stored at u ^ (lane & 7).
+        if (p.out_f32) {
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            uint4 val = make_uint4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
+            *reinterpret_cast<uint4*>(buf + lane * 128 + ((u ^ (lane & 7)) << 4)) = val;
+          }
+        } else {
+          const int half = c & 1;  // which 64 bytes of the 128-byte row
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 val;
+            val.x = pack_bf16(__uint_as_float(v[8 * u + 0]), __uint_as_float(v[8 * u + 1]));
+            val.y = pack_bf16(__uint_as_float(v[8 * u + 2]), __uint_as_float(v[8 * u + 3]));
+            val.z = pack_bf16(__uint_as_float(v[8 * u + 4]), __uint_as_float(v[8 * u + 5]));
+            val.w = pack_bf16(__uint_as_float(v[8 * u + 6]), __uint_as_float(v[8 * u + 7]));
+            const int unit = half * 4 + u;
+            *reinterpret_cast<uint4*>(buf + lane * 128 + ((unit ^ (lane & 7)) << 4)) = val;
+          }
+        }
+        const bool flush = p.out_f32 || (c & 1) == 1;
+        if (flush) {
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const int col = p.out_f32 ? it.n0 + c * 32 : it.n0 + (c >> 1) * 64;
+            tma_store_2d(&map_c, c_smem + c_buf * (32 * 128), col, it.m0 + q * 32);
+            tma_store_commit();
+          }
+          c_buf ^= 1;
+        }
+      }
+      // The accumulator has been read: hand it back to the MMA warp.
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    }
+    if (lane == 0) tma_store_wait_all<0>();
+    __syncwarp();
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    if (*abort_flag) __nanosleep(100000);  // let whatever is still in flight land before TMEM goes away
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int BN, int STAGES>
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const GemmParams& p,
+                       int grid, cudaStream_t stream) {
+  using L = GemmSmem<BN, STAGES>;
+  auto kernel = gemm_kernel<BN, STAGES>;
+  static bool configured[64] = {};
+  int dev = 0;
+  TJX_CUDA(cudaGetDevice(&dev));
+  if (!configured[dev & 63]) {
+    TJX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+    configured[dev & 63] = true;
+  }
+  kernel<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(ma, mb, mc, p);
+  TJX_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace tjx
+
+extern "C" int tjx_gemm_bf16(const void* x, const void* y, void* out, int M, int N, int K, int y_transposed, int tm,
+                             int tn, int tk, int stages, int out_f32, int causal, const int32_t* tile_i,
+                             const int32_t* tile_j, int n_tiles, const int32_t* fill_i, const int32_t* fill_j,
+                             int n_fills, tjx_stream_t stream) {
+  using namespace tjx;
+  if (int rc = check_device()) return rc;
+  if (x == nullptr || y == nullptr || out == nullptr) return fail(TJX_E_ARG, "x, y or out is null");
+  if (M <= 0 || N <= 0 || K <= 0) return fail(TJX_E_ARG, "M, N, K must be positive");
+  if (K % 8 != 0 || N % 8 != 0)
+    return fail(TJX_E_ARG, "K and N must be multiples of 8 (16-byte rows for the TMA descriptors)");
+  if (tm <= 0 || tn <= 0 || tk <= 0) return fail(TJX_E_ARG, "tile sizes must be positive");
+  if (!(tm % 128 == 0 || tm == M)) return fail(TJX_E_ARG, "tm must be a multiple of 128, or all of M");
+  if (!(tn % 128 == 0 || tn == N)) return fail(TJX_E_ARG, "tn must be a multiple of 128, or all of N");
+  if (M % tm != 0 || N % tn != 0) return fail(TJX_E_ARG, "the tiles must cover M and N exactly");
+  if ((tile_i == nullptr) != (tile_j == nullptr)) return fail(TJX_E_ARG, "tile_i and tile_j go together");
+  if (n_fills < 0 || (n_fills > 0 && (fill_i == nullptr || fill_j == nullptr)))
+    return fail(TJX_E_ARG, "fill tables are missing");
+  if (causal && y_transposed == 0 && M != N) { /* tril of a rectangular product is still well defined */ }
+  const int tiles_m = M / tm, tiles_n = N / tn;
+  if (tile_i == nullptr) {
+    if (n_tiles != 0 && n_tiles != tiles_m * tiles_n)
+      return fail(TJX_E_ARG, "without a tile table every tile runs: n_tiles must be 0 or (M/tm)*(N/tn)");
+    n_tiles = tiles_m * tiles_n;
+  } else if (n_tiles <= 0) {
+    return fail(TJX_E_ARG, "a tile table needs n_tiles > 0");
+  }
+  if (stages == 0) stages = 4;
+  const int BN = (tn % 256 == 0) ? 256 : 128;
+  if (!(stages == 4 || (BN == 128 && stages == 6) || (BN == 256 && stages == 3)))
+    return fail(TJX_E_ARG, "stages must be 0 (default), 4, 3 (256-wide CTA tiles) or 6 (128-wide)");
+
+  GemmParams p{};
+  p.M = M, p.N = N, p.K = K, p.tm = tm, p.tn = tn, p.tiles_n = tiles_n;
+  p.sub_m = (tm + BM - 1) / BM;
+  p.sub_n = (tn + BN - 1) / BN;
+  p.n_tiles = n_tiles, p.n_fills = n_fills;
+  p.tile_i = tile_i, p.tile_j = tile_j, p.fill_i = fill_i, p.fill_j = fill_j;
+  p.causal = causal ? 1 : 0, p.out_f32 = out_f32 ? 1 : 0, p.b_kmajor = y_transposed ? 1 : 0;
+  p.num_kb = (K + BK - 1) / BK;
+  p.out = out;
+  p.status = device_status_word();
+  if (p.status == nullptr) return fail(TJX_E_CUDA, "could not allocate the device status word");
+
+  CUtensorMap ma, mb, mc;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(K) * 2};
+    const uint32_t box[2] = {BK, BM};
+    if (int rc = make_tensor_map(&ma, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 2, dims, strides, box,
+                                 CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  }
+  if (y_transposed) {
+    const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(K) * 2};
+    const uint32_t box[2] = {BK, static_cast<uint32_t>(BN)};
+    if (int rc = make_tensor_map(&mb, y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 2, dims, strides, box,
+                                 CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  } else {
+    const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(K)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(N) * 2};
+    const uint32_t box[2] = {64, BK};
+    if (int rc = make_tensor_map(&mb, y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 2, dims, strides, box,
+                                 CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  }
+  {
+    // Output staging: 32 rows x 128 bytes per store (64 bf16 or 32 f32 columns), 128-byte swizzled.
+    const int elt = out_f32 ? 4 : 2;
+    const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(M)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(N) * elt};
+    const uint32_t box[2] = {static_cast<uint32_t>(128 / elt), 32};
+    if (int rc = make_tensor_map(&mc, out, out_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                                 elt, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  }
+
+  const long long total_items = static_cast<long long>(n_tiles + n_fills) * p.sub_m * p.sub_n;
+  if (total_items >= (1ll << 31)) return fail(TJX_E_LIMIT, "too many output tiles");
+  const int grid = static_cast<int>(total_items < sm_count() ? total_items : sm_count());
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (BN == 256) {
+    if (stages == 3) return launch_gemm<256, 3>(ma, mb, mc, p, grid, s);
+    return launch_gemm<256, 4>(ma, mb, mc, p, grid, s);
+  }
+  if (stages == 6) return launch_gemm<128, 6>(ma, mb, mc, p, grid, s);
+  return launch_gemm<128, 4>(ma, mb, mc, p, grid, s);
+}

@@ -1,0 +1,233 @@
+"""The hot-path operators on CUDA tensors: thin host wrappers that check shapes, keep the static tables on the
+device and call the C ABI (include/tilejax_b200.h) on the current CUDA stream.
+
+PyTorch is used for device memory and streams only. Nothing here computes on the CPU, and there is no fallback:
+without the built library or an sm_100 GPU the calls raise.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from functools import lru_cache
+
+import numpy as np
+import torch
+
+from . import schedule as _schedule
+from ._lib import check, library
+
+
+def _ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*tensors: torch.Tensor) -> torch.device:
+    device = tensors[0].device
+    for t in tensors:
+        if not t.is_cuda:
+            raise ValueError("tilejax_b200 operators take CUDA tensors (there is no CPU path)")
+        if t.device != device:
+            raise ValueError("all tensors must be on the same device")
+        if not t.is_contiguous():
+            raise ValueError("tensors must be contiguous (row-major)")
+    return device
+
+
+_table_cache: dict[tuple, torch.Tensor] = {}
+
+
+def device_table(key: tuple, values: np.ndarray, device: torch.device) -> torch.Tensor:
+    """A static int32 table on `device`, uploaded once per (key, device)."""
+    full = (key, str(device))
+    t = _table_cache.get(full)
+    if t is None:
+        t = torch.from_numpy(np.ascontiguousarray(values, np.int32)).to(device)
+        _table_cache[full] = t
+    return t
+
+
+def device_status() -> int:
+    """Synchronise the current stream and return (clearing it) the kernels' error word; raises if non-zero."""
+    code = ctypes.c_int(0)
+    check(library().tjx_device_status(_stream(), ctypes.byref(code)))
+    return code.value
+
+
+# ------------------------------------------------------------------------------------------ step tables
+
+
+def build_steps(lengths: torch.Tensor, blocks: int, value0: int, value_step: int,
+                tile_values: torch.Tensor | None = None):
+    """Device step tables for the runtime mask `value0 + k * value_step >= lengths[tile]: continue`.
+    Returns (step_tile, step_code, step_count, tile_first), all int32 on the device."""
+    device = _need_cuda(lengths)
+    if lengths.dtype != torch.int32:
+        raise ValueError("lengths must be int32")
+    tiles = int(lengths.numel() if tile_values is None else tile_values.numel())
+    step_tile = torch.empty(tiles * blocks, dtype=torch.int32, device=device)
+    step_code = torch.empty(tiles * blocks, dtype=torch.int32, device=device)
+    step_count = torch.empty(1, dtype=torch.int32, device=device)
+    tile_first = torch.empty(tiles + 1, dtype=torch.int32, device=device)
+    with torch.cuda.device(device):
+        check(library().tjx_build_steps(_ptr(lengths), int(lengths.numel()), _ptr(tile_values), tiles, blocks,
+                                        value0, value_step, _ptr(step_tile), _ptr(step_code), _ptr(step_count),
+                                        _ptr(tile_first), _stream()))
+    return step_tile, step_code, step_count, tile_first
+
+
+def build_steps_from_runs(run: torch.Tensor):
+    """Device step tables from an evaluated mask run[tiles, blocks] (uint8 / bool)."""
+    device = _need_cuda(run)
+    run = run.to(torch.uint8).contiguous()
+    tiles, blocks = run.shape
+    step_tile = torch.empty(tiles * blocks, dtype=torch.int32, device=device)
+    step_code = torch.empty(tiles * blocks, dtype=torch.int32, device=device)
+    step_count = torch.empty(1, dtype=torch.int32, device=device)
+    tile_first = torch.empty(tiles + 1, dtype=torch.int32, device=device)
+    with torch.cuda.device(device):
+        check(library().tjx_build_steps_from_runs(_ptr(run), tiles, blocks, _ptr(step_tile), _ptr(step_code),
+                                                  _ptr(step_count), _ptr(tile_first), _stream()))
+    return step_tile, step_code, step_count, tile_first
+
+
+# ------------------------------------------------------------------------------------------ matmul
+
+
+def gemm(x: torch.Tensor, y: torch.Tensor, tm: int, tn: int, tk: int, *, causal: bool = False,
+         out_dtype: torch.dtype | None = None, y_transposed: bool = False, stages: int = 0,
+         tile_i: torch.Tensor | None = None, tile_j: torch.Tensor | None = None,
+         fill_i: torch.Tensor | None = None, fill_j: torch.Tensor | None = None,
+         out: torch.Tensor | None = None) -> torch.Tensor:
+    """out = x @ y (or x @ y.T), bf16 operands, f32 accumulation, by tiles of (tm, tn). With tile tables only the
+    listed tiles are computed and the fill tiles are zeroed; other tiles of `out` are left as they are."""
+    device = _need_cuda(x, y)
+    if x.dtype != torch.bfloat16 or y.dtype != torch.bfloat16:
+        raise ValueError("x and y must be bfloat16")
+    M, K = x.shape
+    N = y.shape[0] if y_transposed else y.shape[1]
+    if (y.shape[1] if y_transposed else y.shape[0]) != K:
+        raise ValueError("x and y do not share their reduction dimension")
+    out_dtype = torch.bfloat16 if out_dtype is None else out_dtype
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("the output is bfloat16 or float32")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=device)
+    elif out.shape != (M, N) or out.dtype != out_dtype or not out.is_contiguous() or out.device != device:
+        raise ValueError("out has the wrong shape, dtype or layout")
+    n_tiles = 0 if tile_i is None else int(tile_i.numel())
+    n_fills = 0 if fill_i is None else int(fill_i.numel())
+    with torch.cuda.device(device):
+        check(library().tjx_gemm_bf16(_ptr(x), _ptr(y), _ptr(out), M, N, K, int(y_transposed), tm, tn, tk, stages,
+                                      int(out_dtype == torch.float32), int(causal), _ptr(tile_i), _ptr(tile_j),
+                                      n_tiles, _ptr(fill_i), _ptr(fill_j), n_fills, _stream()))
+    return out
+
+
+def matmul(x: torch.Tensor, y: torch.Tensor, tm: int = 512, tn: int = 512, tk: int = 512, **kw) -> torch.Tensor:
+    """The `matmul` loop nest (examples/matmul.py:22-35): tiles clipped to the matrix as its prologue does."""
+    M, K = x.shape
+    N = y.shape[1]
+    return gemm(x, y, min(tm, M), min(tn, N), min(tk, K), **kw)
+
+
+def causal_matmul(x: torch.Tensor, y: torch.Tensor, tm: int = 512, tn: int = 512, tk: int = 512, **kw) -> torch.Tensor:
+    """The `causal_matmul` loop nest (examples/causal_matmul.py:23-40): tril(x @ y); tiles wholly above the
+    diagonal are never loaded or multiplied, only written with zeros."""
+    M, K = x.shape
+    N = y.shape[1]
+    tm, tn, tk = min(tm, M), min(tn, N), min(tk, K)
+    sch = _schedule.causal_matmul_schedule(M, N, K, tm, tn, tk)
+    tables = {}
+    for name, values in sch.tables.items():
+        tables[name] = device_table(("causal_matmul", M, N, tm, tn, name), values, x.device)
+    return gemm(x, y, tm, tn, tk, causal=True, **tables, **kw)
+
+
+# ------------------------------------------------------------------------------------------ attention
+
+
+def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, block_q: int = 512, block_kv: int = 512,
+                     out: torch.Tensor | None = None) -> torch.Tensor:
+    """The `causal_attention` loop nest (examples/causal_attention.py:37-63); q pre-scaled by the caller."""
+    device = _need_cuda(q, k, v)
+    B, H, S, D = q.shape
+    if k.shape != q.shape or v.shape != q.shape:
+        raise ValueError("q, k, v must have the same shape (B, H, S, D)")
+    if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
+        raise ValueError("q, k, v must be bfloat16")
+    bq, bk = min(block_q, S), min(block_kv, S)
+    sch = _schedule.causal_attention_schedule(B, H, S, bq, bk)
+    if sch.step_tables:
+        step_tile = device_table(("attn", S, bq, bk, "tile"), sch.tables["step_tile"], device)
+        step_code = device_table(("attn", S, bq, bk, "code"), sch.tables["step_code"], device)
+    else:  # a single block: one tile, one step, first and last
+        step_tile = device_table(("attn1", "tile"), np.zeros(1, np.int32), device)
+        step_code = device_table(("attn1", "code"), np.array([3], np.int32), device)
+    if out is None:
+        out = torch.empty_like(q)
+    with torch.cuda.device(device):
+        check(library().tjx_causal_attention_bf16(_ptr(q), _ptr(k), _ptr(v), _ptr(out), B, H, S, D, bq, bk,
+                                                  _ptr(step_tile), _ptr(step_code), sch.pattern_steps,
+                                                  sch.pattern_tiles, _stream()))
+    return out
+
+
+# ------------------------------------------------------------------------------------------ decode
+
+
+@lru_cache(maxsize=None)
+def _decode_workspace_bytes(B: int, H: int, D: int, pages: int) -> int:
+    return int(library().tjx_paged_gqa_decode_workspace_bytes(B, H, D, pages))
+
+
+class DecodeBuffers:
+    """The step tables and scratch one `paged_gqa_decode` call fills; reusable across calls of the same sizes."""
+
+    def __init__(self, B: int, H: int, D: int, pages_per_seq: int, device: torch.device):
+        n = B * pages_per_seq
+        self.key = (B, H, D, pages_per_seq, str(device))
+        self.step_tile = torch.empty(n, dtype=torch.int32, device=device)
+        self.step_code = torch.empty(n, dtype=torch.int32, device=device)
+        self.step_count = torch.empty(1, dtype=torch.int32, device=device)
+        self.tile_first = torch.empty(B + 1, dtype=torch.int32, device=device)
+        self.workspace_bytes = _decode_workspace_bytes(B, H, D, pages_per_seq)
+        self.workspace = torch.empty(self.workspace_bytes + 256, dtype=torch.uint8, device=device)
+
+    def workspace_ptr(self) -> int:
+        return (self.workspace.data_ptr() + 255) & ~255
+
+
+def paged_gqa_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_tables: torch.Tensor,
+                     lengths: torch.Tensor, out: torch.Tensor | None = None,
+                     buffers: DecodeBuffers | None = None) -> torch.Tensor:
+    """The `paged_gqa_decode` loop nest (examples/decode.py:199-223) for one new token per sequence. The step
+    tables the call built on the device are left in `buffers` (pass one to inspect or reuse them)."""
+    device = _need_cuda(q, k_pages, v_pages, block_tables, lengths)
+    B, T, H, D = q.shape
+    if T != 1:
+        raise ValueError("one new token per sequence (T = 1)")
+    num_pages, page_size, W = k_pages.shape
+    if v_pages.shape != k_pages.shape or W % D != 0:
+        raise ValueError("k_pages and v_pages must both be (num_pages, page_size, Hkv * D)")
+    if block_tables.dtype != torch.int32 or lengths.dtype != torch.int32:
+        raise ValueError("block_tables and lengths must be int32")
+    if block_tables.shape[0] != B or lengths.shape != (B,):
+        raise ValueError("block_tables is (B, pages_per_seq) and lengths (B,)")
+    Hkv = W // D
+    pages_per_seq = block_tables.shape[1]
+    if buffers is None or buffers.key != (B, H, D, pages_per_seq, str(device)):
+        buffers = DecodeBuffers(B, H, D, pages_per_seq, device)
+    if out is None:
+        out = torch.empty_like(q)
+    with torch.cuda.device(device):
+        check(library().tjx_paged_gqa_decode_bf16(
+            _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_tables), _ptr(lengths), _ptr(out), B, H, Hkv, D,
+            page_size, pages_per_seq, num_pages, _ptr(buffers.step_tile), _ptr(buffers.step_code),
+            _ptr(buffers.step_count), _ptr(buffers.tile_first), ctypes.c_void_p(buffers.workspace_ptr()),
+            buffers.workspace_bytes, _stream()))
+    paged_gqa_decode.last_buffers = buffers
+    return out
