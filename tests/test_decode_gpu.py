@@ -1,0 +1,88 @@
+"""Ragged paged GQA decode through the C ABI against the oracle (`paged_gqa_decode`, examples/decode.py:199-223).
+
+Tolerance: atol 2e-2 * max|want| (tests/test_decode.py:168-169); the step tables the call built are bit-exact.
+"""
+
+import numpy as np
+import pytest
+from helpers import f64, rand_bf16, to_device, to_host
+
+import oracle
+from tilejax_b200 import ops, synthetic
+from tilejax_b200._lib import NativeError
+
+pytestmark = pytest.mark.gpu
+
+
+def run_decode(q, kp, vp, bt, lengths):
+    out = ops.paged_gqa_decode(*map(to_device, (q, kp, vp, bt, lengths)))
+    assert ops.device_status() == 0
+    bufs = ops.paged_gqa_decode.last_buffers
+    P, pages = kp.shape[1], bt.shape[1]
+    tile, code, count = oracle.device_step_tables(oracle.lengths_runs(lengths, pages, 0, P))
+    np.testing.assert_array_equal(to_host(bufs.step_tile), tile)
+    np.testing.assert_array_equal(to_host(bufs.step_code), code)
+    assert int(bufs.step_count[0]) == int(count[0])
+    return to_host(out)
+
+
+def close(got, want, tol=2e-2):
+    assert np.abs(f64(got) - f64(want)).max() <= tol * max(np.abs(f64(want)).max(), 1e-6)
+
+
+@pytest.mark.parametrize(("heads", "kv_heads", "page"), [(8, 2, 16), (8, 2, 128), (4, 4, 64), (16, 8, 16), (8, 1, 32)])
+def test_ragged_lengths_match_the_oracle(heads, kv_heads, page):
+    # The reference's ragged case (tests/test_decode.py:163-165): empty, one token, a partial block, full.
+    pages = 512 // page
+    q, kp, vp, bt, lengths = synthetic.decode_inputs(4, heads, kv_heads, 128, page, pages, 4 * pages,
+                                                     distinct_pages=True)
+    lengths[:] = [0, 1, 300, 512]
+    got = run_decode(q, kp, vp, bt, lengths)
+    close(got, oracle.paged_gqa_decode_ref(q, kp, vp, bt, lengths))
+    close(got, oracle.paged_gqa_decode_f64(q, kp, vp, bt, lengths))
+    assert not f64(got[0]).any()  # the empty sequence
+
+
+def test_benchmark_configuration_matches_the_oracle():
+    # BASELINE config 4: batch 64, 32 / 8 heads, D 128, 16-token pages, 8192 pages, lengths in [1, 4096].
+    q, kp, vp, bt, lengths = synthetic.decode_inputs(64, 32, 8, 128, 16, 256, 8192)
+    got = run_decode(q, kp, vp, bt, lengths)
+    close(got, oracle.paged_gqa_decode_ref(q, kp, vp, bt, lengths))
+
+
+def test_out_of_range_pages_are_clamped():
+    q, kp, vp, bt, lengths = synthetic.decode_inputs(3, 8, 2, 128, 16, 8, 24)
+    lengths[:] = [128, 17, 64]
+    bad = bt.copy()
+    bad[0, 1], bad[1, 0] = 9999, -5
+    fixed = bt.copy()
+    fixed[0, 1], fixed[1, 0] = 23, 0
+    np.testing.assert_array_equal(f64(run_decode(q, kp, vp, bad, lengths)), f64(run_decode(q, kp, vp, fixed, lengths)))
+
+
+def test_paged_equals_the_same_cache_laid_out_in_order():
+    # tests/test_decode.py:209: paging is only a layout; the result is bit-equal.
+    B, S, P = 3, 256, 16
+    k, v = rand_bf16((B, S, 256), 1), rand_bf16((B, S, 256), 2)
+    q = rand_bf16((B, 1, 8, 128), 3, 128**-0.5)
+    lengths = np.array([5, 100, 256], np.int32)
+    order = np.random.default_rng(1).permutation(B * S // P).reshape(B, S // P).astype(np.int32)
+    ident = np.arange(B * S // P, dtype=np.int32).reshape(B, S // P)
+    a = run_decode(q, oracle.to_pages(k, order), oracle.to_pages(v, order), order, lengths)
+    b = run_decode(q, oracle.to_pages(k, ident), oracle.to_pages(v, ident), ident, lengths)
+    np.testing.assert_array_equal(f64(a), f64(b))
+
+
+def test_all_sequences_empty():
+    q, kp, vp, bt, lengths = synthetic.decode_inputs(5, 8, 2, 128, 16, 4, 20)
+    lengths[:] = 0
+    assert not f64(run_decode(q, kp, vp, bt, lengths)).any()
+
+
+def test_unsupported_shapes_are_errors():
+    q, kp, vp, bt, lengths = synthetic.decode_inputs(2, 8, 2, 128, 8, 4, 8)
+    with pytest.raises(NativeError, match="multiple of 16"):
+        ops.paged_gqa_decode(*map(to_device, (q, kp, vp, bt, lengths)))
+    q, kp, vp, bt, lengths = synthetic.decode_inputs(2, 6, 2, 128, 16, 4, 8)
+    with pytest.raises(NativeError, match="1, 2, 4 or 8"):
+        ops.paged_gqa_decode(*map(to_device, (q, kp, vp, bt, lengths)))
