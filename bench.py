@@ -272,7 +272,7 @@ def extra_workloads(device, pk: dict, pk_kind: str) -> dict:
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--steps", type=int, default=100)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-extras", action="store_true", help="skip the other single-GPU workloads and the CPU baseline")
@@ -315,10 +315,10 @@ def main() -> None:
         torch.cuda.synchronize()
 
     # ---- device-resident timing
+    sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(device).uuid).replace("GPU-", "")) if rank == 0 else None
     for _ in range(args.warmup):
         op(x, y)
     barrier()
-    sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(device).uuid).replace("GPU-", "")) if rank == 0 else None
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(args.steps):
@@ -332,7 +332,6 @@ def main() -> None:
 
     # ---- the dominant kernel alone (its launches, timed on their stream): the roofline's numerator
     gemm_ms = time_device(lambda: ops.gemm(op.exchange.xs, y, op.tm, op.tn, op.tk, out=op.out), args.steps, 1)
-    clocks = sampler.stop() if sampler else None
     ops.device_status()
 
     # ---- end to end: host buffers in, host result out, copies inside the timed region
@@ -354,6 +353,7 @@ def main() -> None:
     if world > 1:
         dist.all_reduce(e2e_elapsed, op=dist.ReduceOp.MAX)
     e2e_ms = e2e_elapsed.item() / e2e_steps
+    clocks = sampler.stop() if sampler else None  # sampled over the device-timed, kernel-alone and e2e regions
 
     flops_per_gpu = 2.0 * M_TOTAL * K_DIM * N_DIM
     value = world * flops_per_gpu / ms_per_step / 1e9

@@ -1,9 +1,414 @@
-// Placeholder until the attention kernel lands: the symbol exists so the library matches its header.
+// Flash-style causal attention on sm_100a: the step loop of `causal_attention`
+// (examples/causal_attention.py:37-63) with the scores and the output accumulator in TMEM.
+//
+// A CTA owns one (b, h) and two consecutive query tiles of 128 rows ("slots" A and B), and walks the key/value
+// blocks the step table lists for them in sub-blocks of 128 keys; a sub-block wholly in the future of a slot's
+// rows is skipped for that slot (its probabilities would all be exp(-1e30 - max) = 0). Both slots share every
+// K / V load.
+//
+//   warp 0      producer: TMA loads Q (both slots, once), then K and V sub-blocks into two 2-slot rings
+//   warp 1      MMA issuer (one thread): S_t = Q_t K^T into TMEM, then O_t += P_t V with P_t read from TMEM
+//   warps 2-5   softmax of slot A, warps 6-9 of slot B: a thread owns one query row — tcgen05.ld its 128
+//               scores, running max / sum in f32 registers, exp2, P rounded to bf16 and stored back to TMEM over
+//               the scores; rescales O in TMEM when the running max grows; at the end normalises O and stores
+//               it through shared memory with TMA
+//
+// TMEM (512 columns): S_A | S_B | O_A | O_B, 128 f32 columns each; P_t (bf16, two per column) overlays the
+// first 64 columns of S_t. While one slot's softmax runs, the tensor core works on the other slot.
+//
+// Numerics follow the reference: q arrives pre-scaled; scores in f32 from bf16 operands; masked scores are
+// -1e30; the row sum adds the unrounded probabilities while P is rounded to bf16 before P @ V; one division at
+// the end. The running max is only raised when a block's max exceeds it by more than 8 (in log2 units), which
+// changes no result beyond rounding: every term is scaled by the same power of two.
 #include "tjx_host.cuh"
+#include "tjx_ptx.cuh"
 
 #include "../../include/tilejax_b200.h"
 
-extern "C" int tjx_causal_attention_bf16(const void*, const void*, const void*, void*, int, int, int, int, int, int,
-                                         const int32_t*, const int32_t*, int, int, tjx_stream_t) {
-  return tjx::fail(TJX_E_ARG, "tjx_causal_attention_bf16 is not built in this revision");
+namespace tjx {
+
+constexpr int AT_D = 128;
+constexpr int AT_BQ = 128;   // query rows per slot
+constexpr int AT_BKV = 128;  // keys per sub-block
+constexpr int AT_STAGES = 2;
+constexpr int AT_THREADS = 320;
+constexpr float AT_LOG2E = 1.4426950408889634f;
+constexpr float AT_MASK = -1e30f;
+constexpr float AT_RESCALE_THRESHOLD = 8.0f;
+
+struct AttnParams {
+  int B, H, S;
+  int bq, bk;  // the user's blocks
+  int pattern_steps, pattern_tiles;
+  const int32_t* step_tile;
+  const int32_t* step_code;
+  int units_per_bh;  // pairs of 128-row query tiles per (b, h)
+  int* status;
+};
+
+struct AttnSmem {
+  static constexpr int TILE_BYTES = 128 * 128 * 2;  // a 128 x 128 bf16 tile: two 64-column boxes of 16 KB
+  static constexpr int Q_OFF = 0;                    // 2 slots
+  static constexpr int K_OFF = 2 * TILE_BYTES;       // AT_STAGES
+  static constexpr int V_OFF = K_OFF + AT_STAGES * TILE_BYTES;
+  static constexpr int BAR_OFF = V_OFF + AT_STAGES * TILE_BYTES;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Keys a slot's rows [q0, q0 + 128) attend to, as a count of 128-key sub-blocks from key 0: what the step table
+// lists for the user tile holding q0 (blocks 0 .. last, contiguous), cut at the slot's own diagonal.
+__device__ __forceinline__ int slot_blocks(const AttnParams& p, int q0) {
+  if (q0 >= p.S) return 0;
+  const int tile = q0 / p.bq;
+  int last_block = -1;
+  for (int s = 0; s < p.pattern_steps; ++s)
+    if (p.step_tile[s] == tile && !(p.step_code[s] & 4)) last_block = max(last_block, p.step_code[s] >> 3);
+  const int keys = min(min((last_block + 1) * p.bk, q0 + AT_BQ), p.S);
+  return keys / AT_BKV;
+}
+
+__global__ void __launch_bounds__(AT_THREADS, 1)
+    attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
+                     const AttnParams p) {
+  using L = AttnSmem;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bar_base = base + L::BAR_OFF;
+  // barriers: q_full[2], k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2], o_done[2]
+  auto q_full = [&](int t) { return bar_base + 8u * t; };
+  auto k_full = [&](int s) { return bar_base + 8u * (2 + s); };
+  auto k_empty = [&](int s) { return bar_base + 8u * (4 + s); };
+  auto v_full = [&](int s) { return bar_base + 8u * (6 + s); };
+  auto v_empty = [&](int s) { return bar_base + 8u * (8 + s); };
+  auto s_full = [&](int t) { return bar_base + 8u * (10 + t); };
+  auto p_ready = [&](int t) { return bar_base + 8u * (12 + t); };
+  auto o_done = [&](int t) { return bar_base + 8u * (14 + t); };
+  volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(base_ptr + L::BAR_OFF + 8 * 16);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + L::BAR_OFF + 8 * 16 + 8);
+  volatile int* blocks_sh = reinterpret_cast<volatile int*>(base_ptr + L::BAR_OFF + 8 * 16 + 16);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // Work unit: heaviest first (later query tiles attend to more keys).
+  const int bh_count = p.B * p.H;
+  const int unit = p.units_per_bh - 1 - static_cast<int>(blockIdx.x) / bh_count;
+  const int bh = static_cast<int>(blockIdx.x) % bh_count;
+  const int q0_slot[2] = {unit * 2 * AT_BQ, unit * 2 * AT_BQ + AT_BQ};
+  const int row_base = bh * p.S;  // row of (b, h, 0) in the [B * H * S, D] view
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 16; ++i) {
+      const bool softmax_bar = i == 12 || i == 13;  // p_ready: one arrival per softmax warp
+      mbar_init(bar_base + 8u * i, softmax_bar ? 4 : 1);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&map_q);
+    tma_prefetch_desc(&map_k);
+    tma_prefetch_desc(&map_v);
+    tma_prefetch_desc(&map_o);
+  }
+  if (threadIdx.x < 2) blocks_sh[threadIdx.x] = slot_blocks(p, q0_slot[threadIdx.x]);
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_holder)), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+  const int n_slot[2] = {blocks_sh[0], blocks_sh[1]};
+  const int n_blocks = max(n_slot[0], n_slot[1]);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      for (int t = 0; t < 2; ++t) {
+        if (n_slot[t] == 0) continue;
+        const uint32_t dst = base + L::Q_OFF + t * L::TILE_BYTES;
+        mbar_expect_tx(q_full(t), L::TILE_BYTES);
+        tma_load_2d(dst, &map_q, 0, row_base + q0_slot[t], q_full(t));
+        tma_load_2d(dst + L::TILE_BYTES / 2, &map_q, 64, row_base + q0_slot[t], q_full(t));
+      }
+      for (int n = 0; n < n_blocks; ++n) {
+        const int stage = n % AT_STAGES;
+        const uint32_t ph = (n / AT_STAGES) & 1;
+        const int kv_row = row_base + n * AT_BKV;
+        if (!mbar_wait(k_empty(stage), ph ^ 1u, abort_flag, p.status, TJX_ERR_WAIT_EMPTY)) break;
+        const uint32_t kd = base + L::K_OFF + stage * L::TILE_BYTES;
+        mbar_expect_tx(k_full(stage), L::TILE_BYTES);
+        tma_load_2d(kd, &map_k, 0, kv_row, k_full(stage));
+        tma_load_2d(kd + L::TILE_BYTES / 2, &map_k, 64, kv_row, k_full(stage));
+        if (!mbar_wait(v_empty(stage), ph ^ 1u, abort_flag, p.status, TJX_ERR_WAIT_EMPTY)) break;
+        const uint32_t vd = base + L::V_OFF + stage * L::TILE_BYTES;
+        mbar_expect_tx(v_full(stage), L::TILE_BYTES);
+        tma_load_2d(vd, &map_v, 0, kv_row, v_full(stage));
+        tma_load_2d(vd + L::TILE_BYTES / 2, &map_v, 64, kv_row, v_full(stage));
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_qk = idesc_bf16_f32(128, 128, 0, 0);  // Q and K both K-major (K read "transposed")
+      const uint32_t idesc_pv = idesc_bf16_f32(128, 128, 0, 1);  // P from TMEM, V MN-major
+      auto issue_qk = [&](int t, int n) {
+        const int stage = n % AT_STAGES;
+        const uint32_t qa = base + L::Q_OFF + t * L::TILE_BYTES;
+        const uint32_t ka = base + L::K_OFF + stage * L::TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < AT_D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * (L::TILE_BYTES / 2) + (kk & 3) * 32;
+          mma_ss(tmem_base + t * 128, smem_desc_sw128(qa + off, 16, 1024), smem_desc_sw128(ka + off, 16, 1024),
+                 idesc_qk, kk != 0 ? 1u : 0u);
+        }
+        mma_commit(s_full(t));
+      };
+      auto issue_pv = [&](int t, int n) {
+        const int stage = n % AT_STAGES;
+        const uint32_t va = base + L::V_OFF + stage * L::TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < AT_BKV / 16; ++kk)
+          mma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + kk * 8,
+                 smem_desc_sw128(va + kk * (16 * 128), L::TILE_BYTES / 2, 1024), idesc_pv, (n | kk) != 0 ? 1u : 0u);
+        mma_commit(o_done(t));
+      };
+      bool ok = true;
+      for (int t = 0; t < 2 && ok; ++t)
+        if (n_slot[t] > 0) ok = mbar_wait(q_full(t), 0, abort_flag, p.status, TJX_ERR_WAIT_FULL);
+      if (ok && n_blocks > 0) {
+        ok = mbar_wait(k_full(0), 0, abort_flag, p.status, TJX_ERR_WAIT_FULL);
+        if (ok) {
+          tc_fence_after_sync();
+          for (int t = 0; t < 2; ++t)
+            if (n_slot[t] > 0) issue_qk(t, 0);
+          mma_commit(k_empty(0));
+        }
+      }
+      for (int n = 0; n < n_blocks && ok; ++n) {
+        const int stage = n % AT_STAGES;
+        const uint32_t ph = (n / AT_STAGES) & 1;
+        if (!mbar_wait(v_full(stage), ph, abort_flag, p.status, TJX_ERR_WAIT_FULL)) break;
+        bool next_k_waited = false, next_k_used = false;
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (n >= n_slot[t]) continue;
+          if (!mbar_wait(p_ready(t), n & 1, abort_flag, p.status, TJX_ERR_WAIT_OTHER)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          issue_pv(t, n);
+          if (n + 1 < n_slot[t]) {
+            if (!next_k_waited) {
+              const int ns = (n + 1) % AT_STAGES;
+              if (!mbar_wait(k_full(ns), ((n + 1) / AT_STAGES) & 1, abort_flag, p.status, TJX_ERR_WAIT_FULL)) {
+                ok = false;
+                break;
+              }
+              tc_fence_after_sync();
+              next_k_waited = true;
+            }
+            issue_qk(t, n + 1);
+            next_k_used = true;
+          }
+        }
+        if (!ok) break;
+        mma_commit(v_empty(stage));
+        if (next_k_used) mma_commit(k_empty((n + 1) % AT_STAGES));
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ softmax / correction / epilogue
+    const int t = (warp - 2) >> 2;  // slot
+    const int q = warp & 3;         // TMEM lane quarter
+    const int n_mine = n_slot[t];
+    const int q0 = q0_slot[t];
+    const int row = q0 + q * 32 + lane;  // query position of this thread's row
+    const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    const uint32_t s_tmem = tmem_base + lane_addr + t * 128;
+    const uint32_t o_tmem = tmem_base + lane_addr + 256 + t * 128;
+    float m_used = AT_MASK * AT_LOG2E;  // running max, in log2 units
+    float l = 0.f;
+    bool ok = true;
+    for (int n = 0; n < n_mine; ++n) {
+      const bool got = mbar_wait(s_full(t), n & 1, abort_flag, p.status, TJX_ERR_WAIT_TMEM_FULL);
+      if (!__all_sync(0xFFFFFFFFu, got)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const int kv0 = n * AT_BKV;
+      const bool diagonal = kv0 + AT_BKV - 1 > q0;  // some key of the block is in some row's future
+      // Pass 1: the block's row max.
+      float mx = AT_MASK;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(s_tmem + c * 32, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float s = __uint_as_float(v[j]);
+          if (diagonal && kv0 + c * 32 + j > row) s = AT_MASK;
+          mx = fmaxf(mx, s);
+        }
+      }
+      const float m_blk = mx * AT_LOG2E;
+      if (n == 0) {
+        m_used = m_blk;
+      } else if (__any_sync(0xFFFFFFFFu, m_blk > m_used + AT_RESCALE_THRESHOLD)) {
+        // Raise the running max and rescale what has been accumulated. P V of the previous block finished
+        // before this block's scores were produced (the tensor pipe runs one thread's MMAs in order).
+        const float m_new = fmaxf(m_used, m_blk);
+        const float alpha = fast_exp2(m_used - m_new);
+        m_used = m_new;
+        l *= alpha;
+        const bool od = mbar_wait(o_done(t), (n - 1) & 1, abort_flag, p.status, TJX_ERR_WAIT_OTHER);
+        if (!__all_sync(0xFFFFFFFFu, od)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld32(o_tmem + c * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
+          tmem_st32(o_tmem + c * 32, v);
+        }
+        tmem_wait_st();
+      }
+      // Pass 2: probabilities; P (bf16) overwrites the scores already consumed.
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(s_tmem + c * 32, v);
+        tmem_wait_ld();
+        uint32_t pk[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          float s0 = __uint_as_float(v[j]), s1 = __uint_as_float(v[j + 1]);
+          if (diagonal) {
+            if (kv0 + c * 32 + j > row) s0 = AT_MASK;
+            if (kv0 + c * 32 + j + 1 > row) s1 = AT_MASK;
+          }
+          const float p0 = fast_exp2(fmaf(s0, AT_LOG2E, -m_used));
+          const float p1 = fast_exp2(fmaf(s1, AT_LOG2E, -m_used));
+          l += p0 + p1;
+          pk[j >> 1] = pack_bf16(p0, p1);
+        }
+        tmem_st16(s_tmem + c * 16, pk);
+      }
+      tmem_wait_st();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_ready(t));
+    }
+    if (ok && n_mine > 0) {
+      // Epilogue: O / l -> bf16 -> shared memory (over this slot's Q tile, no longer read) -> TMA store.
+      const bool od = mbar_wait(o_done(t), (n_mine - 1) & 1, abort_flag, p.status, TJX_ERR_WAIT_OTHER);
+      if (__all_sync(0xFFFFFFFFu, od)) {
+        tc_fence_after_sync();
+        const float inv = 1.0f / l;
+        uint8_t* stage_ptr = base_ptr + L::Q_OFF + t * L::TILE_BYTES;
+        const int r = q * 32 + lane;  // row within the tile
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld32(o_tmem + c * 32, v);
+          tmem_wait_ld();
+          uint8_t* half_ptr = stage_ptr + (c >> 1) * (L::TILE_BYTES / 2) + r * 128;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 val;
+            val.x = pack_bf16(__uint_as_float(v[8 * u + 0]) * inv, __uint_as_float(v[8 * u + 1]) * inv);
+            val.y = pack_bf16(__uint_as_float(v[8 * u + 2]) * inv, __uint_as_float(v[8 * u + 3]) * inv);
+            val.z = pack_bf16(__uint_as_float(v[8 * u + 4]) * inv, __uint_as_float(v[8 * u + 5]) * inv);
+            val.w = pack_bf16(__uint_as_float(v[8 * u + 6]) * inv, __uint_as_float(v[8 * u + 7]) * inv);
+            const int unit16 = (c & 1) * 4 + u;
+            *reinterpret_cast<uint4*>(half_ptr + ((unit16 ^ (r & 7)) << 4)) = val;
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          const uint32_t src = base + L::Q_OFF + t * L::TILE_BYTES + q * 32 * 128;
+          tma_store_2d(&map_o, src, 0, row_base + q0 + q * 32);
+          tma_store_2d(&map_o, src + L::TILE_BYTES / 2, 64, row_base + q0 + q * 32);
+          tma_store_commit();
+          tma_store_wait_all<0>();
+        }
+        __syncwarp();
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    if (*abort_flag) __nanosleep(100000);
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace tjx
+
+extern "C" int tjx_causal_attention_bf16(const void* q, const void* k, const void* v, void* out, int B, int H, int S,
+                                         int D, int block_q, int block_kv, const int32_t* step_tile,
+                                         const int32_t* step_code, int pattern_steps, int pattern_tiles,
+                                         tjx_stream_t stream) {
+  using namespace tjx;
+  if (int rc = check_device()) return rc;
+  if (!q || !k || !v || !out) return fail(TJX_E_ARG, "q, k, v or out is null");
+  if (!step_tile || !step_code || pattern_steps <= 0 || pattern_tiles <= 0)
+    return fail(TJX_E_ARG, "the step tables are missing");
+  if (B <= 0 || H <= 0 || S <= 0) return fail(TJX_E_ARG, "sizes must be positive");
+  if (D != AT_D) return fail(TJX_E_ARG, "head dimension must be 128");
+  if (S % 128 != 0) return fail(TJX_E_ARG, "S must be a multiple of 128");
+  if (block_q <= 0 || block_kv <= 0 || block_q % 128 != 0 || block_kv % 128 != 0 || S % block_q != 0 || S % block_kv != 0)
+    return fail(TJX_E_ARG, "block_q and block_kv must be multiples of 128 that divide S");
+  if (pattern_tiles != S / block_q) return fail(TJX_E_ARG, "pattern_tiles must be S / block_q");
+  if (static_cast<long long>(B) * H * S >= (1ll << 31)) return fail(TJX_E_LIMIT, "B * H * S must fit in int32");
+
+  AttnParams p{};
+  p.B = B, p.H = H, p.S = S, p.bq = block_q, p.bk = block_kv;
+  p.pattern_steps = pattern_steps, p.pattern_tiles = pattern_tiles;
+  p.step_tile = step_tile, p.step_code = step_code;
+  p.units_per_bh = (S / AT_BQ + 1) / 2;
+  p.status = device_status_word();
+  if (p.status == nullptr) return fail(TJX_E_CUDA, "could not allocate the device status word");
+
+  const uint64_t dims[2] = {static_cast<uint64_t>(D), static_cast<uint64_t>(B) * H * S};
+  const uint64_t strides[1] = {static_cast<uint64_t>(D) * 2};
+  const uint32_t box_in[2] = {64, 128};
+  const uint32_t box_out[2] = {64, 32};
+  CUtensorMap mq, mk, mv, mo;
+  if (int rc = make_tensor_map(&mq, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 2, dims, strides, box_in, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+  if (int rc = make_tensor_map(&mk, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 2, dims, strides, box_in, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+  if (int rc = make_tensor_map(&mv, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 2, dims, strides, box_in, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+  if (int rc = make_tensor_map(&mo, out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 2, dims, strides, box_out, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+
+  static bool configured[64] = {};
+  int dev = 0;
+  TJX_CUDA(cudaGetDevice(&dev));
+  if (!configured[dev & 63]) {
+    TJX_CUDA(cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem::TOTAL));
+    configured[dev & 63] = true;
+  }
+  const int grid = B * H * p.units_per_bh;
+  attention_kernel<<<grid, AT_THREADS, AttnSmem::TOTAL, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, mo, p);
+  TJX_CUDA(cudaGetLastError());
+  return 0;
 }
