@@ -108,6 +108,31 @@ int tjx_paged_gqa_decode_bf16(const void* q, const void* k_pages, const void* v_
                               int32_t* step_count, int32_t* tile_first, void* workspace, size_t workspace_bytes,
                               tjx_stream_t stream);
 
+/* Bytes of scratch built into the library for tjx_paged_gqa_decode_bf16_static (36 MiB). */
+#define TJX_STATIC_SCRATCH_BYTES (36u * 1024u * 1024u)
+size_t tjx_paged_gqa_decode_static_scratch_bytes(void);
+
+/* tjx_paged_gqa_decode_bf16 for callers that must not allocate device memory and have no scratch buffer of their
+ * own to lend: code running inside a memory pool that is already carved up, a plugin whose host forbids
+ * cudaMalloc after start-up, a serving loop that may not touch the allocator on its hot path. This entry point
+ * has no counterpart in the reference; it exists only for those callers. Same arguments and same results as
+ * tjx_paged_gqa_decode_bf16 minus the workspace: the online-softmax partials go to a fixed 36 MiB array inside the
+ * library instead (every GPU that loads the library holds that array until the process exits). The call itself
+ * performs no cudaMalloc / cudaFree and calls no allocating routine.
+ *   Limit: tjx_paged_gqa_decode_workspace_bytes(B, H, D, pages_per_seq) must not exceed TJX_STATIC_SCRATCH_BYTES
+ *   (for example B 64, H 32, 256 pages per sequence fits); beyond it the call returns TJX_E_LIMIT and runs nothing.
+ *   First call on a device: looks the array's device address up (once per device, with that device current).
+ *   Make that first call outside any stream capture.
+ *   Sharing: all calls on a device use the same array. Nothing in it needs clearing between calls (each call
+ *   writes every partial before reading it), but two calls whose kernels overlap on the GPU — different streams,
+ *   or different host threads on different streams — race on it: keep calls to this entry point on one stream,
+ *   or order them with events. */
+int tjx_paged_gqa_decode_bf16_static(const void* q, const void* k_pages, const void* v_pages,
+                                     const int32_t* block_tables, const int32_t* lengths, void* out, int B, int H,
+                                     int Hkv, int D, int page_size, int pages_per_seq, int num_pages,
+                                     int32_t* step_tile, int32_t* step_code, int32_t* step_count, int32_t* tile_first,
+                                     tjx_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -14,6 +14,9 @@
 #include "tjx_host.cuh"
 #include "tjx_ptx.cuh"
 
+#include <mutex>
+#include <string>
+
 #include "../../include/tilejax_b200.h"
 
 namespace tjx {
@@ -297,6 +300,113 @@ int tjx_paged_gqa_decode_bf16(const void* q, const void* k_pages, const void* v_
   TJX_CUDA(cudaGetLastError());
   const int warps = B * H;
   decode_combine_kernel<<<(warps * 32 + 255) / 256, 256, 0, s>>>(p);
+  TJX_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------------------------------------------------
+// Decode without any allocation by anyone: the partials live in a fixed array inside the library's image.
+
+namespace tjx {
+
+constexpr size_t STATIC_SCRATCH_BYTES = static_cast<size_t>(TJX_STATIC_SCRATCH_BYTES);
+
+// Scratch for tjx_paged_gqa_decode_bf16_static. Every GPU that loads the library carries these 36 MiB until the
+// process exits. In host code this name is only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) unsigned char g_decode_scratch[STATIC_SCRATCH_BYTES];
+
+static void* g_decode_scratch_addr[64];  // per device, filled on the device's first call
+static std::mutex g_decode_scratch_mutex;
+
+// The array's address on the current device, looked up once per device with that device current.
+static int static_scratch_address(void** out) {
+  int dev = 0;
+  TJX_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(TJX_E_ARG, "device ordinal out of range");
+  std::lock_guard<std::mutex> lock(g_decode_scratch_mutex);
+  if (g_decode_scratch_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_decode_scratch);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_decode_scratch)");
+    if (ptr == nullptr) return fail(TJX_E_CUDA, "cudaGetSymbolAddress returned a null address");
+    g_decode_scratch_addr[dev] = ptr;
+  }
+  *out = g_decode_scratch_addr[dev];
+  return 0;
+}
+
+}  // namespace tjx
+
+extern "C" {
+
+size_t tjx_paged_gqa_decode_static_scratch_bytes(void) { return tjx::STATIC_SCRATCH_BYTES; }
+
+int tjx_paged_gqa_decode_bf16_static(const void* q, const void* k_pages, const void* v_pages,
+                                     const int32_t* block_tables, const int32_t* lengths, void* out, int B, int H,
+                                     int Hkv, int D, int page_size, int pages_per_seq, int num_pages,
+                                     int32_t* step_tile, int32_t* step_code, int32_t* step_count, int32_t* tile_first,
+                                     tjx_stream_t stream) {
+  using namespace tjx;
+  if (int rc = check_device()) return rc;
+  if (!q || !k_pages || !v_pages || !block_tables || !lengths || !out)
+    return fail(TJX_E_ARG, "an input or output pointer is null");
+  if (!step_tile || !step_code || !step_count || !tile_first)
+    return fail(TJX_E_ARG, "a step table pointer is null");
+  if (B <= 0 || H <= 0 || Hkv <= 0 || pages_per_seq <= 0 || num_pages <= 0)
+    return fail(TJX_E_ARG, "sizes must be positive");
+  if (D != DEC_D) return fail(TJX_E_ARG, "head dimension must be 128");
+  if (page_size <= 0 || page_size % DEC_SUB != 0) return fail(TJX_E_ARG, "page size must be a multiple of 16");
+  if (H % Hkv != 0) return fail(TJX_E_ARG, "H must be a multiple of Hkv");
+  const int group = H / Hkv;
+  if (group != 1 && group != 2 && group != 4 && group != 8)
+    return fail(TJX_E_ARG, "H / Hkv must be 1, 2, 4 or 8");
+  const size_t need = tjx_paged_gqa_decode_workspace_bytes(B, H, D, pages_per_seq);
+  if (need > STATIC_SCRATCH_BYTES)
+    return fail(TJX_E_LIMIT, "these sizes need " + std::to_string(need) + " bytes of scratch, more than the " +
+                                 std::to_string(STATIC_SCRATCH_BYTES) +
+                                 " bytes built into the library: use tjx_paged_gqa_decode_bf16 with a workspace");
+  const uintptr_t ptrs[] = {reinterpret_cast<uintptr_t>(q), reinterpret_cast<uintptr_t>(k_pages),
+                            reinterpret_cast<uintptr_t>(v_pages), reinterpret_cast<uintptr_t>(out)};
+  for (uintptr_t a : ptrs)
+    if (a & 15u) return fail(TJX_E_ARG, "q, k_pages, v_pages and out must be 16-byte aligned");
+  void* scratch = nullptr;
+  if (int rc = static_scratch_address(&scratch)) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+  if (int rc = launch_build_steps_lengths(lengths, B, nullptr, B, pages_per_seq, 0, page_size, step_tile, step_code,
+                                          step_count, tile_first, s))
+    return rc;
+
+  DecodeParams p{};
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.k_pages = static_cast<const __nv_bfloat16*>(k_pages);
+  p.v_pages = static_cast<const __nv_bfloat16*>(v_pages);
+  p.block_tables = block_tables, p.lengths = lengths;
+  p.step_tile = step_tile, p.step_code = step_code, p.step_count = step_count, p.tile_first = tile_first;
+  p.B = B, p.H = H, p.Hkv = Hkv, p.page_size = page_size, p.pages_per_seq = pages_per_seq, p.num_pages = num_pages;
+  p.slots = decode_slots(pages_per_seq);
+  // Nothing in the scratch has to start at zero: every partial the merge kernel reads was written earlier in
+  // this same call, so whatever the previous call left behind is never looked at.
+  const size_t rows = static_cast<size_t>(B) * p.slots * H;
+  uint8_t* ws = static_cast<uint8_t*>(scratch);
+  p.ws_m = reinterpret_cast<float*>(ws);
+  p.ws_l = reinterpret_cast<float*>(ws + align256(rows * sizeof(float)));
+  p.ws_acc = reinterpret_cast<float*>(ws + 2 * align256(rows * sizeof(float)));
+  p.out = static_cast<__nv_bfloat16*>(out);
+
+  const long long capacity = static_cast<long long>(B) * pages_per_seq;
+  const int chunks = static_cast<int>((capacity + DEC_CHUNK - 1) / DEC_CHUNK);
+  dim3 grid(chunks, (Hkv + DEC_WARPS - 1) / DEC_WARPS);
+  switch (group) {
+    case 1: decode_chunks_kernel<1><<<grid, DEC_WARPS * 32, 0, s>>>(p); break;
+    case 2: decode_chunks_kernel<2><<<grid, DEC_WARPS * 32, 0, s>>>(p); break;
+    case 4: decode_chunks_kernel<4><<<grid, DEC_WARPS * 32, 0, s>>>(p); break;
+    default: decode_chunks_kernel<8><<<grid, DEC_WARPS * 32, 0, s>>>(p); break;
+  }
+  TJX_CUDA(cudaGetLastError());
+  decode_combine_kernel<<<(B * H * 32 + 255) / 256, 256, 0, s>>>(p);
   TJX_CUDA(cudaGetLastError());
   return 0;
 }

@@ -231,3 +231,26 @@ def paged_gqa_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
             buffers.workspace_bytes, _stream()))
     paged_gqa_decode.last_buffers = buffers
     return out
+
+
+def paged_gqa_decode_static(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_tables: torch.Tensor,
+                            lengths: torch.Tensor, out: torch.Tensor, step_tile: torch.Tensor, step_code: torch.Tensor,
+                            step_count: torch.Tensor, tile_first: torch.Tensor) -> torch.Tensor:
+    """`paged_gqa_decode` for a caller that may not allocate: every buffer, the output and the step tables
+    included, is passed in, and the kernels' scratch is the fixed array inside the library
+    (tjx_paged_gqa_decode_bf16_static). This wrapper allocates nothing either. Sizes whose scratch would exceed
+    the built-in 36 MiB raise; calls that overlap on the GPU race on the shared scratch."""
+    device = _need_cuda(q, k_pages, v_pages, block_tables, lengths, out, step_tile, step_code, step_count, tile_first)
+    B, T, H, D = q.shape
+    if T != 1:
+        raise ValueError("one new token per sequence (T = 1)")
+    num_pages, page_size, W = k_pages.shape
+    pages_per_seq = block_tables.shape[1]
+    if step_tile.numel() < B * pages_per_seq or step_code.numel() < B * pages_per_seq or tile_first.numel() < B + 1:
+        raise ValueError("the step table buffers are too small")
+    with torch.cuda.device(device):
+        check(library().tjx_paged_gqa_decode_bf16_static(
+            _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_tables), _ptr(lengths), _ptr(out), B, H, W // D, D,
+            page_size, pages_per_seq, num_pages, _ptr(step_tile), _ptr(step_code), _ptr(step_count),
+            _ptr(tile_first), _stream()))
+    return out
