@@ -208,8 +208,9 @@ def workload_name(n: int) -> str:
 # ----------------------------------------------------------------------------------------- extra workloads
 
 
-def extra_workloads(device, pk: dict, pk_kind: str) -> dict:
-    """The other BASELINE configs at one GPU, device-timed with an L2 flush before every run."""
+def extra_workloads(device, pk: dict, pk_kind: str, only: str | None = None, iters: int = 10, warm: int = 3) -> dict:
+    """The other BASELINE configs at one GPU, device-timed with an L2 flush before every run. `only` keeps the
+    workloads whose name contains it (for profiling one kernel with few launches)."""
     import torch
 
     from tilejax_b200 import ops, synthetic
@@ -218,6 +219,7 @@ def extra_workloads(device, pk: dict, pk_kind: str) -> dict:
     flush = lambda: flush_buf.zero_()  # noqa: E731
     tf_peak, hbm_peak = pk["bf16_tflops"], pk["hbm_gbs"]
     out = {}
+    want = lambda name: only is None or only in name  # noqa: E731
 
     def tensor_entry(name, ms, flops, extra=None):
         tf = flops / ms / 1e9
@@ -228,34 +230,45 @@ def extra_workloads(device, pk: dict, pk_kind: str) -> dict:
             out[name].update(extra)
 
     for n in (4096, 8192):
+        if not (want(f"dense_matmul_{n}") or (n == 8192 and want("causal_matmul"))):
+            continue
         x = device_randn_bf16((n, n), 0, device)
         y = device_randn_bf16((n, n), 1, device)
-        ms = time_device(lambda: ops.matmul(x, y, 512, 512, 512), 10, 3, flush)
-        tensor_entry(f"dense_matmul_{n}_tiles512", ms, 2.0 * n**3)
+        if want(f"dense_matmul_{n}"):
+            ms = time_device(lambda: ops.matmul(x, y, 512, 512, 512), iters, warm, flush)
+            tensor_entry(f"dense_matmul_{n}_tiles512", ms, 2.0 * n**3)
         if n == 8192:
             for tiles in ((512, 512, 512), (1024, 2048, 1024)):
-                ms = time_device(lambda: ops.causal_matmul(x, y, *tiles), 10, 3, flush)
-                tensor_entry(f"causal_matmul_8192_tiles{tiles[0]}x{tiles[1]}x{tiles[2]}", ms, float(n) * n * (n + 1),
+                name = f"causal_matmul_8192_tiles{tiles[0]}x{tiles[1]}x{tiles[2]}"
+                if not want(name):
+                    continue
+                ms = time_device(lambda: ops.causal_matmul(x, y, *tiles), iters, warm, flush)
+                tensor_entry(name, ms, float(n) * n * (n + 1),
                              {"dense_equivalent_tflops": 2.0 * n**3 / ms / 1e9,
                               "algorithmic_flops": "K*M*(M+1)"})
         del x, y
 
     for (B, H, S, D) in ((4, 16, 2048, 128), (1, 16, 4096, 128)):
+        if not want(f"causal_attention_B{B}"):
+            continue
         try:
             q = device_randn_bf16((B, H, S, D), 0, device, D**-0.5)
             k = device_randn_bf16((B, H, S, D), 1, device)
             v = device_randn_bf16((B, H, S, D), 2, device)
-            ms = time_device(lambda: ops.causal_attention(q, k, v, 512, 512), 10, 3, flush)
+            ms = time_device(lambda: ops.causal_attention(q, k, v, 512, 512), iters, warm, flush)
             tensor_entry(f"causal_attention_B{B}_H{H}_S{S}_D{D}_blocks512", ms, 4.0 * B * H * D * S * (S + 1) / 2,
                          {"algorithmic_flops": "4*B*H*D*S*(S+1)/2"})
         except Exception as e:  # not built yet, or failed: report, do not hide
             out[f"causal_attention_B{B}_H{H}_S{S}_D{D}_blocks512"] = {"error": str(e)[:200]}
 
+    if not want("paged_gqa_decode"):
+        ops.device_status()
+        return out
     q, kp, vp, bt, lengths = synthetic.decode_inputs(64, 32, 8, 128, 16, 256, 8192)
     qd, kd, vd, btd, ld = (to_device(a, device) for a in (q, kp, vp, bt, lengths))
     bufs = ops.DecodeBuffers(64, 32, 128, 256, device)
     od = torch.empty_like(qd)
-    ms = time_device(lambda: ops.paged_gqa_decode(qd, kd, vd, btd, ld, out=od, buffers=bufs), 20, 3, flush)
+    ms = time_device(lambda: ops.paged_gqa_decode(qd, kd, vd, btd, ld, out=od, buffers=bufs), 2 * iters, warm, flush)
     nbytes = float(lengths.sum()) * 4096.0
     gbs = nbytes / ms / 1e6
     out["paged_gqa_decode_B64_H32_Hkv8_D128_page16"] = {
@@ -276,9 +289,20 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-extras", action="store_true", help="skip the other single-GPU workloads and the CPU baseline")
+    parser.add_argument("--only", default=None, help="run only the single-GPU workloads whose name contains this "
+                        "(dense_matmul_8192, causal_matmul, causal_attention_B4, paged_gqa_decode, ...) for "
+                        "--steps runs after --warmup: a short command to profile one kernel")
     args = parser.parse_args()
     if args.impl == "reference":
         reference_arm(args)
+        return
+    if args.only:
+        import torch
+
+        torch.cuda.set_device(0)
+        pk, pk_kind = peaks()
+        print(json.dumps(extra_workloads(torch.device("cuda", 0), pk, pk_kind, args.only, max(args.steps, 1),
+                                         max(args.warmup, 0))), flush=True)
         return
     args.warmup = max(args.warmup, 3)
 
