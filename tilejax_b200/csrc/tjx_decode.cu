@@ -26,9 +26,9 @@ int launch_build_steps_lengths(const int32_t* lengths, int n_lengths, const int3
                                int32_t* step_count, int32_t* tile_first, cudaStream_t stream);
 
 constexpr int DEC_D = 128;         // head dimension
-constexpr int DEC_SUB = 16;        // tokens a warp handles at a time (a page is a whole number of these)
+constexpr int DEC_SUB = 8;         // tokens a warp handles at a time (a page is a whole number of these)
 constexpr int DEC_CHUNK = 8;       // steps (pages) per CTA
-constexpr int DEC_WARPS = 8;       // KV heads per CTA
+constexpr int DEC_WARPS = 4;       // KV heads per CTA
 constexpr float DEC_MASK = -1e30f;
 
 struct DecodeParams {
@@ -56,8 +56,48 @@ __device__ __forceinline__ uint4 ld_nc_16(const void* p) {
   return v;
 }
 
-template <int DEC_GROUP>
-__global__ void __launch_bounds__(DEC_WARPS * 32) decode_chunks_kernel(const DecodeParams p) {
+// Two f32 in one 64-bit register pair, for the packed FMA of sm_100 (one instruction, two lanes of math).
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// A register holding two bf16 -> the two values as packed f32 (element 0 in the low half).
+__device__ __forceinline__ uint64_t bf16x2_to_f32x2(uint32_t u) {
+  return pack2(__uint_as_float(u << 16), __uint_as_float(u & 0xFFFF0000u));
+}
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+constexpr float DEC_LOG2E = 1.4426950408889634f;
+
+// One warp = one KV head and its G query heads over the chunk's steps. Lane = (half, dl): `half` picks one of
+// the two tokens a warp-wide 16-byte load covers, dl (0..15) the 8 head dimensions 8 dl .. 8 dl + 7.
+//
+// Scores: each lane forms its 8-dimension partial dot product for the G heads with packed FMAs, then the 16
+// lanes of a half-warp sum them with a transposing butterfly: at each of the first log2(G) exchange stages a
+// lane keeps half of its values and hands the other half to its partner, so after the four stages every lane
+// holds the complete score of ONE head (`hsel`, from dl's high bits) for its token. The softmax then runs once
+// per (head, token) quartet of lanes instead of on every lane, and the probabilities travel back to all lanes
+// by shuffle for the P V accumulation.
+template <int G>
+__global__ void __launch_bounds__(DEC_WARPS * 32, G <= 4 ? 4 : 1) decode_chunks_kernel(const DecodeParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kvh = blockIdx.y * DEC_WARPS + warp;
   if (kvh >= p.Hkv) return;
@@ -65,137 +105,209 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) decode_chunks_kernel(const Dec
   const int chunk = blockIdx.x;
   const int s_begin = chunk * DEC_CHUNK;
   if (s_begin >= n_steps) return;
-  const int s_end = min(s_begin + DEC_CHUNK, n_steps);
+  const int n_here = min(DEC_CHUNK, n_steps - s_begin);
 
-  const int half = lane >> 4;        // which of the two tokens a warp-wide load covers
-  const int d0 = (lane & 15) * 8;    // this lane's 8 head dimensions
+  const int half = lane >> 4;
+  const int dl = lane & 15;
+  const int d0 = dl * 8;
   const size_t row_elems = static_cast<size_t>(p.Hkv) * DEC_D;
+  constexpr int LOG_G = G == 1 ? 0 : G == 2 ? 1 : G == 4 ? 2 : 3;
+  // The head whose score this lane ends up with, and the lane (within this half-warp's 16) holding head h's.
+  const int hsel = LOG_G == 0 ? 0 : (dl >> (4 - LOG_G));
+  auto lane_of_head = [&](int h) { return (lane & ~(((1 << LOG_G) - 1) << (4 - LOG_G)) & 31) | (h << (4 - LOG_G)); };
 
-  float q[DEC_GROUP][8];
-  float acc[DEC_GROUP][8];
-  float m[DEC_GROUP], l[DEC_GROUP];
-  int cur = -1, cur_len = 0;
+  // The chunk's steps, one per lane (lanes 0..n_here-1), broadcast by shuffle when needed.
+  int my_tile = -1, my_code = 4, my_page = 0, my_len = 0;
+  if (lane < n_here) {
+    my_tile = p.step_tile[s_begin + lane];
+    my_code = p.step_code[s_begin + lane];
+    my_len = p.lengths[my_tile];
+    if (!(my_code & 4)) {
+      const int pg = my_code >> 3;
+      my_page = p.block_tables[static_cast<size_t>(my_tile) * p.pages_per_seq + pg];
+      my_page = min(max(my_page, 0), p.num_pages - 1);
+    }
+  }
+
+  uint64_t q2[G][4];    // this lane's 8 dimensions of each query head, packed in pairs
+  uint64_t acc2[G][4];  // P V accumulator, same layout
+  float m_run = DEC_MASK * DEC_LOG2E;  // running max of head `hsel`, log2 units
+  float l_run = 0.f;                   // running sum of head `hsel` over this half's tokens
+  int cur = -1;
 
   auto flush = [&]() {
     if (cur < 0) return;
     const int slot = chunk - p.tile_first[cur] / DEC_CHUNK;
-    const size_t base = (static_cast<size_t>(cur) * p.slots + slot) * p.H + kvh * DEC_GROUP;
+    const size_t base = (static_cast<size_t>(cur) * p.slots + slot) * p.H + kvh * G;
+    const float l_all = l_run + __shfl_xor_sync(0xFFFFFFFFu, l_run, 16);
 #pragma unroll
-    for (int h = 0; h < DEC_GROUP; ++h) {
-      const float l_all = l[h] + __shfl_xor_sync(0xFFFFFFFFu, l[h], 16);
+    for (int h = 0; h < G; ++h) {
       float a[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) a[j] = acc[h][j] + __shfl_xor_sync(0xFFFFFFFFu, acc[h][j], 16);
+      for (int j = 0; j < 4; ++j) {
+        float lo, hi;
+        unpack2(acc2[h][j], lo, hi);
+        a[2 * j] = lo + __shfl_xor_sync(0xFFFFFFFFu, lo, 16);
+        a[2 * j + 1] = hi + __shfl_xor_sync(0xFFFFFFFFu, hi, 16);
+      }
       if (half == 0) {
         float4* dst = reinterpret_cast<float4*>(p.ws_acc + (base + h) * DEC_D + d0);
         dst[0] = make_float4(a[0], a[1], a[2], a[3]);
         dst[1] = make_float4(a[4], a[5], a[6], a[7]);
       }
-      if (lane == 0) {
-        p.ws_m[base + h] = m[h];
-        p.ws_l[base + h] = l_all;
+    }
+    // The lane holding head hsel (the first of its quartet, token half 0) writes that head's statistics; the
+    // partials keep the max in natural-log units, as the merge kernel expects.
+    if (half == 0 && (dl & ((16 >> LOG_G) - 1)) == 0) {
+      p.ws_m[base + hsel] = m_run * (1.0f / DEC_LOG2E);
+      p.ws_l[base + hsel] = l_all;
+    }
+  };
+
+  // Micro-steps: (step, 16-token sub-block of its page), visited in order; K of the next micro-step is
+  // prefetched while the current one is being computed.
+  uint4 kr[DEC_SUB / 2], vr[DEC_SUB / 2];
+  auto addr_of = [&](int step, int sub) {
+    const int page = __shfl_sync(0xFFFFFFFFu, my_page, step);
+    return (static_cast<size_t>(page) * p.page_size + sub + half) * row_elems + kvh * DEC_D + d0;
+  };
+  auto load_k = [&](int step, int sub) {
+    const __nv_bfloat16* kp = p.k_pages + addr_of(step, sub);
+#pragma unroll
+    for (int i = 0; i < DEC_SUB / 2; ++i) kr[i] = ld_nc_16(kp + static_cast<size_t>(2 * i) * row_elems);
+  };
+  auto load_v = [&](int step, int sub) {
+    const __nv_bfloat16* vp = p.v_pages + addr_of(step, sub);
+#pragma unroll
+    for (int i = 0; i < DEC_SUB / 2; ++i) vr[i] = ld_nc_16(vp + static_cast<size_t>(2 * i) * row_elems);
+  };
+  // The next micro-step that has data after (step, sub), or step == n_here if none.
+  auto next_data = [&](int step, int sub, int& nstep, int& nsub) {
+    nstep = step, nsub = sub + DEC_SUB;
+    for (;;) {
+      if (nstep >= n_here) return;
+      const int code = __shfl_sync(0xFFFFFFFFu, my_code, nstep);
+      const int len = __shfl_sync(0xFFFFFFFFu, my_len, nstep);
+      if (!(code & 4) && nsub < p.page_size && (code >> 3) * p.page_size + nsub < len) return;
+      ++nstep, nsub = 0;
+      if (nstep < n_here) {
+        const int c2 = __shfl_sync(0xFFFFFFFFu, my_code, nstep);
+        if (!(c2 & 4)) return;  // sub 0 of a non-empty step always holds a valid position
       }
     }
   };
 
-  for (int s = s_begin; s < s_end; ++s) {
-    const int t = p.step_tile[s];
-    const int code = p.step_code[s];
+  // Prefetch K of the first micro-step with data.
+  int pf_step = 0, pf_sub = 0;
+  {
+    const int c0 = __shfl_sync(0xFFFFFFFFu, my_code, 0);
+    if (c0 & 4) next_data(0, p.page_size, pf_step, pf_sub);  // skip an empty first step
+    if (pf_step < n_here) load_k(pf_step, pf_sub);
+  }
+
+  for (int step = 0; step < n_here; ++step) {
+    const int t = __shfl_sync(0xFFFFFFFFu, my_tile, step);
+    const int code = __shfl_sync(0xFFFFFFFFu, my_code, step);
+    const int len = __shfl_sync(0xFFFFFFFFu, my_len, step);
     if (t != cur) {
       flush();
       cur = t;
-      cur_len = p.lengths[t];
-      const __nv_bfloat16* qp = p.q + (static_cast<size_t>(t) * p.H + kvh * DEC_GROUP) * DEC_D + d0;
+      const __nv_bfloat16* qp = p.q + (static_cast<size_t>(t) * p.H + kvh * G) * DEC_D + d0;
 #pragma unroll
-      for (int h = 0; h < DEC_GROUP; ++h) {
+      for (int h = 0; h < G; ++h) {
         const uint4 u = *reinterpret_cast<const uint4*>(qp + h * DEC_D);
-        q[h][0] = bf16_lo(u.x), q[h][1] = bf16_hi(u.x), q[h][2] = bf16_lo(u.y), q[h][3] = bf16_hi(u.y);
-        q[h][4] = bf16_lo(u.z), q[h][5] = bf16_hi(u.z), q[h][6] = bf16_lo(u.w), q[h][7] = bf16_hi(u.w);
-        m[h] = DEC_MASK, l[h] = 0.f;
+        q2[h][0] = bf16x2_to_f32x2(u.x), q2[h][1] = bf16x2_to_f32x2(u.y);
+        q2[h][2] = bf16x2_to_f32x2(u.z), q2[h][3] = bf16x2_to_f32x2(u.w);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[h][j] = 0.f;
+        for (int j = 0; j < 4; ++j) acc2[h][j] = 0ull;
       }
+      m_run = DEC_MASK * DEC_LOG2E, l_run = 0.f;
     }
-    if (code & 4) continue;  // an empty step: the sequence has no valid position
+    if (code & 4) continue;  // an empty step: no position to read
     const int pg = code >> 3;
-    int page = p.block_tables[static_cast<size_t>(t) * p.pages_per_seq + pg];
-    page = min(max(page, 0), p.num_pages - 1);
     for (int sub = 0; sub < p.page_size; sub += DEC_SUB) {
-    if (pg * p.page_size + sub >= cur_len) break;  // the rest of the page holds no valid position
-    const size_t page_off =
-        (static_cast<size_t>(page) * p.page_size + sub + half) * row_elems + kvh * DEC_D + d0;
-    const __nv_bfloat16* kp = p.k_pages + page_off;
-    const __nv_bfloat16* vp = p.v_pages + page_off;
+      const int base_pos = pg * p.page_size + sub;
+      if (base_pos >= len) break;
+      // K of this micro-step is in flight (prefetched); start V.
+      load_v(step, sub);
 
-    uint4 kr[DEC_SUB / 2], vr[DEC_SUB / 2];
+      // Partial dot products over this lane's 8 dimensions, then the transposing butterfly.
+      float sc[DEC_SUB / 2];
 #pragma unroll
-    for (int i = 0; i < DEC_SUB / 2; ++i) kr[i] = ld_nc_16(kp + static_cast<size_t>(2 * i) * row_elems);
+      for (int i = 0; i < DEC_SUB / 2; ++i) {
+        const uint64_t k0 = bf16x2_to_f32x2(kr[i].x), k1 = bf16x2_to_f32x2(kr[i].y);
+        const uint64_t k2 = bf16x2_to_f32x2(kr[i].z), k3 = bf16x2_to_f32x2(kr[i].w);
+        float r[G];
 #pragma unroll
-    for (int i = 0; i < DEC_SUB / 2; ++i) vr[i] = ld_nc_16(vp + static_cast<size_t>(2 * i) * row_elems);
-
-    // Scores of this lane's token of each pair against the 4 query heads, summed over the 16 lanes that
-    // share the token.
-    float sc[DEC_GROUP][DEC_SUB / 2];
+        for (int h = 0; h < G; ++h) {
+          uint64_t a = mul2(q2[h][0], k0);
+          a = fma2(q2[h][1], k1, a), a = fma2(q2[h][2], k2, a), a = fma2(q2[h][3], k3, a);
+          float lo, hi;
+          unpack2(a, lo, hi);
+          r[h] = lo + hi;
+        }
+        int n = G;
 #pragma unroll
-    for (int i = 0; i < DEC_SUB / 2; ++i) {
-      const float k0 = bf16_lo(kr[i].x), k1 = bf16_hi(kr[i].x), k2 = bf16_lo(kr[i].y), k3 = bf16_hi(kr[i].y);
-      const float k4 = bf16_lo(kr[i].z), k5 = bf16_hi(kr[i].z), k6 = bf16_lo(kr[i].w), k7 = bf16_hi(kr[i].w);
+        for (int mask = 8; mask >= 1; mask >>= 1) {
+          if (n > 1) {
+            n >>= 1;
+            const bool up = (dl & mask) != 0;
 #pragma unroll
-      for (int h = 0; h < DEC_GROUP; ++h) {
-        float a = q[h][0] * k0;
-        a = fmaf(q[h][1], k1, a), a = fmaf(q[h][2], k2, a), a = fmaf(q[h][3], k3, a);
-        a = fmaf(q[h][4], k4, a), a = fmaf(q[h][5], k5, a), a = fmaf(q[h][6], k6, a), a = fmaf(q[h][7], k7, a);
-        sc[h][i] = a;
+            for (int j = 0; j < n; ++j) {
+              const float keep = up ? r[j + n] : r[j];
+              const float send = up ? r[j] : r[j + n];
+              r[j] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, mask);
+            }
+          } else {
+            r[0] += __shfl_xor_sync(0xFFFFFFFFu, r[0], mask);
+          }
+        }
+        const int pos = base_pos + 2 * i + half;
+        sc[i] = pos < len ? r[0] * DEC_LOG2E : DEC_MASK * DEC_LOG2E;
       }
-    }
-#pragma unroll
-    for (int i = 0; i < DEC_SUB / 2; ++i)
-#pragma unroll
-      for (int h = 0; h < DEC_GROUP; ++h) {
-        float a = sc[h][i];
-        a += __shfl_xor_sync(0xFFFFFFFFu, a, 8);
-        a += __shfl_xor_sync(0xFFFFFFFFu, a, 4);
-        a += __shfl_xor_sync(0xFFFFFFFFu, a, 2);
-        a += __shfl_xor_sync(0xFFFFFFFFu, a, 1);
-        const int pos = pg * p.page_size + sub + 2 * i + half;
-        sc[h][i] = pos < cur_len ? a : DEC_MASK;
-      }
 
-    // Online softmax over the page; the probabilities are rounded to bf16 before they multiply V.
+      // K registers are free: prefetch the next micro-step's K.
+      next_data(step, sub, pf_step, pf_sub);
+      if (pf_step < n_here) load_k(pf_step, pf_sub);
+
+      // Online softmax of head hsel over this sub-block (both token halves).
+      float mx = sc[0];
 #pragma unroll
-    for (int h = 0; h < DEC_GROUP; ++h) {
-      float mx = sc[h][0];
-#pragma unroll
-      for (int i = 1; i < DEC_SUB / 2; ++i) mx = fmaxf(mx, sc[h][i]);
+      for (int i = 1; i < DEC_SUB / 2; ++i) mx = fmaxf(mx, sc[i]);
       mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 16));
-      const float m_new = fmaxf(m[h], mx);
-      const float alpha = __expf(m[h] - m_new);
-      m[h] = m_new;
+      const float m_new = fmaxf(m_run, mx);
+      const float alpha = ex2(m_run - m_new);
+      m_run = m_new;
       float sum = 0.f;
 #pragma unroll
       for (int i = 0; i < DEC_SUB / 2; ++i) {
-        const float pr = __expf(sc[h][i] - m_new);
+        const float pr = ex2(sc[i] - m_new);
         sum += pr;
-        sc[h][i] = __bfloat162float(__float2bfloat16_rn(pr));
+        sc[i] = __bfloat162float(__float2bfloat16_rn(pr));  // P is rounded before it multiplies V
       }
-      l[h] = l[h] * alpha + sum;
+      l_run = l_run * alpha + sum;
+      // Every lane rescales its accumulators of all heads.
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[h][j] *= alpha;
-    }
+      for (int h = 0; h < G; ++h) {
+        const float a = __shfl_sync(0xFFFFFFFFu, alpha, lane_of_head(h));
+        const uint64_t a2 = pack2(a, a);
 #pragma unroll
-    for (int i = 0; i < DEC_SUB / 2; ++i) {
-      const float v0 = bf16_lo(vr[i].x), v1 = bf16_hi(vr[i].x), v2 = bf16_lo(vr[i].y), v3 = bf16_hi(vr[i].y);
-      const float v4 = bf16_lo(vr[i].z), v5 = bf16_hi(vr[i].z), v6 = bf16_lo(vr[i].w), v7 = bf16_hi(vr[i].w);
+        for (int j = 0; j < 4; ++j) acc2[h][j] = mul2(acc2[h][j], a2);
+      }
+      // P V: each lane needs the probability of every head for its own token.
 #pragma unroll
-      for (int h = 0; h < DEC_GROUP; ++h) {
-        const float pr = sc[h][i];
-        acc[h][0] = fmaf(pr, v0, acc[h][0]), acc[h][1] = fmaf(pr, v1, acc[h][1]);
-        acc[h][2] = fmaf(pr, v2, acc[h][2]), acc[h][3] = fmaf(pr, v3, acc[h][3]);
-        acc[h][4] = fmaf(pr, v4, acc[h][4]), acc[h][5] = fmaf(pr, v5, acc[h][5]);
-        acc[h][6] = fmaf(pr, v6, acc[h][6]), acc[h][7] = fmaf(pr, v7, acc[h][7]);
+      for (int i = 0; i < DEC_SUB / 2; ++i) {
+        const uint64_t v0 = bf16x2_to_f32x2(vr[i].x), v1 = bf16x2_to_f32x2(vr[i].y);
+        const uint64_t v2 = bf16x2_to_f32x2(vr[i].z), v3 = bf16x2_to_f32x2(vr[i].w);
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+          const float pr = __shfl_sync(0xFFFFFFFFu, sc[i], lane_of_head(h));
+          const uint64_t p2 = pack2(pr, pr);
+          acc2[h][0] = fma2(p2, v0, acc2[h][0]), acc2[h][1] = fma2(p2, v1, acc2[h][1]);
+          acc2[h][2] = fma2(p2, v2, acc2[h][2]), acc2[h][3] = fma2(p2, v3, acc2[h][3]);
+        }
       }
     }
-    }  // sub-blocks of the page
   }
   flush();
 }
@@ -254,7 +366,7 @@ int tjx_paged_gqa_decode_bf16(const void* q, const void* k_pages, const void* v_
   if (B <= 0 || H <= 0 || Hkv <= 0 || pages_per_seq <= 0 || num_pages <= 0)
     return fail(TJX_E_ARG, "sizes must be positive");
   if (D != DEC_D) return fail(TJX_E_ARG, "head dimension must be 128");
-  if (page_size <= 0 || page_size % DEC_SUB != 0) return fail(TJX_E_ARG, "page size must be a multiple of 16");
+  if (page_size <= 0 || page_size % 16 != 0) return fail(TJX_E_ARG, "page size must be a multiple of 16");
   if (H % Hkv != 0) return fail(TJX_E_ARG, "H must be a multiple of Hkv");
   const int group = H / Hkv;
   if (group != 1 && group != 2 && group != 4 && group != 8)
@@ -357,7 +469,7 @@ int tjx_paged_gqa_decode_bf16_static(const void* q, const void* k_pages, const v
   if (B <= 0 || H <= 0 || Hkv <= 0 || pages_per_seq <= 0 || num_pages <= 0)
     return fail(TJX_E_ARG, "sizes must be positive");
   if (D != DEC_D) return fail(TJX_E_ARG, "head dimension must be 128");
-  if (page_size <= 0 || page_size % DEC_SUB != 0) return fail(TJX_E_ARG, "page size must be a multiple of 16");
+  if (page_size <= 0 || page_size % 16 != 0) return fail(TJX_E_ARG, "page size must be a multiple of 16");
   if (H % Hkv != 0) return fail(TJX_E_ARG, "H must be a multiple of Hkv");
   const int group = H / Hkv;
   if (group != 1 && group != 2 && group != 4 && group != 8)
