@@ -388,7 +388,7 @@ extern "C" int tjx_causal_attention_bf16(const void* q, const void* k, const voi
   p.step_tile = step_tile, p.step_code = step_code;
   p.units_per_bh = (S / AT_BQ + 1) / 2;
   p.status = device_status_word();
-  if (p.status == nullptr) return fail(TJX_E_CUDA, "could not allocate the device status word");
+  if (p.status == nullptr) return fail(TJX_E_CUDA, "could not locate the device status word");
 
   const uint64_t dims[2] = {static_cast<uint64_t>(D), static_cast<uint64_t>(B) * H * S};
   const uint64_t strides[1] = {static_cast<uint64_t>(D) * 2};

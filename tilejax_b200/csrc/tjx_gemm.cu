@@ -384,7 +384,7 @@ extern "C" int tjx_gemm_bf16(const void* x, const void* y, void* out, int M, int
   p.num_kb = (K + BK - 1) / BK;
   p.out = out;
   p.status = device_status_word();
-  if (p.status == nullptr) return fail(TJX_E_CUDA, "could not allocate the device status word");
+  if (p.status == nullptr) return fail(TJX_E_CUDA, "could not locate the device status word");
 
   CUtensorMap ma, mb, mc;
   {

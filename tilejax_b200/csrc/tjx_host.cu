@@ -29,6 +29,10 @@ static int g_cc_major[MAX_DEVICES];  // 0 = unknown
 static int g_sm_count[MAX_DEVICES];
 static int* g_status[MAX_DEVICES];
 
+// The kernels' error word: a fixed device variable (one per GPU that loads the library), so that no entry
+// point ever has to allocate device memory. Host code only ever takes its address with cudaGetSymbolAddress.
+static __device__ int g_status_word[64];
+
 static int current_device(int* dev) {
   cudaError_t e = cudaGetDevice(dev);
   if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
@@ -66,10 +70,9 @@ int* device_status_word() {
   if (current_device(&dev)) return nullptr;
   std::lock_guard<std::mutex> lock(g_mutex);
   if (g_status[dev] == nullptr) {
-    int* p = nullptr;
-    if (cudaMalloc(&p, 256) != cudaSuccess) return nullptr;
-    if (cudaMemset(p, 0, 256) != cudaSuccess) return nullptr;
-    g_status[dev] = p;
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess || p == nullptr) return nullptr;
+    g_status[dev] = static_cast<int*>(p);  // zero-initialised when the module loads
   }
   return g_status[dev];
 }
@@ -131,7 +134,7 @@ int tjx_device_status(tjx_stream_t stream, int* code) {
   *code = 0;
   if (int rc = tjx::check_device()) return rc;
   int* word = tjx::device_status_word();
-  if (word == nullptr) return tjx::fail(TJX_E_CUDA, "could not allocate the device status word");
+  if (word == nullptr) return tjx::fail(TJX_E_CUDA, "could not locate the device status word");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   TJX_CUDA(cudaStreamSynchronize(s));
   TJX_CUDA(cudaMemcpy(code, word, sizeof(int), cudaMemcpyDeviceToHost));

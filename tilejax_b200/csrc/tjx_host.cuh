@@ -26,7 +26,8 @@ int cuda_fail(cudaError_t e, const char* what);
 int check_device();
 int sm_count();
 
-// Per-device status word the kernels write error codes to (device memory, allocated once per device).
+// Per-device status word the kernels write error codes to: a fixed device variable inside the library (no
+// allocation); the address is looked up once per device.
 int* device_status_word();
 
 // Encode a tiled tensor map over a row-major bf16/f32 matrix viewed as `rank` dims (innermost first).
