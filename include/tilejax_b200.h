@@ -80,6 +80,12 @@ int tjx_gemm_bf16(const void* x, const void* y, void* out, int M, int N, int K, 
                   int tk, int stages, int out_f32, int causal, const int32_t* tile_i, const int32_t* tile_j,
                   int n_tiles, const int32_t* fill_i, const int32_t* fill_j, int n_fills, tjx_stream_t stream);
 
+/* Caps the number of persistent CTAs tjx_gemm_bf16 launches from the calling thread (0 = one per SM, the
+ * default). For callers that run communication kernels beside the GEMM — the collective matmul's exchange rounds
+ * stand in for the ring DMAs of the reference's kernel (src/autokernel/codegen.py:1161-1229), which need no
+ * compute units on a TPU but do on a GPU — so that those kernels find free SMs instead of delaying GEMM CTAs. */
+int tjx_gemm_set_cta_limit(int max_ctas);
+
 /* Flash-style causal attention, the step loop of `causal_attention` (examples/causal_attention.py:37-63):
  * q (pre-scaled), k, v, out [B, H, S, D] bf16, D == 128; online softmax in f32, P rounded to bf16 before P @ v.
  *   step_tile, step_code  int32[pattern_steps]: one (b, h)'s steps (Schedule.tables "step_tile"/"step_code",

@@ -1,0 +1,57 @@
+"""The front end on a B200: `kernel(...)`, `.verify` and `.tuning` for each hot-path loop nest. `verify` compares
+the CUDA kernel (through the C ABI) with the loop nest's reference on the CPU under the reference's tolerances."""
+
+import numpy as np
+import pytest
+import torch
+from helpers import f64, rand_bf16, to_device
+
+import oracle
+from tilejax_b200 import synthetic
+from tilejax_b200.autokernel import Config, Pipeline
+from tilejax_b200.autokernel import kernels as K
+
+pytestmark = pytest.mark.gpu
+TILES = K.MatmulTiles(tm=128, tn=128, tk=128)
+
+
+def test_matmul_verifies_and_takes_host_or_device_arrays():
+    x, y = rand_bf16((256, 384), 0), rand_bf16((384, 256), 1)
+    assert K.matmul.verify(x, y, TILES) <= 0.5
+    on_host = K.matmul(x, y, TILES)
+    assert isinstance(on_host, np.ndarray) and on_host.shape == (256, 256)
+    on_device = K.matmul(to_device(x), to_device(y), TILES)
+    assert isinstance(on_device, torch.Tensor) and on_device.is_cuda
+    oracle.compare("matmul", on_host, oracle.matmul_ref(x, y, 128, 128, 128))
+    # Every pipeline depth runs the same arithmetic.
+    sig = K.matmul.signature(x, y)
+    for pipeline in (Pipeline(2, 2), Pipeline(4, 3)):
+        out = K.matmul.lowered(sig, Config(TILES, pipeline)).run(x, y)
+        oracle.compare("matmul", out, oracle.matmul_ref(x, y, 128, 128, 128))
+
+
+def test_every_loop_nest_verifies():
+    x, y = rand_bf16((512, 256), 0), rand_bf16((256, 512), 1)
+    assert K.causal_matmul.verify(x, y, TILES) <= 0.5
+    assert K.causal_matmul.verify(x, y, K.MatmulTiles(tm=256, tn=512, tk=256)) <= 0.5
+    q, k, v = synthetic.attention_inputs(1, 2, 512, 128)
+    assert K.causal_attention.verify(q, k, v, K.AttentionBlocks(128, 256)) <= 2e-2
+    q, kp, vp, bt, lengths = synthetic.decode_inputs(4, 8, 2, 128, 16, 32, 128, distinct_pages=True)
+    lengths[:] = [0, 1, 300, 512]
+    assert K.paged_gqa_decode.verify(q, kp, vp, bt, lengths) <= 2e-2
+    assert not f64(K.paged_gqa_decode(q, kp, vp, bt, lengths)[0]).any()
+    assert K.all_gather_matmul.verify(x, y, K.CollectiveTiles()) <= 0.5  # one rank: the gather is the identity
+
+
+def test_tuning_tries_schedules_and_keeps_the_fastest():
+    x, y = rand_bf16((1024, 1024), 0), rand_bf16((1024, 1024), 1)
+    tuning = K.matmul.tuning(x, y)
+    assert 1 <= len(tuning.trials) <= 12 and tuning.best in tuning.trials
+    assert all(t.profile is not None or t.error for t in tuning.trials)
+    assert tuning.best.seconds == min(t.seconds for t in tuning.trials) or tuning.best.seconds <= 1.02 * min(
+        t.seconds for t in tuning.trials)
+    text = str(tuning)
+    assert text.startswith("chose MatmulTiles(") and text.count("*") == 1
+    out = K.matmul(x, y)  # uses the tuned schedule
+    oracle.compare("matmul", out, oracle.matmul_ref(x, y, 512, 512, 512))
+    assert K.matmul.tuning(x, y) is tuning  # remembered per signature

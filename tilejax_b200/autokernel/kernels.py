@@ -1,0 +1,186 @@
+"""The hot-path loop nests, written against this package: the workloads the sm_100a kernels run.
+
+Each is the plain loop nest over tiles whose meaning the kernel must reproduce — `kernel.fn` runs it as written on
+the CPU — with the same structure as the reference's examples (examples/matmul.py, causal_matmul.py,
+causal_attention.py, decode.py `paged_gqa_decode`, collective_matmul.py). Row statistics are kept as (rows, 1)
+columns here: the reference's lane-replicated (rows, 128) layout is a TPU register trick, not arithmetic.
+"""
+
+from __future__ import annotations
+
+import tilejax_b200.autokernel as autokernel
+from tilejax_b200.autokernel import jaxlike as jax
+
+jnp = jax.numpy
+MASK_VALUE = -1e30  # finite, so exp(old max - new max) never computes -inf + inf
+
+
+@autokernel.tunable
+class MatmulTiles:
+    """(tm, tn) output tiles, each summing tk-deep products."""
+
+    tm: int = autokernel.choice(128, 256, 512, 1024, 2048, default=512)
+    tn: int = autokernel.choice(128, 256, 512, 1024, 2048, default=512)
+    tk: int = autokernel.choice(128, 256, 512, 1024, 2048, default=512)
+
+
+@autokernel.tunable
+class AttentionBlocks:
+    """Queries and keys per block."""
+
+    block_q: int = autokernel.choice(128, 256, 512, 1024, default=512)
+    block_kv: int = autokernel.choice(128, 256, 512, 1024, default=512)
+
+
+@autokernel.tunable
+class CollectiveTiles:
+    """(tm, tn) output tiles summing tk-deep products; tm rows at a time of one rank's shard of x."""
+
+    tm: int = autokernel.choice(128, 256, 512, 1024, default=256)
+    tn: int = autokernel.choice(128, 256, 512, 1024, 2048, default=512)
+    tk: int = autokernel.choice(128, 256, 512, 1024, 2048, default=512)
+
+
+@autokernel.kernel
+def matmul(x, y, tiles=MatmulTiles()):
+    M, K = x.shape
+    N = y.shape[1]
+    tm, tn, tk = min(tiles.tm, M), min(tiles.tn, N), min(tiles.tk, K)
+    dtype = x.dtype
+    out = jnp.zeros((M, N), dtype)
+    for i in range(0, M, tm):
+        for j in range(0, N, tn):
+            acc = jnp.zeros((tm, tn), jnp.float32)
+            for k in range(0, K, tk):
+                acc += x[i : i + tm, k : k + tk] @ y[k : k + tk, j : j + tn]
+            out = out.at[i : i + tm, j : j + tn].set(acc.astype(dtype))
+    return out
+
+
+@autokernel.kernel
+def causal_matmul(x, y, tiles=MatmulTiles()):
+    M, K = x.shape
+    N = y.shape[1]
+    tm, tn, tk = min(tiles.tm, M), min(tiles.tn, N), min(tiles.tk, K)
+    dtype = x.dtype
+    out = jnp.zeros((M, N), dtype)
+    for i in range(0, M, tm):
+        for j in range(0, N, tn):
+            if j > i + tm - 1:  # the whole tile is above the diagonal
+                continue
+            acc = jnp.zeros((tm, tn), jnp.float32)
+            for k in range(0, K, tk):
+                acc += x[i : i + tm, k : k + tk] @ y[k : k + tk, j : j + tn]
+            rows = i + jax.lax.broadcasted_iota(jnp.int32, (tm, tn), 0)
+            cols = j + jax.lax.broadcasted_iota(jnp.int32, (tm, tn), 1)
+            out = out.at[i : i + tm, j : j + tn].set(jnp.where(cols <= rows, acc, 0.0).astype(dtype))
+    return out
+
+
+@autokernel.kernel
+def causal_attention(q, k, v, blocks=AttentionBlocks()):
+    B, H, S, D = q.shape
+    bq, bk = min(blocks.block_q, S), min(blocks.block_kv, S)
+    dtype = q.dtype
+    out = jnp.zeros((B, H, S, D), dtype)
+    for b in range(B):
+        for h in range(H):
+            for i in range(0, S, bq):
+                row_max = jnp.full((bq, 1), MASK_VALUE, jnp.float32)
+                row_sum = jnp.zeros((bq, 1), jnp.float32)  # of exp(s - row_max)
+                acc = jnp.zeros((bq, D), jnp.float32)  # sum of exp(s - row_max) @ v
+                for j in range(0, S, bk):
+                    if j > i + bq - 1:  # every key is in the future of every query
+                        continue
+                    s = q[b, h, i : i + bq, :] @ k[b, h, j : j + bk, :].T
+                    rows = i + jax.lax.broadcasted_iota(jnp.int32, (bq, bk), 0)
+                    cols = j + jax.lax.broadcasted_iota(jnp.int32, (bq, bk), 1)
+                    s = jnp.where(cols <= rows, s, MASK_VALUE)
+                    max_new = jnp.maximum(row_max, jnp.max(s, axis=1, keepdims=True))
+                    p = jnp.exp(s - max_new)
+                    alpha = jnp.exp(row_max - max_new)
+                    row_sum = alpha * row_sum + jnp.sum(p, axis=1, keepdims=True)
+                    acc = alpha * acc + p.astype(dtype) @ v[b, h, j : j + bk, :]
+                    row_max = max_new
+                out = out.at[b, h, i : i + bq, :].set((acc / row_sum).astype(dtype))
+    return out
+
+
+def queries_by_kv_head(qt, kv_heads):
+    """A sequence's queries (1, H, Dh) as (Hkv, G, Dh): head h attends with KV head h // G."""
+    _, h, d = qt.shape
+    return qt.reshape(kv_heads, h // kv_heads, d)
+
+
+def page_by_kv_head(page, kv_heads):
+    """A page (P, Hkv * Dh) as (Hkv, P, Dh)."""
+    p, w = page.shape
+    return page.reshape(p, kv_heads, w // kv_heads).transpose(1, 0, 2)
+
+
+def visible(page_size, first, length):
+    """Which positions of a page starting at `first` are before the sequence's end: (1, 1, P)."""
+    cols = first + jax.lax.broadcasted_iota(jnp.int32, (1, 1, page_size), 2)
+    return cols < length
+
+
+def online_softmax(s, v, ok, row_max, row_sum, acc):
+    """One online-softmax step over scores s (Hkv, G, P) against values v (Hkv, P, Dh)."""
+    s = jnp.where(ok, s, MASK_VALUE)
+    max_new = jnp.maximum(row_max, jnp.max(s, axis=2, keepdims=True))
+    p = jnp.exp(s - max_new)
+    alpha = jnp.exp(row_max - max_new)
+    row_sum = alpha * row_sum + jnp.sum(p, axis=2, keepdims=True)
+    acc = alpha * acc + jnp.dot(p.astype(v.dtype), v, preferred_element_type=jnp.float32)
+    return max_new, row_sum, acc
+
+
+def finish(acc, row_sum, shape, dtype):
+    """The normalised output as `shape`; rows that saw no key (an empty sequence) are 0."""
+    out = acc * (1.0 / jnp.maximum(row_sum, 1e-30))
+    return out.reshape(shape).astype(dtype)
+
+
+@autokernel.kernel
+def paged_gqa_decode(q, k_pages, v_pages, block_tables, lengths):
+    """GQA decode attention over a paged cache: q (B, 1, H, Dh), pages (num_pages, page_size, Hkv * Dh), sequence
+    b's pages listed in block_tables[b, :], its valid positions lengths[b]."""
+    B, T, H, Dh = q.shape
+    P, W = k_pages.shape[1], k_pages.shape[2]
+    pages = block_tables.shape[1]
+    Hkv = W // Dh
+    dtype = q.dtype
+    out = jnp.zeros((B, T, H, Dh), dtype)
+    for b in range(B):
+        qt = queries_by_kv_head(q[b, :, :, :], Hkv)
+        row_max = jnp.full((Hkv, H // Hkv, 1), MASK_VALUE, jnp.float32)
+        row_sum = jnp.zeros((Hkv, H // Hkv, 1), jnp.float32)
+        acc = jnp.zeros((Hkv, H // Hkv, Dh), jnp.float32)
+        for p in range(pages):
+            if p * P >= lengths[b]:  # past the sequence's end: decided on the device, before the kernel runs
+                continue
+            kt = page_by_kv_head(k_pages[block_tables[b, p], :, :], Hkv)
+            s = jnp.dot(qt, kt.transpose(0, 2, 1), preferred_element_type=jnp.float32)
+            ok = visible(P, p * P, lengths[b])
+            vt = page_by_kv_head(v_pages[block_tables[b, p], :, :], Hkv)
+            row_max, row_sum, acc = online_softmax(s, vt, ok, row_max, row_sum, acc)
+        out = out.at[b, :, :, :].set(finish(acc, row_sum, (T, H, Dh), dtype))
+    return out
+
+
+@autokernel.kernel
+def all_gather_matmul(x, w, tiles=CollectiveTiles()):
+    """x: this rank's rows (m, K); w: (K, n). Every rank's rows times these columns."""
+    xs = autokernel.all_gather(x, "x")
+    M, K = xs.shape
+    N = w.shape[1]
+    tm, tn, tk = min(tiles.tm, x.shape[0]), min(tiles.tn, N), min(tiles.tk, K)
+    dtype = x.dtype
+    out = jnp.zeros((M, N), dtype)
+    for i in range(0, M, tm):
+        for j in range(0, N, tn):
+            acc = jnp.zeros((tm, tn), jnp.float32)
+            for k in range(0, K, tk):
+                acc += xs[i : i + tm, k : k + tk] @ w[k : k + tk, j : j + tn]
+            out = out.at[i : i + tm, j : j + tn].set(acc.astype(dtype))
+    return out

@@ -1,0 +1,348 @@
+"""A parsed nest + input shapes + a tunable -> the numbers a kernel is built from, and which sm_100a kernel family
+runs it.
+
+The prologue is executed on shapes only (allocations are not performed), loop ranges become integers, static
+masks are evaluated per tile and per step into the reference's tables (src/autokernel/schedule.py:138-220), and the
+nest is matched against the schedules this backend has kernels for:
+
+  gemm        two parallel loops, one reduction loop, `acc += a[i:i+tm, k:k+tk] @ b[k:k+tk, j:j+tn]`, an optional tile
+              mask and an optional `where(cols <= rows, acc, 0)` on the stored tile; `a` may be an all-gathered input
+  attention   three parallel loops (b, h, i), a reduction loop over key blocks with the causal step mask, an online
+              softmax, `q @ k.T` and `p @ v`
+  decode      one parallel loop over sequences, a reduction loop over pages masked by an index array, pages chosen
+              through a block table
+Anything else is a KernelError ("not a recognised schedule"): there is no generic code generator and no fallback.
+"""
+
+from __future__ import annotations
+
+import ast
+import itertools
+from dataclasses import dataclass, field
+from typing import Any
+
+import numpy as np
+
+from .. import schedule as _schedule
+from .errors import KernelError
+from .parse import Nest
+
+
+@dataclass(frozen=True)
+class Spec:
+    """An array's shape and dtype, standing in for it while planning."""
+
+    shape: tuple[int, ...]
+    dtype: Any
+
+    @property
+    def ndim(self) -> int:
+        return len(self.shape)
+
+
+@dataclass(frozen=True)
+class Range:
+    var: str
+    start: int
+    stop: int
+    step: int
+
+    @property
+    def count(self) -> int:
+        return max(0, -(-(self.stop - self.start) // self.step))
+
+    def value(self, block: int) -> int:
+        return self.start + block * self.step
+
+
+@dataclass(frozen=True)
+class Plan:
+    nest: Nest
+    family: str                      # "gemm" | "attention" | "decode"
+    specs: tuple[Spec, ...]          # inputs, then gathered arrays
+    outputs: tuple[Spec, ...]
+    parallel: tuple[Range, ...]
+    reductions: tuple[Range, ...]
+    params: dict[str, Any] = field(default_factory=dict)   # what the kernel launch needs (tile sizes, flags)
+    runtime: bool = False
+
+    @property
+    def loops(self) -> tuple[Range, ...]:
+        return self.parallel + self.reductions
+
+
+class _AllocStub:
+    """Stands in for the array module while the prologue runs on shapes: zeros/full give Specs."""
+
+    def __init__(self, real):
+        self._real = real
+
+    def zeros(self, shape, dtype=None):
+        return Spec(tuple(int(s) for s in (shape if isinstance(shape, (tuple, list)) else (shape,))), np.dtype(dtype or np.float32))
+
+    def full(self, shape, value, dtype=None):
+        return self.zeros(shape, dtype)
+
+    def __getattr__(self, name):
+        return getattr(self._real, name)
+
+
+def _namespace(fn) -> dict[str, Any]:
+    ns = dict(fn.__globals__)
+    if fn.__closure__:
+        ns.update({n: c.cell_contents for n, c in zip(fn.__code__.co_freevars, fn.__closure__, strict=True)})
+    return ns
+
+
+def make_plan(nest: Nest, fn, specs: list[Spec], tunable: Any, chips: int = 1) -> Plan:
+    ns = _namespace(fn)
+    for name, spec in zip(nest.inputs, specs, strict=True):
+        ns[name] = spec
+    if nest.tunable:
+        ns[nest.tunable] = tunable
+    gathered = {}
+    for s in nest.prologue:
+        if isinstance(s, ast.Assign) and any(g.node is s for g in nest.all_gathers):
+            g = next(g for g in nest.all_gathers if g.node is s)
+            src = ns[g.source]
+            ns[g.name] = gathered[g.name] = Spec((src.shape[0] * chips, *src.shape[1:]), src.dtype)
+            continue
+        if isinstance(s, ast.Assign) and isinstance(s.value, ast.Call) and isinstance(s.value.func, ast.Attribute) \
+                and s.value.func.attr in ("zeros", "full") and isinstance(s.value.func.value, ast.Name):
+            module = s.value.func.value.id
+            local = dict(ns)
+            local[module] = _AllocStub(ns.get(module))
+            _exec(nest, s, local)
+            ns[s.targets[0].id] = local[s.targets[0].id]
+            continue
+        _exec(nest, s, ns)
+    outputs = []
+    for name in nest.outputs:
+        if not isinstance(ns.get(name), Spec):
+            raise nest.error(f"output `{name}` must be allocated with jnp.zeros or jnp.full", nest.allocations[name])
+        outputs.append(ns[name])
+
+    def ranges(loops):
+        out = []
+        for loop in loops:
+            try:
+                args = [int(eval(compile(ast.Expression(a), nest.filename, "eval"), ns)) for a in loop.args]
+            except Exception as e:
+                raise nest.error(f"the bounds of `{loop.var}`'s range must be integers known from the shapes ({e})",
+                                 loop.node) from e
+            start, stop, step = (0, args[0], 1) if len(args) == 1 else (args[0], args[1], 1) if len(args) == 2 else tuple(args)
+            if step <= 0:
+                raise nest.error("loops count up", loop.node)
+            if (stop - start) % step:
+                raise nest.error(f"`{loop.var}` doesn't take a whole number of steps of {step} from {start} to {stop}",
+                                 loop.node)
+            out.append(Range(loop.var, start, stop, step))
+        return tuple(out)
+
+    parallel, reductions = ranges(nest.parallel), ranges(nest.reductions)
+    all_specs = tuple(specs) + tuple(gathered.values())
+    plan = _recognise(nest, ns, all_specs, tuple(outputs), parallel, reductions, chips)
+    return plan
+
+
+def _exec(nest: Nest, stmt: ast.stmt, ns: dict) -> None:
+    try:
+        exec(compile(ast.Module([stmt], []), nest.filename, "exec"), ns)
+    except KernelError:
+        raise
+    except Exception as e:
+        raise nest.error(f"the code before the loops must run on the inputs' shapes alone: {type(e).__name__}: {e}",
+                         stmt) from e
+
+
+# ------------------------------------------------------------------------------------------ recognition
+
+
+def _unsupported(nest: Nest, why: str, node=None) -> KernelError:
+    return nest.error(f"not a recognised schedule: {why}. This backend runs matmul, causal matmul, causal "
+                      "attention, paged GQA decode and all-gather matmul loop nests on sm_100a and has no "
+                      "fallback for others", node or nest.function)
+
+
+def _window(node: ast.expr):
+    """`v : v + size` -> (v, size expr); `:` -> (None, None); a bare name -> (name, 'index')."""
+    if isinstance(node, ast.Slice):
+        if node.lower is None and node.upper is None:
+            return None, None
+        if isinstance(node.lower, ast.Name) and isinstance(node.upper, ast.BinOp) and isinstance(node.upper.op, ast.Add) \
+                and isinstance(node.upper.left, ast.Name) and node.upper.left.id == node.lower.id:
+            return node.lower.id, node.upper.right
+        return "?", None
+    if isinstance(node, ast.Name):
+        return node.id, "index"
+    return "?", None
+
+
+def _subscripts(node: ast.Subscript):
+    idx = node.slice
+    return list(idx.elts) if isinstance(idx, ast.Tuple) else [idx]
+
+
+def _eval(nest, ns, node) -> int:
+    return int(eval(compile(ast.Expression(node), nest.filename, "eval"), ns))
+
+
+def _mask_fn(nest, ns, mask: ast.expr, names: list[str]):
+    code = compile(ast.Expression(mask), nest.filename, "eval")
+
+    def holds(*values) -> bool:
+        return bool(eval(code, ns, dict(zip(names, values, strict=True))))
+
+    return holds
+
+
+def _recognise(nest, ns, specs, outputs, parallel, reductions, chips) -> Plan:
+    n_par, n_red = len(parallel), len(reductions)
+    if n_red != 1:
+        raise _unsupported(nest, f"{n_red} reduction loops (one is supported)")
+    if nest.runtime_masks:
+        return _recognise_decode(nest, ns, specs, outputs, parallel, reductions)
+    if n_par == 2:
+        return _recognise_gemm(nest, ns, specs, outputs, parallel, reductions, chips)
+    if n_par == 3:
+        return _recognise_attention(nest, ns, specs, outputs, parallel, reductions)
+    raise _unsupported(nest, f"{n_par} parallel loops")
+
+
+def _recognise_gemm(nest, ns, specs, outputs, parallel, reductions, chips) -> Plan:
+    (i, j), (k,) = parallel, reductions
+    body = nest.bodies[0]
+    if len(body) != 1 or not (isinstance(body[0], ast.AugAssign) and isinstance(body[0].op, ast.Add)
+                              and isinstance(body[0].value, ast.BinOp) and isinstance(body[0].value.op, ast.MatMult)):
+        raise _unsupported(nest, "the reduction loop's body must be `acc += a[...] @ b[...]`", nest.reductions[0].node)
+    acc = body[0].target.id
+    left, right = body[0].value.left, body[0].value.right
+    transposed = isinstance(right, ast.Attribute) and right.attr == "T"
+    right = right.value if transposed else right
+    if not (isinstance(left, ast.Subscript) and isinstance(right, ast.Subscript)
+            and isinstance(left.value, ast.Name) and isinstance(right.value, ast.Name)):
+        raise _unsupported(nest, "the matmul's operands must be tiles of inputs", body[0])
+    names = list(nest.inputs) + [g.name for g in nest.all_gathers]
+    a_name, b_name = left.value.id, right.value.id
+    if a_name not in names or b_name not in names:
+        raise _unsupported(nest, "the matmul's operands must be tiles of inputs", body[0])
+    la, lb = _subscripts(left), _subscripts(right)
+    if len(la) != 2 or len(lb) != 2:
+        raise _unsupported(nest, "the matmul's operands must be 2-D tiles", body[0])
+    (a0, tm_e), (a1, tk_e) = _window(la[0]), _window(la[1])
+    b_rows, b_cols = (_window(lb[1]), _window(lb[0])) if transposed else (_window(lb[0]), _window(lb[1]))
+    if (a0, a1, b_rows[0], b_cols[0]) != (i.var, k.var, k.var, j.var):
+        raise _unsupported(nest, "expected `a[i:i+tm, k:k+tk] @ b[k:k+tk, j:j+tn]` over loops (i, j, k)", body[0])
+    tm, tk, tn = _eval(nest, ns, tm_e), _eval(nest, ns, tk_e), _eval(nest, ns, b_cols[1])
+    if (tm, tn, tk) != (i.step, j.step, k.step):
+        raise _unsupported(nest, "tile sizes must equal the loops' steps", body[0])
+    a_spec, b_spec = specs[names.index(a_name)], specs[names.index(b_name)]
+    out = outputs[0]
+    if len(outputs) != 1 or out.ndim != 2:
+        raise _unsupported(nest, "one 2-D output")
+    M, K = a_spec.shape
+    N = b_spec.shape[0] if transposed else b_spec.shape[1]
+    if (i.start, i.stop, j.start, j.stop, k.start, k.stop) != (0, M, 0, N, 0, K) or out.shape != (M, N):
+        raise _unsupported(nest, "the loops must cover the operands exactly")
+    store = nest.stores[nest.outputs[0]]
+    causal = any(isinstance(n, ast.Call) and isinstance(n.func, ast.Attribute) and n.func.attr == "where"
+                 for n in ast.walk(store.value))
+    reads_acc = any(isinstance(n, ast.Name) and n.id == acc for n in ast.walk(store.value))
+    if not reads_acc:
+        raise _unsupported(nest, "the stored tile must be the accumulator", store.node)
+    tile_mask = nest.parallel[1].mask
+    if nest.parallel[0].mask is not None or nest.reductions[0].mask is not None:
+        raise _unsupported(nest, "a mask on this loop")
+    gathered = nest.all_gathers[0] if nest.all_gathers else None
+    if gathered is not None and (tile_mask is not None or a_name != gathered.name):
+        raise _unsupported(nest, "a gathered input is the left operand of an unmasked matmul")
+    tables: dict[str, np.ndarray] = {}
+    tiles = total = i.count * j.count
+    fills = 0
+    if tile_mask is not None:
+        holds = _mask_fn(nest, ns, tile_mask, [i.var, j.var])
+        active, skipped = [], []
+        for bi, bj in itertools.product(range(i.count), range(j.count)):
+            (skipped if holds(i.value(bi), j.value(bj)) else active).append((bi, bj))
+        if not active:
+            raise nest.error("the masks skip every output tile", nest.parallel[0].node)
+        if skipped:
+            tables = {f"tile_{i.var}": np.array([t[0] for t in active], np.int32),
+                      f"tile_{j.var}": np.array([t[1] for t in active], np.int32),
+                      f"fill_{i.var}": np.array([t[0] for t in skipped], np.int32),
+                      f"fill_{j.var}": np.array([t[1] for t in skipped], np.int32)}
+        tiles, fills = len(active), len(skipped)
+    if causal and not _is_tril_mask(nest, ns, tile_mask, i, j):
+        raise _unsupported(nest, "an elementwise `where` on the tile other than the causal `cols <= rows` with "
+                                 "its tile mask `j > i + tm - 1`", store.node)
+    sch = _schedule.Schedule(tiles, total, tiles * k.count, False, bool(fills), tiles, tiles * k.count, fills, 1, tables)
+    params = dict(M=M, N=N, K=K, tm=tm, tn=tn, tk=tk, causal=causal, transposed=transposed, a=a_name, b=b_name,
+                  out_dtype=out.dtype, schedule=sch, gathered=gathered.name if gathered else None,
+                  loop_vars=(i.var, j.var), chips=chips)
+    return Plan(nest, "gemm", specs, outputs, parallel, reductions, params)
+
+
+def _is_tril_mask(nest, ns, tile_mask, i, j) -> bool:
+    """Does the tile mask skip exactly the tiles wholly above the diagonal (`j > i + tm - 1`)?"""
+    if tile_mask is None:
+        return i.count == 1 or j.count == 1 and j.step >= i.stop  # one tile per row band: nothing to skip
+    holds = _mask_fn(nest, ns, tile_mask, [i.var, j.var])
+    return all(holds(i.value(bi), j.value(bj)) == (j.value(bj) > i.value(bi) + i.step - 1)
+               for bi in range(i.count) for bj in range(j.count))
+
+
+def _recognise_attention(nest, ns, specs, outputs, parallel, reductions) -> Plan:
+    (b, h, i), (j,) = parallel, reductions
+    if len(nest.inputs) != 3 or any(s.ndim != 4 for s in specs[:3]) or len(outputs) != 1:
+        raise _unsupported(nest, "causal attention takes q, k, v of shape (B, H, S, D)")
+    B, H, S, D = specs[0].shape
+    if any(s.shape != (B, H, S, D) for s in specs[:3]) or outputs[0].shape != (B, H, S, D):
+        raise _unsupported(nest, "q, k, v and the output must share one shape (B, H, S, D)")
+    text = ast.dump(ast.Module(list(nest.bodies[0]) + list(nest.segments[-1]), []))
+    needs = ("MatMult", "attr='T'", "attr='exp'", "attr='maximum'", "Div")
+    if not all(n in text for n in needs):
+        raise _unsupported(nest, "the tile code is not an online softmax over `q @ k.T` and `p @ v`")
+    mask = nest.reductions[0].mask
+    if mask is None or any(l.mask is not None for l in nest.parallel):
+        raise _unsupported(nest, "causal attention masks its key loop with `j > i + block_q - 1`")
+    holds = _mask_fn(nest, ns, mask, [i.var, j.var])
+    causal = all(holds(i.value(bi), j.value(bj)) == (j.value(bj) > i.value(bi) + i.step - 1)
+                 for bi in range(i.count) for bj in range(j.count))
+    if not causal or (b.count, h.count, i.stop, j.stop) != (B, H, S, S):
+        raise _unsupported(nest, "the step mask must be the causal one, `j > i + block_q - 1`, over whole sequences",
+                           nest.reductions[0].node)
+    sch = _schedule.causal_attention_schedule(B, H, S, i.step, j.step)
+    params = dict(B=B, H=H, S=S, D=D, block_q=i.step, block_kv=j.step, schedule=sch)
+    return Plan(nest, "attention", specs, outputs, parallel, reductions, params)
+
+
+def _recognise_decode(nest, ns, specs, outputs, parallel, reductions) -> Plan:
+    if len(parallel) != 1 or len(nest.inputs) != 5:
+        raise _unsupported(nest, "a runtime mask other than paged decode's (q, k_pages, v_pages, block_tables, lengths)")
+    (b,), (p,) = parallel, reductions
+    q, kp, vp, bt, lengths = specs[:5]
+    mask = nest.reductions[0].mask
+    reads = {n.value.id for n in ast.walk(mask) if isinstance(n, ast.Subscript) and isinstance(n.value, ast.Name)}
+    if reads != {nest.inputs[4]} or np.dtype(lengths.dtype) != np.int32 or np.dtype(bt.dtype) != np.int32:
+        raise _unsupported(nest, "the page loop's mask must compare the page's first position with lengths[b]",
+                           nest.reductions[0].node)
+    if q.ndim != 4 or kp.ndim != 3 or kp.shape != vp.shape or bt.ndim != 2 or lengths.ndim != 1:
+        raise _unsupported(nest, "paged decode takes q (B, T, H, D), pages (num_pages, page, Hkv * D), block tables "
+                                 "(B, pages) and lengths (B,)")
+    B, T, H, D = q.shape
+    num_pages, page, W = kp.shape
+    if T != 1:
+        raise _unsupported(nest, "several new tokens per sequence (T > 1)")
+    # The mask must be `p * page >= lengths[b]`: check it on the extremes with a stand-in for lengths.
+    probe_ns = dict(ns)
+    code = compile(ast.Expression(mask), nest.filename, "eval")
+
+    def skipped(pv: int, length: int) -> bool:
+        return bool(eval(code, probe_ns, {p.var: pv, b.var: 0, nest.inputs[4]: [length]}))
+
+    ok = all(skipped(pv, n) == (pv * page >= n) for pv in (0, 1, p.count - 1) for n in (0, 1, page, page + 1, page * p.count))
+    if not ok or (b.count, p.count) != (B, bt.shape[1]) or p.step != 1 or p.start != 0:
+        raise _unsupported(nest, "the page loop must skip pages with `p * page_size >= lengths[b]`", nest.reductions[0].node)
+    sch = _schedule.paged_decode_schedule(B, p.count)
+    params = dict(B=B, H=H, Hkv=W // D, D=D, page=page, pages=p.count, num_pages=num_pages, schedule=sch)
+    return Plan(nest, "decode", specs, outputs, parallel, reductions, params, runtime=True)

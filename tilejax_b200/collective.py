@@ -88,7 +88,7 @@ class AllGatherMatmul:
     """
 
     def __init__(self, m: int, K: int, N: int, tm: int = 256, tn: int = 512, tk: int = 512, group=None,
-                 device: torch.device | None = None):
+                 device: torch.device | None = None, reserve_sms: int = 16):
         from . import ops  # needs the built library
 
         self._ops = ops
@@ -105,12 +105,15 @@ class AllGatherMatmul:
         self.x_ready = torch.cuda.Event()
         self.arrived = [torch.cuda.Event() for _ in self.exchange.rounds]
         self.done = torch.cuda.Event()
-        # Tile tables per shard: its row blocks (in order) x every column block, row-major.
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        self.cta_limit = max(1, sms - reserve_sms) if self.ranks > 1 and reserve_sms > 0 else 0
+        # Tile tables per received shard: its row blocks (in order) x every column block, row-major. The own
+        # shard needs none: its tiles are read straight from x.
         shard_blocks = m // self.tm
         cols = np.arange(N // self.tn, dtype=np.int32)
         order = _schedule.collective_row_blocks(self.me, self.ranks, shard_blocks)
         self.tables = []
-        for s in range(self.ranks):
+        for s in range(1, self.ranks):
             rows = order[s * shard_blocks : (s + 1) * shard_blocks]
             ti = torch.from_numpy(np.repeat(rows, cols.size).astype(np.int32)).to(device)
             tj = torch.from_numpy(np.tile(cols, rows.size).astype(np.int32)).to(device)
@@ -126,8 +129,10 @@ class AllGatherMatmul:
         if x.shape != (self.m, self.K) or w.shape != (self.K, self.N):
             raise ValueError("x must be this rank's (m, K) shard and w (K, N)")
         compute = torch.cuda.current_stream(self.device)
+        own_out = self.out[self.me * self.m : (self.me + 1) * self.m]
         if self.ranks == 1:
-            return ops.gemm(x, w, self.tm, self.tn, self.tk, out=self.out)
+            ops.gemm(x, w, self.tm, self.tn, self.tk, out=own_out)
+            return self.out
         # Communication stream: all rounds, in the order the tiles will want them.
         self.x_ready.record(compute)
         self.comm_stream.wait_event(self.x_ready)
@@ -137,12 +142,17 @@ class AllGatherMatmul:
                 for req in ex.start_round(x, rnd):
                     req.wait()
                 event.record(self.comm_stream)
-        # Compute stream: own shard at once (straight from x: no copy into xs is needed for the result),
-        # then each shard as its round completes.
-        ex.rows(self.me).copy_(x, non_blocking=True)
-        for s, (ti, tj) in enumerate(self.tables):
-            if s > 0:
-                compute.wait_event(self.arrived[s - 1])
-            ops.gemm(ex.xs, w, self.tm, self.tn, self.tk, tile_i=ti, tile_j=tj, out=self.out)
+        # Compute stream: the own shard at once, straight from x (it is never copied), then each shard as its
+        # round completes. While rounds are in flight the GEMM leaves a few SMs to the exchange's kernels.
+        try:
+            ops.set_gemm_cta_limit(self.cta_limit)
+            ops.gemm(x, w, self.tm, self.tn, self.tk, out=own_out)
+            for s, (ti, tj) in enumerate(self.tables):
+                compute.wait_event(self.arrived[s])
+                if s == len(self.tables) - 1:
+                    ops.set_gemm_cta_limit(0)  # nothing is in flight behind the last shard
+                ops.gemm(ex.xs, w, self.tm, self.tn, self.tk, tile_i=ti, tile_j=tj, out=self.out)
+        finally:
+            ops.set_gemm_cta_limit(0)
         self.done.record(compute)
         return self.out

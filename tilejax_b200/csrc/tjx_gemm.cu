@@ -343,6 +343,16 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
 
 }  // namespace tjx
 
+namespace tjx {
+static thread_local int g_gemm_cta_limit = 0;  // 0 = one CTA per SM
+}
+
+extern "C" int tjx_gemm_set_cta_limit(int max_ctas) {
+  if (max_ctas < 0) return tjx::fail(TJX_E_ARG, "max_ctas must be >= 0");
+  tjx::g_gemm_cta_limit = max_ctas;
+  return 0;
+}
+
 extern "C" int tjx_gemm_bf16(const void* x, const void* y, void* out, int M, int N, int K, int y_transposed, int tm,
                              int tn, int tk, int stages, int out_f32, int causal, const int32_t* tile_i,
                              const int32_t* tile_j, int n_tiles, const int32_t* fill_i, const int32_t* fill_j,
@@ -423,7 +433,8 @@ extern "C" int tjx_gemm_bf16(const void* x, const void* y, void* out, int M, int
 
   const long long total_items = static_cast<long long>(n_tiles + n_fills) * p.sub_m * p.sub_n;
   if (total_items >= (1ll << 31)) return fail(TJX_E_LIMIT, "too many output tiles");
-  const int grid = static_cast<int>(total_items < sm_count() ? total_items : sm_count());
+  int grid = static_cast<int>(total_items < sm_count() ? total_items : sm_count());
+  if (g_gemm_cta_limit > 0 && grid > g_gemm_cta_limit) grid = g_gemm_cta_limit;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (BN == 256) {
     if (stages == 3) return launch_gemm<256, 3>(ma, mb, mc, p, grid, s);

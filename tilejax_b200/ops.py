@@ -127,6 +127,11 @@ def gemm(x: torch.Tensor, y: torch.Tensor, tm: int, tn: int, tk: int, *, causal:
     return out
 
 
+def set_gemm_cta_limit(max_ctas: int) -> None:
+    """Cap the persistent GEMM's grid for this thread's following launches (0 = one CTA per SM)."""
+    check(library().tjx_gemm_set_cta_limit(int(max_ctas)))
+
+
 def matmul(x: torch.Tensor, y: torch.Tensor, tm: int = 512, tn: int = 512, tk: int = 512, **kw) -> torch.Tensor:
     """The `matmul` loop nest (examples/matmul.py:22-35): tiles clipped to the matrix as its prologue does."""
     M, K = x.shape
