@@ -321,6 +321,8 @@ def main() -> None:
     device = torch.device("cuda", local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"  # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=device)
     pk, pk_kind = peaks()
 
@@ -330,7 +332,9 @@ def main() -> None:
     y_host = device_randn_bf16((K_DIM, N_DIM), 1, device).cpu().pin_memory()
     x = x_host.to(device)
     y = y_host.to(device)
-    op = AllGatherMatmul(m, K_DIM, N_DIM, *TILES, reserve_sms=int(os.environ.get("TJX_RESERVE_SMS", "16")))
+    reserve = os.environ.get("TJX_RESERVE_SMS")
+    op = AllGatherMatmul(m, K_DIM, N_DIM, *TILES, reserve_sms=None if reserve is None else int(reserve),
+                         transport=os.environ.get("TJX_TRANSPORT", "peer"))
     op.exchange.rows(op.me).copy_(x)  # (only the kernel-alone timing below reads the own rows of xs)
     out_host = torch.empty((M_TOTAL, N_DIM), dtype=torch.bfloat16).pin_memory()
 
@@ -391,13 +395,14 @@ def main() -> None:
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": workload_name(world), "tiles": list(TILES), "rows_per_gpu": m,
                    "l2": "operands and output (671 MB) are larger than L2; no flush between steps",
-                   "gather": "none (1 GPU)" if world == 1 else f"{world - 1} NCCL send/recv rounds on a second stream"},
+                   "gather": "none (1 GPU)" if world == 1 else
+                   f"{world - 1} rounds on a second stream, transport {op.transport}, {len(op.groups)} GEMM launches"},
         "per_gpu_tflops": value / world,
         "clocks": clocks,
         "e2e": {"value": world * flops_per_gpu / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": x_host.numel() * 2 + y_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2,
                 "api": "tilejax_b200.collective.AllGatherMatmul.__call__ with pinned host x, y and out"},
-        "gpu_launches": args.steps * world + args.steps,
+        "gpu_launches": args.steps * (1 if world == 1 else len(op.groups)) + args.steps,
         "roofline": {"bound": "tensor", "kernel": "gemm_kernel<256,4>", "achieved": gemm_tflops, "peak": peak,
                      "unit": "TFLOP/s", "frac": gemm_tflops / peak,
                      "peak_kind": f"{pk_kind} cuBLAS bf16, {'sustained' if long_run else 'burst'}",

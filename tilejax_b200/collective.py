@@ -11,8 +11,10 @@ straight into its place in the local gathered buffer `xs` — the same arrival o
 expects. The rounds run on a communication stream over NCCL; the compute stream starts on the rank's own shard
 at once and waits, per shard, only for that shard's round. The GEMM kernel always reads this GPU's own memory.
 
-`ShardExchange` is the data movement alone and works on any backend (the host logic is tested with gloo on
-CPU tensors); `AllGatherMatmul` adds the sm_100a GEMM and has no CPU path.
+`ShardExchange` is that data movement over `torch.distributed` send / receive and works on any backend (the host
+logic is tested with gloo on CPU tensors). `PeerExchange` does the same rounds as copy-engine pulls from the peers'
+symmetric memory over NVLink, which take no SM away from the GEMM; it is the default on GPUs. `AllGatherMatmul`
+adds the sm_100a GEMM and has no CPU path.
 """
 
 from __future__ import annotations
@@ -79,22 +81,78 @@ class ShardExchange:
         return self.xs
 
 
+class PeerExchange:
+    """The same gather over NVLink peer memory instead of NCCL kernels: every rank keeps its shard in a
+    symmetric-memory buffer that its peers map, and each round is one device-to-device copy from the peer's
+    buffer into this GPU's own `xs` — issued on the communication stream, carried by the copy engines, so the
+    exchange takes no SM from the GEMM. A stream-ordered barrier over the buffer's signal pads (one tiny kernel)
+    tells every rank that all shards of this call are in place; the send buffer is double-buffered so a rank may
+    write call k + 1's shard while peers still read call k's."""
+
+    def __init__(self, m: int, K: int, dtype: torch.dtype, device: torch.device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = dist.group.WORLD if group is None else group
+        self.ranks, self.me = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.m, self.K = m, K
+        self.send = symm_mem.empty((2, m, K), dtype=dtype, device=device)
+        self.handle = symm_mem.rendezvous(self.send, self.group)
+        self.peers = [self.handle.get_buffer(r, (2, m, K), dtype, 0) for r in range(self.ranks)]
+        self.xs = torch.empty((self.ranks * m, K), dtype=dtype, device=device)
+        self.rounds = exchange_rounds(self.me, self.ranks)
+        self.calls = 0
+
+    def rows(self, rank: int) -> torch.Tensor:
+        return self.xs[rank * self.m : (rank + 1) * self.m]
+
+    def shard_buffer(self) -> torch.Tensor:
+        """Where the next call's shard goes: writing x here directly saves the copy into the send buffer."""
+        return self.send[self.calls & 1]
+
+    def barrier(self) -> None:
+        """All ranks' current-stream work so far is done (enqueued on the current stream)."""
+        self.handle.barrier(channel=0)
+
+    def pull(self, rnd: Round, parity: int) -> None:
+        """Round `rnd`: copy the shard of rank rnd.recv_from from its send buffer into this GPU's xs."""
+        self.rows(rnd.recv_from).copy_(self.peers[rnd.recv_from][parity], non_blocking=True)
+
+
+def shard_groups(ranks: int) -> list[list[int]]:
+    """Which shards (in arrival order: 0 is the own shard) each GEMM launch covers: the own shard alone first —
+    nothing has arrived yet — then the shards that arrive while it runs, then the rest: three launches at most, so
+    the later ones are long enough to fill their waves."""
+    if ranks <= 2:
+        return [[s] for s in range(ranks)]
+    rest = ranks - 1
+    first = -(-rest * 3 // 7)
+    return [[0], list(range(1, 1 + first)), list(range(1 + first, ranks))]
+
+
 class AllGatherMatmul:
     """out = all_gather(x) @ w on each rank, [ranks * m, N] bf16, with the gather hidden behind the compute.
 
-    Buffers (xs, out), the tile tables of each shard, the communication stream and the events are made once;
-    a call only enqueues work. `reserve_sms` leaves that many SMs free of GEMM CTAs while exchanges are in
-    flight, for NCCL's copy kernels to run beside the persistent GEMM.
+    Buffers (xs, out), the tile tables, the communication stream and the events are made once; a call only enqueues
+    work. `transport` is "peer" (copy-engine pulls from peers' symmetric memory: no SMs) or "nccl" (send / receive
+    rounds: NCCL's copy kernels need SMs, so `reserve_sms` of them are kept free of GEMM CTAs while rounds are in
+    flight; "peer" keeps a few free for its barrier kernel).
     """
 
     def __init__(self, m: int, K: int, N: int, tm: int = 256, tn: int = 512, tk: int = 512, group=None,
-                 device: torch.device | None = None, reserve_sms: int = 16):
+                 device: torch.device | None = None, reserve_sms: int | None = None, transport: str = "peer"):
         from . import ops  # needs the built library
 
         self._ops = ops
         device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
         self.device = device
-        self.exchange = ShardExchange(m, K, torch.bfloat16, device, group)
+        ranks = dist.get_world_size(group) if dist.is_initialized() else 1
+        if transport not in ("peer", "nccl"):
+            raise ValueError("transport is 'peer' or 'nccl'")
+        self.transport = transport if ranks > 1 else "none"
+        if self.transport == "peer":
+            self.exchange = PeerExchange(m, K, torch.bfloat16, device, group)
+        else:
+            self.exchange = ShardExchange(m, K, torch.bfloat16, device, group)
         self.ranks, self.me = self.exchange.ranks, self.exchange.me
         self.m, self.K, self.N = m, K, N
         self.tm, self.tn, self.tk = min(tm, m), min(tn, N), min(tk, K)
@@ -103,26 +161,34 @@ class AllGatherMatmul:
         self.out = torch.empty((self.ranks * m, N), dtype=torch.bfloat16, device=device)
         self.comm_stream = torch.cuda.Stream(device=device)
         self.x_ready = torch.cuda.Event()
+        self.barrier_done = torch.cuda.Event()
         self.arrived = [torch.cuda.Event() for _ in self.exchange.rounds]
         self.done = torch.cuda.Event()
         sms = torch.cuda.get_device_properties(device).multi_processor_count
+        if reserve_sms is None:
+            reserve_sms = 4 if self.transport == "peer" else 32
         self.cta_limit = max(1, sms - reserve_sms) if self.ranks > 1 and reserve_sms > 0 else 0
-        # Tile tables per received shard: its row blocks (in order) x every column block, row-major. The own
-        # shard needs none: its tiles are read straight from x.
+        # One GEMM launch per group of shards; the tile table of a group lists its shards' row blocks, in arrival
+        # order, times every column block, row-major. The own shard needs none: its tiles come straight from x.
         shard_blocks = m // self.tm
         cols = np.arange(N // self.tn, dtype=np.int32)
         order = _schedule.collective_row_blocks(self.me, self.ranks, shard_blocks)
+        self.groups = shard_groups(self.ranks)
         self.tables = []
-        for s in range(1, self.ranks):
-            rows = order[s * shard_blocks : (s + 1) * shard_blocks]
+        for group_shards in self.groups[1:]:
+            rows = np.concatenate([order[s * shard_blocks : (s + 1) * shard_blocks] for s in group_shards])
             ti = torch.from_numpy(np.repeat(rows, cols.size).astype(np.int32)).to(device)
             tj = torch.from_numpy(np.tile(cols, rows.size).astype(np.int32)).to(device)
-            self.tables.append((ti, tj))
+            self.tables.append((group_shards[-1], ti, tj))
 
     @property
     def steps(self) -> int:
         """Steps of the reference's schedule: every (tile, reduction block)."""
         return (self.ranks * self.m // self.tm) * (self.N // self.tn) * (self.K // self.tk)
+
+    def shard_buffer(self) -> torch.Tensor | None:
+        """With the peer transport: the buffer to write the next call's x into to save a copy (else None)."""
+        return self.exchange.shard_buffer() if self.transport == "peer" else None
 
     def __call__(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         ops, ex = self._ops, self.exchange
@@ -133,24 +199,42 @@ class AllGatherMatmul:
         if self.ranks == 1:
             ops.gemm(x, w, self.tm, self.tn, self.tk, out=own_out)
             return self.out
-        # Communication stream: all rounds, in the order the tiles will want them.
-        self.x_ready.record(compute)
-        self.comm_stream.wait_event(self.x_ready)
-        self.comm_stream.wait_event(self.done)  # the previous call's GEMMs have finished reading xs
-        with torch.cuda.stream(self.comm_stream):
-            for rnd, event in zip(ex.rounds, self.arrived, strict=True):
-                for req in ex.start_round(x, rnd):
-                    req.wait()
-                event.record(self.comm_stream)
-        # Compute stream: the own shard at once, straight from x (it is never copied), then each shard as its
-        # round completes. While rounds are in flight the GEMM leaves a few SMs to the exchange's kernels.
+        comm = self.comm_stream
+        if self.transport == "peer":
+            parity = ex.calls & 1
+            staged = ex.send[parity]
+            if x.data_ptr() != staged.data_ptr():
+                # Peers finished reading this half two calls ago, before the previous call's barrier.
+                compute.wait_event(self.barrier_done)
+                staged.copy_(x, non_blocking=True)
+            ex.calls += 1
+            self.x_ready.record(compute)
+            comm.wait_event(self.x_ready)
+            comm.wait_event(self.done)  # the previous call's GEMMs have finished reading xs
+            with torch.cuda.stream(comm):
+                ex.barrier()  # every rank's shard of this call is in its send buffer
+                self.barrier_done.record(comm)
+                for rnd, event in zip(ex.rounds, self.arrived, strict=True):
+                    ex.pull(rnd, parity)
+                    event.record(comm)
+        else:
+            self.x_ready.record(compute)
+            comm.wait_event(self.x_ready)
+            comm.wait_event(self.done)
+            with torch.cuda.stream(comm):
+                for rnd, event in zip(ex.rounds, self.arrived, strict=True):
+                    for req in ex.start_round(x, rnd):
+                        req.wait()
+                    event.record(comm)
+        # Compute stream: the own shard at once, straight from x (it is never copied into xs), then each group of
+        # shards once its last round has completed. While the exchange is in flight the GEMM leaves it a few SMs.
         try:
             ops.set_gemm_cta_limit(self.cta_limit)
             ops.gemm(x, w, self.tm, self.tn, self.tk, out=own_out)
-            for s, (ti, tj) in enumerate(self.tables):
-                compute.wait_event(self.arrived[s])
-                if s == len(self.tables) - 1:
-                    ops.set_gemm_cta_limit(0)  # nothing is in flight behind the last shard
+            for n, (last_shard, ti, tj) in enumerate(self.tables):
+                compute.wait_event(self.arrived[last_shard - 1])
+                if n == len(self.tables) - 1:
+                    ops.set_gemm_cta_limit(0)  # nothing is in flight behind the last group
                 ops.gemm(ex.xs, w, self.tm, self.tn, self.tk, tile_i=ti, tile_j=tj, out=self.out)
         finally:
             ops.set_gemm_cta_limit(0)
