@@ -59,7 +59,7 @@ plan, sch = K.all_gather_matmul.build(sig, K.CollectiveTiles(tm=128, tn=128, tk=
 assert sch.steps == ranks and plan.params["chips"] == ranks
 dist.barrier()
 dist.destroy_process_group()
-sys.stdout.write("rank %d ok\n" % me)
+print("rank %d ok" % me, flush=True)
 """
 
 
