@@ -248,19 +248,31 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
       tc_fence_after_sync();
       const int kv0 = n * AT_BKV;
       const bool diagonal = kv0 + AT_BKV - 1 > q0;  // some key of the block is in some row's future
-      // Pass 1: the block's row max.
-      float mx = AT_MASK;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(s_tmem + c * 32, v);
-        tmem_wait_ld();
+      // The row's 128 scores come into registers once: four TMEM loads in flight, one wait.
+      uint32_t v[4][32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float s = __uint_as_float(v[j]);
-          if (diagonal && kv0 + c * 32 + j > row) s = AT_MASK;
-          mx = fmaxf(mx, s);
-        }
+      for (int c = 0; c < 4; ++c) tmem_ld32(s_tmem + c * 32, v[c]);
+      tmem_wait_ld();
+      if (diagonal) {  // only the block on the diagonal holds keys in some row's future
+        const int lim = row - kv0;  // columns j <= lim are visible
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (c * 32 + j > lim) v[c][j] = __float_as_uint(AT_MASK);
+      }
+      // Row max over the block, four independent chains.
+      float mx;
+      {
+        float m0 = AT_MASK, m1 = AT_MASK, m2 = AT_MASK, m3 = AT_MASK;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            m0 = fmaxf(m0, __uint_as_float(v[c][j])), m1 = fmaxf(m1, __uint_as_float(v[c][j + 1]));
+            m2 = fmaxf(m2, __uint_as_float(v[c][j + 2])), m3 = fmaxf(m3, __uint_as_float(v[c][j + 3]));
+          }
+        mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
       }
       const float m_blk = mx * AT_LOG2E;
       if (n == 0) {
@@ -289,26 +301,26 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
         }
         tmem_wait_st();
       }
-      // Pass 2: probabilities; P (bf16) overwrites the scores already consumed.
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(s_tmem + c * 32, v);
-        tmem_wait_ld();
-        uint32_t pk[16];
+      // Probabilities; P (bf16) overwrites the first half of the scores' columns (all already in registers).
+      {
+        float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+        const float neg_m = -m_used;
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          float s0 = __uint_as_float(v[j]), s1 = __uint_as_float(v[j + 1]);
-          if (diagonal) {
-            if (kv0 + c * 32 + j > row) s0 = AT_MASK;
-            if (kv0 + c * 32 + j + 1 > row) s1 = AT_MASK;
+        for (int c = 0; c < 4; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(v[c][j]), AT_LOG2E, neg_m));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(v[c][j + 1]), AT_LOG2E, neg_m));
+            const float p2 = fast_exp2(fmaf(__uint_as_float(v[c][j + 2]), AT_LOG2E, neg_m));
+            const float p3 = fast_exp2(fmaf(__uint_as_float(v[c][j + 3]), AT_LOG2E, neg_m));
+            l0 += p0, l1 += p1, l2 += p2, l3 += p3;
+            pk[j >> 1] = pack_bf16(p0, p1);
+            pk[(j >> 1) + 1] = pack_bf16(p2, p3);
           }
-          const float p0 = fast_exp2(fmaf(s0, AT_LOG2E, -m_used));
-          const float p1 = fast_exp2(fmaf(s1, AT_LOG2E, -m_used));
-          l += p0 + p1;
-          pk[j >> 1] = pack_bf16(p0, p1);
+          tmem_st16(s_tmem + c * 16, pk);
         }
-        tmem_st16(s_tmem + c * 16, pk);
+        l += (l0 + l1) + (l2 + l3);
       }
       tmem_wait_st();
       tc_fence_before_sync();

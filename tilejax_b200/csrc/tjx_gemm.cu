@@ -15,6 +15,8 @@
 //
 // y [K, N] row-major is the MN-major B operand: a slot holds BN / 64 boxes of [64 n x 64 k], each row of a
 // box one k with 64 consecutive n (128 bytes). y [N, K] (x @ y.T) is the K-major operand, one box [64 k x BN].
+#include <algorithm>
+
 #include "tjx_host.cuh"
 #include "tjx_ptx.cuh"
 
@@ -30,7 +32,8 @@ constexpr int EPI_THREADS = 128;
 struct GemmParams {
   int M, N, K;
   int tm, tn;            // the user tile
-  int tiles_n;           // user tiles along N (arithmetic order when there is no table)
+  int tiles_m, tiles_n;  // user tiles along M and N (arithmetic order when there is no table)
+  int band_tiles;        // width, in user tiles, of the column bands the arithmetic order walks
   int sub_m, sub_n;      // CTA tiles per user tile
   int n_tiles, n_fills;  // user tiles that run / that are filled
   const int32_t* tile_i;
@@ -61,8 +64,16 @@ __device__ __forceinline__ Item decode_item(const GemmParams& p, int w) {
       ti = p.tile_i[t];
       tj = p.tile_j[t];
     } else {
-      ti = t / p.tiles_n;
-      tj = t - ti * p.tiles_n;
+      // No table: every tile runs, and their order is not observable, so walk them in column bands of
+      // `band_tiles` tiles: the CTAs in flight then share a few thousand rows of x and columns of y that stay
+      // in L2, instead of streaming all of y once per row of tiles.
+      const int band_size = p.band_tiles * p.tiles_m;          // tiles in a full band
+      const int band = t / band_size;
+      const int first_col = band * p.band_tiles;
+      const int width = min(p.band_tiles, p.tiles_n - first_col);
+      const int in_band = t - band * band_size;
+      ti = in_band / width;
+      tj = first_col + in_band - ti * width;
     }
   } else {
     fill = true;
@@ -385,7 +396,8 @@ extern "C" int tjx_gemm_bf16(const void* x, const void* y, void* out, int M, int
     return fail(TJX_E_ARG, "stages must be 0 (default), 4, 3 (256-wide CTA tiles) or 6 (128-wide)");
 
   GemmParams p{};
-  p.M = M, p.N = N, p.K = K, p.tm = tm, p.tn = tn, p.tiles_n = tiles_n;
+  p.M = M, p.N = N, p.K = K, p.tm = tm, p.tn = tn, p.tiles_m = tiles_m, p.tiles_n = tiles_n;
+  p.band_tiles = std::max(1, 2048 / tn);
   p.sub_m = (tm + BM - 1) / BM;
   p.sub_n = (tn + BN - 1) / BN;
   p.n_tiles = n_tiles, p.n_fills = n_fills;
