@@ -30,7 +30,7 @@ constexpr int DEC_D = 128;         // head dimension
 constexpr int DEC_SUB = 8;         // tokens per micro-step (a page is a whole number of these)
 constexpr int DEC_STAGES = 2;      // ring slots per warp
 constexpr int DEC_STAGE_BYTES = DEC_SUB * DEC_D * 2 * 2;  // K and V of one micro-step for one KV head
-constexpr int DEC_CHUNK = 8;       // steps (pages) per CTA
+constexpr int DEC_CHUNK = 16;      // steps (pages) per CTA
 constexpr int DEC_WARPS = 4;       // KV heads per CTA
 constexpr float DEC_MASK = -1e30f;
 // Shared memory per warp: the K/V ring, the partial-score scratch [4 pairs][G][32], P [8][G] and G rescale factors.
@@ -298,8 +298,11 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, G <= 4 ? 4 : 2)
         const int h = own_h + 4 * j;
         float score = DEC_MASK * DEC_LOG2E;
         if (h < G) {
+          // The 32 lanes read 32 different 64-byte runs that all start on bank 0 or 16: each lane starts at a
+          // different 16-byte unit of its run, so that one LDS.128 spreads over all banks.
           const float4* src = reinterpret_cast<const float4*>(pb + ((own_tok >> 1) * G + h) * 32 + (own_tok & 1) * 16);
-          const float4 a = src[0], b = src[1], c = src[2], d = src[3];
+          const int rot = (h + (own_tok >> 1)) & 3;
+          const float4 a = src[rot], b = src[(rot + 1) & 3], c = src[(rot + 2) & 3], d = src[(rot + 3) & 3];
           const float sum = ((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w)) +
                             (((c.x + c.y) + (c.z + c.w)) + ((d.x + d.y) + (d.z + d.w)));
           if (base_pos + own_tok < len) score = sum * DEC_LOG2E;
