@@ -37,8 +37,8 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 CPU_SAMPLE_ROWS = 2048
 
 # DRAM bytes (read + write) per launch of the dominant kernel from an ncu capture of this command's workload
-# (profiles/gemm_kernel_collective_matmul.md); None until captured.
-NCU_TRAFFIC_BYTES = {"gemm_16384x8192x8192": None}
+# (profiles/gemm_pair_kernel_16384x8192x8192.md): dram__bytes_read.sum + dram__bytes_write.sum.
+NCU_TRAFFIC_BYTES = {"gemm_16384x8192x8192": 2.299167e9 + 0.263586e9}
 
 
 def peaks() -> tuple[dict, str]:
@@ -296,6 +296,10 @@ def main() -> None:
     if args.impl == "reference":
         reference_arm(args)
         return
+    if os.environ.get("TJX_GEMM_PAIRS") is not None:  # A/B switch: 0 = one MMA per SM instead of one per pair of SMs
+        from tilejax_b200 import ops as _ops
+
+        _ops.set_gemm_pair_mode(int(os.environ["TJX_GEMM_PAIRS"]))
     if args.only:
         import torch
 
@@ -407,7 +411,7 @@ def main() -> None:
                 "h2d_bytes_per_step": x_host.numel() * 2 + y_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2,
                 "api": "tilejax_b200.collective.AllGatherMatmul.__call__ with pinned host x, y and out"},
         "gpu_launches": args.steps * (1 if world == 1 else len(op.groups)) + args.steps,
-        "roofline": {"bound": "tensor", "kernel": "gemm_kernel<256,4>", "achieved": gemm_tflops, "peak": peak,
+        "roofline": {"bound": "tensor", "kernel": "gemm_pair_kernel<3,2>", "achieved": gemm_tflops, "peak": peak,
                      "unit": "TFLOP/s", "frac": gemm_tflops / peak,
                      "peak_kind": f"{pk_kind} cuBLAS bf16, {'sustained' if long_run else 'burst'}",
                      "ms_per_launch": gemm_ms, "flops_per_launch": flops_per_gpu,

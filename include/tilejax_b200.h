@@ -86,6 +86,13 @@ int tjx_gemm_bf16(const void* x, const void* y, void* out, int M, int N, int K, 
  * compute units on a TPU but do on a GPU — so that those kernels find free SMs instead of delaying GEMM CTAs. */
 int tjx_gemm_set_cta_limit(int max_ctas);
 
+/* Chooses how tjx_gemm_bf16 maps CTA tiles to SMs for calls from this thread: 1 (default) = one MMA per pair of
+ * SMs (256 x 256 pieces, each SM staging half of y's columns) whenever tm % 256 == 0, tn % 256 == 0 and stages
+ * == 0; 0 = always one 128 x 256 (or 128 x 128) piece per SM. Results are bit-identical: both modes sum K in
+ * the same order. The counterpart in the reference is the choice of tile sizes left to its tuner
+ * (src/autokernel/tune.py:246-300): a launch-shape knob with no effect on values. */
+int tjx_gemm_set_pair_mode(int mode);
+
 /* Flash-style causal attention, the step loop of `causal_attention` (examples/causal_attention.py:37-63):
  * q (pre-scaled), k, v, out [B, H, S, D] bf16, D == 128; online softmax in f32, P rounded to bf16 before P @ v.
  *   step_tile, step_code  int32[pattern_steps]: one (b, h)'s steps (Schedule.tables "step_tile"/"step_code",

@@ -143,6 +143,74 @@ def test_dense_4096_against_sampled_float64_rows_and_linearity():
     assert (other - out).abs().max().item() <= 1e-5 * np.abs(want).max()
 
 
+@pytest.mark.parametrize(("shape", "tiles", "kw"), [
+    ((256, 64, 256), (256, 256, 64), {}),                         # one 256 x 256 piece, one reduction block
+    ((512, 512, 512), (512, 512, 512), {}),
+    ((1024, 768, 1536), (256, 512, 256), {"out_f32": True}),
+    ((1024, 8192, 512), (256, 256, 512), {}),                     # a long reduction: many trips round the ring
+    ((2048, 256, 2048), (512, 256, 256), {"causal": True}),
+    ((4096, 512, 4096), (512, 512, 512), {}),                     # more pieces than SM pairs: persistent loop
+])
+def test_sm_pairs_and_single_ctas_agree_bit_for_bit(shape, tiles, kw):
+    # One MMA per pair of SMs (256 x 256 pieces) and one per SM (128 x 256) sum K in the same order.
+    M, K, N = shape
+    x, y = to_device(rand_bf16((M, K), 0)), to_device(rand_bf16((K, N), 1))
+    dtype = torch.float32 if kw.get("out_f32") else torch.bfloat16
+    outs = []
+    try:
+        for pairs in (True, False):
+            ops.set_gemm_pair_mode(pairs)
+            out = torch.full((M, N), float("nan"), dtype=dtype, device="cuda")
+            if kw.get("causal"):
+                ops.causal_matmul(x, y, *tiles, out=out)
+            else:
+                ops.gemm(x, y, *tiles, out=out, out_dtype=dtype)
+            assert ops.device_status() == 0
+            outs.append(out)
+    finally:
+        ops.set_gemm_pair_mode(True)
+    assert not torch.isnan(outs[0]).any()
+    assert torch.equal(outs[0], outs[1])
+    want = f64(to_host(x))[:8] @ f64(to_host(y))
+    if kw.get("causal"):
+        want = np.where(np.arange(N)[None, :] <= np.arange(8)[:, None], want, 0.0)
+    got = f64(to_host(outs[0][:8]))
+    assert np.abs(got - want).max() <= 2e-2 * max(np.abs(want).max(), 1.0)
+
+
+def test_sm_pairs_with_y_transposed_tables_and_a_cta_limit():
+    x, y = rand_bf16((1024, 256), 0), rand_bf16((512, 256), 1)
+    xd, yd = to_device(x), to_device(y)
+    tile_i = to_device(np.array([3, 0, 2, 1], np.int32))
+    tile_j = to_device(np.array([1, 0, 1, 0], np.int32))
+    fill_i = to_device(np.array([1, 2], np.int32))
+    fill_j = to_device(np.array([1, 0], np.int32))
+    outs = []
+    try:
+        for pairs, limit in ((True, 6), (True, 0), (False, 0)):
+            ops.set_gemm_pair_mode(pairs)
+            ops.set_gemm_cta_limit(limit)
+            out = torch.full((1024, 512), 7.0, dtype=torch.bfloat16, device="cuda")
+            ops.gemm(xd, yd, 256, 256, 256, y_transposed=True, tile_i=tile_i, tile_j=tile_j, fill_i=fill_i,
+                     fill_j=fill_j, out=out)
+            assert ops.device_status() == 0
+            outs.append(out)
+    finally:
+        ops.set_gemm_pair_mode(True)
+        ops.set_gemm_cta_limit(0)
+    assert torch.equal(outs[0], outs[2]) and torch.equal(outs[1], outs[2])
+    got = f64(to_host(outs[0])).reshape(4, 256, 2, 256).transpose(0, 2, 1, 3)
+    want = (f64(x) @ f64(y).T).reshape(4, 256, 2, 256).transpose(0, 2, 1, 3)
+    for i in range(4):
+        for j in range(2):
+            if (i, j) in ((3, 1), (0, 0), (2, 1), (1, 0)):
+                np.testing.assert_allclose(got[i, j], want[i, j], rtol=2e-2, atol=0.5)
+            elif (i, j) in ((1, 1), (2, 0)):
+                assert not got[i, j].any()
+            else:
+                assert (got[i, j] == 7.0).all()
+
+
 def test_bad_arguments_are_errors():
     x = torch.zeros(256, 256, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(NativeError, match="multiple of 128"):

@@ -27,7 +27,6 @@ namespace tjx {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int GEMM_THREADS = 192;
-constexpr int EPI_THREADS = 128;
 
 struct GemmParams {
   int M, N, K;
@@ -52,7 +51,7 @@ struct Item {
   bool valid;    // false: a table entry out of range, nothing is written
 };
 
-template <int BN>
+template <int BMT, int BN>
 __device__ __forceinline__ Item decode_item(const GemmParams& p, int w) {
   const int per = p.sub_m * p.sub_n;
   const int t = w / per, r = w - t * per;
@@ -82,12 +81,89 @@ __device__ __forceinline__ Item decode_item(const GemmParams& p, int w) {
   }
   Item it;
   it.valid = ti >= 0 && tj >= 0 && static_cast<long long>(ti) * p.tm < p.M && static_cast<long long>(tj) * p.tn < p.N;
-  it.m0 = ti * p.tm + sm * BM;
+  it.m0 = ti * p.tm + sm * BMT;
   it.n0 = tj * p.tn + sn * BN;
   if (it.m0 >= p.M || it.n0 >= p.N) it.valid = false;  // a sub-tile wholly past the edge of a clipped tile
   // A sub-tile wholly above the diagonal of a causal tile is all zeros: no loads, no MMA.
-  it.compute = it.valid && !fill && !(p.causal && it.n0 > it.m0 + BM - 1);
+  it.compute = it.valid && !fill && !(p.causal && it.n0 > it.m0 + BMT - 1);
   return it;
+}
+
+// Zeros for 32 rows (row0 .. row0 + 31) of a CTA tile's BN columns from n0: 16 bytes per lane per pass.
+template <int BN>
+__device__ __forceinline__ void zero_rows(const GemmParams& p, int row0, int n0, int lane) {
+  const int out_elt = p.out_f32 ? 4 : 2;
+  const int row_bytes = BN * out_elt;
+  for (int r = 0; r < 32; ++r) {
+    const int row = row0 + r;
+    if (row >= p.M) break;
+    uint8_t* dst = static_cast<uint8_t*>(p.out) + (static_cast<size_t>(row) * p.N + n0) * out_elt;
+    const int valid_bytes = min(row_bytes, (p.N - n0) * out_elt);
+    for (int b = lane * 16; b < valid_bytes; b += 32 * 16)
+      *reinterpret_cast<uint4*>(dst + b) = make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+// One epilogue warp's share of an accumulator: TMEM lanes of `t_row` (32 rows, output rows row0 .. row0 + 31),
+// BN columns from n0. Chunks of 32 accumulator columns are masked (causal), converted, staged in one of the
+// warp's two 32-row x 128-byte buffers (128-byte swizzled) and TMA-stored; the buffers alternate so a store can
+// still be reading one while the warp fills the other. bf16: two chunks fill a buffer; f32: one chunk does.
+template <int BN>
+__device__ __forceinline__ void store_accumulator(const GemmParams& p, const CUtensorMap* map_c, uint32_t t_row,
+                                                  int row0, int n0, uint8_t* c_ptr, uint32_t c_smem, int& c_buf,
+                                                  int lane) {
+  const int row = row0 + lane;
+  constexpr int CHUNKS = BN / 32;
+#pragma unroll 1
+  for (int c = 0; c < CHUNKS; ++c) {
+    uint32_t v[32];
+    tmem_ld32(t_row + c * 32, v);
+    tmem_wait_ld();
+    if (p.causal) {
+      const int col0 = n0 + c * 32;
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j > row) v[j] = 0u;
+    }
+    const bool new_buf = p.out_f32 || (c & 1) == 0;
+    if (new_buf) {
+      // The TMA store issued two buffers ago has finished reading this buffer.
+      if (lane == 0) tma_store_wait_read<1>();
+      __syncwarp();
+    }
+    uint8_t* buf = c_ptr + c_buf * (32 * 128);
+    // Row `lane` of the buffer is 128 bytes = eight 16-byte units; unit u is stored at u ^ (lane & 7).
+    if (p.out_f32) {
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        uint4 val = make_uint4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
+        *reinterpret_cast<uint4*>(buf + lane * 128 + ((u ^ (lane & 7)) << 4)) = val;
+      }
+    } else {
+      const int half = c & 1;  // which 64 bytes of the 128-byte row
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        uint4 val;
+        val.x = pack_bf16(__uint_as_float(v[8 * u + 0]), __uint_as_float(v[8 * u + 1]));
+        val.y = pack_bf16(__uint_as_float(v[8 * u + 2]), __uint_as_float(v[8 * u + 3]));
+        val.z = pack_bf16(__uint_as_float(v[8 * u + 4]), __uint_as_float(v[8 * u + 5]));
+        val.w = pack_bf16(__uint_as_float(v[8 * u + 6]), __uint_as_float(v[8 * u + 7]));
+        const int unit = half * 4 + u;
+        *reinterpret_cast<uint4*>(buf + lane * 128 + ((unit ^ (lane & 7)) << 4)) = val;
+      }
+    }
+    const bool flush = p.out_f32 || (c & 1) == 1;
+    if (flush) {
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        const int col = p.out_f32 ? n0 + c * 32 : n0 + (c >> 1) * 64;
+        tma_store_2d(map_c, c_smem + c_buf * (32 * 128), col, row0);
+        tma_store_commit();
+      }
+      c_buf ^= 1;
+    }
+  }
 }
 
 template <int BN, int STAGES>
@@ -155,7 +231,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       uint32_t phase = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < total_items && ok; w += gridDim.x) {
-        const Item it = decode_item<BN>(p, w);
+        const Item it = decode_item<BM, BN>(p, w);
         if (!it.compute) continue;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, TJX_ERR_WAIT_EMPTY)) {
@@ -189,7 +265,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < total_items && ok; w += gridDim.x) {
-        const Item it = decode_item<BN>(p, w);
+        const Item it = decode_item<BM, BN>(p, w);
         if (!it.compute) continue;
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, TJX_ERR_WAIT_TMEM_EMPTY)) break;
         tc_fence_after_sync();
@@ -230,89 +306,26 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     const int ew = warp - 2;
     int acc = 0;
     uint32_t acc_phase = 0;
-    const int out_elt = p.out_f32 ? 4 : 2;
     // Per warp: two staging buffers of 32 rows x 128 bytes (128-byte swizzled), alternated so a TMA store
     // can still be reading one while the warp fills the other.
     const uint32_t c_smem = base + L::C_OFF + ew * (2 * 32 * 128);
     uint8_t* c_ptr = base_ptr + L::C_OFF + ew * (2 * 32 * 128);
     int c_buf = 0;
     for (int w = blockIdx.x; w < total_items; w += gridDim.x) {
-      const Item it = decode_item<BN>(p, w);
+      const Item it = decode_item<BM, BN>(p, w);
       if (!it.valid) {
         if (lane == 0 && p.status != nullptr) atomicCAS(p.status, 0, TJX_ERR_BAD_TABLE);
         continue;
       }
       if (!it.compute) {
-        // Zeros: rows m0 + 32 q .. + 31, each BN * out_elt bytes, 16 bytes per lane per pass.
-        const int row_bytes = BN * out_elt;
-        for (int r = 0; r < 32; ++r) {
-          const int row = it.m0 + q * 32 + r;
-          if (row >= p.M) break;
-          uint8_t* dst = static_cast<uint8_t*>(p.out) + (static_cast<size_t>(row) * p.N + it.n0) * out_elt;
-          const int valid_bytes = min(row_bytes, (p.N - it.n0) * out_elt);
-          for (int b = lane * 16; b < valid_bytes; b += 32 * 16)
-            *reinterpret_cast<uint4*>(dst + b) = make_uint4(0u, 0u, 0u, 0u);
-        }
+        zero_rows<BN>(p, it.m0 + q * 32, it.n0, lane);
         continue;
       }
       const bool got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, TJX_ERR_WAIT_TMEM_FULL);
       if (!__all_sync(0xFFFFFFFFu, got)) break;
       tc_fence_after_sync();
-      const int row = it.m0 + q * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-      // Chunks of 32 accumulator columns. bf16: two chunks fill one 32 x 64 staging buffer (128 bytes per
-      // row); f32: one chunk does.
-      constexpr int CHUNKS = BN / 32;
-#pragma unroll 1
-      for (int c = 0; c < CHUNKS; ++c) {
-        uint32_t v[32];
-        tmem_ld32(t_row + c * 32, v);
-        tmem_wait_ld();
-        if (p.causal) {
-          const int col0 = it.n0 + c * 32;
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (col0 + j > row) v[j] = 0u;
-        }
-        const bool new_buf = p.out_f32 || (c & 1) == 0;
-        if (new_buf) {
-          // The TMA store issued two buffers ago has finished reading this buffer.
-          if (lane == 0) tma_store_wait_read<1>();
-          __syncwarp();
-        }
-        uint8_t* buf = c_ptr + c_buf * (32 * 128);
-        // Row `lane` of the buffer is 128 bytes = eight 16-byte units; unit u is stored at u ^ (lane & 7).
-        if (p.out_f32) {
-#pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            uint4 val = make_uint4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
-            *reinterpret_cast<uint4*>(buf + lane * 128 + ((u ^ (lane & 7)) << 4)) = val;
-          }
-        } else {
-          const int half = c & 1;  // which 64 bytes of the 128-byte row
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            uint4 val;
-            val.x = pack_bf16(__uint_as_float(v[8 * u + 0]), __uint_as_float(v[8 * u + 1]));
-            val.y = pack_bf16(__uint_as_float(v[8 * u + 2]), __uint_as_float(v[8 * u + 3]));
-            val.z = pack_bf16(__uint_as_float(v[8 * u + 4]), __uint_as_float(v[8 * u + 5]));
-            val.w = pack_bf16(__uint_as_float(v[8 * u + 6]), __uint_as_float(v[8 * u + 7]));
-            const int unit = half * 4 + u;
-            *reinterpret_cast<uint4*>(buf + lane * 128 + ((unit ^ (lane & 7)) << 4)) = val;
-          }
-        }
-        const bool flush = p.out_f32 || (c & 1) == 1;
-        if (flush) {
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            const int col = p.out_f32 ? it.n0 + c * 32 : it.n0 + (c >> 1) * 64;
-            tma_store_2d(&map_c, c_smem + c_buf * (32 * 128), col, it.m0 + q * 32);
-            tma_store_commit();
-          }
-          c_buf ^= 1;
-        }
-      }
+      store_accumulator<BN>(p, &map_c, t_row, it.m0 + q * 32, it.n0, c_ptr, c_smem, c_buf, lane);
       // The accumulator has been read: hand it back to the MMA warp.
       tc_fence_before_sync();
       __syncwarp();
@@ -352,10 +365,257 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
   return 0;
 }
 
+// ------------------------------------------------------------------------------------------------ CTA pairs
+//
+// The same loop with one MMA per PAIR of SMs (a cluster of two CTAs, tcgen05 cta_group::2). A work item is a
+// 256 x 256 piece of a user tile: each CTA of the pair stages its own 128 rows of x and its own 128 columns of y,
+// the even CTA issues the M = 256 MMA, which reads both shared memories, and each CTA ends up with its 128 rows
+// x 256 columns of the accumulator in its own TMEM. Per SM and per K = 16 step that is 4 KB of A + 4 KB of B
+// read from shared memory instead of 4 + 8 KB, and a third fewer bytes from L2 into shared memory per flop: on a
+// part that runs this loop at its power limit, fewer bytes moved per flop is a higher clock.
+//
+//   full[s]    lives in the even CTA: its producer posts the bytes of BOTH CTAs' loads, and the odd CTA's TMA
+//              loads count their bytes on it too
+//   empty[s]   one per CTA, for its own producer: the MMA thread commits to both
+//   tfull[a]   one per CTA, for its own epilogue warps: the MMA thread commits to both
+//   tempty[a]  lives in the even CTA: the eight epilogue warps of the pair arrive on it
+constexpr int PAIR_BN = 256;
+constexpr int PAIR_ROWS = 2 * BM;
+// Three ring slots of two 64-k blocks each: the MMA thread commits (frees a slot) once per eight MMAs. Every
+// commit drains the pair's MMA pipeline, and with one per four MMAs (six slots of one block) the tensor pipe
+// measured 75 % busy against 94 % with this shape; two slots of three blocks prefetch too little.
+constexpr int PAIR_STAGES = 3;
+constexpr int PAIR_KSUB = 2;
+
+template <int STAGES, int KSUB>
+struct PairSmem {
+  static constexpr int A_BYTES = BM * BK * 2;             // this CTA's 128 rows of x, one block of 64 k
+  static constexpr int B_BYTES = (PAIR_BN / 2) * BK * 2;  // this CTA's 128 columns of y, one block of 64 k
+  static constexpr int SUB_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGE_BYTES = KSUB * SUB_BYTES;    // a ring slot holds KSUB blocks of 64 k
+  static constexpr int C_BYTES = 4 * 32 * 64 * 2 * 2;
+  static constexpr int RING_OFF = 0;
+  static constexpr int C_OFF = STAGES * STAGE_BYTES;
+  static constexpr int BAR_OFF = C_OFF + C_BYTES;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+template <int STAGES, int KSUB>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+    gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                     const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
+  using L = PairSmem<STAGES, KSUB>;
+  constexpr int BN = PAIR_BN;
+  const int num_slots = (p.num_kb + KSUB - 1) / KSUB;  // ring slots per work item
+  extern __shared__ uint8_t smem_raw[];
+  // The dynamic shared-memory window starts at the same offset in both CTAs, so the aligned offsets agree.
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bar_base = base + L::BAR_OFF;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
+  auto tempty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 2 + s); };
+  volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(base_ptr + L::BAR_OFF + 8 * (2 * STAGES + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + L::BAR_OFF + 8 * (2 * STAGES + 4) + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();  // 0: issues the MMAs; 1: stages and stores its half
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int per = p.sub_m * p.sub_n;
+  const int total_items = (p.n_tiles + p.n_fills) * per;
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(tfull_bar(s), 1);
+      mbar_init(tempty_bar(s), 8);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+    tma_prefetch_desc(&map_c);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_holder)), TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers are initialised before anything of ours can reach them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer (one per CTA)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      const int row_off = static_cast<int>(rank) * BM, col_off = static_cast<int>(rank) * (BN / 2);
+      for (int w = pair; w < total_items && ok; w += n_pairs) {
+        const Item it = decode_item<PAIR_ROWS, BN>(p, w);
+        if (!it.compute) continue;
+        for (int slot = 0; slot < num_slots; ++slot) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, TJX_ERR_WAIT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          // Blocks past the end of K are loaded all the same: the TMA fills them with zeros, which add nothing.
+          if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * L::STAGE_BYTES);
+          const uint32_t bar = cluster_map(full_bar(stage), 0);
+#pragma unroll
+          for (int sub = 0; sub < KSUB; ++sub) {
+            const int kb = slot * KSUB + sub;
+            const uint32_t a_dst = base + L::RING_OFF + stage * L::STAGE_BYTES + sub * L::SUB_BYTES;
+            const uint32_t b_dst = a_dst + L::A_BYTES;
+            tma_load_2d_pair(a_dst, &map_a, kb * BK, it.m0 + row_off, bar);
+            if (p.b_kmajor) {
+              tma_load_2d_pair(b_dst, &map_b, kb * BK, it.n0 + col_off, bar);
+            } else {
+#pragma unroll
+              for (int nb = 0; nb < BN / 2 / 64; ++nb)
+                tma_load_2d_pair(b_dst + nb * (64 * BK * 2), &map_b, it.n0 + col_off + nb * 64, kb * BK, bar);
+            }
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (even CTA only)
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = idesc_bf16_f32(PAIR_ROWS, BN, 0, p.b_kmajor ? 0 : 1);
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int w = pair; w < total_items && ok; w += n_pairs) {
+        const Item it = decode_item<PAIR_ROWS, BN>(p, w);
+        if (!it.compute) continue;
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, TJX_ERR_WAIT_TMEM_EMPTY)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int slot = 0; slot < num_slots; ++slot) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, TJX_ERR_WAIT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+#pragma unroll
+          for (int sub = 0; sub < KSUB; ++sub) {
+            const uint32_t a_addr = base + L::RING_OFF + stage * L::STAGE_BYTES + sub * L::SUB_BYTES;
+            const uint32_t b_addr = a_addr + L::A_BYTES;
+#pragma unroll
+            for (int kk = 0; kk < BK / 16; ++kk) {
+              const uint64_t a_desc = smem_desc_sw128(a_addr + kk * 32, 16, 1024);
+              const uint64_t b_desc = p.b_kmajor ? smem_desc_sw128(b_addr + kk * 32, 16, 1024)
+                                                 : smem_desc_sw128(b_addr + kk * (16 * 128), 64 * BK * 2, 1024);
+              mma_ss_pair(d_tmem, a_desc, b_desc, idesc, (slot | sub | kk) != 0 ? 1u : 0u);
+            }
+          }
+          // The slot is free in both CTAs once these MMAs have read it.
+          mma_commit_pair(cluster_map(empty_bar(stage), 0));
+          mma_commit_pair(cluster_map(empty_bar(stage), 1));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        mma_commit_pair(cluster_map(tfull_bar(acc), 0));
+        mma_commit_pair(cluster_map(tfull_bar(acc), 1));
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5 of each CTA)
+    const int q = warp & 3;
+    const int ew = warp - 2;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const uint32_t c_smem = base + L::C_OFF + ew * (2 * 32 * 128);
+    uint8_t* c_ptr = base_ptr + L::C_OFF + ew * (2 * 32 * 128);
+    int c_buf = 0;
+    for (int w = pair; w < total_items; w += n_pairs) {
+      const Item it = decode_item<PAIR_ROWS, BN>(p, w);
+      if (!it.valid) {
+        if (lane == 0 && p.status != nullptr) atomicCAS(p.status, 0, TJX_ERR_BAD_TABLE);
+        continue;
+      }
+      const int row0 = it.m0 + static_cast<int>(rank) * BM + q * 32;
+      if (!it.compute) {
+        zero_rows<BN>(p, row0, it.n0, lane);
+        continue;
+      }
+      const bool got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, TJX_ERR_WAIT_TMEM_FULL);
+      if (!__all_sync(0xFFFFFFFFu, got)) break;
+      tc_fence_after_sync();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      if (row0 < p.M) store_accumulator<BN>(p, &map_c, t_row, row0, it.n0, c_ptr, c_smem, c_buf, lane);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(cluster_map(tempty_bar(acc), 0));
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    }
+    if (lane == 0) tma_store_wait_all<0>();
+    __syncwarp();
+  }
+
+  // Neither CTA may leave, or free the pair's TMEM, while the other can still read its shared memory or TMEM.
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    if (*abort_flag) __nanosleep(100000);
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int STAGES, int KSUB>
+static int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
+                            const GemmParams& p, int grid, cudaStream_t stream) {
+  using L = PairSmem<STAGES, KSUB>;
+  auto kernel = gemm_pair_kernel<STAGES, KSUB>;
+  static bool configured[64] = {};
+  int dev = 0;
+  TJX_CUDA(cudaGetDevice(&dev));
+  if (!configured[dev & 63]) {
+    TJX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+    configured[dev & 63] = true;
+  }
+  kernel<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(ma, mb, mc, p);
+  TJX_CUDA(cudaGetLastError());
+  return 0;
+}
+
 }  // namespace tjx
 
 namespace tjx {
 static thread_local int g_gemm_cta_limit = 0;  // 0 = one CTA per SM
+static thread_local int g_gemm_pair_mode = 1;  // 1 = use CTA pairs whenever the tiles allow it
+}
+
+extern "C" int tjx_gemm_set_pair_mode(int mode) {
+  if (mode != 0 && mode != 1) return tjx::fail(TJX_E_ARG, "mode must be 0 (single CTAs) or 1 (pairs when possible)");
+  tjx::g_gemm_pair_mode = mode;
+  return 0;
 }
 
 extern "C" int tjx_gemm_set_cta_limit(int max_ctas) {
@@ -390,6 +650,8 @@ extern "C" int tjx_gemm_bf16(const void* x, const void* y, void* out, int M, int
   } else if (n_tiles <= 0) {
     return fail(TJX_E_ARG, "a tile table needs n_tiles > 0");
   }
+  // CTA pairs need whole 256 x 256 pieces of every user tile; an explicit stage count asks for the single-CTA ring.
+  const bool pair = g_gemm_pair_mode >= 1 && stages == 0 && tm % PAIR_ROWS == 0 && tn % PAIR_BN == 0;
   if (stages == 0) stages = 4;
   const int BN = (tn % 256 == 0) ? 256 : 128;
   if (!(stages == 4 || (BN == 128 && stages == 6) || (BN == 256 && stages == 3)))
@@ -398,7 +660,7 @@ extern "C" int tjx_gemm_bf16(const void* x, const void* y, void* out, int M, int
   GemmParams p{};
   p.M = M, p.N = N, p.K = K, p.tm = tm, p.tn = tn, p.tiles_m = tiles_m, p.tiles_n = tiles_n;
   p.band_tiles = std::max(1, 2048 / tn);
-  p.sub_m = (tm + BM - 1) / BM;
+  p.sub_m = pair ? tm / PAIR_ROWS : (tm + BM - 1) / BM;
   p.sub_n = (tn + BN - 1) / BN;
   p.n_tiles = n_tiles, p.n_fills = n_fills;
   p.tile_i = tile_i, p.tile_j = tile_j, p.fill_i = fill_i, p.fill_j = fill_j;
@@ -420,7 +682,7 @@ extern "C" int tjx_gemm_bf16(const void* x, const void* y, void* out, int M, int
   if (y_transposed) {
     const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
     const uint64_t strides[1] = {static_cast<uint64_t>(K) * 2};
-    const uint32_t box[2] = {BK, static_cast<uint32_t>(BN)};
+    const uint32_t box[2] = {BK, static_cast<uint32_t>(pair ? PAIR_BN / 2 : BN)};
     if (int rc = make_tensor_map(&mb, y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 2, dims, strides, box,
                                  CU_TENSOR_MAP_SWIZZLE_128B))
       return rc;
@@ -448,6 +710,11 @@ extern "C" int tjx_gemm_bf16(const void* x, const void* y, void* out, int M, int
   int grid = static_cast<int>(total_items < sm_count() ? total_items : sm_count());
   if (g_gemm_cta_limit > 0 && grid > g_gemm_cta_limit) grid = g_gemm_cta_limit;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (pair) {
+    int pairs = static_cast<int>(total_items < sm_count() / 2 ? total_items : sm_count() / 2);
+    if (g_gemm_cta_limit > 0) pairs = std::max(1, std::min(pairs, g_gemm_cta_limit / 2));
+    return launch_gemm_pair<PAIR_STAGES, PAIR_KSUB>(ma, mb, mc, p, 2 * pairs, s);
+  }
   if (BN == 256) {
     if (stages == 3) return launch_gemm<256, 3>(ma, mb, mc, p, grid, s);
     return launch_gemm<256, 4>(ma, mb, mc, p, grid, s);

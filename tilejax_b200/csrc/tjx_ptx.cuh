@@ -276,6 +276,81 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
                : "memory");
 }
 
+// ---------------------------------------------------------------------------------------------- CTA pairs
+//
+// The two-SM forms (cta_group::2): a cluster of two CTAs shares one MMA. Each CTA stages its own 128 rows of A
+// and its own half of B's columns at the same shared-memory offsets; the even CTA of the pair issues the MMA,
+// which reads both CTAs' shared memory and writes 128 accumulator rows into each CTA's TMEM.
+
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+// The shared::cluster address of this CTA's shared-memory location `addr` as it appears in CTA `rank`.
+__device__ __forceinline__ uint32_t cluster_map(uint32_t addr, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(addr), "r"(rank));
+  return out;
+}
+
+// Every thread of every CTA of the cluster calls this (a full barrier with release/acquire ordering).
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// One arrival on a barrier anywhere in the cluster (address from cluster_map).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+
+// 2-D tile load into THIS CTA's shared memory whose bytes are counted on a barrier that may live in the peer
+// CTA of the pair (address from cluster_map). Each CTA fetches only what it stages itself.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* m, int x, int y,
+                                                 uint32_t cluster_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];"
+      :
+      : "r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(cluster_bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+// One warp of EACH CTA of the pair executes these, with the same `dst` offset.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst), "r"(cols)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+
+// D[tmem of both CTAs] (+)= A * B over the pair (M = 256: 128 rows per CTA); one thread of the even CTA issues.
+__device__ __forceinline__ void mma_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// One arrival on `cluster_bar` (any CTA of the pair) once every pair MMA this thread issued before has completed.
+__device__ __forceinline__ void mma_commit_pair(uint32_t cluster_bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar)
+               : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------- TMEM <-> regs
 
 // 32 lanes x 32 columns of 32-bit: thread i of the warp gets lane (base lane + i), columns c..c+31.

@@ -132,6 +132,11 @@ def set_gemm_cta_limit(max_ctas: int) -> None:
     check(library().tjx_gemm_set_cta_limit(int(max_ctas)))
 
 
+def set_gemm_pair_mode(pairs: bool) -> None:
+    """Let this thread's GEMM launches use one MMA per pair of SMs when the tiles allow it (the default), or never."""
+    check(library().tjx_gemm_set_pair_mode(int(pairs)))
+
+
 def matmul(x: torch.Tensor, y: torch.Tensor, tm: int = 512, tn: int = 512, tk: int = 512, **kw) -> torch.Tensor:
     """The `matmul` loop nest (examples/matmul.py:22-35): tiles clipped to the matrix as its prologue does."""
     M, K = x.shape
