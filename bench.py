@@ -272,7 +272,7 @@ def extra_workloads(device, pk: dict, pk_kind: str, only: str | None = None, ite
     nbytes = float(lengths.sum()) * 4096.0
     gbs = nbytes / ms / 1e6
     out["paged_gqa_decode_B64_H32_Hkv8_D128_page16"] = {
-        "ms": ms, "value": gbs, "unit": "GB/s", "algorithmic_bytes": nbytes, "includes": "step-table kernel + decode + merge",
+        "ms": ms, "value": gbs, "unit": "GB/s", "algorithmic_bytes": nbytes, "includes": "step-table kernel + decode (the merge of partials is fused into it)",
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak,
                      "peak_kind": pk_kind, "traffic": None}}
     ops.device_status()

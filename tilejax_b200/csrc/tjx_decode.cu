@@ -1,13 +1,14 @@
 // Ragged paged GQA decode attention on sm_100a, bound by HBM bandwidth: every valid K/V page is read once,
-// with 16-byte coalesced loads straight into registers, f32 FMAs and warp-shuffle reductions (no tensor cores).
+// by TMA straight into shared memory, with f32 FMAs on the CUDA cores (no tensor cores: four query heads per KV
+// head is far too little reuse).
 //
 // The work is the device step table (tjx_steps.cu): the steps that run, one K/V page each, in tile (sequence)
-// order. It is cut into chunks of CHUNK consecutive steps, a CTA per chunk, so ragged lengths balance by
-// themselves. Inside a CTA warp w owns KV head w and its 4 query heads: a lane holds 8 of the 128 head
-// dimensions (one 16-byte load) for one of two tokens, so one warp-wide load covers two tokens' K (or V) rows
-// of that head. A chunk may cover the end of one sequence and the start of the next; every (sequence, chunk)
-// piece writes an online-softmax partial (max, sum, accumulator) to scratch, and a small second kernel merges
-// a sequence's partials, normalises and writes bf16.
+// order. It is cut into chunks of CHUNK consecutive steps, a CTA per (chunk, group of 4 KV heads), so ragged
+// lengths balance by themselves. Inside a CTA warp w owns one KV head and its G query heads. A chunk may cover
+// the end of one sequence and the start of the next; a (sequence, chunk) piece that is the sequence's only one
+// is normalised and written at once; otherwise it writes an online-softmax partial (max, sum, accumulator) to
+// scratch and counts itself on the sequence's arrival counter, and the warp that arrives last merges the
+// sequence's partials, normalises and writes bf16 — no second kernel.
 //
 // Follows `paged_gqa_decode` (examples/decode.py:199-223): positions >= lengths[b] masked to -1e30, the
 // probabilities rounded to bf16 before multiplying V, 1 / max(row_sum, 1e-30), zeros for an empty sequence.
@@ -24,19 +25,18 @@ namespace tjx {
 
 int launch_build_steps_lengths(const int32_t* lengths, int n_lengths, const int32_t* tile_values, int tiles,
                                int blocks, int value0, int value_step, int32_t* step_tile, int32_t* step_code,
-                               int32_t* step_count, int32_t* tile_first, cudaStream_t stream);
+                               int32_t* step_count, int32_t* tile_first, int32_t* zero_words, int n_zero,
+                               cudaStream_t stream);
 
 constexpr int DEC_D = 128;         // head dimension
-constexpr int DEC_SUB = 8;         // tokens per micro-step (a page is a whole number of these)
+constexpr int DEC_SUB = 16;        // tokens per micro-step (a page is a whole number of these)
 constexpr int DEC_STAGES = 2;      // ring slots per warp
-constexpr int DEC_STAGE_BYTES = DEC_SUB * DEC_D * 2 * 2;  // K and V of one micro-step for one KV head
+constexpr int DEC_HALF_BYTES = DEC_SUB * 64 * 2;           // one TMA box: 16 tokens x 64 dims, 128-byte rows
+constexpr int DEC_STAGE_BYTES = 4 * DEC_HALF_BYTES;        // K (two dim halves) and V (two) of one micro-step
 constexpr int DEC_CHUNK = 16;      // steps (pages) per CTA
 constexpr int DEC_WARPS = 4;       // KV heads per CTA
 constexpr float DEC_MASK = -1e30f;
-// Shared memory per warp: the K/V ring, the partial-score scratch [4 pairs][G][32], P [8][G] and G rescale factors.
-__host__ __device__ constexpr int dec_warp_bytes(int g) {
-  return (DEC_STAGES * DEC_STAGE_BYTES + 4 * g * 32 * 4 + 8 * g * 4 + 8 * 4 + 127) / 128 * 128;  // TMA wants 128-byte slots
-}
+constexpr int DEC_SMEM = DEC_WARPS * DEC_STAGES * DEC_STAGE_BYTES + 1024;  // + slack to align the ring to 1024
 
 struct DecodeParams {
   const __nv_bfloat16* q;        // [B, 1, H, D]
@@ -51,35 +51,13 @@ struct DecodeParams {
   float* ws_m;                   // [B, slots, H]
   float* ws_l;                   // [B, slots, H]
   float* ws_acc;                 // [B, slots, H, D]
+  int* arrivals;                 // [B, Hkv] pieces of a sequence's KV head that have written their partial
   __nv_bfloat16* out;            // [B, 1, H, D]
   int B, H, Hkv, page_size, pages_per_seq, num_pages, slots;
   int* status;
 };
 
 
-// Two f32 in one 64-bit register pair, for the packed FMA of sm_100 (one instruction, two lanes of math).
-__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
-__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
-  uint64_t d;
-  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-// A register holding two bf16 -> the two values as packed f32 (element 0 in the low half).
-__device__ __forceinline__ uint64_t bf16x2_to_f32x2(uint32_t u) {
-  return pack2(__uint_as_float(u << 16), __uint_as_float(u & 0xFFFF0000u));
-}
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -88,53 +66,138 @@ __device__ __forceinline__ float ex2(float x) {
 
 constexpr float DEC_LOG2E = 1.4426950408889634f;
 
-// One warp = one KV head and its G query heads over the chunk's steps. Lane = (half, dl): `half` picks one of
-// the two tokens a 512-byte row pair holds, dl (0..15) the 8 head dimensions 8 dl .. 8 dl + 7.
-//
-// Data path: the warp owns a ring of DEC_STAGES shared-memory slots; lane 0 issues two TMA tile loads per
-// micro-step (8 tokens of K and of V for this KV head: a [8 tokens x 1 head x 128 dims] box of the 3-D view
-// [tokens, heads, dims] of the page pool, 2 KB each) one micro-step ahead, completing on the slot's mbarrier;
-// the lanes then read their 16 bytes per token with conflict-free LDS.128.
-//
-// Scores: each lane forms its 8-dimension partial dot products for the G heads with packed FMAs and stores them
-// to a per-warp scratch laid out [token pair][head][half][dl], one bank per lane. After the 4 token pairs, lane
-// (h, tok) = (lane / 8, lane % 8) sums the 16 partials of ITS (head, token) — four LDS.128 and 15 adds replace a
-// 16-step shuffle butterfly per token pair — so every lane owns one score (two for G = 8) and the softmax does no
-// redundant work. Probabilities and rescale factors go back through shared memory ([token][head], one LDS.128
-// per token) for the P V accumulation, again with packed FMAs.
+// Four 8x8 b16 matrices from shared memory: lane i gives the address of row i % 8 of matrix i / 8; register j
+// of every lane then holds, of matrix j, row lane / 4, columns 2 (lane % 4) and + 1 — or with .trans, column
+// lane / 4, rows 2 (lane % 4) and + 1.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+// D (16 x 8, f32) += A (16 x 16, bf16, rows) * B (16 x 8, bf16, columns). Rows 8..15 of A are always zero here
+// (a1 = a3 = 0): the rows are the G <= 8 query heads of one KV head.
+__device__ __forceinline__ void mma_16x8x16(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+
+// Merge the partials of the G query heads h0 .. h0 + G - 1 of sequence b (n partials each, in slots 0..n-1),
+// normalise and write bf16. One warp; a lane holds 4 head dimensions of every head, and the G heads go through
+// the loop together so that G times as many loads are in flight. The partials were written by other CTAs: they
+// are read past L1.
 template <int G>
-__global__ void __launch_bounds__(DEC_WARPS * 32, G <= 4 ? 4 : 2)
+__device__ __forceinline__ void decode_merge_heads(const DecodeParams& p, int b, int h0, int n, int lane) {
+  const size_t base = static_cast<size_t>(b) * p.slots * p.H + h0;
+  float mx[G], lsum[G];
+  float4 o[G];
+#pragma unroll
+  for (int h = 0; h < G; ++h) mx[h] = DEC_MASK, lsum[h] = 0.f, o[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+  // Lane i holds partial i's statistics (32 at a time).
+  for (int i0 = 0; i0 < n; i0 += 32)
+    if (i0 + lane < n) {
+#pragma unroll
+      for (int h = 0; h < G; ++h)
+        mx[h] = fmaxf(mx[h], __ldcg(p.ws_m + base + static_cast<size_t>(i0 + lane) * p.H + h));
+    }
+#pragma unroll
+  for (int h = 0; h < G; ++h)
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xFFFFFFFFu, mx[h], d));
+  for (int i0 = 0; i0 < n; i0 += 32) {
+    float w_mine[G];
+#pragma unroll
+    for (int h = 0; h < G; ++h) w_mine[h] = 0.f;
+    if (i0 + lane < n) {
+      const size_t idx = base + static_cast<size_t>(i0 + lane) * p.H;
+#pragma unroll
+      for (int h = 0; h < G; ++h) {
+        w_mine[h] = __expf(__ldcg(p.ws_m + idx + h) - mx[h]);
+        lsum[h] += w_mine[h] * __ldcg(p.ws_l + idx + h);
+      }
+    }
+    const int cnt = min(32, n - i0);
+#pragma unroll 4
+    for (int i = 0; i < cnt; ++i) {
+      const size_t idx = base + static_cast<size_t>(i0 + i) * p.H;
+#pragma unroll
+      for (int h = 0; h < G; ++h) {
+        const float w = __shfl_sync(0xFFFFFFFFu, w_mine[h], i);
+        const float4 a = __ldcg(reinterpret_cast<const float4*>(p.ws_acc + (idx + h) * DEC_D + lane * 4));
+        o[h].x = fmaf(w, a.x, o[h].x), o[h].y = fmaf(w, a.y, o[h].y);
+        o[h].z = fmaf(w, a.z, o[h].z), o[h].w = fmaf(w, a.w, o[h].w);
+      }
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < G; ++h) {
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) lsum[h] += __shfl_xor_sync(0xFFFFFFFFu, lsum[h], d);
+    const float inv = 1.0f / fmaxf(lsum[h], 1e-30f);
+    uint2 r;
+    r.x = pack_bf16(o[h].x * inv, o[h].y * inv);
+    r.y = pack_bf16(o[h].z * inv, o[h].w * inv);
+    *reinterpret_cast<uint2*>(p.out + (static_cast<size_t>(b) * p.H + h0 + h) * DEC_D + lane * 4) = r;
+  }
+}
+
+// One warp = one KV head and its G query heads over the chunk's steps, 16 tokens (a micro-step) at a time.
+//
+// Data path: the warp owns a ring of DEC_STAGES shared-memory slots; lane 0 issues four TMA tile loads per
+// micro-step — K and V of 16 tokens of this KV head, each as two boxes [16 tokens x 1 head x 64 dims] of the 3-D
+// view [tokens, heads, dims] of the page pool, 128-byte swizzled — one micro-step ahead, completing on the slot's
+// mbarrier. The page bytes never pass through registers on their way in.
+//
+// Arithmetic: warp-level mma.sync (m16n8k16, bf16 x bf16 -> f32). The 16 rows of the A operand are the query
+// heads (G of them, the rest zero), so S = Q K^T for 16 tokens is 2 x 8 MMAs whose B fragments come straight from
+// the K slot with ldmatrix, the probabilities — rounded to bf16, as the reference rounds them — are already in A
+// fragment layout when they leave the softmax (no shared-memory round trip), and O += P V is 16 MMAs with B
+// fragments from the V slot with ldmatrix.trans. Lane (g, t) = (lane / 4, lane % 4) holds of head g: scores of
+// tokens 2t, 2t+1, 8+2t, 9+2t and output dims 8 n + 2t, + 1 for n = 0..15. A fifth-generation (tcgen05) MMA needs
+// 64 or 128 rows; with at most 8 query heads per KV head this path stays bound by HBM with the warp-level MMA.
+template <int G>
+__global__ void __launch_bounds__(DEC_WARPS * 32, 3)
     decode_chunks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                          const DecodeParams p) {
-  extern __shared__ __align__(128) uint8_t dec_smem[];
+  extern __shared__ uint8_t dec_smem_raw[];
   __shared__ __align__(8) uint64_t dec_bars[DEC_WARPS * DEC_STAGES];
   __shared__ int dec_abort;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kvh = blockIdx.y * DEC_WARPS + warp;
-  const int n_steps = p.step_count[0];
   if (threadIdx.x == 0) {
     for (int i = 0; i < DEC_WARPS * DEC_STAGES; ++i) mbar_init(smem_u32(&dec_bars[i]), 1);
     dec_abort = 0;
     mbar_fence_init();
+    tma_prefetch_desc(&map_k);
+    tma_prefetch_desc(&map_v);
   }
+  // Launched with programmatic stream serialisation: everything above overlaps the step-table kernel; nothing
+  // that kernel writes (tables, cleared arrival counters) is touched before this returns.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int n_steps = p.step_count[0];
   __syncthreads();
   if (kvh >= p.Hkv) return;
 
-  const int half = lane >> 4;
-  const int dl = lane & 15;
-  const int d0 = dl * 8;
-  constexpr int IT = DEC_SUB / 2;           // token pairs per micro-step
-  constexpr int NSC = G > 4 ? G / 4 : 1;    // scores a lane owns per micro-step
-  // The (head, token) this lane owns: head lane / 8 (+ 4 j), token lane % 8; lanes beyond G heads own nothing.
-  const int own_tok = lane & 7;
-  const int own_h = lane >> 3;
-
-  uint8_t* warp_smem = dec_smem + warp * dec_warp_bytes(G);
-  const uint32_t ring = smem_u32(warp_smem);
-  float* pb = reinterpret_cast<float*>(warp_smem + DEC_STAGES * DEC_STAGE_BYTES);  // [IT][G][32] partials
-  float* pbuf = pb + IT * G * 32;                                                   // [8 tokens][G] P
-  float* abuf = pbuf + 8 * G;                                                       // [G] rescale factors
+  const int g = lane >> 2;  // the query head (row) this lane holds
+  const int t = lane & 3;
+  const uint32_t ring = ((smem_u32(dec_smem_raw) + 1023u) & ~1023u) + warp * (DEC_STAGES * DEC_STAGE_BYTES);
   auto bar = [&](int stage) { return smem_u32(&dec_bars[warp * DEC_STAGES + stage]); };
+  // ldmatrix addressing. A box is [16 tokens][128 bytes], its 16-byte units XOR-swizzled with token % 8.
+  //   K (plain): matrix j of a load = dims 8 j .. 8 j + 7 of 8 tokens: lane i points at token i % 8, unit i / 8.
+  //   V (trans): matrices = (tokens 0-7 | 8-15) x (dims n | n + 8): lane i points at token i % 8 + 8 (i / 8 % 2),
+  //              unit i / 16.
+  const int lrow = lane & 7;
+  const uint32_t k_lane = lrow * 128;
+  const int k_unit = lane >> 3;
+  const uint32_t v_lane = (lrow + 8 * ((lane >> 3) & 1)) * 128;
+  const int v_unit = lane >> 4;
 
   int n = 0;  // micro-steps consumed by this warp so far (ring position and barrier phase)
   bool ok = true;
@@ -156,46 +219,52 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, G <= 4 ? 4 : 2)
     }
   }
 
-  uint64_t q2[G][4];    // this lane's 8 dimensions of each query head, packed in pairs
-  uint64_t acc2[G][4];  // P V accumulator, same layout
-  float m_run[NSC], l_run[NSC];  // running max (log2 units; same in the 8 lanes of a head) and this lane's sum
+  uint32_t qa[8][2];   // A fragments of Q: k-step j covers dims 16 j .. 16 j + 15; [0] = dims + 2t, [1] = dims + 8 + 2t
+  float o[16][4];      // O fragments: [n][0..1] = head g, dims 8 n + 2t, + 1 ([2..3] belong to the zero rows)
+  float m_run = DEC_MASK * DEC_LOG2E, l_run = 0.f;  // head g's running max (log2 units) and this lane's part of its sum
   int cur = -1;
 
   auto flush = [&]() {
     if (cur < 0) return;
-    const int slot = chunk - p.tile_first[cur] / DEC_CHUNK;
+    const int first = p.tile_first[cur], next = p.tile_first[cur + 1];
+    const int pieces = (next - 1) / DEC_CHUNK - first / DEC_CHUNK + 1;  // a tile takes at least one step
+    const int slot = chunk - first / DEC_CHUNK;
     const size_t base = (static_cast<size_t>(cur) * p.slots + slot) * p.H + kvh * G;
+    float l_all = l_run;
+    l_all += __shfl_xor_sync(0xFFFFFFFFu, l_all, 1);
+    l_all += __shfl_xor_sync(0xFFFFFFFFu, l_all, 2);
+    if (g < G) {
+      if (pieces == 1) {
+        // The sequence's only piece: its partial is the result.
+        const float inv = 1.0f / fmaxf(l_all, 1e-30f);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(p.out + (static_cast<size_t>(cur) * p.H + kvh * G + g) * DEC_D);
 #pragma unroll
-    for (int j = 0; j < NSC; ++j) {
-      float l_all = l_run[j];
-      l_all += __shfl_xor_sync(0xFFFFFFFFu, l_all, 1);
-      l_all += __shfl_xor_sync(0xFFFFFFFFu, l_all, 2);
-      l_all += __shfl_xor_sync(0xFFFFFFFFu, l_all, 4);
-      const int h = own_h + 4 * j;
-      if (own_tok == 0 && h < G) {  // the partials keep the max in natural-log units
-        p.ws_m[base + h] = m_run[j] * (1.0f / DEC_LOG2E);
-        p.ws_l[base + h] = l_all;
+        for (int nt = 0; nt < 16; ++nt) dst[nt * 4 + t] = pack_bf16(o[nt][0] * inv, o[nt][1] * inv);
+      } else {
+        if (t == 0) {  // the partials keep the max in natural-log units
+          p.ws_m[base + g] = m_run * (1.0f / DEC_LOG2E);
+          p.ws_l[base + g] = l_all;
+        }
+        float2* dst = reinterpret_cast<float2*>(p.ws_acc + (base + g) * DEC_D);
+#pragma unroll
+        for (int nt = 0; nt < 16; ++nt) dst[nt * 4 + t] = make_float2(o[nt][0], o[nt][1]);
       }
     }
-#pragma unroll
-    for (int h = 0; h < G; ++h) {
-      float a[8];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float lo, hi;
-        unpack2(acc2[h][j], lo, hi);
-        a[2 * j] = lo + __shfl_xor_sync(0xFFFFFFFFu, lo, 16);
-        a[2 * j + 1] = hi + __shfl_xor_sync(0xFFFFFFFFu, hi, 16);
-      }
-      if (half == 0) {
-        float4* dst = reinterpret_cast<float4*>(p.ws_acc + (base + h) * DEC_D + d0);
-        dst[0] = make_float4(a[0], a[1], a[2], a[3]);
-        dst[1] = make_float4(a[4], a[5], a[6], a[7]);
+    if (pieces > 1) {
+      // Count this piece; whoever counts last finds every partial of the sequence's KV head written and merges.
+      __threadfence();
+      __syncwarp();
+      int last = 0;
+      if (lane == 0) last = atomicAdd(p.arrivals + cur * p.Hkv + kvh, 1) == pieces - 1;
+      last = __shfl_sync(0xFFFFFFFFu, last, 0);
+      if (last) {
+        __threadfence();
+        decode_merge_heads<G>(p, cur, kvh * G, pieces, lane);
       }
     }
   };
 
-  // The next micro-step (step, 8-token sub-block) that has data after (step, sub); step == n_here if none.
+  // The next micro-step (step, 16-token sub-block) that has data after (step, sub); step == n_here if none.
   auto next_data = [&](int step, int sub, int& nstep, int& nsub) {
     nstep = step, nsub = sub + DEC_SUB;
     for (;;) {
@@ -219,7 +288,9 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, G <= 4 ? 4 : 2)
       const int token = page * p.page_size + sub;
       mbar_expect_tx(bar(stage), DEC_STAGE_BYTES);
       tma_load_3d(dst, &map_k, 0, kvh, token, bar(stage));
-      tma_load_3d(dst + DEC_STAGE_BYTES / 2, &map_v, 0, kvh, token, bar(stage));
+      tma_load_3d(dst + DEC_HALF_BYTES, &map_k, 64, kvh, token, bar(stage));
+      tma_load_3d(dst + 2 * DEC_HALF_BYTES, &map_v, 0, kvh, token, bar(stage));
+      tma_load_3d(dst + 3 * DEC_HALF_BYTES, &map_v, 64, kvh, token, bar(stage));
     }
   };
 
@@ -235,23 +306,22 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, G <= 4 ? 4 : 2)
   }
 
   for (int step = 0; step < n_here && ok; ++step) {
-    const int t = __shfl_sync(0xFFFFFFFFu, my_tile, step);
+    const int tile = __shfl_sync(0xFFFFFFFFu, my_tile, step);
     const int code = __shfl_sync(0xFFFFFFFFu, my_code, step);
     const int len = __shfl_sync(0xFFFFFFFFu, my_len, step);
-    if (t != cur) {
+    if (tile != cur) {
       flush();
-      cur = t;
-      const __nv_bfloat16* qp = p.q + (static_cast<size_t>(t) * p.H + kvh * G) * DEC_D + d0;
+      cur = tile;
+      const uint32_t* qp =
+          reinterpret_cast<const uint32_t*>(p.q + (static_cast<size_t>(tile) * p.H + kvh * G + (g < G ? g : 0)) * DEC_D);
 #pragma unroll
-      for (int h = 0; h < G; ++h) {
-        const uint4 u = *reinterpret_cast<const uint4*>(qp + h * DEC_D);
-        q2[h][0] = bf16x2_to_f32x2(u.x), q2[h][1] = bf16x2_to_f32x2(u.y);
-        q2[h][2] = bf16x2_to_f32x2(u.z), q2[h][3] = bf16x2_to_f32x2(u.w);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc2[h][j] = 0ull;
+      for (int j = 0; j < 8; ++j) {
+        qa[j][0] = g < G ? qp[8 * j + t] : 0u;
+        qa[j][1] = g < G ? qp[8 * j + 4 + t] : 0u;
       }
 #pragma unroll
-      for (int j = 0; j < NSC; ++j) m_run[j] = DEC_MASK * DEC_LOG2E, l_run[j] = 0.f;
+      for (int nt = 0; nt < 16; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+      m_run = DEC_MASK * DEC_LOG2E, l_run = 0.f;
     }
     if (code & 4) continue;  // an empty step: no position to read
     const int pg = code >> 3;
@@ -270,148 +340,66 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, G <= 4 ? 4 : 2)
         break;
       }
       ++n;
-      const uint8_t* kbuf = warp_smem + stage * DEC_STAGE_BYTES + lane * 16;
-      const uint8_t* vbuf = kbuf + DEC_STAGE_BYTES / 2;
+      const uint32_t kbase = ring + stage * DEC_STAGE_BYTES;
+      const uint32_t vbase = kbase + 2 * DEC_HALF_BYTES;
 
-      // Partial dot products over this lane's 8 dimensions -> scratch [pair][head][lane].
+      // S = Q K^T: two tiles of 8 tokens; [tile][0..1] = head g, tokens 8 tile + 2t, + 1.
+      float sc[2][4];
 #pragma unroll
-      for (int i = 0; i < IT; ++i) {
-        const uint4 kk = *reinterpret_cast<const uint4*>(kbuf + i * 512);
-        const uint64_t k0 = bf16x2_to_f32x2(kk.x), k1 = bf16x2_to_f32x2(kk.y);
-        const uint64_t k2 = bf16x2_to_f32x2(kk.z), k3 = bf16x2_to_f32x2(kk.w);
+      for (int tl = 0; tl < 2; ++tl) {
+        sc[tl][0] = sc[tl][1] = sc[tl][2] = sc[tl][3] = 0.f;
 #pragma unroll
-        for (int h = 0; h < G; ++h) {
-          uint64_t a = mul2(q2[h][0], k0);
-          a = fma2(q2[h][1], k1, a), a = fma2(q2[h][2], k2, a), a = fma2(q2[h][3], k3, a);
-          float lo, hi;
-          unpack2(a, lo, hi);
-          pb[(i * G + h) * 32 + lane] = lo + hi;
+        for (int x = 0; x < 4; ++x) {  // a load covers dims 32 x .. 32 x + 31: k-steps 2x and 2x + 1
+          const int unit = (4 * x + k_unit) & 7;          // the 16-byte unit within the 64-dim half
+          const uint32_t addr = kbase + (x >> 1) * DEC_HALF_BYTES + tl * 1024 + k_lane + ((unit ^ lrow) << 4);
+          uint32_t b[4];
+          ldmatrix_x4(addr, b);
+          mma_16x8x16(sc[tl], qa[2 * x][0], qa[2 * x][1], b[0], b[1]);
+          mma_16x8x16(sc[tl], qa[2 * x + 1][0], qa[2 * x + 1][1], b[2], b[3]);
         }
       }
-      __syncwarp();
-
-      // This lane's score(s): the 16 partials of (head own_h + 4 j, token own_tok), then the online softmax of
-      // that head over the sub-block's 8 tokens (the 8 lanes of a head).
-      bool grew = false;
+      // Online softmax of head g over the 16 tokens (4 per lane, the 4 lanes of a quad share the head).
+      float s4[4] = {sc[0][0], sc[0][1], sc[1][0], sc[1][1]};
 #pragma unroll
-      for (int j = 0; j < NSC; ++j) {
-        const int h = own_h + 4 * j;
-        float score = DEC_MASK * DEC_LOG2E;
-        if (h < G) {
-          // The 32 lanes read 32 different 64-byte runs that all start on bank 0 or 16: each lane starts at a
-          // different 16-byte unit of its run, so that one LDS.128 spreads over all banks.
-          const float4* src = reinterpret_cast<const float4*>(pb + ((own_tok >> 1) * G + h) * 32 + (own_tok & 1) * 16);
-          const int rot = (h + (own_tok >> 1)) & 3;
-          const float4 a = src[rot], b = src[(rot + 1) & 3], c = src[(rot + 2) & 3], d = src[(rot + 3) & 3];
-          const float sum = ((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w)) +
-                            (((c.x + c.y) + (c.z + c.w)) + ((d.x + d.y) + (d.z + d.w)));
-          if (base_pos + own_tok < len) score = sum * DEC_LOG2E;
-        }
-        float mx = score;
-        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
-        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 4));
-        grew |= mx > m_run[j];
-        const float m_new = fmaxf(m_run[j], mx);
-        const float alpha = ex2(m_run[j] - m_new);
-        m_run[j] = m_new;
-        const float pr = ex2(score - m_new);
-        l_run[j] = l_run[j] * alpha + pr;
-        if (h < G) {
-          pbuf[own_tok * G + h] = __bfloat162float(__float2bfloat16_rn(pr));  // P is rounded before P V
-          if (own_tok == 0) abuf[h] = alpha;
-        }
+      for (int i = 0; i < 4; ++i) {
+        const int tok = (i >> 1) * 8 + 2 * t + (i & 1);
+        s4[i] = base_pos + tok < len ? s4[i] * DEC_LOG2E : DEC_MASK * DEC_LOG2E;
       }
-      const bool rescale = __any_sync(0xFFFFFFFFu, grew);
-      __syncwarp();
-
-      if (rescale) {
+      float mx = fmaxf(fmaxf(s4[0], s4[1]), fmaxf(s4[2], s4[3]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
+      const float m_new = fmaxf(m_run, mx);
+      const float alpha = ex2(m_run - m_new);
+      const bool grew = m_new > m_run;
+      m_run = m_new;
+      const float p0 = ex2(s4[0] - m_new), p1 = ex2(s4[1] - m_new), p2 = ex2(s4[2] - m_new), p3 = ex2(s4[3] - m_new);
+      l_run = l_run * alpha + ((p0 + p1) + (p2 + p3));
+      const uint32_t pa0 = pack_bf16(p0, p1), pa2 = pack_bf16(p2, p3);  // P is rounded before P V
+      if (__any_sync(0xFFFFFFFFu, grew)) {
 #pragma unroll
-        for (int h = 0; h < G; ++h) {
-          const float a = abuf[h];
-          const uint64_t a2 = pack2(a, a);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) acc2[h][j] = mul2(acc2[h][j], a2);
-        }
+        for (int nt = 0; nt < 16; ++nt) o[nt][0] *= alpha, o[nt][1] *= alpha;
       }
-      // P V: each lane reads the probabilities of every head for its own token.
+      // O += P V: a load covers dims 16 x .. 16 x + 15 (two output tiles) of all 16 tokens.
 #pragma unroll
-      for (int i = 0; i < IT; ++i) {
-        const uint4 vv = *reinterpret_cast<const uint4*>(vbuf + i * 512);
-        const uint64_t v0 = bf16x2_to_f32x2(vv.x), v1 = bf16x2_to_f32x2(vv.y);
-        const uint64_t v2 = bf16x2_to_f32x2(vv.z), v3 = bf16x2_to_f32x2(vv.w);
-        float prs[G];
-        if constexpr (G >= 4) {
-#pragma unroll
-          for (int h4 = 0; h4 < G / 4; ++h4) {
-            const float4 t4 = reinterpret_cast<const float4*>(pbuf + (2 * i + half) * G)[h4];
-            prs[4 * h4] = t4.x, prs[4 * h4 + 1] = t4.y, prs[4 * h4 + 2] = t4.z, prs[4 * h4 + 3] = t4.w;
-          }
-        } else {
-#pragma unroll
-          for (int h = 0; h < G; ++h) prs[h] = pbuf[(2 * i + half) * G + h];
-        }
-#pragma unroll
-        for (int h = 0; h < G; ++h) {
-          const float pr = prs[h];
-          const uint64_t p2 = pack2(pr, pr);
-          acc2[h][0] = fma2(p2, v0, acc2[h][0]), acc2[h][1] = fma2(p2, v1, acc2[h][1]);
-          acc2[h][2] = fma2(p2, v2, acc2[h][2]), acc2[h][3] = fma2(p2, v3, acc2[h][3]);
-        }
+      for (int x = 0; x < 8; ++x) {
+        const int unit = (2 * x + v_unit) & 7;
+        const uint32_t addr = vbase + (x >> 2) * DEC_HALF_BYTES + v_lane + ((unit ^ lrow) << 4);
+        uint32_t b[4];
+        ldmatrix_x4_trans(addr, b);
+        mma_16x8x16(o[2 * x], pa0, pa2, b[0], b[1]);
+        mma_16x8x16(o[2 * x + 1], pa0, pa2, b[2], b[3]);
       }
-      __syncwarp();  // every lane is done with the slot and the scratch before they are refilled
+      __syncwarp();  // every lane is done with the slot before it is refilled
     }
   }
   if (ok) flush();
   }  // chunks
 }
 
-// Merge a sequence's partials: one warp per (sequence, query head), a lane per 4 head dimensions.
-__global__ void __launch_bounds__(256) decode_combine_kernel(const DecodeParams p) {
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  if (warp >= p.B * p.H) return;
-  const int b = warp / p.H, h = warp - b * p.H;
-  const int first = p.tile_first[b], next = p.tile_first[b + 1];
-  const int n = (next - 1) / DEC_CHUNK - first / DEC_CHUNK + 1;  // a tile takes at least one step
-  const size_t base = static_cast<size_t>(b) * p.slots * p.H + h;
-  // Lane i holds partial i's statistics (32 at a time), so the maxima and weights come from a few parallel loads
-  // and the accumulator rows stream in independent, unrolled loads.
-  float mx = DEC_MASK;
-  for (int i0 = 0; i0 < n; i0 += 32)
-    if (i0 + lane < n) mx = fmaxf(mx, p.ws_m[base + static_cast<size_t>(i0 + lane) * p.H]);
-#pragma unroll
-  for (int d = 16; d >= 1; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, d));
-  float lsum = 0.f;
-  float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int i0 = 0; i0 < n; i0 += 32) {
-    float w_mine = 0.f;
-    if (i0 + lane < n) {
-      const size_t idx = base + static_cast<size_t>(i0 + lane) * p.H;
-      w_mine = __expf(p.ws_m[idx] - mx);
-      lsum += w_mine * p.ws_l[idx];
-    }
-    const int cnt = min(32, n - i0);
-#pragma unroll 8
-    for (int i = 0; i < cnt; ++i) {
-      const float w = __shfl_sync(0xFFFFFFFFu, w_mine, i);
-      const size_t idx = base + static_cast<size_t>(i0 + i) * p.H;
-      const float4 a = *reinterpret_cast<const float4*>(p.ws_acc + idx * DEC_D + lane * 4);
-      o.x = fmaf(w, a.x, o.x), o.y = fmaf(w, a.y, o.y), o.z = fmaf(w, a.z, o.z), o.w = fmaf(w, a.w, o.w);
-    }
-  }
-#pragma unroll
-  for (int d = 16; d >= 1; d >>= 1) lsum += __shfl_xor_sync(0xFFFFFFFFu, lsum, d);
-  const float inv = 1.0f / fmaxf(lsum, 1e-30f);
-  uint2 r;
-  r.x = pack_bf16(o.x * inv, o.y * inv);
-  r.y = pack_bf16(o.z * inv, o.w * inv);
-  *reinterpret_cast<uint2*>(p.out + (static_cast<size_t>(b) * p.H + h) * DEC_D + lane * 4) = r;
-}
-
 template <int G>
 static int launch_chunks_for(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeParams& p, dim3 grid,
                              cudaStream_t s) {
-  constexpr int SMEM = DEC_WARPS * dec_warp_bytes(G);
+  constexpr int SMEM = DEC_SMEM;
   auto kernel = decode_chunks_kernel<G>;
   static bool configured[64] = {};
   int dev = 0;
@@ -420,8 +408,15 @@ static int launch_chunks_for(const CUtensorMap& mk, const CUtensorMap& mv, const
     TJX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
     configured[dev & 63] = true;
   }
-  kernel<<<grid, DEC_WARPS * 32, SMEM, s>>>(mk, mv, p);
-  TJX_CUDA(cudaGetLastError());
+  // Programmatic stream serialisation: the grid may start while the step-table kernel before it in the stream
+  // is still running; the kernel waits (griddepcontrol.wait) before it reads anything that kernel writes.
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid, cfg.blockDim = dim3(DEC_WARPS * 32), cfg.dynamicSmemBytes = SMEM, cfg.stream = s;
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr, cfg.numAttrs = 1;
+  TJX_CUDA(cudaLaunchKernelEx(&cfg, kernel, mk, mv, p));
   return 0;
 }
 
@@ -433,13 +428,13 @@ static int launch_decode_chunks(DecodeParams& p, int group, cudaStream_t s) {
   const uint64_t dims[3] = {DEC_D, static_cast<uint64_t>(p.Hkv),
                             static_cast<uint64_t>(p.num_pages) * static_cast<uint64_t>(p.page_size)};
   const uint64_t strides[2] = {DEC_D * 2, static_cast<uint64_t>(p.Hkv) * DEC_D * 2};
-  const uint32_t box[3] = {DEC_D, 1, DEC_SUB};
+  const uint32_t box[3] = {64, 1, DEC_SUB};
   CUtensorMap mk, mv;
   if (int rc = make_tensor_map(&mk, p.k_pages, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 3, dims, strides, box,
-                               CU_TENSOR_MAP_SWIZZLE_NONE))
+                               CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
   if (int rc = make_tensor_map(&mv, p.v_pages, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 3, dims, strides, box,
-                               CU_TENSOR_MAP_SWIZZLE_NONE))
+                               CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
   const long long capacity = static_cast<long long>(p.B) * p.pages_per_seq;
   const int chunks = static_cast<int>((capacity + DEC_CHUNK - 1) / DEC_CHUNK);
@@ -459,23 +454,19 @@ static int decode_slots(int pages_per_seq) { return (pages_per_seq + DEC_CHUNK -
 
 static size_t align256(size_t n) { return (n + 255) & ~static_cast<size_t>(255); }
 
-}  // namespace tjx
-
-extern "C" {
-
-size_t tjx_paged_gqa_decode_workspace_bytes(int B, int H, int D, int pages_per_seq) {
-  if (B <= 0 || H <= 0 || D <= 0 || pages_per_seq <= 0) return 0;
-  const size_t rows = static_cast<size_t>(B) * tjx::decode_slots(pages_per_seq) * H;
-  return 2 * tjx::align256(rows * sizeof(float)) + tjx::align256(rows * D * sizeof(float));
+// Scratch layout: max [B, slots, H] | sum [B, slots, H] | accumulators [B, slots, H, D] | arrival counters [B, Hkv]
+// (at most H of them per sequence). Nothing in it has to start at zero: the step-table kernel clears the
+// counters at the start of every call, and every partial that is read was written earlier in the same call.
+static size_t decode_scratch_bytes(int B, int H, int D, int pages_per_seq) {
+  const size_t rows = static_cast<size_t>(B) * decode_slots(pages_per_seq) * H;
+  return 2 * align256(rows * sizeof(float)) + align256(rows * D * sizeof(float)) +
+         align256(static_cast<size_t>(B) * H * sizeof(int));
 }
 
-int tjx_paged_gqa_decode_bf16(const void* q, const void* k_pages, const void* v_pages, const int32_t* block_tables,
-                              const int32_t* lengths, void* out, int B, int H, int Hkv, int D, int page_size,
-                              int pages_per_seq, int num_pages, int32_t* step_tile, int32_t* step_code,
-                              int32_t* step_count, int32_t* tile_first, void* workspace, size_t workspace_bytes,
-                              tjx_stream_t stream) {
-  using namespace tjx;
-  if (int rc = check_device()) return rc;
+static int check_decode_args(const void* q, const void* k_pages, const void* v_pages, const int32_t* block_tables,
+                             const int32_t* lengths, const void* out, int B, int H, int Hkv, int D, int page_size,
+                             int pages_per_seq, int num_pages, const int32_t* step_tile, const int32_t* step_code,
+                             const int32_t* step_count, const int32_t* tile_first) {
   if (!q || !k_pages || !v_pages || !block_tables || !lengths || !out)
     return fail(TJX_E_ARG, "an input or output pointer is null");
   if (!step_tile || !step_code || !step_count || !tile_first)
@@ -488,20 +479,19 @@ int tjx_paged_gqa_decode_bf16(const void* q, const void* k_pages, const void* v_
   const int group = H / Hkv;
   if (group != 1 && group != 2 && group != 4 && group != 8)
     return fail(TJX_E_ARG, "H / Hkv must be 1, 2, 4 or 8");
-  const size_t need = tjx_paged_gqa_decode_workspace_bytes(B, H, D, pages_per_seq);
-  if (workspace == nullptr || workspace_bytes < need)
-    return fail(TJX_E_ARG, "workspace is null or smaller than tjx_paged_gqa_decode_workspace_bytes");
-  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(TJX_E_ARG, "workspace must be 256-byte aligned");
   const uintptr_t ptrs[] = {reinterpret_cast<uintptr_t>(q), reinterpret_cast<uintptr_t>(k_pages),
                             reinterpret_cast<uintptr_t>(v_pages), reinterpret_cast<uintptr_t>(out)};
   for (uintptr_t a : ptrs)
     if (a & 15u) return fail(TJX_E_ARG, "q, k_pages, v_pages and out must be 16-byte aligned");
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return 0;
+}
 
-  if (int rc = launch_build_steps_lengths(lengths, B, nullptr, B, pages_per_seq, 0, page_size, step_tile, step_code,
-                                          step_count, tile_first, s))
-    return rc;
-
+// The two launches of a decode call, with the partials and counters in `scratch` (decode_scratch_bytes of it,
+// 256-byte aligned). Allocates nothing.
+static int run_decode(const void* q, const void* k_pages, const void* v_pages, const int32_t* block_tables,
+                      const int32_t* lengths, void* out, int B, int H, int Hkv, int page_size, int pages_per_seq,
+                      int num_pages, int32_t* step_tile, int32_t* step_code, int32_t* step_count,
+                      int32_t* tile_first, void* scratch, cudaStream_t s) {
   DecodeParams p{};
   p.q = static_cast<const __nv_bfloat16*>(q);
   p.k_pages = static_cast<const __nv_bfloat16*>(k_pages);
@@ -511,17 +501,44 @@ int tjx_paged_gqa_decode_bf16(const void* q, const void* k_pages, const void* v_
   p.B = B, p.H = H, p.Hkv = Hkv, p.page_size = page_size, p.pages_per_seq = pages_per_seq, p.num_pages = num_pages;
   p.slots = decode_slots(pages_per_seq);
   const size_t rows = static_cast<size_t>(B) * p.slots * H;
-  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  uint8_t* ws = static_cast<uint8_t*>(scratch);
   p.ws_m = reinterpret_cast<float*>(ws);
   p.ws_l = reinterpret_cast<float*>(ws + align256(rows * sizeof(float)));
   p.ws_acc = reinterpret_cast<float*>(ws + 2 * align256(rows * sizeof(float)));
+  p.arrivals = reinterpret_cast<int*>(ws + 2 * align256(rows * sizeof(float)) + align256(rows * DEC_D * sizeof(float)));
   p.out = static_cast<__nv_bfloat16*>(out);
 
-  if (int rc = launch_decode_chunks(p, group, s)) return rc;
-  const int warps = B * H;
-  decode_combine_kernel<<<(warps * 32 + 255) / 256, 256, 0, s>>>(p);
-  TJX_CUDA(cudaGetLastError());
-  return 0;
+  if (int rc = launch_build_steps_lengths(lengths, B, nullptr, B, pages_per_seq, 0, page_size, step_tile, step_code,
+                                          step_count, tile_first, p.arrivals, B * Hkv, s))
+    return rc;
+  return launch_decode_chunks(p, H / Hkv, s);
+}
+
+}  // namespace tjx
+
+extern "C" {
+
+size_t tjx_paged_gqa_decode_workspace_bytes(int B, int H, int D, int pages_per_seq) {
+  if (B <= 0 || H <= 0 || D <= 0 || pages_per_seq <= 0) return 0;
+  return tjx::decode_scratch_bytes(B, H, D, pages_per_seq);
+}
+
+int tjx_paged_gqa_decode_bf16(const void* q, const void* k_pages, const void* v_pages, const int32_t* block_tables,
+                              const int32_t* lengths, void* out, int B, int H, int Hkv, int D, int page_size,
+                              int pages_per_seq, int num_pages, int32_t* step_tile, int32_t* step_code,
+                              int32_t* step_count, int32_t* tile_first, void* workspace, size_t workspace_bytes,
+                              tjx_stream_t stream) {
+  using namespace tjx;
+  if (int rc = check_device()) return rc;
+  if (int rc = check_decode_args(q, k_pages, v_pages, block_tables, lengths, out, B, H, Hkv, D, page_size,
+                                 pages_per_seq, num_pages, step_tile, step_code, step_count, tile_first))
+    return rc;
+  const size_t need = tjx_paged_gqa_decode_workspace_bytes(B, H, D, pages_per_seq);
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(TJX_E_ARG, "workspace is null or smaller than tjx_paged_gqa_decode_workspace_bytes");
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(TJX_E_ARG, "workspace must be 256-byte aligned");
+  return run_decode(q, k_pages, v_pages, block_tables, lengths, out, B, H, Hkv, page_size, pages_per_seq, num_pages,
+                    step_tile, step_code, step_count, tile_first, workspace, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"
@@ -570,56 +587,18 @@ int tjx_paged_gqa_decode_bf16_static(const void* q, const void* k_pages, const v
                                      tjx_stream_t stream) {
   using namespace tjx;
   if (int rc = check_device()) return rc;
-  if (!q || !k_pages || !v_pages || !block_tables || !lengths || !out)
-    return fail(TJX_E_ARG, "an input or output pointer is null");
-  if (!step_tile || !step_code || !step_count || !tile_first)
-    return fail(TJX_E_ARG, "a step table pointer is null");
-  if (B <= 0 || H <= 0 || Hkv <= 0 || pages_per_seq <= 0 || num_pages <= 0)
-    return fail(TJX_E_ARG, "sizes must be positive");
-  if (D != DEC_D) return fail(TJX_E_ARG, "head dimension must be 128");
-  if (page_size <= 0 || page_size % 16 != 0) return fail(TJX_E_ARG, "page size must be a multiple of 16");
-  if (H % Hkv != 0) return fail(TJX_E_ARG, "H must be a multiple of Hkv");
-  const int group = H / Hkv;
-  if (group != 1 && group != 2 && group != 4 && group != 8)
-    return fail(TJX_E_ARG, "H / Hkv must be 1, 2, 4 or 8");
+  if (int rc = check_decode_args(q, k_pages, v_pages, block_tables, lengths, out, B, H, Hkv, D, page_size,
+                                 pages_per_seq, num_pages, step_tile, step_code, step_count, tile_first))
+    return rc;
   const size_t need = tjx_paged_gqa_decode_workspace_bytes(B, H, D, pages_per_seq);
   if (need > STATIC_SCRATCH_BYTES)
     return fail(TJX_E_LIMIT, "these sizes need " + std::to_string(need) + " bytes of scratch, more than the " +
                                  std::to_string(STATIC_SCRATCH_BYTES) +
                                  " bytes built into the library: use tjx_paged_gqa_decode_bf16 with a workspace");
-  const uintptr_t ptrs[] = {reinterpret_cast<uintptr_t>(q), reinterpret_cast<uintptr_t>(k_pages),
-                            reinterpret_cast<uintptr_t>(v_pages), reinterpret_cast<uintptr_t>(out)};
-  for (uintptr_t a : ptrs)
-    if (a & 15u) return fail(TJX_E_ARG, "q, k_pages, v_pages and out must be 16-byte aligned");
   void* scratch = nullptr;
   if (int rc = static_scratch_address(&scratch)) return rc;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-
-  if (int rc = launch_build_steps_lengths(lengths, B, nullptr, B, pages_per_seq, 0, page_size, step_tile, step_code,
-                                          step_count, tile_first, s))
-    return rc;
-
-  DecodeParams p{};
-  p.q = static_cast<const __nv_bfloat16*>(q);
-  p.k_pages = static_cast<const __nv_bfloat16*>(k_pages);
-  p.v_pages = static_cast<const __nv_bfloat16*>(v_pages);
-  p.block_tables = block_tables, p.lengths = lengths;
-  p.step_tile = step_tile, p.step_code = step_code, p.step_count = step_count, p.tile_first = tile_first;
-  p.B = B, p.H = H, p.Hkv = Hkv, p.page_size = page_size, p.pages_per_seq = pages_per_seq, p.num_pages = num_pages;
-  p.slots = decode_slots(pages_per_seq);
-  // Nothing in the scratch has to start at zero: every partial the merge kernel reads was written earlier in
-  // this same call, so whatever the previous call left behind is never looked at.
-  const size_t rows = static_cast<size_t>(B) * p.slots * H;
-  uint8_t* ws = static_cast<uint8_t*>(scratch);
-  p.ws_m = reinterpret_cast<float*>(ws);
-  p.ws_l = reinterpret_cast<float*>(ws + align256(rows * sizeof(float)));
-  p.ws_acc = reinterpret_cast<float*>(ws + 2 * align256(rows * sizeof(float)));
-  p.out = static_cast<__nv_bfloat16*>(out);
-
-  if (int rc = launch_decode_chunks(p, group, s)) return rc;
-  decode_combine_kernel<<<(B * H * 32 + 255) / 256, 256, 0, s>>>(p);
-  TJX_CUDA(cudaGetLastError());
-  return 0;
+  return run_decode(q, k_pages, v_pages, block_tables, lengths, out, B, H, Hkv, page_size, pages_per_seq, num_pages,
+                    step_tile, step_code, step_count, tile_first, scratch, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

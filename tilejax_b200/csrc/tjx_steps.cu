@@ -14,6 +14,7 @@ namespace tjx {
 
 constexpr int STEPS_THREADS = 1024;
 constexpr int STEPS_MAX_TILES = 8192;  // per-tile counters live in shared memory
+constexpr int STEPS_LEN_CACHE = 2048;  // tables of up to this many tiles fetch every tile's length in one round
 
 // run(t, k): does block k of tile t run? Masks `value0 + k * value_step >= lengths[tile_values[t]]` skip.
 struct RunFromLengths {
@@ -41,15 +42,29 @@ __global__ void __launch_bounds__(STEPS_THREADS) build_steps_kernel(Run mask, in
                                                                     int32_t* __restrict__ step_tile,
                                                                     int32_t* __restrict__ step_code,
                                                                     int32_t* __restrict__ step_count,
-                                                                    int32_t* __restrict__ tile_first) {
+                                                                    int32_t* __restrict__ tile_first,
+                                                                    int32_t* __restrict__ zero_words, int n_zero) {
   __shared__ int s_runs[STEPS_MAX_TILES];   // blocks that run per tile, then the tile's first step (scan)
+  __shared__ int s_len[STEPS_LEN_CACHE];
   __shared__ int s_warp_sums[32];
   __shared__ int s_carry;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = STEPS_THREADS / 32;
+  // A kernel launched behind this one with programmatic stream serialisation may start its prologue now; it
+  // still waits for this whole grid before it reads the tables.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  // Every tile's length in one round of (dependent) global loads, instead of one round per tile per pass.
+  const bool cached = tiles <= STEPS_LEN_CACHE;
+  if (cached) {
+    for (int t = threadIdx.x; t < tiles; t += STEPS_THREADS) s_len[t] = mask.length_of(t);
+  }
+  // Words the caller wants cleared before its next kernel (arrival counters of the decode kernel).
+  for (int i = threadIdx.x; i < n_zero; i += STEPS_THREADS) zero_words[i] = 0;
+  if (cached) __syncthreads();
 
   // Pass 1: blocks that run in each tile.
   for (int t = warp; t < tiles; t += n_warps) {
-    const int len = mask.length_of(t);
+    const int len = cached ? s_len[t] : mask.length_of(t);
     int n = 0;
     for (int k0 = 0; k0 < blocks; k0 += 32) {
       const int k = k0 + lane;
@@ -101,7 +116,7 @@ __global__ void __launch_bounds__(STEPS_THREADS) build_steps_kernel(Run mask, in
   // Pass 2: scatter. Steps that run go to first_step(t) + rank; the others behind all of them, in tile-major
   // order: their position is total + (entries before them) - (kept entries before them).
   for (int t = warp; t < tiles; t += n_warps) {
-    const int len = mask.length_of(t);
+    const int len = cached ? s_len[t] : mask.length_of(t);
     const int first_step = s_runs[t] >> 1;
     const bool empty_tile = s_runs[t] & 1;
     const int next_first = (t + 1 < tiles) ? (s_runs[t + 1] >> 1) : total;
@@ -139,10 +154,11 @@ static int check_common(int tiles, int blocks, const void* a, const void* b, con
 
 int launch_build_steps_lengths(const int32_t* lengths, int n_lengths, const int32_t* tile_values, int tiles,
                                int blocks, int value0, int value_step, int32_t* step_tile, int32_t* step_code,
-                               int32_t* step_count, int32_t* tile_first, cudaStream_t stream) {
+                               int32_t* step_count, int32_t* tile_first, int32_t* zero_words, int n_zero,
+                               cudaStream_t stream) {
   RunFromLengths mask{lengths, tile_values, n_lengths, value0, value_step};
   build_steps_kernel<<<1, STEPS_THREADS, 0, stream>>>(mask, tiles, blocks, step_tile, step_code, step_count,
-                                                      tile_first);
+                                                      tile_first, zero_words, n_zero);
   TJX_CUDA(cudaGetLastError());
   return 0;
 }
@@ -159,7 +175,7 @@ int tjx_build_steps(const int32_t* lengths, int n_lengths, const int32_t* tile_v
   if (lengths == nullptr || n_lengths <= 0) return tjx::fail(TJX_E_ARG, "lengths is null or empty");
   if (value_step <= 0) return tjx::fail(TJX_E_ARG, "value_step must be positive (loops count up)");
   return tjx::launch_build_steps_lengths(lengths, n_lengths, tile_values, tiles, blocks, value0, value_step,
-                                         step_tile, step_code, step_count, tile_first,
+                                         step_tile, step_code, step_count, tile_first, nullptr, 0,
                                          static_cast<cudaStream_t>(stream));
 }
 
@@ -170,7 +186,7 @@ int tjx_build_steps_from_runs(const uint8_t* run, int tiles, int blocks, int32_t
   if (run == nullptr) return tjx::fail(TJX_E_ARG, "run is null");
   tjx::RunFromBitmap mask{run, blocks};
   tjx::build_steps_kernel<<<1, tjx::STEPS_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
-      mask, tiles, blocks, step_tile, step_code, step_count, tile_first);
+      mask, tiles, blocks, step_tile, step_code, step_count, tile_first, nullptr, 0);
   TJX_CUDA(cudaGetLastError());
   return 0;
 }
