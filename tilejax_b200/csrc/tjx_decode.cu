@@ -3,7 +3,7 @@
 // head is far too little reuse).
 //
 // The work is the device step table (tjx_steps.cu): the steps that run, one K/V page each, in tile (sequence)
-// order. It is cut into chunks of CHUNK consecutive steps, a CTA per (chunk, group of 4 KV heads), so ragged
+// order. It is cut into chunks of CHUNK consecutive steps, a CTA per (chunk, pair of KV heads), so ragged
 // lengths balance by themselves. Inside a CTA warp w owns one KV head and its G query heads. A chunk may cover
 // the end of one sequence and the start of the next; a (sequence, chunk) piece that is the sequence's only one
 // is normalised and written at once; otherwise it writes an online-softmax partial (max, sum, accumulator) to
@@ -33,8 +33,8 @@ constexpr int DEC_SUB = 16;        // tokens per micro-step (a page is a whole n
 constexpr int DEC_STAGES = 2;      // ring slots per warp
 constexpr int DEC_HALF_BYTES = DEC_SUB * 64 * 2;           // one TMA box: 16 tokens x 64 dims, 128-byte rows
 constexpr int DEC_STAGE_BYTES = 4 * DEC_HALF_BYTES;        // K (two dim halves) and V (two) of one micro-step
-constexpr int DEC_CHUNK = 16;      // steps (pages) per CTA
-constexpr int DEC_WARPS = 4;       // KV heads per CTA
+constexpr int DEC_CHUNK = 12;      // steps (pages) per CTA (at most 32: a lane holds a step)
+constexpr int DEC_WARPS = 2;       // KV heads per CTA
 constexpr float DEC_MASK = -1e30f;
 constexpr int DEC_SMEM = DEC_WARPS * DEC_STAGES * DEC_STAGE_BYTES + 1024;  // + slack to align the ring to 1024
 
@@ -163,7 +163,7 @@ __device__ __forceinline__ void decode_merge_heads(const DecodeParams& p, int b,
 // tokens 2t, 2t+1, 8+2t, 9+2t and output dims 8 n + 2t, + 1 for n = 0..15. A fifth-generation (tcgen05) MMA needs
 // 64 or 128 rows; with at most 8 query heads per KV head this path stays bound by HBM with the warp-level MMA.
 template <int G>
-__global__ void __launch_bounds__(DEC_WARPS * 32, 3)
+__global__ void __launch_bounds__(DEC_WARPS * 32, 6)
     decode_chunks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                          const DecodeParams p) {
   extern __shared__ uint8_t dec_smem_raw[];
