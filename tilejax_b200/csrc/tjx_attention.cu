@@ -1,17 +1,20 @@
 // Flash-style causal attention on sm_100a: the step loop of `causal_attention`
 // (examples/causal_attention.py:37-63) with the scores and the output accumulator in TMEM.
 //
-// A CTA owns one (b, h) and two consecutive query tiles of 128 rows ("slots" A and B), and walks the key/value
+// A work unit is one (b, h) and two consecutive query tiles of 128 rows ("slots" A and B); it walks the key/value
 // blocks the step table lists for them in sub-blocks of 128 keys; a sub-block wholly in the future of a slot's
 // rows is skipped for that slot (its probabilities would all be exp(-1e30 - max) = 0). Both slots share every
-// K / V load.
+// K / V load. One persistent CTA per SM takes units heaviest first, dealt out in snake order (round k goes
+// forwards over the CTAs for even k, backwards for odd k) so that every CTA gets the same amount of work;
+// barriers, TMEM and the tensor maps are set up once, and the loads of the next unit start while the current
+// one is still in its last blocks.
 //
-//   warp 0      producer: TMA loads Q (both slots, once), then K and V sub-blocks into two 2-slot rings
+//   warp 0      producer: TMA loads Q (both slots, once per unit), then K and V sub-blocks into two 2-slot rings
 //   warp 1      MMA issuer (one thread): S_t = Q_t K^T into TMEM, then O_t += P_t V with P_t read from TMEM
 //   warps 2-5   softmax of slot A, warps 6-9 of slot B: a thread owns one query row — tcgen05.ld its 128
 //               scores, running max / sum in f32 registers, exp2, P rounded to bf16 and stored back to TMEM over
 //               the scores; rescales O in TMEM when the running max grows; at the end normalises O and stores
-//               it through shared memory with TMA
+//               its row (256 contiguous bytes) straight from registers
 //
 // TMEM (512 columns): S_A | S_B | O_A | O_B, 128 f32 columns each; P_t (bf16, two per column) overlays the
 // first 64 columns of S_t. While one slot's softmax runs, the tensor core works on the other slot.
@@ -20,6 +23,8 @@
 // -1e30; the row sum adds the unrounded probabilities while P is rounded to bf16 before P @ V; one division at
 // the end. The running max is only raised when a block's max exceeds it by more than 8 (in log2 units), which
 // changes no result beyond rounding: every term is scaled by the same power of two.
+#include <algorithm>
+
 #include "tjx_host.cuh"
 #include "tjx_ptx.cuh"
 
@@ -43,8 +48,12 @@ struct AttnParams {
   const int32_t* step_tile;
   const int32_t* step_code;
   int units_per_bh;  // pairs of 128-row query tiles per (b, h)
+  int total_units;
+  __nv_bfloat16* out;
   int* status;
 };
+
+constexpr int AT_MAX_TILES = 1024;  // user query tiles per (b, h) whose last key block is cached in shared memory
 
 struct AttnSmem {
   static constexpr int TILE_BYTES = 128 * 128 * 2;  // a 128 x 128 bf16 tile: two 64-column boxes of 16 KB
@@ -52,7 +61,8 @@ struct AttnSmem {
   static constexpr int K_OFF = 2 * TILE_BYTES;       // AT_STAGES
   static constexpr int V_OFF = K_OFF + AT_STAGES * TILE_BYTES;
   static constexpr int BAR_OFF = V_OFF + AT_STAGES * TILE_BYTES;
-  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+  static constexpr int LAST_OFF = BAR_OFF + 256;               // last key block of each user query tile
+  static constexpr int TOTAL = LAST_OFF + AT_MAX_TILES * 4 + 1024;
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -63,26 +73,22 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 // Keys a slot's rows [q0, q0 + 128) attend to, as a count of 128-key sub-blocks from key 0: what the step table
 // lists for the user tile holding q0 (blocks 0 .. last, contiguous), cut at the slot's own diagonal.
-__device__ __forceinline__ int slot_blocks(const AttnParams& p, int q0) {
+__device__ __forceinline__ int slot_blocks(const AttnParams& p, const int* last_block, int q0) {
   if (q0 >= p.S) return 0;
-  const int tile = q0 / p.bq;
-  int last_block = -1;
-  for (int s = 0; s < p.pattern_steps; ++s)
-    if (p.step_tile[s] == tile && !(p.step_code[s] & 4)) last_block = max(last_block, p.step_code[s] >> 3);
-  const int keys = min(min((last_block + 1) * p.bk, q0 + AT_BQ), p.S);
+  const int last = last_block[q0 / p.bq];
+  const int keys = min(min((last + 1) * p.bk, q0 + AT_BQ), p.S);
   return keys / AT_BKV;
 }
 
 __global__ void __launch_bounds__(AT_THREADS, 1)
     attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
-                     const AttnParams p) {
+                     const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
   using L = AttnSmem;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t bar_base = base + L::BAR_OFF;
-  // barriers: q_full[2], k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2], o_done[2]
+  // barriers: q_full[2], k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2], o_done[2], q_empty[2]
   auto q_full = [&](int t) { return bar_base + 8u * t; };
   auto k_full = [&](int s) { return bar_base + 8u * (2 + s); };
   auto k_empty = [&](int s) { return bar_base + 8u * (4 + s); };
@@ -91,21 +97,23 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
   auto s_full = [&](int t) { return bar_base + 8u * (10 + t); };
   auto p_ready = [&](int t) { return bar_base + 8u * (12 + t); };
   auto o_done = [&](int t) { return bar_base + 8u * (14 + t); };
-  volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(base_ptr + L::BAR_OFF + 8 * 16);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + L::BAR_OFF + 8 * 16 + 8);
-  volatile int* blocks_sh = reinterpret_cast<volatile int*>(base_ptr + L::BAR_OFF + 8 * 16 + 16);
+  auto q_empty = [&](int t) { return bar_base + 8u * (16 + t); };
+  constexpr int N_BARS = 18;
+  volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(base_ptr + L::BAR_OFF + 8 * N_BARS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + L::BAR_OFF + 8 * N_BARS + 8);
+  int* last_block = reinterpret_cast<int*>(base_ptr + L::LAST_OFF);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-  // Work unit: heaviest first (later query tiles attend to more keys).
   const int bh_count = p.B * p.H;
-  const int unit = p.units_per_bh - 1 - static_cast<int>(blockIdx.x) / bh_count;
-  const int bh = static_cast<int>(blockIdx.x) % bh_count;
-  const int q0_slot[2] = {unit * 2 * AT_BQ, unit * 2 * AT_BQ + AT_BQ};
-  const int row_base = bh * p.S;  // row of (b, h, 0) in the [B * H * S, D] view
+  const int n_ctas = static_cast<int>(gridDim.x), cta = static_cast<int>(blockIdx.x);
+  // The k-th unit of this CTA in the heaviest-first list (later query tiles attend to more keys), or -1.
+  auto unit_at = [&](int k) {
+    const int i = k * n_ctas + ((k & 1) ? n_ctas - 1 - cta : cta);
+    return i < p.total_units ? i : -1;
+  };
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 16; ++i) {
+    for (int i = 0; i < N_BARS; ++i) {
       const bool softmax_bar = i == 12 || i == 13;  // p_ready: one arrival per softmax warp
       mbar_init(bar_base + 8u * i, softmax_bar ? 4 : 1);
     }
@@ -114,9 +122,14 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
     tma_prefetch_desc(&map_q);
     tma_prefetch_desc(&map_k);
     tma_prefetch_desc(&map_v);
-    tma_prefetch_desc(&map_o);
   }
-  if (threadIdx.x < 2) blocks_sh[threadIdx.x] = slot_blocks(p, q0_slot[threadIdx.x]);
+  // Last key block the step table lists for each user query tile (-1: none).
+  for (int i = threadIdx.x; i < p.pattern_tiles; i += AT_THREADS) last_block[i] = -1;
+  __syncthreads();
+  for (int s = threadIdx.x; s < p.pattern_steps; s += AT_THREADS) {
+    const int code = p.step_code[s], tile = p.step_tile[s];
+    if (!(code & 4) && tile >= 0 && tile < p.pattern_tiles) atomicMax(&last_block[tile], code >> 3);
+  }
   if (warp == 1) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_holder)), 512);
     tmem_relinquish();
@@ -125,33 +138,67 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
-  const int n_slot[2] = {blocks_sh[0], blocks_sh[1]};
-  const int n_blocks = max(n_slot[0], n_slot[1]);
+
+  // What every role derives for a unit, identically.
+  struct Unit {
+    int row_base, q0[2], n_slot[2], n_blocks;
+  };
+  auto describe = [&](int i) {
+    Unit u;
+    const int unit = p.units_per_bh - 1 - i / bh_count;
+    const int bh = i % bh_count;
+    u.row_base = bh * p.S;  // row of (b, h, 0) in the [B * H * S, D] view
+    u.q0[0] = unit * 2 * AT_BQ, u.q0[1] = unit * 2 * AT_BQ + AT_BQ;
+    u.n_slot[0] = slot_blocks(p, last_block, u.q0[0]);
+    u.n_slot[1] = slot_blocks(p, last_block, u.q0[1]);
+    u.n_blocks = max(u.n_slot[0], u.n_slot[1]);
+    return u;
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
-      for (int t = 0; t < 2; ++t) {
-        if (n_slot[t] == 0) continue;
-        const uint32_t dst = base + L::Q_OFF + t * L::TILE_BYTES;
-        mbar_expect_tx(q_full(t), L::TILE_BYTES);
-        tma_load_2d(dst, &map_q, 0, row_base + q0_slot[t], q_full(t));
-        tma_load_2d(dst + L::TILE_BYTES / 2, &map_q, 64, row_base + q0_slot[t], q_full(t));
-      }
-      for (int n = 0; n < n_blocks; ++n) {
-        const int stage = n % AT_STAGES;
-        const uint32_t ph = (n / AT_STAGES) & 1;
-        const int kv_row = row_base + n * AT_BKV;
-        if (!mbar_wait(k_empty(stage), ph ^ 1u, abort_flag, p.status, TJX_ERR_WAIT_EMPTY)) break;
-        const uint32_t kd = base + L::K_OFF + stage * L::TILE_BYTES;
-        mbar_expect_tx(k_full(stage), L::TILE_BYTES);
-        tma_load_2d(kd, &map_k, 0, kv_row, k_full(stage));
-        tma_load_2d(kd + L::TILE_BYTES / 2, &map_k, 64, kv_row, k_full(stage));
-        if (!mbar_wait(v_empty(stage), ph ^ 1u, abort_flag, p.status, TJX_ERR_WAIT_EMPTY)) break;
-        const uint32_t vd = base + L::V_OFF + stage * L::TILE_BYTES;
-        mbar_expect_tx(v_full(stage), L::TILE_BYTES);
-        tma_load_2d(vd, &map_v, 0, kv_row, v_full(stage));
-        tma_load_2d(vd + L::TILE_BYTES / 2, &map_v, 64, kv_row, v_full(stage));
+      int g = 0;          // K/V blocks loaded so far (ring position)
+      int used[2] = {0, 0};  // units that used slot t so far
+      bool ok = true;
+      for (int k = 0; ok; ++k) {
+        const int i = unit_at(k);
+        if (i < 0) break;
+        const Unit u = describe(i);
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (u.n_slot[t] == 0) continue;
+          // The previous unit's last Q K^T of this slot has read the tile.
+          if (!mbar_wait(q_empty(t), (used[t] & 1) ^ 1u, abort_flag, p.status, TJX_ERR_WAIT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          ++used[t];
+          const uint32_t dst = base + L::Q_OFF + t * L::TILE_BYTES;
+          mbar_expect_tx(q_full(t), L::TILE_BYTES);
+          tma_load_2d(dst, &map_q, 0, u.row_base + u.q0[t], q_full(t));
+          tma_load_2d(dst + L::TILE_BYTES / 2, &map_q, 64, u.row_base + u.q0[t], q_full(t));
+        }
+        for (int n = 0; n < u.n_blocks && ok; ++n, ++g) {
+          const int stage = g % AT_STAGES;
+          const uint32_t ph = (g / AT_STAGES) & 1;
+          const int kv_row = u.row_base + n * AT_BKV;
+          if (!mbar_wait(k_empty(stage), ph ^ 1u, abort_flag, p.status, TJX_ERR_WAIT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          const uint32_t kd = base + L::K_OFF + stage * L::TILE_BYTES;
+          mbar_expect_tx(k_full(stage), L::TILE_BYTES);
+          tma_load_2d(kd, &map_k, 0, kv_row, k_full(stage));
+          tma_load_2d(kd + L::TILE_BYTES / 2, &map_k, 64, kv_row, k_full(stage));
+          if (!mbar_wait(v_empty(stage), ph ^ 1u, abort_flag, p.status, TJX_ERR_WAIT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          const uint32_t vd = base + L::V_OFF + stage * L::TILE_BYTES;
+          mbar_expect_tx(v_full(stage), L::TILE_BYTES);
+          tma_load_2d(vd, &map_v, 0, kv_row, v_full(stage));
+          tma_load_2d(vd + L::TILE_BYTES / 2, &map_v, 64, kv_row, v_full(stage));
+        }
       }
     }
     __syncwarp();
@@ -160,8 +207,11 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
     if (lane == 0) {
       const uint32_t idesc_qk = idesc_bf16_f32(128, 128, 0, 0);  // Q and K both K-major (K read "transposed")
       const uint32_t idesc_pv = idesc_bf16_f32(128, 128, 0, 1);  // P from TMEM, V MN-major
-      auto issue_qk = [&](int t, int n) {
-        const int stage = n % AT_STAGES;
+      int g0 = 0;            // ring position of the current unit's block 0
+      int used[2] = {0, 0};  // units that used slot t so far
+      int done[2] = {0, 0};  // blocks of slot t in earlier units (phase of s_full / p_ready / o_done)
+      auto issue_qk = [&](int t, int gn) {
+        const int stage = gn % AT_STAGES;
         const uint32_t qa = base + L::Q_OFF + t * L::TILE_BYTES;
         const uint32_t ka = base + L::K_OFF + stage * L::TILE_BYTES;
 #pragma unroll
@@ -172,57 +222,77 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
         }
         mma_commit(s_full(t));
       };
-      auto issue_pv = [&](int t, int n) {
-        const int stage = n % AT_STAGES;
+      auto issue_pv = [&](int t, int gn, bool first) {
+        const int stage = gn % AT_STAGES;
         const uint32_t va = base + L::V_OFF + stage * L::TILE_BYTES;
 #pragma unroll
         for (int kk = 0; kk < AT_BKV / 16; ++kk)
           mma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + kk * 8,
-                 smem_desc_sw128(va + kk * (16 * 128), L::TILE_BYTES / 2, 1024), idesc_pv, (n | kk) != 0 ? 1u : 0u);
+                 smem_desc_sw128(va + kk * (16 * 128), L::TILE_BYTES / 2, 1024), idesc_pv,
+                 (!first || kk != 0) ? 1u : 0u);
         mma_commit(o_done(t));
       };
       bool ok = true;
-      for (int t = 0; t < 2 && ok; ++t)
-        if (n_slot[t] > 0) ok = mbar_wait(q_full(t), 0, abort_flag, p.status, TJX_ERR_WAIT_FULL);
-      if (ok && n_blocks > 0) {
-        ok = mbar_wait(k_full(0), 0, abort_flag, p.status, TJX_ERR_WAIT_FULL);
-        if (ok) {
-          tc_fence_after_sync();
-          for (int t = 0; t < 2; ++t)
-            if (n_slot[t] > 0) issue_qk(t, 0);
-          mma_commit(k_empty(0));
+      for (int k = 0; ok; ++k) {
+        const int i = unit_at(k);
+        if (i < 0) break;
+        const Unit u = describe(i);
+        for (int t = 0; t < 2 && ok; ++t)
+          if (u.n_slot[t] > 0) ok = mbar_wait(q_full(t), used[t] & 1, abort_flag, p.status, TJX_ERR_WAIT_FULL);
+        if (ok && u.n_blocks > 0) {
+          ok = mbar_wait(k_full(g0 % AT_STAGES), (g0 / AT_STAGES) & 1, abort_flag, p.status, TJX_ERR_WAIT_FULL);
+          if (ok) {
+            tc_fence_after_sync();
+            for (int t = 0; t < 2; ++t)
+              if (u.n_slot[t] > 0) {
+                issue_qk(t, g0);
+                if (u.n_slot[t] == 1) mma_commit(q_empty(t));  // this slot's only Q K^T of the unit
+              }
+            mma_commit(k_empty(g0 % AT_STAGES));
+          }
         }
-      }
-      for (int n = 0; n < n_blocks && ok; ++n) {
-        const int stage = n % AT_STAGES;
-        const uint32_t ph = (n / AT_STAGES) & 1;
-        if (!mbar_wait(v_full(stage), ph, abort_flag, p.status, TJX_ERR_WAIT_FULL)) break;
-        bool next_k_waited = false, next_k_used = false;
-        for (int t = 0; t < 2 && ok; ++t) {
-          if (n >= n_slot[t]) continue;
-          if (!mbar_wait(p_ready(t), n & 1, abort_flag, p.status, TJX_ERR_WAIT_OTHER)) {
+        for (int n = 0; n < u.n_blocks && ok; ++n) {
+          const int gn = g0 + n;
+          const int stage = gn % AT_STAGES;
+          if (!mbar_wait(v_full(stage), (gn / AT_STAGES) & 1, abort_flag, p.status, TJX_ERR_WAIT_FULL)) {
             ok = false;
             break;
           }
-          tc_fence_after_sync();
-          issue_pv(t, n);
-          if (n + 1 < n_slot[t]) {
-            if (!next_k_waited) {
-              const int ns = (n + 1) % AT_STAGES;
-              if (!mbar_wait(k_full(ns), ((n + 1) / AT_STAGES) & 1, abort_flag, p.status, TJX_ERR_WAIT_FULL)) {
-                ok = false;
-                break;
-              }
-              tc_fence_after_sync();
-              next_k_waited = true;
+          bool next_k_waited = false, next_k_used = false;
+          for (int t = 0; t < 2 && ok; ++t) {
+            if (n >= u.n_slot[t]) continue;
+            // Softmax warps reach block 0 of a unit only after their epilogue of the previous one, so this wait
+            // also covers "O of the previous unit has been read".
+            if (!mbar_wait(p_ready(t), (done[t] + n) & 1, abort_flag, p.status, TJX_ERR_WAIT_OTHER)) {
+              ok = false;
+              break;
             }
-            issue_qk(t, n + 1);
-            next_k_used = true;
+            tc_fence_after_sync();
+            issue_pv(t, gn, n == 0);
+            if (n + 1 < u.n_slot[t]) {
+              if (!next_k_waited) {
+                const int ns = (gn + 1) % AT_STAGES;
+                if (!mbar_wait(k_full(ns), ((gn + 1) / AT_STAGES) & 1, abort_flag, p.status, TJX_ERR_WAIT_FULL)) {
+                  ok = false;
+                  break;
+                }
+                tc_fence_after_sync();
+                next_k_waited = true;
+              }
+              issue_qk(t, gn + 1);
+              if (n + 2 == u.n_slot[t]) mma_commit(q_empty(t));  // that was this slot's last Q K^T of the unit
+              next_k_used = true;
+            }
           }
+          if (!ok) break;
+          mma_commit(v_empty(stage));
+          if (next_k_used) mma_commit(k_empty((gn + 1) % AT_STAGES));
         }
-        if (!ok) break;
-        mma_commit(v_empty(stage));
-        if (next_k_used) mma_commit(k_empty((n + 1) % AT_STAGES));
+        g0 += u.n_blocks;
+        for (int t = 0; t < 2; ++t) {
+          done[t] += u.n_slot[t];
+          if (u.n_slot[t] > 0) ++used[t];
+        }
       }
     }
     __syncwarp();
@@ -230,17 +300,22 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
     // ------------------------------------------------------------------ softmax / correction / epilogue
     const int t = (warp - 2) >> 2;  // slot
     const int q = warp & 3;         // TMEM lane quarter
-    const int n_mine = n_slot[t];
-    const int q0 = q0_slot[t];
-    const int row = q0 + q * 32 + lane;  // query position of this thread's row
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     const uint32_t s_tmem = tmem_base + lane_addr + t * 128;
     const uint32_t o_tmem = tmem_base + lane_addr + 256 + t * 128;
+    int done = 0;  // blocks of this slot in earlier units
+    bool ok = true;
+    for (int k = 0; ok; ++k) {
+    const int i = unit_at(k);
+    if (i < 0) break;
+    const Unit u = describe(i);
+    const int n_mine = u.n_slot[t];
+    const int q0 = u.q0[t];
+    const int row = q0 + q * 32 + lane;  // query position of this thread's row
     float m_used = AT_MASK * AT_LOG2E;  // running max, in log2 units
     float l = 0.f;
-    bool ok = true;
     for (int n = 0; n < n_mine; ++n) {
-      const bool got = mbar_wait(s_full(t), n & 1, abort_flag, p.status, TJX_ERR_WAIT_TMEM_FULL);
+      const bool got = mbar_wait(s_full(t), (done + n) & 1, abort_flag, p.status, TJX_ERR_WAIT_TMEM_FULL);
       if (!__all_sync(0xFFFFFFFFu, got)) {
         ok = false;
         break;
@@ -284,7 +359,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
         const float alpha = fast_exp2(m_used - m_new);
         m_used = m_new;
         l *= alpha;
-        const bool od = mbar_wait(o_done(t), (n - 1) & 1, abort_flag, p.status, TJX_ERR_WAIT_OTHER);
+        const bool od = mbar_wait(o_done(t), (done + n - 1) & 1, abort_flag, p.status, TJX_ERR_WAIT_OTHER);
         if (!__all_sync(0xFFFFFFFFu, od)) {
           ok = false;
           break;
@@ -328,42 +403,36 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
       if (lane == 0) mbar_arrive(p_ready(t));
     }
     if (ok && n_mine > 0) {
-      // Epilogue: O / l -> bf16 -> shared memory (over this slot's Q tile, no longer read) -> TMA store.
-      const bool od = mbar_wait(o_done(t), (n_mine - 1) & 1, abort_flag, p.status, TJX_ERR_WAIT_OTHER);
-      if (__all_sync(0xFFFFFFFFu, od)) {
+      // Epilogue: O / l -> bf16 -> this thread's row of the output, 256 contiguous bytes.
+      const bool od = mbar_wait(o_done(t), (done + n_mine - 1) & 1, abort_flag, p.status, TJX_ERR_WAIT_OTHER);
+      if (!__all_sync(0xFFFFFFFFu, od)) {
+        ok = false;
+      } else {
         tc_fence_after_sync();
         const float inv = 1.0f / l;
-        uint8_t* stage_ptr = base_ptr + L::Q_OFF + t * L::TILE_BYTES;
-        const int r = q * 32 + lane;  // row within the tile
+        uint4* dst = reinterpret_cast<uint4*>(p.out + static_cast<size_t>(u.row_base + row) * AT_D);
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           uint32_t v[32];
           tmem_ld32(o_tmem + c * 32, v);
           tmem_wait_ld();
-          uint8_t* half_ptr = stage_ptr + (c >> 1) * (L::TILE_BYTES / 2) + r * 128;
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
+          for (int x = 0; x < 4; ++x) {
             uint4 val;
-            val.x = pack_bf16(__uint_as_float(v[8 * u + 0]) * inv, __uint_as_float(v[8 * u + 1]) * inv);
-            val.y = pack_bf16(__uint_as_float(v[8 * u + 2]) * inv, __uint_as_float(v[8 * u + 3]) * inv);
-            val.z = pack_bf16(__uint_as_float(v[8 * u + 4]) * inv, __uint_as_float(v[8 * u + 5]) * inv);
-            val.w = pack_bf16(__uint_as_float(v[8 * u + 6]) * inv, __uint_as_float(v[8 * u + 7]) * inv);
-            const int unit16 = (c & 1) * 4 + u;
-            *reinterpret_cast<uint4*>(half_ptr + ((unit16 ^ (r & 7)) << 4)) = val;
+            val.x = pack_bf16(__uint_as_float(v[8 * x + 0]) * inv, __uint_as_float(v[8 * x + 1]) * inv);
+            val.y = pack_bf16(__uint_as_float(v[8 * x + 2]) * inv, __uint_as_float(v[8 * x + 3]) * inv);
+            val.z = pack_bf16(__uint_as_float(v[8 * x + 4]) * inv, __uint_as_float(v[8 * x + 5]) * inv);
+            val.w = pack_bf16(__uint_as_float(v[8 * x + 6]) * inv, __uint_as_float(v[8 * x + 7]) * inv);
+            dst[c * 4 + x] = val;
           }
         }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          const uint32_t src = base + L::Q_OFF + t * L::TILE_BYTES + q * 32 * 128;
-          tma_store_2d(&map_o, src, 0, row_base + q0 + q * 32);
-          tma_store_2d(&map_o, src + L::TILE_BYTES / 2, 64, row_base + q0 + q * 32);
-          tma_store_commit();
-          tma_store_wait_all<0>();
-        }
-        __syncwarp();
+        // The reads of O above are ordered before this warp's next arrival on p_ready, which is what the next
+        // unit's first P V waits for before it overwrites O.
+        tc_fence_before_sync();
       }
     }
+    done += n_mine;
+    }  // units
   }
 
   tc_fence_before_sync();
@@ -399,18 +468,19 @@ extern "C" int tjx_causal_attention_bf16(const void* q, const void* k, const voi
   p.pattern_steps = pattern_steps, p.pattern_tiles = pattern_tiles;
   p.step_tile = step_tile, p.step_code = step_code;
   p.units_per_bh = (S / AT_BQ + 1) / 2;
+  p.total_units = B * H * p.units_per_bh;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  if (pattern_tiles > AT_MAX_TILES) return fail(TJX_E_LIMIT, "more than 1024 query tiles per (batch, head)");
   p.status = device_status_word();
   if (p.status == nullptr) return fail(TJX_E_CUDA, "could not locate the device status word");
 
   const uint64_t dims[2] = {static_cast<uint64_t>(D), static_cast<uint64_t>(B) * H * S};
   const uint64_t strides[1] = {static_cast<uint64_t>(D) * 2};
   const uint32_t box_in[2] = {64, 128};
-  const uint32_t box_out[2] = {64, 32};
-  CUtensorMap mq, mk, mv, mo;
+  CUtensorMap mq, mk, mv;
   if (int rc = make_tensor_map(&mq, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 2, dims, strides, box_in, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
   if (int rc = make_tensor_map(&mk, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 2, dims, strides, box_in, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
   if (int rc = make_tensor_map(&mv, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 2, dims, strides, box_in, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
-  if (int rc = make_tensor_map(&mo, out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 2, dims, strides, box_out, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
 
   static bool configured[64] = {};
   int dev = 0;
@@ -419,8 +489,8 @@ extern "C" int tjx_causal_attention_bf16(const void* q, const void* k, const voi
     TJX_CUDA(cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem::TOTAL));
     configured[dev & 63] = true;
   }
-  const int grid = B * H * p.units_per_bh;
-  attention_kernel<<<grid, AT_THREADS, AttnSmem::TOTAL, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, mo, p);
+  const int grid = std::min(p.total_units, sm_count());
+  attention_kernel<<<grid, AT_THREADS, AttnSmem::TOTAL, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, p);
   TJX_CUDA(cudaGetLastError());
   return 0;
 }
