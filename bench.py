@@ -369,9 +369,9 @@ def main() -> None:
 
     # ---- end to end: host buffers in, host result out, copies inside the timed region
     def e2e_step():
-        x.copy_(x_host, non_blocking=True)
-        y.copy_(y_host, non_blocking=True)
-        out_host.copy_(op(x, y), non_blocking=True)
+        # Host shard and weights in, host result out: copies, GEMMs and copies back pipelined on three streams.
+        op.from_host(x_host, y_host, out_host)
+        torch.cuda.current_stream().wait_event(op.host_done)
 
     for _ in range(2):
         e2e_step()
@@ -409,7 +409,7 @@ def main() -> None:
         "clocks": clocks,
         "e2e": {"value": world * flops_per_gpu / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": x_host.numel() * 2 + y_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2,
-                "api": "tilejax_b200.collective.AllGatherMatmul.__call__ with pinned host x, y and out"},
+                "api": "tilejax_b200.collective.AllGatherMatmul.from_host with pinned host x, y and out"},
         "gpu_launches": args.steps * (1 if world == 1 else len(op.groups)) + args.steps,
         "roofline": {"bound": "tensor", "kernel": "gemm_pair_kernel<3,2>", "achieved": gemm_tflops, "peak": peak,
                      "unit": "TFLOP/s", "frac": gemm_tflops / peak,

@@ -41,6 +41,14 @@ for transport in ("peer", "nccl"):
         assert torch.equal(out, ops.gemm((xs * (call + 1)).to(torch.bfloat16), w, 256, 512, 512)), (transport, call)
     assert (out[::97].double() / 3 - exact).abs().max() <= 2e-2 * exact.abs().max()
     assert ops.device_status() == 0
+    # Host buffers in, host result out, pipelined: the same bits, two calls (both halves of the send buffer).
+    x_host, w_host = x.cpu().pin_memory(), w.cpu().pin_memory()
+    out_host = torch.empty((world * m, N), dtype=torch.bfloat16).pin_memory()
+    for call in range(2):
+        out_host.fill_(float("nan"))
+        op.from_host(x_host, w_host, out_host, chunks=4)
+        op.host_done.synchronize()
+        assert torch.equal(out_host, want.cpu()), (transport, "from_host", call)
 dist.barrier()
 dist.destroy_process_group()
 sys.stdout.write("rank %d ok\\n" % rank)

@@ -211,6 +211,24 @@ def test_sm_pairs_with_y_transposed_tables_and_a_cta_limit():
                 assert (got[i, j] == 7.0).all()
 
 
+def test_host_pipeline_matches_the_device_call():
+    # One rank: x and w from pinned host memory in pieces, result back to pinned host memory, against the plain call.
+    from tilejax_b200.collective import AllGatherMatmul
+
+    m, K, N = 2048, 512, 1024
+    x, w = rand_bf16((m, K), 0), rand_bf16((K, N), 1)
+    op = AllGatherMatmul(m, K, N, 256, 512, 512)
+    want = op(to_device(x), to_device(w)).clone()
+    x_host, w_host = to_device(x).cpu().pin_memory(), to_device(w).cpu().pin_memory()
+    out_host = torch.empty((m, N), dtype=torch.bfloat16).pin_memory()
+    for chunks in (8, 3, 1):  # 3 does not divide the 8 row blocks: the largest divisor below it is used
+        out_host.fill_(float("nan"))
+        op.from_host(x_host, w_host, out_host, chunks=chunks)
+        op.host_done.synchronize()
+        assert ops.device_status() == 0
+        assert torch.equal(out_host, want.cpu())
+
+
 def test_bad_arguments_are_errors():
     x = torch.zeros(256, 256, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(NativeError, match="multiple of 128"):

@@ -191,7 +191,7 @@ class AllGatherMatmul:
         return self.exchange.shard_buffer() if self.transport == "peer" else None
 
     def __call__(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-        ops, ex = self._ops, self.exchange
+        ops = self._ops
         if x.shape != (self.m, self.K) or w.shape != (self.K, self.N):
             raise ValueError("x must be this rank's (m, K) shard and w (K, N)")
         compute = torch.cuda.current_stream(self.device)
@@ -199,44 +199,136 @@ class AllGatherMatmul:
         if self.ranks == 1:
             ops.gemm(x, w, self.tm, self.tn, self.tk, out=own_out)
             return self.out
-        comm = self.comm_stream
         if self.transport == "peer":
-            parity = ex.calls & 1
-            staged = ex.send[parity]
+            staged = self.exchange.send[self.exchange.calls & 1]
             if x.data_ptr() != staged.data_ptr():
                 # Peers finished reading this half two calls ago, before the previous call's barrier.
                 compute.wait_event(self.barrier_done)
                 staged.copy_(x, non_blocking=True)
-            ex.calls += 1
-            self.x_ready.record(compute)
-            comm.wait_event(self.x_ready)
-            comm.wait_event(self.done)  # the previous call's GEMMs have finished reading xs
-            with torch.cuda.stream(comm):
-                ex.barrier()  # every rank's shard of this call is in its send buffer
-                self.barrier_done.record(comm)
-                for rnd, event in zip(ex.rounds, self.arrived, strict=True):
-                    ex.pull(rnd, parity)
-                    event.record(comm)
-        else:
-            self.x_ready.record(compute)
-            comm.wait_event(self.x_ready)
-            comm.wait_event(self.done)
-            with torch.cuda.stream(comm):
-                for rnd, event in zip(ex.rounds, self.arrived, strict=True):
-                    for req in ex.start_round(x, rnd):
-                        req.wait()
-                    event.record(comm)
+        self.x_ready.record(compute)
+        self._start_exchange(x)
         # Compute stream: the own shard at once, straight from x (it is never copied into xs), then each group of
         # shards once its last round has completed. While the exchange is in flight the GEMM leaves it a few SMs.
         try:
             ops.set_gemm_cta_limit(self.cta_limit)
             ops.gemm(x, w, self.tm, self.tn, self.tk, out=own_out)
-            for n, (last_shard, ti, tj) in enumerate(self.tables):
-                compute.wait_event(self.arrived[last_shard - 1])
-                if n == len(self.tables) - 1:
-                    ops.set_gemm_cta_limit(0)  # nothing is in flight behind the last group
-                ops.gemm(ex.xs, w, self.tm, self.tn, self.tk, tile_i=ti, tile_j=tj, out=self.out)
+            self._other_groups(w, compute)
         finally:
             ops.set_gemm_cta_limit(0)
         self.done.record(compute)
         return self.out
+
+    def _start_exchange(self, x: torch.Tensor) -> None:
+        """Enqueue the exchange rounds on the communication stream, behind `x_ready` (this rank's shard is in place:
+        in the send buffer for the peer transport, in x for nccl)."""
+        ex, comm = self.exchange, self.comm_stream
+        comm.wait_event(self.x_ready)
+        comm.wait_event(self.done)  # the previous call's GEMMs have finished reading xs
+        with torch.cuda.stream(comm):
+            if self.transport == "peer":
+                parity = ex.calls & 1
+                ex.calls += 1
+                ex.barrier()  # every rank's shard of this call is in its send buffer
+                self.barrier_done.record(comm)
+                for rnd, event in zip(ex.rounds, self.arrived, strict=True):
+                    ex.pull(rnd, parity)
+                    event.record(comm)
+            else:
+                for rnd, event in zip(ex.rounds, self.arrived, strict=True):
+                    for req in ex.start_round(x, rnd):
+                        req.wait()
+                    event.record(comm)
+
+    def _other_groups(self, w: torch.Tensor, compute, after_group=None) -> None:
+        """The GEMM launches over the shards that arrive, each behind its last round; `after_group(shards)` is
+        called after each launch is enqueued."""
+        ops, ex = self._ops, self.exchange
+        for n, (last_shard, ti, tj) in enumerate(self.tables):
+            compute.wait_event(self.arrived[last_shard - 1])
+            if n == len(self.tables) - 1:
+                ops.set_gemm_cta_limit(0)  # nothing is in flight behind the last group
+            ops.gemm(ex.xs, w, self.tm, self.tn, self.tk, tile_i=ti, tile_j=tj, out=self.out)
+            if after_group is not None:
+                after_group(self.groups[n + 1])
+
+    def from_host(self, x_host: torch.Tensor, w_host: torch.Tensor, out_host: torch.Tensor, chunks: int = 8) -> None:
+        """The same product for operands in pinned host memory, result into pinned host memory: the host-to-device
+        copies, the GEMMs and the device-to-host copies run as a pipeline on three streams, so a step costs about
+        its slower copy direction instead of the sum of both copies and the compute. w goes first (every tile needs
+        it), then this rank's rows of x in `chunks` pieces, each multiplied as soon as it has landed and its rows of
+        the result copied back while the next piece is still arriving; the other ranks' shards follow as in
+        `__call__`. Enqueues only: `out_host` is complete once `host_done` has been synchronised."""
+        ops = self._ops
+        if x_host.shape != (self.m, self.K) or w_host.shape != (self.K, self.N):
+            raise ValueError("x must be this rank's (m, K) shard and w (K, N)")
+        if out_host.shape != self.out.shape or out_host.dtype != self.out.dtype:
+            raise ValueError("out_host must be [ranks * m, N] bfloat16")
+        if not (x_host.is_pinned() and w_host.is_pinned() and out_host.is_pinned()):
+            raise ValueError("the host buffers must be pinned")
+        if not hasattr(self, "_stage"):
+            # Two sets of device staging buffers, used alternately, so that the next call's copies never wait for
+            # this call's GEMMs: (w, x, "the GEMMs that read this set are done"). With the peer transport x is
+            # staged in the send buffer, which already has two halves.
+            def stage():
+                w = torch.empty((self.K, self.N), dtype=torch.bfloat16, device=self.device)
+                x = None if self.transport == "peer" else torch.empty((self.m, self.K), dtype=torch.bfloat16,
+                                                                      device=self.device)
+                return w, x, torch.cuda.Event()
+
+            self._stage = [stage(), stage()]
+            self._host_calls = 0
+            self._h2d, self._d2h = torch.cuda.Stream(device=self.device), torch.cuda.Stream(device=self.device)
+            self.host_done = torch.cuda.Event()
+            self._w_ready = torch.cuda.Event()
+        w_dev, x_stage, set_done = self._stage[self._host_calls & 1]
+        self._host_calls += 1
+        blocks = self.m // self.tm
+        chunks = max(c for c in range(1, max(1, min(chunks, blocks)) + 1) if blocks % c == 0)
+        rows = self.m // chunks
+        compute = torch.cuda.current_stream(self.device)
+        h2d, d2h = self._h2d, self._d2h
+        x_dev = self.exchange.send[self.exchange.calls & 1] if self.transport == "peer" else x_stage
+        base = self.me * self.m
+
+        h2d.wait_event(set_done)  # the GEMMs of two calls ago have read this set's w and x
+        compute.wait_event(self.host_done)  # the previous call's rows of `out` have all been copied back
+        if self.transport == "peer":
+            h2d.wait_event(self.barrier_done)  # peers finished reading this half of the send buffer two calls ago
+        with torch.cuda.stream(h2d):
+            w_dev.copy_(w_host, non_blocking=True)
+            self._w_ready.record(h2d)
+        compute.wait_event(self._w_ready)
+        try:
+            ops.set_gemm_cta_limit(self.cta_limit)
+            for c in range(chunks):
+                lo, hi = c * rows, (c + 1) * rows
+                landed, computed = torch.cuda.Event(), torch.cuda.Event()
+                with torch.cuda.stream(h2d):
+                    x_dev[lo:hi].copy_(x_host[lo:hi], non_blocking=True)
+                    landed.record(h2d)
+                compute.wait_event(landed)
+                ops.gemm(x_dev[lo:hi], w_dev, self.tm, self.tn, self.tk, out=self.out[base + lo : base + hi])
+                computed.record(compute)
+                d2h.wait_event(computed)
+                with torch.cuda.stream(d2h):
+                    out_host[base + lo : base + hi].copy_(self.out[base + lo : base + hi], non_blocking=True)
+            if self.ranks > 1:
+                self.x_ready.record(h2d)  # the whole shard is in place
+                self._start_exchange(x_dev)
+                order = shard_order(self.me, self.ranks)
+
+                def copy_back(shards):
+                    computed = torch.cuda.Event()
+                    computed.record(compute)
+                    d2h.wait_event(computed)
+                    with torch.cuda.stream(d2h):
+                        for s in shards:
+                            lo = order[s] * self.m
+                            out_host[lo : lo + self.m].copy_(self.out[lo : lo + self.m], non_blocking=True)
+
+                self._other_groups(w_dev, compute, copy_back)
+        finally:
+            ops.set_gemm_cta_limit(0)
+        self.done.record(compute)
+        set_done.record(compute)
+        self.host_done.record(d2h)
