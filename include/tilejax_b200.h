@@ -93,6 +93,27 @@ int tjx_gemm_set_cta_limit(int max_ctas);
  * (src/autokernel/tune.py:246-300): a launch-shape knob with no effect on values. */
 int tjx_gemm_set_pair_mode(int mode);
 
+/* `all_gather_matmul` in one launch (the ring kernel of src/autokernel/codegen.py:1149-1229, whose remote DMAs run
+ * beside its matmul steps): out[ranks * m, N] = all_gather(x) @ y on this rank. The GEMM kernel carries one extra
+ * warp per CTA that pulls the other ranks' shards out of peer memory (plain loads over NVLink, no multicast) into
+ * `gathered`, 256 rows at a time in the order the ring would deliver them (round r: rank (me - r) mod ranks),
+ * while the tensor cores work through the tile table — the own shard's tiles first, straight from x_own. A tile of
+ * a remote shard starts once every CTA's slice of its 256-row block has landed (`arrivals`).
+ *   peer_shards   ranks pointers: rank r's [m, K] shard as mapped into THIS process (entry `me` is ignored). Every
+ *                 peer's shard must be complete and stay unchanged until this launch has finished on every rank:
+ *                 the caller orders that with its own cross-rank barrier on the stream, before and after.
+ *   gathered      [ranks * m, K] bf16 scratch on this GPU (rows of rank `me` are never written or read)
+ *   tile_i/tile_j every (row tile, column tile) of the output once, in the order to walk them: own shard first, then
+ *                 shards in arrival order (Schedule.tables of `all_gather_matmul`, src/autokernel/schedule.py:150-194)
+ *   arrivals      int32[ranks * m / 256], zero before the first call; `epoch` = 1, 2, 3, ... counts the calls that
+ *                 used this array (it is never reset)
+ * Constraints: tm % 256 == 0, tn % 256 == 0, m % tm == 0, N % tn == 0, K % 8 == 0; 2 <= ranks <= 8. The launch
+ * occupies every SM (its CTAs wait on one another's copier warps): run nothing else on the GPU beside it. */
+int tjx_all_gather_gemm_bf16(const void* x_own, const void* const* peer_shards, void* gathered, const void* y,
+                             void* out, int ranks, int me, int m, int N, int K, int tm, int tn, int tk,
+                             const int32_t* tile_i, const int32_t* tile_j, int n_tiles, int32_t* arrivals, int epoch,
+                             tjx_stream_t stream);
+
 /* Flash-style causal attention, the step loop of `causal_attention` (examples/causal_attention.py:37-63):
  * q (pre-scaled), k, v, out [B, H, S, D] bf16, D == 128; online softmax in f32, P rounded to bf16 before P @ v.
  *   step_tile, step_code  int32[pattern_steps]: one (b, h)'s steps (Schedule.tables "step_tile"/"step_code",

@@ -10,7 +10,7 @@ from pathlib import Path
 import numpy as np
 
 from tilejax_b200 import schedule
-from tilejax_b200.collective import exchange_rounds, shard_order
+from tilejax_b200.collective import banded_tiles, exchange_rounds, shard_order
 
 ROOT = Path(__file__).resolve().parent.parent
 
@@ -27,6 +27,20 @@ def test_exchange_rounds_deliver_shards_in_the_reference_ring_order():
                 peer = exchange_rounds(rnd.send_to, ranks)[rnd.step - 1]
                 assert peer.recv_from == me
     assert exchange_rounds(0, 1) == []
+
+
+def test_banded_tile_tables_list_every_tile_once_shard_by_shard():
+    # A shard's tiles in column bands: every (row block, column tile) exactly once, a band's tiles together, and
+    # within a band row block by row block — for ragged band counts too.
+    for col_tiles, band in ((16, 4), (6, 4), (3, 1), (5, 8)):
+        rows = schedule.collective_row_blocks(1, 4, 3)[3:6]  # the second shard rank 1 of 4 computes
+        ti, tj = banded_tiles(rows, col_tiles, band)
+        assert ti.dtype == np.int32 and tj.dtype == np.int32
+        assert sorted(zip(ti.tolist(), tj.tolist())) == sorted((int(r), c) for r in rows for c in range(col_tiles))
+        bands = (tj // band).tolist()
+        assert bands == sorted(bands)
+        first_band = [(i, j) for i, j in zip(ti.tolist(), tj.tolist()) if j < band]
+        assert first_band == [(int(r), c) for r in rows for c in range(min(band, col_tiles))]
 
 
 WORKER = """

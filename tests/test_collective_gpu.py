@@ -32,7 +32,7 @@ dist.all_gather(parts, x)
 xs = torch.cat(parts)
 want = ops.gemm(xs, w, 256, 512, 512)                      # the same kernel on rows already gathered
 exact = (xs[::97].double() @ w.double())
-for transport in ("peer", "nccl"):
+for transport in ("fused", "peer", "nccl"):
     op = AllGatherMatmul(m, K, N, 256, 512, 512, transport=transport)
     for call in range(3):                                    # several calls: both halves of the send buffer
         xc = (x * (call + 1)).to(torch.bfloat16)

@@ -118,6 +118,18 @@ class PeerExchange:
         self.rows(rnd.recv_from).copy_(self.peers[rnd.recv_from][parity], non_blocking=True)
 
 
+def banded_tiles(row_blocks: np.ndarray, col_tiles: int, band: int) -> tuple[np.ndarray, np.ndarray]:
+    """(tile_i, tile_j) over `row_blocks` x all `col_tiles` column tiles, walked in column bands `band` tiles wide:
+    within a band row block by row block. The CTAs in flight then share a band's slice of y, which stays in L2,
+    instead of streaming all of y once per row block. Every tile appears exactly once."""
+    ti, tj = [], []
+    for first in range(0, col_tiles, band):
+        cols = np.arange(first, min(first + band, col_tiles), dtype=np.int32)
+        ti.append(np.repeat(row_blocks.astype(np.int32), cols.size))
+        tj.append(np.tile(cols, row_blocks.size))
+    return np.concatenate(ti), np.concatenate(tj)
+
+
 def shard_groups(ranks: int) -> list[list[int]]:
     """Which shards (in arrival order: 0 is the own shard) each GEMM launch covers: the own shard alone first —
     nothing has arrived yet — then the shards that arrive while it runs, then the rest: three launches at most, so
@@ -146,10 +158,12 @@ class AllGatherMatmul:
         device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
         self.device = device
         ranks = dist.get_world_size(group) if dist.is_initialized() else 1
-        if transport not in ("peer", "nccl"):
-            raise ValueError("transport is 'peer' or 'nccl'")
+        if transport not in ("fused", "peer", "nccl"):
+            raise ValueError("transport is 'fused', 'peer' or 'nccl'")
         self.transport = transport if ranks > 1 else "none"
-        if self.transport == "peer":
+        if self.transport == "fused" and (min(tm, m) % 256 or min(tn, N) % 256):
+            self.transport = "peer"  # the fused kernel works in 256 x 256 pieces
+        if self.transport in ("peer", "fused"):
             self.exchange = PeerExchange(m, K, torch.bfloat16, device, group)
         else:
             self.exchange = ShardExchange(m, K, torch.bfloat16, device, group)
@@ -166,20 +180,28 @@ class AllGatherMatmul:
         self.done = torch.cuda.Event()
         sms = torch.cuda.get_device_properties(device).multi_processor_count
         if reserve_sms is None:
-            reserve_sms = 4 if self.transport == "peer" else 32
+            reserve_sms = {"peer": 4, "nccl": 32}.get(self.transport, 0)
         self.cta_limit = max(1, sms - reserve_sms) if self.ranks > 1 and reserve_sms > 0 else 0
         # One GEMM launch per group of shards; the tile table of a group lists its shards' row blocks, in arrival
         # order, times every column block, row-major. The own shard needs none: its tiles come straight from x.
         shard_blocks = m // self.tm
-        cols = np.arange(N // self.tn, dtype=np.int32)
+        col_tiles, band = N // self.tn, max(1, 2048 // self.tn)
         order = _schedule.collective_row_blocks(self.me, self.ranks, shard_blocks)
         self.groups = shard_groups(self.ranks)
         self.tables = []
         for group_shards in self.groups[1:]:
             rows = np.concatenate([order[s * shard_blocks : (s + 1) * shard_blocks] for s in group_shards])
-            ti = torch.from_numpy(np.repeat(rows, cols.size).astype(np.int32)).to(device)
-            tj = torch.from_numpy(np.tile(cols, rows.size).astype(np.int32)).to(device)
-            self.tables.append((group_shards[-1], ti, tj))
+            ti, tj = banded_tiles(rows, col_tiles, band)
+            self.tables.append((group_shards[-1], torch.from_numpy(ti).to(device), torch.from_numpy(tj).to(device)))
+        if self.transport == "fused":
+            # One launch over every tile, a shard at a time — own first, then in arrival order — and in column
+            # bands within a shard; the kernel's copier warps count every 256-row block they have brought in.
+            parts = [banded_tiles(order[s * shard_blocks : (s + 1) * shard_blocks], col_tiles, band)
+                     for s in range(self.ranks)]
+            self.all_ti = torch.from_numpy(np.concatenate([p[0] for p in parts])).to(device)
+            self.all_tj = torch.from_numpy(np.concatenate([p[1] for p in parts])).to(device)
+            self.arrivals = torch.zeros(self.ranks * m // 256, dtype=torch.int32, device=device)
+            self.epoch = 0
 
     @property
     def steps(self) -> int:
@@ -187,8 +209,8 @@ class AllGatherMatmul:
         return (self.ranks * self.m // self.tm) * (self.N // self.tn) * (self.K // self.tk)
 
     def shard_buffer(self) -> torch.Tensor | None:
-        """With the peer transport: the buffer to write the next call's x into to save a copy (else None)."""
-        return self.exchange.shard_buffer() if self.transport == "peer" else None
+        """With the peer-memory transports: the buffer to write the next call's x into to save a copy (else None)."""
+        return self.exchange.shard_buffer() if self.transport in ("peer", "fused") else None
 
     def __call__(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         ops = self._ops
@@ -198,6 +220,13 @@ class AllGatherMatmul:
         own_out = self.out[self.me * self.m : (self.me + 1) * self.m]
         if self.ranks == 1:
             ops.gemm(x, w, self.tm, self.tn, self.tk, out=own_out)
+            return self.out
+        if self.transport == "fused":
+            staged = self.exchange.send[self.exchange.calls & 1]
+            if x.data_ptr() != staged.data_ptr():
+                staged.copy_(x, non_blocking=True)  # peers finished with this half before the previous barrier
+            self._fused_launch(w)
+            self.done.record(compute)
             return self.out
         if self.transport == "peer":
             staged = self.exchange.send[self.exchange.calls & 1]
@@ -218,6 +247,19 @@ class AllGatherMatmul:
         self.done.record(compute)
         return self.out
 
+    def _fused_launch(self, w: torch.Tensor) -> None:
+        """Current stream: a barrier (every rank's shard of this call is in its send buffer, and every rank has
+        finished the previous call), then the one launch that gathers and multiplies."""
+        ex = self.exchange
+        parity = ex.calls & 1
+        ex.calls += 1
+        ex.barrier()
+        self.barrier_done.record(torch.cuda.current_stream(self.device))
+        self.epoch += 1
+        shards = [ex.peers[r][parity] for r in range(self.ranks)]
+        self._ops.all_gather_gemm(ex.send[parity], shards, ex.xs, w, self.out, self.me, self.tm, self.tn, self.tk,
+                                  self.all_ti, self.all_tj, self.arrivals, self.epoch)
+
     def _start_exchange(self, x: torch.Tensor) -> None:
         """Enqueue the exchange rounds on the communication stream, behind `x_ready` (this rank's shard is in place:
         in the send buffer for the peer transport, in x for nccl)."""
@@ -225,7 +267,7 @@ class AllGatherMatmul:
         comm.wait_event(self.x_ready)
         comm.wait_event(self.done)  # the previous call's GEMMs have finished reading xs
         with torch.cuda.stream(comm):
-            if self.transport == "peer":
+            if self.transport in ("peer", "fused"):
                 parity = ex.calls & 1
                 ex.calls += 1
                 ex.barrier()  # every rank's shard of this call is in its send buffer
@@ -271,8 +313,8 @@ class AllGatherMatmul:
             # staged in the send buffer, which already has two halves.
             def stage():
                 w = torch.empty((self.K, self.N), dtype=torch.bfloat16, device=self.device)
-                x = None if self.transport == "peer" else torch.empty((self.m, self.K), dtype=torch.bfloat16,
-                                                                      device=self.device)
+                x = None if self.transport in ("peer", "fused") else torch.empty(
+                    (self.m, self.K), dtype=torch.bfloat16, device=self.device)
                 return w, x, torch.cuda.Event()
 
             self._stage = [stage(), stage()]
@@ -287,12 +329,15 @@ class AllGatherMatmul:
         rows = self.m // chunks
         compute = torch.cuda.current_stream(self.device)
         h2d, d2h = self._h2d, self._d2h
-        x_dev = self.exchange.send[self.exchange.calls & 1] if self.transport == "peer" else x_stage
+        # (With the fused transport the pieces of the own shard are multiplied as they land, so the other shards
+        # take the copy-engine path here: one launch over everything could not start before the last piece.)
+        peer_memory = self.transport in ("peer", "fused")
+        x_dev = self.exchange.send[self.exchange.calls & 1] if peer_memory else x_stage
         base = self.me * self.m
 
         h2d.wait_event(set_done)  # the GEMMs of two calls ago have read this set's w and x
         compute.wait_event(self.host_done)  # the previous call's rows of `out` have all been copied back
-        if self.transport == "peer":
+        if peer_memory:
             h2d.wait_event(self.barrier_done)  # peers finished reading this half of the send buffer two calls ago
         with torch.cuda.stream(h2d):
             w_dev.copy_(w_host, non_blocking=True)

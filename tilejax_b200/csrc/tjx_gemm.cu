@@ -43,6 +43,16 @@ struct GemmParams {
   int num_kb;
   void* out;
   int* status;
+  // All-gather fused into the launch (gemm_pair_kernel<.., true> only): rows [own_lo, own_hi) of the gathered
+  // operand are this GPU's shard and come from map_a_own; the other shards are pulled from peer memory into
+  // `gather_dst` by one extra warp per CTA, 256-row block by block in arrival order, and counted in
+  // `gather_arrivals` (one counter per 256-row block of the gathered operand; never reset: a launch waits for
+  // gather_epoch * copier warps).
+  int gather_ranks, gather_me, gather_rows;  // ranks, this rank, rows per shard
+  int gather_epoch;
+  const void* gather_src[8];                 // rank r's shard as mapped into this GPU's address space
+  void* gather_dst;                          // [ranks * rows, K]
+  int* gather_arrivals;
 };
 
 struct Item {
@@ -387,6 +397,33 @@ constexpr int PAIR_ROWS = 2 * BM;
 constexpr int PAIR_STAGES = 3;
 constexpr int PAIR_KSUB = 2;
 
+constexpr int GATHER_THREADS = GEMM_THREADS + 32;  // the pair kernel with its copier warp
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Bounded wait until a 256-row block of the gathered operand has been written by every copier warp.
+__device__ __forceinline__ bool gather_wait(const int* counter, int target, volatile int* abort_flag, int* status) {
+  if (ld_acquire_gpu(counter) >= target) return true;
+  unsigned long long start = 0;
+  for (uint32_t it = 1;; ++it) {
+    if (ld_acquire_gpu(counter) >= target) return true;
+    if ((it & 63u) == 0) {
+      if (*abort_flag) return false;
+      const unsigned long long now = globaltimer_ns();
+      if (start == 0) start = now;
+      if (now - start > WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        if (status != nullptr) atomicCAS(status, 0, TJX_ERR_WAIT_OTHER);
+        return false;
+      }
+    }
+  }
+}
+
 template <int STAGES, int KSUB>
 struct PairSmem {
   static constexpr int A_BYTES = BM * BK * 2;             // this CTA's 128 rows of x, one block of 64 k
@@ -400,10 +437,11 @@ struct PairSmem {
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
-template <int STAGES, int KSUB>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+template <int STAGES, int KSUB, bool GATHER>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THREADS : GEMM_THREADS, 1)
     gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                     const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
+                     const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_a_own,
+                     const GemmParams p) {
   using L = PairSmem<STAGES, KSUB>;
   constexpr int BN = PAIR_BN;
   const int num_slots = (p.num_kb + KSUB - 1) / KSUB;  // ring slots per work item
@@ -440,6 +478,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
     tma_prefetch_desc(&map_a);
     tma_prefetch_desc(&map_b);
     tma_prefetch_desc(&map_c);
+    if (GATHER) tma_prefetch_desc(&map_a_own);
   }
   if (warp == 1) {
     tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_holder)), TMEM_COLS);
@@ -461,6 +500,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
       for (int w = pair; w < total_items && ok; w += n_pairs) {
         const Item it = decode_item<PAIR_ROWS, BN>(p, w);
         if (!it.compute) continue;
+        bool own = true;
+        if (GATHER) {
+          own = it.m0 / p.gather_rows == p.gather_me;
+          if (!own) {
+            // The rows of this piece come from another GPU: wait until the copier warps have all written them,
+            // then order those (generic-proxy) writes before this thread's TMA reads.
+            if (!gather_wait(p.gather_arrivals + it.m0 / PAIR_ROWS, p.gather_epoch * static_cast<int>(gridDim.x),
+                             abort_flag, p.status)) {
+              ok = false;
+              break;
+            }
+            asm volatile("fence.proxy.async;" ::: "memory");
+          }
+        }
         for (int slot = 0; slot < num_slots; ++slot) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, TJX_ERR_WAIT_EMPTY)) {
             ok = false;
@@ -474,7 +527,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
             const int kb = slot * KSUB + sub;
             const uint32_t a_dst = base + L::RING_OFF + stage * L::STAGE_BYTES + sub * L::SUB_BYTES;
             const uint32_t b_dst = a_dst + L::A_BYTES;
-            tma_load_2d_pair(a_dst, &map_a, kb * BK, it.m0 + row_off, bar);
+            if (GATHER && own)
+              tma_load_2d_pair(a_dst, &map_a_own, kb * BK, it.m0 - p.gather_me * p.gather_rows + row_off, bar);
+            else
+              tma_load_2d_pair(a_dst, &map_a, kb * BK, it.m0 + row_off, bar);
             if (p.b_kmajor) {
               tma_load_2d_pair(b_dst, &map_b, kb * BK, it.n0 + col_off, bar);
             } else {
@@ -540,6 +596,36 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
       }
     }
     __syncwarp();
+  } else if (GATHER && warp == 6) {
+    // ------------------------------------------------------------------ copier (one warp per CTA)
+    // Pulls the other ranks' shards from peer memory into this GPU's copy, a 256-row block at a time in the order
+    // the tiles will want them (round r brings the shard of rank (me - r) mod ranks), every CTA's warp a slice
+    // of each block: 16 bytes per lane per load, eight loads in flight. It waits for nothing — the peers' shards
+    // were complete before the launch — so the warps that wait on its counters always see progress.
+    const int per_shard = p.gather_rows / PAIR_ROWS;
+    const size_t block_bytes = static_cast<size_t>(PAIR_ROWS) * p.K * 2;
+    const size_t slice = ((block_bytes + gridDim.x - 1) / gridDim.x + 511) / 512 * 512;
+    const size_t lo = min(block_bytes, slice * blockIdx.x), hi = min(block_bytes, lo + slice);
+    for (int r = 1; r < p.gather_ranks; ++r) {
+      const int src_rank = (p.gather_me - r + p.gather_ranks) % p.gather_ranks;
+      for (int blk = 0; blk < per_shard; ++blk) {
+        const uint8_t* src = static_cast<const uint8_t*>(p.gather_src[src_rank]) + blk * block_bytes;
+        const int row_block = src_rank * per_shard + blk;
+        uint8_t* dst = static_cast<uint8_t*>(p.gather_dst) + row_block * block_bytes;
+        for (size_t off = lo + lane * 16; off < hi; off += 8 * 512) {
+          uint4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (off + u * 512 < hi) v[u] = __ldcg(reinterpret_cast<const uint4*>(src + off + u * 512));
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (off + u * 512 < hi) *reinterpret_cast<uint4*>(dst + off + u * 512) = v[u];
+        }
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) atomicAdd(p.gather_arrivals + row_block, 1);
+      }
+    }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5 of each CTA)
     const int q = warp & 3;
@@ -588,11 +674,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
   }
 }
 
-template <int STAGES, int KSUB>
+template <int STAGES, int KSUB, bool GATHER>
 static int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
-                            const GemmParams& p, int grid, cudaStream_t stream) {
+                            const CUtensorMap& ma_own, const GemmParams& p, int grid, cudaStream_t stream) {
   using L = PairSmem<STAGES, KSUB>;
-  auto kernel = gemm_pair_kernel<STAGES, KSUB>;
+  auto kernel = gemm_pair_kernel<STAGES, KSUB, GATHER>;
   static bool configured[64] = {};
   int dev = 0;
   TJX_CUDA(cudaGetDevice(&dev));
@@ -600,7 +686,7 @@ static int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const 
     TJX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
     configured[dev & 63] = true;
   }
-  kernel<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(ma, mb, mc, p);
+  kernel<<<grid, GATHER ? GATHER_THREADS : GEMM_THREADS, L::TOTAL, stream>>>(ma, mb, mc, ma_own, p);
   TJX_CUDA(cudaGetLastError());
   return 0;
 }
@@ -713,7 +799,7 @@ extern "C" int tjx_gemm_bf16(const void* x, const void* y, void* out, int M, int
   if (pair) {
     int pairs = static_cast<int>(total_items < sm_count() / 2 ? total_items : sm_count() / 2);
     if (g_gemm_cta_limit > 0) pairs = std::max(1, std::min(pairs, g_gemm_cta_limit / 2));
-    return launch_gemm_pair<PAIR_STAGES, PAIR_KSUB>(ma, mb, mc, p, 2 * pairs, s);
+    return launch_gemm_pair<PAIR_STAGES, PAIR_KSUB, false>(ma, mb, mc, ma, p, 2 * pairs, s);
   }
   if (BN == 256) {
     if (stages == 3) return launch_gemm<256, 3>(ma, mb, mc, p, grid, s);
@@ -721,4 +807,78 @@ extern "C" int tjx_gemm_bf16(const void* x, const void* y, void* out, int M, int
   }
   if (stages == 6) return launch_gemm<128, 6>(ma, mb, mc, p, grid, s);
   return launch_gemm<128, 4>(ma, mb, mc, p, grid, s);
+}
+
+// out = all_gather(x) @ y in ONE launch: the pair GEMM whose extra warp per CTA pulls the other ranks' shards from
+// peer memory while the tensor cores work on the shards that are already here (the own one first).
+extern "C" int tjx_all_gather_gemm_bf16(const void* x_own, const void* const* peer_shards, void* gathered,
+                                        const void* y, void* out, int ranks, int me, int m, int N, int K, int tm,
+                                        int tn, int tk, const int32_t* tile_i, const int32_t* tile_j, int n_tiles,
+                                        int32_t* arrivals, int epoch, tjx_stream_t stream) {
+  using namespace tjx;
+  if (int rc = check_device()) return rc;
+  if (!x_own || !peer_shards || !gathered || !y || !out || !arrivals || !tile_i || !tile_j)
+    return fail(TJX_E_ARG, "a pointer is null");
+  if (ranks < 2 || ranks > 8 || me < 0 || me >= ranks) return fail(TJX_E_ARG, "2 to 8 ranks, 0 <= me < ranks");
+  if (m <= 0 || N <= 0 || K <= 0 || K % 8 != 0 || N % 8 != 0) return fail(TJX_E_ARG, "m, N, K must be positive, K and N multiples of 8");
+  if (tm <= 0 || tn <= 0 || tk <= 0 || tm % PAIR_ROWS != 0 || tn % PAIR_BN != 0 || m % tm != 0 || N % tn != 0)
+    return fail(TJX_E_ARG, "tm and tn must be multiples of 256 that divide a shard's rows and N");
+  if (epoch <= 0 || epoch > (1 << 22)) return fail(TJX_E_ARG, "epoch counts this buffer's calls from 1 (at most 2^22)");
+  const long long M = static_cast<long long>(ranks) * m;
+  if (M >= (1ll << 31) || n_tiles != (M / tm) * (N / tn))
+    return fail(TJX_E_ARG, "the tile table must list every tile of the [ranks * m, N] output once");
+  for (int r = 0; r < ranks; ++r)
+    if (r != me && (peer_shards[r] == nullptr || (reinterpret_cast<uintptr_t>(peer_shards[r]) & 15u)))
+      return fail(TJX_E_ARG, "a peer shard pointer is null or not 16-byte aligned");
+
+  GemmParams p{};
+  p.M = static_cast<int>(M), p.N = N, p.K = K, p.tm = tm, p.tn = tn;
+  p.tiles_m = static_cast<int>(M / tm), p.tiles_n = N / tn, p.band_tiles = 1;
+  p.sub_m = tm / PAIR_ROWS, p.sub_n = tn / PAIR_BN;
+  p.n_tiles = n_tiles, p.n_fills = 0, p.tile_i = tile_i, p.tile_j = tile_j;
+  p.num_kb = (K + BK - 1) / BK;
+  p.out = out;
+  p.status = device_status_word();
+  if (p.status == nullptr) return fail(TJX_E_CUDA, "could not locate the device status word");
+  p.gather_ranks = ranks, p.gather_me = me, p.gather_rows = m, p.gather_epoch = epoch;
+  for (int r = 0; r < ranks; ++r) p.gather_src[r] = r == me ? nullptr : peer_shards[r];
+  p.gather_dst = gathered, p.gather_arrivals = arrivals;
+
+  CUtensorMap ma, ma_own, mb, mc;
+  const uint32_t box_a[2] = {BK, BM};
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(K) * 2};
+    if (int rc = make_tensor_map(&ma, gathered, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 2, dims, strides, box_a,
+                                 CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  }
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(m)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(K) * 2};
+    if (int rc = make_tensor_map(&ma_own, x_own, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 2, dims, strides, box_a,
+                                 CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  }
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(K)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(N) * 2};
+    const uint32_t box[2] = {64, BK};
+    if (int rc = make_tensor_map(&mb, y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 2, dims, strides, box,
+                                 CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  }
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(M)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(N) * 2};
+    const uint32_t box[2] = {64, 32};
+    if (int rc = make_tensor_map(&mc, out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 2, dims, strides, box,
+                                 CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  }
+  // Every CTA must be resident at once (the producers wait on counters the copier warps of all CTAs raise): one
+  // CTA per SM, never more CTAs than SMs.
+  const long long total_items = static_cast<long long>(n_tiles) * p.sub_m * p.sub_n;
+  const int pairs = static_cast<int>(std::min<long long>(total_items, sm_count() / 2));
+  return launch_gemm_pair<PAIR_STAGES, PAIR_KSUB, true>(ma, mb, mc, ma_own, p, 2 * pairs, static_cast<cudaStream_t>(stream));
 }

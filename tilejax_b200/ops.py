@@ -127,6 +127,31 @@ def gemm(x: torch.Tensor, y: torch.Tensor, tm: int, tn: int, tk: int, *, causal:
     return out
 
 
+def all_gather_gemm(x_own: torch.Tensor, peer_shards: list[torch.Tensor | None], gathered: torch.Tensor,
+                    y: torch.Tensor, out: torch.Tensor, me: int, tm: int, tn: int, tk: int, tile_i: torch.Tensor,
+                    tile_j: torch.Tensor, arrivals: torch.Tensor, epoch: int) -> torch.Tensor:
+    """out = all_gather(x) @ y in one launch: the GEMM's copier warps pull `peer_shards[r]` (rank r's shard as
+    mapped into this process; entry `me` is ignored) into `gathered` while the own shard's tiles run. The caller
+    orders the launch against the peers with its own barrier (see `collective.AllGatherMatmul`)."""
+    device = _need_cuda(x_own, y)
+    ranks = len(peer_shards)
+    m, K = x_own.shape
+    N = y.shape[1]
+    if gathered.shape != (ranks * m, K) or out.shape != (ranks * m, N) or y.shape[0] != K:
+        raise ValueError("gathered is [ranks * m, K], y [K, N], out [ranks * m, N]")
+    if any(t.dtype != torch.bfloat16 for t in (x_own, gathered, y, out)):
+        raise ValueError("operands and output are bfloat16")
+    if arrivals.dtype != torch.int32 or arrivals.numel() != ranks * m // 256:
+        raise ValueError("arrivals is int32[ranks * m / 256]")
+    pointers = (ctypes.c_void_p * ranks)(*[None if t is None or r == me else t.data_ptr()
+                                           for r, t in enumerate(peer_shards)])
+    with torch.cuda.device(device):
+        check(library().tjx_all_gather_gemm_bf16(_ptr(x_own), pointers, _ptr(gathered), _ptr(y), _ptr(out), ranks, me,
+                                                 m, N, K, tm, tn, tk, _ptr(tile_i), _ptr(tile_j),
+                                                 int(tile_i.numel()), _ptr(arrivals), int(epoch), _stream()))
+    return out
+
+
 def set_gemm_cta_limit(max_ctas: int) -> None:
     """Cap the persistent GEMM's grid for this thread's following launches (0 = one CTA per SM)."""
     check(library().tjx_gemm_set_cta_limit(int(max_ctas)))
