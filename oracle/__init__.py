@@ -18,7 +18,7 @@ which cannot be imported where this was written, so the oracle could not be run 
 
 from .attention import causal_attention_f64, causal_attention_ref
 from .compare import compare
-from .decode import paged_gqa_decode_f64, paged_gqa_decode_ref, to_pages
+from .decode import gqa_decode_ref, paged_gqa_decode_f64, paged_gqa_decode_ref, to_pages
 from .matmul import causal_matmul_ref, collective_row_order, matmul_ref
 from .steps import (
     attention_step_tables,
@@ -37,6 +37,7 @@ __all__ = [
     "collective_row_order",
     "compare",
     "device_step_tables",
+    "gqa_decode_ref",
     "lengths_runs",
     "matmul_ref",
     "paged_gqa_decode_f64",

@@ -62,6 +62,45 @@ def paged_gqa_decode_ref(q, k_pages, v_pages, block_tables, lengths) -> np.ndarr
     return out
 
 
+def gqa_decode_ref(q, k_cache, v_cache, lengths, block_kv: int = 512) -> np.ndarray:
+    """examples/decode.py:176-196 with T = 1: the contiguous cache (B, S, Hkv * Dh) walked in blocks of
+    min(block_kv, S) positions, a block skipped when its first position is >= lengths[b] (:190-191), the same
+    `visible` mask, `online_softmax` and `finish` as the paged nest. Written out on its own (not through the paged
+    restatement) so that the two can be checked against each other."""
+    B, T, H, Dh = q.shape
+    assert T == 1
+    S, W = k_cache.shape[1], k_cache.shape[2]
+    Hkv = W // Dh
+    G = H // Hkv
+    bk = min(block_kv, S)
+    dtype = q.dtype
+    qf = np.asarray(q).astype(np.float32)
+    out = np.zeros((B, T, H, Dh), dtype)
+    for b in range(B):
+        n = int(lengths[b])
+        qt = qf[b, 0].reshape(Hkv, G, Dh)
+        row_max = np.full((Hkv, G, 1), MASK_VALUE, np.float32)
+        row_sum = np.zeros((Hkv, G, 1), np.float32)
+        acc = np.zeros((Hkv, G, Dh), np.float32)
+        for j in range(0, S, bk):
+            if j >= n:
+                continue
+            kt = np.asarray(k_cache[b, j : j + bk]).astype(np.float32).reshape(bk, Hkv, Dh).transpose(1, 0, 2)
+            vt = np.asarray(v_cache[b, j : j + bk]).astype(np.float32).reshape(bk, Hkv, Dh).transpose(1, 0, 2)
+            s = qt @ kt.transpose(0, 2, 1)
+            ok = (j + np.arange(bk)) < n
+            s = np.where(ok[None, None, :], s, MASK_VALUE)
+            max_new = np.maximum(row_max, s.max(axis=2, keepdims=True))
+            pr = np.exp(s - max_new)
+            alpha = np.exp(row_max - max_new)
+            row_sum = alpha * row_sum + pr.sum(axis=2, keepdims=True, dtype=np.float32)
+            acc = alpha * acc + pr.astype(dtype).astype(np.float32) @ vt
+            row_max = max_new
+        res = acc * (np.float32(1.0) / np.maximum(row_sum, np.float32(1e-30)))
+        out[b, 0] = res.reshape(H, Dh).astype(dtype)
+    return out
+
+
 def paged_gqa_decode_f64(q, k_pages, v_pages, block_tables, lengths) -> np.ndarray:
     """Independent check in float64 (the shape of tests/test_decode.py:62-76): gather each sequence's valid
     positions, dense softmax; zeros for an empty sequence."""

@@ -73,6 +73,24 @@ def test_paged_equals_the_same_cache_laid_out_in_order():
     np.testing.assert_array_equal(f64(a), f64(b))
 
 
+@pytest.mark.parametrize("block", [128, 512])
+def test_contiguous_cache_is_the_identity_block_table(block):
+    # `gqa_decode` (examples/decode.py:176-196): against its own oracle, and bit-equal to the paged call over the
+    # same cache cut into pages in order.
+    B, S = 4, 1024
+    k, v = rand_bf16((B, S, 512), 1), rand_bf16((B, S, 512), 2)
+    q = rand_bf16((B, 1, 16, 128), 3, 128**-0.5)
+    lengths = np.array([0, 1, 700, 1024], np.int32)
+    got = to_host(ops.gqa_decode(to_device(q), to_device(k), to_device(v), to_device(lengths), block))
+    assert ops.device_status() == 0
+    want = oracle.gqa_decode_ref(q, k, v, lengths, block)
+    assert np.abs(f64(got) - f64(want)).max() <= 2e-2 * np.abs(f64(want)).max()
+    assert not f64(got[0]).any()
+    ident = np.arange(B * S // block, dtype=np.int32).reshape(B, S // block)
+    paged = run_decode(q, oracle.to_pages(k, ident), oracle.to_pages(v, ident), ident, lengths)
+    np.testing.assert_array_equal(f64(got), f64(paged))
+
+
 def test_all_sequences_empty():
     q, kp, vp, bt, lengths = synthetic.decode_inputs(5, 8, 2, 128, 16, 4, 20)
     lengths[:] = 0

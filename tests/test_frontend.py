@@ -66,6 +66,11 @@ def test_decode_steps_are_found_on_the_device():
                                        spec(4, 4, dtype=np.int32), spec(4, dtype=np.int32))
     assert lowered.schedule.runtime and lowered.schedule.empty and lowered.steps == 16  # at most
     assert "built on the device from lengths" in lowered.source
+    # The contiguous cache is the same kernel over the identity block table (examples/decode.py:176-196).
+    flat = K.gqa_decode.lower(spec(4, 1, 8, 128), spec(4, 1024, 256), spec(4, 1024, 256), spec(4, dtype=np.int32),
+                              K.DecodeTiles(block_kv=256))
+    assert flat.schedule.runtime and flat.steps == 4 * 4 and "identity block table" in flat.source
+    assert flat.plan.params["page"] == 256 and flat.plan.params["num_pages"] == 16
 
 
 def test_tiles_clamp_to_the_matrix_and_neighbours_that_build_the_same_kernel_are_skipped():
@@ -101,6 +106,10 @@ def test_references_equal_the_oracle_for_every_nest():
     got = K.paged_gqa_decode.reference(q, kp, vp, bt, lengths)
     np.testing.assert_array_equal(f64(got), f64(oracle.paged_gqa_decode_ref(q, kp, vp, bt, lengths)))
     assert not f64(got[0]).any()
+    kc, vc = rand_bf16((3, 512, 256), 4), rand_bf16((3, 512, 256), 5)
+    qc, lens = rand_bf16((3, 1, 8, 128), 6, 128**-0.5), np.array([0, 300, 512], np.int32)
+    np.testing.assert_array_equal(f64(K.gqa_decode.reference(qc, kc, vc, lens, K.DecodeTiles(block_kv=128))),
+                                  f64(oracle.gqa_decode_ref(qc, kc, vc, lens, 128)))
     np.testing.assert_array_equal(f64(K.all_gather_matmul.reference(x, y, K.CollectiveTiles())),
                                   f64(oracle.matmul_ref(x, y, 256, 512, 256)))
 

@@ -159,6 +159,11 @@ def test_paged_oracle_equals_contiguous_layout():
     a = oracle.paged_gqa_decode_ref(q, oracle.to_pages(k, order), oracle.to_pages(v, order), order, lengths)
     b = oracle.paged_gqa_decode_ref(q, oracle.to_pages(k, ident), oracle.to_pages(v, ident), ident, lengths)
     np.testing.assert_array_equal(f64(a), f64(b))
+    # And the contiguous nest written out on its own (examples/decode.py:176-196) gives the same bits at the
+    # same block size, and stays within the decode tolerance of float64 at the default one.
+    np.testing.assert_array_equal(f64(oracle.gqa_decode_ref(q, k, v, lengths, P)), f64(b))
+    want = oracle.paged_gqa_decode_f64(q, oracle.to_pages(k, ident), oracle.to_pages(v, ident), ident, lengths)
+    assert np.abs(f64(oracle.gqa_decode_ref(q, k, v, lengths)) - want).max() <= 2e-2 * np.abs(want).max()
 
 
 def test_compare_rule():

@@ -404,11 +404,15 @@ def _lower(plan: Plan, config: Config) -> tuple[str, Callable[..., Any]]:
             f"tables      {', '.join(f'{k}[{len(v)}]' for k, v in sch.tables.items()) or 'none'}\n")
         return text, lambda q, k, v: ops.causal_attention(q, k, v, p["block_q"], p["block_kv"])
     text = header + (
-        f"kernel      tjx_paged_gqa_decode_bf16 (device step tables, per-warp TMA rings, f32 FMAs, split-KV merge)\n"
+        f"kernel      tjx_paged_gqa_decode_bf16 (device step tables, per-warp TMA rings, warp-level MMA, partials "
+        f"merged by the last warp to arrive)\n"
         f"problem     {p['B']} sequences, {p['H']} / {p['Hkv']} heads, head_dim {p['D']}, pages of {p['page']}, "
-        f"{p['pages']} pages per sequence, pool of {p['num_pages']}\n"
+        f"{p['pages']} pages per sequence, pool of {p['num_pages']}"
+        f"{' (a contiguous cache: the identity block table)' if p.get('contiguous') else ''}\n"
         f"steps       at most {sch.steps}: step_tile / step_code / step_count are built on the device from lengths "
         f"before the kernel\n")
+    if p.get("contiguous"):
+        return text, lambda q, kc, vc, lengths: ops.gqa_decode(q, kc, vc, lengths, p["page"])
     return text, lambda q, kp, vp, bt, lengths: ops.paged_gqa_decode(q, kp, vp, bt, lengths)
 
 

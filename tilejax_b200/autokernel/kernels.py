@@ -2,7 +2,7 @@
 
 Each is the plain loop nest over tiles whose meaning the kernel must reproduce — `kernel.fn` runs it as written on
 the CPU — with the same structure as the reference's examples (examples/matmul.py, causal_matmul.py,
-causal_attention.py, decode.py `paged_gqa_decode`, collective_matmul.py). Row statistics are kept as (rows, 1)
+causal_attention.py, decode.py `gqa_decode` and `paged_gqa_decode`, collective_matmul.py). Row statistics are kept as (rows, 1)
 columns here: the reference's lane-replicated (rows, 128) layout is a TPU register trick, not arithmetic.
 """
 
@@ -39,6 +39,13 @@ class CollectiveTiles:
     tm: int = autokernel.choice(128, 256, 512, 1024, default=256)
     tn: int = autokernel.choice(128, 256, 512, 1024, 2048, default=512)
     tk: int = autokernel.choice(128, 256, 512, 1024, 2048, default=512)
+
+
+@autokernel.tunable
+class DecodeTiles:
+    """Cache positions per step."""
+
+    block_kv: int = autokernel.choice(128, 256, 512, 1024, 2048, default=512)
 
 
 @autokernel.kernel
@@ -139,6 +146,32 @@ def finish(acc, row_sum, shape, dtype):
     """The normalised output as `shape`; rows that saw no key (an empty sequence) are 0."""
     out = acc * (1.0 / jnp.maximum(row_sum, 1e-30))
     return out.reshape(shape).astype(dtype)
+
+
+@autokernel.kernel
+def gqa_decode(q, k_cache, v_cache, lengths, tiles=DecodeTiles()):
+    """GQA decode attention over a contiguous cache: q (B, 1, H, Dh), caches (B, S_max, Hkv * Dh), sequence b's
+    valid positions lengths[b]."""
+    B, T, H, Dh = q.shape
+    S, W = k_cache.shape[1], k_cache.shape[2]
+    Hkv = W // Dh
+    bk, dtype = min(tiles.block_kv, S), q.dtype
+    out = jnp.zeros((B, T, H, Dh), dtype)
+    for b in range(B):
+        qt = queries_by_kv_head(q[b, :, :, :], Hkv)
+        row_max = jnp.full((Hkv, H // Hkv, 1), MASK_VALUE, jnp.float32)
+        row_sum = jnp.zeros((Hkv, H // Hkv, 1), jnp.float32)
+        acc = jnp.zeros((Hkv, H // Hkv, Dh), jnp.float32)
+        for j in range(0, S, bk):
+            if j >= lengths[b]:  # past the sequence's end: decided on the device, before the kernel runs
+                continue
+            kt = page_by_kv_head(k_cache[b, j : j + bk, :], Hkv)
+            s = jnp.dot(qt, kt.transpose(0, 2, 1), preferred_element_type=jnp.float32)
+            ok = visible(bk, j, lengths[b])
+            vt = page_by_kv_head(v_cache[b, j : j + bk, :], Hkv)
+            row_max, row_sum, acc = online_softmax(s, vt, ok, row_max, row_sum, acc)
+        out = out.at[b, :, :, :].set(finish(acc, row_sum, (T, H, Dh), dtype))
+    return out
 
 
 @autokernel.kernel

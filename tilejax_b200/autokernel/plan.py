@@ -316,9 +316,44 @@ def _recognise_attention(nest, ns, specs, outputs, parallel, reductions) -> Plan
     return Plan(nest, "attention", specs, outputs, parallel, reductions, params)
 
 
+def _recognise_contiguous_decode(nest, ns, specs, outputs, parallel, reductions) -> Plan:
+    """`gqa_decode`: (q, k_cache, v_cache, lengths), blocks of the cache skipped with `j >= lengths[b]`. It runs as
+    paged decode over the identity block table (block j of sequence b is page b * blocks + j)."""
+    (b,), (j,) = parallel, reductions
+    q, kc, vc, lengths = specs[:4]
+    mask = nest.reductions[0].mask
+    reads = {n.value.id for n in ast.walk(mask) if isinstance(n, ast.Subscript) and isinstance(n.value, ast.Name)}
+    if reads != {nest.inputs[3]} or np.dtype(lengths.dtype) != np.int32:
+        raise _unsupported(nest, "the block loop's mask must compare the block's first position with lengths[b]",
+                           nest.reductions[0].node)
+    if q.ndim != 4 or kc.ndim != 3 or kc.shape != vc.shape or lengths.ndim != 1:
+        raise _unsupported(nest, "decode takes q (B, T, H, D), caches (B, S, Hkv * D) and lengths (B,)")
+    B, T, H, D = q.shape
+    _, S, W = kc.shape
+    if T != 1:
+        raise _unsupported(nest, "several new tokens per sequence (T > 1)")
+    code = compile(ast.Expression(mask), nest.filename, "eval")
+
+    def skipped(jv: int, length: int) -> bool:
+        return bool(eval(code, dict(ns), {j.var: jv, b.var: 0, nest.inputs[3]: [length]}))
+
+    block = j.step
+    ok = all(skipped(jv, n) == (jv >= n) for jv in (0, block, (j.count - 1) * block) for n in (0, 1, block, block + 1, S))
+    if not ok or (b.count, kc.shape[0]) != (B, B) or j.start != 0 or j.stop != S or S % block:
+        raise _unsupported(nest, "the block loop must cover the cache and skip blocks with `j >= lengths[b]`",
+                           nest.reductions[0].node)
+    sch = _schedule.paged_decode_schedule(B, j.count)
+    params = dict(B=B, H=H, Hkv=W // D, D=D, page=block, pages=j.count, num_pages=B * j.count, schedule=sch,
+                  contiguous=True)
+    return Plan(nest, "decode", specs, outputs, parallel, reductions, params, runtime=True)
+
+
 def _recognise_decode(nest, ns, specs, outputs, parallel, reductions) -> Plan:
+    if len(parallel) == 1 and len(nest.inputs) == 4:
+        return _recognise_contiguous_decode(nest, ns, specs, outputs, parallel, reductions)
     if len(parallel) != 1 or len(nest.inputs) != 5:
-        raise _unsupported(nest, "a runtime mask other than paged decode's (q, k_pages, v_pages, block_tables, lengths)")
+        raise _unsupported(nest, "a runtime mask other than decode's: (q, k_cache, v_cache, lengths) or "
+                                 "(q, k_pages, v_pages, block_tables, lengths)")
     (b,), (p,) = parallel, reductions
     q, kp, vp, bt, lengths = specs[:5]
     mask = nest.reductions[0].mask

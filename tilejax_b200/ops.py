@@ -268,6 +268,28 @@ def paged_gqa_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
     return out
 
 
+@lru_cache(maxsize=16)
+def _identity_block_table(B: int, blocks: int, device: str) -> torch.Tensor:
+    return torch.arange(B * blocks, dtype=torch.int32, device=device).reshape(B, blocks)
+
+
+def gqa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, lengths: torch.Tensor,
+               block_kv: int = 512, out: torch.Tensor | None = None,
+               buffers: DecodeBuffers | None = None) -> torch.Tensor:
+    """The `gqa_decode` loop nest (examples/decode.py:176-196) for one new token per sequence: the contiguous cache
+    (B, S, Hkv * D) is the page pool whose block table is the identity — sequence b's block j is page
+    b * (S / block) + j — so the paged kernel runs unchanged, device step tables included."""
+    _need_cuda(q, k_cache, v_cache, lengths)
+    B, S, W = k_cache.shape
+    block = min(block_kv, S)
+    if v_cache.shape != k_cache.shape or S % block or not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise ValueError("caches are contiguous (B, S, Hkv * D) with S a multiple of the block")
+    blocks = S // block
+    table = _identity_block_table(B, blocks, str(q.device))
+    return paged_gqa_decode(q, k_cache.view(B * blocks, block, W), v_cache.view(B * blocks, block, W), table, lengths,
+                            out=out, buffers=buffers)
+
+
 def paged_gqa_decode_static(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_tables: torch.Tensor,
                             lengths: torch.Tensor, out: torch.Tensor, step_tile: torch.Tensor, step_code: torch.Tensor,
                             step_count: torch.Tensor, tile_first: torch.Tensor) -> torch.Tensor:
