@@ -39,6 +39,11 @@ def test_lowered_describes_the_kernel():
     assert K.matmul.source(spec(256, 384), spec(384, 256), TILES) == lowered.source
     assert "MatmulTiles(tm=128, tn=128, tk=128); 3 input / 2 output buffers" in lowered.source
     assert "tjx_gemm_bf16" in lowered.source and "ring of 4 slots" in lowered.source
+    # Tiles that are multiples of 256 run one MMA per pair of SMs unless the pipeline asks for a ring depth.
+    big = K.matmul.lower(spec(1024, 512), spec(512, 1024))
+    assert "CTA pair    256 x 256 x 64" in big.source
+    deep = K.matmul.lowered(K.matmul.signature(spec(1024, 512), spec(512, 1024)), Config(K.MatmulTiles(), Pipeline(4, 2)))
+    assert "CTA tile    128 x 256 x 64, ring of 4 slots" in deep.source
 
 
 def test_causal_matmul_skips_tiles_above_the_diagonal():

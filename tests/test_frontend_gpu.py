@@ -40,6 +40,8 @@ def test_every_loop_nest_verifies():
     lengths[:] = [0, 1, 300, 512]
     assert K.paged_gqa_decode.verify(q, kp, vp, bt, lengths) <= 2e-2
     assert not f64(K.paged_gqa_decode(q, kp, vp, bt, lengths)[0]).any()
+    kc, vc = rand_bf16((4, 512, 256), 4), rand_bf16((4, 512, 256), 5)
+    assert K.gqa_decode.verify(rand_bf16((4, 1, 8, 128), 6, 128**-0.5), kc, vc, lengths, K.DecodeTiles(block_kv=128)) <= 2e-2
     assert K.all_gather_matmul.verify(x, y, K.CollectiveTiles()) <= 0.5  # one rank: the gather is the identity
 
 

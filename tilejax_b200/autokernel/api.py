@@ -336,12 +336,15 @@ def _check_kernel_rules(plan: Plan) -> None:
 
 
 def _stages(pipeline: Pipeline, tn: int) -> int:
-    """Ring depth of the GEMM for a Pipeline: 3 or 4 slots for 256-wide CTA tiles, 4 or 6 for 128-wide."""
+    """The GEMM's `stages` argument for a Pipeline. The default depth (3 input buffers) leaves the choice to the
+    library (0): one MMA per pair of SMs with its own ring when the tiles are multiples of 256, else 4 slots.
+    Shallower or deeper pipelines ask for the single-CTA ring explicitly: 3 or 4 slots for 256-wide CTA tiles, 4 or
+    6 for 128-wide."""
     wide = tn % 256 == 0
     if pipeline.input_buffers <= 2:
         return 3 if wide else 4
     if pipeline.input_buffers == 3:
-        return 4
+        return 0
     return 4 if wide else 6
 
 
@@ -368,13 +371,16 @@ def _lower(plan: Plan, config: Config) -> tuple[str, Callable[..., Any]]:
             f"{'.T' if p['transposed'] else ''}, {'causal (tril), ' if p['causal'] else ''}output {np.dtype(p['out_dtype']).name}\n"
             f"user tile   {p['tm']} x {p['tn']} x {p['tk']}: {sch.tiles} of {sch.total_tiles} tiles run, {sch.steps} steps, "
             f"{sch.fills} filled with zeros\n"
-            f"CTA tile    128 x {bn} x 64, ring of {stages} slots, 2 TMEM accumulators, TMA-store epilogue\n"
+            + (f"CTA pair    256 x 256 x 64 pieces, one MMA per pair of SMs (cta_group::2), ring of 3 slots x 2 K blocks, "
+               f"2 TMEM accumulators per SM, TMA-store epilogue\n"
+               if stages == 0 and p["tm"] % 256 == 0 and p["tn"] % 256 == 0 else
+               f"CTA tile    128 x {bn} x 64, ring of {stages or 4} slots, 2 TMEM accumulators, TMA-store epilogue\n") +
             f"tables      {', '.join(f'{k}[{len(v)}]' for k, v in sch.tables.items()) or 'none (arithmetic tile order)'}\n")
         if p["gathered"]:
             from ..collective import AllGatherMatmul
 
             text += f"gather      {p['gathered']} = all_gather({plan.nest.all_gathers[0].source}) over {p['chips']} rank(s): " \
-                    f"NCCL exchange rounds on a second stream, one GEMM launch per shard, own shard first\n"
+                    f"peer shards pulled over NVLink while the own shard's tiles run (collective.AllGatherMatmul), own shard first\n"
             op_holder: dict = {}
 
             def entry(*inputs):
