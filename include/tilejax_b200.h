@@ -124,20 +124,22 @@ int tjx_causal_attention_bf16(const void* q, const void* k, const void* v, void*
                               int pattern_steps, int pattern_tiles, tjx_stream_t stream);
 
 /* Bytes of scratch tjx_paged_gqa_decode_bf16 needs for these sizes. */
-size_t tjx_paged_gqa_decode_workspace_bytes(int B, int H, int D, int pages_per_seq);
+size_t tjx_paged_gqa_decode_workspace_bytes(int B, int T, int H, int D, int pages_per_seq);
 
-/* Ragged paged GQA decode attention, `paged_gqa_decode` (examples/decode.py:199-223) for one new token:
- * builds the step tables on the device from `lengths` (as the generated entry does before its kernel,
+/* Ragged paged GQA decode attention, `paged_gqa_decode` (examples/decode.py:199-223) for T new tokens per
+ * sequence: builds the step tables on the device from `lengths` (as the generated entry does before its kernel,
  * src/autokernel/codegen.py:465-467), then walks only the pages that hold valid positions.
- *   q [B, 1, H, D] bf16 (pre-scaled); k_pages, v_pages [num_pages, page_size, Hkv * D] bf16
+ *   q [B, T, H, D] bf16 (pre-scaled); k_pages, v_pages [num_pages, page_size, Hkv * D] bf16
  *   block_tables int32[B, pages_per_seq] (entries clamped to [0, num_pages - 1], codegen.py:1045-1048)
- *   lengths int32[B] (0 = empty slot: its output is 0); out [B, 1, H, D] bf16
+ *   lengths int32[B], the new tokens included (0 = empty slot: its output is 0); out [B, T, H, D] bf16.
+ *   New token t sits at position lengths[b] - T + t and attends to the positions up to its own (`visible`,
+ *   examples/decode.py:145-152).
  *   step_tile, step_code int32[B * pages_per_seq], step_count int32[1], tile_first int32[B + 1]: OUT, the
  *   tables this call built and walked (bit-exact with the reference's)
  *   workspace: scratch of at least tjx_paged_gqa_decode_workspace_bytes(...) bytes, 256-byte aligned
- * Constraints: D == 128; H / Hkv in {1, 2, 4, 8}; page_size a multiple of 16. */
+ * Constraints: D == 128; H / Hkv in {1, 2, 4, 8}; T * (H / Hkv) <= 16; page_size a multiple of 16. */
 int tjx_paged_gqa_decode_bf16(const void* q, const void* k_pages, const void* v_pages, const int32_t* block_tables,
-                              const int32_t* lengths, void* out, int B, int H, int Hkv, int D, int page_size,
+                              const int32_t* lengths, void* out, int B, int T, int H, int Hkv, int D, int page_size,
                               int pages_per_seq, int num_pages, int32_t* step_tile, int32_t* step_code,
                               int32_t* step_count, int32_t* tile_first, void* workspace, size_t workspace_bytes,
                               tjx_stream_t stream);
@@ -153,7 +155,7 @@ size_t tjx_paged_gqa_decode_static_scratch_bytes(void);
  * tjx_paged_gqa_decode_bf16 minus the workspace: the online-softmax partials go to a fixed 36 MiB array inside the
  * library instead (every GPU that loads the library holds that array until the process exits). The call itself
  * performs no cudaMalloc / cudaFree and calls no allocating routine.
- *   Limit: tjx_paged_gqa_decode_workspace_bytes(B, H, D, pages_per_seq) must not exceed TJX_STATIC_SCRATCH_BYTES
+ *   Limit: tjx_paged_gqa_decode_workspace_bytes(B, T, H, D, pages_per_seq) must not exceed TJX_STATIC_SCRATCH_BYTES
  *   (for example B 64, H 32, 256 pages per sequence fits); beyond it the call returns TJX_E_LIMIT and runs nothing.
  *   First call on a device: looks the array's device address up (once per device, with that device current).
  *   Make that first call outside any stream capture.
@@ -162,8 +164,8 @@ size_t tjx_paged_gqa_decode_static_scratch_bytes(void);
  *   or different host threads on different streams — race on it: keep calls to this entry point on one stream,
  *   or order them with events. */
 int tjx_paged_gqa_decode_bf16_static(const void* q, const void* k_pages, const void* v_pages,
-                                     const int32_t* block_tables, const int32_t* lengths, void* out, int B, int H,
-                                     int Hkv, int D, int page_size, int pages_per_seq, int num_pages,
+                                     const int32_t* block_tables, const int32_t* lengths, void* out, int B, int T,
+                                     int H, int Hkv, int D, int page_size, int pages_per_seq, int num_pages,
                                      int32_t* step_tile, int32_t* step_code, int32_t* step_count, int32_t* tile_first,
                                      tjx_stream_t stream);
 

@@ -1,4 +1,5 @@
-"""Oracle for `paged_gqa_decode`, one new token per sequence (test infrastructure; see oracle/__init__.py)."""
+"""Oracle for `gqa_decode` and `paged_gqa_decode`, T new tokens per sequence (test infrastructure; see
+oracle/__init__.py)."""
 
 from __future__ import annotations
 
@@ -19,6 +20,28 @@ def to_pages(cache, block_tables, num_pages=None):
     return pages
 
 
+def _rows_by_kv_head(qb, kv_heads):
+    """A sequence's queries (T, H, Dh) as (Hkv, T * G, Dh) in f32: KV head k's rows are (token t, its query head g),
+    t-major — the rows `row_index` assigns to group k (examples/decode.py:118-124)."""
+    T, H, Dh = qb.shape
+    G = H // kv_heads
+    return np.asarray(qb).astype(np.float32).reshape(T, kv_heads, G, Dh).transpose(1, 0, 2, 3).reshape(kv_heads, T * G, Dh)
+
+
+def _visible(first, count, length, T, G):
+    """(1, T * G, count): may row (t, g) attend to position first + c? `visible` (examples/decode.py:145-152): new
+    token t sits at position length - T + t and sees the positions up to its own; for T = 1 that is c < length."""
+    cols = first + np.arange(count)
+    tok = np.repeat(np.arange(T), G)
+    return (cols[None, :] <= (length - T + tok)[:, None])[None]
+
+
+def _rows_to_output(res, T, H, kv_heads, dtype):
+    """(Hkv, T * G, Dh) back to (T, H, Dh)."""
+    G = H // kv_heads
+    return res.reshape(kv_heads, T, G, -1).transpose(1, 0, 2, 3).reshape(T, H, -1).astype(dtype)
+
+
 def paged_gqa_decode_ref(q, k_pages, v_pages, block_tables, lengths) -> np.ndarray:
     """examples/decode.py:199-223 with T = 1, page by page in order. Query head h attends with KV head
     h // (H / Hkv) (`row_index`, :118-124; the block-diagonal layout of :127-142 only places each head's query
@@ -27,30 +50,27 @@ def paged_gqa_decode_ref(q, k_pages, v_pages, block_tables, lengths) -> np.ndarr
     >= lengths[b] masked (`visible`, :145-152); `online_softmax` (:155-165) with P rounded to the cache dtype;
     `finish` (:168-172): acc * 1 / max(row_sum, 1e-30), so an empty sequence gives zeros."""
     B, T, H, Dh = q.shape
-    assert T == 1
     num_pages, P, W = k_pages.shape
     Hkv = W // Dh
     G = H // Hkv
     pages = block_tables.shape[1]
     dtype = q.dtype
-    qf = np.asarray(q).astype(np.float32)
     out = np.zeros((B, T, H, Dh), dtype)
     bt = np.asarray(block_tables)
     for b in range(B):
         n = int(lengths[b])
-        qt = qf[b, 0].reshape(Hkv, G, Dh)
-        row_max = np.full((Hkv, G, 1), MASK_VALUE, np.float32)
-        row_sum = np.zeros((Hkv, G, 1), np.float32)
-        acc = np.zeros((Hkv, G, Dh), np.float32)
+        qt = _rows_by_kv_head(q[b], Hkv)
+        row_max = np.full((Hkv, T * G, 1), MASK_VALUE, np.float32)
+        row_sum = np.zeros((Hkv, T * G, 1), np.float32)
+        acc = np.zeros((Hkv, T * G, Dh), np.float32)
         for p in range(pages):
             if p * P >= n:
                 continue
             page = int(np.clip(bt[b, p], 0, num_pages - 1))
             kt = np.asarray(k_pages[page]).astype(np.float32).reshape(P, Hkv, Dh).transpose(1, 0, 2)
             vt = np.asarray(v_pages[page]).reshape(P, Hkv, Dh).transpose(1, 0, 2)
-            s = qt @ kt.transpose(0, 2, 1)  # (Hkv, G, P)
-            ok = (p * P + np.arange(P)) < n
-            s = np.where(ok[None, None, :], s, MASK_VALUE)
+            s = qt @ kt.transpose(0, 2, 1)  # (Hkv, T * G, P)
+            s = np.where(_visible(p * P, P, n, T, G), s, MASK_VALUE)
             max_new = np.maximum(row_max, s.max(axis=2, keepdims=True))
             pr = np.exp(s - max_new)
             alpha = np.exp(row_max - max_new)
@@ -58,7 +78,7 @@ def paged_gqa_decode_ref(q, k_pages, v_pages, block_tables, lengths) -> np.ndarr
             acc = alpha * acc + pr.astype(dtype).astype(np.float32) @ vt.astype(np.float32)
             row_max = max_new
         res = acc * (np.float32(1.0) / np.maximum(row_sum, np.float32(1e-30)))
-        out[b, 0] = res.reshape(H, Dh).astype(dtype)
+        out[b] = _rows_to_output(res, T, H, Hkv, dtype)
     return out
 
 
@@ -68,28 +88,25 @@ def gqa_decode_ref(q, k_cache, v_cache, lengths, block_kv: int = 512) -> np.ndar
     `visible` mask, `online_softmax` and `finish` as the paged nest. Written out on its own (not through the paged
     restatement) so that the two can be checked against each other."""
     B, T, H, Dh = q.shape
-    assert T == 1
     S, W = k_cache.shape[1], k_cache.shape[2]
     Hkv = W // Dh
     G = H // Hkv
     bk = min(block_kv, S)
     dtype = q.dtype
-    qf = np.asarray(q).astype(np.float32)
     out = np.zeros((B, T, H, Dh), dtype)
     for b in range(B):
         n = int(lengths[b])
-        qt = qf[b, 0].reshape(Hkv, G, Dh)
-        row_max = np.full((Hkv, G, 1), MASK_VALUE, np.float32)
-        row_sum = np.zeros((Hkv, G, 1), np.float32)
-        acc = np.zeros((Hkv, G, Dh), np.float32)
+        qt = _rows_by_kv_head(q[b], Hkv)
+        row_max = np.full((Hkv, T * G, 1), MASK_VALUE, np.float32)
+        row_sum = np.zeros((Hkv, T * G, 1), np.float32)
+        acc = np.zeros((Hkv, T * G, Dh), np.float32)
         for j in range(0, S, bk):
             if j >= n:
                 continue
             kt = np.asarray(k_cache[b, j : j + bk]).astype(np.float32).reshape(bk, Hkv, Dh).transpose(1, 0, 2)
             vt = np.asarray(v_cache[b, j : j + bk]).astype(np.float32).reshape(bk, Hkv, Dh).transpose(1, 0, 2)
             s = qt @ kt.transpose(0, 2, 1)
-            ok = (j + np.arange(bk)) < n
-            s = np.where(ok[None, None, :], s, MASK_VALUE)
+            s = np.where(_visible(j, bk, n, T, G), s, MASK_VALUE)
             max_new = np.maximum(row_max, s.max(axis=2, keepdims=True))
             pr = np.exp(s - max_new)
             alpha = np.exp(row_max - max_new)
@@ -97,7 +114,7 @@ def gqa_decode_ref(q, k_cache, v_cache, lengths, block_kv: int = 512) -> np.ndar
             acc = alpha * acc + pr.astype(dtype).astype(np.float32) @ vt
             row_max = max_new
         res = acc * (np.float32(1.0) / np.maximum(row_sum, np.float32(1e-30)))
-        out[b, 0] = res.reshape(H, Dh).astype(dtype)
+        out[b] = _rows_to_output(res, T, H, Hkv, dtype)
     return out
 
 
@@ -115,11 +132,15 @@ def paged_gqa_decode_f64(q, k_pages, v_pages, block_tables, lengths) -> np.ndarr
         if n == 0:
             continue
         used = bt[b, : -(-n // P)]
-        kk = np.asarray(k_pages[used]).astype(np.float64).reshape(-1, Hkv, Dh)[:n]
-        vv = np.asarray(v_pages[used]).astype(np.float64).reshape(-1, Hkv, Dh)[:n]
-        qq = np.asarray(q[b, 0]).astype(np.float64).reshape(Hkv, G, Dh)
-        s = np.einsum("kgd,nkd->kgn", qq, kk)
-        p = np.exp(s - s.max(axis=-1, keepdims=True))
-        p /= p.sum(axis=-1, keepdims=True)
-        out[b, 0] = np.einsum("kgn,nkd->kgd", p, vv).reshape(H, Dh)
+        kk = np.asarray(k_pages[used]).astype(np.float64).reshape(-1, Hkv, Dh)
+        vv = np.asarray(v_pages[used]).astype(np.float64).reshape(-1, Hkv, Dh)
+        for t in range(T):
+            seen = n - T + t + 1  # new token t sits at position n - T + t and sees the positions up to its own
+            if seen <= 0:
+                continue
+            qq = np.asarray(q[b, t]).astype(np.float64).reshape(Hkv, G, Dh)
+            s = np.einsum("kgd,nkd->kgn", qq, kk[:seen])
+            p = np.exp(s - s.max(axis=-1, keepdims=True))
+            p /= p.sum(axis=-1, keepdims=True)
+            out[b, t] = np.einsum("kgn,nkd->kgd", p, vv[:seen]).reshape(H, Dh)
     return out

@@ -91,6 +91,36 @@ def test_contiguous_cache_is_the_identity_block_table(block):
     np.testing.assert_array_equal(f64(got), f64(paged))
 
 
+@pytest.mark.parametrize(("heads", "kv_heads", "new_tokens", "page"), [(8, 2, 2, 64), (8, 2, 4, 16), (4, 4, 3, 32),
+                                                                       (16, 2, 2, 16), (8, 8, 16, 128)])
+def test_several_new_tokens_per_sequence(heads, kv_heads, new_tokens, page):
+    # tests/test_decode.py:215-220 (64-token pages, T = 2) and wider: new token t sits at position length - T + t
+    # and sees the positions up to its own. Up to 8 query rows per KV head use half of the MMA's rows, up to 16 all.
+    B, S, T = 4, 512, new_tokens
+    k, v = rand_bf16((B, S, kv_heads * 128), 1), rand_bf16((B, S, kv_heads * 128), 2)
+    q = rand_bf16((B, T, heads, 128), 3, 128**-0.5)
+    lengths = np.array([0, T, 300, 512], np.int32)
+    order = np.random.default_rng(1).permutation(B * S // page).reshape(B, S // page).astype(np.int32)
+    kp, vp = oracle.to_pages(k, order), oracle.to_pages(v, order)
+    got = run_decode(q, kp, vp, order, lengths)
+    want = oracle.paged_gqa_decode_ref(q, kp, vp, order, lengths)
+    assert np.abs(f64(got) - f64(want)).max() <= 2e-2 * np.abs(f64(want)).max()
+    exact = oracle.paged_gqa_decode_f64(q, kp, vp, order, lengths)
+    assert np.abs(f64(got) - exact).max() <= 2e-2 * np.abs(exact).max()
+    assert not f64(got[0]).any()
+    # Each new token alone, as a one-token call on the prefix it sees, agrees to rounding.
+    for t in range(T):
+        alone = run_decode(np.ascontiguousarray(q[:, t : t + 1]), kp, vp, order, np.maximum(lengths - (T - 1 - t), 0))
+        assert np.abs(f64(got[1:, t]) - f64(alone[1:, 0])).max() <= 2e-2 * np.abs(exact).max()
+
+
+def test_too_many_query_rows_per_kv_head_is_an_error():
+    q, kp, vp, bt, lengths = synthetic.decode_inputs(2, 8, 2, 128, 16, 4, 8)
+    q5 = np.repeat(q, 5, axis=1)
+    with pytest.raises(NativeError, match="must not exceed 16"):
+        run_decode(q5, kp, vp, bt, lengths)
+
+
 def test_all_sequences_empty():
     q, kp, vp, bt, lengths = synthetic.decode_inputs(5, 8, 2, 128, 16, 4, 20)
     lengths[:] = 0

@@ -166,6 +166,25 @@ def test_paged_oracle_equals_contiguous_layout():
     assert np.abs(f64(oracle.gqa_decode_ref(q, k, v, lengths)) - want).max() <= 2e-2 * np.abs(want).max()
 
 
+def test_several_new_tokens_see_only_positions_up_to_their_own():
+    # tests/test_decode.py:215-220 (64-token pages, T = 2) and `visible` (examples/decode.py:145-152): new token t
+    # sits at position length - T + t. Against float64, and row by row against the single-token call on the
+    # prefix that row sees.
+    B, S, P, T = 3, 256, 64, 2
+    k, v = rand_bf16((B, S, 256), 1), rand_bf16((B, S, 256), 2)
+    q = rand_bf16((B, T, 8, 128), 3, 128**-0.5)
+    lengths = np.array([2, 100, 256], np.int32)
+    ident = np.arange(B * S // P, dtype=np.int32).reshape(B, S // P)
+    kp, vp = oracle.to_pages(k, ident), oracle.to_pages(v, ident)
+    got = oracle.paged_gqa_decode_ref(q, kp, vp, ident, lengths)
+    want = oracle.paged_gqa_decode_f64(q, kp, vp, ident, lengths)
+    assert np.abs(f64(got) - want).max() <= 2e-2 * np.abs(want).max()
+    np.testing.assert_array_equal(f64(oracle.gqa_decode_ref(q, k, v, lengths, P)), f64(got))
+    for t in range(T):
+        alone = oracle.paged_gqa_decode_ref(q[:, t : t + 1], kp, vp, ident, lengths - (T - 1 - t))
+        np.testing.assert_array_equal(f64(got[:, t]), f64(alone[:, 0]))
+
+
 def test_compare_rule():
     # src/autokernel/api.py:320-364 and tests/test_api.py:87-108: NaN equals NaN; 16-bit tolerance scales with
     # the largest value; integers are exact.

@@ -61,7 +61,7 @@ def test_sizes_beyond_the_built_in_scratch_are_refused():
     limit = int(library().tjx_paged_gqa_decode_static_scratch_bytes())
     assert limit == 36 * 1024 * 1024
     B, H, pages = 256, 32, 256  # four times the benchmark's batch: needs about 70 MB
-    assert int(library().tjx_paged_gqa_decode_workspace_bytes(B, H, 128, pages)) > limit
+    assert int(library().tjx_paged_gqa_decode_workspace_bytes(B, 1, H, 128, pages)) > limit
     q = torch.zeros(B, 1, H, 128, dtype=torch.bfloat16, device="cuda")
     kp = torch.zeros(16, 16, 8 * 128, dtype=torch.bfloat16, device="cuda")
     bt = torch.zeros(B, pages, dtype=torch.int32, device="cuda")

@@ -333,6 +333,9 @@ def _check_kernel_rules(plan: Plan) -> None:
         if p["D"] != 128 or p["page"] % 16 or p["H"] % p["Hkv"] or p["H"] // p["Hkv"] not in (1, 2, 4, 8):
             raise nest.error("the decode kernel takes head_dim 128, pages of a multiple of 16 positions and 1, 2, 4 "
                              "or 8 query heads per KV head")
+        if p["T"] * (p["H"] // p["Hkv"]) > 16:
+            raise nest.error(f"{p['T']} new tokens x {p['H'] // p['Hkv']} query heads per KV head: the decode kernel "
+                             "holds at most 16 query rows per KV head (the rows of one warp-level MMA)")
 
 
 def _stages(pipeline: Pipeline, tn: int) -> int:
@@ -412,7 +415,7 @@ def _lower(plan: Plan, config: Config) -> tuple[str, Callable[..., Any]]:
     text = header + (
         f"kernel      tjx_paged_gqa_decode_bf16 (device step tables, per-warp TMA rings, warp-level MMA, partials "
         f"merged by the last warp to arrive)\n"
-        f"problem     {p['B']} sequences, {p['H']} / {p['Hkv']} heads, head_dim {p['D']}, pages of {p['page']}, "
+        f"problem     {p['B']} sequences, {p['T']} new token(s), {p['H']} / {p['Hkv']} heads, head_dim {p['D']}, pages of {p['page']}, "
         f"{p['pages']} pages per sequence, pool of {p['num_pages']}"
         f"{' (a contiguous cache: the identity block table)' if p.get('contiguous') else ''}\n"
         f"steps       at most {sch.steps}: step_tile / step_code / step_count are built on the device from lengths "

@@ -114,9 +114,10 @@ def causal_attention(q, k, v, blocks=AttentionBlocks()):
 
 
 def queries_by_kv_head(qt, kv_heads):
-    """A sequence's queries (1, H, Dh) as (Hkv, G, Dh): head h attends with KV head h // G."""
-    _, h, d = qt.shape
-    return qt.reshape(kv_heads, h // kv_heads, d)
+    """A sequence's queries (T, H, Dh) as (Hkv, T * G, Dh): head h attends with KV head h // G, and a KV head's
+    rows are its (new token, query head) pairs, token-major."""
+    t, h, d = qt.shape
+    return qt.reshape(t, kv_heads, h // kv_heads, d).transpose(1, 0, 2, 3).reshape(kv_heads, t * (h // kv_heads), d)
 
 
 def page_by_kv_head(page, kv_heads):
@@ -125,10 +126,13 @@ def page_by_kv_head(page, kv_heads):
     return page.reshape(p, kv_heads, w // kv_heads).transpose(1, 0, 2)
 
 
-def visible(page_size, first, length):
-    """Which positions of a page starting at `first` are before the sequence's end: (1, 1, P)."""
-    cols = first + jax.lax.broadcasted_iota(jnp.int32, (1, 1, page_size), 2)
-    return cols < length
+def visible(page_size, first, length, new_tokens, group):
+    """Which (query row, position) pairs of a page starting at `first` attend: (1, T * G, P). New token t sits at
+    position length - T + t and sees the positions up to its own; for one new token that is `cols < length`."""
+    rows = new_tokens * group
+    cols = first + jax.lax.broadcasted_iota(jnp.int32, (1, rows, page_size), 2)
+    token = jax.lax.broadcasted_iota(jnp.int32, (1, rows, page_size), 1) // group
+    return cols <= length - new_tokens + token
 
 
 def online_softmax(s, v, ok, row_max, row_sum, acc):
@@ -143,15 +147,18 @@ def online_softmax(s, v, ok, row_max, row_sum, acc):
 
 
 def finish(acc, row_sum, shape, dtype):
-    """The normalised output as `shape`; rows that saw no key (an empty sequence) are 0."""
+    """The normalised output (Hkv, T * G, Dh) as `shape` (T, H, Dh); rows that saw no key (an empty sequence)
+    are 0."""
+    t, h, d = shape
     out = acc * (1.0 / jnp.maximum(row_sum, 1e-30))
-    return out.reshape(shape).astype(dtype)
+    kv_heads = out.shape[0]
+    return out.reshape(kv_heads, t, h // kv_heads, d).transpose(1, 0, 2, 3).reshape(shape).astype(dtype)
 
 
 @autokernel.kernel
 def gqa_decode(q, k_cache, v_cache, lengths, tiles=DecodeTiles()):
-    """GQA decode attention over a contiguous cache: q (B, 1, H, Dh), caches (B, S_max, Hkv * Dh), sequence b's
-    valid positions lengths[b]."""
+    """GQA decode attention over a contiguous cache: q (B, T, H, Dh), caches (B, S_max, Hkv * Dh), sequence b's
+    valid positions lengths[b], its T new tokens included."""
     B, T, H, Dh = q.shape
     S, W = k_cache.shape[1], k_cache.shape[2]
     Hkv = W // Dh
@@ -159,15 +166,15 @@ def gqa_decode(q, k_cache, v_cache, lengths, tiles=DecodeTiles()):
     out = jnp.zeros((B, T, H, Dh), dtype)
     for b in range(B):
         qt = queries_by_kv_head(q[b, :, :, :], Hkv)
-        row_max = jnp.full((Hkv, H // Hkv, 1), MASK_VALUE, jnp.float32)
-        row_sum = jnp.zeros((Hkv, H // Hkv, 1), jnp.float32)
-        acc = jnp.zeros((Hkv, H // Hkv, Dh), jnp.float32)
+        row_max = jnp.full((Hkv, T * (H // Hkv), 1), MASK_VALUE, jnp.float32)
+        row_sum = jnp.zeros((Hkv, T * (H // Hkv), 1), jnp.float32)
+        acc = jnp.zeros((Hkv, T * (H // Hkv), Dh), jnp.float32)
         for j in range(0, S, bk):
             if j >= lengths[b]:  # past the sequence's end: decided on the device, before the kernel runs
                 continue
             kt = page_by_kv_head(k_cache[b, j : j + bk, :], Hkv)
             s = jnp.dot(qt, kt.transpose(0, 2, 1), preferred_element_type=jnp.float32)
-            ok = visible(bk, j, lengths[b])
+            ok = visible(bk, j, lengths[b], T, H // Hkv)
             vt = page_by_kv_head(v_cache[b, j : j + bk, :], Hkv)
             row_max, row_sum, acc = online_softmax(s, vt, ok, row_max, row_sum, acc)
         out = out.at[b, :, :, :].set(finish(acc, row_sum, (T, H, Dh), dtype))
@@ -176,8 +183,8 @@ def gqa_decode(q, k_cache, v_cache, lengths, tiles=DecodeTiles()):
 
 @autokernel.kernel
 def paged_gqa_decode(q, k_pages, v_pages, block_tables, lengths):
-    """GQA decode attention over a paged cache: q (B, 1, H, Dh), pages (num_pages, page_size, Hkv * Dh), sequence
-    b's pages listed in block_tables[b, :], its valid positions lengths[b]."""
+    """GQA decode attention over a paged cache: q (B, T, H, Dh), pages (num_pages, page_size, Hkv * Dh), sequence
+    b's pages listed in block_tables[b, :], its valid positions lengths[b], its T new tokens included."""
     B, T, H, Dh = q.shape
     P, W = k_pages.shape[1], k_pages.shape[2]
     pages = block_tables.shape[1]
@@ -186,15 +193,15 @@ def paged_gqa_decode(q, k_pages, v_pages, block_tables, lengths):
     out = jnp.zeros((B, T, H, Dh), dtype)
     for b in range(B):
         qt = queries_by_kv_head(q[b, :, :, :], Hkv)
-        row_max = jnp.full((Hkv, H // Hkv, 1), MASK_VALUE, jnp.float32)
-        row_sum = jnp.zeros((Hkv, H // Hkv, 1), jnp.float32)
-        acc = jnp.zeros((Hkv, H // Hkv, Dh), jnp.float32)
+        row_max = jnp.full((Hkv, T * (H // Hkv), 1), MASK_VALUE, jnp.float32)
+        row_sum = jnp.zeros((Hkv, T * (H // Hkv), 1), jnp.float32)
+        acc = jnp.zeros((Hkv, T * (H // Hkv), Dh), jnp.float32)
         for p in range(pages):
             if p * P >= lengths[b]:  # past the sequence's end: decided on the device, before the kernel runs
                 continue
             kt = page_by_kv_head(k_pages[block_tables[b, p], :, :], Hkv)
             s = jnp.dot(qt, kt.transpose(0, 2, 1), preferred_element_type=jnp.float32)
-            ok = visible(P, p * P, lengths[b])
+            ok = visible(P, p * P, lengths[b], T, H // Hkv)
             vt = page_by_kv_head(v_pages[block_tables[b, p], :, :], Hkv)
             row_max, row_sum, acc = online_softmax(s, vt, ok, row_max, row_sum, acc)
         out = out.at[b, :, :, :].set(finish(acc, row_sum, (T, H, Dh), dtype))

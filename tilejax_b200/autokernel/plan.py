@@ -330,8 +330,6 @@ def _recognise_contiguous_decode(nest, ns, specs, outputs, parallel, reductions)
         raise _unsupported(nest, "decode takes q (B, T, H, D), caches (B, S, Hkv * D) and lengths (B,)")
     B, T, H, D = q.shape
     _, S, W = kc.shape
-    if T != 1:
-        raise _unsupported(nest, "several new tokens per sequence (T > 1)")
     code = compile(ast.Expression(mask), nest.filename, "eval")
 
     def skipped(jv: int, length: int) -> bool:
@@ -343,7 +341,7 @@ def _recognise_contiguous_decode(nest, ns, specs, outputs, parallel, reductions)
         raise _unsupported(nest, "the block loop must cover the cache and skip blocks with `j >= lengths[b]`",
                            nest.reductions[0].node)
     sch = _schedule.paged_decode_schedule(B, j.count)
-    params = dict(B=B, H=H, Hkv=W // D, D=D, page=block, pages=j.count, num_pages=B * j.count, schedule=sch,
+    params = dict(B=B, T=T, H=H, Hkv=W // D, D=D, page=block, pages=j.count, num_pages=B * j.count, schedule=sch,
                   contiguous=True)
     return Plan(nest, "decode", specs, outputs, parallel, reductions, params, runtime=True)
 
@@ -366,8 +364,6 @@ def _recognise_decode(nest, ns, specs, outputs, parallel, reductions) -> Plan:
                                  "(B, pages) and lengths (B,)")
     B, T, H, D = q.shape
     num_pages, page, W = kp.shape
-    if T != 1:
-        raise _unsupported(nest, "several new tokens per sequence (T > 1)")
     # The mask must be `p * page >= lengths[b]`: check it on the extremes with a stand-in for lengths.
     probe_ns = dict(ns)
     code = compile(ast.Expression(mask), nest.filename, "eval")
@@ -379,5 +375,5 @@ def _recognise_decode(nest, ns, specs, outputs, parallel, reductions) -> Plan:
     if not ok or (b.count, p.count) != (B, bt.shape[1]) or p.step != 1 or p.start != 0:
         raise _unsupported(nest, "the page loop must skip pages with `p * page_size >= lengths[b]`", nest.reductions[0].node)
     sch = _schedule.paged_decode_schedule(B, p.count)
-    params = dict(B=B, H=H, Hkv=W // D, D=D, page=page, pages=p.count, num_pages=num_pages, schedule=sch)
+    params = dict(B=B, T=T, H=H, Hkv=W // D, D=D, page=page, pages=p.count, num_pages=num_pages, schedule=sch)
     return Plan(nest, "decode", specs, outputs, parallel, reductions, params, runtime=True)

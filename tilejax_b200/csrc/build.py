@@ -65,8 +65,11 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if failed:
         raise RuntimeError("nvcc failed:\n" + "\n".join(failed))
     if force or jobs or _stale(LIBRARY, objects):
-        cmd = [nvcc(), *ARCH_FLAGS, "-shared", "-Xcompiler", "-fPIC", "-o", str(LIBRARY), *map(str, objects)]
+        # Link beside the target and rename over it: a reader never sees a half-written library.
+        fresh = LIBRARY.with_suffix(".so.new")
+        cmd = [nvcc(), *ARCH_FLAGS, "-shared", "-Xcompiler", "-fPIC", "-o", str(fresh), *map(str, objects)]
         subprocess.run(cmd, check=True)
+        os.replace(fresh, LIBRARY)
     return LIBRARY
 
 

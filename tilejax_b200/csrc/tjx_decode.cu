@@ -39,7 +39,7 @@ constexpr float DEC_MASK = -1e30f;
 constexpr int DEC_SMEM = DEC_WARPS * DEC_STAGES * DEC_STAGE_BYTES + 1024;  // + slack to align the ring to 1024
 
 struct DecodeParams {
-  const __nv_bfloat16* q;        // [B, 1, H, D]
+  const __nv_bfloat16* q;        // [B, T, H, D]
   const __nv_bfloat16* k_pages;  // [num_pages, PAGE, Hkv * D]
   const __nv_bfloat16* v_pages;
   const int32_t* block_tables;   // [B, pages_per_seq]
@@ -48,12 +48,13 @@ struct DecodeParams {
   const int32_t* step_code;
   const int32_t* step_count;
   const int32_t* tile_first;     // [B + 1]
-  float* ws_m;                   // [B, slots, H]
-  float* ws_l;                   // [B, slots, H]
-  float* ws_acc;                 // [B, slots, H, D]
+  float* ws_m;                   // [B, slots, rows]
+  float* ws_l;                   // [B, slots, rows]
+  float* ws_acc;                 // [B, slots, rows, D]
   int* arrivals;                 // [B, Hkv] pieces of a sequence's KV head that have written their partial
-  __nv_bfloat16* out;            // [B, 1, H, D]
+  __nv_bfloat16* out;            // [B, T, H, D]
   int B, H, Hkv, page_size, pages_per_seq, num_pages, slots;
+  int T, rows;                   // new tokens per sequence; query rows per sequence = T * H (row t * H + h)
   int* status;
 };
 
@@ -79,14 +80,15 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                : "r"(addr));
 }
-// D (16 x 8, f32) += A (16 x 16, bf16, rows) * B (16 x 8, bf16, columns). Rows 8..15 of A are always zero here
-// (a1 = a3 = 0): the rows are the G <= 8 query heads of one KV head.
-__device__ __forceinline__ void mma_16x8x16(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+// D (16 x 8, f32) += A (16 x 16, bf16, rows) * B (16 x 8, bf16, columns). The rows are the query rows of one KV
+// head: (new token, query head) pairs, at most 16; a1 and a3 (rows 8..15) are zero when there are at most 8.
+__device__ __forceinline__ void mma_16x8x16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                            uint32_t b0, uint32_t b1) {
   asm volatile(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
       "{%0, %1, %2, %3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 // Merge the partials of the G query heads h0 .. h0 + G - 1 of sequence b (n partials each, in slots 0..n-1),
@@ -95,7 +97,7 @@ __device__ __forceinline__ void mma_16x8x16(float (&d)[4], uint32_t a0, uint32_t
 // are read past L1.
 template <int G>
 __device__ __forceinline__ void decode_merge_heads(const DecodeParams& p, int b, int h0, int n, int lane) {
-  const size_t base = static_cast<size_t>(b) * p.slots * p.H + h0;
+  const size_t base = static_cast<size_t>(b) * p.slots * p.rows + h0;
   float mx[G], lsum[G];
   float4 o[G];
 #pragma unroll
@@ -105,7 +107,7 @@ __device__ __forceinline__ void decode_merge_heads(const DecodeParams& p, int b,
     if (i0 + lane < n) {
 #pragma unroll
       for (int h = 0; h < G; ++h)
-        mx[h] = fmaxf(mx[h], __ldcg(p.ws_m + base + static_cast<size_t>(i0 + lane) * p.H + h));
+        mx[h] = fmaxf(mx[h], __ldcg(p.ws_m + base + static_cast<size_t>(i0 + lane) * p.rows + h));
     }
 #pragma unroll
   for (int h = 0; h < G; ++h)
@@ -116,7 +118,7 @@ __device__ __forceinline__ void decode_merge_heads(const DecodeParams& p, int b,
 #pragma unroll
     for (int h = 0; h < G; ++h) w_mine[h] = 0.f;
     if (i0 + lane < n) {
-      const size_t idx = base + static_cast<size_t>(i0 + lane) * p.H;
+      const size_t idx = base + static_cast<size_t>(i0 + lane) * p.rows;
 #pragma unroll
       for (int h = 0; h < G; ++h) {
         w_mine[h] = __expf(__ldcg(p.ws_m + idx + h) - mx[h]);
@@ -126,7 +128,7 @@ __device__ __forceinline__ void decode_merge_heads(const DecodeParams& p, int b,
     const int cnt = min(32, n - i0);
 #pragma unroll 4
     for (int i = 0; i < cnt; ++i) {
-      const size_t idx = base + static_cast<size_t>(i0 + i) * p.H;
+      const size_t idx = base + static_cast<size_t>(i0 + i) * p.rows;
 #pragma unroll
       for (int h = 0; h < G; ++h) {
         const float w = __shfl_sync(0xFFFFFFFFu, w_mine[h], i);
@@ -144,7 +146,7 @@ __device__ __forceinline__ void decode_merge_heads(const DecodeParams& p, int b,
     uint2 r;
     r.x = pack_bf16(o[h].x * inv, o[h].y * inv);
     r.y = pack_bf16(o[h].z * inv, o[h].w * inv);
-    *reinterpret_cast<uint2*>(p.out + (static_cast<size_t>(b) * p.H + h0 + h) * DEC_D + lane * 4) = r;
+    *reinterpret_cast<uint2*>(p.out + (static_cast<size_t>(b) * p.rows + h0 + h) * DEC_D + lane * 4) = r;
   }
 }
 
@@ -162,8 +164,8 @@ __device__ __forceinline__ void decode_merge_heads(const DecodeParams& p, int b,
 // fragments from the V slot with ldmatrix.trans. Lane (g, t) = (lane / 4, lane % 4) holds of head g: scores of
 // tokens 2t, 2t+1, 8+2t, 9+2t and output dims 8 n + 2t, + 1 for n = 0..15. A fifth-generation (tcgen05) MMA needs
 // 64 or 128 rows; with at most 8 query heads per KV head this path stays bound by HBM with the warp-level MMA.
-template <int G>
-__global__ void __launch_bounds__(DEC_WARPS * 32, 6)
+template <int G, bool WIDE>
+__global__ void __launch_bounds__(DEC_WARPS * 32, WIDE ? 4 : 6)
     decode_chunks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                          const DecodeParams p) {
   extern __shared__ uint8_t dec_smem_raw[];
@@ -185,8 +187,21 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 6)
   __syncthreads();
   if (kvh >= p.Hkv) return;
 
-  const int g = lane >> 2;  // the query head (row) this lane holds
+  // Query rows of this KV head: row r = (new token r / G, query head r % G of the group), R = T * G of them. A
+  // lane holds row g = lane / 4 and, when there are more than 8 rows (WIDE), row g + 8 as well.
+  constexpr int NR = WIDE ? 2 : 1;
+  const int g = lane >> 2;
   const int t = lane & 3;
+  const int R = p.T * G;
+  bool row_ok[NR];
+  int row_tok[NR], row_head[NR];  // the row's new token, and its index t * H + h among the sequence's query rows
+#pragma unroll
+  for (int x = 0; x < NR; ++x) {
+    const int r = g + 8 * x;
+    row_ok[x] = r < R;
+    row_tok[x] = r / G;
+    row_head[x] = row_tok[x] * p.H + kvh * G + r % G;
+  }
   const uint32_t ring = ((smem_u32(dec_smem_raw) + 1023u) & ~1023u) + warp * (DEC_STAGES * DEC_STAGE_BYTES);
   auto bar = [&](int stage) { return smem_u32(&dec_bars[warp * DEC_STAGES + stage]); };
   // ldmatrix addressing. A box is [16 tokens][128 bytes], its 16-byte units XOR-swizzled with token % 8.
@@ -219,9 +234,11 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 6)
     }
   }
 
-  uint32_t qa[8][2];   // A fragments of Q: k-step j covers dims 16 j .. 16 j + 15; [0] = dims + 2t, [1] = dims + 8 + 2t
-  float o[16][4];      // O fragments: [n][0..1] = head g, dims 8 n + 2t, + 1 ([2..3] belong to the zero rows)
-  float m_run = DEC_MASK * DEC_LOG2E, l_run = 0.f;  // head g's running max (log2 units) and this lane's part of its sum
+  uint32_t qa[8][2 * NR];  // A fragments of Q: k-step j = dims 16 j .. + 15; row x: [2x] = dims + 2t, + 1, [2x + 1] = + 8
+  float o[16][4];          // O fragments: [n][0..1] = row g, dims 8 n + 2t, + 1; [2..3] = row g + 8 (zero rows unless WIDE)
+  float m_run[NR], l_run[NR];  // each row's running max (log2 units) and this lane's part of its sum
+#pragma unroll
+  for (int x = 0; x < NR; ++x) m_run[x] = DEC_MASK * DEC_LOG2E, l_run[x] = 0.f;
   int cur = -1;
 
   auto flush = [&]() {
@@ -229,25 +246,27 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 6)
     const int first = p.tile_first[cur], next = p.tile_first[cur + 1];
     const int pieces = (next - 1) / DEC_CHUNK - first / DEC_CHUNK + 1;  // a tile takes at least one step
     const int slot = chunk - first / DEC_CHUNK;
-    const size_t base = (static_cast<size_t>(cur) * p.slots + slot) * p.H + kvh * G;
-    float l_all = l_run;
-    l_all += __shfl_xor_sync(0xFFFFFFFFu, l_all, 1);
-    l_all += __shfl_xor_sync(0xFFFFFFFFu, l_all, 2);
-    if (g < G) {
+    const size_t base = (static_cast<size_t>(cur) * p.slots + slot) * p.rows;
+#pragma unroll
+    for (int x = 0; x < NR; ++x) {
+      float l_all = l_run[x];
+      l_all += __shfl_xor_sync(0xFFFFFFFFu, l_all, 1);
+      l_all += __shfl_xor_sync(0xFFFFFFFFu, l_all, 2);
+      if (!row_ok[x]) continue;
       if (pieces == 1) {
         // The sequence's only piece: its partial is the result.
         const float inv = 1.0f / fmaxf(l_all, 1e-30f);
-        uint32_t* dst = reinterpret_cast<uint32_t*>(p.out + (static_cast<size_t>(cur) * p.H + kvh * G + g) * DEC_D);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(p.out + (static_cast<size_t>(cur) * p.rows + row_head[x]) * DEC_D);
 #pragma unroll
-        for (int nt = 0; nt < 16; ++nt) dst[nt * 4 + t] = pack_bf16(o[nt][0] * inv, o[nt][1] * inv);
+        for (int nt = 0; nt < 16; ++nt) dst[nt * 4 + t] = pack_bf16(o[nt][2 * x] * inv, o[nt][2 * x + 1] * inv);
       } else {
         if (t == 0) {  // the partials keep the max in natural-log units
-          p.ws_m[base + g] = m_run * (1.0f / DEC_LOG2E);
-          p.ws_l[base + g] = l_all;
+          p.ws_m[base + row_head[x]] = m_run[x] * (1.0f / DEC_LOG2E);
+          p.ws_l[base + row_head[x]] = l_all;
         }
-        float2* dst = reinterpret_cast<float2*>(p.ws_acc + (base + g) * DEC_D);
+        float2* dst = reinterpret_cast<float2*>(p.ws_acc + (base + row_head[x]) * DEC_D);
 #pragma unroll
-        for (int nt = 0; nt < 16; ++nt) dst[nt * 4 + t] = make_float2(o[nt][0], o[nt][1]);
+        for (int nt = 0; nt < 16; ++nt) dst[nt * 4 + t] = make_float2(o[nt][2 * x], o[nt][2 * x + 1]);
       }
     }
     if (pieces > 1) {
@@ -259,7 +278,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 6)
       last = __shfl_sync(0xFFFFFFFFu, last, 0);
       if (last) {
         __threadfence();
-        decode_merge_heads<G>(p, cur, kvh * G, pieces, lane);
+        for (int tok = 0; tok < p.T; ++tok) decode_merge_heads<G>(p, cur, tok * p.H + kvh * G, pieces, lane);
       }
     }
   };
@@ -312,16 +331,19 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 6)
     if (tile != cur) {
       flush();
       cur = tile;
-      const uint32_t* qp =
-          reinterpret_cast<const uint32_t*>(p.q + (static_cast<size_t>(tile) * p.H + kvh * G + (g < G ? g : 0)) * DEC_D);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        qa[j][0] = g < G ? qp[8 * j + t] : 0u;
-        qa[j][1] = g < G ? qp[8 * j + 4 + t] : 0u;
+      for (int x = 0; x < NR; ++x) {
+        const uint32_t* qp = reinterpret_cast<const uint32_t*>(
+            p.q + (static_cast<size_t>(tile) * p.rows + (row_ok[x] ? row_head[x] : 0)) * DEC_D);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          qa[j][2 * x] = row_ok[x] ? qp[8 * j + t] : 0u;
+          qa[j][2 * x + 1] = row_ok[x] ? qp[8 * j + 4 + t] : 0u;
+        }
+        m_run[x] = DEC_MASK * DEC_LOG2E, l_run[x] = 0.f;
       }
 #pragma unroll
       for (int nt = 0; nt < 16; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
-      m_run = DEC_MASK * DEC_LOG2E, l_run = 0.f;
     }
     if (code & 4) continue;  // an empty step: no position to read
     const int pg = code >> 3;
@@ -343,7 +365,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 6)
       const uint32_t kbase = ring + stage * DEC_STAGE_BYTES;
       const uint32_t vbase = kbase + 2 * DEC_HALF_BYTES;
 
-      // S = Q K^T: two tiles of 8 tokens; [tile][0..1] = head g, tokens 8 tile + 2t, + 1.
+      // S = Q K^T: two tiles of 8 tokens; [tile][0..1] = row g, tokens 8 tile + 2t, + 1; [2..3] = row g + 8.
       float sc[2][4];
 #pragma unroll
       for (int tl = 0; tl < 2; ++tl) {
@@ -354,30 +376,46 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 6)
           const uint32_t addr = kbase + (x >> 1) * DEC_HALF_BYTES + tl * 1024 + k_lane + ((unit ^ lrow) << 4);
           uint32_t b[4];
           ldmatrix_x4(addr, b);
-          mma_16x8x16(sc[tl], qa[2 * x][0], qa[2 * x][1], b[0], b[1]);
-          mma_16x8x16(sc[tl], qa[2 * x + 1][0], qa[2 * x + 1][1], b[2], b[3]);
+          if constexpr (WIDE) {
+            mma_16x8x16(sc[tl], qa[2 * x][0], qa[2 * x][2], qa[2 * x][1], qa[2 * x][3], b[0], b[1]);
+            mma_16x8x16(sc[tl], qa[2 * x + 1][0], qa[2 * x + 1][2], qa[2 * x + 1][1], qa[2 * x + 1][3], b[2], b[3]);
+          } else {
+            mma_16x8x16(sc[tl], qa[2 * x][0], 0u, qa[2 * x][1], 0u, b[0], b[1]);
+            mma_16x8x16(sc[tl], qa[2 * x + 1][0], 0u, qa[2 * x + 1][1], 0u, b[2], b[3]);
+          }
         }
       }
-      // Online softmax of head g over the 16 tokens (4 per lane, the 4 lanes of a quad share the head).
-      float s4[4] = {sc[0][0], sc[0][1], sc[1][0], sc[1][1]};
+      // Online softmax of each row over the 16 tokens (4 per lane, the 4 lanes of a quad share a row). Row r's
+      // new token sits at position len - T + token(r) and sees the positions up to its own.
+      uint32_t pa[4] = {0u, 0u, 0u, 0u};  // P as the A fragment: [0] row g tokens 2t.., [1] row g + 8, [2], [3] tokens 8 + 2t..
+      bool grew = false;
+      float alpha[NR];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int tok = (i >> 1) * 8 + 2 * t + (i & 1);
-        s4[i] = base_pos + tok < len ? s4[i] * DEC_LOG2E : DEC_MASK * DEC_LOG2E;
+      for (int x = 0; x < NR; ++x) {
+        float s4[4] = {sc[0][2 * x], sc[0][2 * x + 1], sc[1][2 * x], sc[1][2 * x + 1]};
+        const int last_visible = len - p.T + row_tok[x];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int tok = (i >> 1) * 8 + 2 * t + (i & 1);
+          s4[i] = base_pos + tok <= last_visible ? s4[i] * DEC_LOG2E : DEC_MASK * DEC_LOG2E;
+        }
+        float mx = fmaxf(fmaxf(s4[0], s4[1]), fmaxf(s4[2], s4[3]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
+        const float m_new = fmaxf(m_run[x], mx);
+        alpha[x] = ex2(m_run[x] - m_new);
+        grew |= m_new > m_run[x];
+        m_run[x] = m_new;
+        const float p0 = ex2(s4[0] - m_new), p1 = ex2(s4[1] - m_new), p2 = ex2(s4[2] - m_new), p3 = ex2(s4[3] - m_new);
+        l_run[x] = l_run[x] * alpha[x] + ((p0 + p1) + (p2 + p3));
+        pa[x] = pack_bf16(p0, p1), pa[2 + x] = pack_bf16(p2, p3);  // P is rounded before P V
       }
-      float mx = fmaxf(fmaxf(s4[0], s4[1]), fmaxf(s4[2], s4[3]));
-      mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
-      mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
-      const float m_new = fmaxf(m_run, mx);
-      const float alpha = ex2(m_run - m_new);
-      const bool grew = m_new > m_run;
-      m_run = m_new;
-      const float p0 = ex2(s4[0] - m_new), p1 = ex2(s4[1] - m_new), p2 = ex2(s4[2] - m_new), p3 = ex2(s4[3] - m_new);
-      l_run = l_run * alpha + ((p0 + p1) + (p2 + p3));
-      const uint32_t pa0 = pack_bf16(p0, p1), pa2 = pack_bf16(p2, p3);  // P is rounded before P V
       if (__any_sync(0xFFFFFFFFu, grew)) {
 #pragma unroll
-        for (int nt = 0; nt < 16; ++nt) o[nt][0] *= alpha, o[nt][1] *= alpha;
+        for (int nt = 0; nt < 16; ++nt) {
+          o[nt][0] *= alpha[0], o[nt][1] *= alpha[0];
+          if constexpr (WIDE) o[nt][2] *= alpha[1], o[nt][3] *= alpha[1];
+        }
       }
       // O += P V: a load covers dims 16 x .. 16 x + 15 (two output tiles) of all 16 tokens.
 #pragma unroll
@@ -386,8 +424,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 6)
         const uint32_t addr = vbase + (x >> 2) * DEC_HALF_BYTES + v_lane + ((unit ^ lrow) << 4);
         uint32_t b[4];
         ldmatrix_x4_trans(addr, b);
-        mma_16x8x16(o[2 * x], pa0, pa2, b[0], b[1]);
-        mma_16x8x16(o[2 * x + 1], pa0, pa2, b[2], b[3]);
+        mma_16x8x16(o[2 * x], pa[0], pa[1], pa[2], pa[3], b[0], b[1]);
+        mma_16x8x16(o[2 * x + 1], pa[0], pa[1], pa[2], pa[3], b[2], b[3]);
       }
       __syncwarp();  // every lane is done with the slot before it is refilled
     }
@@ -396,11 +434,11 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 6)
   }  // chunks
 }
 
-template <int G>
+template <int G, bool WIDE>
 static int launch_chunks_for(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeParams& p, dim3 grid,
                              cudaStream_t s) {
   constexpr int SMEM = DEC_SMEM;
-  auto kernel = decode_chunks_kernel<G>;
+  auto kernel = decode_chunks_kernel<G, WIDE>;
   static bool configured[64] = {};
   int dev = 0;
   TJX_CUDA(cudaGetDevice(&dev));
@@ -442,11 +480,12 @@ static int launch_decode_chunks(DecodeParams& p, int group, cudaStream_t s) {
   // One CTA per possible chunk: the hardware scheduler balances the ones that have work (a CTA past the end of
   // the steps that run exits at once). The kernel also accepts a smaller grid and then loops over chunks.
   dim3 grid(chunks, groups);
+  const bool wide = p.T * group > 8;  // more than 8 query rows per KV head: both halves of the MMA's 16 rows
   switch (group) {
-    case 1: return launch_chunks_for<1>(mk, mv, p, grid, s);
-    case 2: return launch_chunks_for<2>(mk, mv, p, grid, s);
-    case 4: return launch_chunks_for<4>(mk, mv, p, grid, s);
-    default: return launch_chunks_for<8>(mk, mv, p, grid, s);
+    case 1: return wide ? launch_chunks_for<1, true>(mk, mv, p, grid, s) : launch_chunks_for<1, false>(mk, mv, p, grid, s);
+    case 2: return wide ? launch_chunks_for<2, true>(mk, mv, p, grid, s) : launch_chunks_for<2, false>(mk, mv, p, grid, s);
+    case 4: return wide ? launch_chunks_for<4, true>(mk, mv, p, grid, s) : launch_chunks_for<4, false>(mk, mv, p, grid, s);
+    default: return wide ? launch_chunks_for<8, true>(mk, mv, p, grid, s) : launch_chunks_for<8, false>(mk, mv, p, grid, s);
   }
 }
 
@@ -454,24 +493,24 @@ static int decode_slots(int pages_per_seq) { return (pages_per_seq + DEC_CHUNK -
 
 static size_t align256(size_t n) { return (n + 255) & ~static_cast<size_t>(255); }
 
-// Scratch layout: max [B, slots, H] | sum [B, slots, H] | accumulators [B, slots, H, D] | arrival counters [B, Hkv]
-// (at most H of them per sequence). Nothing in it has to start at zero: the step-table kernel clears the
+// Scratch layout, with rows = T * H query rows per sequence: max [B, slots, rows] | sum [B, slots, rows] |
+// accumulators [B, slots, rows, D] | arrival counters [B, Hkv] (room for H per sequence). Nothing in it has to start at zero: the step-table kernel clears the
 // counters at the start of every call, and every partial that is read was written earlier in the same call.
-static size_t decode_scratch_bytes(int B, int H, int D, int pages_per_seq) {
-  const size_t rows = static_cast<size_t>(B) * decode_slots(pages_per_seq) * H;
+static size_t decode_scratch_bytes(int B, int T, int H, int D, int pages_per_seq) {
+  const size_t rows = static_cast<size_t>(B) * decode_slots(pages_per_seq) * T * H;
   return 2 * align256(rows * sizeof(float)) + align256(rows * D * sizeof(float)) +
          align256(static_cast<size_t>(B) * H * sizeof(int));
 }
 
 static int check_decode_args(const void* q, const void* k_pages, const void* v_pages, const int32_t* block_tables,
-                             const int32_t* lengths, const void* out, int B, int H, int Hkv, int D, int page_size,
-                             int pages_per_seq, int num_pages, const int32_t* step_tile, const int32_t* step_code,
-                             const int32_t* step_count, const int32_t* tile_first) {
+                             const int32_t* lengths, const void* out, int B, int T, int H, int Hkv, int D,
+                             int page_size, int pages_per_seq, int num_pages, const int32_t* step_tile,
+                             const int32_t* step_code, const int32_t* step_count, const int32_t* tile_first) {
   if (!q || !k_pages || !v_pages || !block_tables || !lengths || !out)
     return fail(TJX_E_ARG, "an input or output pointer is null");
   if (!step_tile || !step_code || !step_count || !tile_first)
     return fail(TJX_E_ARG, "a step table pointer is null");
-  if (B <= 0 || H <= 0 || Hkv <= 0 || pages_per_seq <= 0 || num_pages <= 0)
+  if (B <= 0 || T <= 0 || H <= 0 || Hkv <= 0 || pages_per_seq <= 0 || num_pages <= 0)
     return fail(TJX_E_ARG, "sizes must be positive");
   if (D != DEC_D) return fail(TJX_E_ARG, "head dimension must be 128");
   if (page_size <= 0 || page_size % 16 != 0) return fail(TJX_E_ARG, "page size must be a multiple of 16");
@@ -479,6 +518,8 @@ static int check_decode_args(const void* q, const void* k_pages, const void* v_p
   const int group = H / Hkv;
   if (group != 1 && group != 2 && group != 4 && group != 8)
     return fail(TJX_E_ARG, "H / Hkv must be 1, 2, 4 or 8");
+  if (T * group > 16)
+    return fail(TJX_E_ARG, "new tokens x query heads per KV head must not exceed 16 (the rows of one warp-level MMA)");
   const uintptr_t ptrs[] = {reinterpret_cast<uintptr_t>(q), reinterpret_cast<uintptr_t>(k_pages),
                             reinterpret_cast<uintptr_t>(v_pages), reinterpret_cast<uintptr_t>(out)};
   for (uintptr_t a : ptrs)
@@ -489,8 +530,8 @@ static int check_decode_args(const void* q, const void* k_pages, const void* v_p
 // The two launches of a decode call, with the partials and counters in `scratch` (decode_scratch_bytes of it,
 // 256-byte aligned). Allocates nothing.
 static int run_decode(const void* q, const void* k_pages, const void* v_pages, const int32_t* block_tables,
-                      const int32_t* lengths, void* out, int B, int H, int Hkv, int page_size, int pages_per_seq,
-                      int num_pages, int32_t* step_tile, int32_t* step_code, int32_t* step_count,
+                      const int32_t* lengths, void* out, int B, int T, int H, int Hkv, int page_size,
+                      int pages_per_seq, int num_pages, int32_t* step_tile, int32_t* step_code, int32_t* step_count,
                       int32_t* tile_first, void* scratch, cudaStream_t s) {
   DecodeParams p{};
   p.q = static_cast<const __nv_bfloat16*>(q);
@@ -499,8 +540,9 @@ static int run_decode(const void* q, const void* k_pages, const void* v_pages, c
   p.block_tables = block_tables, p.lengths = lengths;
   p.step_tile = step_tile, p.step_code = step_code, p.step_count = step_count, p.tile_first = tile_first;
   p.B = B, p.H = H, p.Hkv = Hkv, p.page_size = page_size, p.pages_per_seq = pages_per_seq, p.num_pages = num_pages;
+  p.T = T, p.rows = T * H;
   p.slots = decode_slots(pages_per_seq);
-  const size_t rows = static_cast<size_t>(B) * p.slots * H;
+  const size_t rows = static_cast<size_t>(B) * p.slots * p.rows;
   uint8_t* ws = static_cast<uint8_t*>(scratch);
   p.ws_m = reinterpret_cast<float*>(ws);
   p.ws_l = reinterpret_cast<float*>(ws + align256(rows * sizeof(float)));
@@ -518,27 +560,28 @@ static int run_decode(const void* q, const void* k_pages, const void* v_pages, c
 
 extern "C" {
 
-size_t tjx_paged_gqa_decode_workspace_bytes(int B, int H, int D, int pages_per_seq) {
-  if (B <= 0 || H <= 0 || D <= 0 || pages_per_seq <= 0) return 0;
-  return tjx::decode_scratch_bytes(B, H, D, pages_per_seq);
+size_t tjx_paged_gqa_decode_workspace_bytes(int B, int T, int H, int D, int pages_per_seq) {
+  if (B <= 0 || T <= 0 || H <= 0 || D <= 0 || pages_per_seq <= 0) return 0;
+  return tjx::decode_scratch_bytes(B, T, H, D, pages_per_seq);
 }
 
 int tjx_paged_gqa_decode_bf16(const void* q, const void* k_pages, const void* v_pages, const int32_t* block_tables,
-                              const int32_t* lengths, void* out, int B, int H, int Hkv, int D, int page_size,
+                              const int32_t* lengths, void* out, int B, int T, int H, int Hkv, int D, int page_size,
                               int pages_per_seq, int num_pages, int32_t* step_tile, int32_t* step_code,
                               int32_t* step_count, int32_t* tile_first, void* workspace, size_t workspace_bytes,
                               tjx_stream_t stream) {
   using namespace tjx;
   if (int rc = check_device()) return rc;
-  if (int rc = check_decode_args(q, k_pages, v_pages, block_tables, lengths, out, B, H, Hkv, D, page_size,
+  if (int rc = check_decode_args(q, k_pages, v_pages, block_tables, lengths, out, B, T, H, Hkv, D, page_size,
                                  pages_per_seq, num_pages, step_tile, step_code, step_count, tile_first))
     return rc;
-  const size_t need = tjx_paged_gqa_decode_workspace_bytes(B, H, D, pages_per_seq);
+  const size_t need = tjx_paged_gqa_decode_workspace_bytes(B, T, H, D, pages_per_seq);
   if (workspace == nullptr || workspace_bytes < need)
     return fail(TJX_E_ARG, "workspace is null or smaller than tjx_paged_gqa_decode_workspace_bytes");
   if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(TJX_E_ARG, "workspace must be 256-byte aligned");
-  return run_decode(q, k_pages, v_pages, block_tables, lengths, out, B, H, Hkv, page_size, pages_per_seq, num_pages,
-                    step_tile, step_code, step_count, tile_first, workspace, static_cast<cudaStream_t>(stream));
+  return run_decode(q, k_pages, v_pages, block_tables, lengths, out, B, T, H, Hkv, page_size, pages_per_seq,
+                    num_pages, step_tile, step_code, step_count, tile_first, workspace,
+                    static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"
@@ -581,24 +624,25 @@ extern "C" {
 size_t tjx_paged_gqa_decode_static_scratch_bytes(void) { return tjx::STATIC_SCRATCH_BYTES; }
 
 int tjx_paged_gqa_decode_bf16_static(const void* q, const void* k_pages, const void* v_pages,
-                                     const int32_t* block_tables, const int32_t* lengths, void* out, int B, int H,
-                                     int Hkv, int D, int page_size, int pages_per_seq, int num_pages,
+                                     const int32_t* block_tables, const int32_t* lengths, void* out, int B, int T,
+                                     int H, int Hkv, int D, int page_size, int pages_per_seq, int num_pages,
                                      int32_t* step_tile, int32_t* step_code, int32_t* step_count, int32_t* tile_first,
                                      tjx_stream_t stream) {
   using namespace tjx;
   if (int rc = check_device()) return rc;
-  if (int rc = check_decode_args(q, k_pages, v_pages, block_tables, lengths, out, B, H, Hkv, D, page_size,
+  if (int rc = check_decode_args(q, k_pages, v_pages, block_tables, lengths, out, B, T, H, Hkv, D, page_size,
                                  pages_per_seq, num_pages, step_tile, step_code, step_count, tile_first))
     return rc;
-  const size_t need = tjx_paged_gqa_decode_workspace_bytes(B, H, D, pages_per_seq);
+  const size_t need = tjx_paged_gqa_decode_workspace_bytes(B, T, H, D, pages_per_seq);
   if (need > STATIC_SCRATCH_BYTES)
     return fail(TJX_E_LIMIT, "these sizes need " + std::to_string(need) + " bytes of scratch, more than the " +
                                  std::to_string(STATIC_SCRATCH_BYTES) +
                                  " bytes built into the library: use tjx_paged_gqa_decode_bf16 with a workspace");
   void* scratch = nullptr;
   if (int rc = static_scratch_address(&scratch)) return rc;
-  return run_decode(q, k_pages, v_pages, block_tables, lengths, out, B, H, Hkv, page_size, pages_per_seq, num_pages,
-                    step_tile, step_code, step_count, tile_first, scratch, static_cast<cudaStream_t>(stream));
+  return run_decode(q, k_pages, v_pages, block_tables, lengths, out, B, T, H, Hkv, page_size, pages_per_seq,
+                    num_pages, step_tile, step_code, step_count, tile_first, scratch,
+                    static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

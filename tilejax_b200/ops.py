@@ -215,21 +215,21 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, block_q:
 
 
 @lru_cache(maxsize=None)
-def _decode_workspace_bytes(B: int, H: int, D: int, pages: int) -> int:
-    return int(library().tjx_paged_gqa_decode_workspace_bytes(B, H, D, pages))
+def _decode_workspace_bytes(B: int, T: int, H: int, D: int, pages: int) -> int:
+    return int(library().tjx_paged_gqa_decode_workspace_bytes(B, T, H, D, pages))
 
 
 class DecodeBuffers:
     """The step tables and scratch one `paged_gqa_decode` call fills; reusable across calls of the same sizes."""
 
-    def __init__(self, B: int, H: int, D: int, pages_per_seq: int, device: torch.device):
+    def __init__(self, B: int, H: int, D: int, pages_per_seq: int, device: torch.device, T: int = 1):
         n = B * pages_per_seq
-        self.key = (B, H, D, pages_per_seq, str(device))
+        self.key = (B, T, H, D, pages_per_seq, str(device))
         self.step_tile = torch.empty(n, dtype=torch.int32, device=device)
         self.step_code = torch.empty(n, dtype=torch.int32, device=device)
         self.step_count = torch.empty(1, dtype=torch.int32, device=device)
         self.tile_first = torch.empty(B + 1, dtype=torch.int32, device=device)
-        self.workspace_bytes = _decode_workspace_bytes(B, H, D, pages_per_seq)
+        self.workspace_bytes = _decode_workspace_bytes(B, T, H, D, pages_per_seq)
         self.workspace = torch.empty(self.workspace_bytes + 256, dtype=torch.uint8, device=device)
 
     def workspace_ptr(self) -> int:
@@ -239,12 +239,11 @@ class DecodeBuffers:
 def paged_gqa_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_tables: torch.Tensor,
                      lengths: torch.Tensor, out: torch.Tensor | None = None,
                      buffers: DecodeBuffers | None = None) -> torch.Tensor:
-    """The `paged_gqa_decode` loop nest (examples/decode.py:199-223) for one new token per sequence. The step
-    tables the call built on the device are left in `buffers` (pass one to inspect or reuse them)."""
+    """The `paged_gqa_decode` loop nest (examples/decode.py:199-223): q (B, T, H, D) holds T new tokens per
+    sequence (`lengths` counts them; token t sits at position lengths[b] - T + t and sees the positions up to its
+    own). The step tables the call built on the device are left in `buffers` (pass one to inspect or reuse them)."""
     device = _need_cuda(q, k_pages, v_pages, block_tables, lengths)
     B, T, H, D = q.shape
-    if T != 1:
-        raise ValueError("one new token per sequence (T = 1)")
     num_pages, page_size, W = k_pages.shape
     if v_pages.shape != k_pages.shape or W % D != 0:
         raise ValueError("k_pages and v_pages must both be (num_pages, page_size, Hkv * D)")
@@ -254,13 +253,15 @@ def paged_gqa_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
         raise ValueError("block_tables is (B, pages_per_seq) and lengths (B,)")
     Hkv = W // D
     pages_per_seq = block_tables.shape[1]
-    if buffers is None or buffers.key != (B, H, D, pages_per_seq, str(device)):
-        buffers = DecodeBuffers(B, H, D, pages_per_seq, device)
+    if not q.is_contiguous():
+        raise ValueError("q must be contiguous (B, T, H, D)")
+    if buffers is None or buffers.key != (B, T, H, D, pages_per_seq, str(device)):
+        buffers = DecodeBuffers(B, H, D, pages_per_seq, device, T)
     if out is None:
         out = torch.empty_like(q)
     with torch.cuda.device(device):
         check(library().tjx_paged_gqa_decode_bf16(
-            _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_tables), _ptr(lengths), _ptr(out), B, H, Hkv, D,
+            _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_tables), _ptr(lengths), _ptr(out), B, T, H, Hkv, D,
             page_size, pages_per_seq, num_pages, _ptr(buffers.step_tile), _ptr(buffers.step_code),
             _ptr(buffers.step_count), _ptr(buffers.tile_first), ctypes.c_void_p(buffers.workspace_ptr()),
             buffers.workspace_bytes, _stream()))
@@ -276,7 +277,7 @@ def _identity_block_table(B: int, blocks: int, device: str) -> torch.Tensor:
 def gqa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, lengths: torch.Tensor,
                block_kv: int = 512, out: torch.Tensor | None = None,
                buffers: DecodeBuffers | None = None) -> torch.Tensor:
-    """The `gqa_decode` loop nest (examples/decode.py:176-196) for one new token per sequence: the contiguous cache
+    """The `gqa_decode` loop nest (examples/decode.py:176-196), T new tokens per sequence: the contiguous cache
     (B, S, Hkv * D) is the page pool whose block table is the identity — sequence b's block j is page
     b * (S / block) + j — so the paged kernel runs unchanged, device step tables included."""
     _need_cuda(q, k_cache, v_cache, lengths)
@@ -299,15 +300,13 @@ def paged_gqa_decode_static(q: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
     the built-in 36 MiB raise; calls that overlap on the GPU race on the shared scratch."""
     device = _need_cuda(q, k_pages, v_pages, block_tables, lengths, out, step_tile, step_code, step_count, tile_first)
     B, T, H, D = q.shape
-    if T != 1:
-        raise ValueError("one new token per sequence (T = 1)")
     num_pages, page_size, W = k_pages.shape
     pages_per_seq = block_tables.shape[1]
     if step_tile.numel() < B * pages_per_seq or step_code.numel() < B * pages_per_seq or tile_first.numel() < B + 1:
         raise ValueError("the step table buffers are too small")
     with torch.cuda.device(device):
         check(library().tjx_paged_gqa_decode_bf16_static(
-            _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_tables), _ptr(lengths), _ptr(out), B, H, W // D, D,
+            _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_tables), _ptr(lengths), _ptr(out), B, T, H, W // D, D,
             page_size, pages_per_seq, num_pages, _ptr(step_tile), _ptr(step_code), _ptr(step_count),
             _ptr(tile_first), _stream()))
     return out
