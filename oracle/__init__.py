@@ -18,7 +18,14 @@ which cannot be imported where this was written, so the oracle could not be run 
 
 from .attention import causal_attention_f64, causal_attention_ref
 from .compare import compare
-from .decode import gqa_decode_ref, paged_gqa_decode_f64, paged_gqa_decode_ref, to_pages
+from .decode import (
+    gqa_decode_ref,
+    mla_decode_f64,
+    mla_decode_ref,
+    paged_gqa_decode_f64,
+    paged_gqa_decode_ref,
+    to_pages,
+)
 from .matmul import causal_matmul_ref, collective_row_order, matmul_ref
 from .steps import (
     attention_step_tables,
@@ -40,6 +47,8 @@ __all__ = [
     "gqa_decode_ref",
     "lengths_runs",
     "matmul_ref",
+    "mla_decode_f64",
+    "mla_decode_ref",
     "paged_gqa_decode_f64",
     "paged_gqa_decode_ref",
     "to_pages",

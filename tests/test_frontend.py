@@ -76,6 +76,10 @@ def test_decode_steps_are_found_on_the_device():
                               K.DecodeTiles(block_kv=256))
     assert flat.schedule.runtime and flat.steps == 4 * 4 and "identity block table" in flat.source
     assert flat.plan.params["page"] == 256 and flat.plan.params["num_pages"] == 16
+    # Absorbed MLA decode (examples/decode.py:226-250): its own kernel, the same device tables.
+    mla = K.mla_decode.lower(spec(4, 1, 16, 512), spec(4, 1, 16, 128), spec(4, 1024, 512), spec(4, 1024, 128),
+                             spec(4, dtype=np.int32), K.DecodeTiles(block_kv=256))
+    assert mla.schedule.runtime and mla.steps == 4 * 4 and "tjx_mla_decode_bf16" in mla.source
 
 
 def test_tiles_clamp_to_the_matrix_and_neighbours_that_build_the_same_kernel_are_skipped():
@@ -115,6 +119,10 @@ def test_references_equal_the_oracle_for_every_nest():
     qc, lens = rand_bf16((3, 1, 8, 128), 6, 128**-0.5), np.array([0, 300, 512], np.int32)
     np.testing.assert_array_equal(f64(K.gqa_decode.reference(qc, kc, vc, lens, K.DecodeTiles(block_kv=128))),
                                   f64(oracle.gqa_decode_ref(qc, kc, vc, lens, 128)))
+    q_c, q_r = rand_bf16((3, 1, 16, 512), 7, 0.01), rand_bf16((3, 1, 16, 128), 8, 0.07)
+    c_kv, k_rope = rand_bf16((3, 512, 512), 9), rand_bf16((3, 512, 128), 10)
+    np.testing.assert_array_equal(f64(K.mla_decode.reference(q_c, q_r, c_kv, k_rope, lens, K.DecodeTiles(block_kv=128))),
+                                  f64(oracle.mla_decode_ref(q_c, q_r, c_kv, k_rope, lens, 128)))
     np.testing.assert_array_equal(f64(K.all_gather_matmul.reference(x, y, K.CollectiveTiles())),
                                   f64(oracle.matmul_ref(x, y, 256, 512, 256)))
 

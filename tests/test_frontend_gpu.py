@@ -42,6 +42,9 @@ def test_every_loop_nest_verifies():
     assert not f64(K.paged_gqa_decode(q, kp, vp, bt, lengths)[0]).any()
     kc, vc = rand_bf16((4, 512, 256), 4), rand_bf16((4, 512, 256), 5)
     assert K.gqa_decode.verify(rand_bf16((4, 1, 8, 128), 6, 128**-0.5), kc, vc, lengths, K.DecodeTiles(block_kv=128)) <= 2e-2
+    q_c, q_r = rand_bf16((4, 1, 16, 512), 7, 0.01), rand_bf16((4, 1, 16, 128), 8, 0.07)
+    c_kv, k_rope = rand_bf16((4, 512, 512), 9), rand_bf16((4, 512, 128), 10)
+    assert K.mla_decode.verify(q_c, q_r, c_kv, k_rope, lengths, K.DecodeTiles(block_kv=128)) <= 2e-2
     assert K.all_gather_matmul.verify(x, y, K.CollectiveTiles()) <= 0.5  # one rank: the gather is the identity
 
 

@@ -1,0 +1,67 @@
+"""Absorbed MLA decode through the C ABI against the oracle (`mla_decode`, examples/decode.py:226-250).
+
+Tolerance: atol 2e-2 against float64, as tests/test_decode.py:235; the step tables the call built are bit-exact."""
+
+import numpy as np
+import pytest
+from helpers import f64, rand_bf16, to_device, to_host
+
+import oracle
+from tilejax_b200 import ops
+from tilejax_b200._lib import NativeError
+
+pytestmark = pytest.mark.gpu
+
+
+def mla_inputs(B, H, S, seed=0):
+    q_c = rand_bf16((B, 1, H, 512), seed, 192**-0.5 * 0.1)
+    q_r, k_rope = rand_bf16((B, 1, H, 128), seed + 1, 192**-0.5), rand_bf16((B, S, 128), seed + 3)
+    q_r[..., 64:] = 0
+    k_rope[..., 64:] = 0
+    return q_c, q_r, rand_bf16((B, S, 512), seed + 2), k_rope
+
+
+def run(q_c, q_r, c_kv, k_rope, lengths, block):
+    out = ops.mla_decode(*map(to_device, (q_c, q_r, c_kv, k_rope, lengths)), block)
+    assert ops.device_status() == 0
+    bufs = ops.mla_decode.last_buffers
+    blocks = c_kv.shape[1] // min(block, c_kv.shape[1])
+    tile, code, count = oracle.device_step_tables(oracle.lengths_runs(lengths, blocks, 0, min(block, c_kv.shape[1])))
+    np.testing.assert_array_equal(to_host(bufs.step_tile), tile)
+    np.testing.assert_array_equal(to_host(bufs.step_code), code)
+    assert int(bufs.step_count[0]) == int(count[0])
+    return to_host(out)
+
+
+@pytest.mark.parametrize(("heads", "block"), [(16, 128), (16, 512), (32, 64), (128, 256), (16, 16)])
+def test_matches_the_oracle_on_ragged_lengths(heads, block):
+    # tests/test_decode.py:224-235: 16 heads at blocks 128 / 256, lengths (0, 1, 300, S); wider head counts as the
+    # reference's benchmark (H 16-128).
+    q_c, q_r, c_kv, k_rope = mla_inputs(4, heads, 512)
+    lengths = np.array([0, 1, 300, 512], np.int32)
+    got = run(q_c, q_r, c_kv, k_rope, lengths, block)
+    want = oracle.mla_decode_ref(q_c, q_r, c_kv, k_rope, lengths, block)
+    assert np.abs(f64(got) - f64(want)).max() <= 2e-2
+    assert np.abs(f64(got) - oracle.mla_decode_f64(q_c, q_r, c_kv, k_rope, lengths)).max() <= 2e-2
+    assert not f64(got[0]).any()
+
+
+def test_block_size_is_only_a_schedule():
+    # The same cache walked in blocks of 64 or 512 positions agrees to rounding; two calls in a row agree exactly.
+    q_c, q_r, c_kv, k_rope = mla_inputs(8, 16, 2048, seed=5)
+    lengths = np.random.default_rng(0).integers(1, 2049, 8).astype(np.int32)
+    a = run(q_c, q_r, c_kv, k_rope, lengths, 64)
+    b = run(q_c, q_r, c_kv, k_rope, lengths, 512)
+    assert np.abs(f64(a) - f64(b)).max() <= 2e-2
+    np.testing.assert_array_equal(f64(a), f64(run(q_c, q_r, c_kv, k_rope, lengths, 64)))
+    assert np.abs(f64(b) - oracle.mla_decode_f64(q_c, q_r, c_kv, k_rope, lengths)).max() <= 2e-2
+
+
+def test_unsupported_shapes_are_errors():
+    q_c, q_r, c_kv, k_rope = mla_inputs(2, 8, 128)
+    lengths = np.array([5, 128], np.int32)
+    with pytest.raises(NativeError, match="multiple of 16"):
+        run(q_c, q_r, c_kv, k_rope, lengths, 128)
+    q_c, q_r, c_kv, k_rope = mla_inputs(2, 16, 128)
+    with pytest.raises(NativeError, match="multiple of 16 positions"):
+        run(q_c, q_r, c_kv, k_rope, lengths, 8)

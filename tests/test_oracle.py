@@ -185,6 +185,26 @@ def test_several_new_tokens_see_only_positions_up_to_their_own():
         np.testing.assert_array_equal(f64(got[:, t]), f64(alone[:, 0]))
 
 
+def mla_inputs(B, H, S, seed=0):
+    # tests/test_decode.py:152-160 in shape: latents 512 wide, RoPE keys 64 wide padded with zeros to 128.
+    q_c = rand_bf16((B, 1, H, 512), seed, 192**-0.5 * 0.1)
+    q_r, k_rope = rand_bf16((B, 1, H, 128), seed + 1, 192**-0.5), rand_bf16((B, S, 128), seed + 3)
+    q_r[..., 64:] = 0
+    k_rope[..., 64:] = 0
+    return q_c, q_r, rand_bf16((B, S, 512), seed + 2), k_rope
+
+
+def test_mla_decode_oracle_against_float64():
+    # tests/test_decode.py:224-235 (16 heads, block 128) with the ragged lengths of :163-165.
+    q_c, q_r, c_kv, k_rope = mla_inputs(4, 16, 512)
+    lengths = np.array([0, 1, 300, 512], np.int32)
+    want = oracle.mla_decode_f64(q_c, q_r, c_kv, k_rope, lengths)
+    for block in (128, 512):
+        got = oracle.mla_decode_ref(q_c, q_r, c_kv, k_rope, lengths, block)
+        assert np.abs(f64(got) - want).max() <= 2e-2  # atol of tests/test_decode.py:235
+        assert not f64(got[0]).any()
+
+
 def test_compare_rule():
     # src/autokernel/api.py:320-364 and tests/test_api.py:87-108: NaN equals NaN; 16-bit tolerance scales with
     # the largest value; integers are exact.

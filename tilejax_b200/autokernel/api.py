@@ -329,6 +329,10 @@ def _check_kernel_rules(plan: Plan) -> None:
             raise nest.error("the attention kernel takes head_dim 128 and blocks that are multiples of 128")
         if any(np.dtype(s.dtype) != bf16 for s in plan.specs[:3]):
             raise nest.error("the attention kernel takes bfloat16 q, k, v")
+    elif p.get("mla"):
+        if p["C"] != 512 or p["R"] != 128 or p["H"] % 16 or p["page"] % 16 or p["T"] != 1:
+            raise nest.error("the MLA decode kernel takes one new token, 512 latent and 128 RoPE columns, heads in "
+                             "multiples of 16 and blocks of a multiple of 16 positions")
     else:
         if p["D"] != 128 or p["page"] % 16 or p["H"] % p["Hkv"] or p["H"] // p["Hkv"] not in (1, 2, 4, 8):
             raise nest.error("the decode kernel takes head_dim 128, pages of a multiple of 16 positions and 1, 2, 4 "
@@ -412,6 +416,15 @@ def _lower(plan: Plan, config: Config) -> tuple[str, Callable[..., Any]]:
             f"CTA         two 128-row query tiles sharing each 128-key K/V block; future blocks skipped\n"
             f"tables      {', '.join(f'{k}[{len(v)}]' for k, v in sch.tables.items()) or 'none'}\n")
         return text, lambda q, k, v: ops.causal_attention(q, k, v, p["block_q"], p["block_kv"])
+    if p.get("mla"):
+        text = header + (
+            f"kernel      tjx_mla_decode_bf16 (device step tables, CTA-wide TMA ring, warp-level MMA over 16 heads, "
+            f"partials merged by the last CTA to arrive)\n"
+            f"problem     {p['B']} sequences, {p['H']} heads, {p['C']} latent + {p['R']} RoPE columns, blocks of "
+            f"{p['page']} of {p['S']} cache positions\n"
+            f"steps       at most {sch.steps}: step_tile / step_code / step_count are built on the device from lengths "
+            f"before the kernel\n")
+        return text, lambda q_c, q_r, c_kv, k_rope, lengths: ops.mla_decode(q_c, q_r, c_kv, k_rope, lengths, p["page"])
     text = header + (
         f"kernel      tjx_paged_gqa_decode_bf16 (device step tables, per-warp TMA rings, warp-level MMA, partials "
         f"merged by the last warp to arrive)\n"

@@ -2,7 +2,7 @@
 
 Each is the plain loop nest over tiles whose meaning the kernel must reproduce — `kernel.fn` runs it as written on
 the CPU — with the same structure as the reference's examples (examples/matmul.py, causal_matmul.py,
-causal_attention.py, decode.py `gqa_decode` and `paged_gqa_decode`, collective_matmul.py). Row statistics are kept as (rows, 1)
+causal_attention.py, decode.py `gqa_decode`, `mla_decode` and `paged_gqa_decode`, collective_matmul.py). Row statistics are kept as (rows, 1)
 columns here: the reference's lane-replicated (rows, 128) layout is a TPU register trick, not arithmetic.
 """
 
@@ -178,6 +178,49 @@ def gqa_decode(q, k_cache, v_cache, lengths, tiles=DecodeTiles()):
             vt = page_by_kv_head(v_cache[b, j : j + bk, :], Hkv)
             row_max, row_sum, acc = online_softmax(s, vt, ok, row_max, row_sum, acc)
         out = out.at[b, :, :, :].set(finish(acc, row_sum, (T, H, Dh), dtype))
+    return out
+
+
+def mla_softmax_step(s, ct, ok, row_max, row_sum, acc):
+    """One online-softmax step of MLA decode: scores s (H, bk) against the latents ct (bk, C) themselves."""
+    s = jnp.where(ok, s, MASK_VALUE)
+    max_new = jnp.maximum(row_max, jnp.max(s, axis=1, keepdims=True))
+    p = jnp.exp(s - max_new)
+    alpha = jnp.exp(row_max - max_new)
+    row_sum = alpha * row_sum + jnp.sum(p, axis=1, keepdims=True)
+    acc = alpha * acc + jnp.dot(p.astype(ct.dtype), ct, preferred_element_type=jnp.float32)
+    return max_new, row_sum, acc
+
+
+def before_the_end(block, first, length):
+    """Which positions of a block starting at `first` are before the sequence's end: (1, block)."""
+    return first + jax.lax.broadcasted_iota(jnp.int32, (1, block), 1) < length
+
+
+@autokernel.kernel
+def mla_decode(q_c, q_r, c_kv, k_rope, lengths, tiles=DecodeTiles()):
+    """Absorbed MLA decode attention: q_c (B, 1, H, C), q_r (B, 1, H, 128), the latent cache (B, S_max, C) and the
+    RoPE key cache (B, S_max, 128); out (B, 1, H, C), each head's softmax-weighted latents."""
+    B, T, H, C = q_c.shape
+    S = c_kv.shape[1]
+    bk, dtype = min(tiles.block_kv, S), q_c.dtype
+    out = jnp.zeros((B, T, H, C), dtype)
+    for b in range(B):
+        qc = q_c[b, 0, :, :]
+        qr = q_r[b, 0, :, :]
+        row_max = jnp.full((H, 1), MASK_VALUE, jnp.float32)
+        row_sum = jnp.zeros((H, 1), jnp.float32)
+        acc = jnp.zeros((H, C), jnp.float32)
+        for j in range(0, S, bk):
+            if j >= lengths[b]:  # past the sequence's end: decided on the device, before the kernel runs
+                continue
+            ct = c_kv[b, j : j + bk, :]
+            s = jnp.dot(qc, ct.T, preferred_element_type=jnp.float32)
+            s = s + jnp.dot(qr, k_rope[b, j : j + bk, :].T, preferred_element_type=jnp.float32)
+            ok = before_the_end(bk, j, lengths[b])
+            row_max, row_sum, acc = mla_softmax_step(s, ct, ok, row_max, row_sum, acc)
+        res = acc * (1.0 / jnp.maximum(row_sum, 1e-30))
+        out = out.at[b, :, :, :].set(res.reshape(T, H, C).astype(dtype))
     return out
 
 

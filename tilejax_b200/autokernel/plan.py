@@ -346,9 +346,41 @@ def _recognise_contiguous_decode(nest, ns, specs, outputs, parallel, reductions)
     return Plan(nest, "decode", specs, outputs, parallel, reductions, params, runtime=True)
 
 
+def _recognise_mla_decode(nest, ns, specs, outputs, parallel, reductions) -> Plan:
+    """`mla_decode`: (q_c, q_r, c_kv, k_rope, lengths), blocks of the latent cache skipped with `j >= lengths[b]`."""
+    (b,), (j,) = parallel, reductions
+    q_c, q_r, c_kv, k_rope, lengths = specs[:5]
+    mask = nest.reductions[0].mask
+    reads = {n.value.id for n in ast.walk(mask) if isinstance(n, ast.Subscript) and isinstance(n.value, ast.Name)}
+    if reads != {nest.inputs[4]} or np.dtype(lengths.dtype) != np.int32:
+        raise _unsupported(nest, "the block loop's mask must compare the block's first position with lengths[b]",
+                           nest.reductions[0].node)
+    if q_c.ndim != 4 or q_r.ndim != 4 or k_rope.ndim != 3 or lengths.ndim != 1 or q_c.shape[:3] != q_r.shape[:3] \
+            or c_kv.shape[:2] != k_rope.shape[:2] or c_kv.shape[2] != q_c.shape[3] or k_rope.shape[2] != q_r.shape[3]:
+        raise _unsupported(nest, "MLA decode takes q_c (B, T, H, C), q_r (B, T, H, R), c_kv (B, S, C), k_rope (B, S, R) "
+                                 "and lengths (B,)")
+    B, T, H, C = q_c.shape
+    S, R = c_kv.shape[1], k_rope.shape[2]
+    code = compile(ast.Expression(mask), nest.filename, "eval")
+
+    def skipped(jv: int, length: int) -> bool:
+        return bool(eval(code, dict(ns), {j.var: jv, b.var: 0, nest.inputs[4]: [length]}))
+
+    block = j.step
+    ok = all(skipped(jv, n) == (jv >= n) for jv in (0, block, (j.count - 1) * block) for n in (0, 1, block, block + 1, S))
+    if not ok or b.count != B or j.start != 0 or j.stop != S or S % block:
+        raise _unsupported(nest, "the block loop must cover the cache and skip blocks with `j >= lengths[b]`",
+                           nest.reductions[0].node)
+    sch = _schedule.paged_decode_schedule(B, j.count)
+    params = dict(B=B, T=T, H=H, C=C, R=R, S=S, page=block, pages=j.count, schedule=sch, mla=True)
+    return Plan(nest, "decode", specs, outputs, parallel, reductions, params, runtime=True)
+
+
 def _recognise_decode(nest, ns, specs, outputs, parallel, reductions) -> Plan:
     if len(parallel) == 1 and len(nest.inputs) == 4:
         return _recognise_contiguous_decode(nest, ns, specs, outputs, parallel, reductions)
+    if len(parallel) == 1 and len(nest.inputs) == 5 and specs[3].ndim == 3:
+        return _recognise_mla_decode(nest, ns, specs, outputs, parallel, reductions)
     if len(parallel) != 1 or len(nest.inputs) != 5:
         raise _unsupported(nest, "a runtime mask other than decode's: (q, k_cache, v_cache, lengths) or "
                                  "(q, k_pages, v_pages, block_tables, lengths)")
