@@ -211,6 +211,7 @@ def workload_name(n: int) -> str:
 def extra_workloads(device, pk: dict, pk_kind: str, only: str | None = None, iters: int = 10, warm: int = 3) -> dict:
     """The other BASELINE configs at one GPU, device-timed with an L2 flush before every run. `only` keeps the
     workloads whose name contains it (for profiling one kernel with few launches)."""
+    import numpy as np
     import torch
 
     from tilejax_b200 import ops, synthetic
@@ -260,6 +261,36 @@ def extra_workloads(device, pk: dict, pk_kind: str, only: str | None = None, ite
                          {"algorithmic_flops": "4*B*H*D*S*(S+1)/2"})
         except Exception as e:  # not built yet, or failed: report, do not hide
             out[f"causal_attention_B{B}_H{H}_S{S}_D{D}_blocks512"] = {"error": str(e)[:200]}
+
+    if want("mla_decode"):
+        # The reference's MLA benchmark shape (benchmarks/decode.py:152-173): batch 32, contexts around 2048 of a
+        # 4096-position cache, 64 heads, 512 latents + 64 RoPE columns (stored 128 wide), blocks of 512.
+        try:
+            B, H, S = 32, 64, 4096
+            rng = np.random.default_rng(0)
+            lens = rng.integers(1024, 3073, B).astype(np.int32)
+            q_c = device_randn_bf16((B, 1, H, 512), 3, device, 192**-0.5 * 0.1)
+            q_r = device_randn_bf16((B, 1, H, 128), 4, device, 192**-0.5)
+            c_kv = device_randn_bf16((B, S, 512), 5, device)
+            k_rope = device_randn_bf16((B, S, 128), 6, device)
+            q_r[..., 64:] = 0
+            k_rope[..., 64:] = 0
+            lens_d = torch.from_numpy(lens).to(device)
+            mbufs = ops.MlaBuffers(B, H, S, 512, device)
+            mout = torch.empty_like(q_c)
+            ms = time_device(lambda: ops.mla_decode(q_c, q_r, c_kv, k_rope, lens_d, 512, out=mout, buffers=mbufs),
+                             2 * iters, warm, flush)
+            tokens = float(lens.sum())
+            nbytes = tokens * 576 * 2  # what the math reads: 512 latents + 64 RoPE columns per position
+            gbs = nbytes / ms / 1e6
+            out[f"mla_decode_B{B}_H{H}_ctx1024to3072"] = {
+                "ms": ms, "value": gbs, "unit": "GB/s", "algorithmic_bytes": nbytes,
+                "tflops": tokens * H * (2 * 576 + 2 * 512) / ms / 1e9,
+                "includes": "step-table kernel + decode (the merge of partials is fused into it)",
+                "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak,
+                             "peak_kind": pk_kind, "traffic": None}}
+        except Exception as e:  # report, do not hide
+            out["mla_decode"] = {"error": str(e)[:200]}
 
     if not want("paged_gqa_decode"):
         ops.device_status()
