@@ -435,13 +435,16 @@ def main() -> None:
         "config": {"workload": workload_name(world), "tiles": list(TILES), "rows_per_gpu": m,
                    "l2": "operands and output (671 MB) are larger than L2; no flush between steps",
                    "gather": "none (1 GPU)" if world == 1 else
+                   "inside the one GEMM launch: copier warps pull the peers' shards over NVLink (transport fused)"
+                   if op.transport == "fused" else
                    f"{world - 1} rounds on a second stream, transport {op.transport}, {len(op.groups)} GEMM launches"},
         "per_gpu_tflops": value / world,
         "clocks": clocks,
         "e2e": {"value": world * flops_per_gpu / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": x_host.numel() * 2 + y_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2,
                 "api": "tilejax_b200.collective.AllGatherMatmul.from_host with pinned host x, y and out"},
-        "gpu_launches": args.steps * (1 if world == 1 else len(op.groups)) + args.steps,
+        # Kernels of this library launched inside the timed region of `value`: GEMM launches per step x steps.
+        "gpu_launches": args.steps * (1 if world == 1 or op.transport == "fused" else len(op.groups)),
         "roofline": {"bound": "tensor", "kernel": "gemm_pair_kernel<3,2>", "achieved": gemm_tflops, "peak": peak,
                      "unit": "TFLOP/s", "frac": gemm_tflops / peak,
                      "peak_kind": f"{pk_kind} cuBLAS bf16, {'sustained' if long_run else 'burst'}",
