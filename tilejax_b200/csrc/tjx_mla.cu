@@ -115,7 +115,7 @@ __device__ __forceinline__ void mla_merge_rows(const MlaParams& p, int b, int h0
   }
 }
 
-__global__ void __launch_bounds__(MLA_WARPS * 32, 2)
+__global__ void __launch_bounds__(MLA_WARPS * 32, 3)
     mla_decode_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_r,
                       const MlaParams p) {
   extern __shared__ uint8_t mla_smem_raw[];
@@ -204,7 +204,8 @@ __global__ void __launch_bounds__(MLA_WARPS * 32, 2)
   for (int i = 0; i < n_micro; ++i) {
     const int stage = i % MLA_STAGES;
     const uint32_t sbase = ring + stage * MLA_STAGE_BYTES;
-    float sc[2][4] = {};
+    float sc[2][4] = {};  // scores; the odd k-steps accumulate apart (sd) so that four MMA chains run side by side
+    float sd[2][4] = {};
     if (ok) {
       if (threadIdx.x == 0 && i + MLA_STAGES - 1 < n_micro) {
         // The slot of micro-step i - 1 takes micro-step i + STAGES - 1 once every warp has left it.
@@ -229,8 +230,10 @@ __global__ void __launch_bounds__(MLA_WARPS * 32, 2)
             uint32_t bf[4];
             ldmatrix_x4(addr, bf);
             mma_16x8x16(sc[tl], qa[2 * x][0], qa[2 * x][1], qa[2 * x][2], qa[2 * x][3], bf[0], bf[1]);
-            mma_16x8x16(sc[tl], qa[2 * x + 1][0], qa[2 * x + 1][1], qa[2 * x + 1][2], qa[2 * x + 1][3], bf[2], bf[3]);
+            mma_16x8x16(sd[tl], qa[2 * x + 1][0], qa[2 * x + 1][1], qa[2 * x + 1][2], qa[2 * x + 1][3], bf[2], bf[3]);
           }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) sc[tl][e] += sd[tl][e];
         }
       }
     }
