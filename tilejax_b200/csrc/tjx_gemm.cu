@@ -15,6 +15,12 @@
 //
 // y [K, N] row-major is the MN-major B operand: a slot holds BN / 64 boxes of [64 n x 64 k], each row of a
 // box one k with 64 consecutive n (128 bytes). y [N, K] (x @ y.T) is the K-major operand, one box [64 k x BN].
+//
+// Three kernels share this loop (and the epilogue code): gemm_kernel, described above; gemm_pair_kernel, the
+// default whenever the user tile is a multiple of 256 x 256 — one MMA per pair of SMs (cta_group::2), each SM
+// staging half of y's columns (see the section "CTA pairs" below); and its all-gather variant, which adds a
+// copier warp per CTA that pulls the other ranks' rows of x out of peer memory while the tiles of the rows that
+// are already here run (tjx_all_gather_gemm_bf16).
 #include <algorithm>
 
 #include "tjx_host.cuh"
