@@ -95,7 +95,7 @@ int tjx_gemm_set_pair_mode(int mode);
 
 /* `all_gather_matmul` in one launch (the ring kernel of src/autokernel/codegen.py:1149-1229, whose remote DMAs run
  * beside its matmul steps): out[ranks * m, N] = all_gather(x) @ y on this rank. The GEMM kernel carries one extra
- * warp per CTA that pulls the other ranks' shards out of peer memory (plain loads over NVLink, no multicast) into
+ * warp per CTA that pulls the other ranks' shards out of peer memory (plain 16-byte loads over NVLink) into
  * `gathered`, 256 rows at a time in the order the ring would deliver them (round r: rank (me - r) mod ranks),
  * while the tensor cores work through the tile table — the own shard's tiles first, straight from x_own. A tile of
  * a remote shard starts once every CTA's slice of its 256-row block has landed (`arrivals`).
