@@ -369,7 +369,7 @@ def main() -> None:
     y = y_host.to(device)
     reserve = os.environ.get("TJX_RESERVE_SMS")
     op = AllGatherMatmul(m, K_DIM, N_DIM, *TILES, reserve_sms=None if reserve is None else int(reserve),
-                         transport=os.environ.get("TJX_TRANSPORT", "peer"))
+                         transport=os.environ.get("TJX_TRANSPORT", "fused"))
     op.exchange.rows(op.me).copy_(x)  # (only the kernel-alone timing below reads the own rows of xs)
     out_host = torch.empty((M_TOTAL, N_DIM), dtype=torch.bfloat16).pin_memory()
 

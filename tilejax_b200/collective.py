@@ -145,13 +145,15 @@ class AllGatherMatmul:
     """out = all_gather(x) @ w on each rank, [ranks * m, N] bf16, with the gather hidden behind the compute.
 
     Buffers (xs, out), the tile tables, the communication stream and the events are made once; a call only enqueues
-    work. `transport` is "peer" (copy-engine pulls from peers' symmetric memory: no SMs) or "nccl" (send / receive
-    rounds: NCCL's copy kernels need SMs, so `reserve_sms` of them are kept free of GEMM CTAs while rounds are in
-    flight; "peer" keeps a few free for its barrier kernel).
+    work. `transport` is "fused" (the default: one GEMM launch whose copier warps pull the peers' shards out of
+    symmetric memory; tiles that are not multiples of 256 fall back to "peer"), "peer" (copy-engine pulls from
+    peers' symmetric memory on a second stream: no SMs) or "nccl" (send / receive rounds: NCCL's copy kernels need
+    SMs, so `reserve_sms` of them are kept free of GEMM CTAs while rounds are in flight; "peer" keeps a few free for
+    its barrier kernel).
     """
 
     def __init__(self, m: int, K: int, N: int, tm: int = 256, tn: int = 512, tk: int = 512, group=None,
-                 device: torch.device | None = None, reserve_sms: int | None = None, transport: str = "peer"):
+                 device: torch.device | None = None, reserve_sms: int | None = None, transport: str = "fused"):
         from . import ops  # needs the built library
 
         self._ops = ops

@@ -404,6 +404,9 @@ constexpr int PAIR_STAGES = 3;
 constexpr int PAIR_KSUB = 2;
 
 constexpr int GATHER_THREADS = GEMM_THREADS + 32;  // the pair kernel with its copier warp
+// 16-byte loads a copier lane keeps in flight: 148 warps x 32 lanes x 32 x 16 B = 2.4 MB on the wire, what a few
+// microseconds of NVLink latency need at several hundred GB/s.
+constexpr int GATHER_LOADS = 32;
 
 __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
   int v;
@@ -606,7 +609,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
     // ------------------------------------------------------------------ copier (one warp per CTA)
     // Pulls the other ranks' shards from peer memory into this GPU's copy, a 256-row block at a time in the order
     // the tiles will want them (round r brings the shard of rank (me - r) mod ranks), every CTA's warp a slice
-    // of each block: 16 bytes per lane per load, eight loads in flight. It waits for nothing — the peers' shards
+    // of each block: 16 bytes per lane per load, GATHER_LOADS loads in flight. It waits for nothing — the peers' shards
     // were complete before the launch — so the warps that wait on its counters always see progress.
     const int per_shard = p.gather_rows / PAIR_ROWS;
     const size_t block_bytes = static_cast<size_t>(PAIR_ROWS) * p.K * 2;
@@ -618,13 +621,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
         const uint8_t* src = static_cast<const uint8_t*>(p.gather_src[src_rank]) + blk * block_bytes;
         const int row_block = src_rank * per_shard + blk;
         uint8_t* dst = static_cast<uint8_t*>(p.gather_dst) + row_block * block_bytes;
-        for (size_t off = lo + lane * 16; off < hi; off += 8 * 512) {
-          uint4 v[8];
+        for (size_t off = lo + lane * 16; off < hi; off += GATHER_LOADS * 512) {
+          uint4 v[GATHER_LOADS];
 #pragma unroll
-          for (int u = 0; u < 8; ++u)
+          for (int u = 0; u < GATHER_LOADS; ++u)
             if (off + u * 512 < hi) v[u] = __ldcg(reinterpret_cast<const uint4*>(src + off + u * 512));
 #pragma unroll
-          for (int u = 0; u < 8; ++u)
+          for (int u = 0; u < GATHER_LOADS; ++u)
             if (off + u * 512 < hi) *reinterpret_cast<uint4*>(dst + off + u * 512) = v[u];
         }
         __threadfence();
