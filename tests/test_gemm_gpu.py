@@ -240,3 +240,16 @@ def test_bad_arguments_are_errors():
                  torch.zeros(100, 128, dtype=torch.bfloat16, device="cuda"), 128, 128, 100)
     with pytest.raises(ValueError, match="bfloat16"):
         ops.gemm(x.float(), x, 128, 128, 128)
+    with pytest.raises(NativeError, match="mode must be 0"):
+        ops.set_gemm_pair_mode(5)
+    # The one-launch all-gather matmul checks its shapes before anything runs.
+    tables = torch.zeros(4, dtype=torch.int32, device="cuda")
+    arrivals = torch.zeros(2, dtype=torch.int32, device="cuda")
+    big = torch.zeros(512, 256, dtype=torch.bfloat16, device="cuda")
+    out = torch.zeros(512, 256, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(NativeError, match="tile table must list every tile"):
+        ops.all_gather_gemm(x, [None, x], big, x, out, 0, 256, 256, 256, tables[:3], tables[:3], arrivals, 1)
+    with pytest.raises(NativeError, match="multiples of 256"):
+        ops.all_gather_gemm(x, [None, x], big, x, out, 0, 128, 256, 256, tables, tables, arrivals, 1)
+    with pytest.raises(NativeError, match="epoch"):
+        ops.all_gather_gemm(x, [None, x], big, x, out, 0, 256, 256, 256, tables[:2], tables[:2], arrivals, 0)
