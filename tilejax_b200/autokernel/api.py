@@ -360,8 +360,6 @@ def _lower(plan: Plan, config: Config) -> tuple[str, Callable[..., Any]]:
 
     p, name = plan.params, plan.nest.name
     sch = p["schedule"]
-    header = f"# {name}: {config.tunable if config.tunable is not None else 'no tunable'}; {config.pipeline}\n".replace(
-        f"{config.tunable}", str(Config(config.tunable, config.pipeline)).rsplit(", ", 1)[0] if config.tunable is not None else "")
     header = f"# {name}: {str(config).rsplit(', ', 1)[0] if config.tunable is not None else ''}; {config.pipeline}\n"
     if plan.family == "gemm":
         import torch
