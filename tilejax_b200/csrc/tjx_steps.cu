@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(STEPS_THREADS) build_steps_kernel(Run mask, in
     if (lane == 31) s_warp_sums[warp] = incl;
     __syncthreads();
     if (warp == 0) {
-      int w = s_warp_sums[lane];
+      int w = lane < n_warps ? s_warp_sums[lane] : 0;
       for (int d = 1; d < 32; d <<= 1) {
         const int o = __shfl_up_sync(0xFFFFFFFFu, w, d);
         if (lane >= d) w += o;
