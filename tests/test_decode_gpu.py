@@ -121,6 +121,19 @@ def test_too_many_query_rows_per_kv_head_is_an_error():
         run_decode(q5, kp, vp, bt, lengths)
 
 
+def test_long_sequences_merge_more_than_32_partials():
+    # 512 pages per sequence = 43 chunks of 12 steps: the merge walks its partials 32 at a time.
+    B, S, page = 2, 8192, 16
+    k, v = rand_bf16((B, S, 128), 1), rand_bf16((B, S, 128), 2)
+    q = rand_bf16((B, 1, 2, 128), 3, 128**-0.5)
+    lengths = np.array([8192, 7000], np.int32)
+    ident = np.arange(B * S // page, dtype=np.int32).reshape(B, S // page)
+    kp, vp = oracle.to_pages(k, ident), oracle.to_pages(v, ident)
+    got = run_decode(q, kp, vp, ident, lengths)
+    want = oracle.paged_gqa_decode_f64(q, kp, vp, ident, lengths)
+    assert np.abs(f64(got) - want).max() <= 2e-2 * np.abs(want).max()
+
+
 def test_all_sequences_empty():
     q, kp, vp, bt, lengths = synthetic.decode_inputs(5, 8, 2, 128, 16, 4, 20)
     lengths[:] = 0
