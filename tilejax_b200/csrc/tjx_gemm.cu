@@ -70,8 +70,11 @@ struct Item {
 template <int BMT, int BN>
 __device__ __forceinline__ Item decode_item(const GemmParams& p, int w) {
   const int per = p.sub_m * p.sub_n;
-  const int t = w / per, r = w - t * per;
+  const int tw = w / per, r = w - tw * per;
   const int sm = r / p.sub_n, sn = r - sm * p.sub_n;
+  // The fills come first: only the epilogue warps touch them, so their stores to HBM run while the TMA and MMA
+  // warps are already deep into the first tiles that compute (whose order nobody can observe either).
+  const int t = tw >= p.n_fills ? tw - p.n_fills : p.n_tiles + tw;
   int ti, tj;
   bool fill = false;
   if (t < p.n_tiles) {
