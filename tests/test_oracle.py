@@ -216,3 +216,44 @@ def test_compare_rule():
         oracle.compare("x", np.array([4.0, np.nan, 100.0], np.float32).astype(BF16), want)
     with pytest.raises(AssertionError):
         oracle.compare("i", np.array([1, 2]), np.array([1, 3]))
+
+
+def test_committed_known_answers():
+    # tests/golden/known_answers.json (written by tests/golden/make_golden.py from the reference's tests and
+    # sources): the oracle and the host schedules reproduce every integer in it.
+    import json
+    from pathlib import Path
+
+    from tilejax_b200 import schedule
+
+    known = json.loads((Path(__file__).resolve().parent / "golden" / "known_answers.json").read_text())
+    d = known["device_step_tables_lengths_0_1_300_512_block_128"]
+    tile, code, count = oracle.device_step_tables(oracle.lengths_runs(d["lengths"], d["blocks"], 0, d["block_size"]))
+    assert (tile.tolist(), code.tolist(), int(count[0])) == (d["step_tile"], d["step_code"], d["step_count"])
+    a = known["causal_attention_S2048_blocks_512"]
+    sch = schedule.causal_attention_schedule(4, 16, a["S"], a["block_q"], a["block_kv"])
+    assert sch.tables["step_tile"].tolist() == a["step_tile"] and sch.tables["step_code"].tolist() == a["step_code"]
+    assert (sch.tiles, sch.steps) == (a["tiles"], a["steps"])
+    tile, code = oracle.attention_step_tables(a["S"], a["block_q"], a["block_kv"])
+    assert (tile.tolist(), code.tolist()) == (a["step_tile"], a["step_code"])
+    b = known["causal_attention_2_4_512_128_blocks_128"]
+    sch = schedule.causal_attention_schedule(2, 4, 512, 128, 128)
+    assert (sch.steps, sch.repeats, len(sch.tables["step_tile"])) == (b["steps"], b["repeats"], b["pattern_steps"])
+    m = known["matmul_256x384x256_tiles_128"]
+    sch = schedule.matmul_schedule(256, 256, 384, 128, 128, 128)
+    assert (sch.steps, sch.tiles, sch.total_tiles) == (m["steps"], m["tiles"], m["total_tiles"])
+    for key, args in (("causal_matmul_512x256x512_tiles_128", (512, 512, 256, 128, 128, 128)),
+                      ("causal_matmul_8192_tiles_512", (8192, 8192, 8192, 512, 512, 512)),
+                      ("causal_matmul_8192_tiles_1024x2048x1024", (8192, 8192, 8192, 1024, 2048, 1024))):
+        c = known[key]
+        sch = schedule.causal_matmul_schedule(*args)
+        assert (sch.tiles, sch.steps) == (c["tiles"], c["steps"])
+        if "fills" in c:
+            assert sch.fills == c["fills"]
+        if "total_tiles" in c:
+            assert sch.total_tiles == c["total_tiles"]
+    r = known["collective_ring_order_8_chips_2_blocks"]
+    for me in range(r["chips"]):
+        i_blk = np.arange(r["chips"] * r["shard_blocks"])
+        want = ((me + 8 - (i_blk >> 1)) % 8) * 2 + (i_blk & 1)
+        np.testing.assert_array_equal(schedule.collective_row_blocks(me, r["chips"], r["shard_blocks"]), want)
