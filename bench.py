@@ -1,15 +1,21 @@
 """Benchmark of the step-loop hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-extras]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-extras] [--only NAME]
 
-Headline workload at every N: the collective matmul of BASELINE config 5 — x [16384 x 8192] bf16 row-sharded over
-the N GPUs, y [8192 x 8192] bf16 on every GPU, each GPU computing all 16384 rows (weak scaling: per-GPU work is
-constant), the all-gather overlapped with the tile compute. At N = 1 that is one dense 16384 x 8192 x 8192 matmul
-through the persistent tcgen05 GEMM. `value` is whole-job TFLOP/s (N x 2 M N K / step time). A step is one pass.
+Headline workload at every N: the collective matmul `all_gather(x) @ y` (examples/collective_matmul.py:44-59) —
+x [16384 x 8192] bf16 row-sharded over the N GPUs, y [8192 x 8192] bf16 on every GPU, each GPU computing all
+16384 rows (weak scaling: per-GPU work is constant), the all-gather overlapped with the tile compute. At N = 1 that
+is one dense 16384 x 8192 x 8192 matmul through the persistent tcgen05 GEMM. `value` is whole-job TFLOP/s
+(N x 2 M N K / step time). A step is one pass.
 
-At N = 1 the line also carries `workloads`: the other BASELINE configs (dense 4096^3 and 8192^3, causal 8192^3 at
-both tilings, causal attention, paged decode), each timed on the device with its own roofline fraction, and
-`cpu_baseline`: the NumPy port of the same loop nest timed on the host cores on a bounded sample.
+After the timed steps (outside every timed region) each rank checks its result: bit-equal to the same GEMM on rows
+gathered beforehand with a plain all-gather, and sampled rows against float64; the line carries the outcome under
+`parity` and the program exits non-zero on a mismatch.
+
+At N = 1 the line also carries `workloads`: the other hot-path configurations (dense 4096^3 and 8192^3, causal
+8192^3 at both tilings, causal attention, paged decode with shared and with distinct pages, MLA decode), each timed
+on the device with its own roofline fractions and its own CPU baseline, and `cpu_baseline`: the NumPy port of the
+headline loop nest timed on the host cores on a bounded sample.
 
 `--impl reference` times the reference's CPU path (the port; the reference itself needs JAX, which is absent) on
 the host cores for the same metric.
@@ -34,11 +40,16 @@ sys.path.insert(0, str(ROOT))
 M_TOTAL, K_DIM, N_DIM = 16384, 8192, 8192
 TILES = (256, 512, 512)  # CollectiveTiles defaults (examples/collective_matmul.py:35-41)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+NOMINAL = {"bf16_tflops": 2250.0, "hbm_gbs": 8000.0}
 CPU_SAMPLE_ROWS = 2048
 
-# DRAM bytes (read + write) per launch of the dominant kernel from an ncu capture of this command's workload
-# (profiles/gemm_pair_kernel_16384x8192x8192.md): dram__bytes_read.sum + dram__bytes_write.sum.
-NCU_TRAFFIC_BYTES = {"gemm_16384x8192x8192": 2.299167e9 + 0.263586e9}
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch of each workload's dominant kernel, from one
+# ncu capture of `python bench.py --only <workload> --steps 1 --warmup 1` (one kernel, one launch,
+# --clock-control none). A workload that has not been captured since its kernel last changed has no entry and
+# reports `traffic: null`.
+NCU_TRAFFIC_BYTES: dict[str, float] = {
+    "gemm_16384x8192x8192": 2.299167e9 + 0.263586e9,
+}
 
 
 def peaks() -> tuple[dict, str]:
@@ -48,11 +59,24 @@ def peaks() -> tuple[dict, str]:
     return FALLBACK_PEAKS, "fallback"
 
 
+def host_threads() -> int:
+    threads = os.cpu_count() or 1
+    try:
+        from threadpoolctl import threadpool_info
+
+        blas = [p["num_threads"] for p in threadpool_info() if p.get("user_api") == "blas"]
+        if blas:
+            threads = max(blas)
+    except Exception:
+        pass
+    return threads
+
+
 # ----------------------------------------------------------------------------------------- clocks
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed regions run."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -94,7 +118,8 @@ class ClockSampler:
                     reasons.add(name)
         busy = [c for c, p in zip(sm, power) if p > 300.0] or sm
         return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(sm_max) if sm_max else None,
-                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+                "power_w_max": max(power) if power else None, "samples": len(sm), "samples_under_load": len(busy),
+                "reasons": sorted(reasons)}
 
 
 # ----------------------------------------------------------------------------------------- helpers
@@ -125,8 +150,8 @@ def device_randn_bf16(shape, seed, device, scale=1.0):
 
 
 def time_device(fn, iters: int, warmup: int, flush=None) -> float:
-    """Mean device time of fn() in ms over `iters` runs, CUDA events on the current stream; `flush()` (an L2
-    flush) runs untimed before each."""
+    """Mean device time of fn() in ms over `iters` runs, each bracketed by CUDA events on the current stream;
+    `flush()` (an L2 flush) runs untimed before each."""
     import torch
 
     for _ in range(warmup):
@@ -145,46 +170,122 @@ def time_device(fn, iters: int, warmup: int, flush=None) -> float:
     return total / iters
 
 
-# ----------------------------------------------------------------------------------------- reference arm
+def time_sustained(fn, seconds: float, ms_hint: float) -> float:
+    """Mean device time of fn() in ms over a back-to-back loop of at least `seconds`: the figure for a kernel under
+    the power cap, next to the isolated-launch one."""
+    import torch
+
+    iters = max(10, int(seconds * 1e3 / max(ms_hint, 1e-3)))
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(iters):
+        fn()
+    end.record()
+    end.synchronize()
+    return start.elapsed_time(end) / iters
+
+
+def tensor_roofline(tflops: float, pk: dict, pk_kind: str, sustained_tflops: float | None = None,
+                    traffic: float | None = None, **more) -> dict:
+    """The roofline record of a tensor-bound kernel: `frac` is against the burst cuBLAS figure (the kernel was timed
+    in isolated launches); `frac_sustained` compares the back-to-back figure with the sustained cuBLAS one."""
+    r = {"bound": "tensor", "achieved": tflops, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+         "frac": tflops / pk["bf16_tflops"], "frac_burst": tflops / pk["bf16_tflops"],
+         "peak_kind": f"{pk_kind} cuBLAS bf16, burst", "peak_sustained": pk["bf16_tflops_sustained"],
+         "achieved_sustained": sustained_tflops,
+         "frac_sustained": None if sustained_tflops is None else sustained_tflops / pk["bf16_tflops_sustained"],
+         "nominal_frac": tflops / NOMINAL["bf16_tflops"], "traffic": traffic}
+    r.update(more)
+    return r
+
+
+def hbm_roofline(gbs: float, pk: dict, pk_kind: str, algorithmic_bytes: float, ms: float,
+                 traffic: float | None = None) -> dict:
+    """The roofline record of an HBM-bound kernel. `frac` uses the algorithmic bytes; where an ncu capture gave the
+    DRAM bytes of the launch, `frac_dram` = those bytes / time / peak says how much of the figure L2 hits supply."""
+    r = {"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
+         "peak_kind": f"{pk_kind} copy bandwidth", "nominal_frac": gbs / NOMINAL["hbm_gbs"],
+         "algorithmic_bytes": algorithmic_bytes, "traffic": traffic,
+         "frac_dram": None if traffic is None else traffic / ms / 1e6 / pk["hbm_gbs"]}
+    return r
+
+
+# ----------------------------------------------------------------------------------------- CPU baselines
+
+
+def _timed(fn, repeats: int, warmup: int) -> float:
+    for _ in range(warmup):
+        fn()
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        fn()
+        times.append(time.perf_counter() - t0)
+    return sum(times) / len(times)
 
 
 def cpu_port_tflops(rows: int, repeats: int, warmup: int) -> tuple[float, float, int, str]:
     """The NumPy port of the matmul loop nest (oracle.matmul_ref) on `rows` rows of the workload's x against the
     full y, on the host cores. Returns (TFLOP/s, seconds per pass, threads, sample description)."""
-    import numpy as np
-
     import oracle
     from tilejax_b200 import synthetic
 
     x = synthetic.normal_bf16((rows, K_DIM), 0)
     y = synthetic.normal_bf16((K_DIM, N_DIM), 1)
-    for _ in range(warmup):
-        oracle.matmul_ref(x, y, *TILES)
-    times = []
-    for _ in range(repeats):
-        t0 = time.perf_counter()
-        oracle.matmul_ref(x, y, *TILES)
-        times.append(time.perf_counter() - t0)
-    sec = float(np.mean(times))
-    threads = os.cpu_count() or 1
-    try:
-        from threadpoolctl import threadpool_info
-
-        blas = [p["num_threads"] for p in threadpool_info() if p.get("user_api") == "blas"]
-        if blas:
-            threads = max(blas)
-    except Exception:
-        pass
+    sec = _timed(lambda: oracle.matmul_ref(x, y, *TILES), repeats, warmup)
     flops = 2.0 * rows * K_DIM * N_DIM
     sample = (f"{rows} of {M_TOTAL} rows of x against the full y [{K_DIM}x{N_DIM}], tiles {TILES}, "
               f"NumPy f32 BLAS on bf16-rounded inputs, mean of {repeats} passes")
-    return flops / sec / 1e12, sec, threads, sample
+    return flops / sec / 1e12, sec, host_threads(), sample
+
+
+def cpu_baselines_for_workloads() -> dict:
+    """The NumPy port of each side workload's loop nest on a bounded sample (a second or two each), on the host
+    cores: {workload prefix: cpu_baseline record}."""
+    import numpy as np
+
+    import oracle
+    from tilejax_b200 import synthetic
+
+    threads = host_threads()
+    out = {}
+    n = 2048
+    x, y = synthetic.normal_bf16((n, n), 0), synthetic.normal_bf16((n, n), 1)
+    sec = _timed(lambda: oracle.matmul_ref(x, y, 512, 512, 512), 2, 1)
+    out["dense_matmul"] = {"value": 2.0 * n**3 / sec / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                           "sample": f"a {n}^3 product (tiles 512^3) of the same loop nest, NumPy f32 BLAS, mean of 2"}
+    sec = _timed(lambda: oracle.causal_matmul_ref(x, y, 512, 512, 512), 2, 1)
+    out["causal_matmul"] = {"value": float(n) * n * (n + 1) / sec / 1e12, "unit": "TFLOP/s", "cores": threads,
+                            "kind": "port", "sample": f"tril of a {n}^3 product (tiles 512^3), algorithmic flops "
+                                                      "K*M*(M+1), NumPy f32 BLAS, mean of 2"}
+    B, H, S, D = 1, 2, 2048, 128
+    q, k, v = synthetic.attention_inputs(B, H, S, D)
+    sec = _timed(lambda: oracle.causal_attention_ref(q, k, v, 512, 512), 1, 1)
+    out["causal_attention"] = {"value": 4.0 * B * H * D * S * (S + 1) / 2 / sec / 1e12, "unit": "TFLOP/s",
+                               "cores": threads, "kind": "port",
+                               "sample": f"{H} of the 64 (batch, head) pairs at S {S}, blocks 512 x 512, one pass"}
+    Bd = 8
+    qd, kp, vp, bt, lengths = synthetic.decode_inputs(Bd, 32, 8, 128, 16, 256, 1024)
+    sec = _timed(lambda: oracle.paged_gqa_decode_ref(qd, kp, vp, bt, lengths), 1, 0)
+    out["paged_gqa_decode"] = {"value": float(np.sum(lengths)) * 4096.0 / sec / 1e9, "unit": "GB/s", "cores": threads,
+                               "kind": "port", "sample": f"{Bd} of the 64 sequences (lengths uniform in 1..4096, "
+                                                         "16-token pages), one pass of the NumPy loop nest"}
+    return out
 
 
 def reference_arm(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torch.distributed.run sets OMP_NUM_THREADS=1 for its workers; the reference arm uses every host core.
+    cores = os.cpu_count() or 1
+    try:
+        from threadpoolctl import threadpool_limits
+
+        threadpool_limits(limits=cores)
+    except Exception:
+        pass
     tflops, sec, threads, sample = cpu_port_tflops(CPU_SAMPLE_ROWS, max(args.steps, 1), max(args.warmup, 1))
     line = {
         "impl": "reference",
@@ -193,7 +294,8 @@ def reference_arm(args) -> None:
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": workload_name(args.gpus), "tiles": list(TILES),
                    "note": "reference CPU path: NumPy port of examples/collective_matmul.py's loop nest "
-                           "(the reference needs JAX, which is not installed); each step is a bounded sample"},
+                           "(the reference needs JAX, which is not installed); each step is a bounded sample; "
+                           "one host runs it whatever N is"},
         "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -202,33 +304,58 @@ def reference_arm(args) -> None:
 
 def workload_name(n: int) -> str:
     return (f"collective_matmul: all_gather(x[{M_TOTAL}x{K_DIM}] row-sharded over {n} GPU(s)) @ y[{K_DIM}x{N_DIM}] "
-            f"replicated, bf16, f32 accumulation (BASELINE config 5)")
+            f"replicated, bf16, f32 accumulation")
 
 
 # ----------------------------------------------------------------------------------------- extra workloads
 
 
-def extra_workloads(device, pk: dict, pk_kind: str, only: str | None = None, iters: int = 10, warm: int = 3) -> dict:
-    """The other BASELINE configs at one GPU, device-timed with an L2 flush before every run. `only` keeps the
-    workloads whose name contains it (for profiling one kernel with few launches)."""
+def extra_workloads(device, pk: dict, pk_kind: str, only: str | None = None, iters: int = 10, warm: int = 3,
+                    quick: bool = False) -> dict:
+    """The other hot-path configurations at one GPU, device-timed with an L2 flush before every run. `only` keeps
+    the workloads whose name contains it and `quick` drops the sustained loops and the front-end timings (for
+    profiling one kernel with few launches)."""
     import numpy as np
     import torch
 
     from tilejax_b200 import ops, synthetic
+    from tilejax_b200.autokernel import kernels
 
     flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=device)
-    flush = lambda: flush_buf.zero_()  # noqa: E731
-    tf_peak, hbm_peak = pk["bf16_tflops"], pk["hbm_gbs"]
+    flush_mode = os.environ.get("TJX_FLUSH", "write_read")
+
+    def flush():
+        # Write a buffer larger than L2, then read it back: the write evicts every line of the workload, the read
+        # sweep pushes the written (dirty) lines out to HBM, so the timed kernel starts on a cold L2 that owes HBM no
+        # write-backs. (After the write alone, up to 126 MB of dirty lines are written back during the timed kernel,
+        # which costs an HBM-bound kernel a fifth of its bandwidth.)
+        if flush_mode == "none":
+            return
+        flush_buf.zero_()
+        if flush_mode == "write_read":
+            flush_buf.view(torch.int32).sum()
+
     out = {}
     want = lambda name: only is None or only in name  # noqa: E731
 
-    def tensor_entry(name, ms, flops, extra=None):
+    def tensor_entry(name, ms, flops, fn=None, extra=None, sustained=False):
         tf = flops / ms / 1e9
+        sustained_tf = None
+        if sustained and not quick and fn is not None:
+            sustained_tf = flops / time_sustained(fn, 1.2, ms) / 1e9
         out[name] = {"ms": ms, "value": tf, "unit": "TFLOP/s",
-                     "roofline": {"bound": "tensor", "achieved": tf, "peak": tf_peak, "unit": "TFLOP/s",
-                                  "frac": tf / tf_peak, "peak_kind": f"{pk_kind} burst", "traffic": None}}
+                     "roofline": tensor_roofline(tf, pk, pk_kind, sustained_tf, NCU_TRAFFIC_BYTES.get(name))}
         if extra:
             out[name].update(extra)
+
+    def frontend_ms(call):
+        """The same launch through `@autokernel.kernel` (parse, plan and tables cached after the first call)."""
+        if quick:
+            return None
+        try:
+            return time_device(call, max(3, iters // 2), 2, flush)
+        except Exception as e:  # report, do not hide
+            return f"error: {str(e)[:160]}"
 
     for n in (4096, 8192):
         if not (want(f"dense_matmul_{n}") or (n == 8192 and want("causal_matmul"))):
@@ -236,31 +363,41 @@ def extra_workloads(device, pk: dict, pk_kind: str, only: str | None = None, ite
         x = device_randn_bf16((n, n), 0, device)
         y = device_randn_bf16((n, n), 1, device)
         if want(f"dense_matmul_{n}"):
-            ms = time_device(lambda: ops.matmul(x, y, 512, 512, 512), iters, warm, flush)
-            tensor_entry(f"dense_matmul_{n}_tiles512", ms, 2.0 * n**3)
+            fn = lambda: ops.matmul(x, y, 512, 512, 512)  # noqa: E731
+            ms = time_device(fn, iters, warm, flush)
+            tensor_entry(f"dense_matmul_{n}_tiles512", ms, 2.0 * n**3, fn, sustained=True, extra={
+                "via_autokernel_ms": frontend_ms(lambda: kernels.matmul(x, y, kernels.MatmulTiles()))})
         if n == 8192:
             for tiles in ((512, 512, 512), (1024, 2048, 1024)):
                 name = f"causal_matmul_8192_tiles{tiles[0]}x{tiles[1]}x{tiles[2]}"
                 if not want(name):
                     continue
-                ms = time_device(lambda: ops.causal_matmul(x, y, *tiles), iters, warm, flush)
-                tensor_entry(name, ms, float(n) * n * (n + 1),
-                             {"dense_equivalent_tflops": 2.0 * n**3 / ms / 1e9,
-                              "algorithmic_flops": "K*M*(M+1)"})
+                fn = lambda: ops.causal_matmul(x, y, *tiles)  # noqa: E731
+                ms = time_device(fn, iters, warm, flush)
+                dense_ms = out.get("dense_matmul_8192_tiles512", {}).get("ms")
+                tensor_entry(name, ms, float(n) * n * (n + 1), fn, extra={
+                    "dense_equivalent_tflops": 2.0 * n**3 / ms / 1e9, "algorithmic_flops": "K*M*(M+1)",
+                    "time_vs_dense": None if dense_ms is None else ms / dense_ms,
+                    "via_autokernel_ms": frontend_ms(
+                        lambda: kernels.causal_matmul(x, y, kernels.MatmulTiles(*tiles)))})
         del x, y
 
     for (B, H, S, D) in ((4, 16, 2048, 128), (1, 16, 4096, 128)):
         if not want(f"causal_attention_B{B}"):
             continue
+        name = f"causal_attention_B{B}_H{H}_S{S}_D{D}_blocks512"
         try:
             q = device_randn_bf16((B, H, S, D), 0, device, D**-0.5)
             k = device_randn_bf16((B, H, S, D), 1, device)
             v = device_randn_bf16((B, H, S, D), 2, device)
-            ms = time_device(lambda: ops.causal_attention(q, k, v, 512, 512), iters, warm, flush)
-            tensor_entry(f"causal_attention_B{B}_H{H}_S{S}_D{D}_blocks512", ms, 4.0 * B * H * D * S * (S + 1) / 2,
-                         {"algorithmic_flops": "4*B*H*D*S*(S+1)/2"})
+            fn = lambda: ops.causal_attention(q, k, v, 512, 512)  # noqa: E731
+            ms = time_device(fn, iters, warm, flush)
+            tensor_entry(name, ms, 4.0 * B * H * D * S * (S + 1) / 2, fn, extra={
+                "algorithmic_flops": "4*B*H*D*S*(S+1)/2",
+                "via_autokernel_ms": frontend_ms(
+                    lambda: kernels.causal_attention(q, k, v, kernels.AttentionBlocks(512, 512)))})
         except Exception as e:  # not built yet, or failed: report, do not hide
-            out[f"causal_attention_B{B}_H{H}_S{S}_D{D}_blocks512"] = {"error": str(e)[:200]}
+            out[name] = {"error": str(e)[:200]}
 
     if want("mla_decode"):
         # The reference's MLA benchmark shape (benchmarks/decode.py:152-173): batch 32, contexts around 2048 of a
@@ -283,34 +420,83 @@ def extra_workloads(device, pk: dict, pk_kind: str, only: str | None = None, ite
             tokens = float(lens.sum())
             nbytes = tokens * 576 * 2  # what the math reads: 512 latents + 64 RoPE columns per position
             gbs = nbytes / ms / 1e6
-            out[f"mla_decode_B{B}_H{H}_ctx1024to3072"] = {
-                "ms": ms, "value": gbs, "unit": "GB/s", "algorithmic_bytes": nbytes,
+            name = f"mla_decode_B{B}_H{H}_ctx1024to3072"
+            out[name] = {
+                "ms": ms, "value": gbs, "unit": "GB/s",
                 "tflops": tokens * H * (2 * 576 + 2 * 512) / ms / 1e9,
                 "includes": "step-table kernel + decode (the merge of partials is fused into it)",
-                "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak,
-                             "peak_kind": pk_kind, "traffic": None}}
+                "roofline": hbm_roofline(gbs, pk, pk_kind, nbytes, ms, NCU_TRAFFIC_BYTES.get(name))}
         except Exception as e:  # report, do not hide
             out["mla_decode"] = {"error": str(e)[:200]}
 
-    if not want("paged_gqa_decode"):
-        ops.device_status()
-        return out
-    q, kp, vp, bt, lengths = synthetic.decode_inputs(64, 32, 8, 128, 16, 256, 8192)
-    qd, kd, vd, btd, ld = (to_device(a, device) for a in (q, kp, vp, bt, lengths))
-    bufs = ops.DecodeBuffers(64, 32, 128, 256, device)
-    od = torch.empty_like(qd)
-    ms = time_device(lambda: ops.paged_gqa_decode(qd, kd, vd, btd, ld, out=od, buffers=bufs), 2 * iters, warm, flush)
-    nbytes = float(lengths.sum()) * 4096.0
-    gbs = nbytes / ms / 1e6
-    out["paged_gqa_decode_B64_H32_Hkv8_D128_page16"] = {
-        "ms": ms, "value": gbs, "unit": "GB/s", "algorithmic_bytes": nbytes, "includes": "step-table kernel + decode (the merge of partials is fused into it)",
-        "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak,
-                     "peak_kind": pk_kind, "traffic": None}}
+    # Paged GQA decode (examples/decode.py:199-223) on batch 64, 32 / 8 heads, 16-token pages, lengths uniform in
+    # 1..4096: once with the block tables drawn with replacement from a pool of 8192 pages (sequences then share
+    # pages, which L2 serves), once with a page of its own for every slot (examples/kv_cache.py:54-60: a permutation
+    # of a pool of 16384), where every byte comes from HBM.
+    for variant, num_pages, distinct in (("_shared_pages", 8192, False), ("_distinct_pages", 16384, True)):
+        name = f"paged_gqa_decode_B64_H32_Hkv8_D128_page16{variant}"
+        if not want(name):
+            continue
+        rng = np.random.default_rng(0)
+        lengths = rng.integers(1, 4097, 64).astype(np.int32)
+        if distinct:
+            bt = rng.permutation(num_pages)[: 64 * 256].reshape(64, 256).astype(np.int32)
+        else:
+            bt = rng.integers(0, num_pages, (64, 256)).astype(np.int32)
+        kd = device_randn_bf16((num_pages, 16, 1024), 1, device)
+        vd = device_randn_bf16((num_pages, 16, 1024), 2, device)
+        qd = device_randn_bf16((64, 1, 32, 128), 3, device, 128**-0.5)
+        btd, ld = to_device(bt, device), to_device(lengths, device)
+        bufs = ops.DecodeBuffers(64, 32, 128, 256, device)
+        od = torch.empty_like(qd)
+        ms = time_device(lambda: ops.paged_gqa_decode(qd, kd, vd, btd, ld, out=od, buffers=bufs), 2 * iters, warm,
+                         flush)
+        nbytes = float(lengths.sum()) * 4096.0
+        gbs = nbytes / ms / 1e6
+        out[name] = {
+            "ms": ms, "value": gbs, "unit": "GB/s",
+            "includes": "step-table kernel + decode (the merge of partials is fused into it)",
+            "pages": "one page per (sequence, slot): no page is read twice" if distinct else
+                     "block tables drawn with replacement: about 29 % of the page reads hit L2",
+            "via_autokernel_ms": frontend_ms(lambda: kernels.paged_gqa_decode(qd, kd, vd, btd, ld)),
+            "roofline": hbm_roofline(gbs, pk, pk_kind, nbytes, ms, NCU_TRAFFIC_BYTES.get(name))}
+        del kd, vd
     ops.device_status()
     return out
 
 
 # ----------------------------------------------------------------------------------------- main arm
+
+
+def check_parity(op, x, y, world: int, rank: int, device) -> dict:
+    """Outside every timed region: this rank's result against the same GEMM on rows gathered beforehand (bit-equal:
+    same kernel, same order of summation) and sampled rows against float64. Reduced over the ranks."""
+    import torch
+    import torch.distributed as dist
+
+    from tilejax_b200 import ops
+
+    out = op(x, y).clone()
+    torch.cuda.synchronize()
+    if world > 1:
+        parts = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(parts, x)
+        xs = torch.cat(parts)
+    else:
+        xs = x
+    want = ops.gemm(xs, y, op.tm, op.tn, op.tk)
+    bit_equal = bool(torch.equal(out, want))
+    rows = torch.arange(rank % 7, xs.shape[0], 521, device=device)
+    exact = xs[rows].double() @ y.double()
+    rel = float(((out[rows].double() - exact).abs().max() / exact.abs().max()).item())
+    status = ops.device_status()
+    flags = torch.tensor([0.0 if bit_equal else 1.0, rel, float(status)], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(flags, op=dist.ReduceOp.MAX)
+    ok = flags[0].item() == 0.0 and flags[1].item() <= 2e-2 and flags[2].item() == 0.0
+    return {"bit_equal_to_gather_then_gemm": flags[0].item() == 0.0, "sampled_f64_max_rel": flags[1].item(),
+            "tolerance": "2e-2 of the largest value (bf16 output)", "rows_sampled_per_rank": int(rows.numel()),
+            "device_status": int(flags[2].item()), "ranks_checked": world, "ok": ok}
 
 
 def main() -> None:
@@ -319,7 +505,7 @@ def main() -> None:
     parser.add_argument("--steps", type=int, default=100)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--no-extras", action="store_true", help="skip the other single-GPU workloads and the CPU baseline")
+    parser.add_argument("--no-extras", action="store_true", help="skip the other single-GPU workloads and the CPU baselines")
     parser.add_argument("--only", default=None, help="run only the single-GPU workloads whose name contains this "
                         "(dense_matmul_8192, causal_matmul, causal_attention_B4, paged_gqa_decode, ...) for "
                         "--steps runs after --warmup: a short command to profile one kernel")
@@ -327,7 +513,7 @@ def main() -> None:
     if args.impl == "reference":
         reference_arm(args)
         return
-    if os.environ.get("TJX_GEMM_PAIRS") is not None:  # A/B switch: 0 = one MMA per SM instead of one per pair of SMs
+    if os.environ.get("TJX_GEMM_PAIRS") is not None:  # A/B switch: see tjx_gemm_set_pair_mode
         from tilejax_b200 import ops as _ops
 
         _ops.set_gemm_pair_mode(int(os.environ["TJX_GEMM_PAIRS"]))
@@ -337,7 +523,7 @@ def main() -> None:
         torch.cuda.set_device(0)
         pk, pk_kind = peaks()
         print(json.dumps(extra_workloads(torch.device("cuda", 0), pk, pk_kind, args.only, max(args.steps, 1),
-                                         max(args.warmup, 0))), flush=True)
+                                         max(args.warmup, 0), quick=True)), flush=True)
         return
     args.warmup = max(args.warmup, 3)
 
@@ -354,6 +540,7 @@ def main() -> None:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run for N > 1")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(device).uuid).replace("GPU-", "")) if rank == 0 else None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
@@ -362,7 +549,7 @@ def main() -> None:
     pk, pk_kind = peaks()
 
     m = M_TOTAL // world
-    # Seeded synthetic operands: this rank's rows of x (seed 0 + rank), y (seed 1) identical on every rank.
+    # Seeded synthetic operands: this rank's rows of x (seed 1000 + rank), y (seed 1) identical on every rank.
     x_host = device_randn_bf16((m, K_DIM), 1000 + rank, device).cpu().pin_memory()
     y_host = device_randn_bf16((K_DIM, N_DIM), 1, device).cpu().pin_memory()
     x = x_host.to(device)
@@ -379,7 +566,6 @@ def main() -> None:
         torch.cuda.synchronize()
 
     # ---- device-resident timing
-    sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(device).uuid).replace("GPU-", "")) if rank == 0 else None
     for _ in range(args.warmup):
         op(x, y)
     barrier()
@@ -412,14 +598,25 @@ def main() -> None:
         dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
     ms_per_step = elapsed.item() / args.steps
 
-    # ---- the dominant kernel alone (its launches, timed on their stream): the roofline's numerator
-    gemm_ms = time_device(lambda: ops.gemm(op.exchange.xs, y, op.tm, op.tn, op.tk, out=op.out), args.steps, 1)
+    # ---- parity of what was just timed (not timed itself)
+    parity = check_parity(op, x, y, world, rank, device)
+    barrier()
+
+    # ---- the dominant kernel alone, on its stream: isolated launches (the roofline's numerator, against the burst
+    # peak) and a back-to-back loop of more than a second (against the sustained peak)
+    alone = lambda: ops.gemm(op.exchange.xs, y, op.tm, op.tn, op.tk, out=op.out)  # noqa: E731
+    gemm_ms = time_device(alone, min(max(args.steps, 5), 20), 1)
+    gemm_sustained_ms = time_sustained(alone, 1.2, gemm_ms)
     ops.device_status()
+    barrier()
 
     # ---- end to end: host buffers in, host result out, copies inside the timed region
+    own_rows_only = world > 1
+
     def e2e_step():
-        # Host shard and weights in, host result out: copies, GEMMs and copies back pipelined on three streams.
-        op.from_host(x_host, y_host, out_host)
+        # Host shard and weights in, host result out: copies, GEMMs and copies back pipelined on three streams. With
+        # several GPUs every rank computes the whole (replicated) result and hands the host its own rows of it.
+        op.from_host(x_host, y_host, out_host, copy_back="own" if own_rows_only else "all")
         torch.cuda.current_stream().wait_event(op.host_done)
 
     for _ in range(2):
@@ -440,12 +637,6 @@ def main() -> None:
     flops_per_gpu = 2.0 * M_TOTAL * K_DIM * N_DIM
     value = world * flops_per_gpu / ms_per_step / 1e9
     gemm_tflops = flops_per_gpu / gemm_ms / 1e9
-    # The burst figure for a kernel that ran at boost clocks, the sustained one when the run was long enough for
-    # the power cap to pull the SM clock down (as the peak measurement's own 4 s loop was).
-    throttled = bool(clocks and clocks.get("sm_mhz") and clocks.get("sm_max_mhz")
-                     and clocks["sm_mhz"] < 0.85 * clocks["sm_max_mhz"])
-    long_run = gemm_ms * args.steps > 1000.0 or throttled
-    peak = pk["bf16_tflops_sustained"] if long_run else pk["bf16_tflops"]
     line = {
         "metric": "bf16_matmul_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
@@ -457,27 +648,35 @@ def main() -> None:
                    if op.transport == "fused" else
                    f"{world - 1} rounds on a second stream, transport {op.transport}, {len(op.groups)} GEMM launches"},
         "per_gpu_tflops": value / world,
+        "parity": parity,
         "clocks": clocks,
         "e2e": {"value": world * flops_per_gpu / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": x_host.numel() * 2 + y_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2,
-                "api": "tilejax_b200.collective.AllGatherMatmul.from_host with pinned host x, y and out"},
+                "h2d_bytes_per_step": x_host.numel() * 2 + y_host.numel() * 2,
+                "d2h_bytes_per_step": (m if own_rows_only else M_TOTAL) * N_DIM * 2,
+                "bytes_are": "per rank",
+                "api": "tilejax_b200.collective.AllGatherMatmul.from_host with pinned host x, y and out"
+                       + ("; each rank returns its own rows of the replicated result" if own_rows_only else "")},
         # Kernels of this library launched inside the timed region of `value`: GEMM launches per step x steps.
         "gpu_launches": args.steps * (1 if world == 1 or op.transport == "fused" else len(op.groups)),
-        "roofline": {"bound": "tensor", "kernel": "gemm_pair_kernel<3,2>", "achieved": gemm_tflops, "peak": peak,
-                     "unit": "TFLOP/s", "frac": gemm_tflops / peak,
-                     "peak_kind": f"{pk_kind} cuBLAS bf16, {'sustained' if long_run else 'burst'}",
-                     "ms_per_launch": gemm_ms, "flops_per_launch": flops_per_gpu,
-                     "nominal_frac": gemm_tflops / 2250.0,
-                     "traffic": NCU_TRAFFIC_BYTES["gemm_16384x8192x8192"]},
+        "roofline": tensor_roofline(
+            gemm_tflops, pk, pk_kind, flops_per_gpu / gemm_sustained_ms / 1e9,
+            NCU_TRAFFIC_BYTES["gemm_16384x8192x8192"], kernel="gemm_pair_kernel<256,3,2>", ms_per_launch=gemm_ms,
+            ms_per_launch_sustained=gemm_sustained_ms, flops_per_launch=flops_per_gpu),
     }
     if world == 1 and not args.no_extras:
         line["workloads"] = extra_workloads(device, pk, pk_kind)
         tflops, sec, threads, sample = cpu_port_tflops(CPU_SAMPLE_ROWS, 3, 1)
         line["cpu_baseline"] = {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample}
+        for prefix, record in cpu_baselines_for_workloads().items():
+            for name, entry in line["workloads"].items():
+                if name.startswith(prefix) and isinstance(entry, dict) and "error" not in entry:
+                    entry["cpu_baseline"] = record
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+    if not parity["ok"]:
+        raise SystemExit("parity check failed: " + json.dumps(parity))
 
 
 if __name__ == "__main__":

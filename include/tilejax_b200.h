@@ -39,6 +39,13 @@ const char* tjx_last_error(void);
  * and gives up through this word instead of hanging. */
 int tjx_device_status(tjx_stream_t stream, int* code);
 
+/* Sets, for the current device, how long a device-side wait (on a ring slot, an accumulator, a peer's rows) may
+ * last before the kernel gives up, records its code in the status word and returns: 1000 .. 10,000,000
+ * microseconds, 2 s unless changed. Synchronises the device. Replaces nothing in the reference (see
+ * tjx_device_status); a caller that prefers a failed step to a two-second stall lowers it, and the tests use a
+ * short limit to take the give-up path on purpose. */
+int tjx_set_wait_limit_us(int microseconds);
+
 /* The device step-table builder for runtime masks of the form `value(k) >= lengths[tile_value[t]]: continue`
  * with value(k) = value0 + k * value_step — `paged_gqa_decode` (examples/decode.py:214, value = p * page_size)
  * and `gqa_decode` (examples/decode.py:188, value = j).
@@ -86,11 +93,11 @@ int tjx_gemm_bf16(const void* x, const void* y, void* out, int M, int N, int K, 
  * compute units on a TPU but do on a GPU — so that those kernels find free SMs instead of delaying GEMM CTAs. */
 int tjx_gemm_set_cta_limit(int max_ctas);
 
-/* Chooses how tjx_gemm_bf16 maps CTA tiles to SMs for calls from this thread: 1 (default) = one MMA per pair of
- * SMs (256 x 256 pieces, each SM staging half of y's columns) whenever tm % 256 == 0, tn % 256 == 0 and stages
- * == 0; 0 = always one 128 x 256 (or 128 x 128) piece per SM. Results are bit-identical: both modes sum K in
- * the same order. The counterpart in the reference is the choice of tile sizes left to its tuner
- * (src/autokernel/tune.py:246-300): a launch-shape knob with no effect on values. */
+/* Chooses how tjx_gemm_bf16 maps CTA tiles to SMs for calls from this thread: 1 (default; 3 is the same) = one MMA
+ * per pair of SMs, in pieces of 256 x 256, whenever tm % 256 == 0, tn % 256 == 0 and stages == 0; 2 = pairs with
+ * 256 x 128 pieces (an A/B switch: measured slower); 0 = always one 128 x 256 (or 128 x 128) piece per SM. Results
+ * are bit-identical: every mode sums K in the same order. The counterpart in the reference is the choice of tile
+ * sizes left to its tuner (src/autokernel/tune.py:246-300): a launch-shape knob with no effect on values. */
 int tjx_gemm_set_pair_mode(int mode);
 
 /* `all_gather_matmul` in one launch (the ring kernel of src/autokernel/codegen.py:1149-1229, whose remote DMAs run

@@ -10,7 +10,11 @@ import threading
 from ctypes import c_char_p, c_int, c_size_t, c_void_p
 from pathlib import Path
 
-LIBRARY = Path(__file__).resolve().parent / "libtilejax_b200.so"
+import os
+
+# The library built in-tree; TILEJAX_B200_LIBRARY names another build of the same sources (a variant made with
+# `python -m tilejax_b200.csrc.build -D... --output ...`) to load instead.
+LIBRARY = Path(os.environ.get("TILEJAX_B200_LIBRARY") or Path(__file__).resolve().parent / "libtilejax_b200.so")
 
 # Every symbol include/tilejax_b200.h declares: name -> (restype, argtypes).
 _P = c_void_p
@@ -18,6 +22,7 @@ SYMBOLS: dict[str, tuple] = {
     "tjx_version": (c_int, []),
     "tjx_last_error": (c_char_p, []),
     "tjx_device_status": (c_int, [_P, ctypes.POINTER(c_int)]),
+    "tjx_set_wait_limit_us": (c_int, [c_int]),
     "tjx_build_steps": (c_int, [_P, c_int, _P, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P]),
     "tjx_build_steps_from_runs": (c_int, [_P, c_int, c_int, _P, _P, _P, _P, _P]),
     "tjx_gemm_bf16": (c_int, [_P, _P, _P] + [c_int] * 10 + [_P, _P, c_int, _P, _P, c_int, _P]),

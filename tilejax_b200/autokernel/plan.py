@@ -209,6 +209,111 @@ def _recognise(nest, ns, specs, outputs, parallel, reductions, chips) -> Plan:
     raise _unsupported(nest, f"{n_par} parallel loops")
 
 
+def _call_of(node, attr: str):
+    """The call's arguments if `node` is `<anything>.attr(...)` (or a bare `attr(...)`), else None."""
+    if not isinstance(node, ast.Call) or node.keywords and attr != "zeros" and attr != "full":
+        return None
+    f = node.func
+    name = f.attr if isinstance(f, ast.Attribute) else f.id if isinstance(f, ast.Name) else None
+    return node.args if name == attr else None
+
+
+def _is_name(node, name: str) -> bool:
+    return isinstance(node, ast.Name) and node.id == name
+
+
+def _is_zero(node) -> bool:
+    return isinstance(node, ast.Constant) and isinstance(node.value, (int, float)) and not isinstance(node.value, bool) \
+        and node.value == 0
+
+
+def _iota_plus(nest, ns, value, loop_var: str, shape: tuple[int, int], dimension: int) -> bool:
+    """Is `value` the expression `loop_var + broadcasted_iota(int32, shape, dimension)` (either order)?"""
+    if not (isinstance(value, ast.BinOp) and isinstance(value.op, ast.Add)):
+        return False
+    for var, iota in ((value.left, value.right), (value.right, value.left)):
+        args = _call_of(iota, "broadcasted_iota")
+        if not _is_name(var, loop_var) or args is None or len(args) != 3:
+            continue
+        try:
+            dtype, shp, dim = (eval(compile(ast.Expression(a), nest.filename, "eval"), ns) for a in args)
+            if np.dtype(dtype) == np.int32 and tuple(int(v) for v in shp) == shape and int(dim) == dimension:
+                return True
+        except Exception:
+            return False
+    return False
+
+
+def _match_gemm_tile_code(nest, ns, acc: str, i, j, tm: int, tn: int, out: Spec) -> bool:
+    """The tile code around the reduction loop must be exactly a matmul's or a causal matmul's; returns whether it
+    is the causal one. Before the loop: `acc = zeros((tm, tn), float32)`. After it: the store of `acc.astype(dtype)`
+    (or `acc` itself), or of `where(cols <= rows, acc, 0).astype(dtype)` with `rows = i + iota(dim 0)` and
+    `cols = j + iota(dim 1)` assigned just before. The output must be allocated with zeros: the skipped tiles and
+    the masked entries are written as zeros. Anything else (a scale, a bias, another fill) would be computed
+    wrongly by the fixed kernel, so it is refused here."""
+    before, after = nest.segments[0], nest.segments[-1]
+    args = _call_of(before[0].value, "zeros") if len(before) == 1 and isinstance(before[0], ast.Assign) else None
+    ok = args is not None and len(before[0].targets) == 1 and _is_name(before[0].targets[0], acc) and len(args) >= 1
+    if ok:
+        try:
+            shape = tuple(int(v) for v in eval(compile(ast.Expression(args[0]), nest.filename, "eval"), ns))
+            kw = {k.arg: k.value for k in before[0].value.keywords}
+            dtype_node = args[1] if len(args) > 1 else kw.get("dtype")
+            dtype = np.float32 if dtype_node is None else eval(compile(ast.Expression(dtype_node), nest.filename, "eval"), ns)
+            ok = shape == (tm, tn) and np.dtype(dtype) == np.float32
+        except Exception:
+            ok = False
+    if not ok:
+        raise _unsupported(nest, f"before the reduction loop the tile code must be `{acc} = jnp.zeros((tm, tn), "
+                                 "jnp.float32)` and nothing else", before[0] if before else nest.reductions[0].node)
+    alloc = nest.allocations[nest.outputs[0]].value
+    fill_args = _call_of(alloc, "full")
+    if _call_of(alloc, "zeros") is None and not (fill_args is not None and len(fill_args) >= 2 and _is_zero(fill_args[1])):
+        raise _unsupported(nest, "the output must be allocated with zeros: skipped tiles are written as zeros",
+                           nest.allocations[nest.outputs[0]])
+    store = nest.stores[nest.outputs[0]]
+    if not after or after[-1] is not store.node:
+        raise _unsupported(nest, "the tile's store must be the last statement after the reduction loop", store.node)
+    idx = store.index.elts if isinstance(store.index, ast.Tuple) else [store.index]
+    if len(idx) != 2 or _window(idx[0])[0] != i.var or _window(idx[1])[0] != j.var:
+        raise _unsupported(nest, "the tile is stored at `[i : i + tm, j : j + tn]`", store.node)
+    value = store.value
+    cast = _call_of(value, "astype")
+    if cast is not None and isinstance(value.func, ast.Attribute) and len(cast) == 1:
+        try:
+            to = np.dtype(eval(compile(ast.Expression(cast[0]), nest.filename, "eval"), ns))
+        except Exception as e:
+            raise _unsupported(nest, f"the stored tile's dtype is not known from the shapes ({e})", store.node) from e
+        if to != np.dtype(out.dtype):
+            raise _unsupported(nest, "the stored tile must be cast to the output's dtype", store.node)
+        value = value.func.value
+    elif np.dtype(out.dtype) != np.float32:
+        raise _unsupported(nest, "the stored tile must be `acc.astype(dtype)`", store.node)
+    if _is_name(value, acc):
+        if len(after) != 1:
+            raise _unsupported(nest, "code after the reduction loop other than the store (a fused epilogue)", after[0])
+        return False
+    where = _call_of(value, "where")
+    cond_ok = False
+    if where is not None and len(where) == 3 and _is_name(where[1], acc) and _is_zero(where[2]):
+        cond = where[0]
+        if isinstance(cond, ast.Compare) and len(cond.ops) == 1 and len(cond.comparators) == 1 \
+                and isinstance(cond.left, ast.Name) and isinstance(cond.comparators[0], ast.Name):
+            left, right = cond.left.id, cond.comparators[0].id
+            cols, rows = (left, right) if isinstance(cond.ops[0], ast.LtE) else (right, left) \
+                if isinstance(cond.ops[0], ast.GtE) else (None, None)
+            defs = {s.targets[0].id: s.value for s in after[:-1]
+                    if isinstance(s, ast.Assign) and len(s.targets) == 1 and isinstance(s.targets[0], ast.Name)}
+            cond_ok = (cols is not None and len(after) == 3 and set(defs) == {rows, cols} and rows != cols
+                       and _iota_plus(nest, ns, defs[rows], i.var, (tm, tn), 0)
+                       and _iota_plus(nest, ns, defs[cols], j.var, (tm, tn), 1))
+    if not cond_ok:
+        raise _unsupported(nest, "the stored tile must be the accumulator, `acc.astype(dtype)`, or its causal form "
+                                 "`jnp.where(cols <= rows, acc, 0.0).astype(dtype)` with `rows = i + iota(.., 0)` and "
+                                 "`cols = j + iota(.., 1)`; other epilogues are not built", store.node)
+    return True
+
+
 def _recognise_gemm(nest, ns, specs, outputs, parallel, reductions, chips) -> Plan:
     (i, j), (k,) = parallel, reductions
     body = nest.bodies[0]
@@ -244,12 +349,8 @@ def _recognise_gemm(nest, ns, specs, outputs, parallel, reductions, chips) -> Pl
     N = b_spec.shape[0] if transposed else b_spec.shape[1]
     if (i.start, i.stop, j.start, j.stop, k.start, k.stop) != (0, M, 0, N, 0, K) or out.shape != (M, N):
         raise _unsupported(nest, "the loops must cover the operands exactly")
+    causal = _match_gemm_tile_code(nest, ns, acc, i, j, tm, tn, out)
     store = nest.stores[nest.outputs[0]]
-    causal = any(isinstance(n, ast.Call) and isinstance(n.func, ast.Attribute) and n.func.attr == "where"
-                 for n in ast.walk(store.value))
-    reads_acc = any(isinstance(n, ast.Name) and n.id == acc for n in ast.walk(store.value))
-    if not reads_acc:
-        raise _unsupported(nest, "the stored tile must be the accumulator", store.node)
     tile_mask = nest.parallel[1].mask
     if nest.parallel[0].mask is not None or nest.reductions[0].mask is not None:
         raise _unsupported(nest, "a mask on this loop")

@@ -295,13 +295,18 @@ class AllGatherMatmul:
             if after_group is not None:
                 after_group(self.groups[n + 1])
 
-    def from_host(self, x_host: torch.Tensor, w_host: torch.Tensor, out_host: torch.Tensor, chunks: int = 8) -> None:
+    def from_host(self, x_host: torch.Tensor, w_host: torch.Tensor, out_host: torch.Tensor, chunks: int = 8,
+                  copy_back: str = "all") -> None:
         """The same product for operands in pinned host memory, result into pinned host memory: the host-to-device
         copies, the GEMMs and the device-to-host copies run as a pipeline on three streams, so a step costs about
         its slower copy direction instead of the sum of both copies and the compute. w goes first (every tile needs
         it), then this rank's rows of x in `chunks` pieces, each multiplied as soon as it has landed and its rows of
         the result copied back while the next piece is still arriving; the other ranks' shards follow as in
-        `__call__`. Enqueues only: `out_host` is complete once `host_done` has been synchronised."""
+        `__call__`. With `copy_back="own"` only this rank's m rows of the result are copied to `out_host` (where w is
+        the same on every rank the result is too, and the ranks together hand the host every row once); the whole
+        result stays in `self.out`. Enqueues only: `out_host` is complete once `host_done` has been synchronised."""
+        if copy_back not in ("all", "own"):
+            raise ValueError("copy_back is 'all' or 'own'")
         ops = self._ops
         if x_host.shape != (self.m, self.K) or w_host.shape != (self.K, self.N):
             raise ValueError("x must be this rank's (m, K) shard and w (K, N)")
@@ -364,7 +369,9 @@ class AllGatherMatmul:
                 self._start_exchange(x_dev)
                 order = shard_order(self.me, self.ranks)
 
-                def copy_back(shards):
+                def copy_rows_back(shards):
+                    if copy_back == "own":
+                        return
                     computed = torch.cuda.Event()
                     computed.record(compute)
                     d2h.wait_event(computed)
@@ -373,7 +380,7 @@ class AllGatherMatmul:
                             lo = order[s] * self.m
                             out_host[lo : lo + self.m].copy_(self.out[lo : lo + self.m], non_blocking=True)
 
-                self._other_groups(w_dev, compute, copy_back)
+                self._other_groups(w_dev, compute, copy_rows_back)
         finally:
             ops.set_gemm_cta_limit(0)
         self.done.record(compute)

@@ -39,10 +39,12 @@ def _stale(target: Path, deps: list[Path]) -> bool:
     return any(d.stat().st_mtime > built for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every source that changed and link the shared library; returns its path."""
-    objdir = CSRC / "build"
-    objdir.mkdir(exist_ok=True)
+def build(force: bool = False, verbose: bool = False, defines: tuple[str, ...] = (), output: Path | None = None) -> Path:
+    """Compile every source that changed and link the shared library; returns its path. `defines` (-D macros: the
+    kernels' tuning constants) and `output` build a variant beside the default library, in its own object folder."""
+    library = LIBRARY if output is None else Path(output).resolve()
+    objdir = CSRC / "build" if output is None else library.parent / (library.stem + "_obj")
+    objdir.mkdir(parents=True, exist_ok=True)
     headers = [(CSRC / h).resolve() for h in HEADERS] + [Path(__file__).resolve()]
     sources = [CSRC / s for s in SOURCES if (CSRC / s).exists()]
     objects = []
@@ -51,7 +53,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         obj = objdir / (src.stem + ".o")
         objects.append(obj)
         if force or _stale(obj, [src, *headers]):
-            cmd = [nvcc(), *ARCH_FLAGS, *COMMON_FLAGS, "-c", str(src), "-o", str(obj)]
+            cmd = [nvcc(), *ARCH_FLAGS, *COMMON_FLAGS, *[f"-D{d}" for d in defines], "-c", str(src), "-o", str(obj)]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             jobs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
@@ -64,19 +66,22 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             print(f"--- {src.name}\n{out}", file=sys.stderr)
     if failed:
         raise RuntimeError("nvcc failed:\n" + "\n".join(failed))
-    if force or jobs or _stale(LIBRARY, objects):
+    if force or jobs or _stale(library, objects):
         # Link beside the target and rename over it: a reader never sees a half-written library.
-        fresh = LIBRARY.with_suffix(".so.new")
+        fresh = library.with_suffix(".so.new")
         cmd = [nvcc(), *ARCH_FLAGS, "-shared", "-Xcompiler", "-fPIC", "-o", str(fresh), *map(str, objects)]
         subprocess.run(cmd, check=True)
-        os.replace(fresh, LIBRARY)
-    return LIBRARY
+        os.replace(fresh, library)
+    return library
 
 
 if __name__ == "__main__":
     parser = argparse.ArgumentParser()
     parser.add_argument("--force", action="store_true")
     parser.add_argument("--verbose", action="store_true", help="print ptxas resource usage (registers, spills, smem)")
+    parser.add_argument("-D", dest="defines", action="append", default=[], help="a macro for every source, e.g. TJX_DEC_STAGES=3")
+    parser.add_argument("--output", default=None, help="write a variant library here instead of the package's own")
     args = parser.parse_args()
+    output = Path(args.output).resolve() if args.output else None
     os.chdir(CSRC)
-    print(build(args.force, args.verbose))
+    print(build(args.force, args.verbose, tuple(args.defines), output))

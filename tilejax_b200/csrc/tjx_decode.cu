@@ -1,12 +1,18 @@
 // Ragged paged GQA decode attention on sm_100a, bound by HBM bandwidth: every valid K/V page is read once,
-// by TMA straight into shared memory, with f32 FMAs on the CUDA cores (no tensor cores: four query heads per KV
-// head is far too little reuse).
+// by TMA straight into shared memory, and multiplied with warp-level MMAs (mma.sync m16n8k16, bf16 -> f32) whose
+// 16 rows are the query heads of one KV head; the fifth-generation tensor core needs 64 or 128 rows and would
+// compute mostly padding here.
 //
-// The work is the device step table (tjx_steps.cu): the steps that run, one K/V page each, in tile (sequence)
-// order. It is cut into chunks of CHUNK consecutive steps, a CTA per (chunk, pair of KV heads), so ragged
-// lengths balance by themselves. Inside a CTA warp w owns one KV head and its G query heads. A chunk may cover
-// the end of one sequence and the start of the next; a (sequence, chunk) piece that is the sequence's only one
-// is normalised and written at once; otherwise it writes an online-softmax partial (max, sum, accumulator) to
+// The work is the list of steps that run, one K/V page each, in tile (sequence) order — the same list the device
+// step table (tjx_steps.cu) holds. For up to DEC_SELF_MAX_B (2048) sequences every CTA derives the list itself from
+// `lengths` (a prefix sum in its prologue), so the kernel does not wait for the step-table kernel that runs
+// beside it and only emits the tables for the caller; larger batches read the tables.
+//
+// The list is shared out evenly: as many CTAs as are resident at once (4 per SM) per pair of KV heads, each taking
+// one contiguous share of the steps (at least DEC_CHUNK), so ragged lengths balance to within a step and a sequence
+// is cut into as few pieces as possible. Inside a CTA warp w owns one KV head and its G query heads. A share may
+// cover the end of one sequence and the start of the next; a (sequence, share) piece that is the sequence's only
+// one is normalised and written at once; otherwise it writes an online-softmax partial (max, sum, accumulator) to
 // scratch and counts itself on the sequence's arrival counter, and the warp that arrives last merges the
 // sequence's partials, normalises and writes bf16 — no second kernel.
 //
@@ -30,13 +36,28 @@ int launch_build_steps_lengths(const int32_t* lengths, int n_lengths, const int3
 
 constexpr int DEC_D = 128;         // head dimension
 constexpr int DEC_SUB = 16;        // tokens per micro-step (a page is a whole number of these)
-constexpr int DEC_STAGES = 2;      // ring slots per warp
+#ifndef TJX_DEC_STAGES
+#define TJX_DEC_STAGES 2
+#endif
+#ifndef TJX_DEC_WARPS
+#define TJX_DEC_WARPS 2
+#endif
+#ifndef TJX_DEC_CTAS
+#define TJX_DEC_CTAS 4  // resident CTAs per SM: 8 warps per SM measured fastest (12: +5 %, 6: +8 %, 4: +40 % time)
+#endif
+#ifndef TJX_DEC_CHUNK
+#define TJX_DEC_CHUNK 12
+#endif
+constexpr int DEC_STAGES = TJX_DEC_STAGES;  // ring slots per warp
 constexpr int DEC_HALF_BYTES = DEC_SUB * 64 * 2;           // one TMA box: 16 tokens x 64 dims, 128-byte rows
 constexpr int DEC_STAGE_BYTES = 4 * DEC_HALF_BYTES;        // K (two dim halves) and V (two) of one micro-step
-constexpr int DEC_CHUNK = 12;      // steps (pages) per CTA (at most 32: a lane holds a step)
-constexpr int DEC_WARPS = 2;       // KV heads per CTA
+constexpr int DEC_CHUNK = TJX_DEC_CHUNK;  // steps (pages) per CTA (at most 32: a lane holds a step)
+constexpr int DEC_WARPS = TJX_DEC_WARPS;  // KV heads per CTA
 constexpr float DEC_MASK = -1e30f;
 constexpr int DEC_SMEM = DEC_WARPS * DEC_STAGES * DEC_STAGE_BYTES + 1024;  // + slack to align the ring to 1024
+// Up to this many sequences a CTA computes every sequence's first step itself (B + 1 ints of shared memory behind
+// the ring); beyond it the kernel reads the tables the step-table kernel built.
+constexpr int DEC_SELF_MAX_B = 2048;
 
 struct DecodeParams {
   const __nv_bfloat16* q;        // [B, T, H, D]
@@ -55,6 +76,7 @@ struct DecodeParams {
   __nv_bfloat16* out;            // [B, T, H, D]
   int B, H, Hkv, page_size, pages_per_seq, num_pages, slots;
   int T, rows;                   // new tokens per sequence; query rows per sequence = T * H (row t * H + h)
+  int self_steps;                // != 0: derive the steps from `lengths` in the prologue instead of reading the tables
   int* status;
 };
 
@@ -135,7 +157,7 @@ __device__ __forceinline__ void decode_merge_heads(const DecodeParams& p, int b,
 // tokens 2t, 2t+1, 8+2t, 9+2t and output dims 8 n + 2t, + 1 for n = 0..15. A fifth-generation (tcgen05) MMA needs
 // 64 or 128 rows; with at most 8 query heads per KV head this path stays bound by HBM with the warp-level MMA.
 template <int G, bool WIDE>
-__global__ void __launch_bounds__(DEC_WARPS * 32, WIDE ? 4 : 6)
+__global__ void __launch_bounds__(DEC_WARPS * 32, WIDE ? (TJX_DEC_CTAS * 2 / 3) : TJX_DEC_CTAS)
     decode_chunks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                          const DecodeParams p) {
   extern __shared__ uint8_t dec_smem_raw[];
@@ -150,12 +172,42 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, WIDE ? 4 : 6)
     tma_prefetch_desc(&map_k);
     tma_prefetch_desc(&map_v);
   }
-  // Launched with programmatic stream serialisation: everything above overlaps the step-table kernel; nothing
-  // that kernel writes (tables, cleared arrival counters) is touched before this returns.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  const int n_steps = p.step_count[0];
-  __syncthreads();
-  if (kvh >= p.Hkv) return;
+  // Launched with programmatic stream serialisation: this grid may run beside the step-table kernel before it in
+  // the stream. Nothing that kernel writes (the tables, the cleared arrival counters) is touched before a
+  // griddepcontrol.wait: at once when the steps come from its tables, else only before the first arrival is
+  // counted — the pages, lengths and block tables were complete before that kernel started.
+  int* s_first = reinterpret_cast<int*>(dec_smem_raw + DEC_SMEM);  // [B + 1] first step of every sequence (self_steps)
+  int n_steps;
+  if (p.self_steps) {
+    __shared__ int s_part[DEC_WARPS * 32];
+    // A sequence takes one step per page that holds a valid position, or one empty step if it has none
+    // (src/autokernel/codegen.py:386-431). Thread i sums a contiguous range of sequences, then a scan over threads.
+    const int per = (p.B + DEC_WARPS * 32 - 1) / (DEC_WARPS * 32);
+    const int lo = min(p.B, static_cast<int>(threadIdx.x) * per), hi = min(p.B, lo + per);
+    int sum = 0;
+    for (int b = lo; b < hi; ++b) {
+      const int len = p.lengths[b];
+      const int runs = len > 0 ? min(p.pages_per_seq, (len + p.page_size - 1) / p.page_size) : 0;
+      s_first[b] = sum;
+      sum += max(runs, 1);
+    }
+    s_part[threadIdx.x] = sum;
+    __syncthreads();
+    int before = 0;
+    for (int i = 0; i < static_cast<int>(threadIdx.x); ++i) before += s_part[i];
+    for (int b = lo; b < hi; ++b) s_first[b] += before;
+    if (threadIdx.x == DEC_WARPS * 32 - 1) s_first[p.B] = before + sum;
+    __syncthreads();
+    n_steps = s_first[p.B];
+  } else {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    n_steps = p.step_count[0];
+    __syncthreads();
+  }
+  if (kvh >= p.Hkv) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    return;
+  }
 
   // Query rows of this KV head: row r = (new token r / G, query head r % G of the group), R = T * G of them. A
   // lane holds row g = lane / 4 and, when there are more than 8 rows (WIDE), row g + 8 as well.
@@ -186,23 +238,10 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, WIDE ? 4 : 6)
 
   int n = 0;  // micro-steps consumed by this warp so far (ring position and barrier phase)
   bool ok = true;
-  // A persistent CTA: chunks blockIdx.x, blockIdx.x + gridDim.x, ... of the steps that run.
-  for (int chunk = blockIdx.x; chunk * DEC_CHUNK < n_steps && ok; chunk += gridDim.x) {
-  const int s_begin = chunk * DEC_CHUNK;
-  const int n_here = min(DEC_CHUNK, n_steps - s_begin);
-
-  // The chunk's steps, one per lane (lanes 0..n_here-1), broadcast by shuffle when needed.
-  int my_tile = -1, my_code = 4, my_page = 0, my_len = 0;
-  if (lane < n_here) {
-    my_tile = p.step_tile[s_begin + lane];
-    my_code = p.step_code[s_begin + lane];
-    my_len = p.lengths[my_tile];
-    if (!(my_code & 4)) {
-      const int pg = my_code >> 3;
-      my_page = p.block_tables[static_cast<size_t>(my_tile) * p.pages_per_seq + pg];
-      my_page = min(max(my_page, 0), p.num_pages - 1);
-    }
-  }
+  // A persistent CTA takes one contiguous share of the steps that run — the same number for every CTA, at least
+  // DEC_CHUNK — so ragged lengths balance to within a step and a sequence is cut into as few pieces as possible.
+  const int per = max(DEC_CHUNK, (n_steps + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x));
+  const int r_begin = min(n_steps, static_cast<int>(blockIdx.x) * per), r_end = min(n_steps, r_begin + per);
 
   uint32_t qa[8][2 * NR];  // A fragments of Q: k-step j = dims 16 j .. + 15; row x: [2x] = dims + 2t, + 1, [2x + 1] = + 8
   float o[16][4];          // O fragments: [n][0..1] = row g, dims 8 n + 2t, + 1; [2..3] = row g + 8 (zero rows unless WIDE)
@@ -213,9 +252,10 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, WIDE ? 4 : 6)
 
   auto flush = [&]() {
     if (cur < 0) return;
-    const int first = p.tile_first[cur], next = p.tile_first[cur + 1];
-    const int pieces = (next - 1) / DEC_CHUNK - first / DEC_CHUNK + 1;  // a tile takes at least one step
-    const int slot = chunk - first / DEC_CHUNK;
+    const int first = p.self_steps ? s_first[cur] : p.tile_first[cur];
+    const int next = p.self_steps ? s_first[cur + 1] : p.tile_first[cur + 1];
+    const int pieces = (next - 1) / per - first / per + 1;  // shares the sequence's steps fall in (it takes at least one)
+    const int slot = static_cast<int>(blockIdx.x) - first / per;
     const size_t base = (static_cast<size_t>(cur) * p.slots + slot) * p.rows;
 #pragma unroll
     for (int x = 0; x < NR; ++x) {
@@ -241,6 +281,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, WIDE ? 4 : 6)
     }
     if (pieces > 1) {
       // Count this piece; whoever counts last finds every partial of the sequence's KV head written and merges.
+      // The counters were cleared by the step-table kernel: it must have finished.
+      asm volatile("griddepcontrol.wait;" ::: "memory");
       __threadfence();
       __syncwarp();
       int last = 0;
@@ -252,6 +294,36 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, WIDE ? 4 : 6)
       }
     }
   };
+
+  // The share is walked 32 steps at a time (a lane holds a step); the accumulators carry over.
+  for (int s_begin = r_begin; s_begin < r_end && ok; s_begin += 32) {
+  const int n_here = min(32, r_end - s_begin);
+
+  // The chunk's steps, one per lane (lanes 0..n_here-1), broadcast by shuffle when needed.
+  int my_tile = -1, my_code = 4, my_page = 0, my_len = 0;
+  if (lane < n_here) {
+    if (p.self_steps) {
+      // The sequence holding step s: the last one whose first step is <= s (every sequence takes a step).
+      const int st = s_begin + lane;
+      int lo = 0, hi = p.B;
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (s_first[mid] <= st) lo = mid; else hi = mid;
+      }
+      my_tile = lo;
+      my_len = p.lengths[lo];
+      my_code = ((st - s_first[lo]) << 3) | (my_len > 0 ? 0 : 4);
+    } else {
+      my_tile = p.step_tile[s_begin + lane];
+      my_code = p.step_code[s_begin + lane];
+      my_len = p.lengths[my_tile];
+    }
+    if (!(my_code & 4)) {
+      const int pg = my_code >> 3;
+      my_page = p.block_tables[static_cast<size_t>(my_tile) * p.pages_per_seq + pg];
+      my_page = min(max(my_page, 0), p.num_pages - 1);
+    }
+  }
 
   // The next micro-step (step, 16-token sub-block) that has data after (step, sub); step == n_here if none.
   auto next_data = [&](int step, int sub, int& nstep, int& nsub) {
@@ -400,14 +472,15 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, WIDE ? 4 : 6)
       __syncwarp();  // every lane is done with the slot before it is refilled
     }
   }
+  }  // 32 steps of the share
   if (ok) flush();
-  }  // chunks
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // never outlive the step-table kernel's writes unordered
 }
 
 template <int G, bool WIDE>
 static int launch_chunks_for(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeParams& p, dim3 grid,
                              cudaStream_t s) {
-  constexpr int SMEM = DEC_SMEM;
+  constexpr int SMEM = DEC_SMEM + (DEC_SELF_MAX_B + 1) * 4;
   auto kernel = decode_chunks_kernel<G, WIDE>;
   static bool configured[64] = {};
   int dev = 0;
@@ -419,7 +492,8 @@ static int launch_chunks_for(const CUtensorMap& mk, const CUtensorMap& mv, const
   // Programmatic stream serialisation: the grid may start while the step-table kernel before it in the stream
   // is still running; the kernel waits (griddepcontrol.wait) before it reads anything that kernel writes.
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = grid, cfg.blockDim = dim3(DEC_WARPS * 32), cfg.dynamicSmemBytes = SMEM, cfg.stream = s;
+  cfg.gridDim = grid, cfg.blockDim = dim3(DEC_WARPS * 32), cfg.stream = s;
+  cfg.dynamicSmemBytes = DEC_SMEM + (p.self_steps ? (p.B + 1) * 4 : 0);
   cudaLaunchAttribute attr{};
   attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr.val.programmaticStreamSerializationAllowed = 1;
@@ -447,10 +521,11 @@ static int launch_decode_chunks(DecodeParams& p, int group, cudaStream_t s) {
   const long long capacity = static_cast<long long>(p.B) * p.pages_per_seq;
   const int chunks = static_cast<int>((capacity + DEC_CHUNK - 1) / DEC_CHUNK);
   const int groups = (p.Hkv + DEC_WARPS - 1) / DEC_WARPS;
-  // One CTA per possible chunk: the hardware scheduler balances the ones that have work (a CTA past the end of
-  // the steps that run exits at once). The kernel also accepts a smaller grid and then loops over chunks.
-  dim3 grid(chunks, groups);
   const bool wide = p.T * group > 8;  // more than 8 query rows per KV head: both halves of the MMA's 16 rows
+  // As many CTAs as are resident at once (never more than there are chunks of DEC_CHUNK steps): each takes an equal
+  // contiguous share of the steps that run.
+  const int resident = sm_count() * (wide ? TJX_DEC_CTAS * 2 / 3 : TJX_DEC_CTAS);
+  dim3 grid(std::max(1, std::min(chunks, resident / groups)), groups);
   switch (group) {
     case 1: return wide ? launch_chunks_for<1, true>(mk, mv, p, grid, s) : launch_chunks_for<1, false>(mk, mv, p, grid, s);
     case 2: return wide ? launch_chunks_for<2, true>(mk, mv, p, grid, s) : launch_chunks_for<2, false>(mk, mv, p, grid, s);
@@ -511,6 +586,7 @@ static int run_decode(const void* q, const void* k_pages, const void* v_pages, c
   p.step_tile = step_tile, p.step_code = step_code, p.step_count = step_count, p.tile_first = tile_first;
   p.B = B, p.H = H, p.Hkv = Hkv, p.page_size = page_size, p.pages_per_seq = pages_per_seq, p.num_pages = num_pages;
   p.T = T, p.rows = T * H;
+  p.self_steps = B <= DEC_SELF_MAX_B ? 1 : 0;
   p.slots = decode_slots(pages_per_seq);
   const size_t rows = static_cast<size_t>(B) * p.slots * p.rows;
   uint8_t* ws = static_cast<uint8_t*>(scratch);

@@ -405,6 +405,7 @@ constexpr int PAIR_ROWS = 2 * BM;
 // measured 75 % busy against 94 % with this shape; two slots of three blocks prefetch too little.
 constexpr int PAIR_STAGES = 3;
 constexpr int PAIR_KSUB = 2;
+constexpr int PAIR_STAGES_128 = 4;  // 128-wide pieces stage 8 KB less per K block: a fourth slot fits
 
 constexpr int GATHER_THREADS = GEMM_THREADS + 32;  // the pair kernel with its copier warp
 // 16-byte loads a copier lane keeps in flight: 148 warps x 32 lanes x 32 x 16 B = 2.4 MB on the wire, what a few
@@ -420,14 +421,14 @@ __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
 // Bounded wait until a 256-row block of the gathered operand has been written by every copier warp.
 __device__ __forceinline__ bool gather_wait(const int* counter, int target, volatile int* abort_flag, int* status) {
   if (ld_acquire_gpu(counter) >= target) return true;
-  unsigned long long start = 0;
+  unsigned long long start = 0, limit = 0;
   for (uint32_t it = 1;; ++it) {
     if (ld_acquire_gpu(counter) >= target) return true;
     if ((it & 63u) == 0) {
       if (*abort_flag) return false;
       const unsigned long long now = globaltimer_ns();
-      if (start == 0) start = now;
-      if (now - start > WAIT_LIMIT_NS) {
+      if (start == 0) start = now, limit = wait_limit_ns(status);
+      if (now - start > limit) {
         *abort_flag = 1;
         if (status != nullptr) atomicCAS(status, 0, TJX_ERR_WAIT_OTHER);
         return false;
@@ -436,10 +437,10 @@ __device__ __forceinline__ bool gather_wait(const int* counter, int target, vola
   }
 }
 
-template <int STAGES, int KSUB>
+template <int PBN, int STAGES, int KSUB>
 struct PairSmem {
-  static constexpr int A_BYTES = BM * BK * 2;             // this CTA's 128 rows of x, one block of 64 k
-  static constexpr int B_BYTES = (PAIR_BN / 2) * BK * 2;  // this CTA's 128 columns of y, one block of 64 k
+  static constexpr int A_BYTES = BM * BK * 2;         // this CTA's 128 rows of x, one block of 64 k
+  static constexpr int B_BYTES = (PBN / 2) * BK * 2;  // this CTA's half of the piece's columns of y, one block of 64 k
   static constexpr int SUB_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGE_BYTES = KSUB * SUB_BYTES;    // a ring slot holds KSUB blocks of 64 k
   static constexpr int C_BYTES = 4 * 32 * 64 * 2 * 2;
@@ -449,13 +450,15 @@ struct PairSmem {
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
-template <int STAGES, int KSUB, bool GATHER>
+// PBN = columns of a piece (the N of the pair's MMA): 256, or 128 as an A/B switch (half-size pieces; slower: more
+// operand bytes per flop through shared memory); both sum K in the same order, so their results are bit-identical.
+template <int PBN, int STAGES, int KSUB, bool GATHER>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THREADS : GEMM_THREADS, 1)
     gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                      const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_a_own,
                      const GemmParams p) {
-  using L = PairSmem<STAGES, KSUB>;
-  constexpr int BN = PAIR_BN;
+  using L = PairSmem<PBN, STAGES, KSUB>;
+  constexpr int BN = PBN;
   const int num_slots = (p.num_kb + KSUB - 1) / KSUB;  // ring slots per work item
   extern __shared__ uint8_t smem_raw[];
   // The dynamic shared-memory window starts at the same offset in both CTAs, so the aligned offsets agree.
@@ -686,11 +689,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
   }
 }
 
-template <int STAGES, int KSUB, bool GATHER>
+template <int PBN, int STAGES, int KSUB, bool GATHER>
 static int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
                             const CUtensorMap& ma_own, const GemmParams& p, int grid, cudaStream_t stream) {
-  using L = PairSmem<STAGES, KSUB>;
-  auto kernel = gemm_pair_kernel<STAGES, KSUB, GATHER>;
+  using L = PairSmem<PBN, STAGES, KSUB>;
+  auto kernel = gemm_pair_kernel<PBN, STAGES, KSUB, GATHER>;
   static bool configured[64] = {};
   int dev = 0;
   TJX_CUDA(cudaGetDevice(&dev));
@@ -707,11 +710,12 @@ static int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const 
 
 namespace tjx {
 static thread_local int g_gemm_cta_limit = 0;  // 0 = one CTA per SM
-static thread_local int g_gemm_pair_mode = 1;  // 1 = use CTA pairs whenever the tiles allow it
+static thread_local int g_gemm_pair_mode = 1;  // 0 never pairs; 1 (and 3) pairs with 256-wide pieces; 2 pairs with 128-wide
 }
 
 extern "C" int tjx_gemm_set_pair_mode(int mode) {
-  if (mode != 0 && mode != 1) return tjx::fail(TJX_E_ARG, "mode must be 0 (single CTAs) or 1 (pairs when possible)");
+  if (mode < 0 || mode > 3)
+    return tjx::fail(TJX_E_ARG, "mode must be 0 (single CTAs), 1 or 3 (pairs, 256-wide pieces) or 2 (pairs, 128-wide pieces)");
   tjx::g_gemm_pair_mode = mode;
   return 0;
 }
@@ -750,6 +754,10 @@ extern "C" int tjx_gemm_bf16(const void* x, const void* y, void* out, int M, int
   }
   // CTA pairs need whole 256 x 256 pieces of every user tile; an explicit stage count asks for the single-CTA ring.
   const bool pair = g_gemm_pair_mode >= 1 && stages == 0 && tm % PAIR_ROWS == 0 && tn % PAIR_BN == 0;
+  // Piece width of the pair kernel: 256 columns. 128-wide pieces (mode 2) would fill the last round of a launch
+  // better (4096^3 would take 3.5 rounds' time instead of 4) but move 1.5x the operand bytes per flop through shared
+  // memory and measured 1.3 - 1.4x slower (8192^3: 0.97 ms against 0.68 ms), so they are only kept as an A/B switch.
+  const int pbn = (pair && g_gemm_pair_mode == 2) ? 128 : PAIR_BN;
   if (stages == 0) stages = 4;
   const int BN = (tn % 256 == 0) ? 256 : 128;
   if (!(stages == 4 || (BN == 128 && stages == 6) || (BN == 256 && stages == 3)))
@@ -759,7 +767,7 @@ extern "C" int tjx_gemm_bf16(const void* x, const void* y, void* out, int M, int
   p.M = M, p.N = N, p.K = K, p.tm = tm, p.tn = tn, p.tiles_m = tiles_m, p.tiles_n = tiles_n;
   p.band_tiles = std::max(1, 2048 / tn);
   p.sub_m = pair ? tm / PAIR_ROWS : (tm + BM - 1) / BM;
-  p.sub_n = (tn + BN - 1) / BN;
+  p.sub_n = pair ? tn / pbn : (tn + BN - 1) / BN;
   p.n_tiles = n_tiles, p.n_fills = n_fills;
   p.tile_i = tile_i, p.tile_j = tile_j, p.fill_i = fill_i, p.fill_j = fill_j;
   p.causal = causal ? 1 : 0, p.out_f32 = out_f32 ? 1 : 0, p.b_kmajor = y_transposed ? 1 : 0;
@@ -780,7 +788,7 @@ extern "C" int tjx_gemm_bf16(const void* x, const void* y, void* out, int M, int
   if (y_transposed) {
     const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
     const uint64_t strides[1] = {static_cast<uint64_t>(K) * 2};
-    const uint32_t box[2] = {BK, static_cast<uint32_t>(pair ? PAIR_BN / 2 : BN)};
+    const uint32_t box[2] = {BK, static_cast<uint32_t>(pair ? pbn / 2 : BN)};
     if (int rc = make_tensor_map(&mb, y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 2, dims, strides, box,
                                  CU_TENSOR_MAP_SWIZZLE_128B))
       return rc;
@@ -811,7 +819,8 @@ extern "C" int tjx_gemm_bf16(const void* x, const void* y, void* out, int M, int
   if (pair) {
     int pairs = static_cast<int>(total_items < sm_count() / 2 ? total_items : sm_count() / 2);
     if (g_gemm_cta_limit > 0) pairs = std::max(1, std::min(pairs, g_gemm_cta_limit / 2));
-    return launch_gemm_pair<PAIR_STAGES, PAIR_KSUB, false>(ma, mb, mc, ma, p, 2 * pairs, s);
+    if (pbn == 128) return launch_gemm_pair<128, PAIR_STAGES_128, PAIR_KSUB, false>(ma, mb, mc, ma, p, 2 * pairs, s);
+    return launch_gemm_pair<PAIR_BN, PAIR_STAGES, PAIR_KSUB, false>(ma, mb, mc, ma, p, 2 * pairs, s);
   }
   if (BN == 256) {
     if (stages == 3) return launch_gemm<256, 3>(ma, mb, mc, p, grid, s);
@@ -892,5 +901,6 @@ extern "C" int tjx_all_gather_gemm_bf16(const void* x_own, const void* const* pe
   // CTA per SM, never more CTAs than SMs.
   const long long total_items = static_cast<long long>(n_tiles) * p.sub_m * p.sub_n;
   const int pairs = static_cast<int>(std::min<long long>(total_items, sm_count() / 2));
-  return launch_gemm_pair<PAIR_STAGES, PAIR_KSUB, true>(ma, mb, mc, ma_own, p, 2 * pairs, static_cast<cudaStream_t>(stream));
+  return launch_gemm_pair<PAIR_BN, PAIR_STAGES, PAIR_KSUB, true>(ma, mb, mc, ma_own, p, 2 * pairs,
+                                                                static_cast<cudaStream_t>(stream));
 }

@@ -31,7 +31,8 @@ static int* g_status[MAX_DEVICES];
 
 // The kernels' error word: a fixed device variable (one per GPU that loads the library), so that no entry
 // point ever has to allocate device memory. Host code only ever takes its address with cudaGetSymbolAddress.
-static __device__ int g_status_word[64];
+// Word 0 is the status; word 1 is the longest a device-side wait may last, in microseconds (0 = the built-in 2 s).
+static __device__ int g_status_word[64] = {0, 2000000};
 
 static int current_device(int* dev) {
   cudaError_t e = cudaGetDevice(dev);
@@ -128,6 +129,17 @@ extern "C" {
 int tjx_version(void) { return 100; }
 
 const char* tjx_last_error(void) { return tjx::g_error.c_str(); }
+
+int tjx_set_wait_limit_us(int microseconds) {
+  if (microseconds < 1000 || microseconds > 10000000)
+    return tjx::fail(TJX_E_ARG, "the wait limit is between 1000 microseconds and 10 seconds");
+  if (int rc = tjx::check_device()) return rc;
+  int* word = tjx::device_status_word();
+  if (word == nullptr) return tjx::fail(TJX_E_CUDA, "could not locate the device status word");
+  TJX_CUDA(cudaDeviceSynchronize());  // no kernel is in the middle of a wait while the limit changes
+  TJX_CUDA(cudaMemcpy(word + 1, &microseconds, sizeof(int), cudaMemcpyHostToDevice));
+  return 0;
+}
 
 int tjx_device_status(tjx_stream_t stream, int* code) {
   if (code == nullptr) return tjx::fail(TJX_E_ARG, "code is null");

@@ -21,8 +21,16 @@ enum : int {
   TJX_ERR_BAD_TABLE = 110,    // a step/tile table entry out of range
 };
 
-// Longest a single wait may last before the kernel gives up (nanoseconds of %globaltimer).
+// Longest a single wait may last before the kernel gives up (nanoseconds of %globaltimer) when the kernel has no
+// status word to read the limit from. With a status word the limit is the word after it, in microseconds
+// (tjx_set_wait_limit_us; 2 s unless changed).
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+__device__ __forceinline__ unsigned long long wait_limit_ns(const int* status) {
+  if (status == nullptr) return WAIT_LIMIT_NS;
+  const unsigned us = static_cast<unsigned>(*reinterpret_cast<const volatile int*>(status + 1));
+  return us == 0 ? WAIT_LIMIT_NS : static_cast<unsigned long long>(us) * 1000ull;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -78,14 +86,14 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
                                           int code) {
   if (mbar_try_wait(bar, parity)) return true;
-  unsigned long long start = 0;
+  unsigned long long start = 0, limit = 0;
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 255u) == 0) {
       if (*abort_flag) return false;
       unsigned long long now = globaltimer_ns();
-      if (start == 0) start = now;
-      if (now - start > WAIT_LIMIT_NS) {
+      if (start == 0) start = now, limit = wait_limit_ns(status);
+      if (now - start > limit) {
         *abort_flag = 1;
         if (status != nullptr) atomicCAS(status, 0, code);
         return false;

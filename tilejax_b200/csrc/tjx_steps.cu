@@ -156,6 +156,9 @@ int launch_build_steps_lengths(const int32_t* lengths, int n_lengths, const int3
                                int blocks, int value0, int value_step, int32_t* step_tile, int32_t* step_code,
                                int32_t* step_count, int32_t* tile_first, int32_t* zero_words, int n_zero,
                                cudaStream_t stream) {
+  // Every caller comes through here, the decode entry points included: the size limits of the kernel's shared
+  // arrays are enforced before anything is launched.
+  if (int rc = check_common(tiles, blocks, step_tile, step_code, step_count)) return rc;
   RunFromLengths mask{lengths, tile_values, n_lengths, value0, value_step};
   build_steps_kernel<<<1, STEPS_THREADS, 0, stream>>>(mask, tiles, blocks, step_tile, step_code, step_count,
                                                       tile_first, zero_words, n_zero);
@@ -171,7 +174,6 @@ int tjx_build_steps(const int32_t* lengths, int n_lengths, const int32_t* tile_v
                     int value0, int value_step, int32_t* step_tile, int32_t* step_code, int32_t* step_count,
                     int32_t* tile_first, tjx_stream_t stream) {
   if (int rc = tjx::check_device()) return rc;
-  if (int rc = tjx::check_common(tiles, blocks, step_tile, step_code, step_count)) return rc;
   if (lengths == nullptr || n_lengths <= 0) return tjx::fail(TJX_E_ARG, "lengths is null or empty");
   if (value_step <= 0) return tjx::fail(TJX_E_ARG, "value_step must be positive (loops count up)");
   return tjx::launch_build_steps_lengths(lengths, n_lengths, tile_values, tiles, blocks, value0, value_step,

@@ -57,6 +57,12 @@ def device_status() -> int:
     return code.value
 
 
+def set_wait_limit_us(microseconds: int) -> None:
+    """How long a device-side wait may last on the current device before the kernel gives up and records its code
+    (1000 .. 10,000,000 microseconds; 2 s unless changed). Synchronises the device."""
+    check(library().tjx_set_wait_limit_us(int(microseconds)))
+
+
 # ------------------------------------------------------------------------------------------ step tables
 
 
@@ -157,9 +163,11 @@ def set_gemm_cta_limit(max_ctas: int) -> None:
     check(library().tjx_gemm_set_cta_limit(int(max_ctas)))
 
 
-def set_gemm_pair_mode(pairs: bool) -> None:
-    """Let this thread's GEMM launches use one MMA per pair of SMs when the tiles allow it (the default), or never."""
-    check(library().tjx_gemm_set_pair_mode(int(pairs)))
+def set_gemm_pair_mode(mode: int | bool) -> None:
+    """How this thread's GEMM launches map pieces to SMs: 1 / True (the default; 3 is the same) one MMA per pair of
+    SMs in 256 x 256 pieces when the tiles allow it; 2 the same with 256 x 128 pieces (an A/B switch, slower);
+    0 / False never pairs. Values do not depend on it."""
+    check(library().tjx_gemm_set_pair_mode(int(mode)))
 
 
 def matmul(x: torch.Tensor, y: torch.Tensor, tm: int = 512, tn: int = 512, tk: int = 512, **kw) -> torch.Tensor:
