@@ -57,3 +57,42 @@ def test_operators_refuse_cpu_tensors():
     x = torch.zeros(128, 128, dtype=torch.bfloat16)
     with pytest.raises(ValueError, match="no CPU path"):
         ops.matmul(x, x)
+
+
+def test_the_no_allocation_decode_wrapper_checks_its_buffers_on_the_host():
+    # Every buffer of ops.paged_gqa_decode_static is the caller's: a wrong dtype or a short buffer would become
+    # out-of-bounds device writes, so each is refused before the library is called (no GPU needed to see that).
+    import pytest
+    import torch
+
+    from tilejax_b200 import ops
+
+    B, T, H, D, pages, page, num_pages, Hkv = 2, 1, 8, 128, 4, 16, 8, 2
+
+    def good():
+        i32 = lambda *shape: torch.zeros(shape, dtype=torch.int32)  # noqa: E731
+        q = torch.zeros(B, T, H, D, dtype=torch.bfloat16)
+        kp = torch.zeros(num_pages, page, Hkv * D, dtype=torch.bfloat16)
+        return dict(q=q, k_pages=kp, v_pages=kp.clone(), block_tables=i32(B, pages), lengths=i32(B),
+                    out=torch.zeros_like(q), step_tile=i32(B * pages), step_code=i32(B * pages), step_count=i32(1),
+                    tile_first=i32(B + 1))
+
+    bad = {
+        "bfloat16": [("q", lambda a: a["q"].float()), ("out", lambda a: a["out"].float()),
+                     ("v_pages", lambda a: a["v_pages"].half())],
+        "int32": [("block_tables", lambda a: a["block_tables"].long()), ("lengths", lambda a: a["lengths"].long()),
+                  ("step_tile", lambda a: a["step_tile"].long()), ("tile_first", lambda a: a["tile_first"].long())],
+        "out must have q's shape": [("out", lambda a: a["out"][:1])],
+        "both be": [("v_pages", lambda a: a["v_pages"][:4]), ("k_pages", lambda a: torch.zeros(8, 16, 200, dtype=torch.bfloat16))],
+        "block_tables is": [("lengths", lambda a: a["lengths"][:1]), ("block_tables", lambda a: a["block_tables"][:1])],
+        "too small": [("step_tile", lambda a: a["step_tile"][:-1]), ("step_code", lambda a: a["step_code"][:3]),
+                      ("tile_first", lambda a: a["tile_first"][:B]), ("step_count", lambda a: a["step_count"][:0])],
+    }
+    for message, cases in bad.items():
+        for name, change in cases:
+            args = good()
+            args[name] = change(args)
+            with pytest.raises(ValueError, match=message):
+                ops.paged_gqa_decode_static(**args)
+    with pytest.raises(ValueError, match="CUDA tensors"):  # and only then: these operators have no CPU path
+        ops.paged_gqa_decode_static(**good())

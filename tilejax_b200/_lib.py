@@ -23,6 +23,7 @@ SYMBOLS: dict[str, tuple] = {
     "tjx_last_error": (c_char_p, []),
     "tjx_device_status": (c_int, [_P, ctypes.POINTER(c_int)]),
     "tjx_set_wait_limit_us": (c_int, [c_int]),
+    "tjx_set_profile_buffer": (c_int, [_P, c_size_t]),
     "tjx_build_steps": (c_int, [_P, c_int, _P, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P]),
     "tjx_build_steps_from_runs": (c_int, [_P, c_int, c_int, _P, _P, _P, _P, _P]),
     "tjx_gemm_bf16": (c_int, [_P, _P, _P] + [c_int] * 10 + [_P, _P, c_int, _P, _P, c_int, _P]),

@@ -49,6 +49,7 @@ struct GemmParams {
   int num_kb;
   void* out;
   int* status;
+  long long* profile;  // per-CTA counters (PROFILE_WORDS each) or null
   // All-gather fused into the launch (gemm_pair_kernel<.., true> only): rows [own_lo, own_hi) of the gathered
   // operand are this GPU's shard and come from map_a_own; the other shards are pulled from peer memory into
   // `gather_dst` by one extra warp per CTA, 256-row block by block in arrival order, and counted in
@@ -218,6 +219,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   const int per = p.sub_m * p.sub_n;
   const int total_items = (p.n_tiles + p.n_fills) * per;
   constexpr uint32_t TMEM_COLS = 2 * BN;
+  long long* prof = p.profile == nullptr ? nullptr : p.profile + static_cast<size_t>(blockIdx.x) * PROFILE_WORDS;
+  if (prof != nullptr && threadIdx.x == 0) prof[0] = clock64();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -283,17 +286,20 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
+      long long t_first = 0, in_wait = 0, fill_wait = -1, out_wait = 0, items = 0;
       for (int w = blockIdx.x; w < total_items && ok; w += gridDim.x) {
         const Item it = decode_item<BM, BN>(p, w);
         if (!it.compute) continue;
-        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, TJX_ERR_WAIT_TMEM_EMPTY)) break;
+        if (items++ == 0) t_first = clock64();
+        if (!mbar_wait_timed(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, TJX_ERR_WAIT_TMEM_EMPTY, out_wait)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, TJX_ERR_WAIT_FULL)) {
+          if (!mbar_wait_timed(full_bar(stage), phase, abort_flag, p.status, TJX_ERR_WAIT_FULL, in_wait)) {
             ok = false;
             break;
           }
+          if (fill_wait < 0) fill_wait = in_wait;
           tc_fence_after_sync();
           const uint32_t a_addr = base + L::RING_OFF + stage * L::STAGE_BYTES;
           const uint32_t b_addr = a_addr + L::A_BYTES;
@@ -316,6 +322,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
           acc = 0;
           acc_phase ^= 1u;
         }
+      }
+      if (prof != nullptr) {
+        prof[1] = t_first, prof[2] = clock64(), prof[3] = in_wait, prof[4] = max(fill_wait, 0ll), prof[5] = out_wait;
+        prof[6] = items;
       }
     }
     __syncwarp();
@@ -360,6 +370,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 
   tc_fence_before_sync();
   __syncthreads();
+  if (prof != nullptr && threadIdx.x == 0) prof[7] = clock64();
   if (warp == 1) {
     if (*abort_flag) __nanosleep(100000);  // let whatever is still in flight land before TMEM goes away
     tc_fence_after_sync();
@@ -478,6 +489,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
   const int per = p.sub_m * p.sub_n;
   const int total_items = (p.n_tiles + p.n_fills) * per;
   constexpr uint32_t TMEM_COLS = 2 * BN;
+  long long* prof = p.profile == nullptr ? nullptr : p.profile + static_cast<size_t>(blockIdx.x) * PROFILE_WORDS;
+  if (prof != nullptr && threadIdx.x == 0) prof[0] = clock64();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -569,17 +582,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
+      long long t_first = 0, in_wait = 0, fill_wait = -1, out_wait = 0, items = 0;
       for (int w = pair; w < total_items && ok; w += n_pairs) {
         const Item it = decode_item<PAIR_ROWS, BN>(p, w);
         if (!it.compute) continue;
-        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, TJX_ERR_WAIT_TMEM_EMPTY)) break;
+        if (items++ == 0) t_first = clock64();
+        if (!mbar_wait_timed(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, TJX_ERR_WAIT_TMEM_EMPTY, out_wait)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int slot = 0; slot < num_slots; ++slot) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, TJX_ERR_WAIT_FULL)) {
+          if (!mbar_wait_timed(full_bar(stage), phase, abort_flag, p.status, TJX_ERR_WAIT_FULL, in_wait)) {
             ok = false;
             break;
           }
+          if (fill_wait < 0) fill_wait = in_wait;
           tc_fence_after_sync();
 #pragma unroll
           for (int sub = 0; sub < KSUB; ++sub) {
@@ -608,6 +624,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
           acc = 0;
           acc_phase ^= 1u;
         }
+      }
+      if (prof != nullptr) {
+        prof[1] = t_first, prof[2] = clock64(), prof[3] = in_wait, prof[4] = max(fill_wait, 0ll), prof[5] = out_wait;
+        prof[6] = items;
       }
     }
     __syncwarp();
@@ -682,6 +702,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
   tc_fence_before_sync();
   __syncthreads();
   cluster_sync_all();
+  if (prof != nullptr && threadIdx.x == 0) prof[7] = clock64();
   if (warp == 1) {
     if (*abort_flag) __nanosleep(100000);
     tc_fence_after_sync();
@@ -819,9 +840,11 @@ extern "C" int tjx_gemm_bf16(const void* x, const void* y, void* out, int M, int
   if (pair) {
     int pairs = static_cast<int>(total_items < sm_count() / 2 ? total_items : sm_count() / 2);
     if (g_gemm_cta_limit > 0) pairs = std::max(1, std::min(pairs, g_gemm_cta_limit / 2));
+    p.profile = profile_buffer(2 * pairs);
     if (pbn == 128) return launch_gemm_pair<128, PAIR_STAGES_128, PAIR_KSUB, false>(ma, mb, mc, ma, p, 2 * pairs, s);
     return launch_gemm_pair<PAIR_BN, PAIR_STAGES, PAIR_KSUB, false>(ma, mb, mc, ma, p, 2 * pairs, s);
   }
+  p.profile = profile_buffer(grid);
   if (BN == 256) {
     if (stages == 3) return launch_gemm<256, 3>(ma, mb, mc, p, grid, s);
     return launch_gemm<256, 4>(ma, mb, mc, p, grid, s);
@@ -901,6 +924,7 @@ extern "C" int tjx_all_gather_gemm_bf16(const void* x_own, const void* const* pe
   // CTA per SM, never more CTAs than SMs.
   const long long total_items = static_cast<long long>(n_tiles) * p.sub_m * p.sub_n;
   const int pairs = static_cast<int>(std::min<long long>(total_items, sm_count() / 2));
+  p.profile = profile_buffer(2 * pairs);
   return launch_gemm_pair<PAIR_BN, PAIR_STAGES, PAIR_KSUB, true>(ma, mb, mc, ma_own, p, 2 * pairs,
                                                                 static_cast<cudaStream_t>(stream));
 }

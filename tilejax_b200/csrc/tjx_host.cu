@@ -78,6 +78,14 @@ int* device_status_word() {
   return g_status[dev];
 }
 
+static thread_local long long* g_profile = nullptr;
+static thread_local size_t g_profile_bytes = 0;
+
+long long* profile_buffer(int ctas) {
+  if (g_profile == nullptr || static_cast<size_t>(ctas) * 8 * sizeof(long long) > g_profile_bytes) return nullptr;
+  return g_profile;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -129,6 +137,14 @@ extern "C" {
 int tjx_version(void) { return 100; }
 
 const char* tjx_last_error(void) { return tjx::g_error.c_str(); }
+
+int tjx_set_profile_buffer(void* device_buffer, size_t bytes) {
+  if (device_buffer != nullptr && (reinterpret_cast<uintptr_t>(device_buffer) & 7u) != 0)
+    return tjx::fail(TJX_E_ARG, "the profile buffer must be 8-byte aligned");
+  tjx::g_profile = static_cast<long long*>(device_buffer);
+  tjx::g_profile_bytes = device_buffer == nullptr ? 0 : bytes;
+  return 0;
+}
 
 int tjx_set_wait_limit_us(int microseconds) {
   if (microseconds < 1000 || microseconds > 10000000)

@@ -30,6 +30,9 @@ int sm_count();
 // allocation); the address is looked up once per device.
 int* device_status_word();
 
+// The calling thread's profile buffer (tjx_set_profile_buffer) if it has room for `ctas` records, else null.
+long long* profile_buffer(int ctas);
+
 // Encode a tiled tensor map over a row-major bf16/f32 matrix viewed as `rank` dims (innermost first).
 // dims/box in elements, strides in bytes for dims 1..rank-1. Returns 0 or an error code.
 int make_tensor_map(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, int elem_bytes, int rank,

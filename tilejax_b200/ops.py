@@ -8,6 +8,7 @@ without the built library or an sm_100 GPU the calls raise.
 from __future__ import annotations
 
 import ctypes
+import hashlib
 from functools import lru_cache
 
 import numpy as np
@@ -41,11 +42,13 @@ _table_cache: dict[tuple, torch.Tensor] = {}
 
 
 def device_table(key: tuple, values: np.ndarray, device: torch.device) -> torch.Tensor:
-    """A static int32 table on `device`, uploaded once per (key, device)."""
-    full = (key, str(device))
+    """A static int32 table on `device`, uploaded once per (contents, device). `key` only labels the entry: two
+    kernels whose names and shapes agree but whose masks differ get different tables."""
+    host = np.ascontiguousarray(values, np.int32)
+    full = (key, host.shape, hashlib.blake2b(host.tobytes(), digest_size=16).digest(), str(device))
     t = _table_cache.get(full)
     if t is None:
-        t = torch.from_numpy(np.ascontiguousarray(values, np.int32)).to(device)
+        t = torch.from_numpy(host).to(device)
         _table_cache[full] = t
     return t
 
@@ -109,7 +112,9 @@ def gemm(x: torch.Tensor, y: torch.Tensor, tm: int, tn: int, tk: int, *, causal:
          fill_i: torch.Tensor | None = None, fill_j: torch.Tensor | None = None,
          out: torch.Tensor | None = None) -> torch.Tensor:
     """out = x @ y (or x @ y.T), bf16 operands, f32 accumulation, by tiles of (tm, tn). With tile tables only the
-    listed tiles are computed and the fill tiles are zeroed; other tiles of `out` are left as they are."""
+    listed tiles are computed and the fill tiles are zeroed; other tiles of `out` are left as they are. K is always
+    summed in one order, so a product computed in several launches over row ranges is bit-equal to the same product
+    in one launch (the collective matmul relies on that)."""
     device = _need_cuda(x, y)
     if x.dtype != torch.bfloat16 or y.dtype != torch.bfloat16:
         raise ValueError("x and y must be bfloat16")
@@ -355,12 +360,25 @@ def paged_gqa_decode_static(q: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
     included, is passed in, and the kernels' scratch is the fixed array inside the library
     (tjx_paged_gqa_decode_bf16_static). This wrapper allocates nothing either. Sizes whose scratch would exceed
     the built-in 36 MiB raise; calls that overlap on the GPU race on the shared scratch."""
-    device = _need_cuda(q, k_pages, v_pages, block_tables, lengths, out, step_tile, step_code, step_count, tile_first)
+    if q.dim() != 4 or k_pages.dim() != 3 or block_tables.dim() != 2:
+        raise ValueError("q is (B, T, H, D), the pages (num_pages, page_size, Hkv * D), block_tables (B, pages_per_seq)")
     B, T, H, D = q.shape
     num_pages, page_size, W = k_pages.shape
     pages_per_seq = block_tables.shape[1]
-    if step_tile.numel() < B * pages_per_seq or step_code.numel() < B * pages_per_seq or tile_first.numel() < B + 1:
+    if any(t.dtype != torch.bfloat16 for t in (q, k_pages, v_pages, out)):
+        raise ValueError("q, k_pages, v_pages and out must be bfloat16")
+    if any(t.dtype != torch.int32 for t in (block_tables, lengths, step_tile, step_code, step_count, tile_first)):
+        raise ValueError("block_tables, lengths and the step table buffers must be int32")
+    if out.shape != q.shape:
+        raise ValueError("out must have q's shape (B, T, H, D)")
+    if v_pages.shape != k_pages.shape or W % D != 0:
+        raise ValueError("k_pages and v_pages must both be (num_pages, page_size, Hkv * D)")
+    if block_tables.shape[0] != B or lengths.shape != (B,):
+        raise ValueError("block_tables is (B, pages_per_seq) and lengths (B,)")
+    if step_tile.numel() < B * pages_per_seq or step_code.numel() < B * pages_per_seq or tile_first.numel() < B + 1 \
+            or step_count.numel() < 1:
         raise ValueError("the step table buffers are too small")
+    device = _need_cuda(q, k_pages, v_pages, block_tables, lengths, out, step_tile, step_code, step_count, tile_first)
     with torch.cuda.device(device):
         check(library().tjx_paged_gqa_decode_bf16_static(
             _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_tables), _ptr(lengths), _ptr(out), B, T, H, W // D, D,
