@@ -42,11 +42,12 @@ int tjx_device_status(tjx_stream_t stream, int* code);
 /* In-kernel profile, the counterpart of the trace regions the reference's generated kernels carry
  * (`<kernel>/wait`, `/out_wait`, `/compute`: src/autokernel/profiling.py:1-20, src/autokernel/codegen.py REGIONS).
  * While a buffer is set for the calling thread, every matmul, attention and paged-decode launch from it whose grid
- * fits writes one record of eight int64 per CTA (record i = CTA i; later launches overwrite earlier ones):
+ * fits writes one record of sixteen int64 per CTA (record i = CTA i; later launches overwrite earlier ones):
  *   [0] SM clock at CTA start, [1] when its issuing thread (MMA issuer; decode: warp 0) starts its first work item,
  *   [2] after its last, [3] cycles that thread waited for inputs, [4] of which its first wait (the pipeline
  *   filling), [5] cycles it waited for room for results (accumulator / output slot still draining), [6] work items,
- *   [7] SM clock at CTA end.
+ *   [7] SM clock at CTA end, [8..15] kernel-specific (attention: [8] cycles the MMA thread waited for the softmax
+ *   warps' probabilities).
  * NULL unsets it. The buffer is device memory the caller owns: zero it before a launch to tell which CTAs wrote. */
 int tjx_set_profile_buffer(void* device_buffer, size_t bytes);
 

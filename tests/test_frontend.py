@@ -237,8 +237,10 @@ def test_a_tunable_is_a_frozen_dataclass_of_choices():
         autokernel.choice(1, 2, default=3)
 
 
-def profile(seconds):
-    return KernelProfile(seconds, 0.5, 0.1, 4)
+def profile(seconds, config=None, steps=4, wait=0.0, out_wait=0.0, compute=None, regions=True):
+    """A KernelProfile with these times; `compute` defaults to all of the time not waiting (tests/test_tune.py:44-47)."""
+    compute = seconds - wait - out_wait if compute is None else compute
+    return KernelProfile("f", config, 1, seconds, regions, steps, wait, 0.0, out_wait, compute)
 
 
 def test_search_climbs_to_the_fastest_and_stops():
@@ -260,17 +262,75 @@ def test_search_climbs_to_the_fastest_and_stops():
 
 
 def test_proposals_follow_the_bottleneck():
+    # tests/test_tune.py:97-120, on the matmul nest: what the counters say decides what is tried next.
     kernel = K.matmul
     sig = kernel.signature(spec(2048, 2048), spec(2048, 2048))
     here = Config(K.MatmulTiles(), Pipeline(3, 2))
-    memory_bound = proposals(kernel, sig, Trial(here, KernelProfile(1e-4, 0.2, 0.6, 64)))
-    assert memory_bound[0] == Config(K.MatmulTiles(), Pipeline(4, 2))  # more ring slots first
-    overhead = proposals(kernel, sig, Trial(here, KernelProfile(1e-4, 0.05, 0.05, 64)))
-    assert all(kernel.build(sig, c.tunable)[1].steps < 64 for c in overhead)  # only bigger tiles
+    steps = kernel.build(sig, here.tunable)[1].steps
+    # Exposed input copies: a deeper ring first, then only schedules that move fewer bytes (bigger tiles).
+    dma = proposals(kernel, sig, Trial(here, profile(10.0, here, wait=5.0)))
+    assert dma[0] == Config(K.MatmulTiles(), Pipeline(4, 2))
+    assert dma[1:] and all(c.pipeline == here.pipeline and c.tunable in (K.MatmulTiles(tm=1024), K.MatmulTiles(tn=1024))
+                           for c in dma[1:])
+    # Per-step overhead: bigger tiles only, fewest steps first.
+    overhead = proposals(kernel, sig, Trial(here, profile(10.0, here, compute=1.0)))
+    assert overhead and all(kernel.build(sig, c.tunable)[1].steps < steps for c in overhead)
+    # Compute-bound, or no counters: every neighbour that launches something else, fewest steps first.
+    compute = proposals(kernel, sig, Trial(here, profile(10.0, here)))
+    assert {c.tunable for c in compute} == {K.MatmulTiles(tm=1024), K.MatmulTiles(tn=1024), K.MatmulTiles(tm=256),
+                                            K.MatmulTiles(tn=256)}
+    assert [kernel.build(sig, c.tunable)[1].steps for c in compute] == sorted(
+        kernel.build(sig, c.tunable)[1].steps for c in compute)
+    blind = proposals(kernel, sig, Trial(here, profile(10.0, here, wait=5.0, regions=False)))
+    assert blind == compute
+    # The kernel walks K in its own blocks: a neighbour that only changes tk launches the same thing and is never
+    # proposed; nor is a deeper output buffering, which no kernel here has.
+    assert all(c.tunable.tk == 512 for c in compute)
+    outs = proposals(kernel, sig, Trial(here, profile(10.0, here, out_wait=5.0)))
+    assert all(c.pipeline == here.pipeline for c in outs)
+    # At the deepest ring there is, no deeper one is proposed.
+    deepest = Config(K.MatmulTiles(), Pipeline(4, 2))
+    assert all(c.pipeline == deepest.pipeline for c in proposals(kernel, sig, Trial(deepest, profile(10.0, deepest, wait=3.0))))
     failed = proposals(kernel, sig, Trial(here, error="boom"))
     assert failed[0] == Config(K.MatmulTiles(), Pipeline(2, 2))
     with pytest.raises(KernelError, match="1 to 4 input buffers"):
         Pipeline(5, 1)
+
+
+def test_schedules_that_launch_the_same_kernel_are_not_tuned_over():
+    # The attention kernel visits the same keys whatever the block sizes: nothing to propose, one trial at most.
+    attention = K.causal_attention
+    sig = attention.signature(*[spec(1, 2, 1024, 128)] * 3)
+    here = Config(K.AttentionBlocks(), Pipeline())
+    assert proposals(attention, sig, Trial(here, profile(1.0, here))) == []
+    # Contiguous decode walks blocks of the chosen size: its neighbours are real candidates.
+    decode = K.gqa_decode
+    sig = decode.signature(spec(4, 1, 8, 128), spec(4, 2048, 256), spec(4, 2048, 256), spec(4, dtype=np.int32))
+    here = Config(K.DecodeTiles(), Pipeline())
+    assert {c.tunable.block_kv for c in proposals(decode, sig, Trial(here, profile(1.0, here)))} == {256, 1024}
+
+
+def test_a_profile_names_its_bottleneck():
+    # src/autokernel/profiling.py:128-140: exposed copies above 20 % -> dma; else time outside waits and compute
+    # above 30 % -> overhead; else compute; nothing without counters.
+    assert profile(10.0, wait=2.5).bottleneck == "dma" and profile(10.0, out_wait=2.5).bottleneck == "dma"
+    filling = KernelProfile("f", None, 1, 10.0, True, 4, 2.5, 2.0, 0.0, 7.5)  # most of the wait fills the ring
+    assert filling.exposed_wait_s == 0.5 and filling.bottleneck == "compute"
+    assert profile(10.0, compute=6.0).bottleneck == "overhead" and profile(10.0, compute=6.0).other_s == 4.0
+    assert profile(10.0).bottleneck == "compute" and profile(10.0, regions=False).bottleneck is None
+    text = str(profile(10e-6, Config(None), steps=4, wait=2e-6))
+    assert "input waits" in text and "bottleneck: compute" in text and "4" in text
+    # The counters of three CTAs (one of them without work) as shares of a CTA's lifetime.
+    from tilejax_b200.autokernel.profiling import shares
+
+    records = np.zeros((3, 16), np.int64)
+    records[0, :8] = [100, 150, 1050, 200, 50, 100, 5, 1100]   # lifetime 1000: wait 200 (50 filling), room 100
+    records[1, :8] = [0, 100, 900, 0, 0, 0, 2, 1000]
+    records[2, :8] = [0, 0, 0, 0, 0, 0, 0, 1000]                 # the odd CTA of a pair: no issuing thread
+    found = shares(records)
+    assert found["ctas"] == 2 and found["wait"] == pytest.approx(0.1) and found["fill"] == pytest.approx(0.025)
+    assert found["out_wait"] == pytest.approx(0.05) and found["compute"] == pytest.approx((0.6 + 0.8) / 2)
+    assert found["outside"] == pytest.approx((0.1 + 0.2) / 2) and shares(records[2:]) is None
 
 
 def test_without_a_gpu_tuning_returns_the_defaults(monkeypatch):

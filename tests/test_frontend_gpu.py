@@ -60,3 +60,30 @@ def test_tuning_tries_schedules_and_keeps_the_fastest():
     out = K.matmul(x, y)  # uses the tuned schedule
     oracle.compare("matmul", out, oracle.matmul_ref(x, y, 512, 512, 512))
     assert K.matmul.tuning(x, y) is tuning  # remembered per signature
+
+
+def test_profile_says_where_the_time_goes():
+    # autokernel.profile (src/autokernel/profiling.py:267-274): device time from CUDA events, the split from the
+    # kernels' own counters. The parts are non-negative and add up to the device time.
+    import tilejax_b200.autokernel as autokernel
+
+    x, y = rand_bf16((2048, 2048), 0), rand_bf16((2048, 2048), 1)
+    for tiles in (K.MatmulTiles(), TILES):  # one MMA per pair of SMs, and the single-CTA ring
+        report = autokernel.profile(K.matmul, (x, y, tiles), runs=3)
+        assert report.regions and report.calls == 3 and report.device_s > 0 and report.steps > 0
+        parts = (report.wait_s, report.out_wait_s, report.compute_s, report.other_s)
+        assert all(p >= 0 for p in parts) and sum(parts) == pytest.approx(report.device_s, rel=1e-6)
+        assert report.fill_s <= report.wait_s and report.compute_s > 0
+        assert report.bottleneck in ("dma", "overhead", "compute") and "bottleneck:" in str(report)
+    q, k, v = synthetic.attention_inputs(1, 4, 1024, 128)
+    report = autokernel.profile(K.causal_attention, (q, k, v, K.AttentionBlocks()))
+    assert report.regions and report.compute_s > 0 and "softmax" in report.scopes
+    q, kp, vp, bt, lengths = synthetic.decode_inputs(8, 32, 8, 128, 16, 64, 1024)
+    report = autokernel.profile(K.paged_gqa_decode, (q, kp, vp, bt, lengths))
+    assert report.regions and report.wait_s > 0 and report.steps == 8 * 64
+    # A kernel that carries no counters still reports its device time.
+    lengths4 = np.array([0, 1, 300, 512], np.int32)
+    q_c, q_r = rand_bf16((4, 1, 16, 512), 7, 0.01), rand_bf16((4, 1, 16, 128), 8, 0.07)
+    c_kv, k_rope = rand_bf16((4, 512, 512), 9), rand_bf16((4, 512, 128), 10)
+    blind = autokernel.profile(K.mla_decode, (q_c, q_r, c_kv, k_rope, lengths4, K.DecodeTiles(block_kv=128)))
+    assert not blind.regions and blind.bottleneck is None and blind.device_s > 0

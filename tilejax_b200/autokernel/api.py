@@ -25,7 +25,8 @@ from .errors import KernelError
 from .parse import Nest, parse
 from .plan import Plan, Spec, make_plan
 from .tunable import is_tunable, neighbours
-from .tune import Config, KernelProfile, Pipeline, Tuning, tune
+from .profiling import KernelProfile
+from .tune import Config, Pipeline, Tuning, tune
 
 Signature = tuple[tuple[tuple[int, ...], np.dtype], ...]
 
@@ -124,38 +125,10 @@ class Lowered:
         return tuple(to_host(o) for o in out) if isinstance(out, tuple) else to_host(out)
 
     def profile(self, *inputs, runs: int = 5) -> KernelProfile:
-        """Seconds per call from CUDA events around `runs` launches, and the roofline fractions they imply."""
-        import torch
+        """Seconds per call from CUDA events around `runs` launches, and where they go from the kernel's counters."""
+        from . import profiling
 
-        from ..ops import device_status
-
-        dev = [to_device(x) for x in inputs]
-        self.entry(*dev)
-        torch.cuda.synchronize()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for _ in range(runs):
-            self.entry(*dev)
-        end.record()
-        end.synchronize()
-        device_status()
-        seconds = start.elapsed_time(end) / runs / 1e3
-        flops, nbytes = _work(self.plan, dev)
-        return KernelProfile(seconds, flops / seconds / 1.65e15, nbytes / seconds / 6.5e12, self.steps)
-
-
-def _work(plan: Plan, dev) -> tuple[float, float]:
-    """Algorithmic flops on the tensor pipe and bytes the math needs from HBM, for the roofline fractions."""
-    p = plan.params
-    if plan.family == "gemm":
-        flops = 2.0 * p["M"] * p["N"] * p["K"] * p["schedule"].tiles / max(p["schedule"].total_tiles, 1)
-        return flops, 2.0 * (p["M"] * p["K"] + p["K"] * p["N"] + p["M"] * p["N"])
-    if plan.family == "attention":
-        sch = p["schedule"]
-        per_step = 4.0 * p["block_q"] * p["block_kv"] * p["D"]
-        return per_step * sch.steps, 2.0 * 4 * p["B"] * p["H"] * p["S"] * p["D"]
-    lengths = dev[4]
-    return 0.0, float(lengths.sum().item()) * p["Hkv"] * p["D"] * 2 * 2
+        return profiling.measure(self, inputs, runs)
 
 
 class Kernel:
@@ -164,14 +137,17 @@ class Kernel:
     with them, and remembers the result."""
 
     def __init__(self, fn: Callable[..., Any]) -> None:
+        functools.update_wrapper(self, fn)
         self.fn = fn
         self.nest: Nest = parse(fn)
-        functools.update_wrapper(self, fn)
-        self.default_tunable = fn.__defaults__[-1] if self.nest.tunable else None
-        if self.nest.tunable and not is_tunable(self.default_tunable):
-            raise self.nest.error(
-                f"`{self.nest.tunable}`'s default must be an @autokernel.tunable, not {self.default_tunable!r}",
-                self.nest.function.args)
+        self.default_tunable = None
+        if self.nest.tunable is not None:
+            self.default_tunable = (fn.__defaults__ or (None,))[-1]
+            if not is_tunable(self.default_tunable):
+                raise self.nest.error(
+                    f"`{self.nest.tunable}`'s default must be an @autokernel.tunable, not {self.default_tunable!r}",
+                    self.nest.function.args)
+        # What has been planned, bound to a launch and tuned so far, each keyed by the inputs' signature.
         self._builds: dict = {}
         self._lowered: dict = {}
         self._tunings: dict = {}
@@ -180,16 +156,18 @@ class Kernel:
         return f"<autokernel.Kernel {self.nest.name}>"
 
     def __call__(self, *args: Any) -> Any:
-        arrays, _ = self._split(args)
-        return self.lower(*args).run(*arrays)
+        return self.lower(*args).run(*self._split(args)[0])
 
     def lower(self, *args: Any) -> Lowered:
+        """The kernel for inputs like these (arrays or `Spec`s), and the tunable if given."""
         arrays, tunable = self._split(args)
         signature = self.signature(*arrays)
-        if tunable is None:
-            return self.lowered(signature, self.tuning(*arrays).config)
-        self.build(signature, tunable)
-        return self.lowered(signature, Config(tunable, Pipeline()))
+        if tunable is not None:
+            self.build(signature, tunable)  # a KernelError here names the user's line
+            config = Config(tunable, Pipeline())
+        else:
+            config = self.tuning(*arrays).config
+        return self.lowered(signature, config)
 
     def source(self, *args: Any) -> str:
         return self.lower(*args).source
@@ -197,71 +175,68 @@ class Kernel:
     def reference(self, *args: Any) -> Any:
         """What the kernel computes: the loop nest run as written on the CPU, with `@` accumulating in f32."""
         arrays, tunable = self._split(args)
-        if self.nest.tunable and tunable is None:
-            tunable = self.lower(*arrays).config.tunable
-        host = [jaxlike.Array(to_host(x)) for x in arrays]
+        call = [jaxlike.Array(to_host(x)) for x in arrays]
+        if self.nest.tunable is not None:
+            call.append(tunable if tunable is not None else self.lower(*arrays).config.tunable)
         with jaxlike.mxu_semantics():
-            out = self.fn(*host, tunable) if self.nest.tunable else self.fn(*host)
-        return tuple(to_host(o) for o in out) if isinstance(out, tuple) else to_host(out)
+            result = self.fn(*call)
+        return tuple(map(to_host, result)) if isinstance(result, tuple) else to_host(result)
 
     def verify(self, *args: Any, rtol: float | None = None, atol: float | None = None) -> float:
         """Run the kernel and its reference; AssertionError unless they agree within the tolerances for the dtypes
         (or `rtol` / `atol`). Returns the largest absolute difference."""
         arrays, tunable = self._split(args)
-        if self.nest.tunable:
-            tunable = tunable if tunable is not None else self.lower(*arrays).config.tunable
-            full = (*arrays, tunable)
-        else:
-            full = arrays
-        got, want = self(*full), self.reference(*full)
+        call = tuple(arrays)
+        if self.nest.tunable is not None:
+            call += (tunable if tunable is not None else self.lower(*arrays).config.tunable,)
+        got, want = self(*call), self.reference(*call)
+        if not isinstance(got, tuple):
+            got, want = (got,), (want,)
         dtypes = tuple(dtype for _, dtype in self.signature(*arrays)[: len(self.nest.inputs)])
-        got, want = (got, want) if isinstance(got, tuple) else ((got,), (want,))
-        return max(compare(f"{self.nest.name} output {name!r}", to_host(g), w, rtol, atol, dtypes)
-                   for name, g, w in zip(self.nest.outputs, got, want, strict=True))
+        worst = 0.0
+        for name, g, w in zip(self.nest.outputs, got, want, strict=True):
+            worst = max(worst, compare(f"{self.nest.name} output {name!r}", to_host(g), w, rtol, atol, dtypes))
+        return worst
 
     def tuning(self, *arrays: Any) -> Tuning:
+        """The schedule for inputs like these: tuned on the GPU when first asked, the defaults elsewhere."""
         signature = self.signature(*arrays)
-        if signature not in self._tunings:
-            self._tunings[signature] = tune(self, signature, arrays)
-        return self._tunings[signature]
+        found = self._tunings.get(signature)
+        if found is None:
+            found = self._tunings[signature] = tune(self, signature, arrays)
+        return found
 
     # ------------------------------------------------------------------ building (used by tune.py too)
 
     def signature(self, *arrays: Any) -> Signature:
-        signature = []
-        for name, x in zip(self.nest.inputs, arrays, strict=True):
-            if not (hasattr(x, "shape") and hasattr(x, "dtype")) or not tuple(x.shape):
+        """What the kernel is built for: each input's (shape, dtype), then each gathered array's (its input's rows
+        times the ranks it is gathered over)."""
+        names = self.nest.inputs
+        if len(arrays) != len(names):
+            raise KernelError(f"{self.nest.name} takes {len(names)} input arrays ({', '.join(names)}); got {len(arrays)}")
+        entries: list[tuple[tuple[int, ...], np.dtype]] = []
+        for name, x in zip(names, arrays):
+            shape = tuple(int(d) for d in getattr(x, "shape", ()))
+            if not shape or not hasattr(x, "dtype"):
                 raise KernelError(f"{self.nest.name}: input `{name}` must be an array, got {type(x).__name__}")
-            signature.append((tuple(int(s) for s in x.shape), _np_dtype(x)))
+            entries.append((shape, _np_dtype(x)))
         for gather in self.nest.all_gathers:
-            (rows, *rest), dtype = signature[self.nest.inputs.index(gather.source)]
-            signature.append(((rows * collective.axis_size(gather.axis), *rest), dtype))
-        return tuple(signature)
+            shape, dtype = entries[names.index(gather.source)]
+            entries.append(((shape[0] * collective.axis_size(gather.axis), *shape[1:]), dtype))
+        return tuple(entries)
 
     def default_config(self, signature: Signature) -> Config:
-        """The schedule to start from: the tunable's defaults, or the nearest tunable that builds."""
-        tunable = self.default_tunable
-        try:
-            self.build(signature, tunable)
+        """The schedule to start from: the tunable's defaults or, if they do not build for these inputs, the
+        tunable the fewest single-field steps away that does (ties in the order `neighbours` lists them)."""
+        first_error = None
+        for tunable in _outwards(self.default_tunable):
+            try:
+                self.build(signature, tunable)
+            except KernelError as e:
+                first_error = first_error or e
+                continue
             return Config(tunable, Pipeline())
-        except KernelError:
-            if tunable is None:
-                raise
-            seen, frontier = {tunable}, [tunable]
-            while frontier:
-                later = []
-                for t in frontier:
-                    for n in neighbours(t):
-                        if n in seen:
-                            continue
-                        seen.add(n)
-                        try:
-                            self.build(signature, n)
-                            return Config(n, Pipeline())
-                        except KernelError:
-                            later.append(n)
-                frontier = later
-            raise
+        raise first_error
 
     def build(self, signature: Signature, tunable: Any, cursor: bool = False):
         """(plan, schedule) for this signature and tunable; KernelError if the nest is not a recognised schedule or
@@ -285,19 +260,39 @@ class Kernel:
         return self._lowered[key]
 
     def _split(self, args: tuple[Any, ...]) -> tuple[tuple[Any, ...], Any]:
-        n = len(self.nest.inputs)
-        if self.nest.tunable and len(args) == n + 1:
-            tunable = args[-1]
-            if type(tunable) is not type(self.default_tunable):
-                raise KernelError(
-                    f"{self.nest.name}: `{self.nest.tunable}` must be a {type(self.default_tunable).__name__}, "
-                    f"not {type(tunable).__name__}")
-            return args[:-1], tunable
-        if len(args) != n:
-            more = f", then optionally `{self.nest.tunable}`" if self.nest.tunable else ""
+        """(the input arrays, the tunable or None) of a call's arguments."""
+        inputs, name = self.nest.inputs, self.nest.tunable
+        with_tunable = name is not None and len(args) == len(inputs) + 1
+        if len(args) != len(inputs) and not with_tunable:
+            optional = f", then optionally `{name}`" if name is not None else ""
             raise KernelError(
-                f"{self.nest.name} takes {n} input arrays ({', '.join(self.nest.inputs)}){more}; got {len(args)}")
-        return args, None
+                f"{self.nest.name} takes {len(inputs)} input arrays ({', '.join(inputs)}){optional}; got {len(args)}")
+        if not with_tunable:
+            return tuple(args), None
+        *arrays, tunable = args
+        wanted = type(self.default_tunable)
+        if type(tunable) is not wanted:
+            raise KernelError(
+                f"{self.nest.name}: `{name}` must be a {wanted.__name__}, not {type(tunable).__name__}")
+        return tuple(arrays), tunable
+
+
+def _outwards(tunable: Any):
+    """`tunable`, then every tunable reachable from it by single-field steps, nearest first (None yields itself)."""
+    yield tunable
+    if tunable is None:
+        return
+    reached = {tunable}
+    ring = [tunable]
+    while ring:
+        next_ring = []
+        for centre in ring:
+            for other in neighbours(centre):
+                if other not in reached:
+                    reached.add(other)
+                    next_ring.append(other)
+                    yield other
+        ring = next_ring
 
 
 def kernel(fn: Callable[..., Any]) -> Kernel:
@@ -353,6 +348,22 @@ def _stages(pipeline: Pipeline, tn: int) -> int:
     if pipeline.input_buffers == 3:
         return 0
     return 4 if wide else 6
+
+
+def launch_key(plan: Plan, config: Config) -> tuple:
+    """What a schedule makes the C ABI launch, as a hashable key: schedules with equal keys run the same kernel on the
+    same tiles and differ in nothing that can be timed. The matmul kernels walk K in their own blocks of 64 (`tk` is
+    not part of the key) and only their single-CTA ring has a depth (`output_buffers` never is); the attention
+    kernel works in 128 x 128 blocks cut at each tile's diagonal whatever the user's blocks; paged decode reads the
+    pages as they are; contiguous and MLA decode walk blocks of the chosen size."""
+    p = plan.params
+    if plan.family == "gemm":
+        return ("gemm", p["tm"], p["tn"], _stages(config.pipeline, p["tn"]), p["causal"], p["transposed"])
+    if plan.family == "attention":
+        return ("attention",)
+    if p.get("mla") or p.get("contiguous"):
+        return ("decode", p["page"])
+    return ("decode",)
 
 
 def _lower(plan: Plan, config: Config) -> tuple[str, Callable[..., Any]]:
@@ -441,38 +452,50 @@ def _lower(plan: Plan, config: Config) -> tuple[str, Callable[..., Any]]:
 
 def compare(what: str, got: Any, want: Any, rtol: float | None = None, atol: float | None = None,
             inputs: tuple[Any, ...] = ()) -> float:
-    """The largest absolute difference between `got` and `want`; AssertionError beyond `rtol` and `atol` (default:
-    exact for integers, 1e-4 for f32, 2e-2 of the largest value for 16-bit results and for f32 results computed
-    from 16-bit inputs). NaN equals NaN. The reference's rule, src/autokernel/api.py:320-364."""
+    """The largest absolute difference between `got` and `want`; AssertionError beyond `rtol` and `atol`. Defaults:
+    exact for integers; 1e-4 for f32; for 16-bit results, and f32 results computed from 16-bit `inputs`, 2e-2
+    relative and 2e-2 of the largest finite |want| absolute. NaN equals NaN. The arrays are walked in pieces of
+    COMPARE_CHUNK elements so that float64 copies of a multi-GB output never exist at once. The reference's rule
+    (src/autokernel/api.py:320-364), message included."""
     got, want = to_host(got), to_host(want)
-    dtype = np.dtype(want.dtype)
 
-    def floating(d) -> bool:
+    def is_float(d) -> bool:
         d = np.dtype(d)
         return d.kind == "f" or d == _bf16()
 
-    narrow = any(floating(d) and np.dtype(d).itemsize <= 2 for d in inputs)
-    default = 0.0 if not floating(dtype) else (2e-2 if dtype.itemsize <= 2 or narrow else 1e-4)
+    if not is_float(want.dtype):
+        loose, default = False, 0.0
+    else:
+        loose = np.dtype(want.dtype).itemsize <= 2 or any(is_float(d) and np.dtype(d).itemsize <= 2 for d in inputs)
+        default = 2e-2 if loose else 1e-4
     rtol = default if rtol is None else rtol
-    got_all, want_all = got.reshape(-1), want.reshape(-1)
-    chunks = range(0, want_all.size, COMPARE_CHUNK)
+    flat_got, flat_want = got.reshape(-1), want.reshape(-1)
+
+    def pieces():
+        for lo in range(0, flat_want.size, COMPARE_CHUNK):
+            yield (flat_got[lo : lo + COMPARE_CHUNK].astype(np.float64), flat_want[lo : lo + COMPARE_CHUNK].astype(np.float64))
+
     if atol is None:
-        scale = 1.0
-        if default >= 2e-2:
-            for start in chunks:
-                w = want_all[start : start + COMPARE_CHUNK].astype(np.float64)
-                scale = max(scale, float(np.max(np.abs(w), where=np.isfinite(w), initial=0.0)))
-        atol = default * scale
-    error, differ = 0.0, 0
-    for start in chunks:
-        g = got_all[start : start + COMPARE_CHUNK].astype(np.float64)
-        w = want_all[start : start + COMPARE_CHUNK].astype(np.float64)
-        same = (g == w) | (np.isnan(g) & np.isnan(w))
+        largest = 1.0
+        if loose:  # 16-bit results round at every step: the error grows with the output's magnitude
+            for _, w in pieces():
+                finite = np.abs(w[np.isfinite(w)])
+                if finite.size:
+                    largest = max(largest, float(finite.max()))
+        atol = default * largest
+    worst, mismatched = 0.0, 0
+    for g, w in pieces():
+        both_nan = np.isnan(g) & np.isnan(w)
+        equal = (g == w) | both_nan
         with np.errstate(invalid="ignore"):
-            error = max(error, float(np.max(np.abs(np.where(same, 0.0, g - w)), initial=0.0)))
-        differ += int(np.sum(~np.isclose(g, w, rtol=rtol, atol=atol, equal_nan=True)))
-    if differ:
+            gap = np.abs(g - w)
+            within = equal | (np.isfinite(w) & (gap <= atol + rtol * np.abs(w)))
+        gap[equal] = 0.0
+        if gap.size:
+            worst = max(worst, float(np.nanmax(gap)) if not np.all(np.isnan(gap)) else 0.0)
+        mismatched += int(np.count_nonzero(~within))
+    if mismatched:
         raise AssertionError(
-            f"{what}: the kernel and its reference differ in {differ} of {want_all.size} elements "
-            f"(largest difference {error:.3g}; rtol={rtol}, atol={atol:.3g})")
-    return error
+            f"{what}: the kernel and its reference differ in {mismatched} of {flat_want.size} elements "
+            f"(largest difference {worst:.3g}; rtol={rtol}, atol={atol:.3g})")
+    return worst

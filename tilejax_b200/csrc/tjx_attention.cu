@@ -51,6 +51,7 @@ struct AttnParams {
   int total_units;
   __nv_bfloat16* out;
   int* status;
+  long long* profile;  // per-CTA counters (PROFILE_WORDS each) or null
 };
 
 constexpr int AT_MAX_TILES = 1024;  // user query tiles per (b, h) whose last key block is cached in shared memory
@@ -80,6 +81,9 @@ __device__ __forceinline__ int slot_blocks(const AttnParams& p, const int* last_
   return keys / AT_BKV;
 }
 
+// PROFILE: the instantiation a launch with a profile buffer runs; it alone reads the clock and keeps the counters
+// (they cost the softmax warps registers they do not have to spare: 7 % of the kernel's time when always on).
+template <bool PROFILE>
 __global__ void __launch_bounds__(AT_THREADS, 1)
     attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                      const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
@@ -112,6 +116,9 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
     return i < p.total_units ? i : -1;
   };
 
+  long long* prof = !PROFILE || p.profile == nullptr ? nullptr
+                        : p.profile + static_cast<size_t>(blockIdx.x) * PROFILE_WORDS;
+  if (PROFILE && prof != nullptr && threadIdx.x == 0) prof[0] = clock64();
   if (threadIdx.x == 0) {
     for (int i = 0; i < N_BARS; ++i) {
       const bool softmax_bar = i == 12 || i == 13;  // p_ready: one arrival per softmax warp
@@ -233,14 +240,17 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
         mma_commit(o_done(t));
       };
       bool ok = true;
+      long long t_first = 0, in_wait = 0, fill_wait = -1, p_wait = 0, units = 0;
       for (int k = 0; ok; ++k) {
         const int i = unit_at(k);
         if (i < 0) break;
         const Unit u = describe(i);
+        if (PROFILE && units++ == 0) t_first = clock64();
         for (int t = 0; t < 2 && ok; ++t)
-          if (u.n_slot[t] > 0) ok = mbar_wait(q_full(t), used[t] & 1, abort_flag, p.status, TJX_ERR_WAIT_FULL);
+          if (u.n_slot[t] > 0) ok = mbar_wait_timed(q_full(t), used[t] & 1, abort_flag, p.status, TJX_ERR_WAIT_FULL, in_wait, PROFILE && prof != nullptr);
         if (ok && u.n_blocks > 0) {
-          ok = mbar_wait(k_full(g0 % AT_STAGES), (g0 / AT_STAGES) & 1, abort_flag, p.status, TJX_ERR_WAIT_FULL);
+          ok = mbar_wait_timed(k_full(g0 % AT_STAGES), (g0 / AT_STAGES) & 1, abort_flag, p.status, TJX_ERR_WAIT_FULL, in_wait, PROFILE && prof != nullptr);
+          if (PROFILE && fill_wait < 0) fill_wait = in_wait;
           if (ok) {
             tc_fence_after_sync();
             for (int t = 0; t < 2; ++t)
@@ -254,7 +264,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
         for (int n = 0; n < u.n_blocks && ok; ++n) {
           const int gn = g0 + n;
           const int stage = gn % AT_STAGES;
-          if (!mbar_wait(v_full(stage), (gn / AT_STAGES) & 1, abort_flag, p.status, TJX_ERR_WAIT_FULL)) {
+          if (!mbar_wait_timed(v_full(stage), (gn / AT_STAGES) & 1, abort_flag, p.status, TJX_ERR_WAIT_FULL, in_wait, PROFILE && prof != nullptr)) {
             ok = false;
             break;
           }
@@ -263,7 +273,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
             if (n >= u.n_slot[t]) continue;
             // Softmax warps reach block 0 of a unit only after their epilogue of the previous one, so this wait
             // also covers "O of the previous unit has been read".
-            if (!mbar_wait(p_ready(t), (done[t] + n) & 1, abort_flag, p.status, TJX_ERR_WAIT_OTHER)) {
+            if (!mbar_wait_timed(p_ready(t), (done[t] + n) & 1, abort_flag, p.status, TJX_ERR_WAIT_OTHER, p_wait, PROFILE && prof != nullptr)) {
               ok = false;
               break;
             }
@@ -272,7 +282,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
             if (n + 1 < u.n_slot[t]) {
               if (!next_k_waited) {
                 const int ns = (gn + 1) % AT_STAGES;
-                if (!mbar_wait(k_full(ns), ((gn + 1) / AT_STAGES) & 1, abort_flag, p.status, TJX_ERR_WAIT_FULL)) {
+                if (!mbar_wait_timed(k_full(ns), ((gn + 1) / AT_STAGES) & 1, abort_flag, p.status, TJX_ERR_WAIT_FULL, in_wait, PROFILE && prof != nullptr)) {
                   ok = false;
                   break;
                 }
@@ -293,6 +303,10 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
           done[t] += u.n_slot[t];
           if (u.n_slot[t] > 0) ++used[t];
         }
+      }
+      if (PROFILE && prof != nullptr) {
+        prof[1] = t_first, prof[2] = clock64(), prof[3] = in_wait, prof[4] = max(fill_wait, 0ll), prof[5] = 0;
+        prof[6] = units, prof[8] = p_wait;
       }
     }
     __syncwarp();
@@ -437,6 +451,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
 
   tc_fence_before_sync();
   __syncthreads();
+  if (PROFILE && prof != nullptr && threadIdx.x == 0) prof[7] = clock64();
   if (warp == 1) {
     if (*abort_flag) __nanosleep(100000);
     tc_fence_after_sync();
@@ -486,11 +501,16 @@ extern "C" int tjx_causal_attention_bf16(const void* q, const void* k, const voi
   int dev = 0;
   TJX_CUDA(cudaGetDevice(&dev));
   if (!configured[dev & 63]) {
-    TJX_CUDA(cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem::TOTAL));
+    TJX_CUDA(cudaFuncSetAttribute(attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem::TOTAL));
+    TJX_CUDA(cudaFuncSetAttribute(attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem::TOTAL));
     configured[dev & 63] = true;
   }
   const int grid = std::min(p.total_units, sm_count());
-  attention_kernel<<<grid, AT_THREADS, AttnSmem::TOTAL, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, p);
+  p.profile = profile_buffer(grid);
+  if (p.profile != nullptr)
+    attention_kernel<true><<<grid, AT_THREADS, AttnSmem::TOTAL, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, p);
+  else
+    attention_kernel<false><<<grid, AT_THREADS, AttnSmem::TOTAL, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, p);
   TJX_CUDA(cudaGetLastError());
   return 0;
 }

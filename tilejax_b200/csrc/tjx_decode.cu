@@ -78,6 +78,7 @@ struct DecodeParams {
   int T, rows;                   // new tokens per sequence; query rows per sequence = T * H (row t * H + h)
   int self_steps;                // != 0: derive the steps from `lengths` in the prologue instead of reading the tables
   int* status;
+  long long* profile;            // per-CTA counters (PROFILE_WORDS each) or null
 };
 
 
@@ -165,6 +166,10 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, WIDE ? (TJX_DEC_CTAS * 2 / 3) 
   __shared__ int dec_abort;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kvh = blockIdx.y * DEC_WARPS + warp;
+  long long* prof = p.profile == nullptr ? nullptr
+                        : p.profile + (static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * PROFILE_WORDS;
+  long long in_wait = 0, fill_wait = -1, t_first = 0;
+  if (prof != nullptr && threadIdx.x == 0) prof[0] = clock64();
   if (threadIdx.x == 0) {
     for (int i = 0; i < DEC_WARPS * DEC_STAGES; ++i) mbar_init(smem_u32(&dec_bars[i]), 1);
     dec_abort = 0;
@@ -398,7 +403,9 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, WIDE ? (TJX_DEC_CTAS * 2 / 3) 
         next_data(pf_step, pf_sub, pf_step, pf_sub);
       }
       const int stage = n % DEC_STAGES;
-      const bool got = mbar_wait(bar(stage), (n / DEC_STAGES) & 1, &dec_abort, p.status, TJX_ERR_WAIT_FULL);
+      if (n == 0) t_first = clock64();
+      const bool got = mbar_wait_timed(bar(stage), (n / DEC_STAGES) & 1, &dec_abort, p.status, TJX_ERR_WAIT_FULL, in_wait, prof != nullptr);
+      if (fill_wait < 0) fill_wait = in_wait;
       if (!__all_sync(0xFFFFFFFFu, got)) {
         ok = false;
         break;
@@ -473,7 +480,12 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, WIDE ? (TJX_DEC_CTAS * 2 / 3) 
     }
   }
   }  // 32 steps of the share
+  const long long t_last = clock64();
   if (ok) flush();
+  if (prof != nullptr && threadIdx.x == 0) {
+    prof[1] = t_first, prof[2] = t_last, prof[3] = in_wait, prof[4] = max(fill_wait, 0ll), prof[5] = 0, prof[6] = n;
+    prof[7] = clock64();
+  }
   asm volatile("griddepcontrol.wait;" ::: "memory");  // never outlive the step-table kernel's writes unordered
 }
 
@@ -526,6 +538,7 @@ static int launch_decode_chunks(DecodeParams& p, int group, cudaStream_t s) {
   // contiguous share of the steps that run.
   const int resident = sm_count() * (wide ? TJX_DEC_CTAS * 2 / 3 : TJX_DEC_CTAS);
   dim3 grid(std::max(1, std::min(chunks, resident / groups)), groups);
+  p.profile = profile_buffer(static_cast<int>(grid.x * grid.y));
   switch (group) {
     case 1: return wide ? launch_chunks_for<1, true>(mk, mv, p, grid, s) : launch_chunks_for<1, false>(mk, mv, p, grid, s);
     case 2: return wide ? launch_chunks_for<2, true>(mk, mv, p, grid, s) : launch_chunks_for<2, false>(mk, mv, p, grid, s);

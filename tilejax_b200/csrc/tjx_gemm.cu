@@ -291,11 +291,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         const Item it = decode_item<BM, BN>(p, w);
         if (!it.compute) continue;
         if (items++ == 0) t_first = clock64();
-        if (!mbar_wait_timed(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, TJX_ERR_WAIT_TMEM_EMPTY, out_wait)) break;
+        if (!mbar_wait_timed(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, TJX_ERR_WAIT_TMEM_EMPTY, out_wait, prof != nullptr)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait_timed(full_bar(stage), phase, abort_flag, p.status, TJX_ERR_WAIT_FULL, in_wait)) {
+          if (!mbar_wait_timed(full_bar(stage), phase, abort_flag, p.status, TJX_ERR_WAIT_FULL, in_wait, prof != nullptr)) {
             ok = false;
             break;
           }
@@ -587,11 +587,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
         const Item it = decode_item<PAIR_ROWS, BN>(p, w);
         if (!it.compute) continue;
         if (items++ == 0) t_first = clock64();
-        if (!mbar_wait_timed(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, TJX_ERR_WAIT_TMEM_EMPTY, out_wait)) break;
+        if (!mbar_wait_timed(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, TJX_ERR_WAIT_TMEM_EMPTY, out_wait, prof != nullptr)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int slot = 0; slot < num_slots; ++slot) {
-          if (!mbar_wait_timed(full_bar(stage), phase, abort_flag, p.status, TJX_ERR_WAIT_FULL, in_wait)) {
+          if (!mbar_wait_timed(full_bar(stage), phase, abort_flag, p.status, TJX_ERR_WAIT_FULL, in_wait, prof != nullptr)) {
             ok = false;
             break;
           }

@@ -82,7 +82,7 @@ static thread_local long long* g_profile = nullptr;
 static thread_local size_t g_profile_bytes = 0;
 
 long long* profile_buffer(int ctas) {
-  if (g_profile == nullptr || static_cast<size_t>(ctas) * 8 * sizeof(long long) > g_profile_bytes) return nullptr;
+  if (g_profile == nullptr || static_cast<size_t>(ctas) * 16 * sizeof(long long) > g_profile_bytes) return nullptr;
   return g_profile;
 }
 

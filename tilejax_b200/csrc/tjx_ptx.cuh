@@ -102,23 +102,25 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
-// The same wait with the cycles it lasted added to `waited` (nothing is read from the clock when the barrier is
-// already through): what the in-kernel profile counts as time blocked on inputs, on the epilogue, on the tensor pipe.
+// The same wait with the cycles it lasted added to `waited` when `timed` (a launch with a profile buffer): what the
+// in-kernel profile counts as time blocked on inputs, on the epilogue, on the softmax. The clock is read around the
+// whole wait — mbarrier.try_wait may itself suspend the thread for a while before it answers.
 __device__ __forceinline__ bool mbar_wait_timed(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                                int code, long long& waited) {
-  if (mbar_try_wait(bar, parity)) return true;
+                                                int code, long long& waited, bool timed) {
+  if (!timed) return mbar_wait(bar, parity, abort_flag, status, code);
   const long long t0 = clock64();
   const bool ok = mbar_wait(bar, parity, abort_flag, status, code);
   waited += clock64() - t0;
   return ok;
 }
 
-// One CTA's record in the profile buffer (tjx_set_profile_buffer): eight 64-bit words.
+// One CTA's record in the profile buffer (tjx_set_profile_buffer): sixteen 64-bit words.
 //   [0] clock at CTA start   [1] clock when the issuing thread starts its first work item   [2] clock after its last
 //   [3] cycles it waited for inputs (ring slots to fill)   [4] of which the first wait: the pipeline filling
 //   [5] cycles it waited for room for its results (accumulator or output slot still being drained)
 //   [6] work items it ran   [7] clock at CTA end
-constexpr int PROFILE_WORDS = 8;
+//   [8..15] kernel-specific (attention: [8] cycles the MMA thread waited for the softmax warps' probabilities)
+constexpr int PROFILE_WORDS = 16;
 
 // ---------------------------------------------------------------------------------------------- fences
 
