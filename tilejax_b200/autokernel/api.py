@@ -251,6 +251,16 @@ class Kernel:
             self._builds[key] = (plan, plan.params["schedule"])
         return self._builds[key]
 
+    def schedule_of(self, *arrays: Any, tunable: Any = None):
+        """The schedule (tiles, steps, tables) of this loop nest for inputs like these, whether or not a kernel here
+        can run it: what `make_schedule` makes of its loops and masks (src/autokernel/schedule.py:147-220)."""
+        from . import plan as _plan
+
+        signature = self.signature(*arrays)
+        specs = [Spec(shape, dtype) for shape, dtype in signature[: len(self.nest.inputs)]]
+        tunable = tunable if tunable is not None else self.default_tunable
+        return _plan.schedule_only(self.nest, self.fn, specs, tunable)
+
     def lowered(self, signature: Signature, config: Config, trace: bool = False) -> Lowered:
         key = (signature, config)
         if key not in self._lowered:

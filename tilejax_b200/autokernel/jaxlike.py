@@ -217,7 +217,7 @@ def _broadcasted_iota(dtype, shape, dimension):
 
 numpy = types.SimpleNamespace(
     float32=np.float32, float64=np.float64, int32=np.int32, int8=np.int8, uint32=np.uint32, bool_=np.bool_,
-    bfloat16=ml_dtypes.bfloat16, float16=np.float16, ndarray=Array,
+    bfloat16=ml_dtypes.bfloat16, float16=np.float16, ndarray=Array, inf=np.inf, nan=np.nan, pi=np.pi,
     asarray=lambda x, dtype=None: Array(np.asarray(_raw(x), dtype)),
     array=lambda x, dtype=None: Array(np.asarray(_raw(x), dtype)),
     zeros=lambda shape, dtype=None: Array(np.zeros(shape, dtype or np.float32)),
@@ -226,9 +226,11 @@ numpy = types.SimpleNamespace(
     where=_where, exp=_lift(np.exp), maximum=_lift(np.maximum), minimum=_lift(np.minimum),
     max=_lift(np.max), sum=_lift(np.sum), tile=_lift(np.tile), concatenate=_concatenate,
     arange=_lift(np.arange), clip=_lift(np.clip), dot=_dot, matmul=_matmul, tril=_lift(np.tril),
-    abs=_lift(np.abs), logical_not=_lift(np.logical_not),
+    abs=_lift(np.abs), logical_not=_lift(np.logical_not), sqrt=_lift(np.sqrt), mean=_lift(np.mean),
+    square=_lift(np.square), transpose=_lift(np.transpose), reshape=_lift(np.reshape),
 )
-lax = types.SimpleNamespace(broadcasted_iota=_broadcasted_iota)
+lax = types.SimpleNamespace(broadcasted_iota=_broadcasted_iota,
+                            rsqrt=_lift(lambda x: (1.0 / np.sqrt(np.asarray(x, np.float64))).astype(np.asarray(x).dtype)))
 
 
 def to_numpy(x) -> np.ndarray:

@@ -40,19 +40,7 @@ class Spec:
         return len(self.shape)
 
 
-@dataclass(frozen=True)
-class Range:
-    var: str
-    start: int
-    stop: int
-    step: int
-
-    @property
-    def count(self) -> int:
-        return max(0, -(-(self.stop - self.start) // self.step))
-
-    def value(self, block: int) -> int:
-        return self.start + block * self.step
+Range = _schedule.Range  # one `for var in range(start, stop, step)` loop
 
 
 @dataclass(frozen=True)
@@ -94,7 +82,20 @@ def _namespace(fn) -> dict[str, Any]:
     return ns
 
 
+def schedule_only(nest: Nest, fn, specs: list[Spec], tunable: Any, chips: int = 1) -> _schedule.Schedule:
+    """The nest's schedule without asking whether a kernel can run it."""
+    ns, _, _, parallel, reductions = _run_prologue(nest, fn, specs, tunable, chips, need_outputs=False)
+    return nest_schedule(nest, ns, parallel, reductions)
+
+
 def make_plan(nest: Nest, fn, specs: list[Spec], tunable: Any, chips: int = 1) -> Plan:
+    ns, all_specs, outputs, parallel, reductions = _run_prologue(nest, fn, specs, tunable, chips)
+    return _recognise(nest, ns, all_specs, outputs, parallel, reductions, chips)
+
+
+def _run_prologue(nest: Nest, fn, specs: list[Spec], tunable: Any, chips: int = 1, need_outputs: bool = True):
+    """Run the code before the loops on shapes alone and turn the loops' ranges into integers: (namespace, specs of
+    inputs and gathered arrays, output specs, parallel ranges, reduction ranges)."""
     ns = _namespace(fn)
     for name, spec in zip(nest.inputs, specs, strict=True):
         ns[name] = spec
@@ -119,6 +120,8 @@ def make_plan(nest: Nest, fn, specs: list[Spec], tunable: Any, chips: int = 1) -
     outputs = []
     for name in nest.outputs:
         if not isinstance(ns.get(name), Spec):
+            if not need_outputs:
+                continue
             raise nest.error(f"output `{name}` must be allocated with jnp.zeros or jnp.full", nest.allocations[name])
         outputs.append(ns[name])
 
@@ -140,9 +143,7 @@ def make_plan(nest: Nest, fn, specs: list[Spec], tunable: Any, chips: int = 1) -
         return tuple(out)
 
     parallel, reductions = ranges(nest.parallel), ranges(nest.reductions)
-    all_specs = tuple(specs) + tuple(gathered.values())
-    plan = _recognise(nest, ns, all_specs, tuple(outputs), parallel, reductions, chips)
-    return plan
+    return ns, tuple(specs) + tuple(gathered.values()), tuple(outputs), parallel, reductions
 
 
 def _exec(nest: Nest, stmt: ast.stmt, ns: dict) -> None:
@@ -194,6 +195,41 @@ def _mask_fn(nest, ns, mask: ast.expr, names: list[str]):
         return bool(eval(code, ns, dict(zip(names, values, strict=True))))
 
     return holds
+
+
+def _loop_names_read(mask: ast.expr, loop_vars: set[str]) -> frozenset[str]:
+    return frozenset(n.id for n in ast.walk(mask) if isinstance(n, ast.Name) and n.id in loop_vars)
+
+
+def nest_schedule(nest: Nest, ns, parallel, reductions) -> _schedule.Schedule:
+    """The schedule of any parsed nest — recognised family or not — from its loops and masks: static masks are
+    evaluated here through `schedule.make_schedule` (src/autokernel/schedule.py:147-220); a mask that reads an index
+    array makes it a runtime schedule, whose tables the device builds."""
+    if nest.runtime_masks:
+        return _schedule.runtime_schedule(parallel, reductions)
+    loop_vars = {r.var for r in (*parallel, *reductions)}
+    masks = []
+    for loop in (*nest.parallel, *nest.reductions):
+        if loop.mask is None:
+            continue
+        code = compile(ast.Expression(loop.mask), nest.filename, "eval")
+
+        def holds(values, code=code, node=loop.mask) -> bool:
+            try:
+                result = eval(code, ns, dict(values))
+            except NameError as e:
+                raise nest.error(f"can't evaluate `{e.name}` in a mask: masks read loop variables and constants", node) from e
+            try:
+                return bool(result)
+            except Exception as e:
+                raise nest.error("masks are Python conditions on loop variables and constants, evaluated when "
+                                 f"planning; this one gave {type(result).__name__}", node) from e
+
+        masks.append(_schedule.Mask(loop.var, _loop_names_read(loop.mask, loop_vars), holds))
+    try:
+        return _schedule.make_schedule(parallel, reductions, masks)
+    except _schedule.ScheduleError as e:
+        raise nest.error(str(e), nest.parallel[0].node) from e
 
 
 def _recognise(nest, ns, specs, outputs, parallel, reductions, chips) -> Plan:
@@ -357,26 +393,10 @@ def _recognise_gemm(nest, ns, specs, outputs, parallel, reductions, chips) -> Pl
     gathered = nest.all_gathers[0] if nest.all_gathers else None
     if gathered is not None and (tile_mask is not None or a_name != gathered.name):
         raise _unsupported(nest, "a gathered input is the left operand of an unmasked matmul")
-    tables: dict[str, np.ndarray] = {}
-    tiles = total = i.count * j.count
-    fills = 0
-    if tile_mask is not None:
-        holds = _mask_fn(nest, ns, tile_mask, [i.var, j.var])
-        active, skipped = [], []
-        for bi, bj in itertools.product(range(i.count), range(j.count)):
-            (skipped if holds(i.value(bi), j.value(bj)) else active).append((bi, bj))
-        if not active:
-            raise nest.error("the masks skip every output tile", nest.parallel[0].node)
-        if skipped:
-            tables = {f"tile_{i.var}": np.array([t[0] for t in active], np.int32),
-                      f"tile_{j.var}": np.array([t[1] for t in active], np.int32),
-                      f"fill_{i.var}": np.array([t[0] for t in skipped], np.int32),
-                      f"fill_{j.var}": np.array([t[1] for t in skipped], np.int32)}
-        tiles, fills = len(active), len(skipped)
+    sch = nest_schedule(nest, ns, parallel, reductions)
     if causal and not _is_tril_mask(nest, ns, tile_mask, i, j):
         raise _unsupported(nest, "an elementwise `where` on the tile other than the causal `cols <= rows` with "
                                  "its tile mask `j > i + tm - 1`", store.node)
-    sch = _schedule.Schedule(tiles, total, tiles * k.count, False, bool(fills), tiles, tiles * k.count, fills, 1, tables)
     params = dict(M=M, N=N, K=K, tm=tm, tn=tn, tk=tk, causal=causal, transposed=transposed, a=a_name, b=b_name,
                   out_dtype=out.dtype, schedule=sch, gathered=gathered.name if gathered else None,
                   loop_vars=(i.var, j.var), chips=chips)
@@ -412,7 +432,7 @@ def _recognise_attention(nest, ns, specs, outputs, parallel, reductions) -> Plan
     if not causal or (b.count, h.count, i.stop, j.stop) != (B, H, S, S):
         raise _unsupported(nest, "the step mask must be the causal one, `j > i + block_q - 1`, over whole sequences",
                            nest.reductions[0].node)
-    sch = _schedule.causal_attention_schedule(B, H, S, i.step, j.step)
+    sch = nest_schedule(nest, ns, parallel, reductions)
     params = dict(B=B, H=H, S=S, D=D, block_q=i.step, block_kv=j.step, schedule=sch)
     return Plan(nest, "attention", specs, outputs, parallel, reductions, params)
 

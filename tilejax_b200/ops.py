@@ -210,17 +210,19 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, block_q:
     bq, bk = min(block_q, S), min(block_kv, S)
     sch = _schedule.causal_attention_schedule(B, H, S, bq, bk)
     if sch.step_tables:
-        step_tile = device_table(("attn", S, bq, bk, "tile"), sch.tables["step_tile"], device)
-        step_code = device_table(("attn", S, bq, bk, "code"), sch.tables["step_code"], device)
-    else:  # a single block: one tile, one step, first and last
-        step_tile = device_table(("attn1", "tile"), np.zeros(1, np.int32), device)
-        step_code = device_table(("attn1", "code"), np.array([3], np.int32), device)
+        tile, code = sch.tables["step_tile"], sch.tables["step_code"]
+    else:  # the mask skips nothing (one query block, or one key block): every (tile, block) step, written out
+        nq, nk = S // bq, S // bk
+        tile = np.repeat(np.arange(nq, dtype=np.int32), nk)
+        block = np.tile(np.arange(nk, dtype=np.int32), nq)
+        code = (block << _schedule.CODE_SHIFT) | ((block == 0) << 1) | (block == nk - 1)
+    step_tile = device_table(("attn", S, bq, bk, "tile"), tile, device)
+    step_code = device_table(("attn", S, bq, bk, "code"), code, device)
     if out is None:
         out = torch.empty_like(q)
     with torch.cuda.device(device):
         check(library().tjx_causal_attention_bf16(_ptr(q), _ptr(k), _ptr(v), _ptr(out), B, H, S, D, bq, bk,
-                                                  _ptr(step_tile), _ptr(step_code), sch.pattern_steps,
-                                                  sch.pattern_tiles, _stream()))
+                                                  _ptr(step_tile), _ptr(step_code), int(tile.size), S // bq, _stream()))
     return out
 
 
