@@ -49,10 +49,10 @@ def make_function(source: str, name: str = "f", **names):
     return ns[name]
 
 
-def make_kernel(source: str, **names):
+def make_kernel(source: str, name: str = "f", **names):
     import tilejax_b200.autokernel as autokernel
 
-    return autokernel.kernel(make_function(source, **names))
+    return autokernel.kernel(make_function(source, name, **names))
 
 
 def spec(*shape, dtype=None):

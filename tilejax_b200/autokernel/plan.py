@@ -90,7 +90,7 @@ def schedule_only(nest: Nest, fn, specs: list[Spec], tunable: Any, chips: int = 
 
 def make_plan(nest: Nest, fn, specs: list[Spec], tunable: Any, chips: int = 1) -> Plan:
     ns, all_specs, outputs, parallel, reductions = _run_prologue(nest, fn, specs, tunable, chips)
-    return _recognise(nest, ns, all_specs, outputs, parallel, reductions, chips)
+    return _recognise(nest, fn, ns, all_specs, outputs, parallel, reductions, chips)
 
 
 def _run_prologue(nest: Nest, fn, specs: list[Spec], tunable: Any, chips: int = 1, need_outputs: bool = True):
@@ -232,16 +232,37 @@ def nest_schedule(nest: Nest, ns, parallel, reductions) -> _schedule.Schedule:
         raise nest.error(str(e), nest.parallel[0].node) from e
 
 
-def _recognise(nest, ns, specs, outputs, parallel, reductions, chips) -> Plan:
+def _require_known_form(nest: Nest, fn, family: str) -> None:
+    """The nest's code (and its helpers') must be one of the forms the family's kernel computes: see fingerprint.py."""
+    from .fingerprint import fingerprint
+    from .recognised import RECOGNISED
+
+    try:
+        digest = fingerprint(fn)
+    except (OSError, TypeError) as e:
+        raise _unsupported(nest, f"its source cannot be read to identify it ({e})") from e
+    if digest not in RECOGNISED[family]:
+        what = {"attention": "causal attention's online softmax over `q @ k.T` and `p @ v`",
+                "decode": "GQA decode's online softmax over the cache blocks",
+                "mla": "absorbed MLA decode's online softmax over the latent cache"}[family]
+        raise _unsupported(nest, f"the loops and masks are those of {what}, but the tile code is not a form of it this "
+                                 f"backend's kernel is known to compute (fingerprint {digest[:12]})")
+
+
+def _recognise(nest, fn, ns, specs, outputs, parallel, reductions, chips) -> Plan:
     n_par, n_red = len(parallel), len(reductions)
     if n_red != 1:
         raise _unsupported(nest, f"{n_red} reduction loops (one is supported)")
     if nest.runtime_masks:
-        return _recognise_decode(nest, ns, specs, outputs, parallel, reductions)
+        plan = _recognise_decode(nest, ns, specs, outputs, parallel, reductions)
+        _require_known_form(nest, fn, "mla" if plan.params.get("mla") else "decode")
+        return plan
     if n_par == 2:
         return _recognise_gemm(nest, ns, specs, outputs, parallel, reductions, chips)
     if n_par == 3:
-        return _recognise_attention(nest, ns, specs, outputs, parallel, reductions)
+        plan = _recognise_attention(nest, ns, specs, outputs, parallel, reductions)
+        _require_known_form(nest, fn, "attention")
+        return plan
     raise _unsupported(nest, f"{n_par} parallel loops")
 
 
@@ -287,7 +308,7 @@ def _match_gemm_tile_code(nest, ns, acc: str, i, j, tm: int, tn: int, out: Spec)
     `cols = j + iota(dim 1)` assigned just before. The output must be allocated with zeros: the skipped tiles and
     the masked entries are written as zeros. Anything else (a scale, a bias, another fill) would be computed
     wrongly by the fixed kernel, so it is refused here."""
-    before, after = nest.segments[0], nest.segments[-1]
+    before, after = ([s for s in seg if not isinstance(s, ast.Pass)] for seg in (nest.segments[0], nest.segments[-1]))
     args = _call_of(before[0].value, "zeros") if len(before) == 1 and isinstance(before[0], ast.Assign) else None
     ok = args is not None and len(before[0].targets) == 1 and _is_name(before[0].targets[0], acc) and len(args) >= 1
     if ok:
@@ -419,10 +440,6 @@ def _recognise_attention(nest, ns, specs, outputs, parallel, reductions) -> Plan
     B, H, S, D = specs[0].shape
     if any(s.shape != (B, H, S, D) for s in specs[:3]) or outputs[0].shape != (B, H, S, D):
         raise _unsupported(nest, "q, k, v and the output must share one shape (B, H, S, D)")
-    text = ast.dump(ast.Module(list(nest.bodies[0]) + list(nest.segments[-1]), []))
-    needs = ("MatMult", "attr='T'", "attr='exp'", "attr='maximum'", "Div")
-    if not all(n in text for n in needs):
-        raise _unsupported(nest, "the tile code is not an online softmax over `q @ k.T` and `p @ v`")
     mask = nest.reductions[0].mask
     if mask is None or any(l.mask is not None for l in nest.parallel):
         raise _unsupported(nest, "causal attention masks its key loop with `j > i + block_q - 1`")

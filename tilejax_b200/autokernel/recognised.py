@@ -1,0 +1,22 @@
+"""Fingerprints (fingerprint.py) of the loop nests the attention and decode kernels accept, by family.
+
+Written by `python -m tilejax_b200.autokernel.fingerprint [reference/examples]`: the forms in this package's
+kernels.py and, when the reference's example files are at hand, the forms in examples/causal_attention.py and
+examples/decode.py (lane-replicated row statistics, block-diagonal queries). Do not edit by hand."""
+
+RECOGNISED: dict[str, dict[str, str]] = {
+    "attention": {
+        "c0907b9932813d96d8d5d1f74db165d93c89872bf5fd1650ac21326ccad72e03": "examples/causal_attention.py causal_attention",
+        "dffc41f8367fc51d53b1060ab8009f21a063452afd282a1bc6d325036bca8e97": "tilejax_b200/autokernel/kernels.py causal_attention",
+    },
+    "decode": {
+        "51a65e439275a796e84d550d1efbeca191aa4c8dcadf30cddde5bacac4a58c87": "examples/decode.py gqa_decode",
+        "ce6c35ee904aa743e268168c44b35ae4d64e545a5b1fb7d672b9187c1434147e": "examples/decode.py paged_gqa_decode",
+        "9f93df037dfb1451472f851a52f91a9008e3db6637d8b62a8964fffc10d6bfef": "tilejax_b200/autokernel/kernels.py gqa_decode",
+        "897c9c9ab27439d4820244e1191ff336b32075fe8275a78a9ab02fcba97f16ad": "tilejax_b200/autokernel/kernels.py paged_gqa_decode",
+    },
+    "mla": {
+        "8040e261b18bb83fef376fc89112926911a5d9cb73e4c2b39e44d2ae6d5aaa26": "examples/decode.py mla_decode",
+        "94a8eb751fcb24fac52945adf4e075a5b2716a89b73da9974dec6934fbd4411d": "tilejax_b200/autokernel/kernels.py mla_decode",
+    },
+}

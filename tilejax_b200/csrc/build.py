@@ -75,13 +75,44 @@ def build(force: bool = False, verbose: bool = False, defines: tuple[str, ...] =
     return library
 
 
+def ffi_include_dir() -> str | None:
+    """Where jaxlib keeps the XLA FFI headers, or None where JAX is not installed."""
+    try:
+        import jax
+
+        return jax.ffi.include_dir()
+    except Exception:
+        return None
+
+
+def build_ffi(verbose: bool = False) -> Path | None:
+    """Compile tjx_xla_ffi.cc (the jax.ffi handlers over the C ABI) into libtilejax_b200_ffi.so beside the library, if
+    jaxlib's FFI headers are there; returns None (and builds nothing) otherwise."""
+    include = ffi_include_dir()
+    if include is None:
+        return None
+    build()
+    target = PACKAGE / "libtilejax_b200_ffi.so"
+    source = CSRC / "tjx_xla_ffi.cc"
+    if _stale(target, [source, LIBRARY]):
+        cmd = [nvcc(), *ARCH_FLAGS, "-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-shared", f"-I{include}", str(source),
+               "-o", str(target), f"-L{PACKAGE}", "-ltilejax_b200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
+        if verbose:
+            print(" ".join(cmd), file=sys.stderr)
+        subprocess.run(cmd, check=True)
+    return target
+
+
 if __name__ == "__main__":
     parser = argparse.ArgumentParser()
     parser.add_argument("--force", action="store_true")
     parser.add_argument("--verbose", action="store_true", help="print ptxas resource usage (registers, spills, smem)")
     parser.add_argument("-D", dest="defines", action="append", default=[], help="a macro for every source, e.g. TJX_DEC_STAGES=3")
     parser.add_argument("--output", default=None, help="write a variant library here instead of the package's own")
+    parser.add_argument("--ffi", action="store_true", help="also build the jax.ffi handler library (needs jaxlib's headers)")
     args = parser.parse_args()
     output = Path(args.output).resolve() if args.output else None
     os.chdir(CSRC)
     print(build(args.force, args.verbose, tuple(args.defines), output))
+    if args.ffi:
+        print(build_ffi(args.verbose) or "jax.ffi.include_dir() is not available: the handler library was not built")

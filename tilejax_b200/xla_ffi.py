@@ -1,0 +1,115 @@
+"""The jax.ffi binding of the C ABI: the seam the reference's front end needs to run these kernels from jitted JAX
+code — `Kernel.lowered(...).entry(*inputs)` (src/autokernel/api.py:258-266) becomes a `jax.ffi.ffi_call`.
+
+Needs JAX with a CUDA backend, and libtilejax_b200_ffi.so (tilejax_b200/csrc/tjx_xla_ffi.cc, built by
+`python -m tilejax_b200.csrc.build --ffi` where `jax.ffi.include_dir()` exists). Where either is missing `available()`
+is False and everything else raises; the ctypes path (tilejax_b200.ops) is the one that is always there and always
+tested. Nothing here computes anything: each function only describes a custom call.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+import numpy as np
+
+from . import schedule as _schedule
+from ._lib import LIBRARY
+
+FFI_LIBRARY = Path(__file__).resolve().parent / "libtilejax_b200_ffi.so"
+TARGETS = {"tjx_build_steps": "TjxBuildSteps", "tjx_gemm": "TjxGemm", "tjx_causal_attention": "TjxCausalAttention",
+           "tjx_paged_gqa_decode": "TjxPagedGqaDecode"}
+_registered = False
+
+
+def available() -> bool:
+    """Is JAX importable and has the handler library been built?"""
+    try:
+        import jax  # noqa: F401
+    except Exception:
+        return False
+    return FFI_LIBRARY.exists()
+
+
+def register() -> None:
+    """Load the handler library and register its targets with XLA for the CUDA platform (once per process)."""
+    global _registered
+    if _registered:
+        return
+    if not available():
+        raise RuntimeError("the XLA FFI binding needs JAX and libtilejax_b200_ffi.so "
+                           "(python -m tilejax_b200.csrc.build --ffi); use tilejax_b200.ops otherwise")
+    import jax
+
+    ctypes.CDLL(str(LIBRARY), mode=ctypes.RTLD_GLOBAL)  # the C ABI the handlers call into
+    handlers = ctypes.CDLL(str(FFI_LIBRARY))
+    for target, symbol in TARGETS.items():
+        jax.ffi.register_ffi_target(target, jax.ffi.pycapsule(getattr(handlers, symbol)), platform="CUDA")
+    _registered = True
+
+
+def _i32(values):
+    import jax.numpy as jnp
+
+    return jnp.asarray(np.asarray(values, np.int32))
+
+
+def gemm(x, y, tm: int, tn: int, tk: int, *, causal: bool = False, out_dtype=None, y_transposed: bool = False,
+         stages: int = 0, tables: dict | None = None):
+    """out = x @ y through `tjx_gemm`; `tables` holds the schedule's tile_i / tile_j / fill_i / fill_j (NumPy)."""
+    import jax
+    import jax.numpy as jnp
+
+    register()
+    tables = tables or {}
+    M, N = x.shape[0], (y.shape[0] if y_transposed else y.shape[1])
+    empty = np.zeros(0, np.int32)
+    args = [_i32(tables.get(name, empty)) for name in ("tile_i", "tile_j", "fill_i", "fill_j")]
+    call = jax.ffi.ffi_call("tjx_gemm", jax.ShapeDtypeStruct((M, N), out_dtype or jnp.bfloat16))
+    return call(x, y, *args, tm=np.int32(tm), tn=np.int32(tn), tk=np.int32(tk), stages=np.int32(stages),
+                causal=np.int32(causal), y_transposed=np.int32(y_transposed))
+
+
+def causal_matmul(x, y, tm: int = 512, tn: int = 512, tk: int = 512):
+    M, K = x.shape
+    N = y.shape[1]
+    tm, tn, tk = min(tm, M), min(tn, N), min(tk, K)
+    return gemm(x, y, tm, tn, tk, causal=True, tables=_schedule.causal_matmul_schedule(M, N, K, tm, tn, tk).tables)
+
+
+def causal_attention(q, k, v, block_q: int = 512, block_kv: int = 512):
+    import jax
+
+    register()
+    B, H, S, D = q.shape
+    bq, bk = min(block_q, S), min(block_kv, S)
+    sch = _schedule.causal_attention_schedule(B, H, S, bq, bk)
+    if sch.step_tables:
+        tile, code = sch.tables["step_tile"], sch.tables["step_code"]
+    else:
+        nq, nk = S // bq, S // bk
+        tile, block = np.repeat(np.arange(nq, dtype=np.int32), nk), np.tile(np.arange(nk, dtype=np.int32), nq)
+        code = (block << _schedule.CODE_SHIFT) | ((block == 0) << 1) | (block == nk - 1)
+    call = jax.ffi.ffi_call("tjx_causal_attention", jax.ShapeDtypeStruct(q.shape, q.dtype))
+    return call(q, k, v, _i32(tile), _i32(code), block_q=np.int32(bq), block_kv=np.int32(bk),
+                pattern_tiles=np.int32(S // bq))
+
+
+def paged_gqa_decode(q, k_pages, v_pages, block_tables, lengths):
+    """Returns (out, step_tile, step_code, step_count): the tables the call built on the device ride along as extra
+    results, the scratch as a last one that is dropped here."""
+    import jax
+    import jax.numpy as jnp
+
+    register()
+    B, T, H, D = q.shape
+    pages = block_tables.shape[1]
+    lib = ctypes.CDLL(str(LIBRARY))
+    lib.tjx_paged_gqa_decode_workspace_bytes.restype = ctypes.c_size_t
+    scratch = int(lib.tjx_paged_gqa_decode_workspace_bytes(B, T, H, D, pages)) + 256
+    results = (jax.ShapeDtypeStruct(q.shape, q.dtype), jax.ShapeDtypeStruct((B * pages,), jnp.int32),
+               jax.ShapeDtypeStruct((B * pages,), jnp.int32), jax.ShapeDtypeStruct((1,), jnp.int32),
+               jax.ShapeDtypeStruct((B + 1,), jnp.int32), jax.ShapeDtypeStruct((scratch,), jnp.uint8))
+    out, tile, code, count, _, _ = jax.ffi.ffi_call("tjx_paged_gqa_decode", results)(q, k_pages, v_pages, block_tables, lengths)
+    return out, tile, code, count
