@@ -152,6 +152,8 @@ class AllGatherMatmul:
     its barrier kernel).
     """
 
+    MAX_EPOCH = 1 << 20  # calls of the one-launch kernel between resets of its arrival counters (the C ABI takes 2^22)
+
     def __init__(self, m: int, K: int, N: int, tm: int = 256, tn: int = 512, tk: int = 512, group=None,
                  device: torch.device | None = None, reserve_sms: int | None = None, transport: str = "fused"):
         from . import ops  # needs the built library
@@ -257,6 +259,11 @@ class AllGatherMatmul:
         ex.calls += 1
         ex.barrier()
         self.barrier_done.record(torch.cuda.current_stream(self.device))
+        if self.epoch >= self.MAX_EPOCH:
+            # The arrival counters only ever grow (a launch waits for epoch x copier warps): start them over, in
+            # stream order behind the previous launch, before the entry point's epoch limit is reached.
+            self.arrivals.zero_()
+            self.epoch = 0
         self.epoch += 1
         shards = [ex.peers[r][parity] for r in range(self.ranks)]
         self._ops.all_gather_gemm(ex.send[parity], shards, ex.xs, w, self.out, self.me, self.tm, self.tn, self.tk,
