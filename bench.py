@@ -49,6 +49,8 @@ CPU_SAMPLE_ROWS = 2048
 # reports `traffic: null`.
 NCU_TRAFFIC_BYTES: dict[str, float] = {
     "gemm_16384x8192x8192": 2.299167e9 + 0.263586e9,
+    "paged_gqa_decode_B64_H32_Hkv8_D128_page16_shared_pages": 467166208.0 + 4148480.0,
+    "paged_gqa_decode_B64_H32_Hkv8_D128_page16_distinct_pages": 551334656.0 + 4222208.0,
 }
 
 
@@ -150,14 +152,15 @@ def device_randn_bf16(shape, seed, device, scale=1.0):
 
 
 def time_device(fn, iters: int, warmup: int, flush=None) -> float:
-    """Mean device time of fn() in ms over `iters` runs, each bracketed by CUDA events on the current stream;
-    `flush()` (an L2 flush) runs untimed before each."""
+    """Median device time of fn() in ms over `iters` runs, each bracketed by CUDA events on the current stream;
+    `flush()` (an L2 flush) runs untimed before each. (The median, as the reference's benchmarks take it,
+    benchmarks/timing.py:12-22: under the board's power cap single launches scatter by several per cent.)"""
     import torch
 
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
-    total = 0.0
+    times = []
     for _ in range(iters):
         if flush is not None:
             flush()
@@ -166,8 +169,8 @@ def time_device(fn, iters: int, warmup: int, flush=None) -> float:
         fn()
         end.record()
         end.synchronize()
-        total += start.elapsed_time(end)
-    return total / iters
+        times.append(start.elapsed_time(end))
+    return statistics.median(times)
 
 
 def time_sustained(fn, seconds: float, ms_hint: float) -> float:
@@ -310,7 +313,7 @@ def workload_name(n: int) -> str:
 # ----------------------------------------------------------------------------------------- extra workloads
 
 
-def extra_workloads(device, pk: dict, pk_kind: str, only: str | None = None, iters: int = 10, warm: int = 3,
+def extra_workloads(device, pk: dict, pk_kind: str, only: str | None = None, iters: int = 20, warm: int = 3,
                     quick: bool = False) -> dict:
     """The other hot-path configurations at one GPU, device-timed with an L2 flush before every run. `only` keeps
     the workloads whose name contains it and `quick` drops the sustained loops and the front-end timings (for
@@ -338,15 +341,16 @@ def extra_workloads(device, pk: dict, pk_kind: str, only: str | None = None, ite
     out = {}
     want = lambda name: only is None or only in name  # noqa: E731
 
+    later = []  # back-to-back loops of more than a second: run after every isolated timing, they heat the chip
+
     def tensor_entry(name, ms, flops, fn=None, extra=None, sustained=False):
         tf = flops / ms / 1e9
-        sustained_tf = None
-        if sustained and not quick and fn is not None:
-            sustained_tf = flops / time_sustained(fn, 1.2, ms) / 1e9
         out[name] = {"ms": ms, "value": tf, "unit": "TFLOP/s",
-                     "roofline": tensor_roofline(tf, pk, pk_kind, sustained_tf, NCU_TRAFFIC_BYTES.get(name))}
+                     "roofline": tensor_roofline(tf, pk, pk_kind, None, NCU_TRAFFIC_BYTES.get(name))}
         if extra:
             out[name].update(extra)
+        if sustained and not quick and fn is not None:
+            later.append((name, fn, flops, ms))
 
     def frontend_ms(call):
         """The same launch through `@autokernel.kernel` (parse, plan and tables cached after the first call)."""
@@ -363,7 +367,7 @@ def extra_workloads(device, pk: dict, pk_kind: str, only: str | None = None, ite
         x = device_randn_bf16((n, n), 0, device)
         y = device_randn_bf16((n, n), 1, device)
         if want(f"dense_matmul_{n}"):
-            fn = lambda: ops.matmul(x, y, 512, 512, 512)  # noqa: E731
+            fn = lambda x=x, y=y: ops.matmul(x, y, 512, 512, 512)  # noqa: E731
             ms = time_device(fn, iters, warm, flush)
             tensor_entry(f"dense_matmul_{n}_tiles512", ms, 2.0 * n**3, fn, sustained=True, extra={
                 "via_autokernel_ms": frontend_ms(lambda: kernels.matmul(x, y, kernels.MatmulTiles()))})
@@ -372,7 +376,7 @@ def extra_workloads(device, pk: dict, pk_kind: str, only: str | None = None, ite
                 name = f"causal_matmul_8192_tiles{tiles[0]}x{tiles[1]}x{tiles[2]}"
                 if not want(name):
                     continue
-                fn = lambda: ops.causal_matmul(x, y, *tiles)  # noqa: E731
+                fn = lambda x=x, y=y, tiles=tiles: ops.causal_matmul(x, y, *tiles)  # noqa: E731
                 ms = time_device(fn, iters, warm, flush)
                 dense_ms = out.get("dense_matmul_8192_tiles512", {}).get("ms")
                 tensor_entry(name, ms, float(n) * n * (n + 1), fn, extra={
@@ -380,7 +384,6 @@ def extra_workloads(device, pk: dict, pk_kind: str, only: str | None = None, ite
                     "time_vs_dense": None if dense_ms is None else ms / dense_ms,
                     "via_autokernel_ms": frontend_ms(
                         lambda: kernels.causal_matmul(x, y, kernels.MatmulTiles(*tiles)))})
-        del x, y
 
     for (B, H, S, D) in ((4, 16, 2048, 128), (1, 16, 4096, 128)):
         if not want(f"causal_attention_B{B}"):
@@ -461,6 +464,10 @@ def extra_workloads(device, pk: dict, pk_kind: str, only: str | None = None, ite
             "via_autokernel_ms": frontend_ms(lambda: kernels.paged_gqa_decode(qd, kd, vd, btd, ld)),
             "roofline": hbm_roofline(gbs, pk, pk_kind, nbytes, ms, NCU_TRAFFIC_BYTES.get(name))}
         del kd, vd
+    for name, fn, flops, ms in later:
+        sustained_tf = flops / time_sustained(fn, 1.2, ms) / 1e9
+        out[name]["roofline"].update(achieved_sustained=sustained_tf,
+                                     frac_sustained=sustained_tf / pk["bf16_tflops_sustained"])
     ops.device_status()
     return out
 
@@ -606,7 +613,6 @@ def main() -> None:
     # peak) and a back-to-back loop of more than a second (against the sustained peak)
     alone = lambda: ops.gemm(op.exchange.xs, y, op.tm, op.tn, op.tk, out=op.out)  # noqa: E731
     gemm_ms = time_device(alone, min(max(args.steps, 5), 20), 1)
-    gemm_sustained_ms = time_sustained(alone, 1.2, gemm_ms)
     ops.device_status()
     barrier()
 
@@ -632,9 +638,17 @@ def main() -> None:
     if world > 1:
         dist.all_reduce(e2e_elapsed, op=dist.ReduceOp.MAX)
     e2e_ms = e2e_elapsed.item() / e2e_steps
-    clocks = sampler.stop() if sampler else None  # sampled over the device-timed, kernel-alone and e2e regions
-
     flops_per_gpu = 2.0 * M_TOTAL * K_DIM * N_DIM
+    workloads = cpu = None
+    if world == 1 and not args.no_extras:
+        workloads = extra_workloads(device, pk, pk_kind)  # isolated launches first, its back-to-back loops last
+    # The dominant kernel back to back for more than a second: last, so that it does not heat the chip under the
+    # isolated timings above.
+    gemm_sustained_ms = time_sustained(alone, 1.2, gemm_ms)
+    ops.device_status()
+    barrier()
+    clocks = sampler.stop() if sampler else None  # sampled over every timed region of this run
+
     value = world * flops_per_gpu / ms_per_step / 1e9
     gemm_tflops = flops_per_gpu / gemm_ms / 1e9
     line = {
@@ -663,8 +677,8 @@ def main() -> None:
             NCU_TRAFFIC_BYTES["gemm_16384x8192x8192"], kernel="gemm_pair_kernel<256,3,2>", ms_per_launch=gemm_ms,
             ms_per_launch_sustained=gemm_sustained_ms, flops_per_launch=flops_per_gpu),
     }
-    if world == 1 and not args.no_extras:
-        line["workloads"] = extra_workloads(device, pk, pk_kind)
+    if workloads is not None:
+        line["workloads"] = workloads
         tflops, sec, threads, sample = cpu_port_tflops(CPU_SAMPLE_ROWS, 3, 1)
         line["cpu_baseline"] = {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample}
         for prefix, record in cpu_baselines_for_workloads().items():
