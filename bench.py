@@ -385,6 +385,18 @@ def extra_workloads(device, pk: dict, pk_kind: str, only: str | None = None, ite
                     "via_autokernel_ms": frontend_ms(
                         lambda: kernels.causal_matmul(x, y, kernels.MatmulTiles(*tiles)))})
 
+    if want("rmsnorm_matmul"):
+        # RMSNorm fused with the projection after it (examples/rmsnorm_matmul.py:31-47) at the dense config's size:
+        # the same product plus one pass over x (2 M D bytes read, 2 M D + 4 M written).
+        n = 8192
+        x = device_randn_bf16((n, n), 0, device)
+        gamma = (1 + 0.1 * device_randn_bf16((1, n), 7, device).float()).to(torch.bfloat16)
+        w = device_randn_bf16((n, n), 1, device, n**-0.5)
+        ms = time_device(lambda: ops.rmsnorm_matmul(x, gamma, w, 512, 512, 512), iters, warm, flush)
+        tensor_entry("rmsnorm_matmul_8192_tiles512", ms, 2.0 * n**3, extra={
+            "includes": "the pass over x that writes the gamma-scaled operand and the row scales, then the matmul",
+            "via_autokernel_ms": frontend_ms(lambda: kernels.rmsnorm_matmul(x, gamma, w, kernels.NormMatmulTiles()))})
+
     for (B, H, S, D) in ((4, 16, 2048, 128), (1, 16, 4096, 128)):
         if not want(f"causal_attention_B{B}"):
             continue

@@ -99,6 +99,21 @@ int tjx_gemm_bf16(const void* x, const void* y, void* out, int M, int N, int K, 
                   int tk, int stages, int out_f32, int causal, const int32_t* tile_i, const int32_t* tile_j,
                   int n_tiles, const int32_t* fill_i, const int32_t* fill_j, int n_fills, tjx_stream_t stream);
 
+/* Bytes of scratch tjx_rmsnorm_gemm_bf16 needs for these sizes. */
+size_t tjx_rmsnorm_gemm_workspace_bytes(int M, int D);
+
+/* RMSNorm fused with the projection after it, the loop nest `rmsnorm_matmul` (examples/rmsnorm_matmul.py:31-47):
+ * out = rsqrt(mean(x^2, axis 1) + eps) * ((x * gamma) @ w). One pass over x writes the gamma-scaled operand
+ * bf16(f32(x) * f32(gamma)) — what the reference's `@` is fed (examples/rmsnorm_matmul.py:44) — and each row's scale
+ * into `workspace`; the matmul step loop then multiplies row r of its f32 accumulator by scale[r] before the one
+ * rounding to the output dtype (the nest's fused epilogue, examples/rmsnorm_matmul.py:45-46).
+ *   x [M, D] bf16, gamma [1, D] bf16, w [D, N] bf16, out [M, N] bf16 (f32 if out_f32)
+ *   workspace: at least tjx_rmsnorm_gemm_workspace_bytes(M, D) bytes, 256-byte aligned
+ * Constraints: those of tjx_gemm_bf16 with K = D. */
+int tjx_rmsnorm_gemm_bf16(const void* x, const void* gamma, const void* w, void* out, int M, int N, int D, float eps,
+                          int tm, int tn, int tk, int out_f32, void* workspace, size_t workspace_bytes,
+                          tjx_stream_t stream);
+
 /* Caps the number of persistent CTAs tjx_gemm_bf16 launches from the calling thread (0 = one per SM, the
  * default). For callers that run communication kernels beside the GEMM — the collective matmul's exchange rounds
  * stand in for the ring DMAs of the reference's kernel (src/autokernel/codegen.py:1161-1229), which need no

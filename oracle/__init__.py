@@ -27,6 +27,7 @@ from .decode import (
     to_pages,
 )
 from .matmul import causal_matmul_ref, collective_row_order, matmul_ref
+from .rmsnorm import rmsnorm_matmul_f64, rmsnorm_matmul_ref
 from .steps import (
     attention_step_tables,
     causal_tile_tables,
@@ -51,6 +52,8 @@ __all__ = [
     "mla_decode_ref",
     "paged_gqa_decode_f64",
     "paged_gqa_decode_ref",
+    "rmsnorm_matmul_f64",
+    "rmsnorm_matmul_ref",
     "to_pages",
     "walk_nest",
 ]

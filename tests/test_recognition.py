@@ -133,7 +133,7 @@ def test_attention_is_accepted_by_what_it_computes_not_by_what_it_mentions():
 
 def test_every_nest_of_this_package_is_in_the_table():
     for family, names in (("attention", ["causal_attention"]), ("decode", ["paged_gqa_decode", "gqa_decode"]),
-                          ("mla", ["mla_decode"])):
+                          ("mla", ["mla_decode"]), ("rmsnorm", ["rmsnorm_matmul"])):
         for name in names:
             assert fingerprint.fingerprint(getattr(K, name)) in RECOGNISED[family], name
 
@@ -202,6 +202,48 @@ def test_the_references_decode_examples_run_unmodified():
     assert mla.lower(q_c, q_r, c_kv, k_rope, lengths, tiles).plan.params["mla"]
     oracle.compare("mla_decode.reference", mla.reference(q_c, q_r, c_kv, k_rope, lengths, tiles),
                    oracle.mla_decode_ref(q_c, q_r, c_kv, k_rope, lengths, 128), rtol=1e-6, atol=1e-6)
+
+
+@needs_reference
+def test_the_references_rmsnorm_matmul_example_runs_unmodified():
+    ns = example("rmsnorm_matmul.py")  # the sum of squares kept lane-wide, (tm, 128), widened with jnp.tile
+    kernel = ns["rmsnorm_matmul"]
+    assert fingerprint.fingerprint(kernel) in RECOGNISED["rmsnorm"]
+    rng = np.random.default_rng(0)
+    x = rand_bf16((256, 384), 0)
+    gamma = (1 + 0.1 * rng.standard_normal((1, 384), np.float32)).astype(BF16)
+    w = rand_bf16((384, 256), 2, 1 / 16)
+    tiles = ns["NormMatmulTiles"](tm=128, tn=128, tk=128)
+    lowered = kernel.lower(x, gamma, w, tiles)
+    assert lowered.plan.family == "rmsnorm_gemm" and (lowered.tiles, lowered.steps) == (4, 12)
+    assert "tjx_rmsnorm_gemm_bf16" in lowered.source
+    want = oracle.rmsnorm_matmul_ref(x, gamma, w, 128, 128, 128)
+    np.testing.assert_array_equal(f64(kernel.reference(x, gamma, w, tiles)), f64(want))
+    np.testing.assert_allclose(f64(want), oracle.rmsnorm_matmul_f64(x, gamma, w), rtol=2e-2, atol=0.05)
+    # This package's own form of the nest means the same.
+    np.testing.assert_array_equal(f64(K.rmsnorm_matmul.reference(x, gamma, w, K.NormMatmulTiles(128, 128, 128))), f64(want))
+
+
+def test_a_norm_matmul_with_other_tile_code_is_refused():
+    source = """
+        def f(x, gamma, w):
+            M, D = x.shape
+            N = w.shape[1]
+            out = jnp.zeros((M, N), x.dtype)
+            for i in range(0, M, 128):
+                for j in range(0, N, 128):
+                    acc = jnp.zeros((128, 128), jnp.float32)
+                    sum_sq = jnp.zeros((128, 1), jnp.float32)
+                    for k in range(0, D, 128):
+                        xk = x[i : i + 128, k : k + 128].astype(jnp.float32)
+                        sum_sq += jnp.sum(xk * xk, axis=1, keepdims=True)
+                        acc += (xk * gamma[0:1, k : k + 128].astype(jnp.float32)).astype(x.dtype) @ w[k : k + 128, j : j + 128]
+                    scale = jax.lax.rsqrt(sum_sq / D + 1e-5)
+                    out = out.at[i : i + 128, j : j + 128].set((acc * scale).astype(x.dtype))
+            return out
+        """
+    with pytest.raises(KernelError, match="not a form of it this backend's kernel is known to compute"):
+        make_kernel(source).lower(spec(256, 256), spec(1, 256), spec(256, 256))  # another eps: another function
 
 
 @needs_reference

@@ -319,8 +319,8 @@ def _check_kernel_rules(plan: Plan) -> None:
     its TPU layout rules the same way, tests/test_plan.py:150-170)."""
     p, nest = plan.params, plan.nest
     bf16 = _bf16()
-    if plan.family == "gemm":
-        if any(np.dtype(s.dtype) != bf16 for s in plan.specs[:2]):
+    if plan.family in ("gemm", "rmsnorm_gemm"):
+        if any(np.dtype(s.dtype) != bf16 for s in plan.specs[: 2 if plan.family == "gemm" else 3]):
             raise nest.error("the matmul kernel takes bfloat16 operands")
         if np.dtype(p["out_dtype"]) not in (bf16, np.dtype(np.float32)):
             raise nest.error("the matmul kernel writes bfloat16 or float32")
@@ -369,6 +369,8 @@ def launch_key(plan: Plan, config: Config) -> tuple:
     p = plan.params
     if plan.family == "gemm":
         return ("gemm", p["tm"], p["tn"], _stages(config.pipeline, p["tn"]), p["causal"], p["transposed"])
+    if plan.family == "rmsnorm_gemm":
+        return ("rmsnorm_gemm", p["tm"], p["tn"])
     if plan.family == "attention":
         return ("attention",)
     if p.get("mla") or p.get("contiguous"):
@@ -426,6 +428,17 @@ def _lower(plan: Plan, config: Config) -> tuple[str, Callable[..., Any]]:
                             y_transposed=p["transposed"], stages=stages, **tables)
 
         return text, entry
+    if plan.family == "rmsnorm_gemm":
+        import torch
+
+        out_dtype = torch.float32 if np.dtype(p["out_dtype"]) == np.float32 else torch.bfloat16
+        text = header + (
+            f"kernel      tjx_rmsnorm_gemm_bf16 (one pass over x for the gamma-scaled operand and the row scales, then the "
+            f"persistent TMA + tcgen05 matmul with the row scale in its epilogue)\n"
+            f"problem     out[{p['M']}, {p['N']}] = rsqrt(mean(x^2) + {p['eps']:g}) * ((x * gamma)[{p['M']}, {p['K']}] @ w), "
+            f"output {np.dtype(p['out_dtype']).name}\n"
+            f"user tile   {p['tm']} x {p['tn']} x {p['tk']}: {sch.tiles} tiles, {sch.steps} steps\n")
+        return text, lambda x, gamma, w: ops.rmsnorm_matmul(x, gamma, w, p["tm"], p["tn"], p["tk"], p["eps"], out_dtype)
     if plan.family == "attention":
         text = header + (
             f"kernel      tjx_causal_attention_bf16 (TMA rings, tcgen05 with S, P and O in TMEM, online softmax)\n"

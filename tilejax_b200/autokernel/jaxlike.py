@@ -230,7 +230,7 @@ numpy = types.SimpleNamespace(
     square=_lift(np.square), transpose=_lift(np.transpose), reshape=_lift(np.reshape),
 )
 lax = types.SimpleNamespace(broadcasted_iota=_broadcasted_iota,
-                            rsqrt=_lift(lambda x: (1.0 / np.sqrt(np.asarray(x, np.float64))).astype(np.asarray(x).dtype)))
+                            rsqrt=_lift(lambda x: (1.0 / np.sqrt(np.asarray(x))).astype(np.asarray(x).dtype)))
 
 
 def to_numpy(x) -> np.ndarray:

@@ -2,7 +2,8 @@
 
 Each is the plain loop nest over tiles whose meaning the kernel must reproduce — `kernel.fn` runs it as written on
 the CPU — with the same structure as the reference's examples (examples/matmul.py, causal_matmul.py,
-causal_attention.py, decode.py `gqa_decode`, `mla_decode` and `paged_gqa_decode`, collective_matmul.py). Row statistics are kept as (rows, 1)
+causal_attention.py, rmsnorm_matmul.py, decode.py `gqa_decode`, `mla_decode` and `paged_gqa_decode`,
+collective_matmul.py). Row statistics are kept as (rows, 1)
 columns here: the reference's lane-replicated (rows, 128) layout is a TPU register trick, not arithmetic.
 """
 
@@ -81,6 +82,40 @@ def causal_matmul(x, y, tiles=MatmulTiles()):
             rows = i + jax.lax.broadcasted_iota(jnp.int32, (tm, tn), 0)
             cols = j + jax.lax.broadcasted_iota(jnp.int32, (tm, tn), 1)
             out = out.at[i : i + tm, j : j + tn].set(jnp.where(cols <= rows, acc, 0.0).astype(dtype))
+    return out
+
+
+EPS = 1e-6
+
+
+@autokernel.tunable
+class NormMatmulTiles:
+    """(tm, tn) output tiles, each summing tk-deep products (and tm rows' squares) over the model dim."""
+
+    tm: int = autokernel.choice(128, 256, 512, 1024, 2048, default=512)
+    tn: int = autokernel.choice(128, 256, 512, 1024, 2048, default=512)
+    tk: int = autokernel.choice(128, 256, 512, 1024, 2048, default=512)
+
+
+@autokernel.kernel
+def rmsnorm_matmul(x, gamma, w, tiles=NormMatmulTiles()):
+    """rmsnorm(x) @ w in one pass over x: the row scale commutes with the matmul, so one reduction accumulates
+    (x * gamma) @ w and each row's sum of squares, and the tile is scaled once at the end."""
+    M, D = x.shape
+    N = w.shape[1]
+    tm, tn, tk = min(tiles.tm, M), min(tiles.tn, N), min(tiles.tk, D)
+    dtype = x.dtype
+    out = jnp.zeros((M, N), dtype)
+    for i in range(0, M, tm):
+        for j in range(0, N, tn):
+            acc = jnp.zeros((tm, tn), jnp.float32)  # (x * gamma) @ w
+            sum_sq = jnp.zeros((tm, 1), jnp.float32)  # each row's sum of squares
+            for k in range(0, D, tk):
+                xk = x[i : i + tm, k : k + tk].astype(jnp.float32)
+                sum_sq += jnp.sum(xk * xk, axis=1, keepdims=True)
+                acc += (xk * gamma[0:1, k : k + tk].astype(jnp.float32)).astype(dtype) @ w[k : k + tk, j : j + tn]
+            scale = jax.lax.rsqrt(sum_sq / D + EPS)
+            out = out.at[i : i + tm, j : j + tn].set((acc * scale).astype(dtype))
     return out
 
 

@@ -242,7 +242,8 @@ def _require_known_form(nest: Nest, fn, family: str) -> None:
     except (OSError, TypeError) as e:
         raise _unsupported(nest, f"its source cannot be read to identify it ({e})") from e
     if digest not in RECOGNISED[family]:
-        what = {"attention": "causal attention's online softmax over `q @ k.T` and `p @ v`",
+        what = {"rmsnorm": "RMSNorm fused with the projection after it, `rsqrt(mean(x^2) + eps) * ((x * gamma) @ w)`",
+                "attention": "causal attention's online softmax over `q @ k.T` and `p @ v`",
                 "decode": "GQA decode's online softmax over the cache blocks",
                 "mla": "absorbed MLA decode's online softmax over the latent cache"}[family]
         raise _unsupported(nest, f"the loops and masks are those of {what}, but the tile code is not a form of it this "
@@ -256,6 +257,10 @@ def _recognise(nest, fn, ns, specs, outputs, parallel, reductions, chips) -> Pla
     if nest.runtime_masks:
         plan = _recognise_decode(nest, ns, specs, outputs, parallel, reductions)
         _require_known_form(nest, fn, "mla" if plan.params.get("mla") else "decode")
+        return plan
+    if n_par == 2 and len(nest.inputs) == 3 and not nest.all_gathers and len(nest.bodies[0]) == 3:
+        plan = _recognise_rmsnorm(nest, ns, specs, outputs, parallel, reductions)
+        _require_known_form(nest, fn, "rmsnorm")
         return plan
     if n_par == 2:
         return _recognise_gemm(nest, ns, specs, outputs, parallel, reductions, chips)
@@ -369,6 +374,27 @@ def _match_gemm_tile_code(nest, ns, acc: str, i, j, tm: int, tn: int, out: Spec)
                                  "`jnp.where(cols <= rows, acc, 0.0).astype(dtype)` with `rows = i + iota(.., 0)` and "
                                  "`cols = j + iota(.., 1)`; other epilogues are not built", store.node)
     return True
+
+
+def _recognise_rmsnorm(nest, ns, specs, outputs, parallel, reductions) -> Plan:
+    """`rmsnorm_matmul` (examples/rmsnorm_matmul.py:31-47): (x, gamma, w) with x (M, D), gamma (1, D), w (D, N); loops
+    (i, j) over the output's tiles and k over the model dimension, no masks. What the tile code computes is pinned
+    by its fingerprint (the caller checks it); here the shapes and the loops."""
+    (i, j), (k,) = parallel, reductions
+    x, gamma, w = specs[:3]
+    if x.ndim != 2 or gamma.ndim != 2 or w.ndim != 2 or len(outputs) != 1 or outputs[0].ndim != 2:
+        raise _unsupported(nest, "RMSNorm + matmul takes x (M, D), gamma (1, D) and w (D, N)")
+    (M, D), N = x.shape, w.shape[1]
+    if gamma.shape != (1, D) or w.shape[0] != D or outputs[0].shape != (M, N):
+        raise _unsupported(nest, "RMSNorm + matmul takes x (M, D), gamma (1, D) and w (D, N) and stores (M, N)")
+    if any(l.mask is not None for l in (*nest.parallel, *nest.reductions)):
+        raise _unsupported(nest, "a mask on this loop")
+    if (i.start, i.stop, j.start, j.stop, k.start, k.stop) != (0, M, 0, N, 0, D):
+        raise _unsupported(nest, "the loops must cover the operands exactly")
+    sch = nest_schedule(nest, ns, parallel, reductions)
+    params = dict(M=M, N=N, K=D, tm=i.step, tn=j.step, tk=k.step, eps=float(ns.get("EPS", 1e-6)),
+                  out_dtype=outputs[0].dtype, schedule=sch, causal=False, transposed=False)
+    return Plan(nest, "rmsnorm_gemm", specs, outputs, parallel, reductions, params)
 
 
 def _recognise_gemm(nest, ns, specs, outputs, parallel, reductions, chips) -> Plan:

@@ -1,8 +1,9 @@
 """Fingerprints (fingerprint.py) of the loop nests the attention and decode kernels accept, by family.
 
 Written by `python -m tilejax_b200.autokernel.fingerprint [reference/examples]`: the forms in this package's
-kernels.py and, when the reference's example files are at hand, the forms in examples/causal_attention.py and
-examples/decode.py (lane-replicated row statistics, block-diagonal queries). Do not edit by hand."""
+kernels.py and, when the reference's example files are at hand, the forms in examples/causal_attention.py,
+examples/decode.py and examples/rmsnorm_matmul.py (lane-replicated row statistics, block-diagonal queries).
+Do not edit by hand."""
 
 RECOGNISED: dict[str, dict[str, str]] = {
     "attention": {
@@ -18,5 +19,9 @@ RECOGNISED: dict[str, dict[str, str]] = {
     "mla": {
         "8040e261b18bb83fef376fc89112926911a5d9cb73e4c2b39e44d2ae6d5aaa26": "examples/decode.py mla_decode",
         "94a8eb751fcb24fac52945adf4e075a5b2716a89b73da9974dec6934fbd4411d": "tilejax_b200/autokernel/kernels.py mla_decode",
+    },
+    "rmsnorm": {
+        "ebbdf02fc35cd281f7cba2fdd95589e0d8717f3476647b2313b8393a40b81e26": "examples/rmsnorm_matmul.py rmsnorm_matmul",
+        "bc7e5bbddff3f245c47e9cbeea906d10d142f2fe1e7f9fd7b4a7eeb32f1c031d": "tilejax_b200/autokernel/kernels.py rmsnorm_matmul",
     },
 }

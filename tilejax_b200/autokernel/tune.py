@@ -143,7 +143,7 @@ def _traffic(plan, schedule) -> int:
     """Bytes a schedule's copies move between HBM and the SMs, from its tiles and steps (what the reference's
     `_stats` counts, src/autokernel/tune.py:141-155)."""
     p = plan.params
-    if plan.family == "gemm":
+    if plan.family in ("gemm", "rmsnorm_gemm"):
         per_step = (p["tm"] * p["tk"] + p["tk"] * p["tn"]) * 2
         per_tile = p["tm"] * p["tn"] * (4 if str(p["out_dtype"]) == "float32" else 2)
         return schedule.steps * per_step + (schedule.tiles + schedule.fills) * per_tile

@@ -50,6 +50,7 @@ struct GemmParams {
   void* out;
   int* status;
   long long* profile;  // per-CTA counters (PROFILE_WORDS each) or null
+  const float* row_scale;  // [M] or null: the epilogue multiplies row r of the accumulator by row_scale[r] (rmsnorm)
   // All-gather fused into the launch (gemm_pair_kernel<.., true> only): rows [own_lo, own_hi) of the gathered
   // operand are this GPU's shard and come from map_a_own; the other shards are pulled from peer memory into
   // `gather_dst` by one extra warp per CTA, 256-row block by block in arrival order, and counted in
@@ -134,11 +135,16 @@ __device__ __forceinline__ void store_accumulator(const GemmParams& p, const CUt
                                                   int lane) {
   const int row = row0 + lane;
   constexpr int CHUNKS = BN / 32;
+  const float scale = p.row_scale != nullptr && row < p.M ? p.row_scale[row] : 1.0f;
 #pragma unroll 1
   for (int c = 0; c < CHUNKS; ++c) {
     uint32_t v[32];
     tmem_ld32(t_row + c * 32, v);
     tmem_wait_ld();
+    if (p.row_scale != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * scale);
+    }
     if (p.causal) {
       const int col0 = n0 + c * 32;
 #pragma unroll
@@ -747,11 +753,11 @@ extern "C" int tjx_gemm_set_cta_limit(int max_ctas) {
   return 0;
 }
 
-extern "C" int tjx_gemm_bf16(const void* x, const void* y, void* out, int M, int N, int K, int y_transposed, int tm,
-                             int tn, int tk, int stages, int out_f32, int causal, const int32_t* tile_i,
-                             const int32_t* tile_j, int n_tiles, const int32_t* fill_i, const int32_t* fill_j,
-                             int n_fills, tjx_stream_t stream) {
-  using namespace tjx;
+namespace tjx {
+// The matmul launch behind tjx_gemm_bf16 and tjx_rmsnorm_gemm_bf16 (`row_scale`: see GemmParams).
+int gemm_launch(const void* x, const void* y, void* out, int M, int N, int K, int y_transposed, int tm, int tn, int tk,
+                int stages, int out_f32, int causal, const int32_t* tile_i, const int32_t* tile_j, int n_tiles,
+                const int32_t* fill_i, const int32_t* fill_j, int n_fills, const float* row_scale, tjx_stream_t stream) {
   if (int rc = check_device()) return rc;
   if (x == nullptr || y == nullptr || out == nullptr) return fail(TJX_E_ARG, "x, y or out is null");
   if (M <= 0 || N <= 0 || K <= 0) return fail(TJX_E_ARG, "M, N, K must be positive");
@@ -794,6 +800,7 @@ extern "C" int tjx_gemm_bf16(const void* x, const void* y, void* out, int M, int
   p.causal = causal ? 1 : 0, p.out_f32 = out_f32 ? 1 : 0, p.b_kmajor = y_transposed ? 1 : 0;
   p.num_kb = (K + BK - 1) / BK;
   p.out = out;
+  p.row_scale = row_scale;
   p.status = device_status_word();
   if (p.status == nullptr) return fail(TJX_E_CUDA, "could not locate the device status word");
 
@@ -851,6 +858,15 @@ extern "C" int tjx_gemm_bf16(const void* x, const void* y, void* out, int M, int
   }
   if (stages == 6) return launch_gemm<128, 6>(ma, mb, mc, p, grid, s);
   return launch_gemm<128, 4>(ma, mb, mc, p, grid, s);
+}
+}  // namespace tjx
+
+extern "C" int tjx_gemm_bf16(const void* x, const void* y, void* out, int M, int N, int K, int y_transposed, int tm,
+                             int tn, int tk, int stages, int out_f32, int causal, const int32_t* tile_i,
+                             const int32_t* tile_j, int n_tiles, const int32_t* fill_i, const int32_t* fill_j,
+                             int n_fills, tjx_stream_t stream) {
+  return tjx::gemm_launch(x, y, out, M, N, K, y_transposed, tm, tn, tk, stages, out_f32, causal, tile_i, tile_j, n_tiles,
+                          fill_i, fill_j, n_fills, nullptr, stream);
 }
 
 // out = all_gather(x) @ y in ONE launch: the pair GEMM whose extra warp per CTA pulls the other ranks' shards from

@@ -138,6 +138,41 @@ def gemm(x: torch.Tensor, y: torch.Tensor, tm: int, tn: int, tk: int, *, causal:
     return out
 
 
+_rmsnorm_workspaces: dict[tuple, torch.Tensor] = {}
+
+
+def rmsnorm_matmul(x: torch.Tensor, gamma: torch.Tensor, w: torch.Tensor, tm: int = 512, tn: int = 512, tk: int = 512,
+                   eps: float = 1e-6, out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """The `rmsnorm_matmul` loop nest (examples/rmsnorm_matmul.py:31-47): rsqrt(mean(x^2) + eps) * ((x * gamma) @ w),
+    x (M, D), gamma (1, D), w (D, N). The gamma-scaled operand and the row scales go through a scratch buffer kept
+    per (M, D, device, stream)."""
+    device = _need_cuda(x, gamma, w)
+    if any(t.dtype != torch.bfloat16 for t in (x, gamma, w)):
+        raise ValueError("x, gamma and w must be bfloat16")
+    M, D = x.shape
+    if gamma.shape != (1, D) or w.shape[0] != D or w.dim() != 2:
+        raise ValueError("x is (M, D), gamma (1, D), w (D, N)")
+    N = w.shape[1]
+    out_dtype = torch.bfloat16 if out_dtype is None else out_dtype
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("the output is bfloat16 or float32")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=device)
+    elif out.shape != (M, N) or out.dtype != out_dtype or not out.is_contiguous() or out.device != device:
+        raise ValueError("out has the wrong shape, dtype or layout")
+    with torch.cuda.device(device):
+        key = (M, D, str(device), torch.cuda.current_stream(device).cuda_stream)
+        ws = _rmsnorm_workspaces.get(key)
+        if ws is None:
+            ws = torch.empty(int(library().tjx_rmsnorm_gemm_workspace_bytes(M, D)), dtype=torch.uint8, device=device)
+            _rmsnorm_workspaces.clear()  # one shape at a time: the scratch is as large as x
+            _rmsnorm_workspaces[key] = ws
+        check(library().tjx_rmsnorm_gemm_bf16(_ptr(x), _ptr(gamma), _ptr(w), _ptr(out), M, N, D, float(eps), min(tm, M),
+                                              min(tn, N), min(tk, D), int(out_dtype == torch.float32), _ptr(ws),
+                                              ws.numel(), _stream()))
+    return out
+
+
 def all_gather_gemm(x_own: torch.Tensor, peer_shards: list[torch.Tensor | None], gathered: torch.Tensor,
                     y: torch.Tensor, out: torch.Tensor, me: int, tm: int, tn: int, tk: int, tile_i: torch.Tensor,
                     tile_j: torch.Tensor, arrivals: torch.Tensor, epoch: int) -> torch.Tensor:
