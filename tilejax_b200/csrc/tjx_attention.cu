@@ -66,10 +66,17 @@ struct AttnSmem {
   static constexpr int TOTAL = LAST_OFF + AT_MAX_TILES * 4 + 1024;
 };
 
+#ifndef TJX_AT_KDIV
+#define TJX_AT_KDIV 1
+#endif
 __device__ __forceinline__ float fast_exp2(float x) {
+#ifdef TJX_AT_WHATIF_NOEXP
+  return x * 1e-3f;  // (timing experiment only: wrong values)
+#else
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+#endif
 }
 
 // Keys a slot's rows [q0, q0 + 128) attend to, as a count of 128-key sub-blocks from key 0: what the step table
@@ -107,7 +114,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + L::BAR_OFF + 8 * N_BARS + 8);
   int* last_block = reinterpret_cast<int*>(base_ptr + L::LAST_OFF);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
   const int bh_count = p.B * p.H;
   const int n_ctas = static_cast<int>(gridDim.x), cta = static_cast<int>(blockIdx.x);
   // The k-th unit of this CTA in the heaviest-first list (later query tiles attend to more keys), or -1.
@@ -144,7 +151,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tmem_base = __shfl_sync(0xFFFFFFFFu, *tmem_holder, 0);
 
   // What every role derives for a unit, identically.
   struct Unit {
@@ -210,61 +217,86 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------------ MMA issuer (whole warp; one lane issues)
+    {
+#ifdef TJX_AT_WHATIF_N64
+      const uint32_t idesc_qk = idesc_bf16_f32(128, 64, 0, 0);
+      const uint32_t idesc_pv = idesc_bf16_f32(128, 64, 0, 1);
+#else
       const uint32_t idesc_qk = idesc_bf16_f32(128, 128, 0, 0);  // Q and K both K-major (K read "transposed")
       const uint32_t idesc_pv = idesc_bf16_f32(128, 128, 0, 1);  // P from TMEM, V MN-major
+#endif
       int g0 = 0;            // ring position of the current unit's block 0
       int used[2] = {0, 0};  // units that used slot t so far
       int done[2] = {0, 0};  // blocks of slot t in earlier units (phase of s_full / p_ready / o_done)
+      auto commit = [&](uint32_t bar) {
+        if (elect_one()) mma_commit(bar);
+      };
+      long long issue_cyc = 0, issue_first = 0, issue_n = 0;
       auto issue_qk = [&](int t, int gn) {
+        const long long c0 = PROFILE ? clock64() : 0;
         const int stage = gn % AT_STAGES;
         const uint32_t qa = base + L::Q_OFF + t * L::TILE_BYTES;
         const uint32_t ka = base + L::K_OFF + stage * L::TILE_BYTES;
+        // The k-th 16-wide slice of a 128-byte-swizzled K-major tile: 32 bytes further along the row, the second
+        // 64-column box after the first. (Descriptor addresses count 16 bytes; no carry out of their 14 bits.)
+        const uint64_t q0 = smem_desc_sw128(qa, 16, 1024), k0 = smem_desc_sw128(ka, 16, 1024);
+        uint64_t qd[8], kd[8];
 #pragma unroll
-        for (int kk = 0; kk < AT_D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * (L::TILE_BYTES / 2) + (kk & 3) * 32;
-          mma_ss(tmem_base + t * 128, smem_desc_sw128(qa + off, 16, 1024), smem_desc_sw128(ka + off, 16, 1024),
-                 idesc_qk, kk != 0 ? 1u : 0u);
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = ((kk >> 2) * (L::TILE_BYTES / 2) + (kk & 3) * 32) >> 4;
+          qd[kk] = q0 + off, kd[kk] = k0 + off;
         }
-        mma_commit(s_full(t));
+        mma_ss_x8_commit(tmem_base + t * 128, qd, kd, idesc_qk, 0u, s_full(t));
+        if (PROFILE) {
+          const long long dt = clock64() - c0;
+          if (issue_n++ == 0) issue_first = dt;
+          issue_cyc += dt;
+        }
       };
       auto issue_pv = [&](int t, int gn, bool first) {
         const int stage = gn % AT_STAGES;
         const uint32_t va = base + L::V_OFF + stage * L::TILE_BYTES;
+        const uint64_t v0 = smem_desc_sw128(va, L::TILE_BYTES / 2, 1024);
+        uint64_t vd[8];
+        uint32_t pa[8];
 #pragma unroll
-        for (int kk = 0; kk < AT_BKV / 16; ++kk)
-          mma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + kk * 8,
-                 smem_desc_sw128(va + kk * (16 * 128), L::TILE_BYTES / 2, 1024), idesc_pv,
-                 (!first || kk != 0) ? 1u : 0u);
-        mma_commit(o_done(t));
+        for (int kk = 0; kk < 8; ++kk) vd[kk] = v0 + ((kk * 16 * 128) >> 4), pa[kk] = tmem_base + t * 128 + kk * 8;
+        mma_ts_x8_commit(tmem_base + 256 + t * 128, pa, vd, idesc_pv, first ? 0u : 1u, o_done(t));
       };
       bool ok = true;
       long long t_first = 0, in_wait = 0, fill_wait = -1, p_wait = 0, units = 0;
+      // Every lane waits; the vote makes the outcome one value for the warp, so the loops below stay uniform.
+      auto wait = [&](uint32_t bar, uint32_t parity, int code, long long& waited) {
+        return __all_sync(0xFFFFFFFFu, mbar_wait_timed(bar, parity, abort_flag, p.status, code, waited, PROFILE && prof != nullptr)) != 0;
+      };
       for (int k = 0; ok; ++k) {
         const int i = unit_at(k);
         if (i < 0) break;
-        const Unit u = describe(i);
+        Unit u = describe(i);
+        // (Read from shared memory: the same in every lane, and said so to the compiler.)
+        u.n_slot[0] = __shfl_sync(0xFFFFFFFFu, u.n_slot[0], 0), u.n_slot[1] = __shfl_sync(0xFFFFFFFFu, u.n_slot[1], 0);
+        u.n_blocks = max(u.n_slot[0], u.n_slot[1]);
         if (PROFILE && units++ == 0) t_first = clock64();
         for (int t = 0; t < 2 && ok; ++t)
-          if (u.n_slot[t] > 0) ok = mbar_wait_timed(q_full(t), used[t] & 1, abort_flag, p.status, TJX_ERR_WAIT_FULL, in_wait, PROFILE && prof != nullptr);
+          if (u.n_slot[t] > 0) ok = wait(q_full(t), used[t] & 1, TJX_ERR_WAIT_FULL, in_wait);
         if (ok && u.n_blocks > 0) {
-          ok = mbar_wait_timed(k_full(g0 % AT_STAGES), (g0 / AT_STAGES) & 1, abort_flag, p.status, TJX_ERR_WAIT_FULL, in_wait, PROFILE && prof != nullptr);
+          ok = wait(k_full(g0 % AT_STAGES), (g0 / AT_STAGES) & 1, TJX_ERR_WAIT_FULL, in_wait);
           if (PROFILE && fill_wait < 0) fill_wait = in_wait;
           if (ok) {
             tc_fence_after_sync();
             for (int t = 0; t < 2; ++t)
               if (u.n_slot[t] > 0) {
                 issue_qk(t, g0);
-                if (u.n_slot[t] == 1) mma_commit(q_empty(t));  // this slot's only Q K^T of the unit
+                if (u.n_slot[t] == 1) commit(q_empty(t));  // this slot's only Q K^T of the unit
               }
-            mma_commit(k_empty(g0 % AT_STAGES));
+            commit(k_empty(g0 % AT_STAGES));
           }
         }
         for (int n = 0; n < u.n_blocks && ok; ++n) {
           const int gn = g0 + n;
           const int stage = gn % AT_STAGES;
-          if (!mbar_wait_timed(v_full(stage), (gn / AT_STAGES) & 1, abort_flag, p.status, TJX_ERR_WAIT_FULL, in_wait, PROFILE && prof != nullptr)) {
+          if (!wait(v_full(stage), (gn / AT_STAGES) & 1, TJX_ERR_WAIT_FULL, in_wait)) {
             ok = false;
             break;
           }
@@ -273,7 +305,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
             if (n >= u.n_slot[t]) continue;
             // Softmax warps reach block 0 of a unit only after their epilogue of the previous one, so this wait
             // also covers "O of the previous unit has been read".
-            if (!mbar_wait_timed(p_ready(t), (done[t] + n) & 1, abort_flag, p.status, TJX_ERR_WAIT_OTHER, p_wait, PROFILE && prof != nullptr)) {
+            if (!wait(p_ready(t), (done[t] + n) & 1, TJX_ERR_WAIT_OTHER, p_wait)) {
               ok = false;
               break;
             }
@@ -282,7 +314,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
             if (n + 1 < u.n_slot[t]) {
               if (!next_k_waited) {
                 const int ns = (gn + 1) % AT_STAGES;
-                if (!mbar_wait_timed(k_full(ns), ((gn + 1) / AT_STAGES) & 1, abort_flag, p.status, TJX_ERR_WAIT_FULL, in_wait, PROFILE && prof != nullptr)) {
+                if (!wait(k_full(ns), ((gn + 1) / AT_STAGES) & 1, TJX_ERR_WAIT_FULL, in_wait)) {
                   ok = false;
                   break;
                 }
@@ -290,13 +322,13 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
                 next_k_waited = true;
               }
               issue_qk(t, gn + 1);
-              if (n + 2 == u.n_slot[t]) mma_commit(q_empty(t));  // that was this slot's last Q K^T of the unit
+              if (n + 2 == u.n_slot[t]) commit(q_empty(t));  // that was this slot's last Q K^T of the unit
               next_k_used = true;
             }
           }
           if (!ok) break;
-          mma_commit(v_empty(stage));
-          if (next_k_used) mma_commit(k_empty((gn + 1) % AT_STAGES));
+          commit(v_empty(stage));
+          if (next_k_used) commit(k_empty((gn + 1) % AT_STAGES));
         }
         g0 += u.n_blocks;
         for (int t = 0; t < 2; ++t) {
@@ -304,9 +336,10 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
           if (u.n_slot[t] > 0) ++used[t];
         }
       }
-      if (PROFILE && prof != nullptr) {
+      if (PROFILE && prof != nullptr && lane == 0) {
         prof[1] = t_first, prof[2] = clock64(), prof[3] = in_wait, prof[4] = max(fill_wait, 0ll), prof[5] = 0;
         prof[6] = units, prof[8] = p_wait;
+        prof[9] = issue_first, prof[10] = issue_cyc, prof[11] = issue_n;
       }
     }
     __syncwarp();
@@ -319,6 +352,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
     const uint32_t o_tmem = tmem_base + lane_addr + 256 + t * 128;
     int done = 0;  // blocks of this slot in earlier units
     bool ok = true;
+    long long sm_wait = 0, sm_busy = 0, sm_blocks = 0;
     for (int k = 0; ok; ++k) {
     const int i = unit_at(k);
     if (i < 0) break;
@@ -329,12 +363,21 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
     float m_used = AT_MASK * AT_LOG2E;  // running max, in log2 units
     float l = 0.f;
     for (int n = 0; n < n_mine; ++n) {
+      const long long w0 = PROFILE ? clock64() : 0;
       const bool got = mbar_wait(s_full(t), (done + n) & 1, abort_flag, p.status, TJX_ERR_WAIT_TMEM_FULL);
+      const long long w1 = PROFILE ? clock64() : 0;
+      if (PROFILE) sm_wait += w1 - w0, ++sm_blocks;
       if (!__all_sync(0xFFFFFFFFu, got)) {
         ok = false;
         break;
       }
       tc_fence_after_sync();
+#ifdef TJX_AT_WHATIF_NOSOFTMAX
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_ready(t));
+      continue;
+#endif
       const int kv0 = n * AT_BKV;
       const bool diagonal = kv0 + AT_BKV - 1 > q0;  // some key of the block is in some row's future
       // The row's 128 scores come into registers once: four TMEM loads in flight, one wait.
@@ -415,6 +458,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_ready(t));
+      if (PROFILE) sm_busy += clock64() - w1;
     }
     if (ok && n_mine > 0) {
       // Epilogue: O / l -> bf16 -> this thread's row of the output, 256 contiguous bytes.
@@ -447,6 +491,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
     }
     done += n_mine;
     }  // units
+    if (PROFILE && prof != nullptr && warp == 2 && lane == 0) prof[12] = sm_busy, prof[13] = sm_wait, prof[14] = sm_blocks;
   }
 
   tc_fence_before_sync();

@@ -298,6 +298,75 @@ __device__ __forceinline__ void mma_ts_c(uint32_t d_tmem, uint32_t a_tmem, uint6
   }
 }
 
+// True in exactly one lane of a converged warp, the same lane every time. A role that issues tcgen05.mma runs its
+// loop with the whole warp, so that the compiler keeps descriptors and addresses in uniform registers, and puts
+// only the instruction itself under this predicate; a loop run by one lane of a diverged warp computes them in
+// per-thread registers and pays a transfer to the uniform file for every operand of every MMA.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\telect.sync _|P, 0xFFFFFFFF;\n\tselp.u32 %0, 1, 0, P;\n\t}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
+
+// Eight MMAs of one accumulation (K = 128 in steps of 16) and the commit that follows them, issued by the warp's
+// elected lane without a branch in between: D[tmem] (+)= A_k * B_k for k = 0..7, `accumulate_first` deciding whether
+// the first one adds to what D holds; then one arrival on `bar` when they have completed. Called by a whole warp.
+__device__ __forceinline__ void mma_ss_x8_commit(uint32_t d_tmem, const uint64_t (&a)[8], const uint64_t (&b)[8],
+                                                 uint32_t idesc, uint32_t accumulate_first, uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred L, F, T;\n\t"
+      "elect.sync _|L, 0xFFFFFFFF;\n\t"
+      "setp.ne.b32 F, %2, 0;\n\t"
+      "setp.eq.b32 T, 0, 0;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], %4, %12, %1, F;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], %5, %13, %1, T;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], %6, %14, %1, T;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], %7, %15, %1, T;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], %8, %16, %1, T;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], %9, %17, %1, T;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], %10, %18, %1, T;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], %11, %19, %1, T;\n\t"
+      "@L tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%3];\n\t"
+      "}\n"
+      :
+      : "r"(d_tmem), "r"(idesc), "r"(accumulate_first), "r"(bar), "l"(a[0]), "l"(a[1]), "l"(a[2]), "l"(a[3]), "l"(a[4]),
+        "l"(a[5]), "l"(a[6]), "l"(a[7]), "l"(b[0]), "l"(b[1]), "l"(b[2]), "l"(b[3]), "l"(b[4]), "l"(b[5]), "l"(b[6]),
+        "l"(b[7])
+      : "memory");
+}
+
+// The same with A in TMEM (bf16, two per 32-bit column): a[k] is the TMEM address of the k-th 16-wide slice.
+__device__ __forceinline__ void mma_ts_x8_commit(uint32_t d_tmem, const uint32_t (&a)[8], const uint64_t (&b)[8],
+                                                 uint32_t idesc, uint32_t accumulate_first, uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred L, F, T;\n\t"
+      "elect.sync _|L, 0xFFFFFFFF;\n\t"
+      "setp.ne.b32 F, %2, 0;\n\t"
+      "setp.eq.b32 T, 0, 0;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], [%4], %12, %1, F;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], [%5], %13, %1, T;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], [%6], %14, %1, T;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], [%7], %15, %1, T;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], [%8], %16, %1, T;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], [%9], %17, %1, T;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], [%10], %18, %1, T;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], [%11], %19, %1, T;\n\t"
+      "@L tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%3];\n\t"
+      "}\n"
+      :
+      : "r"(d_tmem), "r"(idesc), "r"(accumulate_first), "r"(bar), "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(a[4]),
+        "r"(a[5]), "r"(a[6]), "r"(a[7]), "l"(b[0]), "l"(b[1]), "l"(b[2]), "l"(b[3]), "l"(b[4]), "l"(b[5]), "l"(b[6]),
+        "l"(b[7])
+      : "memory");
+}
+
+// The warp's index, known to the compiler as the same in every lane.
+__device__ __forceinline__ int uniform_warp_index() {
+  return __shfl_sync(0xFFFFFFFFu, static_cast<int>(threadIdx.x >> 5), 0);
+}
+
 // The barrier gets one arrival once every tcgen05.mma this thread issued before has completed.
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
