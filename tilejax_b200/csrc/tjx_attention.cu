@@ -69,6 +69,12 @@ struct AttnSmem {
 #ifndef TJX_AT_KDIV
 #define TJX_AT_KDIV 1
 #endif
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
 #ifdef TJX_AT_WHATIF_NOEXP
   return x * 1e-3f;  // (timing experiment only: wrong values)
@@ -77,6 +83,39 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 #endif
+}
+
+// 2^x for a pair of elements. POLY: on the FMA pipe — x = n + f with n the nearest integer (the float trick of
+// adding 1.5 * 2^23) and f in [-0.5, 0.5]; 2^f by a cubic fitted to a relative error of 7.5e-5 (P is rounded to
+// bf16, 3.9e-3, right after); n goes into the exponent field by integer addition. x below -125 is held there
+// (2^-125: nothing, after the rounding of P V and of the row sum).
+#ifndef TJX_AT_POLY_PAIRS
+#define TJX_AT_POLY_PAIRS 1
+#endif
+constexpr int AT_POLY_PAIRS = TJX_AT_POLY_PAIRS;  // of every four pairs, how many use the polynomial
+__host__ __device__ constexpr bool poly_pair(int pair) {
+  return AT_POLY_PAIRS == 4   ? true
+         : AT_POLY_PAIRS == 3 ? (pair & 3) != 0
+         : AT_POLY_PAIRS == 2 ? (pair & 1) != 0
+         : AT_POLY_PAIRS == 1 ? (pair & 3) == 3
+                              : false;
+}
+__device__ __forceinline__ float2 exp2_pair(float2 x, bool poly) {  // `poly` is a constant after unrolling
+  if (!poly) {
+    return make_float2(fast_exp2(x.x), fast_exp2(x.y));
+  } else {
+    constexpr float MAGIC = 12582912.f;  // 1.5 * 2^23
+    x.x = fmaxf(x.x, -125.f), x.y = fmaxf(x.y, -125.f);
+    const float2 t = __fadd2_rn(x, make_float2(MAGIC, MAGIC));
+    const float2 n = __fadd2_rn(t, make_float2(-MAGIC, -MAGIC));
+    const float2 f = __ffma2_rn(n, make_float2(-1.f, -1.f), x);
+    float2 p = __ffma2_rn(f, make_float2(0.05517164617776871f, 0.05517164617776871f),
+                          make_float2(0.2426111251115799f, 0.2426111251115799f));
+    p = __ffma2_rn(p, f, make_float2(0.6932609677314758f, 0.6932609677314758f));
+    p = __ffma2_rn(p, f, make_float2(0.9999280571937561f, 0.9999280571937561f));
+    return make_float2(__int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23)),
+                       __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23)));
+  }
 }
 
 // Keys a slot's rows [q0, q0 + 128) attend to, as a count of 128-key sub-blocks from key 0: what the step table
@@ -99,7 +138,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t bar_base = base + L::BAR_OFF;
-  // barriers: q_full[2], k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2], o_done[2], q_empty[2]
+  // barriers: q_full[2], k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2], o_done[2], q_empty[2],
+  // p_half[2]
   auto q_full = [&](int t) { return bar_base + 8u * t; };
   auto k_full = [&](int s) { return bar_base + 8u * (2 + s); };
   auto k_empty = [&](int s) { return bar_base + 8u * (4 + s); };
@@ -109,7 +149,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
   auto p_ready = [&](int t) { return bar_base + 8u * (12 + t); };
   auto o_done = [&](int t) { return bar_base + 8u * (14 + t); };
   auto q_empty = [&](int t) { return bar_base + 8u * (16 + t); };
-  constexpr int N_BARS = 18;
+  auto p_half = [&](int t) { return bar_base + 8u * (18 + t); };
+  constexpr int N_BARS = 20;
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(base_ptr + L::BAR_OFF + 8 * N_BARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + L::BAR_OFF + 8 * N_BARS + 8);
   int* last_block = reinterpret_cast<int*>(base_ptr + L::LAST_OFF);
@@ -128,7 +169,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
   if (PROFILE && prof != nullptr && threadIdx.x == 0) prof[0] = clock64();
   if (threadIdx.x == 0) {
     for (int i = 0; i < N_BARS; ++i) {
-      const bool softmax_bar = i == 12 || i == 13;  // p_ready: one arrival per softmax warp
+      const bool softmax_bar = i == 12 || i == 13 || i >= 18;  // p_ready, p_half: one arrival per softmax warp
       mbar_init(bar_base + 8u * i, softmax_bar ? 4 : 1);
     }
     *abort_flag = 0;
@@ -254,15 +295,23 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
           issue_cyc += dt;
         }
       };
-      auto issue_pv = [&](int t, int gn, bool first) {
+      // P V in two halves: keys 0..63 of the block as soon as their probabilities are in TMEM, the rest (and the
+      // commit) when the block's are all there.
+      auto issue_pv = [&](int t, int gn, bool first, int half) {
         const int stage = gn % AT_STAGES;
         const uint32_t va = base + L::V_OFF + stage * L::TILE_BYTES;
         const uint64_t v0 = smem_desc_sw128(va, L::TILE_BYTES / 2, 1024);
-        uint64_t vd[8];
-        uint32_t pa[8];
+        uint64_t vd[4];
+        uint32_t pa[4];
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) vd[kk] = v0 + ((kk * 16 * 128) >> 4), pa[kk] = tmem_base + t * 128 + kk * 8;
-        mma_ts_x8_commit(tmem_base + 256 + t * 128, pa, vd, idesc_pv, first ? 0u : 1u, o_done(t));
+        for (int kk = 0; kk < 4; ++kk) {
+          vd[kk] = v0 + (((half * 4 + kk) * 16 * 128) >> 4);
+          pa[kk] = tmem_base + t * 128 + (half * 4 + kk) * 8;
+        }
+        if (half == 0)
+          mma_ts_x4(tmem_base + 256 + t * 128, pa, vd, idesc_pv, first ? 0u : 1u);
+        else
+          mma_ts_x4_commit(tmem_base + 256 + t * 128, pa, vd, idesc_pv, 1u, o_done(t));
       };
       bool ok = true;
       long long t_first = 0, in_wait = 0, fill_wait = -1, p_wait = 0, units = 0;
@@ -305,12 +354,18 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
             if (n >= u.n_slot[t]) continue;
             // Softmax warps reach block 0 of a unit only after their epilogue of the previous one, so this wait
             // also covers "O of the previous unit has been read".
+            if (!wait(p_half(t), (done[t] + n) & 1, TJX_ERR_WAIT_OTHER, p_wait)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            issue_pv(t, gn, n == 0, 0);
             if (!wait(p_ready(t), (done[t] + n) & 1, TJX_ERR_WAIT_OTHER, p_wait)) {
               ok = false;
               break;
             }
             tc_fence_after_sync();
-            issue_pv(t, gn, n == 0);
+            issue_pv(t, gn, n == 0, 1);
             if (n + 1 < u.n_slot[t]) {
               if (!next_k_waited) {
                 const int ns = (gn + 1) % AT_STAGES;
@@ -353,6 +408,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
     int done = 0;  // blocks of this slot in earlier units
     bool ok = true;
     long long sm_wait = 0, sm_busy = 0, sm_blocks = 0;
+    int ph_ld = 0, ph_max = 0, ph_exp = 0;
     for (int k = 0; ok; ++k) {
     const int i = unit_at(k);
     if (i < 0) break;
@@ -372,12 +428,6 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
         break;
       }
       tc_fence_after_sync();
-#ifdef TJX_AT_WHATIF_NOSOFTMAX
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(p_ready(t));
-      continue;
-#endif
       const int kv0 = n * AT_BKV;
       const bool diagonal = kv0 + AT_BKV - 1 > q0;  // some key of the block is in some row's future
       // The row's 128 scores come into registers once: four TMEM loads in flight, one wait.
@@ -385,6 +435,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld32(s_tmem + c * 32, v[c]);
       tmem_wait_ld();
+      const int c_ld = PROFILE ? clock() : 0;
+      if (PROFILE) ph_ld += c_ld - static_cast<int>(w1);
       if (diagonal) {  // only the block on the diagonal holds keys in some row's future
         const int lim = row - kv0;  // columns j <= lim are visible
 #pragma unroll
@@ -393,16 +445,18 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
           for (int j = 0; j < 32; ++j)
             if (c * 32 + j > lim) v[c][j] = __float_as_uint(AT_MASK);
       }
-      // Row max over the block, four independent chains.
+      // Row max over the block: three-input max, four independent chains.
       float mx;
       {
         float m0 = AT_MASK, m1 = AT_MASK, m2 = AT_MASK, m3 = AT_MASK;
 #pragma unroll
         for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            m0 = fmaxf(m0, __uint_as_float(v[c][j])), m1 = fmaxf(m1, __uint_as_float(v[c][j + 1]));
-            m2 = fmaxf(m2, __uint_as_float(v[c][j + 2])), m3 = fmaxf(m3, __uint_as_float(v[c][j + 3]));
+          for (int j = 0; j < 32; j += 8) {
+            m0 = fmax3(m0, __uint_as_float(v[c][j]), __uint_as_float(v[c][j + 1]));
+            m1 = fmax3(m1, __uint_as_float(v[c][j + 2]), __uint_as_float(v[c][j + 3]));
+            m2 = fmax3(m2, __uint_as_float(v[c][j + 4]), __uint_as_float(v[c][j + 5]));
+            m3 = fmax3(m3, __uint_as_float(v[c][j + 6]), __uint_as_float(v[c][j + 7]));
           }
         mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
       }
@@ -433,27 +487,38 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
         }
         tmem_wait_st();
       }
-      // Probabilities; P (bf16) overwrites the first half of the scores' columns (all already in registers).
+      const int c_max = PROFILE ? clock() : 0;
+      if (PROFILE) ph_max += c_max - c_ld;
+      // Probabilities; P (bf16) overwrites the first half of the scores' columns (all already in registers). The
+      // arithmetic is two elements per instruction, and AT_POLY_PAIRS of every four pairs take their exponential
+      // from the FMA pipe instead of the MUFU unit, which two softmax warps per scheduler would otherwise saturate.
       {
-        float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
-        const float neg_m = -m_used;
+        float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
+        const float2 scale = make_float2(AT_LOG2E, AT_LOG2E), neg_m = make_float2(-m_used, -m_used);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t pk[16];
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(v[c][j]), AT_LOG2E, neg_m));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(v[c][j + 1]), AT_LOG2E, neg_m));
-            const float p2 = fast_exp2(fmaf(__uint_as_float(v[c][j + 2]), AT_LOG2E, neg_m));
-            const float p3 = fast_exp2(fmaf(__uint_as_float(v[c][j + 3]), AT_LOG2E, neg_m));
-            l0 += p0, l1 += p1, l2 += p2, l3 += p3;
-            pk[j >> 1] = pack_bf16(p0, p1);
-            pk[(j >> 1) + 1] = pack_bf16(p2, p3);
+            const float2 x0 = __ffma2_rn(make_float2(__uint_as_float(v[c][j]), __uint_as_float(v[c][j + 1])), scale, neg_m);
+            const float2 x1 = __ffma2_rn(make_float2(__uint_as_float(v[c][j + 2]), __uint_as_float(v[c][j + 3])), scale, neg_m);
+            const float2 p0 = exp2_pair(x0, poly_pair(j / 2));
+            const float2 p1 = exp2_pair(x1, poly_pair(j / 2 + 1));
+            la = __fadd2_rn(la, p0), lb = __fadd2_rn(lb, p1);
+            pk[j >> 1] = pack_bf16(p0.x, p0.y);
+            pk[(j >> 1) + 1] = pack_bf16(p1.x, p1.y);
           }
           tmem_st16(s_tmem + c * 16, pk);
+          if (c == 1) {  // the first 64 keys' probabilities are on their way: P V may begin with them
+            tmem_wait_st();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_half(t));
+          }
         }
-        l += (l0 + l1) + (l2 + l3);
+        l += (la.x + la.y) + (lb.x + lb.y);
       }
+      if (PROFILE) ph_exp += clock() - c_max;
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
@@ -491,7 +556,10 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
     }
     done += n_mine;
     }  // units
-    if (PROFILE && prof != nullptr && warp == 2 && lane == 0) prof[12] = sm_busy, prof[13] = sm_wait, prof[14] = sm_blocks;
+    if (PROFILE && prof != nullptr && warp == 2 && lane == 0) {
+      prof[12] = sm_busy, prof[13] = sm_wait, prof[14] = sm_blocks;
+      prof[15] = (static_cast<long long>(ph_ld) << 42) | (static_cast<long long>(ph_max) << 21) | ph_exp;
+    }
   }
 
   tc_fence_before_sync();

@@ -362,6 +362,44 @@ __device__ __forceinline__ void mma_ts_x8_commit(uint32_t d_tmem, const uint32_t
       : "memory");
 }
 
+// Half of such an accumulation with A in TMEM (four MMAs), without and with the commit: the two halves of a P V
+// product whose P arrives in two parts.
+__device__ __forceinline__ void mma_ts_x4(uint32_t d_tmem, const uint32_t* a, const uint64_t* b, uint32_t idesc,
+                                          uint32_t accumulate_first) {
+  asm volatile(
+      "{\n\t.reg .pred L, F, T;\n\t"
+      "elect.sync _|L, 0xFFFFFFFF;\n\t"
+      "setp.ne.b32 F, %2, 0;\n\t"
+      "setp.eq.b32 T, 0, 0;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], [%3], %7, %1, F;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], [%4], %8, %1, T;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], [%5], %9, %1, T;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], [%6], %10, %1, T;\n\t"
+      "}\n"
+      :
+      : "r"(d_tmem), "r"(idesc), "r"(accumulate_first), "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "l"(b[0]), "l"(b[1]),
+        "l"(b[2]), "l"(b[3])
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts_x4_commit(uint32_t d_tmem, const uint32_t* a, const uint64_t* b, uint32_t idesc,
+                                                 uint32_t accumulate_first, uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred L, F, T;\n\t"
+      "elect.sync _|L, 0xFFFFFFFF;\n\t"
+      "setp.ne.b32 F, %2, 0;\n\t"
+      "setp.eq.b32 T, 0, 0;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], [%4], %8, %1, F;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], [%5], %9, %1, T;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], [%6], %10, %1, T;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], [%7], %11, %1, T;\n\t"
+      "@L tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%3];\n\t"
+      "}\n"
+      :
+      : "r"(d_tmem), "r"(idesc), "r"(accumulate_first), "r"(bar), "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "l"(b[0]),
+        "l"(b[1]), "l"(b[2]), "l"(b[3])
+      : "memory");
+}
+
 // The warp's index, known to the compiler as the same in every lane.
 __device__ __forceinline__ int uniform_warp_index() {
   return __shfl_sync(0xFFFFFFFFu, static_cast<int>(threadIdx.x >> 5), 0);
