@@ -10,14 +10,21 @@
 // one is still in its last blocks.
 //
 //   warp 0      producer: TMA loads Q (both slots, once per unit), then K and V sub-blocks into two 2-slot rings
-//   warp 1      MMA issuer (one thread): S_t = Q_t K^T into TMEM, then O_t += P_t V with P_t read from TMEM
+//   warp 1      MMA issuer: S_t = Q_t K^T into TMEM, then O_t += P_t V with P_t read from TMEM. The whole warp
+//               runs the loop (addresses and descriptors stay in uniform registers) and one elected lane issues
+//               each accumulation's MMAs and its commit as one predicated block: issuing from inside a
+//               one-lane branch cost ~60 cycles per MMA, as long as the 128 x 128 x 16 MMA itself takes
 //   warps 2-5   softmax of slot A, warps 6-9 of slot B: a thread owns one query row — tcgen05.ld its 128
-//               scores, running max / sum in f32 registers, exp2, P rounded to bf16 and stored back to TMEM over
-//               the scores; rescales O in TMEM when the running max grows; at the end normalises O and stores
-//               its row (256 contiguous bytes) straight from registers
+//               scores, running max / sum in f32 registers, exp2 (a quarter of them by a cubic on the FMA pipe,
+//               the rest on the MUFU unit), P rounded to bf16 and stored back to TMEM over the scores, announced
+//               in two halves so that P V starts on the first 64 keys while the rest are computed; rescales O in
+//               TMEM when the running max grows; at the end normalises O and stores its row (256 contiguous
+//               bytes) straight from registers
 //
 // TMEM (512 columns): S_A | S_B | O_A | O_B, 128 f32 columns each; P_t (bf16, two per column) overlays the
-// first 64 columns of S_t. While one slot's softmax runs, the tensor core works on the other slot.
+// first 64 columns of S_t. While one slot's softmax runs, the tensor core works on the other slot. Per slot the
+// chain softmax -> P V -> next Q K^T is serial (S and P alias), which is what bounds the kernel: ~1800 cycles of
+// softmax and ~1400 from its last store to the next scores, against 1024 cycles of MMAs per block and slot.
 //
 // Numerics follow the reference: q arrives pre-scaled; scores in f32 from bf16 operands; masked scores are
 // -1e30; the row sum adds the unrounded probabilities while P is rounded to bf16 before P @ V; one division at
@@ -66,9 +73,6 @@ struct AttnSmem {
   static constexpr int TOTAL = LAST_OFF + AT_MAX_TILES * 4 + 1024;
 };
 
-#ifndef TJX_AT_KDIV
-#define TJX_AT_KDIV 1
-#endif
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -76,13 +80,9 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
 }
 
 __device__ __forceinline__ float fast_exp2(float x) {
-#ifdef TJX_AT_WHATIF_NOEXP
-  return x * 1e-3f;  // (timing experiment only: wrong values)
-#else
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
-#endif
 }
 
 // 2^x for a pair of elements. POLY: on the FMA pipe — x = n + f with n the nearest integer (the float trick of
@@ -260,13 +260,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (whole warp; one lane issues)
     {
-#ifdef TJX_AT_WHATIF_N64
-      const uint32_t idesc_qk = idesc_bf16_f32(128, 64, 0, 0);
-      const uint32_t idesc_pv = idesc_bf16_f32(128, 64, 0, 1);
-#else
       const uint32_t idesc_qk = idesc_bf16_f32(128, 128, 0, 0);  // Q and K both K-major (K read "transposed")
       const uint32_t idesc_pv = idesc_bf16_f32(128, 128, 0, 1);  // P from TMEM, V MN-major
-#endif
       int g0 = 0;            // ring position of the current unit's block 0
       int used[2] = {0, 0};  // units that used slot t so far
       int done[2] = {0, 0};  // blocks of slot t in earlier units (phase of s_full / p_ready / o_done)

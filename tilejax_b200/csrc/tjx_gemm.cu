@@ -221,7 +221,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(base_ptr + L::BAR_OFF + 8 * (2 * STAGES + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + L::BAR_OFF + 8 * (2 * STAGES + 4) + 8);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
   const int per = p.sub_m * p.sub_n;
   const int total_items = (p.n_tiles + p.n_fills) * per;
   constexpr uint32_t TMEM_COLS = 2 * BN;
@@ -250,7 +250,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tmem_base = __shfl_sync(0xFFFFFFFFu, *tmem_holder, 0);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -287,21 +287,26 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp runs the loop, so that addresses and descriptors stay in uniform registers; one elected lane
+    // issues each ring slot's four MMAs and the commit as one predicated block.
+    {
       const uint32_t idesc = idesc_bf16_f32(BM, BN, 0, p.b_kmajor ? 0 : 1);
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
       long long t_first = 0, in_wait = 0, fill_wait = -1, out_wait = 0, items = 0;
+      auto wait = [&](uint32_t bar, uint32_t parity, int code, long long& waited) {
+        return __all_sync(0xFFFFFFFFu, mbar_wait_timed(bar, parity, abort_flag, p.status, code, waited, prof != nullptr)) != 0;
+      };
       for (int w = blockIdx.x; w < total_items && ok; w += gridDim.x) {
         const Item it = decode_item<BM, BN>(p, w);
-        if (!it.compute) continue;
+        if (!__shfl_sync(0xFFFFFFFFu, static_cast<int>(it.compute), 0)) continue;
         if (items++ == 0) t_first = clock64();
-        if (!mbar_wait_timed(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, TJX_ERR_WAIT_TMEM_EMPTY, out_wait, prof != nullptr)) break;
+        if (!wait(tempty_bar(acc), acc_phase ^ 1u, TJX_ERR_WAIT_TMEM_EMPTY, out_wait)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait_timed(full_bar(stage), phase, abort_flag, p.status, TJX_ERR_WAIT_FULL, in_wait, prof != nullptr)) {
+          if (!wait(full_bar(stage), phase, TJX_ERR_WAIT_FULL, in_wait)) {
             ok = false;
             break;
           }
@@ -309,27 +314,28 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
           tc_fence_after_sync();
           const uint32_t a_addr = base + L::RING_OFF + stage * L::STAGE_BYTES;
           const uint32_t b_addr = a_addr + L::A_BYTES;
+          // (Descriptor addresses count 16 bytes; adding a slice's offset never carries out of the field.)
+          const uint64_t a0 = smem_desc_sw128(a_addr, 16, 1024);
+          const uint64_t b0 = p.b_kmajor ? smem_desc_sw128(b_addr, 16, 1024) : smem_desc_sw128(b_addr, 64 * BK * 2, 1024);
+          const uint32_t b_step = p.b_kmajor ? 32 >> 4 : (16 * 128) >> 4;
+          uint64_t ad[4], bd[4];
 #pragma unroll
-          for (int kk = 0; kk < BK / 16; ++kk) {
-            const uint64_t a_desc = smem_desc_sw128(a_addr + kk * 32, 16, 1024);
-            const uint64_t b_desc = p.b_kmajor ? smem_desc_sw128(b_addr + kk * 32, 16, 1024)
-                                               : smem_desc_sw128(b_addr + kk * (16 * 128), 64 * BK * 2, 1024);
-            mma_ss(d_tmem, a_desc, b_desc, idesc, (kb | kk) != 0 ? 1u : 0u);
-          }
-          mma_commit(empty_bar(stage));  // the slot is free once these MMAs have read it
+          for (int kk = 0; kk < 4; ++kk) ad[kk] = a0 + kk * (32 >> 4), bd[kk] = b0 + kk * b_step;
+          // The slot is free once these MMAs have read it.
+          mma_ss_x4_commit(d_tmem, ad, bd, idesc, kb != 0 ? 1u : 0u, empty_bar(stage));
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (!ok) break;
-        mma_commit(tfull_bar(acc));  // the accumulator is complete once every MMA above has finished
+        mma_commit_elected(tfull_bar(acc));  // the accumulator is complete once every MMA above has finished
         if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1u;
         }
       }
-      if (prof != nullptr) {
+      if (prof != nullptr && lane == 0) {
         prof[1] = t_first, prof[2] = clock64(), prof[3] = in_wait, prof[4] = max(fill_wait, 0ll), prof[5] = out_wait;
         prof[6] = items;
       }
@@ -489,8 +495,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(base_ptr + L::BAR_OFF + 8 * (2 * STAGES + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + L::BAR_OFF + 8 * (2 * STAGES + 4) + 8);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t rank = cluster_cta_rank();  // 0: issues the MMAs; 1: stages and stores its half
+  const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
+  const uint32_t rank = __shfl_sync(0xFFFFFFFFu, cluster_cta_rank(), 0);  // 0: issues the MMAs; 1: stages and stores its half
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int per = p.sub_m * p.sub_n;
   const int total_items = (p.n_tiles + p.n_fills) * per;
@@ -522,7 +528,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
   __syncthreads();
   cluster_sync_all();  // the peer's barriers are initialised before anything of ours can reach them
   tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tmem_base = __shfl_sync(0xFFFFFFFFu, *tmem_holder, 0);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer (one per CTA)
@@ -583,55 +589,58 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (even CTA only)
-    if (lane == 0 && rank == 0) {
+    // The whole warp runs the loop (uniform registers for addresses and descriptors); one elected lane issues.
+    if (rank == 0) {
       const uint32_t idesc = idesc_bf16_f32(PAIR_ROWS, BN, 0, p.b_kmajor ? 0 : 1);
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
       long long t_first = 0, in_wait = 0, fill_wait = -1, out_wait = 0, items = 0;
+      auto wait = [&](uint32_t bar, uint32_t parity, int code, long long& waited) {
+        return __all_sync(0xFFFFFFFFu, mbar_wait_timed(bar, parity, abort_flag, p.status, code, waited, prof != nullptr)) != 0;
+      };
       for (int w = pair; w < total_items && ok; w += n_pairs) {
         const Item it = decode_item<PAIR_ROWS, BN>(p, w);
-        if (!it.compute) continue;
+        if (!__shfl_sync(0xFFFFFFFFu, static_cast<int>(it.compute), 0)) continue;
         if (items++ == 0) t_first = clock64();
-        if (!mbar_wait_timed(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, TJX_ERR_WAIT_TMEM_EMPTY, out_wait, prof != nullptr)) break;
+        if (!wait(tempty_bar(acc), acc_phase ^ 1u, TJX_ERR_WAIT_TMEM_EMPTY, out_wait)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int slot = 0; slot < num_slots; ++slot) {
-          if (!mbar_wait_timed(full_bar(stage), phase, abort_flag, p.status, TJX_ERR_WAIT_FULL, in_wait, prof != nullptr)) {
+          if (!wait(full_bar(stage), phase, TJX_ERR_WAIT_FULL, in_wait)) {
             ok = false;
             break;
           }
           if (fill_wait < 0) fill_wait = in_wait;
           tc_fence_after_sync();
+          const uint32_t b_step = p.b_kmajor ? 32 >> 4 : (16 * 128) >> 4;
 #pragma unroll
           for (int sub = 0; sub < KSUB; ++sub) {
             const uint32_t a_addr = base + L::RING_OFF + stage * L::STAGE_BYTES + sub * L::SUB_BYTES;
             const uint32_t b_addr = a_addr + L::A_BYTES;
+            // (Descriptor addresses count 16 bytes; adding a slice's offset never carries out of the field.)
+            const uint64_t a0 = smem_desc_sw128(a_addr, 16, 1024);
+            const uint64_t b0 = p.b_kmajor ? smem_desc_sw128(b_addr, 16, 1024) : smem_desc_sw128(b_addr, 64 * BK * 2, 1024);
+            uint64_t ad[4], bd[4];
 #pragma unroll
-            for (int kk = 0; kk < BK / 16; ++kk) {
-              const uint64_t a_desc = smem_desc_sw128(a_addr + kk * 32, 16, 1024);
-              const uint64_t b_desc = p.b_kmajor ? smem_desc_sw128(b_addr + kk * 32, 16, 1024)
-                                                 : smem_desc_sw128(b_addr + kk * (16 * 128), 64 * BK * 2, 1024);
-              mma_ss_pair(d_tmem, a_desc, b_desc, idesc, (slot | sub | kk) != 0 ? 1u : 0u);
-            }
+            for (int kk = 0; kk < 4; ++kk) ad[kk] = a0 + kk * (32 >> 4), bd[kk] = b0 + kk * b_step;
+            mma_ss_pair_x4(d_tmem, ad, bd, idesc, (slot | sub) != 0 ? 1u : 0u);
           }
           // The slot is free in both CTAs once these MMAs have read it.
-          mma_commit_pair(cluster_map(empty_bar(stage), 0));
-          mma_commit_pair(cluster_map(empty_bar(stage), 1));
+          mma_commit_pair_both(cluster_map(empty_bar(stage), 0), cluster_map(empty_bar(stage), 1));
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (!ok) break;
-        mma_commit_pair(cluster_map(tfull_bar(acc), 0));
-        mma_commit_pair(cluster_map(tfull_bar(acc), 1));
+        mma_commit_pair_both(cluster_map(tfull_bar(acc), 0), cluster_map(tfull_bar(acc), 1));
         if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1u;
         }
       }
-      if (prof != nullptr) {
+      if (prof != nullptr && lane == 0) {
         prof[1] = t_first, prof[2] = clock64(), prof[3] = in_wait, prof[4] = max(fill_wait, 0ll), prof[5] = out_wait;
         prof[6] = items;
       }

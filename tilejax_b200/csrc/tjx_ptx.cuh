@@ -119,7 +119,11 @@ __device__ __forceinline__ bool mbar_wait_timed(uint32_t bar, uint32_t parity, v
 //   [3] cycles it waited for inputs (ring slots to fill)   [4] of which the first wait: the pipeline filling
 //   [5] cycles it waited for room for its results (accumulator or output slot still being drained)
 //   [6] work items it ran   [7] clock at CTA end
-//   [8..15] kernel-specific (attention: [8] cycles the MMA thread waited for the softmax warps' probabilities)
+//   [8..15] kernel-specific. Attention: [8] cycles the MMA warp waited for the softmax warps' probabilities;
+//           [9] cycles to issue the first Q K^T (idle pipe), [10] cycles in all Q K^T issues, [11] their count;
+//           slot A's first softmax warp: [12] cycles busy, [13] cycles waiting for scores, [14] blocks,
+//           [15] three 21-bit fields, high to low: cycles in the TMEM load, in the row max (and rescale), in the
+//           exponentials
 constexpr int PROFILE_WORDS = 16;
 
 // ---------------------------------------------------------------------------------------------- fences
@@ -484,6 +488,63 @@ __device__ __forceinline__ void mma_ss_pair(uint32_t d_tmem, uint64_t a_desc, ui
 __device__ __forceinline__ void mma_commit_pair(uint32_t cluster_bar) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar)
                : "memory");
+}
+
+// Four MMAs with both operands in shared memory (one 64-deep ring slot) and the commit that frees the slot.
+__device__ __forceinline__ void mma_ss_x4_commit(uint32_t d_tmem, const uint64_t* a, const uint64_t* b, uint32_t idesc,
+                                                 uint32_t accumulate_first, uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred L, F, T;\n\t"
+      "elect.sync _|L, 0xFFFFFFFF;\n\t"
+      "setp.ne.b32 F, %2, 0;\n\t"
+      "setp.eq.b32 T, 0, 0;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], %4, %8, %1, F;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], %5, %9, %1, T;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], %6, %10, %1, T;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], %7, %11, %1, T;\n\t"
+      "@L tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%3];\n\t"
+      "}\n"
+      :
+      : "r"(d_tmem), "r"(idesc), "r"(accumulate_first), "r"(bar), "l"(a[0]), "l"(a[1]), "l"(a[2]), "l"(a[3]), "l"(b[0]),
+        "l"(b[1]), "l"(b[2]), "l"(b[3])
+      : "memory");
+}
+
+// The pair forms: four pair MMAs; one arrival on a barrier of each CTA of the pair.
+__device__ __forceinline__ void mma_ss_pair_x4(uint32_t d_tmem, const uint64_t* a, const uint64_t* b, uint32_t idesc,
+                                               uint32_t accumulate_first) {
+  asm volatile(
+      "{\n\t.reg .pred L, F, T;\n\t"
+      "elect.sync _|L, 0xFFFFFFFF;\n\t"
+      "setp.ne.b32 F, %2, 0;\n\t"
+      "setp.eq.b32 T, 0, 0;\n\t"
+      "@L tcgen05.mma.cta_group::2.kind::f16 [%0], %3, %7, %1, F;\n\t"
+      "@L tcgen05.mma.cta_group::2.kind::f16 [%0], %4, %8, %1, T;\n\t"
+      "@L tcgen05.mma.cta_group::2.kind::f16 [%0], %5, %9, %1, T;\n\t"
+      "@L tcgen05.mma.cta_group::2.kind::f16 [%0], %6, %10, %1, T;\n\t"
+      "}\n"
+      :
+      : "r"(d_tmem), "r"(idesc), "r"(accumulate_first), "l"(a[0]), "l"(a[1]), "l"(a[2]), "l"(a[3]), "l"(b[0]), "l"(b[1]),
+        "l"(b[2]), "l"(b[3])
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit_pair_both(uint32_t cluster_bar0, uint32_t cluster_bar1) {
+  asm volatile(
+      "{\n\t.reg .pred L;\n\t"
+      "elect.sync _|L, 0xFFFFFFFF;\n\t"
+      "@L tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+      "@L tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%1];\n\t"
+      "}\n" ::"r"(cluster_bar0),
+      "r"(cluster_bar1)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit_elected(uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred L;\n\t"
+      "elect.sync _|L, 0xFFFFFFFF;\n\t"
+      "@L tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+      "}\n" ::"r"(bar)
+      : "memory");
 }
 
 // ---------------------------------------------------------------------------------------------- TMEM <-> regs
