@@ -414,6 +414,30 @@ def extra_workloads(device, pk: dict, pk_kind: str, only: str | None = None, ite
         except Exception as e:  # not built yet, or failed: report, do not hide
             out[name] = {"error": str(e)[:200]}
 
+    if want("attention_block"):
+        # A whole attention block (examples/attention_block.py:49-85) at the size the reference lowers for its TPU
+        # (tests/test_examples.py:201-206): B 4, 8 heads of 128, S 2048, D 1024, F 4096. Four launches: attention,
+        # row norm, matmul + GELU, matmul. Flops: the causal attention's plus 4 * B * S * D * F for the two matmuls.
+        name = "attention_block_B4_H8_S2048_D1024_F4096"
+        try:
+            B, H, S, Dh, F = 4, 8, 2048, 128, 4096
+            D = H * Dh
+            q = device_randn_bf16((B, H, S, Dh), 0, device, Dh**-0.5)
+            k = device_randn_bf16((B, H, S, Dh), 1, device)
+            v = device_randn_bf16((B, H, S, Dh), 2, device)
+            gamma = (1 + 0.1 * device_randn_bf16((1, D), 7, device).float()).to(torch.bfloat16)
+            w_up = device_randn_bf16((D, F), 8, device, D**-0.5)
+            w_down = device_randn_bf16((F, D), 9, device, F**-0.5)
+            fn = lambda: ops.attention_block(q, k, v, gamma, w_up, w_down, 256, 512, 1024)  # noqa: E731
+            ms = time_device(fn, iters, warm, flush)
+            tensor_entry(name, ms, 4.0 * B * H * Dh * S * (S + 1) / 2 + 4.0 * B * S * D * F, extra={
+                "algorithmic_flops": "4*B*H*Dh*S*(S+1)/2 + 4*B*S*D*F",
+                "launches": "attention_kernel, rmsnorm_rows_kernel, gemm (GELU epilogue), gemm",
+                "via_autokernel_ms": frontend_ms(
+                    lambda: kernels.attention_block(q, k, v, gamma, w_up, w_down, kernels.BlockTiles(256, 512, 1024)))})
+        except Exception as e:
+            out[name] = {"error": str(e)[:200]}
+
     if want("mla_decode"):
         # The reference's MLA benchmark shape (benchmarks/decode.py:152-173): batch 32, contexts around 2048 of a
         # 4096-position cache, 64 heads, 512 latents + 64 RoPE columns (stored 128 wide), blocks of 512.

@@ -114,6 +114,26 @@ int tjx_rmsnorm_gemm_bf16(const void* x, const void* gamma, const void* w, void*
                           int tm, int tn, int tk, int out_f32, void* workspace, size_t workspace_bytes,
                           tjx_stream_t stream);
 
+/* Bytes of scratch tjx_attention_block_bf16 needs for these sizes. */
+size_t tjx_attention_block_workspace_bytes(int B, int H, int S, int Dh, int F);
+
+/* A whole attention block, the two-phase loop nest `attention_block` (examples/attention_block.py:49-85): causal
+ * multi-head attention (phase 1, the step tables' key blocks per query tile, as tjx_causal_attention_bf16), the heads
+ * put side by side in f32, RMSNorm over the model dimension D = H * Dh, and the feed-forward layer
+ * out = bf16(gelu(n @ w_up)) @ w_down (phase 2; tanh GELU, jax.nn.gelu's default) with f32 accumulation in both
+ * products (src/autokernel/mxu.py:21-35). Where the reference keeps a query block's intermediates on chip, this runs
+ * four launches on `stream` with them in `workspace`: attention, a row-wise norm, and two matmul step loops.
+ *   q, k, v [B, H, S, Dh] bf16 (q pre-scaled); gamma [1, D] bf16; w_up [D, F] bf16; w_down [F, D] bf16
+ *   out [B, S, D] bf16
+ *   block_q, block_kv, step_tile, step_code, pattern_steps, pattern_tiles: as tjx_causal_attention_bf16
+ *   workspace: at least tjx_attention_block_workspace_bytes(B, H, S, Dh, F) bytes, 256-byte aligned
+ * Constraints: Dh == 128; S % 128 == 0; F % 128 == 0. */
+int tjx_attention_block_bf16(const void* q, const void* k, const void* v, const void* gamma, const void* w_up,
+                             const void* w_down, void* out, int B, int H, int S, int Dh, int F, int block_q,
+                             int block_kv, float eps, const int32_t* step_tile, const int32_t* step_code,
+                             int pattern_steps, int pattern_tiles, void* workspace, size_t workspace_bytes,
+                             tjx_stream_t stream);
+
 /* Caps the number of persistent CTAs tjx_gemm_bf16 launches from the calling thread (0 = one per SM, the
  * default). For callers that run communication kernels beside the GEMM — the collective matmul's exchange rounds
  * stand in for the ring DMAs of the reference's kernel (src/autokernel/codegen.py:1161-1229), which need no

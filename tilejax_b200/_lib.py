@@ -30,6 +30,8 @@ SYMBOLS: dict[str, tuple] = {
     "tjx_rmsnorm_gemm_workspace_bytes": (c_size_t, [c_int, c_int]),
     "tjx_rmsnorm_gemm_bf16": (c_int, [_P, _P, _P, _P, c_int, c_int, c_int, ctypes.c_float, c_int, c_int, c_int, c_int, _P,
                                       c_size_t, _P]),
+    "tjx_attention_block_workspace_bytes": (c_size_t, [c_int] * 5),
+    "tjx_attention_block_bf16": (c_int, [_P] * 7 + [c_int] * 7 + [ctypes.c_float, _P, _P, c_int, c_int, _P, c_size_t, _P]),
     "tjx_gemm_set_cta_limit": (c_int, [c_int]),
     "tjx_gemm_set_pair_mode": (c_int, [c_int]),
     "tjx_all_gather_gemm_bf16": (c_int, [_P] * 5 + [c_int] * 8 + [_P, _P, c_int, _P, c_int, _P]),

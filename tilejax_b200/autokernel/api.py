@@ -329,6 +329,12 @@ def _check_kernel_rules(plan: Plan) -> None:
         if not (p["tm"] % 128 == 0 or p["tm"] == p["M"]) or not (p["tn"] % 128 == 0 or p["tn"] == p["N"]):
             raise nest.error(f"tiles of {p['tm']} x {p['tn']}: output tiles must be multiples of 128 (the tensor core's "
                              "tile) or span the matrix")
+    elif plan.family == "attention_block":
+        if p["D"] != 128 or p["S"] % 128 or p["block_q"] % 128 or p["block_kv"] % 128 or p["F"] % 128:
+            raise nest.error("the attention block's kernels take head_dim 128, blocks that are multiples of 128 and a "
+                             "hidden width that is a multiple of 128")
+        if any(np.dtype(s.dtype) != bf16 for s in plan.specs[:6]):
+            raise nest.error("the attention block's kernels take bfloat16 inputs")
     elif plan.family == "attention":
         if p["D"] != 128 or p["S"] % 128 or p["block_q"] % 128 or p["block_kv"] % 128:
             raise nest.error("the attention kernel takes head_dim 128 and blocks that are multiples of 128")
@@ -373,6 +379,8 @@ def launch_key(plan: Plan, config: Config) -> tuple:
         return ("rmsnorm_gemm", p["tm"], p["tn"])
     if plan.family == "attention":
         return ("attention",)
+    if plan.family == "attention_block":
+        return ("attention_block",)
     if p.get("mla") or p.get("contiguous"):
         return ("decode", p["page"])
     return ("decode",)
@@ -448,6 +456,19 @@ def _lower(plan: Plan, config: Config) -> tuple[str, Callable[..., Any]]:
             f"CTA         two 128-row query tiles sharing each 128-key K/V block; future blocks skipped\n"
             f"tables      {', '.join(f'{k}[{len(v)}]' for k, v in sch.tables.items()) or 'none'}\n")
         return text, lambda q, k, v: ops.causal_attention(q, k, v, p["block_q"], p["block_kv"])
+    if plan.family == "attention_block":
+        D = p["H"] * p["D"]
+        text = header + (
+            f"kernel      tjx_attention_block_bf16 (four launches on one stream: tcgen05 attention writing the heads side "
+            f"by side in f32, a row-wise RMSNorm, the matmul step loop with tanh GELU in its epilogue, the matmul step loop)\n"
+            f"problem     q, k, v [{p['B']}, {p['H']}, {p['S']}, {p['D']}], gamma [1, {D}], w_up [{D}, {p['F']}], "
+            f"w_down [{p['F']}, {D}] bfloat16 -> out [{p['B']}, {p['S']}, {D}]\n"
+            f"user blocks {p['block_q']} x {p['block_kv']}, {p['block_f']} hidden units: {sch.tiles} tiles, {sch.steps} steps, "
+            f"phases {', '.join(p['phases']) or 'none'}\n"
+            f"on chip     the reference keeps a tile's attention output and hidden activations in VMEM; here they pass "
+            f"through a workspace that stays in L2 at these sizes\n")
+        return text, lambda q, k, v, gamma, w_up, w_down: ops.attention_block(
+            q, k, v, gamma, w_up, w_down, p["block_q"], p["block_kv"], p["block_f"], p["eps"])
     if p.get("mla"):
         text = header + (
             f"kernel      tjx_mla_decode_bf16 (device step tables, CTA-wide TMA ring, warp-level MMA over 16 heads, "

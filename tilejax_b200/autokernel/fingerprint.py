@@ -170,7 +170,8 @@ def _write(path: str, found: dict[str, dict[str, str]]) -> None:
              "",
              "Written by `python -m tilejax_b200.autokernel.fingerprint [reference/examples]`: the forms in this package's",
              "kernels.py and, when the reference's example files are at hand, the forms in examples/causal_attention.py,",
-             'examples/decode.py and examples/rmsnorm_matmul.py (lane-replicated row statistics, block-diagonal queries).',
+             'examples/decode.py, examples/rmsnorm_matmul.py and examples/attention_block.py (lane-replicated row',
+             'statistics, block-diagonal queries).',
              'Do not edit by hand."""',
              "", "RECOGNISED: dict[str, dict[str, str]] = {"]
     for family in sorted(found):
@@ -189,14 +190,14 @@ def main(argv: list[str]) -> None:
     from tilejax_b200.autokernel import jaxlike, kernels
 
     families = {"attention": ["causal_attention"], "decode": ["paged_gqa_decode", "gqa_decode"], "mla": ["mla_decode"],
-                "rmsnorm": ["rmsnorm_matmul"]}
+                "rmsnorm": ["rmsnorm_matmul"], "attention_block": ["attention_block"]}
     found: dict[str, dict[str, str]] = {f: {} for f in families}
     for family, names in families.items():
         for name in names:
             found[family][fingerprint(getattr(kernels, name))] = f"tilejax_b200/autokernel/kernels.py {name}"
     if len(argv) > 1:
         stand_ins = {"jax": jaxlike, "jnp": jaxlike.numpy, "autokernel": autokernel, "__name__": "example"}
-        for file in ("causal_attention.py", "decode.py", "rmsnorm_matmul.py"):
+        for file in ("causal_attention.py", "decode.py", "rmsnorm_matmul.py", "attention_block.py"):
             ns = load_example(os.path.join(argv[1], file), stand_ins)
             for family, names in families.items():
                 for name in names:

@@ -204,6 +204,20 @@ def _concatenate(arrays, axis=0):
     return Array(np.concatenate([np.asarray(_raw(a)) for a in arrays], axis=axis))
 
 
+def _stack(arrays, axis=0):
+    return Array(np.stack([np.asarray(_raw(a)) for a in arrays], axis=axis))
+
+
+def _gelu(x, approximate=True):
+    """jax.nn.gelu: the tanh form by default, in x's own precision."""
+    x = np.asarray(_raw(x))
+    if not approximate:
+        raise NotImplementedError("the exact (erf) GELU is not used by the hot-path loop nests")
+    one, half = x.dtype.type(1), x.dtype.type(0.5)
+    cubic = x + x.dtype.type(0.044715) * x * x * x
+    return Array((half * x * (one + np.tanh(x.dtype.type(np.sqrt(2.0 / np.pi)) * cubic))).astype(x.dtype))
+
+
 def _full(shape, value, dtype=None):
     return Array(np.full(shape, _raw(value), dtype or np.float32))
 
@@ -227,8 +241,10 @@ numpy = types.SimpleNamespace(
     max=_lift(np.max), sum=_lift(np.sum), tile=_lift(np.tile), concatenate=_concatenate,
     arange=_lift(np.arange), clip=_lift(np.clip), dot=_dot, matmul=_matmul, tril=_lift(np.tril),
     abs=_lift(np.abs), logical_not=_lift(np.logical_not), sqrt=_lift(np.sqrt), mean=_lift(np.mean),
-    square=_lift(np.square), transpose=_lift(np.transpose), reshape=_lift(np.reshape),
+    square=_lift(np.square), transpose=_lift(np.transpose), reshape=_lift(np.reshape), stack=_stack,
+    tanh=_lift(np.tanh),
 )
+nn = types.SimpleNamespace(gelu=_gelu)
 lax = types.SimpleNamespace(broadcasted_iota=_broadcasted_iota,
                             rsqrt=_lift(lambda x: (1.0 / np.sqrt(np.asarray(x))).astype(np.asarray(x).dtype)))
 

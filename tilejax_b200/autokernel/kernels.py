@@ -148,6 +148,56 @@ def causal_attention(q, k, v, blocks=AttentionBlocks()):
     return out
 
 
+@autokernel.tunable
+class BlockTiles:
+    """Queries per output tile, keys per attention step, and hidden units per feed-forward step (one block of all
+    of them makes the feed-forward phase a single step)."""
+
+    block_q: int = autokernel.choice(128, 256, 512, 1024, default=256)
+    block_kv: int = autokernel.choice(128, 256, 512, 1024, default=256)
+    block_f: int = autokernel.choice(256, 512, 1024, 2048, 4096, 8192, 16384, default=1024)
+
+
+@autokernel.kernel
+def attention_block(q, k, v, gamma, w_up, w_down, tiles=BlockTiles()):
+    """Causal multi-head attention, the RMSNorm after it and the feed-forward layer: per (batch, query block) two
+    reduction loops, one after the other — the key blocks (an online softmax for every head), then, with the heads
+    side by side and normalised together, the blocks of hidden units. q arrives pre-scaled."""
+    B, H, S, Dh = q.shape
+    D, F = H * Dh, w_up.shape[1]
+    bq, bk, bf = min(tiles.block_q, S), min(tiles.block_kv, S), min(tiles.block_f, F)
+    dtype = q.dtype
+    out = jnp.zeros((B, S, D), dtype)
+    for b in range(B):
+        for i in range(0, S, bq):
+            row_max = jnp.full((H, bq, 1), MASK_VALUE, jnp.float32)
+            row_sum = jnp.zeros((H, bq, 1), jnp.float32)  # of exp(s - row_max)
+            acc = jnp.zeros((H, bq, Dh), jnp.float32)  # sum of exp(s - row_max) @ v
+            for j in range(0, S, bk):  # phase 1: causal attention, every head
+                if j > i + bq - 1:  # every key is in the future of every query
+                    continue
+                qt, kt, vt = q[b, :, i : i + bq, :], k[b, :, j : j + bk, :], v[b, :, j : j + bk, :]
+                rows = i + jax.lax.broadcasted_iota(jnp.int32, (bq, bk), 0)
+                cols = j + jax.lax.broadcasted_iota(jnp.int32, (bq, bk), 1)
+                s = jnp.stack([jnp.where(cols <= rows, qt[h] @ kt[h].T, MASK_VALUE) for h in range(H)])
+                max_new = jnp.maximum(row_max, jnp.max(s, axis=2, keepdims=True))
+                p = jnp.exp(s - max_new)
+                alpha = jnp.exp(row_max - max_new)
+                row_sum = alpha * row_sum + jnp.sum(p, axis=2, keepdims=True)
+                pv = jnp.stack([p[h].astype(dtype) @ vt[h] for h in range(H)])
+                acc = alpha * acc + pv
+                row_max = max_new
+            heads = acc / row_sum
+            a = jnp.concatenate([heads[h] for h in range(H)], axis=1)  # (bq, D): the heads side by side
+            normed = (a * jax.lax.rsqrt(jnp.mean(a * a, axis=1, keepdims=True) + EPS) * gamma[0:1, :]).astype(dtype)
+            y = jnp.zeros((bq, D), jnp.float32)
+            for f in range(0, F, bf):  # phase 2: the feed-forward layer, bf hidden units at a time
+                hidden = jax.nn.gelu(normed @ w_up[:, f : f + bf])
+                y += hidden.astype(dtype) @ w_down[f : f + bf, :]
+            out = out.at[b, i : i + bq, :].set(y.astype(dtype))
+    return out
+
+
 def queries_by_kv_head(qt, kv_heads):
     """A sequence's queries (T, H, Dh) as (Hkv, T * G, Dh): head h attends with KV head h // G, and a KV head's
     rows are its (new token, query head) pairs, token-major."""

@@ -11,6 +11,9 @@ nest is matched against the schedules this backend has kernels for:
               softmax, `q @ k.T` and `p @ v`
   decode      one parallel loop over sequences, a reduction loop over pages masked by an index array, pages chosen
               through a block table
+  attention_block  two parallel loops (b, i) and two reduction loops per tile: the key blocks of causal attention
+              over all heads, then the hidden units of the feed-forward layer after an RMSNorm
+  rmsnorm_gemm     RMSNorm fused with the projection after it
 Anything else is a KernelError ("not a recognised schedule"): there is no generic code generator and no fallback.
 """
 
@@ -244,6 +247,8 @@ def _require_known_form(nest: Nest, fn, family: str) -> None:
     if digest not in RECOGNISED[family]:
         what = {"rmsnorm": "RMSNorm fused with the projection after it, `rsqrt(mean(x^2) + eps) * ((x * gamma) @ w)`",
                 "attention": "causal attention's online softmax over `q @ k.T` and `p @ v`",
+                "attention_block": "an attention block: causal attention over all heads, RMSNorm of the heads side by "
+                                   "side, then `gelu(n @ w_up) @ w_down`",
                 "decode": "GQA decode's online softmax over the cache blocks",
                 "mla": "absorbed MLA decode's online softmax over the latent cache"}[family]
         raise _unsupported(nest, f"the loops and masks are those of {what}, but the tile code is not a form of it this "
@@ -252,8 +257,12 @@ def _require_known_form(nest: Nest, fn, family: str) -> None:
 
 def _recognise(nest, fn, ns, specs, outputs, parallel, reductions, chips) -> Plan:
     n_par, n_red = len(parallel), len(reductions)
+    if n_red == 2 and n_par == 2 and len(nest.inputs) == 6 and not nest.runtime_masks and not nest.all_gathers:
+        plan = _recognise_attention_block(nest, ns, specs, outputs, parallel, reductions)
+        _require_known_form(nest, fn, "attention_block")
+        return plan
     if n_red != 1:
-        raise _unsupported(nest, f"{n_red} reduction loops (one is supported)")
+        raise _unsupported(nest, f"{n_red} reduction loops (one is supported, or the two phases of an attention block)")
     if nest.runtime_masks:
         plan = _recognise_decode(nest, ns, specs, outputs, parallel, reductions)
         _require_known_form(nest, fn, "mla" if plan.params.get("mla") else "decode")
@@ -478,6 +487,44 @@ def _recognise_attention(nest, ns, specs, outputs, parallel, reductions) -> Plan
     sch = nest_schedule(nest, ns, parallel, reductions)
     params = dict(B=B, H=H, S=S, D=D, block_q=i.step, block_kv=j.step, schedule=sch)
     return Plan(nest, "attention", specs, outputs, parallel, reductions, params)
+
+
+def phases_of(nest: Nest, reductions) -> tuple[Range, ...]:
+    """The reduction loops that take steps of their own: one of a single iteration and no mask runs inline, in the
+    code around it (src/autokernel/plan.py:8-11)."""
+    return tuple(r for r, loop in zip(reductions, nest.reductions, strict=True) if r.count > 1 or loop.mask is not None)
+
+
+def _recognise_attention_block(nest, ns, specs, outputs, parallel, reductions) -> Plan:
+    """`attention_block` (examples/attention_block.py:49-85): (q, k, v, gamma, w_up, w_down) with q, k, v
+    (B, H, S, Dh), gamma (1, D), w_up (D, F), w_down (F, D), D = H * Dh; loops (b, i) over the query blocks, then two
+    phases per tile: j over the key blocks with the causal step mask, f over the hidden units. What the tile code
+    computes is pinned by its fingerprint (the caller checks it); here the shapes, the loops and the mask."""
+    (b, i), (j, f) = parallel, reductions
+    q, k, v, gamma, w_up, w_down = specs[:6]
+    if q.ndim != 4 or k.shape != q.shape or v.shape != q.shape or len(outputs) != 1:
+        raise _unsupported(nest, "an attention block takes q, k, v of one shape (B, H, S, Dh)")
+    B, H, S, Dh = q.shape
+    D = H * Dh
+    if gamma.shape != (1, D) or w_up.ndim != 2 or w_up.shape[0] != D or w_down.shape != (w_up.shape[1], D) \
+            or outputs[0].shape != (B, S, D):
+        raise _unsupported(nest, f"an attention block takes gamma (1, {D}), w_up ({D}, F) and w_down (F, {D}) and "
+                                 f"stores ({B}, {S}, {D})")
+    F = w_up.shape[1]
+    mask = nest.reductions[0].mask
+    if mask is None or nest.reductions[1].mask is not None or any(l.mask is not None for l in nest.parallel):
+        raise _unsupported(nest, "an attention block masks its key loop with `j > i + block_q - 1`, and nothing else")
+    holds = _mask_fn(nest, ns, mask, [i.var, j.var])
+    causal = all(holds(i.value(bi), j.value(bj)) == (j.value(bj) > i.value(bi) + i.step - 1)
+                 for bi in range(i.count) for bj in range(j.count))
+    if not causal or (b.start, b.stop, b.step, i.start, i.stop, j.start, j.stop, f.start, f.stop) != (0, B, 1, 0, S, 0, S, 0, F):
+        raise _unsupported(nest, "the step mask must be the causal one, `j > i + block_q - 1`, and the loops must "
+                                 "cover the batch, the sequence and the hidden units", nest.reductions[0].node)
+    phases = phases_of(nest, reductions)
+    sch = nest_schedule(nest, ns, parallel, phases)
+    params = dict(B=B, H=H, S=S, D=Dh, F=F, block_q=i.step, block_kv=j.step, block_f=f.step,
+                  eps=float(ns.get("EPS", 1e-6)), schedule=sch, phases=tuple(r.var for r in phases))
+    return Plan(nest, "attention_block", specs, outputs, parallel, reductions, params)
 
 
 def _recognise_contiguous_decode(nest, ns, specs, outputs, parallel, reductions) -> Plan:

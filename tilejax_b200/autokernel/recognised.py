@@ -2,13 +2,18 @@
 
 Written by `python -m tilejax_b200.autokernel.fingerprint [reference/examples]`: the forms in this package's
 kernels.py and, when the reference's example files are at hand, the forms in examples/causal_attention.py,
-examples/decode.py and examples/rmsnorm_matmul.py (lane-replicated row statistics, block-diagonal queries).
+examples/decode.py, examples/rmsnorm_matmul.py and examples/attention_block.py (lane-replicated row
+statistics, block-diagonal queries).
 Do not edit by hand."""
 
 RECOGNISED: dict[str, dict[str, str]] = {
     "attention": {
         "c0907b9932813d96d8d5d1f74db165d93c89872bf5fd1650ac21326ccad72e03": "examples/causal_attention.py causal_attention",
         "dffc41f8367fc51d53b1060ab8009f21a063452afd282a1bc6d325036bca8e97": "tilejax_b200/autokernel/kernels.py causal_attention",
+    },
+    "attention_block": {
+        "7ef581c0a492777f44e2645bb412d36121f2fb4a0b2ade0d8fa6f96a66531503": "examples/attention_block.py attention_block",
+        "a0d794a17081d7572269488d57098f6abb0aa4e8683247f5daa1f64fe00e94d6": "tilejax_b200/autokernel/kernels.py attention_block",
     },
     "decode": {
         "51a65e439275a796e84d550d1efbeca191aa4c8dcadf30cddde5bacac4a58c87": "examples/decode.py gqa_decode",

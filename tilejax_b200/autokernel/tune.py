@@ -149,6 +149,9 @@ def _traffic(plan, schedule) -> int:
         return schedule.steps * per_step + (schedule.tiles + schedule.fills) * per_tile
     if plan.family == "attention":
         return schedule.tiles * 2 * p["block_q"] * p["D"] * 2 + schedule.steps * 2 * p["block_kv"] * p["D"] * 2
+    if plan.family == "attention_block":  # q and the output per tile, a K/V block of every head per step (an upper
+        width = p["H"] * p["D"]           # bound once the weights stream: their steps move weights, not K/V)
+        return schedule.tiles * 2 * p["block_q"] * width * 2 + schedule.steps * 2 * p["block_kv"] * width * 2
     width = (p["C"] + p["R"]) if p.get("mla") else 2 * p["Hkv"] * p["D"]
     return schedule.steps * p["page"] * width * 2
 

@@ -19,7 +19,7 @@ from pathlib import Path
 CSRC = Path(__file__).resolve().parent
 PACKAGE = CSRC.parent
 LIBRARY = PACKAGE / "libtilejax_b200.so"
-SOURCES = ["tjx_host.cu", "tjx_steps.cu", "tjx_gemm.cu", "tjx_rmsnorm.cu", "tjx_decode.cu", "tjx_mla.cu", "tjx_attention.cu"]
+SOURCES = ["tjx_host.cu", "tjx_steps.cu", "tjx_gemm.cu", "tjx_rmsnorm.cu", "tjx_block.cu", "tjx_decode.cu", "tjx_mla.cu", "tjx_attention.cu"]
 HEADERS = ["tjx_host.cuh", "tjx_ptx.cuh", "../../include/tilejax_b200.h"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]

@@ -56,7 +56,8 @@ struct AttnParams {
   const int32_t* step_code;
   int units_per_bh;  // pairs of 128-row query tiles per (b, h)
   int total_units;
-  __nv_bfloat16* out;
+  __nv_bfloat16* out;  // (B, H, S, D) in the input dtype, or null when `out_heads` is given
+  float* out_heads;    // (B, S, H * D) f32: the heads side by side, unrounded (attention_block's `a`), or null
   int* status;
   long long* profile;  // per-CTA counters (PROFILE_WORDS each) or null
 };
@@ -528,20 +529,37 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
       } else {
         tc_fence_after_sync();
         const float inv = 1.0f / l;
-        uint4* dst = reinterpret_cast<uint4*>(p.out + static_cast<size_t>(u.row_base + row) * AT_D);
+        if (p.out_heads != nullptr) {
+          // Row (b, s) of the (B * S, H * D) f32 matrix, columns h * D .. h * D + 127: 512 contiguous bytes.
+          const int bh = u.row_base / p.S, b = bh / p.H, h = bh % p.H;
+          float4* dst = reinterpret_cast<float4*>(
+              p.out_heads + (static_cast<size_t>(b) * p.S + row) * (static_cast<size_t>(p.H) * AT_D) + h * AT_D);
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tmem_ld32(o_tmem + c * 32, v);
-          tmem_wait_ld();
+          for (int c = 0; c < 4; ++c) {
+            uint32_t v[32];
+            tmem_ld32(o_tmem + c * 32, v);
+            tmem_wait_ld();
 #pragma unroll
-          for (int x = 0; x < 4; ++x) {
-            uint4 val;
-            val.x = pack_bf16(__uint_as_float(v[8 * x + 0]) * inv, __uint_as_float(v[8 * x + 1]) * inv);
-            val.y = pack_bf16(__uint_as_float(v[8 * x + 2]) * inv, __uint_as_float(v[8 * x + 3]) * inv);
-            val.z = pack_bf16(__uint_as_float(v[8 * x + 4]) * inv, __uint_as_float(v[8 * x + 5]) * inv);
-            val.w = pack_bf16(__uint_as_float(v[8 * x + 6]) * inv, __uint_as_float(v[8 * x + 7]) * inv);
-            dst[c * 4 + x] = val;
+            for (int x = 0; x < 8; ++x)
+              dst[c * 8 + x] = make_float4(__uint_as_float(v[4 * x]) * inv, __uint_as_float(v[4 * x + 1]) * inv,
+                                           __uint_as_float(v[4 * x + 2]) * inv, __uint_as_float(v[4 * x + 3]) * inv);
+          }
+        } else {
+          uint4* dst = reinterpret_cast<uint4*>(p.out + static_cast<size_t>(u.row_base + row) * AT_D);
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t v[32];
+            tmem_ld32(o_tmem + c * 32, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+              uint4 val;
+              val.x = pack_bf16(__uint_as_float(v[8 * x + 0]) * inv, __uint_as_float(v[8 * x + 1]) * inv);
+              val.y = pack_bf16(__uint_as_float(v[8 * x + 2]) * inv, __uint_as_float(v[8 * x + 3]) * inv);
+              val.z = pack_bf16(__uint_as_float(v[8 * x + 4]) * inv, __uint_as_float(v[8 * x + 5]) * inv);
+              val.w = pack_bf16(__uint_as_float(v[8 * x + 6]) * inv, __uint_as_float(v[8 * x + 7]) * inv);
+              dst[c * 4 + x] = val;
+            }
           }
         }
         // The reads of O above are ordered before this warp's next arrival on p_ready, which is what the next
@@ -569,13 +587,14 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
 
 }  // namespace tjx
 
-extern "C" int tjx_causal_attention_bf16(const void* q, const void* k, const void* v, void* out, int B, int H, int S,
-                                         int D, int block_q, int block_kv, const int32_t* step_tile,
-                                         const int32_t* step_code, int pattern_steps, int pattern_tiles,
-                                         tjx_stream_t stream) {
-  using namespace tjx;
+namespace tjx {
+// The launch behind tjx_causal_attention_bf16 (`out`: (B, H, S, D) bf16) and tjx_attention_block_bf16 (`out_heads`:
+// (B, S, H * D) f32); exactly one of the two is given.
+int attention_launch(const void* q, const void* k, const void* v, void* out, float* out_heads, int B, int H, int S,
+                     int D, int block_q, int block_kv, const int32_t* step_tile, const int32_t* step_code,
+                     int pattern_steps, int pattern_tiles, tjx_stream_t stream) {
   if (int rc = check_device()) return rc;
-  if (!q || !k || !v || !out) return fail(TJX_E_ARG, "q, k, v or out is null");
+  if (!q || !k || !v || (!out && !out_heads)) return fail(TJX_E_ARG, "q, k, v or out is null");
   if (!step_tile || !step_code || pattern_steps <= 0 || pattern_tiles <= 0)
     return fail(TJX_E_ARG, "the step tables are missing");
   if (B <= 0 || H <= 0 || S <= 0) return fail(TJX_E_ARG, "sizes must be positive");
@@ -593,6 +612,7 @@ extern "C" int tjx_causal_attention_bf16(const void* q, const void* k, const voi
   p.units_per_bh = (S / AT_BQ + 1) / 2;
   p.total_units = B * H * p.units_per_bh;
   p.out = static_cast<__nv_bfloat16*>(out);
+  p.out_heads = out_heads;
   if (pattern_tiles > AT_MAX_TILES) return fail(TJX_E_LIMIT, "more than 1024 query tiles per (batch, head)");
   p.status = device_status_word();
   if (p.status == nullptr) return fail(TJX_E_CUDA, "could not locate the device status word");
@@ -621,4 +641,14 @@ extern "C" int tjx_causal_attention_bf16(const void* q, const void* k, const voi
     attention_kernel<false><<<grid, AT_THREADS, AttnSmem::TOTAL, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, p);
   TJX_CUDA(cudaGetLastError());
   return 0;
+}
+}  // namespace tjx
+
+extern "C" int tjx_causal_attention_bf16(const void* q, const void* k, const void* v, void* out, int B, int H, int S,
+                                         int D, int block_q, int block_kv, const int32_t* step_tile,
+                                         const int32_t* step_code, int pattern_steps, int pattern_tiles,
+                                         tjx_stream_t stream) {
+  if (!out) return tjx::fail(TJX_E_ARG, "q, k, v or out is null");
+  return tjx::attention_launch(q, k, v, out, nullptr, B, H, S, D, block_q, block_kv, step_tile, step_code, pattern_steps,
+                               pattern_tiles, stream);
 }

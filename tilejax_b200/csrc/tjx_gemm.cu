@@ -51,6 +51,7 @@ struct GemmParams {
   int* status;
   long long* profile;  // per-CTA counters (PROFILE_WORDS each) or null
   const float* row_scale;  // [M] or null: the epilogue multiplies row r of the accumulator by row_scale[r] (rmsnorm)
+  int activation;          // 0: none; 1: tanh GELU of the f32 accumulator before the rounding (attention_block)
   // All-gather fused into the launch (gemm_pair_kernel<.., true> only): rows [own_lo, own_hi) of the gathered
   // operand are this GPU's shard and come from map_a_own; the other shards are pulled from peer memory into
   // `gather_dst` by one extra warp per CTA, 256-row block by block in arrival order, and counted in
@@ -110,6 +111,14 @@ __device__ __forceinline__ Item decode_item(const GemmParams& p, int w) {
   return it;
 }
 
+// jax.nn.gelu's default (approximate) form: 0.5 x (1 + tanh(sqrt(2 / pi) (x + 0.044715 x^3))), with
+// tanh(u) = 1 - 2 / (exp(2 u) + 1); exp overflowing to inf gives exactly 1, underflowing to 0 gives exactly -1.
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float u = 0.7978845608028654f * fmaf(0.044715f * x * x, x, x);
+  const float t = 1.0f - __fdividef(2.0f, __expf(2.0f * u) + 1.0f);
+  return 0.5f * x * (1.0f + t);
+}
+
 // Zeros for 32 rows (row0 .. row0 + 31) of a CTA tile's BN columns from n0: 16 bytes per lane per pass.
 template <int BN>
 __device__ __forceinline__ void zero_rows(const GemmParams& p, int row0, int n0, int lane) {
@@ -144,6 +153,10 @@ __device__ __forceinline__ void store_accumulator(const GemmParams& p, const CUt
     if (p.row_scale != nullptr) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * scale);
+    }
+    if (p.activation == 1) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(gelu_tanh(__uint_as_float(v[j])));
     }
     if (p.causal) {
       const int col0 = n0 + c * 32;
@@ -763,10 +776,12 @@ extern "C" int tjx_gemm_set_cta_limit(int max_ctas) {
 }
 
 namespace tjx {
-// The matmul launch behind tjx_gemm_bf16 and tjx_rmsnorm_gemm_bf16 (`row_scale`: see GemmParams).
+// The matmul launch behind tjx_gemm_bf16, tjx_rmsnorm_gemm_bf16 and tjx_attention_block_bf16 (`row_scale`,
+// `activation`: see GemmParams).
 int gemm_launch(const void* x, const void* y, void* out, int M, int N, int K, int y_transposed, int tm, int tn, int tk,
                 int stages, int out_f32, int causal, const int32_t* tile_i, const int32_t* tile_j, int n_tiles,
-                const int32_t* fill_i, const int32_t* fill_j, int n_fills, const float* row_scale, tjx_stream_t stream) {
+                const int32_t* fill_i, const int32_t* fill_j, int n_fills, const float* row_scale, int activation,
+                tjx_stream_t stream) {
   if (int rc = check_device()) return rc;
   if (x == nullptr || y == nullptr || out == nullptr) return fail(TJX_E_ARG, "x, y or out is null");
   if (M <= 0 || N <= 0 || K <= 0) return fail(TJX_E_ARG, "M, N, K must be positive");
@@ -810,6 +825,7 @@ int gemm_launch(const void* x, const void* y, void* out, int M, int N, int K, in
   p.num_kb = (K + BK - 1) / BK;
   p.out = out;
   p.row_scale = row_scale;
+  p.activation = activation;
   p.status = device_status_word();
   if (p.status == nullptr) return fail(TJX_E_CUDA, "could not locate the device status word");
 
@@ -875,7 +891,7 @@ extern "C" int tjx_gemm_bf16(const void* x, const void* y, void* out, int M, int
                              const int32_t* tile_j, int n_tiles, const int32_t* fill_i, const int32_t* fill_j,
                              int n_fills, tjx_stream_t stream) {
   return tjx::gemm_launch(x, y, out, M, N, K, y_transposed, tm, tn, tk, stages, out_f32, causal, tile_i, tile_j, n_tiles,
-                          fill_i, fill_j, n_fills, nullptr, stream);
+                          fill_i, fill_j, n_fills, nullptr, 0, stream);
 }
 
 // out = all_gather(x) @ y in ONE launch: the pair GEMM whose extra warp per CTA pulls the other ranks' shards from

@@ -19,7 +19,8 @@ namespace tjx {
 
 int gemm_launch(const void* x, const void* y, void* out, int M, int N, int K, int y_transposed, int tm, int tn, int tk,
                 int stages, int out_f32, int causal, const int32_t* tile_i, const int32_t* tile_j, int n_tiles,
-                const int32_t* fill_i, const int32_t* fill_j, int n_fills, const float* row_scale, tjx_stream_t stream);
+                const int32_t* fill_i, const int32_t* fill_j, int n_fills, const float* row_scale, int activation,
+                tjx_stream_t stream);
 
 constexpr int RMS_WARPS = 8;  // rows per CTA: a warp per row
 
@@ -85,7 +86,7 @@ int tjx_rmsnorm_gemm_bf16(const void* x, const void* gamma, const void* w, void*
   rmsnorm_prepare_kernel<<<grid, RMS_WARPS * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(gamma), xg, scale, M, D, eps);
   TJX_CUDA(cudaGetLastError());
-  return gemm_launch(xg, w, out, M, N, D, 0, tm, tn, tk, 0, out_f32, 0, nullptr, nullptr, 0, nullptr, nullptr, 0, scale,
+  return gemm_launch(xg, w, out, M, N, D, 0, tm, tn, tk, 0, out_f32, 0, nullptr, nullptr, 0, nullptr, nullptr, 0, scale, 0,
                      stream);
 }
 

@@ -243,6 +243,17 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, block_q:
     if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
         raise ValueError("q, k, v must be bfloat16")
     bq, bk = min(block_q, S), min(block_kv, S)
+    step_tile, step_code = _attention_tables(B, H, S, bq, bk, device)
+    if out is None:
+        out = torch.empty_like(q)
+    with torch.cuda.device(device):
+        check(library().tjx_causal_attention_bf16(_ptr(q), _ptr(k), _ptr(v), _ptr(out), B, H, S, D, bq, bk,
+                                                  _ptr(step_tile), _ptr(step_code), step_tile.numel(), S // bq, _stream()))
+    return out
+
+
+def _attention_tables(B: int, H: int, S: int, bq: int, bk: int, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """The causal step tables of one (batch, head): which key blocks each query tile visits, on the device."""
     sch = _schedule.causal_attention_schedule(B, H, S, bq, bk)
     if sch.step_tables:
         tile, code = sch.tables["step_tile"], sch.tables["step_code"]
@@ -251,13 +262,45 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, block_q:
         tile = np.repeat(np.arange(nq, dtype=np.int32), nk)
         block = np.tile(np.arange(nk, dtype=np.int32), nq)
         code = (block << _schedule.CODE_SHIFT) | ((block == 0) << 1) | (block == nk - 1)
-    step_tile = device_table(("attn", S, bq, bk, "tile"), tile, device)
-    step_code = device_table(("attn", S, bq, bk, "code"), code, device)
+    return (device_table(("attn", S, bq, bk, "tile"), tile, device), device_table(("attn", S, bq, bk, "code"), code, device))
+
+
+_block_workspaces: dict[tuple, torch.Tensor] = {}
+
+
+def attention_block(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gamma: torch.Tensor, w_up: torch.Tensor,
+                    w_down: torch.Tensor, block_q: int = 256, block_kv: int = 256, block_f: int = 1024,
+                    eps: float = 1e-6, out: torch.Tensor | None = None) -> torch.Tensor:
+    """The `attention_block` loop nest (examples/attention_block.py:49-85): causal attention over all heads, RMSNorm
+    of the heads side by side, then gelu(n @ w_up) @ w_down; q pre-scaled by the caller. `block_f` is accepted for
+    the nest's signature: it orders the reference's f32 additions, nothing else."""
+    tensors = (q, k, v, gamma, w_up, w_down)
+    if any(t.dtype != torch.bfloat16 for t in tensors):
+        raise ValueError("q, k, v, gamma, w_up and w_down must be bfloat16")
+    if q.ndim != 4 or k.shape != q.shape or v.shape != q.shape:
+        raise ValueError("q, k, v must have the same shape (B, H, S, Dh)")
+    B, H, S, Dh = q.shape
+    D = H * Dh
+    if gamma.shape != (1, D) or w_up.ndim != 2 or w_up.shape[0] != D or w_down.shape != (w_up.shape[1], D):
+        raise ValueError(f"gamma must be (1, {D}), w_up ({D}, F) and w_down (F, {D})")
+    F = w_up.shape[1]
+    if block_f <= 0:
+        raise ValueError("block_f must be positive")
+    device = _need_cuda(*tensors)
+    bq, bk = min(block_q, S), min(block_kv, S)
+    step_tile, step_code = _attention_tables(B, H, S, bq, bk, device)
     if out is None:
-        out = torch.empty_like(q)
+        out = torch.empty(B, S, D, dtype=torch.bfloat16, device=device)
     with torch.cuda.device(device):
-        check(library().tjx_causal_attention_bf16(_ptr(q), _ptr(k), _ptr(v), _ptr(out), B, H, S, D, bq, bk,
-                                                  _ptr(step_tile), _ptr(step_code), int(tile.size), S // bq, _stream()))
+        need = int(library().tjx_attention_block_workspace_bytes(B, H, S, Dh, F))
+        key = (device, need)
+        ws = _block_workspaces.get(key)
+        if ws is None:
+            _block_workspaces.clear()  # one shape at a time: the scratch holds every intermediate of the block
+            ws = _block_workspaces[key] = torch.empty(max(need, 256), dtype=torch.uint8, device=device)
+        check(library().tjx_attention_block_bf16(_ptr(q), _ptr(k), _ptr(v), _ptr(gamma), _ptr(w_up), _ptr(w_down), _ptr(out),
+                                                 B, H, S, Dh, F, bq, bk, float(eps), _ptr(step_tile), _ptr(step_code),
+                                                 step_tile.numel(), S // bq, _ptr(ws), ws.numel(), _stream()))
     return out
 
 
