@@ -199,19 +199,20 @@ int tjx_paged_gqa_decode_bf16(const void* q, const void* k_pages, const void* v_
                               tjx_stream_t stream);
 
 /* Bytes of scratch tjx_mla_decode_bf16 needs for these sizes (0 if block does not divide S). */
-size_t tjx_mla_decode_workspace_bytes(int B, int H, int S, int block);
+size_t tjx_mla_decode_workspace_bytes(int B, int T, int H, int S, int block);
 
-/* Absorbed MLA decode attention, `mla_decode` (examples/decode.py:226-250) for one new token per sequence: scores
- * q_c . c_kv + q_r . k_rope against a contiguous latent cache, softmax over the positions before lengths[b], output
- * = each head's softmax-weighted latents. Builds the step tables on the device from `lengths` (a step = one block
- * of `block` positions; blocks with block_index * block >= lengths[b] are skipped) and walks only those.
- *   q_c [B, 1, H, 512], q_r [B, 1, H, 128] bf16 (pre-scaled); c_kv [B, S, 512], k_rope [B, S, 128] bf16
- *   lengths int32[B] (0 = empty: output 0); out [B, 1, H, 512] bf16
+/* Absorbed MLA decode attention, `mla_decode` (examples/decode.py:226-250) for T new tokens per sequence: scores
+ * q_c . c_kv + q_r . k_rope against a contiguous latent cache, softmax over the positions new token t sees (those up
+ * to lengths[b] - T + t, `visible`, examples/decode.py:145-152), output = each head's softmax-weighted latents.
+ * Builds the step tables on the device from `lengths` (a step = one block of `block` positions; blocks with
+ * block_index * block >= lengths[b] are skipped) and walks only those.
+ *   q_c [B, T, H, 512], q_r [B, T, H, 128] bf16 (pre-scaled); c_kv [B, S, 512], k_rope [B, S, 128] bf16
+ *   lengths int32[B], the new tokens included (0 = empty: output 0); out [B, T, H, 512] bf16
  *   step_tile, step_code int32[B * S / block], step_count int32[1], tile_first int32[B + 1]: OUT, the tables built
  *   workspace: at least tjx_mla_decode_workspace_bytes(...) bytes, 256-byte aligned
  * Constraints: C == 512, R == 128, H % 16 == 0, block % 16 == 0, S % block == 0. */
 int tjx_mla_decode_bf16(const void* q_c, const void* q_r, const void* c_kv, const void* k_rope,
-                        const int32_t* lengths, void* out, int B, int H, int S, int C, int R, int block,
+                        const int32_t* lengths, void* out, int B, int T, int H, int S, int C, int R, int block,
                         int32_t* step_tile, int32_t* step_code, int32_t* step_count, int32_t* tile_first,
                         void* workspace, size_t workspace_bytes, tjx_stream_t stream);
 

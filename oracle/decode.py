@@ -147,35 +147,37 @@ def paged_gqa_decode_f64(q, k_pages, v_pages, block_tables, lengths) -> np.ndarr
 
 
 def mla_decode_ref(q_c, q_r, c_kv, k_rope, lengths, block_kv: int = 512) -> np.ndarray:
-    """examples/decode.py:226-250 with T = 1: scores `qc @ ct.T + qr @ k_rope.T` in f32 from the cache dtype's
-    operands (:246), blocks of min(block_kv, S) positions skipped when their first position is >= lengths[b]
-    (:243-244), `visible` and `online_softmax` against the latents themselves (:247-248), `finish` (:249)."""
+    """examples/decode.py:226-250: a sequence's rows are its (new token, head) pairs, token-major (`query_rows`,
+    :104-107); scores `qc @ ct.T + qr @ k_rope.T` in f32 from the cache dtype's operands (:246), blocks of
+    min(block_kv, S) positions skipped when their first position is >= lengths[b] (:243-244), `visible` (new token t
+    sees the positions up to lengths[b] - T + t, :145-152) and `online_softmax` against the latents themselves
+    (:247-248), `finish` (:249)."""
     B, T, H, C = q_c.shape
-    assert T == 1
     S = c_kv.shape[1]
     bk = min(block_kv, S)
     dtype = q_c.dtype
     out = np.zeros((B, T, H, C), dtype)
+    token = (np.arange(T * H) // H)[:, None]
     for b in range(B):
         n = int(lengths[b])
-        qc = np.asarray(q_c[b, 0]).astype(np.float32)
-        qr = np.asarray(q_r[b, 0]).astype(np.float32)
-        row_max = np.full((H, 1), MASK_VALUE, np.float32)
-        row_sum = np.zeros((H, 1), np.float32)
-        acc = np.zeros((H, C), np.float32)
+        qc = np.asarray(q_c[b]).reshape(T * H, C).astype(np.float32)
+        qr = np.asarray(q_r[b]).reshape(T * H, -1).astype(np.float32)
+        row_max = np.full((T * H, 1), MASK_VALUE, np.float32)
+        row_sum = np.zeros((T * H, 1), np.float32)
+        acc = np.zeros((T * H, C), np.float32)
         for j in range(0, S, bk):
             if j >= n:
                 continue
             ct = np.asarray(c_kv[b, j : j + bk]).astype(np.float32)
             s = qc @ ct.T + qr @ np.asarray(k_rope[b, j : j + bk]).astype(np.float32).T
-            s = np.where(((j + np.arange(bk)) < n)[None, :], s, MASK_VALUE)
+            s = np.where((j + np.arange(bk))[None, :] <= n - T + token, s, MASK_VALUE)
             max_new = np.maximum(row_max, s.max(axis=1, keepdims=True))
             pr = np.exp(s - max_new)
             alpha = np.exp(row_max - max_new)
             row_sum = alpha * row_sum + pr.sum(axis=1, keepdims=True, dtype=np.float32)
             acc = alpha * acc + pr.astype(dtype).astype(np.float32) @ ct
             row_max = max_new
-        out[b, 0] = (acc * (np.float32(1.0) / np.maximum(row_sum, np.float32(1e-30)))).astype(dtype)
+        out[b] = (acc * (np.float32(1.0) / np.maximum(row_sum, np.float32(1e-30)))).astype(dtype).reshape(T, H, C)
     return out
 
 
@@ -186,12 +188,14 @@ def mla_decode_f64(q_c, q_r, c_kv, k_rope, lengths) -> np.ndarray:
     out = np.zeros((B, T, H, C))
     for b in range(B):
         n = int(lengths[b])
-        if n == 0:
-            continue
-        c = np.asarray(c_kv[b, :n]).astype(np.float64)
-        s = np.asarray(q_c[b, 0]).astype(np.float64) @ c.T
-        s += np.asarray(q_r[b, 0]).astype(np.float64) @ np.asarray(k_rope[b, :n]).astype(np.float64).T
-        p = np.exp(s - s.max(axis=1, keepdims=True))
-        p /= p.sum(axis=1, keepdims=True)
-        out[b, 0] = p @ c
+        for t in range(T):
+            seen = n - T + t + 1  # new token t sees the positions before this one
+            if seen <= 0:
+                continue
+            c = np.asarray(c_kv[b, :seen]).astype(np.float64)
+            s = np.asarray(q_c[b, t]).astype(np.float64) @ c.T
+            s += np.asarray(q_r[b, t]).astype(np.float64) @ np.asarray(k_rope[b, :seen]).astype(np.float64).T
+            p = np.exp(s - s.max(axis=1, keepdims=True))
+            p /= p.sum(axis=1, keepdims=True)
+            out[b, t] = p @ c
     return out

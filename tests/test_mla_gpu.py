@@ -13,9 +13,9 @@ from tilejax_b200._lib import NativeError
 pytestmark = pytest.mark.gpu
 
 
-def mla_inputs(B, H, S, seed=0):
-    q_c = rand_bf16((B, 1, H, 512), seed, 192**-0.5 * 0.1)
-    q_r, k_rope = rand_bf16((B, 1, H, 128), seed + 1, 192**-0.5), rand_bf16((B, S, 128), seed + 3)
+def mla_inputs(B, H, S, seed=0, T=1):
+    q_c = rand_bf16((B, T, H, 512), seed, 192**-0.5 * 0.1)
+    q_r, k_rope = rand_bf16((B, T, H, 128), seed + 1, 192**-0.5), rand_bf16((B, S, 128), seed + 3)
     q_r[..., 64:] = 0
     k_rope[..., 64:] = 0
     return q_c, q_r, rand_bf16((B, S, 512), seed + 2), k_rope
@@ -44,6 +44,22 @@ def test_matches_the_oracle_on_ragged_lengths(heads, block):
     assert np.abs(f64(got) - f64(want)).max() <= 2e-2
     assert np.abs(f64(got) - oracle.mla_decode_f64(q_c, q_r, c_kv, k_rope, lengths)).max() <= 2e-2
     assert not f64(got[0]).any()
+
+
+@pytest.mark.parametrize(("tokens", "heads", "block"), [(2, 16, 128), (4, 32, 64), (3, 16, 512)])
+def test_several_new_tokens_each_see_the_positions_up_to_their_own(tokens, heads, block):
+    # tests/test_decode.py:163-220 runs the decode kernels with T new tokens; `visible` (examples/decode.py:145-152):
+    # token t of T sits at lengths[b] - T + t. Lengths (the new tokens included, so never below T): exactly T, one
+    # more, a partial block, the whole cache.
+    q_c, q_r, c_kv, k_rope = mla_inputs(4, heads, 512, seed=11, T=tokens)
+    lengths = np.array([tokens, tokens + 1, 300, 512], np.int32)
+    got = run(q_c, q_r, c_kv, k_rope, lengths, block)
+    want = oracle.mla_decode_ref(q_c, q_r, c_kv, k_rope, lengths, block)
+    assert np.abs(f64(got) - f64(want)).max() <= 2e-2
+    assert np.abs(f64(got) - oracle.mla_decode_f64(q_c, q_r, c_kv, k_rope, lengths)).max() <= 2e-2
+    # The last new token sees everything the single-token call sees.
+    single = run(q_c[:, -1:].copy(), q_r[:, -1:].copy(), c_kv, k_rope, lengths, block)
+    assert np.abs(f64(got[:, -1:]) - f64(single)).max() <= 2e-2
 
 
 def test_block_size_is_only_a_schedule():

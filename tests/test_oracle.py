@@ -205,6 +205,26 @@ def test_mla_decode_oracle_against_float64():
         assert not f64(got[0]).any()
 
 
+def test_mla_decode_oracle_with_several_new_tokens():
+    # `visible` (examples/decode.py:145-152): new token t of T sees the positions up to lengths[b] - T + t.
+    B, T, H, S = 3, 2, 16, 256
+    q_c, q_r = rand_bf16((B, T, H, 512), 20, 192**-0.5 * 0.1), rand_bf16((B, T, H, 128), 21, 192**-0.5)
+    c_kv, k_rope = rand_bf16((B, S, 512), 22), rand_bf16((B, S, 128), 23)
+    lengths = np.array([2, 130, 256], np.int32)
+    want = oracle.mla_decode_f64(q_c, q_r, c_kv, k_rope, lengths)
+    for block in (128, 256):
+        got = oracle.mla_decode_ref(q_c, q_r, c_kv, k_rope, lengths, block)
+        assert np.abs(f64(got) - want).max() <= 2e-2
+    # Token 0 of a 2-token step is the single-token step one position earlier.
+    one = oracle.mla_decode_ref(q_c[:, :1], q_r[:, :1], c_kv, k_rope, lengths - 1, 128)
+    two = oracle.mla_decode_ref(q_c, q_r, c_kv, k_rope, lengths, 128)
+    np.testing.assert_array_equal(f64(two[:, :1]), f64(one))
+    # And this package's nest means the same.
+    from tilejax_b200.autokernel import kernels as K
+    np.testing.assert_array_equal(f64(K.mla_decode.reference(q_c, q_r, c_kv, k_rope, lengths, K.DecodeTiles(block_kv=128))),
+                                  f64(two))
+
+
 def test_compare_rule():
     # src/autokernel/api.py:320-364 and tests/test_api.py:87-108: NaN equals NaN; 16-bit tolerance scales with
     # the largest value; integers are exact.

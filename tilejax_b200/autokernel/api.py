@@ -341,9 +341,9 @@ def _check_kernel_rules(plan: Plan) -> None:
         if any(np.dtype(s.dtype) != bf16 for s in plan.specs[:3]):
             raise nest.error("the attention kernel takes bfloat16 q, k, v")
     elif p.get("mla"):
-        if p["C"] != 512 or p["R"] != 128 or p["H"] % 16 or p["page"] % 16 or p["T"] != 1:
-            raise nest.error("the MLA decode kernel takes one new token, 512 latent and 128 RoPE columns, heads in "
-                             "multiples of 16 and blocks of a multiple of 16 positions")
+        if p["C"] != 512 or p["R"] != 128 or p["H"] % 16 or p["page"] % 16:
+            raise nest.error("the MLA decode kernel takes 512 latent and 128 RoPE columns, heads in multiples of 16 and "
+                             "blocks of a multiple of 16 positions")
     else:
         if p["D"] != 128 or p["page"] % 16 or p["H"] % p["Hkv"] or p["H"] // p["Hkv"] not in (1, 2, 4, 8):
             raise nest.error("the decode kernel takes head_dim 128, pages of a multiple of 16 positions and 1, 2, 4 "
@@ -473,7 +473,7 @@ def _lower(plan: Plan, config: Config) -> tuple[str, Callable[..., Any]]:
         text = header + (
             f"kernel      tjx_mla_decode_bf16 (device step tables, CTA-wide TMA ring, warp-level MMA over 16 heads, "
             f"partials merged by the last CTA to arrive)\n"
-            f"problem     {p['B']} sequences, {p['H']} heads, {p['C']} latent + {p['R']} RoPE columns, blocks of "
+            f"problem     {p['B']} sequences, {p['T']} new token(s), {p['H']} heads, {p['C']} latent + {p['R']} RoPE columns, blocks of "
             f"{p['page']} of {p['S']} cache positions\n"
             f"steps       at most {sch.steps}: step_tile / step_code / step_count are built on the device from lengths "
             f"before the kernel\n")

@@ -277,32 +277,38 @@ def mla_softmax_step(s, ct, ok, row_max, row_sum, acc):
     return max_new, row_sum, acc
 
 
-def before_the_end(block, first, length):
-    """Which positions of a block starting at `first` are before the sequence's end: (1, block)."""
-    return first + jax.lax.broadcasted_iota(jnp.int32, (1, block), 1) < length
+def rows_see(new_tokens, heads, block, first, length):
+    """Which (query row, position) pairs of a block starting at `first` attend: (T * H, block). Row t * H + h is new
+    token t, at position length - T + t, and sees the positions up to its own; for one new token that is
+    `cols < length`."""
+    rows = new_tokens * heads
+    cols = first + jax.lax.broadcasted_iota(jnp.int32, (rows, block), 1)
+    token = jax.lax.broadcasted_iota(jnp.int32, (rows, block), 0) // heads
+    return cols <= length - new_tokens + token
 
 
 @autokernel.kernel
 def mla_decode(q_c, q_r, c_kv, k_rope, lengths, tiles=DecodeTiles()):
-    """Absorbed MLA decode attention: q_c (B, 1, H, C), q_r (B, 1, H, 128), the latent cache (B, S_max, C) and the
-    RoPE key cache (B, S_max, 128); out (B, 1, H, C), each head's softmax-weighted latents."""
+    """Absorbed MLA decode attention: q_c (B, T, H, C), q_r (B, T, H, 128), the latent cache (B, S_max, C) and the
+    RoPE key cache (B, S_max, 128); out (B, T, H, C), each head's softmax-weighted latents. A sequence's rows are
+    its (new token, head) pairs, token-major."""
     B, T, H, C = q_c.shape
     S = c_kv.shape[1]
     bk, dtype = min(tiles.block_kv, S), q_c.dtype
     out = jnp.zeros((B, T, H, C), dtype)
     for b in range(B):
-        qc = q_c[b, 0, :, :]
-        qr = q_r[b, 0, :, :]
-        row_max = jnp.full((H, 1), MASK_VALUE, jnp.float32)
-        row_sum = jnp.zeros((H, 1), jnp.float32)
-        acc = jnp.zeros((H, C), jnp.float32)
+        qc = q_c[b, :, :, :].reshape(T * H, C)
+        qr = q_r[b, :, :, :].reshape(T * H, 128)
+        row_max = jnp.full((T * H, 1), MASK_VALUE, jnp.float32)
+        row_sum = jnp.zeros((T * H, 1), jnp.float32)
+        acc = jnp.zeros((T * H, C), jnp.float32)
         for j in range(0, S, bk):
             if j >= lengths[b]:  # past the sequence's end: decided on the device, before the kernel runs
                 continue
             ct = c_kv[b, j : j + bk, :]
             s = jnp.dot(qc, ct.T, preferred_element_type=jnp.float32)
             s = s + jnp.dot(qr, k_rope[b, j : j + bk, :].T, preferred_element_type=jnp.float32)
-            ok = before_the_end(bk, j, lengths[b])
+            ok = rows_see(T, H, bk, j, lengths[b])
             row_max, row_sum, acc = mla_softmax_step(s, ct, ok, row_max, row_sum, acc)
         res = acc * (1.0 / jnp.maximum(row_sum, 1e-30))
         out = out.at[b, :, :, :].set(res.reshape(T, H, C).astype(dtype))

@@ -23,7 +23,7 @@ RECOGNISED: dict[str, dict[str, str]] = {
     },
     "mla": {
         "8040e261b18bb83fef376fc89112926911a5d9cb73e4c2b39e44d2ae6d5aaa26": "examples/decode.py mla_decode",
-        "94a8eb751fcb24fac52945adf4e075a5b2716a89b73da9974dec6934fbd4411d": "tilejax_b200/autokernel/kernels.py mla_decode",
+        "63bc9dae7ce3b319b7958f67d95b958eb7131acaa7f7f993789d798a913dcbd5": "tilejax_b200/autokernel/kernels.py mla_decode",
     },
     "rmsnorm": {
         "ebbdf02fc35cd281f7cba2fdd95589e0d8717f3476647b2313b8393a40b81e26": "examples/rmsnorm_matmul.py rmsnorm_matmul",

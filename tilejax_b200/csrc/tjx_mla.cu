@@ -1,5 +1,6 @@
-// Absorbed MLA decode attention on sm_100a, `mla_decode` (examples/decode.py:226-250) for one new token per
-// sequence: every query head scores the same latent cache (512 latents + 128 RoPE columns per position) and the
+// Absorbed MLA decode attention on sm_100a, `mla_decode` (examples/decode.py:226-250): the rows of a sequence are its
+// (new token, head) pairs, token-major, and new token t of T sees the cache positions up to lengths[b] - T + t
+// (`visible`, examples/decode.py:145-152). Every query head scores the same latent cache (512 latents + 128 RoPE columns per position) and the
 // output of a head is its softmax-weighted latents, so a position's 1280 bytes are read once for all the heads of
 // a head group.
 //
@@ -59,7 +60,9 @@ struct MlaParams {
   float* ws_acc;                 // [B, blocks, H, 512]
   int* arrivals;                 // [B, H / 16]
   __nv_bfloat16* out;            // [B, 1, H, 512]
-  int B, H, S, block, blocks;    // cache positions per sequence, positions per step, steps per sequence
+  int B, H, S, block, blocks;    // H: rows per sequence (new tokens x heads); cache positions per sequence,
+                                 // positions per step, steps per sequence
+  int heads, T;                  // heads per token, new tokens per sequence
   int* status;
 };
 
@@ -149,6 +152,9 @@ __global__ void __launch_bounds__(MLA_WARPS * 32, 3)
   const int len = p.lengths[b];
   const int j0 = (code >> 3) * p.block;  // first cache position of the step
   const int n_micro = (code & 4) ? 0 : (min(p.block, len - j0) + MLA_SUB - 1) / MLA_SUB;
+  // The 16 rows of a group belong to one new token (heads per token is a multiple of 16): it sees the positions
+  // before lengths[b] - T + token + 1.
+  const int visible_end = len - p.T + h0 / p.heads + 1;
   const int first = p.tile_first[b], pieces = p.tile_first[b + 1] - first;
   const int slot = step - first;
 
@@ -262,7 +268,7 @@ __global__ void __launch_bounds__(MLA_WARPS * 32, 3)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int tok = (e >> 1) * 8 + 2 * t + (e & 1);
-        s4[e] = pos0 + tok < len ? s4[e] * MLA_LOG2E : MLA_MASK * MLA_LOG2E;
+        s4[e] = pos0 + tok < visible_end ? s4[e] * MLA_LOG2E : MLA_MASK * MLA_LOG2E;
       }
       float mx = fmaxf(fmaxf(s4[0], s4[1]), fmaxf(s4[2], s4[3]));
       mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
@@ -338,28 +344,31 @@ static size_t mla_align256(size_t n) { return (n + 255) & ~static_cast<size_t>(2
 
 extern "C" {
 
-size_t tjx_mla_decode_workspace_bytes(int B, int H, int S, int block) {
-  if (B <= 0 || H <= 0 || S <= 0 || block <= 0 || S % block != 0) return 0;
+size_t tjx_mla_decode_workspace_bytes(int B, int T, int H, int S, int block) {
+  if (B <= 0 || T <= 0 || H <= 0 || S <= 0 || block <= 0 || S % block != 0) return 0;
+  H *= T;  // rows per sequence
   const size_t rows = static_cast<size_t>(B) * (S / block) * H;
   return 2 * tjx::mla_align256(rows * sizeof(float)) + tjx::mla_align256(rows * tjx::MLA_C * sizeof(float)) +
          tjx::mla_align256(static_cast<size_t>(B) * H * sizeof(int));
 }
 
 int tjx_mla_decode_bf16(const void* q_c, const void* q_r, const void* c_kv, const void* k_rope,
-                        const int32_t* lengths, void* out, int B, int H, int S, int C, int R, int block,
+                        const int32_t* lengths, void* out, int B, int T, int H, int S, int C, int R, int block,
                         int32_t* step_tile, int32_t* step_code, int32_t* step_count, int32_t* tile_first,
                         void* workspace, size_t workspace_bytes, tjx_stream_t stream) {
   using namespace tjx;
   if (int rc = check_device()) return rc;
   if (!q_c || !q_r || !c_kv || !k_rope || !lengths || !out) return fail(TJX_E_ARG, "an input or output pointer is null");
   if (!step_tile || !step_code || !step_count || !tile_first) return fail(TJX_E_ARG, "a step table pointer is null");
-  if (B <= 0 || H <= 0 || S <= 0 || block <= 0) return fail(TJX_E_ARG, "sizes must be positive");
+  if (B <= 0 || T <= 0 || H <= 0 || S <= 0 || block <= 0) return fail(TJX_E_ARG, "sizes must be positive");
   if (C != MLA_C || R != MLA_R) return fail(TJX_E_ARG, "the latent cache is 512 columns wide and the RoPE cache 128");
   if (H % MLA_HEADS != 0) return fail(TJX_E_ARG, "the number of heads must be a multiple of 16");
   if (block % MLA_SUB != 0 || S % block != 0)
     return fail(TJX_E_ARG, "the block must be a multiple of 16 positions that divides the cache length");
   if (static_cast<long long>(B) * S >= (1ll << 31)) return fail(TJX_E_LIMIT, "B * S must fit in int32");
-  const size_t need = tjx_mla_decode_workspace_bytes(B, H, S, block);
+  const size_t need = tjx_mla_decode_workspace_bytes(B, T, H, S, block);
+  const int heads = H;
+  H *= T;  // rows per sequence from here on
   if (workspace == nullptr || workspace_bytes < need)
     return fail(TJX_E_ARG, "workspace is null or smaller than tjx_mla_decode_workspace_bytes");
   if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(TJX_E_ARG, "workspace must be 256-byte aligned");
@@ -375,6 +384,7 @@ int tjx_mla_decode_bf16(const void* q_c, const void* q_r, const void* c_kv, cons
   p.lengths = lengths;
   p.step_tile = step_tile, p.step_code = step_code, p.step_count = step_count, p.tile_first = tile_first;
   p.B = B, p.H = H, p.S = S, p.block = block, p.blocks = S / block;
+  p.heads = heads, p.T = T;
   const size_t rows = static_cast<size_t>(B) * p.blocks * H;
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   p.ws_m = reinterpret_cast<float*>(ws);

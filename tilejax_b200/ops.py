@@ -387,14 +387,14 @@ def gqa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, le
 class MlaBuffers:
     """The step tables and scratch one `mla_decode` call fills; reusable across calls of the same sizes."""
 
-    def __init__(self, B: int, H: int, S: int, block: int, device: torch.device):
+    def __init__(self, B: int, H: int, S: int, block: int, device: torch.device, T: int = 1):
         n = B * (S // block)
-        self.key = (B, H, S, block, str(device))
+        self.key = (B, T, H, S, block, str(device))
         self.step_tile = torch.empty(n, dtype=torch.int32, device=device)
         self.step_code = torch.empty(n, dtype=torch.int32, device=device)
         self.step_count = torch.empty(1, dtype=torch.int32, device=device)
         self.tile_first = torch.empty(B + 1, dtype=torch.int32, device=device)
-        self.workspace_bytes = int(library().tjx_mla_decode_workspace_bytes(B, H, S, block))
+        self.workspace_bytes = int(library().tjx_mla_decode_workspace_bytes(B, T, H, S, block))
         self.workspace = torch.empty(self.workspace_bytes + 256, dtype=torch.uint8, device=device)
 
     def workspace_ptr(self) -> int:
@@ -403,16 +403,14 @@ class MlaBuffers:
 
 def mla_decode(q_c: torch.Tensor, q_r: torch.Tensor, c_kv: torch.Tensor, k_rope: torch.Tensor, lengths: torch.Tensor,
                block_kv: int = 512, out: torch.Tensor | None = None, buffers: MlaBuffers | None = None) -> torch.Tensor:
-    """The `mla_decode` loop nest (examples/decode.py:226-250) for one new token per sequence: q_c (B, 1, H, 512),
-    q_r (B, 1, H, 128), the latent cache (B, S, 512) and the RoPE key cache (B, S, 128); out (B, 1, H, 512), each
-    head's softmax-weighted latents."""
+    """The `mla_decode` loop nest (examples/decode.py:226-250) for T new tokens per sequence: q_c (B, T, H, 512),
+    q_r (B, T, H, 128), the latent cache (B, S, 512) and the RoPE key cache (B, S, 128); out (B, T, H, 512), each
+    head's softmax-weighted latents. New token t sees the positions up to lengths[b] - T + t."""
     device = _need_cuda(q_c, q_r, c_kv, k_rope, lengths)
     B, T, H, C = q_c.shape
     S, R = c_kv.shape[1], k_rope.shape[2]
-    if T != 1:
-        raise ValueError("one new token per sequence (T = 1)")
     if q_r.shape != (B, T, H, R) or c_kv.shape != (B, S, C) or k_rope.shape != (B, S, R) or lengths.shape != (B,):
-        raise ValueError("q_c (B, 1, H, C), q_r (B, 1, H, R), c_kv (B, S, C), k_rope (B, S, R), lengths (B,)")
+        raise ValueError("q_c (B, T, H, C), q_r (B, T, H, R), c_kv (B, S, C), k_rope (B, S, R), lengths (B,)")
     if lengths.dtype != torch.int32 or any(t.dtype != torch.bfloat16 for t in (q_c, q_r, c_kv, k_rope)):
         raise ValueError("lengths is int32, the other operands bfloat16")
     if not all(t.is_contiguous() for t in (q_c, q_r, c_kv, k_rope)):
@@ -420,13 +418,13 @@ def mla_decode(q_c: torch.Tensor, q_r: torch.Tensor, c_kv: torch.Tensor, k_rope:
     block = min(block_kv, S)
     if S % block:
         raise ValueError("the block must divide the cache length")
-    if buffers is None or buffers.key != (B, H, S, block, str(device)):
-        buffers = MlaBuffers(B, H, S, block, device)
+    if buffers is None or buffers.key != (B, T, H, S, block, str(device)):
+        buffers = MlaBuffers(B, H, S, block, device, T)
     if out is None:
         out = torch.empty_like(q_c)
     with torch.cuda.device(device):
         check(library().tjx_mla_decode_bf16(
-            _ptr(q_c), _ptr(q_r), _ptr(c_kv), _ptr(k_rope), _ptr(lengths), _ptr(out), B, H, S, C, R, block,
+            _ptr(q_c), _ptr(q_r), _ptr(c_kv), _ptr(k_rope), _ptr(lengths), _ptr(out), B, T, H, S, C, R, block,
             _ptr(buffers.step_tile), _ptr(buffers.step_code), _ptr(buffers.step_count), _ptr(buffers.tile_first),
             ctypes.c_void_p(buffers.workspace_ptr()), buffers.workspace_bytes, _stream()))
     mla_decode.last_buffers = buffers
