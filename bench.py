@@ -153,7 +153,8 @@ def device_randn_bf16(shape, seed, device, scale=1.0):
 
 def time_device(fn, iters: int, warmup: int, flush=None) -> float:
     """Median device time of fn() in ms over `iters` runs, each bracketed by CUDA events on the current stream;
-    `flush()` (an L2 flush) runs untimed before each. (The median, as the reference's benchmarks take it,
+    `flush()` (an L2 flush) runs untimed before each, then a spin kernel behind which the host queues the timed
+    launches. (The median, as the reference's benchmarks take it,
     benchmarks/timing.py:12-22: under the board's power cap single launches scatter by several per cent.)"""
     import torch
 
@@ -164,6 +165,10 @@ def time_device(fn, iters: int, warmup: int, flush=None) -> float:
     for _ in range(iters):
         if flush is not None:
             flush()
+        # Half a millisecond of spinning on the device ahead of the first event: the host queues the events and fn's
+        # launches behind it, so the interval holds device time only and not the host's time to issue a launch
+        # (tens of microseconds through Python, as long as the shortest kernels here run).
+        torch.cuda._sleep(1_000_000)
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         fn()

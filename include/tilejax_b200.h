@@ -198,6 +198,11 @@ int tjx_paged_gqa_decode_bf16(const void* q, const void* k_pages, const void* v_
                               int32_t* step_count, int32_t* tile_first, void* workspace, size_t workspace_bytes,
                               tjx_stream_t stream);
 
+/* Which kernel tjx_mla_decode_bf16 launches from now on: 1 (the default) the tcgen05 kernel, 64 rows per CTA with
+ * scores and output in TMEM; 0 the warp-level MMA kernel, 16 rows per CTA. An A/B switch for measurements: the two
+ * agree to rounding. No counterpart in the reference. */
+int tjx_mla_set_mode(int mode);
+
 /* Bytes of scratch tjx_mla_decode_bf16 needs for these sizes (0 if block does not divide S). */
 size_t tjx_mla_decode_workspace_bytes(int B, int T, int H, int S, int block);
 

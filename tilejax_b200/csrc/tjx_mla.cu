@@ -63,6 +63,7 @@ struct MlaParams {
   int B, H, S, block, blocks;    // H: rows per sequence (new tokens x heads); cache positions per sequence,
                                  // positions per step, steps per sequence
   int heads, T;                  // heads per token, new tokens per sequence
+  long long* profile;            // per-CTA counters (PROFILE_WORDS each) or null: the tcgen05 kernel fills them
   int* status;
 };
 
@@ -338,11 +339,358 @@ __global__ void __launch_bounds__(MLA_WARPS * 32, 3)
   }
 }
 
+// ------------------------------------------------------------------------------------------------ tcgen05 path
+//
+// The same step on the tensor cores' own path: a CTA takes one step (a block of cache positions of one sequence)
+// and 64 rows ((new token, head) pairs) — the M of a 64-row tcgen05.mma — so a position's 1280 bytes are staged
+// once for 64 heads instead of once per 16, and the scores and the output accumulate in TMEM.
+//
+//   warp 0      producer: the 64 rows' queries once (ten 128-byte-swizzled boxes [64 rows x 64 columns], 80 KB), then
+//               the block 32 positions at a time through a ring of three 40 KB slots (ten boxes [32 x 64])
+//   warp 1      MMA issuer (whole warp, one elected lane): S = Q K^T over the 640 columns (40 MMAs of 64 x 32 x 16 into
+//               one of two score buffers), then O += P V as two halves of 256 latent columns, P read from TMEM
+//   warps 2-5   softmax: a 64-row accumulator sits in TMEM lanes 0-15 of each 32-lane quarter (row 16 q + i in
+//               lane 32 q + i); a second 64-row tile may use lanes 16-31 of the same columns. S uses the lower
+//               lanes; O's two halves are the two tiles of columns 0-255. Lane i < 16 of warp q owns row 16 q + i:
+//               its scores and O's latent columns 0-255; lane i + 16 mirrors it (same scores, same P, written to its
+//               own TMEM lane so that the upper tile's MMA finds P beside its accumulator) and owns columns 256-511.
+//
+// TMEM: columns 0-255 O (both tiles), 256-287 and 288-319 the two score buffers; P (bf16, two per column)
+// overlays the first 16 columns of its score buffer. Partials and the merge are those of the kernel above.
+constexpr int MT_ROWS = 64;
+constexpr int MT_POS = 32;                                   // positions per micro-step
+constexpr int MT_STAGES = 3;
+constexpr int MT_KV_BOX = MT_POS * 128;                      // 32 positions x 64 columns
+constexpr int MT_STAGE_BYTES = MLA_BOXES * MT_KV_BOX;        // 40 KB
+constexpr int MT_Q_BOX = MT_ROWS * 128;                      // 64 rows x 64 columns
+constexpr int MT_Q_BYTES = MLA_BOXES * MT_Q_BOX;             // 80 KB
+constexpr int MT_KV_OFF = MT_Q_BYTES;
+constexpr int MT_BAR_OFF = MT_KV_OFF + MT_STAGES * MT_STAGE_BYTES;
+constexpr int MT_SMEM = MT_BAR_OFF + 256 + 1024;
+constexpr int MT_THREADS = 192;
+constexpr int MT_S_COL = 256;                                // first column of the score buffers
+constexpr float MT_RESCALE_THRESHOLD = 8.0f;
+
+__global__ void __launch_bounds__(MT_THREADS, 1)
+    mla_tc_kernel(const __grid_constant__ CUtensorMap map_qc, const __grid_constant__ CUtensorMap map_qr,
+                  const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_r,
+                  const MlaParams p) {
+  extern __shared__ uint8_t mt_smem_raw[];
+  __shared__ int last_sh;
+  const uint32_t base = (smem_u32(mt_smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = mt_smem_raw + (base - smem_u32(mt_smem_raw));
+  const uint32_t bar_base = base + MT_BAR_OFF;
+  // barriers: q_full, kv_full[3], kv_empty[3], s_full[2], p_ready[2], o_done
+  const uint32_t q_full = bar_base;
+  auto kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
+  auto kv_empty = [&](int s) { return bar_base + 8u * (4 + s); };
+  auto s_full = [&](int t) { return bar_base + 8u * (7 + t); };
+  auto p_ready = [&](int t) { return bar_base + 8u * (9 + t); };
+  const uint32_t o_done = bar_base + 8u * 11;
+  constexpr int N_BARS = 12;
+  volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(base_ptr + MT_BAR_OFF + 8 * N_BARS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + MT_BAR_OFF + 8 * N_BARS + 8);
+
+  const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
+  long long* prof = p.profile == nullptr
+                        ? nullptr
+                        : p.profile + (static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * PROFILE_WORDS;
+  if (prof != nullptr && threadIdx.x == 0) prof[0] = clock64(), prof[9] = globaltimer_ns();
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < N_BARS; ++i) mbar_init(bar_base + 8u * i, (i == 9 || i == 10) ? 4 : 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&map_qc);
+    tma_prefetch_desc(&map_qr);
+    tma_prefetch_desc(&map_c);
+    tma_prefetch_desc(&map_r);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_holder)), 512);
+    tmem_relinquish();
+  }
+  // Launched with programmatic stream serialisation behind the step-table kernel: nothing it writes is read
+  // before this returns.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (prof != nullptr && threadIdx.x == 0) prof[11] = globaltimer_ns();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = __shfl_sync(0xFFFFFFFFu, *tmem_holder, 0);
+
+  const int step = blockIdx.x;
+  const bool active = step < p.step_count[0];
+  const int b = active ? p.step_tile[step] : 0;
+  const int code = active ? p.step_code[step] : 4;
+  const int row0 = blockIdx.y * MT_ROWS;       // first of this CTA's rows among the sequence's p.H rows
+  const int len = p.lengths[b];
+  const int j0 = (code >> 3) * p.block;        // first cache position of the step
+  const int n_pos = (code & 4) ? 0 : min(p.block, len - j0);
+  const int n_micro = __shfl_sync(0xFFFFFFFFu, (n_pos + MT_POS - 1) / MT_POS, 0);
+  const int first = p.tile_first[b], pieces = p.tile_first[b + 1] - first;
+  const int slot = step - first;
+
+  if (!active) {
+    // (No step for this CTA: nothing to do but give the TMEM back.)
+  } else if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0 && n_micro > 0) {
+      const int q_row = b * p.H + row0;
+      mbar_expect_tx(q_full, MT_Q_BYTES);
+      for (int x = 0; x < MLA_C / 64; ++x) tma_load_2d(base + x * MT_Q_BOX, &map_qc, 64 * x, q_row, q_full);
+      for (int x = 0; x < MLA_R / 64; ++x) tma_load_2d(base + (MLA_C / 64 + x) * MT_Q_BOX, &map_qr, 64 * x, q_row, q_full);
+      const int token0 = b * p.S + j0;
+      for (int i = 0; i < n_micro; ++i) {
+        const int stage = i % MT_STAGES;
+        if (i >= MT_STAGES &&
+            !mbar_wait(kv_empty(stage), ((i / MT_STAGES) - 1) & 1, abort_flag, p.status, TJX_ERR_WAIT_EMPTY))
+          break;
+        const uint32_t dst = base + MT_KV_OFF + stage * MT_STAGE_BYTES;
+        const int row = token0 + i * MT_POS;
+        mbar_expect_tx(kv_full(stage), MT_STAGE_BYTES);
+        for (int x = 0; x < MLA_C / 64; ++x) tma_load_2d(dst + x * MT_KV_BOX, &map_c, 64 * x, row, kv_full(stage));
+        for (int x = 0; x < MLA_R / 64; ++x)
+          tma_load_2d(dst + (MLA_C / 64 + x) * MT_KV_BOX, &map_r, 64 * x, row, kv_full(stage));
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (whole warp; one lane issues)
+    const uint32_t idesc_qk = idesc_bf16_f32(MT_ROWS, MT_POS, 0, 0);  // Q and K both K-major
+    const uint32_t idesc_pv = idesc_bf16_f32(MT_ROWS, 256, 0, 1);     // P from TMEM, the latents MN-major
+    long long in_wait = 0, p_wait = 0, fill_wait = 0;
+    const long long t_first = prof != nullptr ? clock64() : 0;
+    auto wait = [&](uint32_t bar, uint32_t parity, int err, long long& waited) {
+      return __all_sync(0xFFFFFFFFu, mbar_wait_timed(bar, parity, abort_flag, p.status, err, waited, prof != nullptr)) != 0;
+    };
+    auto issue_qk = [&](int i) {
+      const int stage = i % MT_STAGES;
+      const uint32_t kv = base + MT_KV_OFF + stage * MT_STAGE_BYTES;
+      const uint32_t d = tmem_base + MT_S_COL + (i & 1) * MT_POS;
+#pragma unroll
+      for (int pair = 0; pair < MLA_BOXES / 2; ++pair) {  // two 64-column boxes = eight MMAs at a time
+        uint64_t qd[8], kd[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int box = 2 * pair + (k >> 2);
+          qd[k] = smem_desc_sw128(base + box * MT_Q_BOX, 16, 1024) + (((k & 3) * 32) >> 4);
+          kd[k] = smem_desc_sw128(kv + box * MT_KV_BOX, 16, 1024) + (((k & 3) * 32) >> 4);
+        }
+        mma_ss_x8(d, qd, kd, idesc_qk, pair != 0 ? 1u : 0u);
+      }
+      mma_commit_elected(s_full(i & 1));
+    };
+    bool ok = n_micro == 0 || wait(q_full, 0, TJX_ERR_WAIT_FULL, in_wait);
+    if (ok && n_micro > 0) {
+      ok = wait(kv_full(0), 0, TJX_ERR_WAIT_FULL, in_wait);
+      fill_wait = in_wait;
+      if (ok) {
+        tc_fence_after_sync();
+        issue_qk(0);
+      }
+    }
+    for (int i = 0; i < n_micro && ok; ++i) {
+      const int stage = i % MT_STAGES;
+      if (i + 1 < n_micro) {  // the next block's scores run while this one's softmax does
+        ok = wait(kv_full((i + 1) % MT_STAGES), ((i + 1) / MT_STAGES) & 1, TJX_ERR_WAIT_FULL, in_wait);
+        if (!ok) break;
+        tc_fence_after_sync();
+        issue_qk(i + 1);
+      }
+      ok = wait(p_ready(i & 1), (i >> 1) & 1, TJX_ERR_WAIT_OTHER, p_wait);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t kv = base + MT_KV_OFF + stage * MT_STAGE_BYTES;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {  // latent columns 256 half .. 256 half + 255: the tile at lanes 16 half
+        const uint32_t tile = static_cast<uint32_t>(16 * half) << 16;
+#pragma unroll
+        for (int kk = 0; kk < MT_POS / 16; ++kk) {
+          const uint64_t vd = smem_desc_sw128(kv + half * 4 * MT_KV_BOX + kk * (16 * 128), MT_KV_BOX, 1024);
+          const uint32_t pa = tmem_base + tile + MT_S_COL + (i & 1) * MT_POS + kk * 8;
+          if (elect_one()) mma_ts(tmem_base + tile, pa, vd, idesc_pv, (i != 0 || kk != 0) ? 1u : 0u);
+        }
+      }
+      mma_commit_elected(kv_empty(stage));
+      mma_commit_elected(o_done);
+    }
+    if (prof != nullptr && lane == 0) {
+      prof[1] = t_first, prof[2] = clock64(), prof[3] = in_wait, prof[4] = fill_wait, prof[5] = 0, prof[6] = n_micro;
+      prof[8] = p_wait;
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax, correction, flush (warps 2..5)
+    const int q = warp & 3;                      // the TMEM lane quarter this warp may touch
+    const int r = 16 * q + (lane & 15);          // row within the CTA's 64
+    const int half = lane >> 4;                  // which 256 latent columns of O this lane owns
+    const int row = row0 + r;                    // row within the sequence
+    const uint32_t quarter = static_cast<uint32_t>(32 * q) << 16;
+    const uint32_t o_tmem = tmem_base + quarter;  // this lane: lane 32 q + lane, columns 0..255
+    // New token `row / heads` sees the positions before lengths[b] - T + token + 1; the step ends at j0 + n_pos.
+    const int limit = min(len - p.T + row / p.heads + 1, j0 + n_pos);
+    float m_used = MLA_MASK * MLA_LOG2E, l = 0.f;
+    bool ok = true;
+    for (int i = 0; i < n_micro; ++i) {
+      const bool got = mbar_wait(s_full(i & 1), (i >> 1) & 1, abort_flag, p.status, TJX_ERR_WAIT_TMEM_FULL);
+      if (!__all_sync(0xFFFFFFFFu, got)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t s_tmem = tmem_base + quarter + MT_S_COL + (i & 1) * MT_POS;
+      uint32_t v[32];
+      tmem_ld32(s_tmem, v);
+      tmem_wait_ld();
+      const int pos0 = j0 + i * MT_POS;
+      float mx = MLA_MASK * MLA_LOG2E;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        // Lanes 16-31 take the scores of the lane 16 below: the same row.
+        const float sc = __shfl_sync(0xFFFFFFFFu, __uint_as_float(v[j]), lane & 15);
+        const float x = pos0 + j < limit ? sc * MLA_LOG2E : MLA_MASK * MLA_LOG2E;
+        v[j] = __float_as_uint(x);
+        mx = fmaxf(mx, x);
+      }
+      if (i == 0) {
+        m_used = mx;
+      } else if (__any_sync(0xFFFFFFFFu, mx > m_used + MT_RESCALE_THRESHOLD)) {
+        // Raise the running max and rescale what has been accumulated: O += P V of the previous block is complete.
+        const float m_new = fmaxf(m_used, mx);
+        const float alpha = ex2(m_used - m_new);
+        m_used = m_new;
+        l *= alpha;
+        const bool od = mbar_wait(o_done, (i - 1) & 1, abort_flag, p.status, TJX_ERR_WAIT_OTHER);
+        if (!__all_sync(0xFFFFFFFFu, od)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+          uint32_t o[32];
+          tmem_ld32(o_tmem + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+          tmem_st32(o_tmem + c * 32, o);
+        }
+        tmem_wait_st();
+      }
+      uint32_t pk[16];
+      float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        const float p0 = ex2(__uint_as_float(v[j]) - m_used), p1 = ex2(__uint_as_float(v[j + 1]) - m_used);
+        l0 += p0, l1 += p1;
+        pk[j >> 1] = pack_bf16(p0, p1);  // P is rounded before P V
+      }
+      l += l0 + l1;
+      tmem_st16(s_tmem, pk);
+      tmem_wait_st();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_ready(i & 1));
+      // Keep up with o_done: a parity wait is only right for a waiter at most one phase behind, and nothing else
+      // makes this warp see P V of block i - 1 complete (the scores of block i were issued before it).
+      if (i >= 1) {
+        const bool od = mbar_wait(o_done, (i - 1) & 1, abort_flag, p.status, TJX_ERR_WAIT_OTHER);
+        if (!__all_sync(0xFFFFFFFFu, od)) {
+          ok = false;
+          break;
+        }
+      }
+    }
+    if (n_micro > 0 && ok) {
+      const bool od = mbar_wait(o_done, (n_micro - 1) & 1, abort_flag, p.status, TJX_ERR_WAIT_OTHER);
+      ok = __all_sync(0xFFFFFFFFu, od) != 0;
+      tc_fence_after_sync();
+    }
+    // Flush this lane's 256 latent columns of its row: the output itself, or a partial for the merge.
+    if (ok && row < p.H) {
+      const int c0 = 256 * half;
+      const float inv = 1.0f / fmaxf(l, 1e-30f);
+      const size_t part = (static_cast<size_t>(b) * p.blocks + slot) * p.H + row;
+      if (pieces > 1 && half == 0) {  // the partials keep the max in natural-log units
+        p.ws_m[part] = m_used * (1.0f / MLA_LOG2E);
+        p.ws_l[part] = l;
+      }
+#pragma unroll 1
+      for (int c = 0; c < 8; ++c) {
+        uint32_t o[32];
+        if (n_micro > 0) {
+          tmem_ld32(o_tmem + c * 32, o);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] = 0u;
+        }
+        if (pieces == 1) {
+          uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(b) * p.H + row) * MLA_C + c0 + c * 32);
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            uint4 val;
+            val.x = pack_bf16(__uint_as_float(o[8 * x + 0]) * inv, __uint_as_float(o[8 * x + 1]) * inv);
+            val.y = pack_bf16(__uint_as_float(o[8 * x + 2]) * inv, __uint_as_float(o[8 * x + 3]) * inv);
+            val.z = pack_bf16(__uint_as_float(o[8 * x + 4]) * inv, __uint_as_float(o[8 * x + 5]) * inv);
+            val.w = pack_bf16(__uint_as_float(o[8 * x + 6]) * inv, __uint_as_float(o[8 * x + 7]) * inv);
+            dst[x] = val;
+          }
+        } else {
+          uint4* dst = reinterpret_cast<uint4*>(p.ws_acc + part * MLA_C + c0 + c * 32);
+#pragma unroll
+          for (int x = 0; x < 8; ++x) dst[x] = make_uint4(o[4 * x], o[4 * x + 1], o[4 * x + 2], o[4 * x + 3]);
+        }
+      }
+    }
+    tc_fence_before_sync();
+    if (pieces > 1) {
+      // Count this step on each of its 16-row groups; the CTA that counts last on a group finds every partial of
+      // (sequence, group) written and merges it. The four softmax warps meet on a named barrier, whatever happened
+      // before: a warp whose wait gave up raised the CTA's abort flag, which all of them read after the barrier.
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const bool healthy = *abort_flag == 0;
+      if (healthy && warp == 2 && lane == 0) {
+        int last = 0;
+        for (int gq = 0; gq < 4; ++gq)
+          if (row0 + 16 * gq < p.H)
+            last |= (atomicAdd(p.arrivals + b * (p.H / MLA_HEADS) + (row0 / MLA_HEADS) + gq, 1) == pieces - 1) << gq;
+        last_sh = last;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const int last = healthy ? last_sh : 0;
+      if (last) {
+        __threadfence();
+        for (int gq = 0; gq < 4; ++gq)
+          if ((last >> gq) & 1)
+            for (int rr = 0; rr < MLA_HEADS; rr += 4) mla_merge_rows(p, b, row0 + 16 * gq + rr, 128 * q, pieces, lane);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (prof != nullptr && threadIdx.x == 0) prof[7] = clock64(), prof[10] = globaltimer_ns();
+  if (warp == 1) {
+    if (*abort_flag) __nanosleep(100000);
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+int g_mla_mode = 1;  // 1: the tcgen05 kernel; 0: the warp-level MMA kernel (an A/B switch; values agree to rounding)
+
 static size_t mla_align256(size_t n) { return (n + 255) & ~static_cast<size_t>(255); }
 
 }  // namespace tjx
 
 extern "C" {
+
+int tjx_mla_set_mode(int mode) {
+  if (mode != 0 && mode != 1) return tjx::fail(TJX_E_ARG, "mode must be 0 (warp-level MMA) or 1 (tcgen05)");
+  tjx::g_mla_mode = mode;
+  return 0;
+}
 
 size_t tjx_mla_decode_workspace_bytes(int B, int T, int H, int S, int block) {
   if (B <= 0 || T <= 0 || H <= 0 || S <= 0 || block <= 0 || S % block != 0) return 0;
@@ -400,6 +748,39 @@ int tjx_mla_decode_bf16(const void* q_c, const void* q_r, const void* c_kv, cons
   if (int rc = launch_build_steps_lengths(lengths, B, nullptr, B, p.blocks, 0, block, step_tile, step_code, step_count,
                                           tile_first, p.arrivals, B * (H / MLA_HEADS), s))
     return rc;
+
+  if (g_mla_mode == 1) {
+    CUtensorMap mqc, mqr, mc, mr;
+    const uint32_t q_box[2] = {64, MT_ROWS}, kv_box[2] = {64, MT_POS};
+    const uint64_t q_rows = static_cast<uint64_t>(B) * H, kv_rows = static_cast<uint64_t>(B) * S;
+    const struct { CUtensorMap* map; const void* ptr; uint64_t cols, rows; const uint32_t* box; } maps[4] = {
+        {&mqc, q_c, MLA_C, q_rows, q_box}, {&mqr, q_r, MLA_R, q_rows, q_box},
+        {&mc, c_kv, MLA_C, kv_rows, kv_box}, {&mr, k_rope, MLA_R, kv_rows, kv_box}};
+    for (const auto& m : maps) {
+      const uint64_t dims[2] = {m.cols, m.rows};
+      const uint64_t strides[1] = {m.cols * 2};
+      if (int rc = make_tensor_map(m.map, m.ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 2, dims, strides, m.box,
+                                   CU_TENSOR_MAP_SWIZZLE_128B))
+        return rc;
+    }
+    static bool tc_configured[64] = {};
+    int dev = 0;
+    TJX_CUDA(cudaGetDevice(&dev));
+    if (!tc_configured[dev & 63]) {
+      TJX_CUDA(cudaFuncSetAttribute(mla_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MT_SMEM));
+      tc_configured[dev & 63] = true;
+    }
+    p.profile = profile_buffer(B * p.blocks * ((H + MT_ROWS - 1) / MT_ROWS));
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(B * p.blocks, (H + MT_ROWS - 1) / MT_ROWS), cfg.blockDim = dim3(MT_THREADS);
+    cfg.dynamicSmemBytes = MT_SMEM, cfg.stream = s;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr, cfg.numAttrs = 1;
+    TJX_CUDA(cudaLaunchKernelEx(&cfg, mla_tc_kernel, mqc, mqr, mc, mr, p));
+    return 0;
+  }
 
   CUtensorMap mc, mr;
   const uint32_t box[2] = {64, MLA_SUB};

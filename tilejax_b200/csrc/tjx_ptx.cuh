@@ -341,6 +341,30 @@ __device__ __forceinline__ void mma_ss_x8_commit(uint32_t d_tmem, const uint64_t
       : "memory");
 }
 
+// Eight MMAs of one accumulation with both operands in shared memory, without a commit (a longer accumulation
+// issues several of these and commits once).
+__device__ __forceinline__ void mma_ss_x8(uint32_t d_tmem, const uint64_t (&a)[8], const uint64_t (&b)[8], uint32_t idesc,
+                                          uint32_t accumulate_first) {
+  asm volatile(
+      "{\n\t.reg .pred L, F, T;\n\t"
+      "elect.sync _|L, 0xFFFFFFFF;\n\t"
+      "setp.ne.b32 F, %2, 0;\n\t"
+      "setp.eq.b32 T, 0, 0;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], %3, %11, %1, F;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], %4, %12, %1, T;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], %5, %13, %1, T;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], %6, %14, %1, T;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], %7, %15, %1, T;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], %8, %16, %1, T;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], %9, %17, %1, T;\n\t"
+      "@L tcgen05.mma.cta_group::1.kind::f16 [%0], %10, %18, %1, T;\n\t"
+      "}\n"
+      :
+      : "r"(d_tmem), "r"(idesc), "r"(accumulate_first), "l"(a[0]), "l"(a[1]), "l"(a[2]), "l"(a[3]), "l"(a[4]), "l"(a[5]),
+        "l"(a[6]), "l"(a[7]), "l"(b[0]), "l"(b[1]), "l"(b[2]), "l"(b[3]), "l"(b[4]), "l"(b[5]), "l"(b[6]), "l"(b[7])
+      : "memory");
+}
+
 // The same with A in TMEM (bf16, two per 32-bit column): a[k] is the TMEM address of the k-th 16-wide slice.
 __device__ __forceinline__ void mma_ts_x8_commit(uint32_t d_tmem, const uint32_t (&a)[8], const uint64_t (&b)[8],
                                                  uint32_t idesc, uint32_t accumulate_first, uint32_t bar) {

@@ -401,6 +401,12 @@ class MlaBuffers:
         return (self.workspace.data_ptr() + 255) & ~255
 
 
+def set_mla_mode(mode: int) -> None:
+    """Which kernel `mla_decode` launches: 1 (the default) tcgen05 with 64 rows per CTA, 0 warp-level MMA with 16.
+    Values agree to rounding."""
+    check(library().tjx_mla_set_mode(int(mode)))
+
+
 def mla_decode(q_c: torch.Tensor, q_r: torch.Tensor, c_kv: torch.Tensor, k_rope: torch.Tensor, lengths: torch.Tensor,
                block_kv: int = 512, out: torch.Tensor | None = None, buffers: MlaBuffers | None = None) -> torch.Tensor:
     """The `mla_decode` loop nest (examples/decode.py:226-250) for T new tokens per sequence: q_c (B, T, H, 512),
