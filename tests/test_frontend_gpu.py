@@ -7,7 +7,7 @@ import torch
 from helpers import f64, rand_bf16, to_device
 
 import oracle
-from tilejax_b200 import synthetic
+from tilejax_b200 import ops, synthetic
 from tilejax_b200.autokernel import Config, Pipeline
 from tilejax_b200.autokernel import kernels as K
 
@@ -81,9 +81,16 @@ def test_profile_says_where_the_time_goes():
     q, kp, vp, bt, lengths = synthetic.decode_inputs(8, 32, 8, 128, 16, 64, 1024)
     report = autokernel.profile(K.paged_gqa_decode, (q, kp, vp, bt, lengths))
     assert report.regions and report.wait_s > 0 and report.steps == 8 * 64
-    # A kernel that carries no counters still reports its device time.
+    # The MLA decode kernel counts too: its issuing warp's waits for the cache blocks and for the softmax warps.
     lengths4 = np.array([0, 1, 300, 512], np.int32)
     q_c, q_r = rand_bf16((4, 1, 16, 512), 7, 0.01), rand_bf16((4, 1, 16, 128), 8, 0.07)
     c_kv, k_rope = rand_bf16((4, 512, 512), 9), rand_bf16((4, 512, 128), 10)
-    blind = autokernel.profile(K.mla_decode, (q_c, q_r, c_kv, k_rope, lengths4, K.DecodeTiles(block_kv=128)))
+    report = autokernel.profile(K.mla_decode, (q_c, q_r, c_kv, k_rope, lengths4, K.DecodeTiles(block_kv=128)))
+    assert report.regions and report.device_s > 0 and report.wait_s > 0
+    # A kernel that carries no counters still reports its device time: the warp-level MLA kernel behind the switch.
+    ops.set_mla_mode(0)
+    try:
+        blind = autokernel.profile(K.mla_decode, (q_c, q_r, c_kv, k_rope, lengths4, K.DecodeTiles(block_kv=128)))
+    finally:
+        ops.set_mla_mode(1)
     assert not blind.regions and blind.bottleneck is None and blind.device_s > 0

@@ -4,6 +4,9 @@
 // output of a head is its softmax-weighted latents, so a position's 1280 bytes are read once for all the heads of
 // a head group.
 //
+// Two kernels: the tcgen05 one further down (the default) and the warp-level one described here (kept behind
+// tjx_mla_set_mode(0), and used for more than 2048 sequences).
+//
 // Work = the device step table built from `lengths` (tjx_steps.cu): a step is one block of `block` cache
 // positions of one sequence. A CTA takes one step and one group of 16 heads — the 16 rows of a warp-level MMA
 // (mma.sync m16n8k16, bf16 -> f32). The block streams through a CTA-wide ring of shared-memory slots, 16
@@ -69,8 +72,10 @@ struct MlaParams {
 
 // Merge `n` partials of rows h0 .. h0 + 3 of sequence b over this warp's 128 latent columns (from column c0; a
 // lane holds 4 of them), normalise and write bf16. The partials were written by other CTAs: read past L1.
-__device__ __forceinline__ void mla_merge_rows(const MlaParams& p, int b, int h0, int c0, int n, int lane) {
-  const size_t base = static_cast<size_t>(b) * p.blocks * p.H + h0;
+// `first_piece` is the index of the sequence's first partial in the workspace's [piece][row] arrays.
+__device__ __forceinline__ void mla_merge_rows(const MlaParams& p, size_t first_piece, int b, int h0, int c0, int n,
+                                               int lane) {
+  const size_t base = first_piece * p.H + h0;
   float mx[4], lsum[4];
   float4 o[4];
 #pragma unroll
@@ -334,19 +339,21 @@ __global__ void __launch_bounds__(MLA_WARPS * 32, 3)
     __syncthreads();
     if (last_sh) {
       __threadfence();
-      for (int r = 0; r < MLA_HEADS; r += 4) mla_merge_rows(p, b, h0 + r, c0, pieces, lane);
+      for (int r = 0; r < MLA_HEADS; r += 4)
+        mla_merge_rows(p, static_cast<size_t>(b) * p.blocks, b, h0 + r, c0, pieces, lane);
     }
   }
 }
 
 // ------------------------------------------------------------------------------------------------ tcgen05 path
 //
-// The same step on the tensor cores' own path: a CTA takes one step (a block of cache positions of one sequence)
-// and 64 rows ((new token, head) pairs) — the M of a 64-row tcgen05.mma — so a position's 1280 bytes are staged
-// once for 64 heads instead of once per 16, and the scores and the output accumulate in TMEM.
+// The same attention on the tensor cores' own path: a CTA works on 64 rows ((new token, head) pairs) — the M of a
+// 64-row tcgen05.mma — so a position's 1280 bytes are staged once for 64 heads instead of once per 16, and the
+// scores and the output accumulate in TMEM. One persistent CTA per SM takes a contiguous range of the launch's
+// 32-position units (see MtPiece below).
 //
-//   warp 0      producer: the 64 rows' queries once (ten 128-byte-swizzled boxes [64 rows x 64 columns], 80 KB), then
-//               the block 32 positions at a time through a ring of three 40 KB slots (ten boxes [32 x 64])
+//   warp 0      producer: per piece the 64 rows' queries (ten 128-byte-swizzled boxes [64 rows x 64 columns], 80 KB),
+//               then its units, 32 positions at a time, through a ring of three 40 KB slots (ten boxes [32 x 64])
 //   warp 1      MMA issuer (whole warp, one elected lane): S = Q K^T over the 640 columns (40 MMAs of 64 x 32 x 16 into
 //               one of two score buffers), then O += P V as two halves of 256 latent columns, P read from TMEM
 //   warps 2-5   softmax: a 64-row accumulator sits in TMEM lanes 0-15 of each 32-lane quarter (row 16 q + i in
@@ -356,9 +363,12 @@ __global__ void __launch_bounds__(MLA_WARPS * 32, 3)
 //               own TMEM lane so that the upper tile's MMA finds P beside its accumulator) and owns columns 256-511.
 //
 // TMEM: columns 0-255 O (both tiles), 256-287 and 288-319 the two score buffers; P (bf16, two per column)
-// overlays the first 16 columns of its score buffer. Partials and the merge are those of the kernel above.
+// overlays the first 16 columns of its score buffer.
+//
+// What bounds it: the 40 MMAs of 64 x 32 x 16 a unit's scores take (the queries' 80 KB leave shared memory room for
+// 32 positions per ring slot only) cost ~65 cycles each whatever their size: ~3000 cycles per unit of 40 KB.
 constexpr int MT_ROWS = 64;
-constexpr int MT_POS = 32;                                   // positions per micro-step
+constexpr int MT_POS = 32;                                   // positions per unit of work (one pass of the pipeline)
 constexpr int MT_STAGES = 3;
 constexpr int MT_KV_BOX = MT_POS * 128;                      // 32 positions x 64 columns
 constexpr int MT_STAGE_BYTES = MLA_BOXES * MT_KV_BOX;        // 40 KB
@@ -366,36 +376,53 @@ constexpr int MT_Q_BOX = MT_ROWS * 128;                      // 64 rows x 64 col
 constexpr int MT_Q_BYTES = MLA_BOXES * MT_Q_BOX;             // 80 KB
 constexpr int MT_KV_OFF = MT_Q_BYTES;
 constexpr int MT_BAR_OFF = MT_KV_OFF + MT_STAGES * MT_STAGE_BYTES;
-constexpr int MT_SMEM = MT_BAR_OFF + 256 + 1024;
+constexpr int MT_MAX_B = 2048;                               // sequences whose unit counts fit the shared-memory table
+constexpr int MT_FIRST_OFF = MT_BAR_OFF + 256;               // int[B + 1]: units before each sequence
+constexpr int MT_SMEM = MT_FIRST_OFF + (MT_MAX_B + 1) * 4 + 252 + 1024;
 constexpr int MT_THREADS = 192;
 constexpr int MT_S_COL = 256;                                // first column of the score buffers
+constexpr int MT_MAX_CTAS = 256;                             // CTAs per 64-row group (the SMs of one GPU)
+constexpr int MT_MIN_SHARE = 2;                              // units a CTA takes at least
 constexpr float MT_RESCALE_THRESHOLD = 8.0f;
+
+// The work of a launch is every sequence's cache in units of 32 positions, in sequence order; the CTAs of a 64-row
+// group share the units out evenly, each taking one contiguous range, so ragged lengths balance to within a unit
+// and a sequence is cut into as few pieces as there are CTAs crossing it. Every CTA derives the list itself from
+// `lengths` (a warp scan in its prologue); the step-table kernel runs beside it and only emits the caller's tables.
+// A piece = (sequence, range of its units) is one pass of the pipeline below; a piece that is its sequence's only
+// one is normalised and written at once, else its partial goes to the workspace at index (CTA + sequence) — unique,
+// and consecutive for the pieces of one sequence — and the last CTA to count itself on the sequence merges.
+struct MtPiece {
+  int b, unit0, n_units, len, pieces;
+  size_t index, first_index;  // this piece's partial, the sequence's first
+};
 
 __global__ void __launch_bounds__(MT_THREADS, 1)
     mla_tc_kernel(const __grid_constant__ CUtensorMap map_qc, const __grid_constant__ CUtensorMap map_qr,
                   const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_r,
                   const MlaParams p) {
   extern __shared__ uint8_t mt_smem_raw[];
-  __shared__ int last_sh;
   const uint32_t base = (smem_u32(mt_smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = mt_smem_raw + (base - smem_u32(mt_smem_raw));
   const uint32_t bar_base = base + MT_BAR_OFF;
-  // barriers: q_full, kv_full[3], kv_empty[3], s_full[2], p_ready[2], o_done
+  // barriers: q_full, kv_full[3], kv_empty[3], s_full[2], p_ready[2], o_done, q_empty
   const uint32_t q_full = bar_base;
   auto kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
   auto kv_empty = [&](int s) { return bar_base + 8u * (4 + s); };
   auto s_full = [&](int t) { return bar_base + 8u * (7 + t); };
   auto p_ready = [&](int t) { return bar_base + 8u * (9 + t); };
   const uint32_t o_done = bar_base + 8u * 11;
-  constexpr int N_BARS = 12;
+  const uint32_t q_empty = bar_base + 8u * 12;
+  constexpr int N_BARS = 13;
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(base_ptr + MT_BAR_OFF + 8 * N_BARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + MT_BAR_OFF + 8 * N_BARS + 8);
+  int* first_unit = reinterpret_cast<int*>(base_ptr + MT_FIRST_OFF);  // [B + 1]
 
   const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
   long long* prof = p.profile == nullptr
                         ? nullptr
                         : p.profile + (static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * PROFILE_WORDS;
-  if (prof != nullptr && threadIdx.x == 0) prof[0] = clock64(), prof[9] = globaltimer_ns();
+  if (prof != nullptr && threadIdx.x == 0) prof[0] = clock64();
   if (threadIdx.x == 0) {
     for (int i = 0; i < N_BARS; ++i) mbar_init(bar_base + 8u * i, (i == 9 || i == 10) ? 4 : 1);
     *abort_flag = 0;
@@ -408,49 +435,83 @@ __global__ void __launch_bounds__(MT_THREADS, 1)
   if (warp == 1) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_holder)), 512);
     tmem_relinquish();
+  } else if (warp == 0) {
+    // Units before each sequence: an inclusive warp scan over the sequences, 32 at a time.
+    int carry = 0;
+    for (int b0 = 0; b0 < p.B; b0 += 32) {
+      const int b = b0 + lane;
+      int x = b < p.B ? (min(max(p.lengths[b], 0), p.S) + MT_POS - 1) / MT_POS : 0;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int y = __shfl_up_sync(0xFFFFFFFFu, x, d);
+        if (lane >= d) x += y;
+      }
+      if (b < p.B) first_unit[b + 1] = carry + x;
+      carry += __shfl_sync(0xFFFFFFFFu, x, 31);
+    }
+    if (lane == 0) first_unit[0] = 0;
   }
-  // Launched with programmatic stream serialisation behind the step-table kernel: nothing it writes is read
-  // before this returns.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  if (prof != nullptr && threadIdx.x == 0) prof[11] = globaltimer_ns();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = __shfl_sync(0xFFFFFFFFu, *tmem_holder, 0);
 
-  const int step = blockIdx.x;
-  const bool active = step < p.step_count[0];
-  const int b = active ? p.step_tile[step] : 0;
-  const int code = active ? p.step_code[step] : 4;
-  const int row0 = blockIdx.y * MT_ROWS;       // first of this CTA's rows among the sequence's p.H rows
-  const int len = p.lengths[b];
-  const int j0 = (code >> 3) * p.block;        // first cache position of the step
-  const int n_pos = (code & 4) ? 0 : min(p.block, len - j0);
-  const int n_micro = __shfl_sync(0xFFFFFFFFu, (n_pos + MT_POS - 1) / MT_POS, 0);
-  const int first = p.tile_first[b], pieces = p.tile_first[b + 1] - first;
-  const int slot = step - first;
+  const int row0 = blockIdx.y * MT_ROWS;  // first of this CTA's rows among a sequence's p.H rows
+  // (Read from shared memory: the same in every lane, and said so to the compiler, so that the MMA warp's loops over
+  // this CTA's range stay warp-uniform and its descriptors in uniform registers.)
+  const int total_units = __shfl_sync(0xFFFFFFFFu, first_unit[p.B], 0);
+  const int share = max(MT_MIN_SHARE, (total_units + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x));
+  const int cta = static_cast<int>(blockIdx.x);
+  const int u_begin = min(cta * share, total_units), u_end = min(u_begin + share, total_units);
+  // The piece that starts at unit `u` of this CTA's range (u < u_end): the same in every thread.
+  auto piece_at = [&](int u) {
+    int lo = 0, hi = p.B;  // the sequence with first_unit[b] <= u < first_unit[b + 1]
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (first_unit[mid] <= u) lo = mid; else hi = mid;
+    }
+    MtPiece pc;
+    pc.b = lo;
+    const int f = first_unit[lo], l = first_unit[lo + 1];
+    pc.unit0 = u - f;
+    pc.n_units = min(u_end, l) - u;
+    pc.len = min(max(p.lengths[lo], 0), p.S);
+    const int first_cta = f / share;
+    pc.pieces = (l - 1) / share - first_cta + 1;
+    pc.index = static_cast<size_t>(cta) + lo;
+    pc.first_index = static_cast<size_t>(first_cta) + lo;
+    return pc;
+  };
 
-  if (!active) {
-    // (No step for this CTA: nothing to do but give the TMEM back.)
-  } else if (warp == 0) {
+  if (warp == 0) {
     // ------------------------------------------------------------------ producer
-    if (lane == 0 && n_micro > 0) {
-      const int q_row = b * p.H + row0;
-      mbar_expect_tx(q_full, MT_Q_BYTES);
-      for (int x = 0; x < MLA_C / 64; ++x) tma_load_2d(base + x * MT_Q_BOX, &map_qc, 64 * x, q_row, q_full);
-      for (int x = 0; x < MLA_R / 64; ++x) tma_load_2d(base + (MLA_C / 64 + x) * MT_Q_BOX, &map_qr, 64 * x, q_row, q_full);
-      const int token0 = b * p.S + j0;
-      for (int i = 0; i < n_micro; ++i) {
-        const int stage = i % MT_STAGES;
-        if (i >= MT_STAGES &&
-            !mbar_wait(kv_empty(stage), ((i / MT_STAGES) - 1) & 1, abort_flag, p.status, TJX_ERR_WAIT_EMPTY))
-          break;
-        const uint32_t dst = base + MT_KV_OFF + stage * MT_STAGE_BYTES;
-        const int row = token0 + i * MT_POS;
-        mbar_expect_tx(kv_full(stage), MT_STAGE_BYTES);
-        for (int x = 0; x < MLA_C / 64; ++x) tma_load_2d(dst + x * MT_KV_BOX, &map_c, 64 * x, row, kv_full(stage));
-        for (int x = 0; x < MLA_R / 64; ++x)
-          tma_load_2d(dst + (MLA_C / 64 + x) * MT_KV_BOX, &map_r, 64 * x, row, kv_full(stage));
+    if (lane == 0) {
+      int g = 0, done = 0;  // units and pieces loaded so far
+      bool ok = true;
+      for (int u = u_begin; u < u_end && ok; ++done) {
+        const MtPiece pc = piece_at(u);
+        // The previous piece's last Q K^T has read the queries.
+        if (done > 0 && !mbar_wait(q_empty, (done - 1) & 1, abort_flag, p.status, TJX_ERR_WAIT_EMPTY)) break;
+        const int q_row = pc.b * p.H + row0;
+        mbar_expect_tx(q_full, MT_Q_BYTES);
+        for (int x = 0; x < MLA_C / 64; ++x) tma_load_2d(base + x * MT_Q_BOX, &map_qc, 64 * x, q_row, q_full);
+        for (int x = 0; x < MLA_R / 64; ++x) tma_load_2d(base + (MLA_C / 64 + x) * MT_Q_BOX, &map_qr, 64 * x, q_row, q_full);
+        const int token0 = pc.b * p.S + pc.unit0 * MT_POS;
+        for (int i = 0; i < pc.n_units; ++i, ++g) {
+          const int stage = g % MT_STAGES;
+          if (g >= MT_STAGES &&
+              !mbar_wait(kv_empty(stage), ((g / MT_STAGES) - 1) & 1, abort_flag, p.status, TJX_ERR_WAIT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          const uint32_t dst = base + MT_KV_OFF + stage * MT_STAGE_BYTES;
+          const int row = token0 + i * MT_POS;
+          mbar_expect_tx(kv_full(stage), MT_STAGE_BYTES);
+          for (int x = 0; x < MLA_C / 64; ++x) tma_load_2d(dst + x * MT_KV_BOX, &map_c, 64 * x, row, kv_full(stage));
+          for (int x = 0; x < MLA_R / 64; ++x)
+            tma_load_2d(dst + (MLA_C / 64 + x) * MT_KV_BOX, &map_r, 64 * x, row, kv_full(stage));
+        }
+        u += pc.n_units;
       }
     }
     __syncwarp();
@@ -458,15 +519,15 @@ __global__ void __launch_bounds__(MT_THREADS, 1)
     // ------------------------------------------------------------------ MMA issuer (whole warp; one lane issues)
     const uint32_t idesc_qk = idesc_bf16_f32(MT_ROWS, MT_POS, 0, 0);  // Q and K both K-major
     const uint32_t idesc_pv = idesc_bf16_f32(MT_ROWS, 256, 0, 1);     // P from TMEM, the latents MN-major
-    long long in_wait = 0, p_wait = 0, fill_wait = 0;
+    long long in_wait = 0, p_wait = 0, fill_wait = -1, units = 0;
     const long long t_first = prof != nullptr ? clock64() : 0;
     auto wait = [&](uint32_t bar, uint32_t parity, int err, long long& waited) {
       return __all_sync(0xFFFFFFFFu, mbar_wait_timed(bar, parity, abort_flag, p.status, err, waited, prof != nullptr)) != 0;
     };
-    auto issue_qk = [&](int i) {
-      const int stage = i % MT_STAGES;
+    auto issue_qk = [&](int g) {  // the scores of unit g (counted over the CTA's whole range)
+      const int stage = g % MT_STAGES;
       const uint32_t kv = base + MT_KV_OFF + stage * MT_STAGE_BYTES;
-      const uint32_t d = tmem_base + MT_S_COL + (i & 1) * MT_POS;
+      const uint32_t d = tmem_base + MT_S_COL + (g & 1) * MT_POS;
 #pragma unroll
       for (int pair = 0; pair < MLA_BOXES / 2; ++pair) {  // two 64-column boxes = eight MMAs at a time
         uint64_t qd[8], kd[8];
@@ -478,44 +539,52 @@ __global__ void __launch_bounds__(MT_THREADS, 1)
         }
         mma_ss_x8(d, qd, kd, idesc_qk, pair != 0 ? 1u : 0u);
       }
-      mma_commit_elected(s_full(i & 1));
+      mma_commit_elected(s_full(g & 1));
     };
-    bool ok = n_micro == 0 || wait(q_full, 0, TJX_ERR_WAIT_FULL, in_wait);
-    if (ok && n_micro > 0) {
-      ok = wait(kv_full(0), 0, TJX_ERR_WAIT_FULL, in_wait);
-      fill_wait = in_wait;
-      if (ok) {
-        tc_fence_after_sync();
-        issue_qk(0);
-      }
-    }
-    for (int i = 0; i < n_micro && ok; ++i) {
-      const int stage = i % MT_STAGES;
-      if (i + 1 < n_micro) {  // the next block's scores run while this one's softmax does
-        ok = wait(kv_full((i + 1) % MT_STAGES), ((i + 1) / MT_STAGES) & 1, TJX_ERR_WAIT_FULL, in_wait);
-        if (!ok) break;
-        tc_fence_after_sync();
-        issue_qk(i + 1);
-      }
-      ok = wait(p_ready(i & 1), (i >> 1) & 1, TJX_ERR_WAIT_OTHER, p_wait);
+    int g0 = 0, done = 0;  // units and pieces issued so far
+    bool ok = true;
+    for (int u = u_begin; u < u_end && ok; ++done) {
+      const MtPiece pc = piece_at(u);
+      const int n = __shfl_sync(0xFFFFFFFFu, pc.n_units, 0);
+      ok = wait(q_full, done & 1, TJX_ERR_WAIT_FULL, in_wait) &&
+           wait(kv_full(g0 % MT_STAGES), (g0 / MT_STAGES) & 1, TJX_ERR_WAIT_FULL, in_wait);
+      if (fill_wait < 0) fill_wait = in_wait;
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t kv = base + MT_KV_OFF + stage * MT_STAGE_BYTES;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {  // latent columns 256 half .. 256 half + 255: the tile at lanes 16 half
-        const uint32_t tile = static_cast<uint32_t>(16 * half) << 16;
-#pragma unroll
-        for (int kk = 0; kk < MT_POS / 16; ++kk) {
-          const uint64_t vd = smem_desc_sw128(kv + half * 4 * MT_KV_BOX + kk * (16 * 128), MT_KV_BOX, 1024);
-          const uint32_t pa = tmem_base + tile + MT_S_COL + (i & 1) * MT_POS + kk * 8;
-          if (elect_one()) mma_ts(tmem_base + tile, pa, vd, idesc_pv, (i != 0 || kk != 0) ? 1u : 0u);
+      issue_qk(g0);
+      if (n == 1) mma_commit_elected(q_empty);
+      for (int i = 0; i < n && ok; ++i) {
+        const int g = g0 + i;
+        const int stage = g % MT_STAGES;
+        if (i + 1 < n) {  // the next unit's scores run while this one's softmax does
+          ok = wait(kv_full((g + 1) % MT_STAGES), ((g + 1) / MT_STAGES) & 1, TJX_ERR_WAIT_FULL, in_wait);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_qk(g + 1);
+          if (i + 2 == n) mma_commit_elected(q_empty);  // that was the piece's last Q K^T
         }
+        ok = wait(p_ready(g & 1), (g >> 1) & 1, TJX_ERR_WAIT_OTHER, p_wait);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t kv = base + MT_KV_OFF + stage * MT_STAGE_BYTES;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {  // latent columns 256 half .. 256 half + 255: the tile at lanes 16 half
+          const uint32_t tile = static_cast<uint32_t>(16 * half) << 16;
+#pragma unroll
+          for (int kk = 0; kk < MT_POS / 16; ++kk) {
+            const uint64_t vd = smem_desc_sw128(kv + half * 4 * MT_KV_BOX + kk * (16 * 128), MT_KV_BOX, 1024);
+            const uint32_t pa = tmem_base + tile + MT_S_COL + (g & 1) * MT_POS + kk * 8;
+            if (elect_one()) mma_ts(tmem_base + tile, pa, vd, idesc_pv, (i != 0 || kk != 0) ? 1u : 0u);
+          }
+        }
+        mma_commit_elected(kv_empty(stage));
+        mma_commit_elected(o_done);
       }
-      mma_commit_elected(kv_empty(stage));
-      mma_commit_elected(o_done);
+      g0 += n, units += n;
+      u += n;
     }
     if (prof != nullptr && lane == 0) {
-      prof[1] = t_first, prof[2] = clock64(), prof[3] = in_wait, prof[4] = fill_wait, prof[5] = 0, prof[6] = n_micro;
+      prof[1] = t_first, prof[2] = clock64(), prof[3] = in_wait, prof[4] = max(fill_wait, 0ll), prof[5] = 0, prof[6] = units;
       prof[8] = p_wait;
     }
   } else {
@@ -526,156 +595,225 @@ __global__ void __launch_bounds__(MT_THREADS, 1)
     const int row = row0 + r;                    // row within the sequence
     const uint32_t quarter = static_cast<uint32_t>(32 * q) << 16;
     const uint32_t o_tmem = tmem_base + quarter;  // this lane: lane 32 q + lane, columns 0..255
-    // New token `row / heads` sees the positions before lengths[b] - T + token + 1; the step ends at j0 + n_pos.
-    const int limit = min(len - p.T + row / p.heads + 1, j0 + n_pos);
-    float m_used = MLA_MASK * MLA_LOG2E, l = 0.f;
+    // Sequences without a position have no piece: their rows are zeros.
+    if (row < p.H)
+      for (int b = cta; b < p.B; b += static_cast<int>(gridDim.x))
+        if (first_unit[b + 1] == first_unit[b]) {
+          uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(b) * p.H + row) * MLA_C + 256 * half);
+          for (int x = 0; x < 32; ++x) dst[x] = make_uint4(0u, 0u, 0u, 0u);
+        }
+    int g0 = 0;  // units seen so far
     bool ok = true;
-    for (int i = 0; i < n_micro; ++i) {
-      const bool got = mbar_wait(s_full(i & 1), (i >> 1) & 1, abort_flag, p.status, TJX_ERR_WAIT_TMEM_FULL);
-      if (!__all_sync(0xFFFFFFFFu, got)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after_sync();
-      const uint32_t s_tmem = tmem_base + quarter + MT_S_COL + (i & 1) * MT_POS;
-      uint32_t v[32];
-      tmem_ld32(s_tmem, v);
-      tmem_wait_ld();
-      const int pos0 = j0 + i * MT_POS;
-      float mx = MLA_MASK * MLA_LOG2E;
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        // Lanes 16-31 take the scores of the lane 16 below: the same row.
-        const float sc = __shfl_sync(0xFFFFFFFFu, __uint_as_float(v[j]), lane & 15);
-        const float x = pos0 + j < limit ? sc * MLA_LOG2E : MLA_MASK * MLA_LOG2E;
-        v[j] = __float_as_uint(x);
-        mx = fmaxf(mx, x);
-      }
-      if (i == 0) {
-        m_used = mx;
-      } else if (__any_sync(0xFFFFFFFFu, mx > m_used + MT_RESCALE_THRESHOLD)) {
-        // Raise the running max and rescale what has been accumulated: O += P V of the previous block is complete.
-        const float m_new = fmaxf(m_used, mx);
-        const float alpha = ex2(m_used - m_new);
-        m_used = m_new;
-        l *= alpha;
-        const bool od = mbar_wait(o_done, (i - 1) & 1, abort_flag, p.status, TJX_ERR_WAIT_OTHER);
-        if (!__all_sync(0xFFFFFFFFu, od)) {
+    for (int u = u_begin; u < u_end && ok;) {
+      const MtPiece pc = piece_at(u);
+      const int n = pc.n_units;
+      const int j0 = pc.unit0 * MT_POS;
+      // New token `row / heads` sees the positions before lengths[b] - T + token + 1.
+      const int limit = min(pc.len - p.T + row / p.heads + 1, pc.len);
+      float m_used = MLA_MASK * MLA_LOG2E, l = 0.f;
+      for (int i = 0; i < n; ++i) {
+        const int g = g0 + i;
+        const bool got = mbar_wait(s_full(g & 1), (g >> 1) & 1, abort_flag, p.status, TJX_ERR_WAIT_TMEM_FULL);
+        if (!__all_sync(0xFFFFFFFFu, got)) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
+        const uint32_t s_tmem = tmem_base + quarter + MT_S_COL + (g & 1) * MT_POS;
+        uint32_t v[32];
+        tmem_ld32(s_tmem, v);
+        tmem_wait_ld();
+        const int pos0 = j0 + i * MT_POS;
+        float mx = MLA_MASK * MLA_LOG2E;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          // Lanes 16-31 take the scores of the lane 16 below: the same row.
+          const float sc = __shfl_sync(0xFFFFFFFFu, __uint_as_float(v[j]), lane & 15);
+          const float x = pos0 + j < limit ? sc * MLA_LOG2E : MLA_MASK * MLA_LOG2E;
+          v[j] = __float_as_uint(x);
+          mx = fmaxf(mx, x);
+        }
+        if (i == 0) {
+          m_used = mx;
+        } else if (__any_sync(0xFFFFFFFFu, mx > m_used + MT_RESCALE_THRESHOLD)) {
+          // Raise the running max and rescale what has been accumulated, once O += P V of the previous unit is complete.
+          const float m_new = fmaxf(m_used, mx);
+          const float alpha = ex2(m_used - m_new);
+          m_used = m_new;
+          l *= alpha;
+          const bool od = mbar_wait(o_done, (g - 1) & 1, abort_flag, p.status, TJX_ERR_WAIT_OTHER);
+          if (!__all_sync(0xFFFFFFFFu, od)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+#pragma unroll 1
+          for (int c = 0; c < 8; ++c) {
+            uint32_t o[32];
+            tmem_ld32(o_tmem + c * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+            tmem_st32(o_tmem + c * 32, o);
+          }
+          tmem_wait_st();
+        }
+        uint32_t pk[16];
+        float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          const float p0 = ex2(__uint_as_float(v[j]) - m_used), p1 = ex2(__uint_as_float(v[j + 1]) - m_used);
+          l0 += p0, l1 += p1;
+          pk[j >> 1] = pack_bf16(p0, p1);  // P is rounded before P V
+        }
+        l += l0 + l1;
+        tmem_st16(s_tmem, pk);
+        tmem_wait_st();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_ready(g & 1));
+        // Keep up with o_done: a parity wait is only right for a waiter at most one phase behind, and nothing else
+        // makes this warp see P V of the previous unit complete (this unit's scores were issued before it). The
+        // piece's last P V is waited for below, before O is read.
+        if (i >= 1) {
+          const bool od = mbar_wait(o_done, (g - 1) & 1, abort_flag, p.status, TJX_ERR_WAIT_OTHER);
+          ok = __all_sync(0xFFFFFFFFu, od) != 0;
+        }
+        if (ok && i + 1 == n) {
+          const bool od = mbar_wait(o_done, g & 1, abort_flag, p.status, TJX_ERR_WAIT_OTHER);
+          ok = __all_sync(0xFFFFFFFFu, od) != 0;
+        }
+        if (!ok) break;
+        tc_fence_after_sync();
+      }
+      if (!ok) break;
+      // Flush this lane's 256 latent columns of its row: the output itself, or a partial for the merge.
+      if (row < p.H) {
+        const int c0 = 256 * half;
+        const float inv = 1.0f / fmaxf(l, 1e-30f);
+        const size_t part = pc.index * p.H + row;
+        if (pc.pieces > 1 && half == 0) {  // the partials keep the max in natural-log units
+          p.ws_m[part] = m_used * (1.0f / MLA_LOG2E);
+          p.ws_l[part] = l;
+        }
 #pragma unroll 1
         for (int c = 0; c < 8; ++c) {
           uint32_t o[32];
           tmem_ld32(o_tmem + c * 32, o);
           tmem_wait_ld();
+          if (pc.pieces == 1) {
+            uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(pc.b) * p.H + row) * MLA_C + c0 + c * 32);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
-          tmem_st32(o_tmem + c * 32, o);
-        }
-        tmem_wait_st();
-      }
-      uint32_t pk[16];
-      float l0 = 0.f, l1 = 0.f;
+            for (int x = 0; x < 4; ++x) {
+              uint4 val;
+              val.x = pack_bf16(__uint_as_float(o[8 * x + 0]) * inv, __uint_as_float(o[8 * x + 1]) * inv);
+              val.y = pack_bf16(__uint_as_float(o[8 * x + 2]) * inv, __uint_as_float(o[8 * x + 3]) * inv);
+              val.z = pack_bf16(__uint_as_float(o[8 * x + 4]) * inv, __uint_as_float(o[8 * x + 5]) * inv);
+              val.w = pack_bf16(__uint_as_float(o[8 * x + 6]) * inv, __uint_as_float(o[8 * x + 7]) * inv);
+              dst[x] = val;
+            }
+          } else {
+            uint4* dst = reinterpret_cast<uint4*>(p.ws_acc + part * MLA_C + c0 + c * 32);
 #pragma unroll
-      for (int j = 0; j < 32; j += 2) {
-        const float p0 = ex2(__uint_as_float(v[j]) - m_used), p1 = ex2(__uint_as_float(v[j + 1]) - m_used);
-        l0 += p0, l1 += p1;
-        pk[j >> 1] = pack_bf16(p0, p1);  // P is rounded before P V
-      }
-      l += l0 + l1;
-      tmem_st16(s_tmem, pk);
-      tmem_wait_st();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(p_ready(i & 1));
-      // Keep up with o_done: a parity wait is only right for a waiter at most one phase behind, and nothing else
-      // makes this warp see P V of block i - 1 complete (the scores of block i were issued before it).
-      if (i >= 1) {
-        const bool od = mbar_wait(o_done, (i - 1) & 1, abort_flag, p.status, TJX_ERR_WAIT_OTHER);
-        if (!__all_sync(0xFFFFFFFFu, od)) {
-          ok = false;
-          break;
-        }
-      }
-    }
-    if (n_micro > 0 && ok) {
-      const bool od = mbar_wait(o_done, (n_micro - 1) & 1, abort_flag, p.status, TJX_ERR_WAIT_OTHER);
-      ok = __all_sync(0xFFFFFFFFu, od) != 0;
-      tc_fence_after_sync();
-    }
-    // Flush this lane's 256 latent columns of its row: the output itself, or a partial for the merge.
-    if (ok && row < p.H) {
-      const int c0 = 256 * half;
-      const float inv = 1.0f / fmaxf(l, 1e-30f);
-      const size_t part = (static_cast<size_t>(b) * p.blocks + slot) * p.H + row;
-      if (pieces > 1 && half == 0) {  // the partials keep the max in natural-log units
-        p.ws_m[part] = m_used * (1.0f / MLA_LOG2E);
-        p.ws_l[part] = l;
-      }
-#pragma unroll 1
-      for (int c = 0; c < 8; ++c) {
-        uint32_t o[32];
-        if (n_micro > 0) {
-          tmem_ld32(o_tmem + c * 32, o);
-          tmem_wait_ld();
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) o[j] = 0u;
-        }
-        if (pieces == 1) {
-          uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(b) * p.H + row) * MLA_C + c0 + c * 32);
-#pragma unroll
-          for (int x = 0; x < 4; ++x) {
-            uint4 val;
-            val.x = pack_bf16(__uint_as_float(o[8 * x + 0]) * inv, __uint_as_float(o[8 * x + 1]) * inv);
-            val.y = pack_bf16(__uint_as_float(o[8 * x + 2]) * inv, __uint_as_float(o[8 * x + 3]) * inv);
-            val.z = pack_bf16(__uint_as_float(o[8 * x + 4]) * inv, __uint_as_float(o[8 * x + 5]) * inv);
-            val.w = pack_bf16(__uint_as_float(o[8 * x + 6]) * inv, __uint_as_float(o[8 * x + 7]) * inv);
-            dst[x] = val;
+            for (int x = 0; x < 8; ++x) dst[x] = make_uint4(o[4 * x], o[4 * x + 1], o[4 * x + 2], o[4 * x + 3]);
           }
-        } else {
-          uint4* dst = reinterpret_cast<uint4*>(p.ws_acc + part * MLA_C + c0 + c * 32);
-#pragma unroll
-          for (int x = 0; x < 8; ++x) dst[x] = make_uint4(o[4 * x], o[4 * x + 1], o[4 * x + 2], o[4 * x + 3]);
         }
       }
-    }
-    tc_fence_before_sync();
-    if (pieces > 1) {
-      // Count this step on each of its 16-row groups; the CTA that counts last on a group finds every partial of
-      // (sequence, group) written and merges it. The four softmax warps meet on a named barrier, whatever happened
-      // before: a warp whose wait gave up raised the CTA's abort flag, which all of them read after the barrier.
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      const bool healthy = *abort_flag == 0;
-      if (healthy && warp == 2 && lane == 0) {
-        int last = 0;
-        for (int gq = 0; gq < 4; ++gq)
-          if (row0 + 16 * gq < p.H)
-            last |= (atomicAdd(p.arrivals + b * (p.H / MLA_HEADS) + (row0 / MLA_HEADS) + gq, 1) == pieces - 1) << gq;
-        last_sh = last;
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      const int last = healthy ? last_sh : 0;
-      if (last) {
-        __threadfence();
-        for (int gq = 0; gq < 4; ++gq)
-          if ((last >> gq) & 1)
-            for (int rr = 0; rr < MLA_HEADS; rr += 4) mla_merge_rows(p, b, row0 + 16 * gq + rr, 128 * q, pieces, lane);
-      }
+      // The reads of O above are ordered before this warp's next arrival on p_ready, which is what the next piece's
+      // first P V waits for before it overwrites O. (Partials are merged by mla_tc_merge_kernel, launched behind this.)
+      tc_fence_before_sync();
+      g0 += n;
+      u += n;
     }
   }
 
   tc_fence_before_sync();
   __syncthreads();
-  if (prof != nullptr && threadIdx.x == 0) prof[7] = clock64(), prof[10] = globaltimer_ns();
+  if (prof != nullptr && threadIdx.x == 0) prof[7] = clock64();
   if (warp == 1) {
     if (*abort_flag) __nanosleep(100000);
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }
+}
+
+// Merges the partials mla_tc_kernel left: a CTA per (sequence, 8 rows), a warp per row, a lane 16 of the row's 512
+// latent columns. It works out the sequence's pieces as the main kernel did (units before the sequence, the share
+// of a CTA), returns at once for a sequence written directly, and otherwise reads the pieces' (max, sum,
+// accumulator) past L1, weights them by exp(max_i - max), and writes the normalised row in bf16. Launched with
+// programmatic stream serialisation: the prologue runs beside the main kernel's tail.
+constexpr int MG_WARPS = 8;
+
+__global__ void __launch_bounds__(MG_WARPS * 32)
+    mla_tc_merge_kernel(const MlaParams p, int main_ctas) {
+  __shared__ int seq_units[3];  // units before sequence b, before b + 1, in total
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.x;
+  if (warp == 0) {
+    int carry = 0, before = 0, through = 0;
+    for (int b0 = 0; b0 < p.B; b0 += 32) {
+      const int i = b0 + lane;
+      int x = i < p.B ? (min(max(p.lengths[i], 0), p.S) + MT_POS - 1) / MT_POS : 0;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int y = __shfl_up_sync(0xFFFFFFFFu, x, d);
+        if (lane >= d) x += y;
+      }
+      const int incl = carry + x;
+      if (i == b) through = incl;
+      if (i == b - 1) before = incl;
+      carry += __shfl_sync(0xFFFFFFFFu, x, 31);
+    }
+    // (Each of the two values was seen by one lane.)
+    before = __reduce_max_sync(0xFFFFFFFFu, before), through = __reduce_max_sync(0xFFFFFFFFu, through);
+    if (lane == 0) seq_units[0] = before, seq_units[1] = through, seq_units[2] = carry;
+  }
+  __syncthreads();
+  const int f = seq_units[0], l = seq_units[1], total = seq_units[2];
+  if (l == f) return;  // no position: the main kernel wrote zeros
+  const int share = max(MT_MIN_SHARE, (total + main_ctas - 1) / main_ctas);
+  const int first_cta = f / share;
+  const int n = (l - 1) / share - first_cta + 1;
+  if (n <= 1) return;  // written directly
+  const int row = blockIdx.y * MG_WARPS + warp;
+  if (row >= p.H) return;
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // the partials are the main kernel's
+  const size_t base = (static_cast<size_t>(first_cta) + b) * p.H + row;  // piece i: base + i * p.H
+  float mx = MLA_MASK;
+  for (int i = lane; i < n; i += 32) mx = fmaxf(mx, __ldcg(p.ws_m + base + static_cast<size_t>(i) * p.H));
+#pragma unroll
+  for (int d = 16; d >= 1; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, d));
+  float lsum = 0.f;
+  float4 o[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) o[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int i0 = 0; i0 < n; i0 += 32) {
+    float w_mine = 0.f;
+    if (i0 + lane < n) {
+      const size_t idx = base + static_cast<size_t>(i0 + lane) * p.H;
+      w_mine = __expf(__ldcg(p.ws_m + idx) - mx);
+      lsum += w_mine * __ldcg(p.ws_l + idx);
+    }
+    const int cnt = min(32, n - i0);
+#pragma unroll 4
+    for (int i = 0; i < cnt; ++i) {
+      const float w = __shfl_sync(0xFFFFFFFFu, w_mine, i);
+      const float4* src = reinterpret_cast<const float4*>(p.ws_acc + (base + static_cast<size_t>(i0 + i) * p.H) * MLA_C);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float4 a = __ldcg(src + lane + 32 * k);
+        o[k].x = fmaf(w, a.x, o[k].x), o[k].y = fmaf(w, a.y, o[k].y);
+        o[k].z = fmaf(w, a.z, o[k].z), o[k].w = fmaf(w, a.w, o[k].w);
+      }
+    }
+  }
+#pragma unroll
+  for (int d = 16; d >= 1; d >>= 1) lsum += __shfl_xor_sync(0xFFFFFFFFu, lsum, d);
+  const float inv = 1.0f / fmaxf(lsum, 1e-30f);
+  uint2* dst = reinterpret_cast<uint2*>(p.out + (static_cast<size_t>(b) * p.H + row) * MLA_C);
+#pragma unroll
+  for (int k = 0; k < 4; ++k)
+    dst[lane + 32 * k] = make_uint2(pack_bf16(o[k].x * inv, o[k].y * inv), pack_bf16(o[k].z * inv, o[k].w * inv));
 }
 
 int g_mla_mode = 1;  // 1: the tcgen05 kernel; 0: the warp-level MMA kernel (an A/B switch; values agree to rounding)
@@ -695,7 +833,7 @@ int tjx_mla_set_mode(int mode) {
 size_t tjx_mla_decode_workspace_bytes(int B, int T, int H, int S, int block) {
   if (B <= 0 || T <= 0 || H <= 0 || S <= 0 || block <= 0 || S % block != 0) return 0;
   H *= T;  // rows per sequence
-  const size_t rows = static_cast<size_t>(B) * (S / block) * H;
+  const size_t rows = std::max(static_cast<size_t>(B) * (S / block), static_cast<size_t>(tjx::MT_MAX_CTAS) + B) * H;
   return 2 * tjx::mla_align256(rows * sizeof(float)) + tjx::mla_align256(rows * tjx::MLA_C * sizeof(float)) +
          tjx::mla_align256(static_cast<size_t>(B) * H * sizeof(int));
 }
@@ -717,6 +855,7 @@ int tjx_mla_decode_bf16(const void* q_c, const void* q_r, const void* c_kv, cons
   const size_t need = tjx_mla_decode_workspace_bytes(B, T, H, S, block);
   const int heads = H;
   H *= T;  // rows per sequence from here on
+  const bool tensor_path = g_mla_mode == 1 && B <= MT_MAX_B;
   if (workspace == nullptr || workspace_bytes < need)
     return fail(TJX_E_ARG, "workspace is null or smaller than tjx_mla_decode_workspace_bytes");
   if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(TJX_E_ARG, "workspace must be 256-byte aligned");
@@ -733,7 +872,9 @@ int tjx_mla_decode_bf16(const void* q_c, const void* q_r, const void* c_kv, cons
   p.step_tile = step_tile, p.step_code = step_code, p.step_count = step_count, p.tile_first = tile_first;
   p.B = B, p.H = H, p.S = S, p.block = block, p.blocks = S / block;
   p.heads = heads, p.T = T;
-  const size_t rows = static_cast<size_t>(B) * p.blocks * H;
+  // Partials: [sequence][block] for the warp-level kernel, [CTA + sequence] for the tcgen05 kernel; the workspace
+  // holds the larger of the two.
+  const size_t rows = std::max(static_cast<size_t>(B) * p.blocks, static_cast<size_t>(MT_MAX_CTAS) + B) * H;
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   p.ws_m = reinterpret_cast<float*>(ws);
   p.ws_l = reinterpret_cast<float*>(ws + mla_align256(rows * sizeof(float)));
@@ -749,7 +890,7 @@ int tjx_mla_decode_bf16(const void* q_c, const void* q_r, const void* c_kv, cons
                                           tile_first, p.arrivals, B * (H / MLA_HEADS), s))
     return rc;
 
-  if (g_mla_mode == 1) {
+  if (tensor_path) {
     CUtensorMap mqc, mqr, mc, mr;
     const uint32_t q_box[2] = {64, MT_ROWS}, kv_box[2] = {64, MT_POS};
     const uint64_t q_rows = static_cast<uint64_t>(B) * H, kv_rows = static_cast<uint64_t>(B) * S;
@@ -770,15 +911,22 @@ int tjx_mla_decode_bf16(const void* q_c, const void* q_r, const void* c_kv, cons
       TJX_CUDA(cudaFuncSetAttribute(mla_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MT_SMEM));
       tc_configured[dev & 63] = true;
     }
-    p.profile = profile_buffer(B * p.blocks * ((H + MT_ROWS - 1) / MT_ROWS));
+    const int groups = (H + MT_ROWS - 1) / MT_ROWS;
+    const int ctas = std::max(1, std::min(MT_MAX_CTAS, sm_count() / groups));
+    p.profile = profile_buffer(ctas * groups);
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(B * p.blocks, (H + MT_ROWS - 1) / MT_ROWS), cfg.blockDim = dim3(MT_THREADS);
+    cfg.gridDim = dim3(ctas, groups), cfg.blockDim = dim3(MT_THREADS);
     cfg.dynamicSmemBytes = MT_SMEM, cfg.stream = s;
     cudaLaunchAttribute attr{};
     attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr, cfg.numAttrs = 1;
     TJX_CUDA(cudaLaunchKernelEx(&cfg, mla_tc_kernel, mqc, mqr, mc, mr, p));
+    cudaLaunchConfig_t merge{};
+    merge.gridDim = dim3(B, (H + MG_WARPS - 1) / MG_WARPS), merge.blockDim = dim3(MG_WARPS * 32);
+    merge.dynamicSmemBytes = 0, merge.stream = s;
+    merge.attrs = &attr, merge.numAttrs = 1;
+    TJX_CUDA(cudaLaunchKernelEx(&merge, mla_tc_merge_kernel, p, ctas));
     return 0;
   }
 
