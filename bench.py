@@ -51,6 +51,11 @@ NCU_TRAFFIC_BYTES: dict[str, float] = {
     "gemm_16384x8192x8192": 2.299167e9 + 0.263586e9,
     "paged_gqa_decode_B64_H32_Hkv8_D128_page16_shared_pages": 467166208.0 + 4148480.0,
     "paged_gqa_decode_B64_H32_Hkv8_D128_page16_distinct_pages": 551334656.0 + 4222208.0,
+    # profiles/attention_kernel_b4_h16_s2048_d128.md: 132.9 MB read + 13.9 MB written (134.2 MB algorithmic).
+    "causal_attention_B4_H16_S2048_D128_blocks512": 132.940288e6 + 13.855488e6,
+    # profiles/mla_tc_kernel_b32_h64_ctx1024to3072.md: the main kernel's 89.9 MB read + 3.8 MB written (the cache rows
+    # as stored are 83.8 MB; 75.4 MB as the reference counts them).
+    "mla_decode_B32_H64_ctx1024to3072": 89.857792e6 + 3.791104e6,
 }
 
 
@@ -468,7 +473,7 @@ def extra_workloads(device, pk: dict, pk_kind: str, only: str | None = None, ite
             out[name] = {
                 "ms": ms, "value": gbs, "unit": "GB/s",
                 "tflops": tokens * H * (2 * 576 + 2 * 512) / ms / 1e9,
-                "includes": "step-table kernel + decode (the merge of partials is fused into it)",
+                "includes": "step-table kernel, the tcgen05 decode kernel and the kernel that merges its partials",
                 "roofline": hbm_roofline(gbs, pk, pk_kind, nbytes, ms, NCU_TRAFFIC_BYTES.get(name))}
         except Exception as e:  # report, do not hide
             out["mla_decode"] = {"error": str(e)[:200]}

@@ -198,6 +198,31 @@ int tjx_paged_gqa_decode_bf16(const void* q, const void* k_pages, const void* v_
                               int32_t* step_count, int32_t* tile_first, void* workspace, size_t workspace_bytes,
                               tjx_stream_t stream);
 
+/* Ragged paged attention, the in-place cache write (`rpa_write` with its runs, examples/ragged_paged_attention.py:33-79):
+ * the step's new keys and values [T, Hkv, D] go to positions [kv_len - q_len, kv_len) of their sequences in the cache
+ * [num_pages, page_size, Hkv, 2, D] (each head's key and value side by side), through page_indices
+ * [S * pages_per_seq]; cu_q_lens [S + 1] gives each sequence's first token; sequences from distribution[2] on and
+ * padding tokens (t >= cu_q_lens[S]) write nothing. One launch, a CTA per token. Constraint: D == 128. */
+int tjx_rpa_write_bf16(void* kv_cache, const void* keys, const void* values, const int32_t* kv_lens,
+                       const int32_t* page_indices, const int32_t* cu_q_lens, const int32_t* distribution, int T,
+                       int S, int Hkv, int D, int page_size, int pages_per_seq, int num_pages, tjx_stream_t stream);
+
+/* Bytes of scratch tjx_rpa_decode_bf16 needs for these sizes. */
+size_t tjx_rpa_decode_workspace_bytes(int T, int S, int H, int D, int pages_per_seq);
+
+/* Ragged paged attention, the decode case (`rpa_decode`, examples/ragged_paged_attention.py:121-149): sequence
+ * s < distribution[0] is token s; its query row q[s] [H, D] attends over the kv_lens[s] positions of its pages in the
+ * cache (the new token already written), scores scaled by sm_scale; out[s] is the attention output and every other
+ * row of out [T, H, D] is q's (out may be q: the update in place the reference's donated buffer gets). Runs the paged
+ * decode kernel of tjx_paged_gqa_decode_bf16 on the cache's own layout (two tensor maps over the one buffer).
+ *   workspace: at least tjx_rpa_decode_workspace_bytes(...) bytes, 256-byte aligned
+ * Constraints: D == 128; H / Hkv in {1, 2, 4, 8}; page_size a multiple of 16. The prefill / mixed case
+ * (`rpa_prefill`, :196-243) has no entry point. */
+int tjx_rpa_decode_bf16(const void* q, void* out, const void* kv_cache, const int32_t* kv_lens,
+                        const int32_t* page_indices, const int32_t* distribution, int T, int S, int H, int Hkv, int D,
+                        int page_size, int pages_per_seq, int num_pages, float sm_scale, void* workspace,
+                        size_t workspace_bytes, tjx_stream_t stream);
+
 /* Which kernel tjx_mla_decode_bf16 launches from now on: 1 (the default) the tcgen05 kernel, 64 rows per CTA with
  * scores and output in TMEM; 0 the warp-level MMA kernel, 16 rows per CTA. An A/B switch for measurements: the two
  * agree to rounding. No counterpart in the reference. */

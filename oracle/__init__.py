@@ -28,6 +28,7 @@ from .decode import (
 )
 from .matmul import causal_matmul_ref, collective_row_order, matmul_ref
 from .rmsnorm import rmsnorm_matmul_f64, rmsnorm_matmul_ref
+from .rpa import rpa_decode_f64, rpa_decode_ref, rpa_inputs, rpa_write_ref
 from .steps import (
     attention_step_tables,
     causal_tile_tables,
@@ -54,6 +55,10 @@ __all__ = [
     "paged_gqa_decode_ref",
     "rmsnorm_matmul_f64",
     "rmsnorm_matmul_ref",
+    "rpa_decode_f64",
+    "rpa_decode_ref",
+    "rpa_inputs",
+    "rpa_write_ref",
     "to_pages",
     "walk_nest",
 ]

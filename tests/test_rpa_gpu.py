@@ -1,0 +1,75 @@
+"""Ragged paged attention's cache write and decode case through the C ABI (examples/ragged_paged_attention.py:33-79,
+:121-149) against the oracle: the write bit for bit, the decode within the decode tolerance (2e-2,
+tests/test_decode.py:235) of the oracle and of float64."""
+
+import numpy as np
+import pytest
+import torch
+from helpers import f64, to_device, to_host
+
+import oracle
+from tilejax_b200 import ops
+from tilejax_b200._lib import NativeError
+
+pytestmark = pytest.mark.gpu
+
+NAMES = ("kv_cache", "keys", "values", "kv_lens", "page_indices", "cu_q_lens", "distribution")
+
+
+def step(q_lens, kv_lens, **sizes):
+    inp = oracle.rpa_inputs(q_lens, kv_lens, **sizes)
+    dev = {k: to_device(v) for k, v in inp.items()}
+    return inp, dev
+
+
+@pytest.mark.parametrize(("q_lens", "kv_lens", "sizes"), [
+    ([1, 1, 1, 300, 7, 130], [513, 1, 128, 300, 135, 400], dict(max_len=1024, max_tokens=448, max_seqs=8)),
+    ([1] * 16, list(range(1, 1025, 64)), dict(max_len=1024)),                       # decode only
+    ([5, 129], [5, 1000], dict(heads=8, kv_heads=2, max_len=1024, page_size=16)),   # no decode sequence; small pages
+])
+def test_the_write_is_bit_exact_and_touches_nothing_else(q_lens, kv_lens, sizes):
+    inp, dev = step(q_lens, kv_lens, **sizes)
+    want = oracle.rpa_write_ref(*(inp[n] for n in NAMES))
+    got = to_host(ops.rpa_write(*(dev[n] for n in NAMES)))
+    np.testing.assert_array_equal(got.view(np.uint16), want.view(np.uint16))
+    assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize(("q_lens", "kv_lens", "sizes"), [
+    ([1, 1, 1, 1, 9], [1, 128, 129, 700, 64], dict(max_len=1024, max_seqs=8)),      # Llama-3-8B heads: 32 / 8
+    ([1] * 24, [int(x) for x in np.random.default_rng(0).integers(1, 2049, 24)], dict(max_len=2048)),
+    ([1, 1, 40], [77, 513, 40], dict(heads=8, kv_heads=8, max_len=1024, page_size=64)),   # one query head per KV head
+    ([6, 3], [6, 30], dict(heads=16, kv_heads=2, max_len=256)),                     # no decode sequence: q comes back
+])
+def test_decode_matches_the_oracle_and_float64(q_lens, kv_lens, sizes):
+    inp, dev = step(q_lens, kv_lens, **sizes)
+    cache = ops.rpa_write(*(dev[n] for n in NAMES))
+    scale = 128**-0.5
+    args = (dev["q"], cache, dev["kv_lens"], dev["page_indices"], dev["distribution"], scale)
+    got = to_host(ops.rpa_decode(*args))
+    assert ops.device_status() == 0
+    host_cache = to_host(cache)
+    want = oracle.rpa_decode_ref(inp["q"], host_cache, inp["kv_lens"], inp["page_indices"], inp["distribution"], scale)
+    exact = oracle.rpa_decode_f64(inp["q"], host_cache, inp["kv_lens"], inp["page_indices"], inp["distribution"], scale)
+    assert np.abs(f64(got) - f64(want)).max() <= 2e-2
+    assert np.abs(f64(got) - exact).max() <= 2e-2
+    d0 = int(inp["distribution"][0])
+    np.testing.assert_array_equal(got[d0:].view(np.uint16), inp["q"][d0:].view(np.uint16))  # the other rows: the query
+    # In place, as the reference's donated queries: the same values.
+    q_in_place = dev["q"].clone()
+    same = ops.rpa_decode(q_in_place, *args[1:], out=q_in_place)
+    assert same.data_ptr() == q_in_place.data_ptr()
+    np.testing.assert_array_equal(to_host(same).view(np.uint16), got.view(np.uint16))
+
+
+def test_bad_arguments_are_errors():
+    inp, dev = step([1, 2], [5, 9], max_len=256)
+    with pytest.raises(ValueError, match="side by side"):
+        ops.rpa_decode(dev["q"], dev["kv_cache"][:, :, :, 0], dev["kv_lens"], dev["page_indices"], dev["distribution"])
+    with pytest.raises(ValueError, match=r"\(T, Hkv, D\)"):
+        ops.rpa_write(dev["kv_cache"], dev["keys"][:, :4].contiguous(), dev["values"], dev["kv_lens"],
+                      dev["page_indices"], dev["cu_q_lens"], dev["distribution"])
+    cache64 = torch.zeros(4, 128, 8, 2, 64, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(NativeError, match="head dimension must be 128"):
+        ops.rpa_decode(torch.zeros(3, 32, 64, dtype=torch.bfloat16, device="cuda"), cache64, dev["kv_lens"],
+                       dev["page_indices"], dev["distribution"])

@@ -77,6 +77,9 @@ struct DecodeParams {
   int B, H, Hkv, page_size, pages_per_seq, num_pages, slots;
   int T, rows;                   // new tokens per sequence; query rows per sequence = T * H (row t * H + h)
   int self_steps;                // != 0: derive the steps from `lengths` in the prologue instead of reading the tables
+  float score_scale;             // scores are multiplied by this before the base-2 exponential: log2(e), times the
+                                 // softmax scale when the queries do not arrive pre-scaled (ragged paged attention)
+  long long kv_head_stride, kv_token_stride;  // elements between KV heads / tokens in the page pools (0: packed)
   int* status;
   long long* profile;            // per-CTA counters (PROFILE_WORDS each) or null
 };
@@ -446,7 +449,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, WIDE ? (TJX_DEC_CTAS * 2 / 3) 
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int tok = (i >> 1) * 8 + 2 * t + (i & 1);
-          s4[i] = base_pos + tok <= last_visible ? s4[i] * DEC_LOG2E : DEC_MASK * DEC_LOG2E;
+          s4[i] = base_pos + tok <= last_visible ? s4[i] * p.score_scale : DEC_MASK * DEC_LOG2E;
         }
         float mx = fmaxf(fmaxf(s4[0], s4[1]), fmaxf(s4[2], s4[3]));
         mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
@@ -521,7 +524,10 @@ static int launch_decode_chunks(DecodeParams& p, int group, cudaStream_t s) {
   if (p.status == nullptr) return fail(TJX_E_CUDA, "could not locate the device status word");
   const uint64_t dims[3] = {DEC_D, static_cast<uint64_t>(p.Hkv),
                             static_cast<uint64_t>(p.num_pages) * static_cast<uint64_t>(p.page_size)};
-  const uint64_t strides[2] = {DEC_D * 2, static_cast<uint64_t>(p.Hkv) * DEC_D * 2};
+  const uint64_t head_stride = p.kv_head_stride > 0 ? static_cast<uint64_t>(p.kv_head_stride) : DEC_D;
+  const uint64_t token_stride = p.kv_token_stride > 0 ? static_cast<uint64_t>(p.kv_token_stride)
+                                                      : static_cast<uint64_t>(p.Hkv) * DEC_D;
+  const uint64_t strides[2] = {head_stride * 2, token_stride * 2};
   const uint32_t box[3] = {64, 1, DEC_SUB};
   CUtensorMap mk, mv;
   if (int rc = make_tensor_map(&mk, p.k_pages, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 3, dims, strides, box,
@@ -590,8 +596,11 @@ static int check_decode_args(const void* q, const void* k_pages, const void* v_p
 static int run_decode(const void* q, const void* k_pages, const void* v_pages, const int32_t* block_tables,
                       const int32_t* lengths, void* out, int B, int T, int H, int Hkv, int page_size,
                       int pages_per_seq, int num_pages, int32_t* step_tile, int32_t* step_code, int32_t* step_count,
-                      int32_t* tile_first, void* scratch, cudaStream_t s) {
+                      int32_t* tile_first, void* scratch, cudaStream_t s, float softmax_scale = 1.0f,
+                      long long kv_head_stride = 0, long long kv_token_stride = 0) {
   DecodeParams p{};
+  p.score_scale = DEC_LOG2E * softmax_scale;
+  p.kv_head_stride = kv_head_stride, p.kv_token_stride = kv_token_stride;
   p.q = static_cast<const __nv_bfloat16*>(q);
   p.k_pages = static_cast<const __nv_bfloat16*>(k_pages);
   p.v_pages = static_cast<const __nv_bfloat16*>(v_pages);
@@ -641,6 +650,160 @@ int tjx_paged_gqa_decode_bf16(const void* q, const void* k_pages, const void* v_
   return run_decode(q, k_pages, v_pages, block_tables, lengths, out, B, T, H, Hkv, page_size, pages_per_seq,
                     num_pages, step_tile, step_code, step_count, tile_first, workspace,
                     static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------------------------------------------------
+// Ragged paged attention's cache write and decode case (examples/ragged_paged_attention.py:33-47, :121-149): q
+// (T, H, D) with every sequence's new tokens concatenated, a cache (pages, page_size, Hkv, 2, D) holding each head's
+// key and value side by side, kv_lens (S,) with the new tokens included, page_indices (S * pages_per_seq,),
+// cu_q_lens (S + 1,), distribution (3,): sequences [0, d0) decode one token each (sequence s is token s).
+// The decode case is the paged decode kernel above on the cache's own layout — K of (token, head) 2 D elements
+// apart, V D elements after K: two tensor maps over one buffer — with the softmax scale folded into the score
+// scale, the lengths of sequences outside [0, d0) set to zero, and only the decode tokens' rows written back.
+
+namespace tjx {
+
+// One CTA per new token: its sequence by bisection in cu_q_lens, its position kv_len - q_len + (t - first token),
+// its page through page_indices; 128 threads copy the token's Hkv * D keys and values, 16 bytes at a time.
+__global__ void __launch_bounds__(128)
+    rpa_write_kernel(__nv_bfloat16* __restrict__ cache, const __nv_bfloat16* __restrict__ keys,
+                     const __nv_bfloat16* __restrict__ values, const int32_t* __restrict__ kv_lens,
+                     const int32_t* __restrict__ page_indices, const int32_t* __restrict__ cu_q_lens,
+                     const int32_t* __restrict__ distribution, int S, int Hkv, int page_size, int pages_per_seq,
+                     int num_pages) {
+  const int t = blockIdx.x;
+  int lo = 0, hi = S;  // the sequence with cu_q_lens[s] <= t < cu_q_lens[s + 1]
+  if (t >= cu_q_lens[S]) return;  // a padding token
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (cu_q_lens[mid] <= t) lo = mid; else hi = mid;
+  }
+  const int s = lo;
+  if (s >= distribution[2]) return;
+  const int first = cu_q_lens[s], q_len = cu_q_lens[s + 1] - first;
+  const int pos = kv_lens[s] - q_len + (t - first);
+  if (pos < 0 || pos >= pages_per_seq * page_size) return;
+  const int page = min(max(page_indices[s * pages_per_seq + pos / page_size], 0), num_pages - 1);
+  __nv_bfloat16* dst = cache + (static_cast<size_t>(page) * page_size + pos % page_size) * Hkv * 2 * DEC_D;
+  const uint4* k = reinterpret_cast<const uint4*>(keys + static_cast<size_t>(t) * Hkv * DEC_D);
+  const uint4* v = reinterpret_cast<const uint4*>(values + static_cast<size_t>(t) * Hkv * DEC_D);
+  for (int u = threadIdx.x; u < Hkv * DEC_D / 8; u += blockDim.x) {
+    const int h = u / (DEC_D / 8), d = (u % (DEC_D / 8)) * 8;
+    *reinterpret_cast<uint4*>(dst + h * 2 * DEC_D + d) = k[u];
+    *reinterpret_cast<uint4*>(dst + h * 2 * DEC_D + DEC_D + d) = v[u];
+  }
+}
+
+// lengths[s] = kv_lens[s] for the decode sequences, 0 for the others (which then take one empty step).
+__global__ void rpa_decode_lengths_kernel(const int32_t* __restrict__ kv_lens, const int32_t* __restrict__ distribution,
+                                          int32_t* __restrict__ lengths, int n, int max_len) {
+  const int s = blockIdx.x * blockDim.x + threadIdx.x;
+  if (s < n) lengths[s] = s < distribution[0] ? min(max(kv_lens[s], 0), max_len) : 0;
+}
+
+// out[s] = result[s] for the decode tokens (one CTA per token, 16 bytes per thread per pass); other rows keep q.
+__global__ void __launch_bounds__(128)
+    rpa_decode_scatter_kernel(const __nv_bfloat16* __restrict__ result, __nv_bfloat16* __restrict__ out,
+                              const int32_t* __restrict__ distribution, int row_elements) {
+  const int s = blockIdx.x;
+  if (s >= distribution[0]) return;
+  const uint4* src = reinterpret_cast<const uint4*>(result + static_cast<size_t>(s) * row_elements);
+  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(s) * row_elements);
+  for (int u = threadIdx.x; u < row_elements / 8; u += blockDim.x) dst[u] = src[u];
+}
+
+struct RpaScratch {
+  int32_t *lengths, *step_tile, *step_code, *step_count, *tile_first;
+  __nv_bfloat16* result;
+  void* decode;
+  size_t bytes;
+};
+
+static RpaScratch rpa_scratch(void* workspace, int n, int H, int pages_per_seq) {
+  uint8_t* w = static_cast<uint8_t*>(workspace);
+  size_t at = 0;
+  auto take = [&](size_t bytes) {
+    uint8_t* ptr = w == nullptr ? nullptr : w + at;
+    at += align256(bytes);
+    return ptr;
+  };
+  RpaScratch r{};
+  r.lengths = reinterpret_cast<int32_t*>(take(static_cast<size_t>(n) * 4));
+  r.step_tile = reinterpret_cast<int32_t*>(take(static_cast<size_t>(n) * pages_per_seq * 4));
+  r.step_code = reinterpret_cast<int32_t*>(take(static_cast<size_t>(n) * pages_per_seq * 4));
+  r.step_count = reinterpret_cast<int32_t*>(take(4));
+  r.tile_first = reinterpret_cast<int32_t*>(take(static_cast<size_t>(n + 1) * 4));
+  r.result = reinterpret_cast<__nv_bfloat16*>(take(static_cast<size_t>(n) * H * DEC_D * 2));
+  r.decode = take(decode_scratch_bytes(n, 1, H, DEC_D, pages_per_seq));
+  r.bytes = at;
+  return r;
+}
+
+}  // namespace tjx
+
+extern "C" {
+
+int tjx_rpa_write_bf16(void* kv_cache, const void* keys, const void* values, const int32_t* kv_lens,
+                       const int32_t* page_indices, const int32_t* cu_q_lens, const int32_t* distribution, int T,
+                       int S, int Hkv, int D, int page_size, int pages_per_seq, int num_pages, tjx_stream_t stream) {
+  using namespace tjx;
+  if (int rc = check_device()) return rc;
+  if (!kv_cache || !keys || !values || !kv_lens || !page_indices || !cu_q_lens || !distribution)
+    return fail(TJX_E_ARG, "an input pointer is null");
+  if (T <= 0 || S <= 0 || Hkv <= 0 || page_size <= 0 || pages_per_seq <= 0 || num_pages <= 0)
+    return fail(TJX_E_ARG, "sizes must be positive");
+  if (D != DEC_D) return fail(TJX_E_ARG, "head dimension must be 128");
+  const uintptr_t ptrs[] = {reinterpret_cast<uintptr_t>(kv_cache), reinterpret_cast<uintptr_t>(keys),
+                            reinterpret_cast<uintptr_t>(values)};
+  for (uintptr_t a : ptrs)
+    if (a & 15u) return fail(TJX_E_ARG, "kv_cache, keys and values must be 16-byte aligned");
+  rpa_write_kernel<<<T, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(kv_cache), static_cast<const __nv_bfloat16*>(keys),
+      static_cast<const __nv_bfloat16*>(values), kv_lens, page_indices, cu_q_lens, distribution, S, Hkv, page_size,
+      pages_per_seq, num_pages);
+  TJX_CUDA(cudaGetLastError());
+  return 0;
+}
+
+size_t tjx_rpa_decode_workspace_bytes(int T, int S, int H, int D, int pages_per_seq) {
+  if (T <= 0 || S <= 0 || H <= 0 || D <= 0 || pages_per_seq <= 0) return 0;
+  return tjx::rpa_scratch(nullptr, std::min(S, T), H, pages_per_seq).bytes;
+}
+
+int tjx_rpa_decode_bf16(const void* q, void* out, const void* kv_cache, const int32_t* kv_lens,
+                        const int32_t* page_indices, const int32_t* distribution, int T, int S, int H, int Hkv, int D,
+                        int page_size, int pages_per_seq, int num_pages, float sm_scale, void* workspace,
+                        size_t workspace_bytes, tjx_stream_t stream) {
+  using namespace tjx;
+  if (int rc = check_device()) return rc;
+  if (!kv_lens || !page_indices || !distribution) return fail(TJX_E_ARG, "an index array pointer is null");
+  const int n = std::min(S, T);  // sequence s is token s
+  const size_t need = tjx_rpa_decode_workspace_bytes(T, S, H, D, pages_per_seq);
+  if (T <= 0 || S <= 0 || need == 0) return fail(TJX_E_ARG, "sizes must be positive");
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(TJX_E_ARG, "workspace is null or smaller than tjx_rpa_decode_workspace_bytes");
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(TJX_E_ARG, "workspace must be 256-byte aligned");
+  const RpaScratch w = rpa_scratch(workspace, n, H, pages_per_seq);
+  const __nv_bfloat16* cache = static_cast<const __nv_bfloat16*>(kv_cache);
+  if (int rc = check_decode_args(q, cache, cache == nullptr ? nullptr : cache + DEC_D, page_indices, w.lengths, out, n, 1,
+                                 H, Hkv, D, page_size, pages_per_seq, num_pages, w.step_tile, w.step_code, w.step_count,
+                                 w.tile_first))
+    return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (out != q)  // rows that are not decode tokens keep the query
+    TJX_CUDA(cudaMemcpyAsync(out, q, static_cast<size_t>(T) * H * DEC_D * 2, cudaMemcpyDeviceToDevice, s));
+  rpa_decode_lengths_kernel<<<(n + 127) / 128, 128, 0, s>>>(kv_lens, distribution, w.lengths, n,
+                                                            pages_per_seq * page_size);
+  TJX_CUDA(cudaGetLastError());
+  if (int rc = run_decode(q, cache, cache + DEC_D, page_indices, w.lengths, w.result, n, 1, H, Hkv, page_size,
+                          pages_per_seq, num_pages, w.step_tile, w.step_code, w.step_count, w.tile_first, w.decode, s,
+                          sm_scale, 2 * DEC_D, static_cast<long long>(Hkv) * 2 * DEC_D))
+    return rc;
+  rpa_decode_scatter_kernel<<<n, 128, 0, s>>>(w.result, static_cast<__nv_bfloat16*>(out), distribution, H * DEC_D);
+  TJX_CUDA(cudaGetLastError());
+  return 0;
 }
 
 }  // extern "C"

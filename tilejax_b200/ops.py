@@ -437,6 +437,73 @@ def mla_decode(q_c: torch.Tensor, q_r: torch.Tensor, c_kv: torch.Tensor, k_rope:
     return out
 
 
+# ------------------------------------------------------------------------------------------ ragged paged attention
+
+
+def _rpa_sizes(kv_cache: torch.Tensor, kv_lens: torch.Tensor, page_indices: torch.Tensor) -> tuple[int, ...]:
+    if kv_cache.dim() != 5 or kv_cache.shape[3] != 2 or kv_cache.dtype != torch.bfloat16:
+        raise ValueError("the cache is (pages, page_size, Hkv, 2, D) bfloat16: each head's key and value side by side")
+    num_pages, page_size, Hkv, _, D = kv_cache.shape
+    S = kv_lens.shape[0]
+    if page_indices.dim() != 1 or S == 0 or page_indices.shape[0] % S:
+        raise ValueError("page_indices is (S * pages_per_seq,), sequence s's pages at s * pages_per_seq")
+    if any(t.dtype != torch.int32 for t in (kv_lens, page_indices)):
+        raise ValueError("kv_lens and page_indices must be int32")
+    return num_pages, page_size, Hkv, D, S, page_indices.shape[0] // S
+
+
+def rpa_write(kv_cache: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, kv_lens: torch.Tensor,
+              page_indices: torch.Tensor, cu_q_lens: torch.Tensor, distribution: torch.Tensor) -> torch.Tensor:
+    """`write_new_tokens` (examples/ragged_paged_attention.py:74-79): the step's new keys and values (T, Hkv, D)
+    written IN PLACE into the cache at positions [kv_len - q_len, kv_len) of their sequences; returns the cache."""
+    num_pages, page_size, Hkv, D, S, pps = _rpa_sizes(kv_cache, kv_lens, page_indices)
+    device = _need_cuda(kv_cache, keys, values, kv_lens, page_indices, cu_q_lens, distribution)
+    if keys.shape != values.shape or keys.dim() != 3 or keys.shape[1:] != (Hkv, D) or keys.dtype != torch.bfloat16 \
+            or values.dtype != torch.bfloat16:
+        raise ValueError("keys and values are (T, Hkv, D) bfloat16")
+    if cu_q_lens.shape != (S + 1,) or distribution.shape != (3,) or cu_q_lens.dtype != torch.int32 \
+            or distribution.dtype != torch.int32:
+        raise ValueError("cu_q_lens is int32 (S + 1,), distribution int32 (3,)")
+    with torch.cuda.device(device):
+        check(library().tjx_rpa_write_bf16(_ptr(kv_cache), _ptr(keys), _ptr(values), _ptr(kv_lens), _ptr(page_indices),
+                                           _ptr(cu_q_lens), _ptr(distribution), keys.shape[0], S, Hkv, D, page_size, pps,
+                                           num_pages, _stream()))
+    return kv_cache
+
+
+_rpa_workspaces: dict[tuple, torch.Tensor] = {}
+
+
+def rpa_decode(q: torch.Tensor, kv_cache: torch.Tensor, kv_lens: torch.Tensor, page_indices: torch.Tensor,
+               distribution: torch.Tensor, sm_scale: float = 1.0, out: torch.Tensor | None = None) -> torch.Tensor:
+    """`rpa_decode` (examples/ragged_paged_attention.py:121-149): q (T, H, D); sequence s < distribution[0] is token
+    s, whose row becomes its attention output over the kv_lens[s] cached positions (scores times sm_scale); every
+    other row stays the query. `out=q` updates the queries in place, as the reference's donated buffer is."""
+    num_pages, page_size, Hkv, D, S, pps = _rpa_sizes(kv_cache, kv_lens, page_indices)
+    device = _need_cuda(q, kv_cache, kv_lens, page_indices, distribution)
+    if q.dim() != 3 or q.shape[2] != D or q.dtype != torch.bfloat16:
+        raise ValueError("q is (T, H, D) bfloat16")
+    if distribution.shape != (3,) or distribution.dtype != torch.int32:
+        raise ValueError("distribution is int32 (3,)")
+    T, H, _ = q.shape
+    if out is None:
+        out = torch.empty_like(q)
+    elif out.shape != q.shape or out.dtype != q.dtype or not out.is_contiguous() or out.device != q.device:
+        raise ValueError("out must look like q")
+    with torch.cuda.device(device):
+        need = int(library().tjx_rpa_decode_workspace_bytes(T, S, H, D, pps))
+        key = (str(device), need)
+        ws = _rpa_workspaces.get(key)
+        if ws is None:
+            _rpa_workspaces.clear()
+            ws = _rpa_workspaces[key] = torch.empty(need + 256, dtype=torch.uint8, device=device)
+        ws_ptr = (ws.data_ptr() + 255) & ~255
+        check(library().tjx_rpa_decode_bf16(_ptr(q), _ptr(out), _ptr(kv_cache), _ptr(kv_lens), _ptr(page_indices),
+                                            _ptr(distribution), T, S, H, Hkv, D, page_size, pps, num_pages,
+                                            float(sm_scale), ctypes.c_void_p(ws_ptr), need, _stream()))
+    return out
+
+
 def paged_gqa_decode_static(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_tables: torch.Tensor,
                             lengths: torch.Tensor, out: torch.Tensor, step_tile: torch.Tensor, step_code: torch.Tensor,
                             step_count: torch.Tensor, tile_first: torch.Tensor) -> torch.Tensor:
