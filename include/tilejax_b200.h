@@ -216,12 +216,28 @@ size_t tjx_rpa_decode_workspace_bytes(int T, int S, int H, int D, int pages_per_
  * row of out [T, H, D] is q's (out may be q: the update in place the reference's donated buffer gets). Runs the paged
  * decode kernel of tjx_paged_gqa_decode_bf16 on the cache's own layout (two tensor maps over the one buffer).
  *   workspace: at least tjx_rpa_decode_workspace_bytes(...) bytes, 256-byte aligned
- * Constraints: D == 128; H / Hkv in {1, 2, 4, 8}; page_size a multiple of 16. The prefill / mixed case
- * (`rpa_prefill`, :196-243) has no entry point. */
+ * Constraints: D == 128; H / Hkv in {1, 2, 4, 8}; page_size a multiple of 16. */
 int tjx_rpa_decode_bf16(const void* q, void* out, const void* kv_cache, const int32_t* kv_lens,
                         const int32_t* page_indices, const int32_t* distribution, int T, int S, int H, int Hkv, int D,
                         int page_size, int pages_per_seq, int num_pages, float sm_scale, void* workspace,
                         size_t workspace_bytes, tjx_stream_t stream);
+
+/* Bytes of scratch tjx_rpa_prefill_bf16 needs for these sizes (its tile arrays). */
+size_t tjx_rpa_prefill_workspace_bytes(int T, int S);
+
+/* Ragged paged attention, the prefill and mixed cases (`rpa_prefill` with its tiles,
+ * examples/ragged_paged_attention.py:196-275): every sequence s in [distribution[0], distribution[2]) has
+ * q_len = cu_q_lens[s + 1] - cu_q_lens[s] new tokens at cache positions [kv_lens[s] - q_len, kv_lens[s]); each attends
+ * causally over its sequence's cache (the new tokens already written), scores scaled by sm_scale; the outputs replace
+ * those tokens' rows of out [T, H, D], every other row of out is q's (out may be q). The tiles (here blocks of 128
+ * queries; the reference's are 256) are built on the device; the kernel is the causal attention kernel's paged
+ * instantiation: a unit is (tile, KV head, two of its query heads), a block one page.
+ *   workspace: at least tjx_rpa_prefill_workspace_bytes(T, S) bytes, 256-byte aligned
+ * Constraints: D == 128; page_size == 128; H / Hkv even. */
+int tjx_rpa_prefill_bf16(const void* q, void* out, const void* kv_cache, const int32_t* kv_lens,
+                         const int32_t* page_indices, const int32_t* cu_q_lens, const int32_t* distribution, int T,
+                         int S, int H, int Hkv, int D, int page_size, int pages_per_seq, int num_pages, float sm_scale,
+                         void* workspace, size_t workspace_bytes, tjx_stream_t stream);
 
 /* Which kernel tjx_mla_decode_bf16 launches from now on: 1 (the default) the tcgen05 kernel, 64 rows per CTA with
  * scores and output in TMEM; 0 the warp-level MMA kernel, 16 rows per CTA. An A/B switch for measurements: the two

@@ -130,3 +130,73 @@ def rpa_decode_f64(q, kv_cache, kv_lens, page_indices, distribution, sm_scale: f
             w = np.exp(sc - sc.max())
             out[s, h] = (w / w.sum()) @ kv[:, h // G, 1, :]
     return out
+
+
+BLOCK_Q = 256  # examples/ragged_paged_attention.py:154
+
+
+def rpa_prefill_ref(q, kv_cache, kv_lens, page_indices, cu_q_lens, distribution, sm_scale: float, pages_per_step: int = 4):
+    """examples/ragged_paged_attention.py:196-275, tile by tile and step by step: a tile is a block of up to 256 new
+    tokens of a sequence in [distribution[0], distribution[2]) (`prefill_tiles`, :252-275), its first token at cache
+    position kv_len - q_len + 256 b; a step is `pages_per_step` pages (:219); scores `s * sm_scale` in f32 (:232),
+    a query at position p sees the positions up to p (`visible`, :172-181); `online_softmax_heads` (:184-193) with P
+    rounded to the cache dtype before P @ v; rows not in a tile keep q."""
+    T, H, D = q.shape
+    ps, Hkv = kv_cache.shape[1], kv_cache.shape[2]
+    G = H // Hkv
+    S = kv_lens.shape[0]
+    pps = page_indices.shape[0] // S
+    dtype = q.dtype
+    out = np.array(q, copy=True)
+    scale = np.float32(sm_scale)
+    for s in range(int(distribution[0]), min(S, int(distribution[2]))):
+        first, q_len = int(cu_q_lens[s]), int(cu_q_lens[s + 1] - cu_q_lens[s])
+        for b0 in range(0, q_len, BLOCK_Q):
+            rows = min(BLOCK_Q, q_len - b0)
+            pos0 = int(kv_lens[s]) - q_len + b0
+            stop = pos0 + rows
+            qt = np.asarray(q[first + b0 : first + b0 + rows]).astype(np.float32)  # (rows, H, D)
+            row_max = np.full((H, rows, 1), MASK_VALUE, np.float32)
+            row_sum = np.zeros((H, rows, 1), np.float32)
+            acc = np.zeros((H, rows, D), np.float32)
+            pos = pos0 + np.arange(rows)[:, None]
+            for j in range(0, stop, pages_per_step * ps):
+                pages = [int(page_indices[s * pps + min(j // ps + x, pps - 1)]) for x in range(pages_per_step)]
+                kv = np.concatenate([np.asarray(kv_cache[pg]).astype(np.float32) for pg in pages])  # (NP * ps, Hkv, 2, D)
+                col = j + np.arange(kv.shape[0])[None, :]
+                ok = (col <= pos) & (col < stop)
+                sc = np.stack([np.where(ok, (qt[:, h, :] @ kv[:, h // G, 0, :].T) * scale, MASK_VALUE) for h in range(H)])
+                max_new = np.maximum(row_max, sc.max(axis=2, keepdims=True))
+                pr = np.exp(sc - max_new)
+                alpha = np.exp(row_max - max_new)
+                row_sum = alpha * row_sum + pr.sum(axis=2, keepdims=True, dtype=np.float32)
+                prb = pr.astype(dtype).astype(np.float32)
+                acc = alpha * acc + np.stack([prb[h] @ kv[:, h // G, 1, :] for h in range(H)])
+                row_max = max_new
+            o = acc * (np.float32(1.0) / np.maximum(row_sum, np.float32(1e-30)))
+            out[first + b0 : first + b0 + rows] = o.transpose(1, 0, 2).astype(dtype)
+    return out
+
+
+def rpa_prefill_f64(q, kv_cache, kv_lens, page_indices, cu_q_lens, distribution, sm_scale: float) -> np.ndarray:
+    """Independent check in float64: dense causal softmax of every new token of the prefill / mixed sequences over
+    its sequence's cached positions up to its own."""
+    T, H, D = q.shape
+    ps, Hkv = kv_cache.shape[1], kv_cache.shape[2]
+    G = H // Hkv
+    S = kv_lens.shape[0]
+    pps = page_indices.shape[0] // S
+    out = np.asarray(q).astype(np.float64)
+    for s in range(int(distribution[0]), min(S, int(distribution[2]))):
+        first, q_len, n = int(cu_q_lens[s]), int(cu_q_lens[s + 1] - cu_q_lens[s]), int(kv_lens[s])
+        if q_len == 0:
+            continue
+        pages = [int(page_indices[s * pps + x]) for x in range((n + ps - 1) // ps)]
+        kv = np.concatenate([np.asarray(kv_cache[pg]).astype(np.float64) for pg in pages])[:n]
+        for i in range(q_len):
+            seen = n - q_len + i + 1
+            for h in range(H):
+                sc = kv[:seen, h // G, 0, :] @ np.asarray(q[first + i, h]).astype(np.float64) * sm_scale
+                w = np.exp(sc - sc.max())
+                out[first + i, h] = (w / w.sum()) @ kv[:seen, h // G, 1, :]
+    return out

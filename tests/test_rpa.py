@@ -58,3 +58,21 @@ def test_decode_oracle_against_float64():
     page = inp["page_indices"][0]
     for h in range(8):
         np.testing.assert_array_equal(got[0, h].view(np.uint16), cache[page, 0, h // 4, 1].view(np.uint16))
+
+
+def test_prefill_oracle_against_float64():
+    inp = oracle.rpa_inputs([1, 1, 300, 7, 130], [513, 1, 300, 135, 400], heads=4, kv_heads=2, max_len=1024,
+                            max_tokens=448, max_seqs=8, seed=3)
+    cache = oracle.rpa_write_ref(inp["kv_cache"], inp["keys"], inp["values"], inp["kv_lens"], inp["page_indices"],
+                                 inp["cu_q_lens"], inp["distribution"])
+    scale = 128**-0.5
+    args = (inp["q"], cache, inp["kv_lens"], inp["page_indices"], inp["cu_q_lens"], inp["distribution"], scale)
+    got = oracle.rpa_prefill_ref(*args)
+    want = oracle.rpa_prefill_f64(*args)
+    assert np.abs(got.astype(np.float64) - want).max() <= 2e-2
+    # Steps of one page or of four: the same attention.
+    one = oracle.rpa_prefill_ref(*args, pages_per_step=1)
+    assert np.abs(one.astype(np.float64) - got.astype(np.float64)).max() <= 2e-2
+    # The decode tokens and the padding rows keep the query.
+    np.testing.assert_array_equal(got[:2].view(np.uint16), inp["q"][:2].view(np.uint16))
+    np.testing.assert_array_equal(got[439:].view(np.uint16), inp["q"][439:].view(np.uint16))

@@ -73,3 +73,56 @@ def test_bad_arguments_are_errors():
     with pytest.raises(NativeError, match="head dimension must be 128"):
         ops.rpa_decode(torch.zeros(3, 32, 64, dtype=torch.bfloat16, device="cuda"), cache64, dev["kv_lens"],
                        dev["page_indices"], dev["distribution"])
+
+
+@pytest.mark.parametrize(("q_lens", "kv_lens", "sizes"), [
+    ([1, 1, 300, 7, 130], [513, 1, 300, 135, 400], dict(max_len=1024, max_tokens=448, max_seqs=8, seed=3)),
+    ([128, 129, 1], [128, 1000, 1], dict(heads=8, kv_heads=4, max_len=1024)),   # a whole block; a prefix of 871; then...
+    ([5], [5], dict(heads=4, kv_heads=2, max_len=256)),                           # fewer rows than a tile
+    ([700, 3], [2048, 1500], dict(heads=16, kv_heads=2, max_len=2048)),           # chunked prefill deep in the cache
+])
+def test_prefill_matches_the_oracle_and_float64(q_lens, kv_lens, sizes):
+    if q_lens == [128, 129, 1]:
+        q_lens, kv_lens = [1, 128, 129], [1, 128, 1000]  # decode sequences come first in the ABI
+    inp, dev = step(q_lens, kv_lens, **sizes)
+    cache = ops.rpa_write(*(dev[n] for n in NAMES))
+    scale = 128**-0.5
+    args = (dev["q"], cache, dev["kv_lens"], dev["page_indices"], dev["cu_q_lens"], dev["distribution"], scale)
+    got = to_host(ops.rpa_prefill(*args))
+    assert ops.device_status() == 0
+    host = (inp["q"], to_host(cache), inp["kv_lens"], inp["page_indices"], inp["cu_q_lens"], inp["distribution"], scale)
+    want = oracle.rpa_prefill_ref(*host)
+    exact = oracle.rpa_prefill_f64(*host)
+    assert np.abs(f64(got) - f64(want)).max() <= 2e-2
+    assert np.abs(f64(got) - exact).max() <= 2e-2
+    d0, tokens = int(inp["distribution"][0]), int(inp["cu_q_lens"][-1])
+    np.testing.assert_array_equal(got[:d0].view(np.uint16), inp["q"][:d0].view(np.uint16))      # decode rows: untouched
+    np.testing.assert_array_equal(got[tokens:].view(np.uint16), inp["q"][tokens:].view(np.uint16))  # padding rows
+    in_place = dev["q"].clone()
+    same = ops.rpa_prefill(in_place, *args[1:], out=in_place)
+    np.testing.assert_array_equal(to_host(same).view(np.uint16), got.view(np.uint16))
+
+
+def test_the_whole_step_is_write_then_decode_then_prefill():
+    inp, dev = step([1, 1, 1, 200, 64], [900, 1, 257, 200, 700], max_len=1024, max_tokens=320, max_seqs=8, seed=9)
+    scale = 128**-0.5
+    out, cache = ops.ragged_paged_attention(dev["q"], dev["keys"], dev["values"], dev["kv_cache"], dev["kv_lens"],
+                                            dev["page_indices"], dev["cu_q_lens"], dev["distribution"], scale)
+    assert ops.device_status() == 0
+    want_cache = oracle.rpa_write_ref(*(inp[n] for n in NAMES))
+    np.testing.assert_array_equal(to_host(cache).view(np.uint16), want_cache.view(np.uint16))
+    want = oracle.rpa_decode_f64(inp["q"], want_cache, inp["kv_lens"], inp["page_indices"], inp["distribution"], scale)
+    pre = oracle.rpa_prefill_f64(inp["q"], want_cache, inp["kv_lens"], inp["page_indices"], inp["cu_q_lens"],
+                                 inp["distribution"], scale)
+    want[3:] = pre[3:]
+    assert np.abs(f64(to_host(out)) - want).max() <= 2e-2
+    np.testing.assert_array_equal(to_host(dev["q"]).view(np.uint16), inp["q"].view(np.uint16))  # q itself is left alone
+
+
+def test_prefill_limits_are_errors():
+    inp, dev = step([4], [4], heads=4, kv_heads=4, max_len=256)  # one query head per KV head
+    with pytest.raises(NativeError, match="even number of query heads per KV head"):
+        ops.rpa_prefill(dev["q"], dev["kv_cache"], dev["kv_lens"], dev["page_indices"], dev["cu_q_lens"], dev["distribution"])
+    inp, dev = step([4], [4], heads=4, kv_heads=2, max_len=256, page_size=64)
+    with pytest.raises(NativeError, match="pages of 128 positions"):
+        ops.rpa_prefill(dev["q"], dev["kv_cache"], dev["kv_lens"], dev["page_indices"], dev["cu_q_lens"], dev["distribution"])

@@ -60,6 +60,16 @@ struct AttnParams {
   float* out_heads;    // (B, S, H * D) f32: the heads side by side, unrounded (attention_block's `a`), or null
   int* status;
   long long* profile;  // per-CTA counters (PROFILE_WORDS each) or null
+  // The paged variant (ragged paged attention's prefill case): tiles of up to 128 query tokens of one sequence.
+  const int32_t* tile_row0;      // [tiles] first token (row of q (T, H, D)) of each tile
+  const int32_t* tile_rows;      // [tiles] its tokens (1..128)
+  const int32_t* tile_pos;       // [tiles] cache position of its first token
+  const int32_t* tile_page;      // [tiles] index into page_indices of its sequence's first page
+  const int32_t* n_tiles;        // [1]
+  const int32_t* page_indices;
+  int Hkv, group, num_pages;     // KV heads, query heads per KV head (even), pages in the pool
+  float scale_log2e;             // log2(e) times the softmax scale (the queries do not arrive pre-scaled)
+  __nv_bfloat16* out_tokens;     // (T, H, D): row (token, head)
 };
 
 constexpr int AT_MAX_TILES = 1024;  // user query tiles per (b, h) whose last key block is cached in shared memory
@@ -128,9 +138,14 @@ __device__ __forceinline__ int slot_blocks(const AttnParams& p, const int* last_
   return keys / AT_BKV;
 }
 
+// PAGED: ragged paged attention's prefill case on the same pipeline. A unit is (tile of up to 128 query tokens of one
+// sequence, KV head, pair of that KV head's query heads): the two slots are two query heads over the same tokens, so
+// they share every K / V block as the two query tiles of the dense kernel do; a block is one 128-position page of the
+// cache (pages, 128, Hkv, 2, D), found through page_indices; the tile's first token sits at cache position
+// tile_pos and token r sees the positions up to tile_pos + r; the outputs replace the queries' rows.
 // PROFILE: the instantiation a launch with a profile buffer runs; it alone reads the clock and keeps the counters
 // (they cost the softmax warps registers they do not have to spare: 7 % of the kernel's time when always on).
-template <bool PROFILE>
+template <bool PROFILE, bool PAGED>
 __global__ void __launch_bounds__(AT_THREADS, 1)
     attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                      const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
@@ -159,10 +174,12 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
   const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
   const int bh_count = p.B * p.H;
   const int n_ctas = static_cast<int>(gridDim.x), cta = static_cast<int>(blockIdx.x);
+  const int pairs_per_tile = PAGED ? p.Hkv * (p.group / 2) : 1;
+  const int total_units = PAGED ? __shfl_sync(0xFFFFFFFFu, p.n_tiles[0], 0) * pairs_per_tile : p.total_units;
   // The k-th unit of this CTA in the heaviest-first list (later query tiles attend to more keys), or -1.
   auto unit_at = [&](int k) {
     const int i = k * n_ctas + ((k & 1) ? n_ctas - 1 - cta : cta);
-    return i < p.total_units ? i : -1;
+    return i < total_units ? i : -1;
   };
 
   long long* prof = !PROFILE || p.profile == nullptr ? nullptr
@@ -179,12 +196,14 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
     tma_prefetch_desc(&map_k);
     tma_prefetch_desc(&map_v);
   }
-  // Last key block the step table lists for each user query tile (-1: none).
-  for (int i = threadIdx.x; i < p.pattern_tiles; i += AT_THREADS) last_block[i] = -1;
-  __syncthreads();
-  for (int s = threadIdx.x; s < p.pattern_steps; s += AT_THREADS) {
-    const int code = p.step_code[s], tile = p.step_tile[s];
-    if (!(code & 4) && tile >= 0 && tile < p.pattern_tiles) atomicMax(&last_block[tile], code >> 3);
+  if (!PAGED) {
+    // Last key block the step table lists for each user query tile (-1: none).
+    for (int i = threadIdx.x; i < p.pattern_tiles; i += AT_THREADS) last_block[i] = -1;
+    __syncthreads();
+    for (int s = threadIdx.x; s < p.pattern_steps; s += AT_THREADS) {
+      const int code = p.step_code[s], tile = p.step_tile[s];
+      if (!(code & 4) && tile >= 0 && tile < p.pattern_tiles) atomicMax(&last_block[tile], code >> 3);
+    }
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_holder)), 512);
@@ -198,9 +217,21 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
   // What every role derives for a unit, identically.
   struct Unit {
     int row_base, q0[2], n_slot[2], n_blocks;
+    int tok0, rows, head[2], kv_head, page0;  // paged: the tile's first token and tokens, the slots' query heads, ...
   };
   auto describe = [&](int i) {
     Unit u;
+    if (PAGED) {
+      const int tile = i / pairs_per_tile, rem = i % pairs_per_tile;
+      u.kv_head = rem / (p.group / 2);
+      u.head[0] = u.kv_head * p.group + 2 * (rem % (p.group / 2)), u.head[1] = u.head[0] + 1;
+      u.tok0 = p.tile_row0[tile], u.rows = p.tile_rows[tile], u.page0 = p.tile_page[tile];
+      u.q0[0] = u.q0[1] = p.tile_pos[tile];  // the cache position of the slots' first row
+      u.row_base = 0;
+      u.n_slot[0] = u.n_slot[1] = u.n_blocks = (u.q0[0] + u.rows + AT_BKV - 1) / AT_BKV;
+      return u;
+    }
+    u.tok0 = u.rows = u.head[0] = u.head[1] = u.kv_head = u.page0 = 0;
     const int unit = p.units_per_bh - 1 - i / bh_count;
     const int bh = i % bh_count;
     u.row_base = bh * p.S;  // row of (b, h, 0) in the [B * H * S, D] view
@@ -231,8 +262,13 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
           ++used[t];
           const uint32_t dst = base + L::Q_OFF + t * L::TILE_BYTES;
           mbar_expect_tx(q_full(t), L::TILE_BYTES);
-          tma_load_2d(dst, &map_q, 0, u.row_base + u.q0[t], q_full(t));
-          tma_load_2d(dst + L::TILE_BYTES / 2, &map_q, 64, u.row_base + u.q0[t], q_full(t));
+          if (PAGED) {  // q as (D, H, T): 128 tokens of one head
+            tma_load_3d(dst, &map_q, 0, u.head[t], u.tok0, q_full(t));
+            tma_load_3d(dst + L::TILE_BYTES / 2, &map_q, 64, u.head[t], u.tok0, q_full(t));
+          } else {
+            tma_load_2d(dst, &map_q, 0, u.row_base + u.q0[t], q_full(t));
+            tma_load_2d(dst + L::TILE_BYTES / 2, &map_q, 64, u.row_base + u.q0[t], q_full(t));
+          }
         }
         for (int n = 0; n < u.n_blocks && ok; ++n, ++g) {
           const int stage = g % AT_STAGES;
@@ -243,17 +279,30 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
             break;
           }
           const uint32_t kd = base + L::K_OFF + stage * L::TILE_BYTES;
+          // Paged: block n is page page_indices[page0 + n] of the cache seen as (D, Hkv * 2, pages * 128), the key
+          // of KV head g at index 2 g of the middle dimension, its value at 2 g + 1.
+          const int page_row = PAGED ? min(max(p.page_indices[u.page0 + n], 0), p.num_pages - 1) * AT_BKV : 0;
           mbar_expect_tx(k_full(stage), L::TILE_BYTES);
-          tma_load_2d(kd, &map_k, 0, kv_row, k_full(stage));
-          tma_load_2d(kd + L::TILE_BYTES / 2, &map_k, 64, kv_row, k_full(stage));
+          if (PAGED) {
+            tma_load_3d(kd, &map_k, 0, 2 * u.kv_head, page_row, k_full(stage));
+            tma_load_3d(kd + L::TILE_BYTES / 2, &map_k, 64, 2 * u.kv_head, page_row, k_full(stage));
+          } else {
+            tma_load_2d(kd, &map_k, 0, kv_row, k_full(stage));
+            tma_load_2d(kd + L::TILE_BYTES / 2, &map_k, 64, kv_row, k_full(stage));
+          }
           if (!mbar_wait(v_empty(stage), ph ^ 1u, abort_flag, p.status, TJX_ERR_WAIT_EMPTY)) {
             ok = false;
             break;
           }
           const uint32_t vd = base + L::V_OFF + stage * L::TILE_BYTES;
           mbar_expect_tx(v_full(stage), L::TILE_BYTES);
-          tma_load_2d(vd, &map_v, 0, kv_row, v_full(stage));
-          tma_load_2d(vd + L::TILE_BYTES / 2, &map_v, 64, kv_row, v_full(stage));
+          if (PAGED) {
+            tma_load_3d(vd, &map_v, 0, 2 * u.kv_head + 1, page_row, v_full(stage));
+            tma_load_3d(vd + L::TILE_BYTES / 2, &map_v, 64, 2 * u.kv_head + 1, page_row, v_full(stage));
+          } else {
+            tma_load_2d(vd, &map_v, 0, kv_row, v_full(stage));
+            tma_load_2d(vd + L::TILE_BYTES / 2, &map_v, 64, kv_row, v_full(stage));
+          }
         }
       }
     }
@@ -403,6 +452,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
     const uint32_t o_tmem = tmem_base + lane_addr + 256 + t * 128;
     int done = 0;  // blocks of this slot in earlier units
     bool ok = true;
+    const float score_scale = PAGED ? p.scale_log2e : AT_LOG2E;  // scores to base-2 exponents
     long long sm_wait = 0, sm_busy = 0, sm_blocks = 0;
     int ph_ld = 0, ph_max = 0, ph_exp = 0;
     for (int k = 0; ok; ++k) {
@@ -456,7 +506,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
           }
         mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
       }
-      const float m_blk = mx * AT_LOG2E;
+      const float m_blk = mx * score_scale;
       if (n == 0) {
         m_used = m_blk;
       } else if (__any_sync(0xFFFFFFFFu, m_blk > m_used + AT_RESCALE_THRESHOLD)) {
@@ -490,7 +540,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
       // from the FMA pipe instead of the MUFU unit, which two softmax warps per scheduler would otherwise saturate.
       {
         float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
-        const float2 scale = make_float2(AT_LOG2E, AT_LOG2E), neg_m = make_float2(-m_used, -m_used);
+        const float2 scale = make_float2(score_scale, score_scale), neg_m = make_float2(-m_used, -m_used);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t pk[16];
@@ -529,7 +579,30 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
       } else {
         tc_fence_after_sync();
         const float inv = 1.0f / l;
-        if (p.out_heads != nullptr) {
+        if (PAGED) {
+          // Token tok0 + r, head head[t]: 256 contiguous bytes of (T, H, D); rows past the tile's tokens belong to
+          // other sequences and are not written (every lane still takes part in the TMEM loads).
+          const int r = q * 32 + lane;
+          uint4* dst = reinterpret_cast<uint4*>(
+              p.out_tokens + (static_cast<size_t>(u.tok0 + r) * p.H + u.head[t]) * AT_D);
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t v[32];
+            tmem_ld32(o_tmem + c * 32, v);
+            tmem_wait_ld();
+            if (r < u.rows) {
+#pragma unroll
+              for (int x = 0; x < 4; ++x) {
+                uint4 val;
+                val.x = pack_bf16(__uint_as_float(v[8 * x + 0]) * inv, __uint_as_float(v[8 * x + 1]) * inv);
+                val.y = pack_bf16(__uint_as_float(v[8 * x + 2]) * inv, __uint_as_float(v[8 * x + 3]) * inv);
+                val.z = pack_bf16(__uint_as_float(v[8 * x + 4]) * inv, __uint_as_float(v[8 * x + 5]) * inv);
+                val.w = pack_bf16(__uint_as_float(v[8 * x + 6]) * inv, __uint_as_float(v[8 * x + 7]) * inv);
+                dst[c * 4 + x] = val;
+              }
+            }
+          }
+        } else if (p.out_heads != nullptr) {
           // Row (b, s) of the (B * S, H * D) f32 matrix, columns h * D .. h * D + 127: 512 contiguous bytes.
           const int bh = u.row_base / p.S, b = bh / p.H, h = bh % p.H;
           float4* dst = reinterpret_cast<float4*>(
@@ -629,20 +702,147 @@ int attention_launch(const void* q, const void* k, const void* v, void* out, flo
   int dev = 0;
   TJX_CUDA(cudaGetDevice(&dev));
   if (!configured[dev & 63]) {
-    TJX_CUDA(cudaFuncSetAttribute(attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem::TOTAL));
-    TJX_CUDA(cudaFuncSetAttribute(attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem::TOTAL));
+    TJX_CUDA(cudaFuncSetAttribute(attention_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem::TOTAL));
+    TJX_CUDA(cudaFuncSetAttribute(attention_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem::TOTAL));
     configured[dev & 63] = true;
   }
   const int grid = std::min(p.total_units, sm_count());
   p.profile = profile_buffer(grid);
   if (p.profile != nullptr)
-    attention_kernel<true><<<grid, AT_THREADS, AttnSmem::TOTAL, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, p);
+    attention_kernel<true, false><<<grid, AT_THREADS, AttnSmem::TOTAL, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, p);
   else
-    attention_kernel<false><<<grid, AT_THREADS, AttnSmem::TOTAL, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, p);
+    attention_kernel<false, false><<<grid, AT_THREADS, AttnSmem::TOTAL, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, p);
   TJX_CUDA(cudaGetLastError());
   return 0;
 }
 }  // namespace tjx
+
+namespace tjx {
+
+// The prefill tiles of one step, on the device (what `prefill_tiles` computes in plain JAX,
+// examples/ragged_paged_attention.py:252-275, for blocks of 128 queries): a tile per block of 128 new tokens of each
+// sequence in [distribution[0], distribution[2]). One CTA; thread s handles sequences s, s + 256, ...; an exclusive
+// scan of the sequences' tile counts gives each its first tile.
+__global__ void __launch_bounds__(256)
+    rpa_prefill_tiles_kernel(const int32_t* __restrict__ kv_lens, const int32_t* __restrict__ cu_q_lens,
+                             const int32_t* __restrict__ distribution, int S, int pages_per_seq, int max_tiles,
+                             int32_t* __restrict__ tile_row0, int32_t* __restrict__ tile_rows,
+                             int32_t* __restrict__ tile_pos, int32_t* __restrict__ tile_page,
+                             int32_t* __restrict__ n_tiles) {
+  __shared__ int carry_sh, scan_sh[256];
+  if (threadIdx.x == 0) carry_sh = 0;
+  __syncthreads();
+  const int d0 = distribution[0], d2 = min(distribution[2], S);
+  for (int s0 = 0; s0 < S; s0 += 256) {
+    const int s = s0 + threadIdx.x;
+    const int q_len = s < S ? cu_q_lens[s + 1] - cu_q_lens[s] : 0;
+    const int mine = (s >= d0 && s < d2 && q_len > 0) ? (q_len + AT_BQ - 1) / AT_BQ : 0;
+    scan_sh[threadIdx.x] = mine;
+    __syncthreads();
+    for (int d = 1; d < 256; d <<= 1) {  // inclusive scan
+      const int y = threadIdx.x >= d ? scan_sh[threadIdx.x - d] : 0;
+      __syncthreads();
+      scan_sh[threadIdx.x] += y;
+      __syncthreads();
+    }
+    const int first = carry_sh + scan_sh[threadIdx.x] - mine;
+    for (int b = 0; b < mine; ++b) {
+      const int k = first + b;
+      if (k >= max_tiles) break;
+      tile_row0[k] = cu_q_lens[s] + b * AT_BQ;
+      tile_rows[k] = min(AT_BQ, q_len - b * AT_BQ);
+      tile_pos[k] = kv_lens[s] - q_len + b * AT_BQ;
+      tile_page[k] = s * pages_per_seq;
+    }
+    __syncthreads();
+    if (threadIdx.x == 255) carry_sh += scan_sh[255];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) n_tiles[0] = min(carry_sh, max_tiles);
+}
+
+static size_t attn_align256(size_t n) { return (n + 255) & ~static_cast<size_t>(255); }
+
+}  // namespace tjx
+
+extern "C" size_t tjx_rpa_prefill_workspace_bytes(int T, int S) {
+  if (T <= 0 || S <= 0) return 0;
+  const size_t max_tiles = static_cast<size_t>((T + tjx::AT_BQ - 1) / tjx::AT_BQ) + S;
+  return 4 * tjx::attn_align256(max_tiles * 4) + 256;
+}
+
+extern "C" int tjx_rpa_prefill_bf16(const void* q, void* out, const void* kv_cache, const int32_t* kv_lens,
+                                    const int32_t* page_indices, const int32_t* cu_q_lens,
+                                    const int32_t* distribution, int T, int S, int H, int Hkv, int D, int page_size,
+                                    int pages_per_seq, int num_pages, float sm_scale, void* workspace,
+                                    size_t workspace_bytes, tjx_stream_t stream) {
+  using namespace tjx;
+  if (int rc = check_device()) return rc;
+  if (!q || !out || !kv_cache || !kv_lens || !page_indices || !cu_q_lens || !distribution)
+    return fail(TJX_E_ARG, "an input or output pointer is null");
+  if (T <= 0 || S <= 0 || H <= 0 || Hkv <= 0 || pages_per_seq <= 0 || num_pages <= 0)
+    return fail(TJX_E_ARG, "sizes must be positive");
+  if (D != AT_D) return fail(TJX_E_ARG, "head dimension must be 128");
+  if (page_size != AT_BKV) return fail(TJX_E_ARG, "the prefill kernel takes pages of 128 positions");
+  if (H % Hkv != 0 || (H / Hkv) % 2 != 0)
+    return fail(TJX_E_ARG, "the prefill kernel takes an even number of query heads per KV head (two share each K / V block)");
+  if (static_cast<long long>(num_pages) * page_size >= (1ll << 31) || static_cast<long long>(T) * H >= (1ll << 31))
+    return fail(TJX_E_LIMIT, "num_pages * page_size and T * H must fit in int32");
+  const size_t need = tjx_rpa_prefill_workspace_bytes(T, S);
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(TJX_E_ARG, "workspace is null or smaller than tjx_rpa_prefill_workspace_bytes");
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(TJX_E_ARG, "workspace must be 256-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (out != q)  // rows no tile covers keep what q holds (the decode case's outputs among them)
+    TJX_CUDA(cudaMemcpyAsync(out, q, static_cast<size_t>(T) * H * AT_D * 2, cudaMemcpyDeviceToDevice, s));
+  const int max_tiles = (T + AT_BQ - 1) / AT_BQ + S;
+  uint8_t* w = static_cast<uint8_t*>(workspace);
+  const size_t stride = attn_align256(static_cast<size_t>(max_tiles) * 4);
+  AttnParams p{};
+  p.tile_row0 = reinterpret_cast<int32_t*>(w), p.tile_rows = reinterpret_cast<int32_t*>(w + stride);
+  p.tile_pos = reinterpret_cast<int32_t*>(w + 2 * stride), p.tile_page = reinterpret_cast<int32_t*>(w + 3 * stride);
+  p.n_tiles = reinterpret_cast<int32_t*>(w + 4 * stride);
+  rpa_prefill_tiles_kernel<<<1, 256, 0, s>>>(kv_lens, cu_q_lens, distribution, S, pages_per_seq, max_tiles,
+                                             const_cast<int32_t*>(p.tile_row0), const_cast<int32_t*>(p.tile_rows),
+                                             const_cast<int32_t*>(p.tile_pos), const_cast<int32_t*>(p.tile_page),
+                                             const_cast<int32_t*>(p.n_tiles));
+  TJX_CUDA(cudaGetLastError());
+  p.B = 1, p.H = H, p.S = 0, p.bq = p.bk = AT_BQ;
+  p.page_indices = page_indices, p.Hkv = Hkv, p.group = H / Hkv, p.num_pages = num_pages;
+  p.scale_log2e = AT_LOG2E * sm_scale;
+  p.out_tokens = static_cast<__nv_bfloat16*>(out);
+  p.status = device_status_word();
+  if (p.status == nullptr) return fail(TJX_E_CUDA, "could not locate the device status word");
+  // q (T, H, D) as (D, H, T); the cache (pages, 128, Hkv, 2, D) as (D, Hkv * 2, pages * 128). The queries are read from
+  // `out`: the rows the decode case has already replaced are not query tiles of this case.
+  CUtensorMap mq, mkv;
+  {
+    const uint64_t dims[3] = {AT_D, static_cast<uint64_t>(H), static_cast<uint64_t>(T)};
+    const uint64_t strides[2] = {AT_D * 2, static_cast<uint64_t>(H) * AT_D * 2};
+    const uint32_t box[3] = {64, 1, AT_BQ};
+    if (int rc = make_tensor_map(&mq, out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  }
+  {
+    const uint64_t dims[3] = {AT_D, static_cast<uint64_t>(Hkv) * 2, static_cast<uint64_t>(num_pages) * AT_BKV};
+    const uint64_t strides[2] = {AT_D * 2, static_cast<uint64_t>(Hkv) * 2 * AT_D * 2};
+    const uint32_t box[3] = {64, 1, AT_BKV};
+    if (int rc = make_tensor_map(&mkv, kv_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  }
+  static bool configured[64] = {};
+  int dev = 0;
+  TJX_CUDA(cudaGetDevice(&dev));
+  if (!configured[dev & 63]) {
+    TJX_CUDA(cudaFuncSetAttribute(attention_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem::TOTAL));
+    configured[dev & 63] = true;
+  }
+  const long long bound = static_cast<long long>(max_tiles) * Hkv * (p.group / 2);
+  const int grid = static_cast<int>(std::min<long long>(bound, sm_count()));
+  attention_kernel<false, true><<<grid, AT_THREADS, AttnSmem::TOTAL, s>>>(mq, mkv, mkv, p);
+  TJX_CUDA(cudaGetLastError());
+  return 0;
+}
 
 extern "C" int tjx_causal_attention_bf16(const void* q, const void* k, const void* v, void* out, int B, int H, int S,
                                          int D, int block_q, int block_kv, const int32_t* step_tile,

@@ -504,6 +504,47 @@ def rpa_decode(q: torch.Tensor, kv_cache: torch.Tensor, kv_lens: torch.Tensor, p
     return out
 
 
+def rpa_prefill(q: torch.Tensor, kv_cache: torch.Tensor, kv_lens: torch.Tensor, page_indices: torch.Tensor,
+                cu_q_lens: torch.Tensor, distribution: torch.Tensor, sm_scale: float = 1.0,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+    """`rpa_prefill` with its tiles (examples/ragged_paged_attention.py:196-275): the new tokens of every sequence in
+    [distribution[0], distribution[2]) attend causally over their sequence's cache; their rows of q (T, H, D) become the
+    outputs, every other row stays. `out=q` updates in place."""
+    num_pages, page_size, Hkv, D, S, pps = _rpa_sizes(kv_cache, kv_lens, page_indices)
+    device = _need_cuda(q, kv_cache, kv_lens, page_indices, cu_q_lens, distribution)
+    if q.dim() != 3 or q.shape[2] != D or q.dtype != torch.bfloat16:
+        raise ValueError("q is (T, H, D) bfloat16")
+    if cu_q_lens.shape != (S + 1,) or distribution.shape != (3,) or cu_q_lens.dtype != torch.int32 \
+            or distribution.dtype != torch.int32:
+        raise ValueError("cu_q_lens is int32 (S + 1,), distribution int32 (3,)")
+    T, H, _ = q.shape
+    if out is None:
+        out = torch.empty_like(q)
+    elif out.shape != q.shape or out.dtype != q.dtype or not out.is_contiguous() or out.device != q.device:
+        raise ValueError("out must look like q")
+    with torch.cuda.device(device):
+        need = int(library().tjx_rpa_prefill_workspace_bytes(T, S))
+        ws = torch.empty(need + 256, dtype=torch.uint8, device=device)
+        ws_ptr = (ws.data_ptr() + 255) & ~255
+        check(library().tjx_rpa_prefill_bf16(_ptr(q), _ptr(out), _ptr(kv_cache), _ptr(kv_lens), _ptr(page_indices),
+                                             _ptr(cu_q_lens), _ptr(distribution), T, S, H, Hkv, D, page_size, pps,
+                                             num_pages, float(sm_scale), ctypes.c_void_p(ws_ptr), need, _stream()))
+        ws.record_stream(torch.cuda.current_stream(device))
+    return out
+
+
+def ragged_paged_attention(q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, kv_cache: torch.Tensor,
+                           kv_lens: torch.Tensor, page_indices: torch.Tensor, cu_q_lens: torch.Tensor,
+                           distribution: torch.Tensor, sm_scale: float = 1.0) -> tuple[torch.Tensor, torch.Tensor]:
+    """RPA v3's step (`autokernel_rpa`, examples/ragged_paged_attention.py:279-290): the new tokens' keys and values
+    written into the cache in place, the decode sequences' attention, then the others'. Returns (out (T, H, D), the
+    cache); q is left as it was."""
+    cache = rpa_write(kv_cache, keys, values, kv_lens, page_indices, cu_q_lens, distribution)
+    out = rpa_decode(q, cache, kv_lens, page_indices, distribution, sm_scale)
+    out = rpa_prefill(out, cache, kv_lens, page_indices, cu_q_lens, distribution, sm_scale, out=out)
+    return out, cache
+
+
 def paged_gqa_decode_static(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_tables: torch.Tensor,
                             lengths: torch.Tensor, out: torch.Tensor, step_tile: torch.Tensor, step_code: torch.Tensor,
                             step_count: torch.Tensor, tile_first: torch.Tensor) -> torch.Tensor:
