@@ -448,6 +448,41 @@ def extra_workloads(device, pk: dict, pk_kind: str, only: str | None = None, ite
         except Exception as e:
             out[name] = {"error": str(e)[:200]}
 
+    if want("ragged_paged_attention"):
+        # One step of ragged paged attention in RPA v3's layout (examples/ragged_paged_attention.py:279-290): 32 decode
+        # sequences with caches uniform in 1..4096 and 4 prefill sequences of 1024 new tokens on a prefix of 1024,
+        # Llama-3-8B heads (32 / 8 x 128), pages of 128: the cache write, the decode case, the prefill case.
+        name = "ragged_paged_attention_decode32_prefill4x1024_H32_Hkv8_page128"
+        try:
+            rng = np.random.default_rng(0)
+            H, Hkv, D, ps, max_len = 32, 8, 128, 128, 4096
+            q_lens = [1] * 32 + [1024] * 4
+            kv_lens = [int(x) for x in rng.integers(1, 4097, 32)] + [2048] * 4
+            S, T, pps = len(q_lens), sum(q_lens), max_len // ps
+            used = [-(-n // ps) for n in kv_lens]
+            pages = sum(used) + 1
+            table = np.zeros((S, pps), np.int32)
+            pool, at = 1 + rng.permutation(pages - 1), 0
+            for i, n in enumerate(used):
+                table[i, :n] = pool[at:at + n]
+                at += n
+            cache = device_randn_bf16((pages, ps, Hkv, 2, D), 11, device)
+            qd = device_randn_bf16((T, H, D), 12, device)
+            kd2, vd2 = device_randn_bf16((T, Hkv, D), 13, device), device_randn_bf16((T, Hkv, D), 14, device)
+            dev = lambda a: torch.from_numpy(np.asarray(a, np.int32)).to(device)  # noqa: E731
+            lens_d, table_d = dev(kv_lens), dev(table.reshape(-1))
+            cu_d, dist_d = dev(np.concatenate([[0], np.cumsum(q_lens)])), dev([32, 32, S])
+            fn = lambda: ops.ragged_paged_attention(qd, kd2, vd2, cache, lens_d, table_d, cu_d, dist_d, D**-0.5)  # noqa: E731
+            ms = time_device(fn, iters, warm, flush)
+            seen = sum(q * (k - q) + q * (q + 1) // 2 for q, k in zip(q_lens[32:], kv_lens[32:], strict=True))
+            tensor_entry(name, ms, 4.0 * H * D * seen, extra={
+                "algorithmic_flops": "the prefill tokens' 4*H*D*(positions seen); the decode part reads "
+                                     f"{sum(kv_lens[:32]) * Hkv * 2 * D * 2 / 1e6:.0f} MB of cache",
+                "launches": "rpa_write, decode lengths + step tables + decode + scatter, prefill tiles + attention (paged)",
+                "new_tokens": T})
+        except Exception as e:
+            out[name] = {"error": str(e)[:200]}
+
     if want("mla_decode"):
         # The reference's MLA benchmark shape (benchmarks/decode.py:152-173): batch 32, contexts around 2048 of a
         # 4096-position cache, 64 heads, 512 latents + 64 RoPE columns (stored 128 wide), blocks of 512.
