@@ -371,7 +371,8 @@ def launch_key(plan: Plan, config: Config) -> tuple:
     same tiles and differ in nothing that can be timed. The matmul kernels walk K in their own blocks of 64 (`tk` is
     not part of the key) and only their single-CTA ring has a depth (`output_buffers` never is); the attention
     kernel works in 128 x 128 blocks cut at each tile's diagonal whatever the user's blocks; paged decode reads the
-    pages as they are; contiguous and MLA decode walk blocks of the chosen size."""
+    pages as they are; contiguous decode walks blocks of the chosen size; the MLA decode kernel shares the cache out in
+    its own units of 32 positions, whatever the block (which only shapes the caller's step tables)."""
     p = plan.params
     if plan.family == "gemm":
         return ("gemm", p["tm"], p["tn"], _stages(config.pipeline, p["tn"]), p["causal"], p["transposed"])
@@ -381,7 +382,9 @@ def launch_key(plan: Plan, config: Config) -> tuple:
         return ("attention",)
     if plan.family == "attention_block":
         return ("attention_block",)
-    if p.get("mla") or p.get("contiguous"):
+    if p.get("mla"):
+        return ("mla_decode",)
+    if p.get("contiguous"):
         return ("decode", p["page"])
     return ("decode",)
 
@@ -471,8 +474,9 @@ def _lower(plan: Plan, config: Config) -> tuple[str, Callable[..., Any]]:
             q, k, v, gamma, w_up, w_down, p["block_q"], p["block_kv"], p["block_f"], p["eps"])
     if p.get("mla"):
         text = header + (
-            f"kernel      tjx_mla_decode_bf16 (device step tables, CTA-wide TMA ring, warp-level MMA over 16 heads, "
-            f"partials merged by the last CTA to arrive)\n"
+            f"kernel      tjx_mla_decode_bf16 (tcgen05: 64 (token, head) rows per CTA, scores and output in TMEM, the "
+            f"cache shared out in units of 32 positions over persistent CTAs; partials merged by a second kernel; the "
+            f"device step tables are built beside it)\n"
             f"problem     {p['B']} sequences, {p['T']} new token(s), {p['H']} heads, {p['C']} latent + {p['R']} RoPE columns, blocks of "
             f"{p['page']} of {p['S']} cache positions\n"
             f"steps       at most {sch.steps}: step_tile / step_code / step_count are built on the device from lengths "
