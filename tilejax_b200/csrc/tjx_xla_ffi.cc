@@ -130,6 +130,78 @@ ffi::Error PagedGqaDecodeImpl(cudaStream_t stream, ffi::AnyBuffer q, ffi::AnyBuf
   return rc == 0 ? ffi::Error::Success() : Failed(rc);
 }
 
+// Scratch comes as a uint8 result of the entry point's `..._workspace_bytes` + 256 bytes; XLA aligns buffers, but the
+// offset to a 256-byte boundary is taken anyway. Returns null if the result is too small.
+void* Aligned(ffi::Result<ffi::AnyBuffer>& workspace, size_t need) {
+  const uintptr_t ws = reinterpret_cast<uintptr_t>(workspace->untyped_data());
+  const uintptr_t aligned = (ws + 255) & ~static_cast<uintptr_t>(255);
+  return workspace->size_bytes() < need + (aligned - ws) ? nullptr : reinterpret_cast<void*>(aligned);
+}
+
+// ------------------------------------------------------------------------------------------------ fused epilogues
+
+ffi::Error RmsnormGemmImpl(cudaStream_t stream, ffi::AnyBuffer x, ffi::AnyBuffer gamma, ffi::AnyBuffer w,
+                           ffi::Result<ffi::AnyBuffer> out, ffi::Result<ffi::AnyBuffer> workspace, int32_t tm,
+                           int32_t tn, int32_t tk, float eps) {
+  if (x.element_type() != ffi::BF16 || gamma.element_type() != ffi::BF16 || w.element_type() != ffi::BF16)
+    return Bad("x, gamma and w must be bfloat16");
+  if (x.dimensions().size() != 2 || w.dimensions().size() != 2 || Dim(w, 0) != Dim(x, 1))
+    return Bad("x [M, D], gamma [1, D], w [D, N]");
+  const int M = Dim(x, 0), D = Dim(x, 1), N = Dim(w, 1);
+  const int out_f32 = out->element_type() == ffi::F32 ? 1 : 0;
+  if (!out_f32 && out->element_type() != ffi::BF16) return Bad("out must be bfloat16 or float32");
+  const size_t need = tjx_rmsnorm_gemm_workspace_bytes(M, D);
+  void* ws = Aligned(workspace, need);
+  if (ws == nullptr) return Bad("the workspace result is too small");
+  const int rc = tjx_rmsnorm_gemm_bf16(x.untyped_data(), gamma.untyped_data(), w.untyped_data(), out->untyped_data(), M,
+                                       N, D, eps, tm, tn, tk, out_f32, ws, need, stream);
+  return rc == 0 ? ffi::Error::Success() : Failed(rc);
+}
+
+ffi::Error AttentionBlockImpl(cudaStream_t stream, ffi::AnyBuffer q, ffi::AnyBuffer k, ffi::AnyBuffer v,
+                              ffi::AnyBuffer gamma, ffi::AnyBuffer w_up, ffi::AnyBuffer w_down, ffi::AnyBuffer step_tile,
+                              ffi::AnyBuffer step_code, ffi::Result<ffi::AnyBuffer> out,
+                              ffi::Result<ffi::AnyBuffer> workspace, int32_t block_q, int32_t block_kv,
+                              int32_t pattern_tiles, float eps) {
+  for (const ffi::AnyBuffer* b : {&q, &k, &v, &gamma, &w_up, &w_down})
+    if (b->element_type() != ffi::BF16) return Bad("q, k, v, gamma, w_up and w_down must be bfloat16");
+  if (q.dimensions().size() != 4 || w_up.dimensions().size() != 2) return Bad("q [B, H, S, Dh], w_up [D, F]");
+  const int B = Dim(q, 0), H = Dim(q, 1), S = Dim(q, 2), Dh = Dim(q, 3), F = Dim(w_up, 1);
+  const size_t need = tjx_attention_block_workspace_bytes(B, H, S, Dh, F);
+  void* ws = Aligned(workspace, need);
+  if (ws == nullptr) return Bad("the workspace result is too small");
+  const int rc = tjx_attention_block_bf16(q.untyped_data(), k.untyped_data(), v.untyped_data(), gamma.untyped_data(),
+                                          w_up.untyped_data(), w_down.untyped_data(), out->untyped_data(), B, H, S, Dh,
+                                          F, block_q, block_kv, eps, Table(step_tile), Table(step_code),
+                                          static_cast<int>(step_tile.element_count()), pattern_tiles, ws, need, stream);
+  return rc == 0 ? ffi::Error::Success() : Failed(rc);
+}
+
+// ------------------------------------------------------------------------------------------------ MLA decode
+
+ffi::Error MlaDecodeImpl(cudaStream_t stream, ffi::AnyBuffer q_c, ffi::AnyBuffer q_r, ffi::AnyBuffer c_kv,
+                         ffi::AnyBuffer k_rope, ffi::AnyBuffer lengths, ffi::Result<ffi::AnyBuffer> out,
+                         ffi::Result<ffi::AnyBuffer> step_tile, ffi::Result<ffi::AnyBuffer> step_code,
+                         ffi::Result<ffi::AnyBuffer> step_count, ffi::Result<ffi::AnyBuffer> tile_first,
+                         ffi::Result<ffi::AnyBuffer> workspace, int32_t block) {
+  for (const ffi::AnyBuffer* b : {&q_c, &q_r, &c_kv, &k_rope})
+    if (b->element_type() != ffi::BF16) return Bad("q_c, q_r, c_kv and k_rope must be bfloat16");
+  if (lengths.element_type() != ffi::S32) return Bad("lengths must be int32");
+  if (q_c.dimensions().size() != 4 || c_kv.dimensions().size() != 3 || k_rope.dimensions().size() != 3)
+    return Bad("q_c [B, T, H, C], c_kv [B, S, C], k_rope [B, S, R]");
+  const int B = Dim(q_c, 0), T = Dim(q_c, 1), H = Dim(q_c, 2), C = Dim(q_c, 3), S = Dim(c_kv, 1), R = Dim(k_rope, 2);
+  const size_t need = tjx_mla_decode_workspace_bytes(B, T, H, S, block);
+  void* ws = need == 0 ? nullptr : Aligned(workspace, need);
+  if (ws == nullptr) return Bad("the block must divide the cache length, and the workspace result hold the scratch");
+  const int rc = tjx_mla_decode_bf16(q_c.untyped_data(), q_r.untyped_data(), c_kv.untyped_data(), k_rope.untyped_data(),
+                                     static_cast<const int32_t*>(lengths.untyped_data()), out->untyped_data(), B, T, H,
+                                     S, C, R, block, static_cast<int32_t*>(step_tile->untyped_data()),
+                                     static_cast<int32_t*>(step_code->untyped_data()),
+                                     static_cast<int32_t*>(step_count->untyped_data()),
+                                     static_cast<int32_t*>(tile_first->untyped_data()), ws, need, stream);
+  return rc == 0 ? ffi::Error::Success() : Failed(rc);
+}
+
 }  // namespace
 
 XLA_FFI_DEFINE_HANDLER_SYMBOL(TjxBuildSteps, BuildStepsImpl,
@@ -189,3 +261,50 @@ XLA_FFI_DEFINE_HANDLER_SYMBOL(TjxPagedGqaDecode, PagedGqaDecodeImpl,
                                   .Ret<ffi::AnyBuffer>()   // step_count
                                   .Ret<ffi::AnyBuffer>()   // tile_first
                                   .Ret<ffi::AnyBuffer>());  // workspace (uint8)
+
+XLA_FFI_DEFINE_HANDLER_SYMBOL(TjxRmsnormGemm, RmsnormGemmImpl,
+                              ffi::Ffi::Bind()
+                                  .Ctx<ffi::PlatformStream<cudaStream_t>>()
+                                  .Arg<ffi::AnyBuffer>()   // x
+                                  .Arg<ffi::AnyBuffer>()   // gamma
+                                  .Arg<ffi::AnyBuffer>()   // w
+                                  .Ret<ffi::AnyBuffer>()   // out
+                                  .Ret<ffi::AnyBuffer>()   // workspace (uint8)
+                                  .Attr<int32_t>("tm")
+                                  .Attr<int32_t>("tn")
+                                  .Attr<int32_t>("tk")
+                                  .Attr<float>("eps"));
+
+XLA_FFI_DEFINE_HANDLER_SYMBOL(TjxAttentionBlock, AttentionBlockImpl,
+                              ffi::Ffi::Bind()
+                                  .Ctx<ffi::PlatformStream<cudaStream_t>>()
+                                  .Arg<ffi::AnyBuffer>()   // q
+                                  .Arg<ffi::AnyBuffer>()   // k
+                                  .Arg<ffi::AnyBuffer>()   // v
+                                  .Arg<ffi::AnyBuffer>()   // gamma
+                                  .Arg<ffi::AnyBuffer>()   // w_up
+                                  .Arg<ffi::AnyBuffer>()   // w_down
+                                  .Arg<ffi::AnyBuffer>()   // step_tile
+                                  .Arg<ffi::AnyBuffer>()   // step_code
+                                  .Ret<ffi::AnyBuffer>()   // out
+                                  .Ret<ffi::AnyBuffer>()   // workspace (uint8)
+                                  .Attr<int32_t>("block_q")
+                                  .Attr<int32_t>("block_kv")
+                                  .Attr<int32_t>("pattern_tiles")
+                                  .Attr<float>("eps"));
+
+XLA_FFI_DEFINE_HANDLER_SYMBOL(TjxMlaDecode, MlaDecodeImpl,
+                              ffi::Ffi::Bind()
+                                  .Ctx<ffi::PlatformStream<cudaStream_t>>()
+                                  .Arg<ffi::AnyBuffer>()   // q_c
+                                  .Arg<ffi::AnyBuffer>()   // q_r
+                                  .Arg<ffi::AnyBuffer>()   // c_kv
+                                  .Arg<ffi::AnyBuffer>()   // k_rope
+                                  .Arg<ffi::AnyBuffer>()   // lengths
+                                  .Ret<ffi::AnyBuffer>()   // out
+                                  .Ret<ffi::AnyBuffer>()   // step_tile
+                                  .Ret<ffi::AnyBuffer>()   // step_code
+                                  .Ret<ffi::AnyBuffer>()   // step_count
+                                  .Ret<ffi::AnyBuffer>()   // tile_first
+                                  .Ret<ffi::AnyBuffer>()   // workspace (uint8)
+                                  .Attr<int32_t>("block"));

@@ -19,7 +19,8 @@ from ._lib import LIBRARY
 
 FFI_LIBRARY = Path(__file__).resolve().parent / "libtilejax_b200_ffi.so"
 TARGETS = {"tjx_build_steps": "TjxBuildSteps", "tjx_gemm": "TjxGemm", "tjx_causal_attention": "TjxCausalAttention",
-           "tjx_paged_gqa_decode": "TjxPagedGqaDecode"}
+           "tjx_paged_gqa_decode": "TjxPagedGqaDecode", "tjx_rmsnorm_gemm": "TjxRmsnormGemm",
+           "tjx_attention_block": "TjxAttentionBlock", "tjx_mla_decode": "TjxMlaDecode"}
 _registered = False
 
 
@@ -112,4 +113,68 @@ def paged_gqa_decode(q, k_pages, v_pages, block_tables, lengths):
                jax.ShapeDtypeStruct((B * pages,), jnp.int32), jax.ShapeDtypeStruct((1,), jnp.int32),
                jax.ShapeDtypeStruct((B + 1,), jnp.int32), jax.ShapeDtypeStruct((scratch,), jnp.uint8))
     out, tile, code, count, _, _ = jax.ffi.ffi_call("tjx_paged_gqa_decode", results)(q, k_pages, v_pages, block_tables, lengths)
+    return out, tile, code, count
+
+
+def _scratch(symbol: str, *sizes: int) -> int:
+    lib = ctypes.CDLL(str(LIBRARY))
+    fn = getattr(lib, symbol)
+    fn.restype = ctypes.c_size_t
+    return int(fn(*sizes)) + 256
+
+
+def rmsnorm_matmul(x, gamma, w, tm: int = 512, tn: int = 512, tk: int = 512, eps: float = 1e-6):
+    """rmsnorm(x) @ w through `tjx_rmsnorm_gemm` (examples/rmsnorm_matmul.py:31-47)."""
+    import jax
+    import jax.numpy as jnp
+
+    register()
+    (M, D), N = x.shape, w.shape[1]
+    results = (jax.ShapeDtypeStruct((M, N), x.dtype),
+               jax.ShapeDtypeStruct((_scratch("tjx_rmsnorm_gemm_workspace_bytes", M, D),), jnp.uint8))
+    out, _ = jax.ffi.ffi_call("tjx_rmsnorm_gemm", results)(x, gamma, w, tm=np.int32(min(tm, M)), tn=np.int32(min(tn, N)),
+                                                           tk=np.int32(min(tk, D)), eps=np.float32(eps))
+    return out
+
+
+def attention_block(q, k, v, gamma, w_up, w_down, block_q: int = 256, block_kv: int = 256, eps: float = 1e-6):
+    """The two-phase attention block through `tjx_attention_block` (examples/attention_block.py:49-85)."""
+    import jax
+    import jax.numpy as jnp
+
+    register()
+    B, H, S, Dh = q.shape
+    bq, bk = min(block_q, S), min(block_kv, S)
+    sch = _schedule.causal_attention_schedule(B, H, S, bq, bk)
+    if sch.step_tables:
+        tile, code = sch.tables["step_tile"], sch.tables["step_code"]
+    else:
+        nq, nk = S // bq, S // bk
+        tile, block = np.repeat(np.arange(nq, dtype=np.int32), nk), np.tile(np.arange(nk, dtype=np.int32), nq)
+        code = (block << _schedule.CODE_SHIFT) | ((block == 0) << 1) | (block == nk - 1)
+    scratch = _scratch("tjx_attention_block_workspace_bytes", B, H, S, Dh, w_up.shape[1])
+    results = (jax.ShapeDtypeStruct((B, S, H * Dh), q.dtype), jax.ShapeDtypeStruct((scratch,), jnp.uint8))
+    out, _ = jax.ffi.ffi_call("tjx_attention_block", results)(
+        q, k, v, gamma, w_up, w_down, _i32(tile), _i32(code), block_q=np.int32(bq), block_kv=np.int32(bk),
+        pattern_tiles=np.int32(S // bq), eps=np.float32(eps))
+    return out
+
+
+def mla_decode(q_c, q_r, c_kv, k_rope, lengths, block_kv: int = 512):
+    """Absorbed MLA decode through `tjx_mla_decode` (examples/decode.py:226-250): (out, step_tile, step_code,
+    step_count)."""
+    import jax
+    import jax.numpy as jnp
+
+    register()
+    B, T, H, _ = q_c.shape
+    S = c_kv.shape[1]
+    block = min(block_kv, S)
+    n = B * (S // block)
+    results = (jax.ShapeDtypeStruct(q_c.shape, q_c.dtype), jax.ShapeDtypeStruct((n,), jnp.int32),
+               jax.ShapeDtypeStruct((n,), jnp.int32), jax.ShapeDtypeStruct((1,), jnp.int32),
+               jax.ShapeDtypeStruct((B + 1,), jnp.int32),
+               jax.ShapeDtypeStruct((_scratch("tjx_mla_decode_workspace_bytes", B, T, H, S, block),), jnp.uint8))
+    out, tile, code, count, _, _ = jax.ffi.ffi_call("tjx_mla_decode", results)(q_c, q_r, c_kv, k_rope, lengths,
+                                                                               block=np.int32(block))
     return out, tile, code, count
