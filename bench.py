@@ -284,6 +284,48 @@ def cpu_baselines_for_workloads() -> dict:
     out["paged_gqa_decode"] = {"value": float(np.sum(lengths)) * 4096.0 / sec / 1e9, "unit": "GB/s", "cores": threads,
                                "kind": "port", "sample": f"{Bd} of the 64 sequences (lengths uniform in 1..4096, "
                                                          "16-token pages), one pass of the NumPy loop nest"}
+    n = 1024
+    rng = np.random.default_rng(7)
+    xr, wr = synthetic.normal_bf16((n, n), 0), synthetic.normal_bf16((n, n), 1)
+    gamma = (1 + 0.1 * rng.standard_normal((1, n), np.float32)).astype(xr.dtype)
+    sec = _timed(lambda: oracle.rmsnorm_matmul_ref(xr, gamma, wr, 512, 512, 512), 2, 1)
+    out["rmsnorm_matmul"] = {"value": 2.0 * n**3 / sec / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                             "sample": f"a {n}^3 problem (tiles 512^3) of the same loop nest, NumPy f32, mean of 2"}
+    from oracle.attention_block import attention_block_ref
+
+    Bb, Hb, Sb, Db, Fb = 1, 2, 512, 128, 1024
+    qb, kb, vb = synthetic.attention_inputs(Bb, Hb, Sb, Db)
+    gb = (1 + 0.1 * rng.standard_normal((1, Hb * Db), np.float32)).astype(qb.dtype)
+    up = (rng.standard_normal((Hb * Db, Fb), np.float32) / (Hb * Db) ** 0.5).astype(qb.dtype)
+    down = (rng.standard_normal((Fb, Hb * Db), np.float32) / Fb**0.5).astype(qb.dtype)
+    sec = _timed(lambda: attention_block_ref(qb, kb, vb, gb, up, down, 256, 256, 1024), 1, 0)
+    flops = 4.0 * Bb * Hb * Db * Sb * (Sb + 1) / 2 + 4.0 * Bb * Sb * Hb * Db * Fb
+    out["attention_block"] = {"value": flops / sec / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                              "sample": f"a block of {Hb} heads, S {Sb}, F {Fb} (blocks 256 x 256), one pass of the NumPy "
+                                        "loop nest"}
+    Bm, Hm, Sm = 2, 64, 2048
+    lens = np.array([1500, 2048], np.int32)
+    q_c, q_r = synthetic.normal_bf16((Bm, 1, Hm, 512), 3), synthetic.normal_bf16((Bm, 1, Hm, 128), 4)
+    c_kv, k_rope = synthetic.normal_bf16((Bm, Sm, 512), 5), synthetic.normal_bf16((Bm, Sm, 128), 6)
+    sec = _timed(lambda: oracle.mla_decode_ref(q_c, q_r, c_kv, k_rope, lens, 512), 1, 0)
+    out["mla_decode"] = {"value": float(lens.sum()) * 576 * 2 / sec / 1e9, "unit": "GB/s", "cores": threads,
+                         "kind": "port", "sample": f"{Bm} sequences of the 32 (64 heads, contexts 1500 and 2048), one "
+                                                   "pass of the NumPy loop nest"}
+    inp = oracle.rpa_inputs([1] * 4 + [256], [1000, 2000, 300, 4000, 512], max_len=4096, seed=0)
+    cache = oracle.rpa_write_ref(inp["kv_cache"], inp["keys"], inp["values"], inp["kv_lens"], inp["page_indices"],
+                                 inp["cu_q_lens"], inp["distribution"])
+
+    def rpa_step():
+        o = oracle.rpa_decode_ref(inp["q"], cache, inp["kv_lens"], inp["page_indices"], inp["distribution"], 128**-0.5)
+        return oracle.rpa_prefill_ref(o, cache, inp["kv_lens"], inp["page_indices"], inp["cu_q_lens"],
+                                      inp["distribution"], 128**-0.5)
+
+    sec = _timed(rpa_step, 1, 0)
+    seen = 256 * 256 + 256 * 257 // 2
+    out["ragged_paged_attention"] = {"value": 4.0 * 32 * 128 * seen / sec / 1e12, "unit": "TFLOP/s", "cores": threads,
+                                     "kind": "port", "sample": "4 decode sequences and one prefill sequence of 256 tokens "
+                                                               "on a prefix of 256, one pass of the NumPy loop nests; "
+                                                               "flops of the prefill tokens as in the GPU figure"}
     return out
 
 
