@@ -89,3 +89,57 @@ def test_a_wait_that_cannot_end_gives_up_reports_105_and_leaves_the_gpu_usable()
     assert torch.equal(out[:m], ops.gemm(shards[me], w, tm, tn, tk))
     assert torch.equal(ops.gemm(torch.cat(shards), w, tm, tn, tk)[m:], ops.gemm(shards[1], w, tm, tn, tk))
     assert ops.device_status() == 0
+
+
+def test_headline_size_as_rank_4_of_8_on_one_gpu_and_where_its_producers_wait(capsys):
+    # 16384 x 8192 x 8192 as eight shards of 2048 rows, walked a shard at a time as AllGatherMatmul walks them. The
+    # result is bit-equal to the plain GEMM over the same rows; the kernel's counters say what the gather costs: the
+    # producers barely wait for rows to arrive (the copier warps are far ahead), the MMA thread waits longer for its
+    # ring slots than in the plain GEMM while the copy shares L2 and the SM-to-L2 paths with the tile loads.
+    import ctypes
+
+    from tilejax_b200._lib import check, library
+
+    ranks, me, M, K, N, (tm, tn, tk) = 8, 4, 16384, 8192, 8192, (512, 512, 512)
+    m = M // ranks
+    shards = shards_for(ranks, m, K, 21)
+    w = shards_for(1, K, N, 22)[0]
+    order = schedule.collective_row_blocks(me, ranks, m // tm)
+    per = m // tm
+    parts = [collective.banded_tiles(order[s * per : (s + 1) * per], N // tn, 2048 // tn) for s in range(ranks)]
+    ti = torch.from_numpy(np.concatenate([p[0] for p in parts])).cuda()
+    tj = torch.from_numpy(np.concatenate([p[1] for p in parts])).cuda()
+    arrivals = torch.zeros(M // 256, dtype=torch.int32, device="cuda")
+    gathered = torch.zeros((M, K), dtype=torch.bfloat16, device="cuda")
+    out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    xs = torch.cat(shards)
+
+    def counters(launch):
+        buf = torch.zeros(148 * 16, dtype=torch.int64, device="cuda")
+        check(library().tjx_set_profile_buffer(ctypes.c_void_p(buf.data_ptr()), buf.numel() * 8))
+        try:
+            launch()
+            torch.cuda.synchronize()
+        finally:
+            check(library().tjx_set_profile_buffer(None, 0))
+        return buf.cpu().numpy().reshape(-1, 16)
+
+    ops.all_gather_gemm(shards[me], shards, gathered, w, out, me, tm, tn, tk, ti, tj, arrivals, 1)  # warm
+    fused = counters(lambda: ops.all_gather_gemm(shards[me], shards, gathered, w, out, me, tm, tn, tk, ti, tj, arrivals, 2))
+    assert ops.device_status() == 0
+    want = ops.gemm(xs, w, tm, tn, tk)
+    plain = counters(lambda: ops.gemm(xs, w, tm, tn, tk))
+    assert torch.equal(out, want)
+    for r in range(ranks):
+        if r != me:
+            assert torch.equal(gathered[r * m : (r + 1) * m], shards[r])
+    life, plain_life = fused[:, 7] - fused[:, 0], plain[:, 7] - plain[:, 0]
+    issuing = fused[:, 6] > 0
+    copier_done = fused[:, 11] - fused[:, 0]
+    assert (copier_done > 0).all() and (copier_done <= life).all()
+    assert (fused[:, 10] >= 0).all() and fused[:, 10].mean() < 0.05 * life.mean()
+    with capsys.disabled():
+        print(f"\n  cycles per CTA (mean): plain GEMM {plain_life.mean():.0f}, of which the MMA thread waits for inputs "
+              f"{plain[plain[:, 6] > 0, 3].mean():.0f}; as rank {me} of {ranks}: {life.mean():.0f}, MMA thread waits "
+              f"{fused[issuing, 3].mean():.0f}, producers wait for gathered rows {fused[:, 10].mean():.0f} "
+              f"(max {fused[:, 10].max()}), copier warps done after {copier_done.mean():.0f} (max {copier_done.max()})")

@@ -549,6 +549,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      long long gather_waited = 0;
       const int row_off = static_cast<int>(rank) * BM, col_off = static_cast<int>(rank) * (BN / 2);
       for (int w = pair; w < total_items && ok; w += n_pairs) {
         const Item it = decode_item<PAIR_ROWS, BN>(p, w);
@@ -557,6 +558,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
         if (GATHER) {
           own = it.m0 / p.gather_rows == p.gather_me;
           if (!own) {
+            const long long t0 = prof != nullptr ? clock64() : 0;
             // The rows of this piece come from another GPU: wait until the copier warps have all written them,
             // then order those (generic-proxy) writes before this thread's TMA reads.
             if (!gather_wait(p.gather_arrivals + it.m0 / PAIR_ROWS, p.gather_epoch * static_cast<int>(gridDim.x),
@@ -564,6 +566,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
               ok = false;
               break;
             }
+            if (prof != nullptr) gather_waited += clock64() - t0;
             asm volatile("fence.proxy.async;" ::: "memory");
           }
         }
@@ -598,6 +601,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
           }
         }
       }
+      if (GATHER && prof != nullptr) prof[10] = gather_waited;
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -689,6 +693,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
         if (lane == 0) atomicAdd(p.gather_arrivals + row_block, 1);
       }
     }
+    if (prof != nullptr && lane == 0) prof[11] = clock64();
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5 of each CTA)
     const int q = warp & 3;
