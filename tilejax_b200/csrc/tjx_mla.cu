@@ -352,35 +352,42 @@ __global__ void __launch_bounds__(MLA_WARPS * 32, 3)
 // scores and the output accumulate in TMEM. One persistent CTA per SM takes a contiguous range of the launch's
 // 32-position units (see MtPiece below).
 //
-//   warp 0      producer: per piece the 64 rows' queries (ten 128-byte-swizzled boxes [64 rows x 64 columns], 80 KB),
-//               then its units, 32 positions at a time, through a ring of three 40 KB slots (ten boxes [32 x 64])
-//   warp 1      MMA issuer (whole warp, one elected lane): S = Q K^T over the 640 columns (40 MMAs of 64 x 32 x 16 into
-//               one of two score buffers), then O += P V as two halves of 256 latent columns, P read from TMEM
-//   warps 2-5   softmax: a 64-row accumulator sits in TMEM lanes 0-15 of each 32-lane quarter (row 16 q + i in
-//               lane 32 q + i); a second 64-row tile may use lanes 16-31 of the same columns. S uses the lower
-//               lanes; O's two halves are the two tiles of columns 0-255. Lane i < 16 of warp q owns row 16 q + i:
-//               its scores and O's latent columns 0-255; lane i + 16 mirrors it (same scores, same P, written to its
-//               own TMEM lane so that the upper tile's MMA finds P beside its accumulator) and owns columns 256-511.
+//   warp 0      producer: one ring of five 40 KB slots (ten 128-byte-swizzled boxes [32 rows x 64 columns]). A piece
+//               sends its 64 rows of queries through two slots (rows 0-31, rows 32-63), then its units, 32 positions
+//               a slot
+//   warp 1      MMA issuer (whole warp, one elected lane): S = Q K^T over the 640 columns with Q read from TENSOR MEMORY
+//               (40 MMAs of 64 x 32 x 16 into one of two score buffers), then O += P V as two halves of 256 latent
+//               columns, P read from TMEM too
+//   warps 2-5   queries, softmax, flush: a 64-row tile sits in TMEM lanes 0-15 of each 32-lane quarter (row 16 q + i in
+//               lane 32 q + i); a second 64-row tile may use lanes 16-31 of the same columns. Lane i < 16 of warp q owns
+//               row 16 q + i together with lane i + 16. At the start of a piece the pair copies the row's queries from the
+//               ring into TMEM as the A operand: columns 0-319 (twenty K = 16 slices) into the lower lane, 320-639 into
+//               the upper one. The scores of the two column halves accumulate in the lower and the upper lanes of one
+//               score buffer, and the pair adds them (one shuffle). O's two halves of 256 latent columns are the two
+//               tiles of columns 0-255; both lanes compute the same P and each stores it in its own lane, beside its
+//               accumulator.
 //
-// TMEM: columns 0-255 O (both tiles), 256-287 and 288-319 the two score buffers; P (bf16, two per column)
-// overlays the first 16 columns of its score buffer.
+// TMEM: columns 0-255 O (both tiles), 256-287 and 288-319 the two score buffers (P, bf16, two per column, overlays
+// the first 16 columns of its buffer), 320-479 the queries.
 //
-// What bounds it: the 40 MMAs of 64 x 32 x 16 a unit's scores take (the queries' 80 KB leave shared memory room for
-// 32 positions per ring slot only) cost ~65 cycles each whatever their size: ~3000 cycles per unit of 40 KB.
+// Why the queries live in tensor memory: an MMA whose operands both come from shared memory is bound by the 128 bytes
+// per cycle shared memory delivers (64 x 32 x 16 reads 2 KB of Q and 1 KB of K: 27.6 cycles measured back to back on
+// an idle SM, 19.9 with Q in TMEM, against 16 of arithmetic at the half rate of a 64-row tile), and the queries' 80 KB
+// were read again for every 32 positions. Out of shared memory they also leave room for a five-slot ring instead
+// of three: a slot is wanted one unit after it is freed with three.
 constexpr int MT_ROWS = 64;
 constexpr int MT_POS = 32;                                   // positions per unit of work (one pass of the pipeline)
-constexpr int MT_STAGES = 3;
+constexpr int MT_STAGES = 5;
 constexpr int MT_KV_BOX = MT_POS * 128;                      // 32 positions x 64 columns
 constexpr int MT_STAGE_BYTES = MLA_BOXES * MT_KV_BOX;        // 40 KB
-constexpr int MT_Q_BOX = MT_ROWS * 128;                      // 64 rows x 64 columns
-constexpr int MT_Q_BYTES = MLA_BOXES * MT_Q_BOX;             // 80 KB
-constexpr int MT_KV_OFF = MT_Q_BYTES;
-constexpr int MT_BAR_OFF = MT_KV_OFF + MT_STAGES * MT_STAGE_BYTES;
+constexpr int MT_Q_SLOTS = MT_ROWS / MT_POS;                 // ring slots a piece's queries take (32 rows each)
+constexpr int MT_BAR_OFF = MT_STAGES * MT_STAGE_BYTES;
 constexpr int MT_MAX_B = 2048;                               // sequences whose unit counts fit the shared-memory table
 constexpr int MT_FIRST_OFF = MT_BAR_OFF + 256;               // int[B + 1]: units before each sequence
 constexpr int MT_SMEM = MT_FIRST_OFF + (MT_MAX_B + 1) * 4 + 252 + 1024;
 constexpr int MT_THREADS = 192;
 constexpr int MT_S_COL = 256;                                // first column of the score buffers
+constexpr int MT_Q_COL = 320;                                // first column of the queries (160 columns, both lane halves)
 constexpr int MT_MAX_CTAS = 256;                             // CTAs per 64-row group (the SMs of one GPU)
 constexpr int MT_MIN_SHARE = 2;                              // units a CTA takes at least
 constexpr float MT_RESCALE_THRESHOLD = 8.0f;
@@ -405,17 +412,18 @@ __global__ void __launch_bounds__(MT_THREADS, 1)
   const uint32_t base = (smem_u32(mt_smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = mt_smem_raw + (base - smem_u32(mt_smem_raw));
   const uint32_t bar_base = base + MT_BAR_OFF;
-  // barriers: q_full, kv_full[3], kv_empty[3], s_full[2], p_ready[2], o_done, q_empty
-  const uint32_t q_full = bar_base;
-  auto kv_full = [&](int s) { return bar_base + 8u * (1 + s); };
-  auto kv_empty = [&](int s) { return bar_base + 8u * (4 + s); };
-  auto s_full = [&](int t) { return bar_base + 8u * (7 + t); };
-  auto p_ready = [&](int t) { return bar_base + 8u * (9 + t); };
-  const uint32_t o_done = bar_base + 8u * 11;
-  const uint32_t q_empty = bar_base + 8u * 12;
-  constexpr int N_BARS = 13;
+  // barriers: kv_full[5], kv_empty[5], s_full[2], p_ready[2] (four warps arrive), o_done, q_ready (four warps)
+  auto kv_full = [&](int s) { return bar_base + 8u * s; };
+  auto kv_empty = [&](int s) { return bar_base + 8u * (MT_STAGES + s); };
+  auto s_full = [&](int t) { return bar_base + 8u * (2 * MT_STAGES + t); };
+  auto p_ready = [&](int t) { return bar_base + 8u * (2 * MT_STAGES + 2 + t); };
+  const uint32_t o_done = bar_base + 8u * (2 * MT_STAGES + 4);
+  const uint32_t q_ready = bar_base + 8u * (2 * MT_STAGES + 5);
+  constexpr int N_BARS = 2 * MT_STAGES + 6;
+  static_assert(8 * N_BARS + 32 <= 256, "barriers and flags fit before the unit table");
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(base_ptr + MT_BAR_OFF + 8 * N_BARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + MT_BAR_OFF + 8 * N_BARS + 8);
+  int* q_release = reinterpret_cast<int*>(base_ptr + MT_BAR_OFF + 8 * N_BARS + 16);  // [2]: warps done with a query slot
   int* first_unit = reinterpret_cast<int*>(base_ptr + MT_FIRST_OFF);  // [B + 1]
 
   const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
@@ -424,8 +432,10 @@ __global__ void __launch_bounds__(MT_THREADS, 1)
                         : p.profile + (static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * PROFILE_WORDS;
   if (prof != nullptr && threadIdx.x == 0) prof[0] = clock64();
   if (threadIdx.x == 0) {
-    for (int i = 0; i < N_BARS; ++i) mbar_init(bar_base + 8u * i, (i == 9 || i == 10) ? 4 : 1);
+    for (int i = 0; i < N_BARS; ++i)
+      mbar_init(bar_base + 8u * i, (i == 2 * MT_STAGES + 2 || i == 2 * MT_STAGES + 3 || i == 2 * MT_STAGES + 5) ? 4 : 1);
     *abort_flag = 0;
+    q_release[0] = 0, q_release[1] = 0;
     mbar_fence_init();
     tma_prefetch_desc(&map_qc);
     tma_prefetch_desc(&map_qr);
@@ -455,6 +465,9 @@ __global__ void __launch_bounds__(MT_THREADS, 1)
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = __shfl_sync(0xFFFFFFFFu, *tmem_holder, 0);
+  // The merge kernel may be scheduled from here on: its CTAs take no shared memory, work out their sequence's pieces,
+  // and then wait for this whole grid to complete before they read a partial.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   const int row0 = blockIdx.y * MT_ROWS;  // first of this CTA's rows among a sequence's p.H rows
   // (Read from shared memory: the same in every lane, and said so to the compiler, so that the MMA warp's loops over
@@ -486,87 +499,90 @@ __global__ void __launch_bounds__(MT_THREADS, 1)
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
-      int g = 0, done = 0;  // units and pieces loaded so far
+      int slot = 0;  // ring slots filled so far: a piece's two query slots, then one per unit
       bool ok = true;
-      for (int u = u_begin; u < u_end && ok; ++done) {
+      auto fill = [&](const CUtensorMap* wide, const CUtensorMap* narrow, int row) {
+        const int stage = slot % MT_STAGES;
+        if (slot >= MT_STAGES &&
+            !mbar_wait(kv_empty(stage), ((slot / MT_STAGES) - 1) & 1, abort_flag, p.status, TJX_ERR_WAIT_EMPTY))
+          return false;
+        const uint32_t dst = base + stage * MT_STAGE_BYTES;
+        mbar_expect_tx(kv_full(stage), MT_STAGE_BYTES);
+        for (int x = 0; x < MLA_C / 64; ++x) tma_load_2d(dst + x * MT_KV_BOX, wide, 64 * x, row, kv_full(stage));
+        for (int x = 0; x < MLA_R / 64; ++x)
+          tma_load_2d(dst + (MLA_C / 64 + x) * MT_KV_BOX, narrow, 64 * x, row, kv_full(stage));
+        ++slot;
+        return true;
+      };
+      for (int u = u_begin; u < u_end && ok;) {
         const MtPiece pc = piece_at(u);
-        // The previous piece's last Q K^T has read the queries.
-        if (done > 0 && !mbar_wait(q_empty, (done - 1) & 1, abort_flag, p.status, TJX_ERR_WAIT_EMPTY)) break;
         const int q_row = pc.b * p.H + row0;
-        mbar_expect_tx(q_full, MT_Q_BYTES);
-        for (int x = 0; x < MLA_C / 64; ++x) tma_load_2d(base + x * MT_Q_BOX, &map_qc, 64 * x, q_row, q_full);
-        for (int x = 0; x < MLA_R / 64; ++x) tma_load_2d(base + (MLA_C / 64 + x) * MT_Q_BOX, &map_qr, 64 * x, q_row, q_full);
+        for (int h = 0; h < MT_Q_SLOTS && ok; ++h) ok = fill(&map_qc, &map_qr, q_row + h * MT_POS);
         const int token0 = pc.b * p.S + pc.unit0 * MT_POS;
-        for (int i = 0; i < pc.n_units; ++i, ++g) {
-          const int stage = g % MT_STAGES;
-          if (g >= MT_STAGES &&
-              !mbar_wait(kv_empty(stage), ((g / MT_STAGES) - 1) & 1, abort_flag, p.status, TJX_ERR_WAIT_EMPTY)) {
-            ok = false;
-            break;
-          }
-          const uint32_t dst = base + MT_KV_OFF + stage * MT_STAGE_BYTES;
-          const int row = token0 + i * MT_POS;
-          mbar_expect_tx(kv_full(stage), MT_STAGE_BYTES);
-          for (int x = 0; x < MLA_C / 64; ++x) tma_load_2d(dst + x * MT_KV_BOX, &map_c, 64 * x, row, kv_full(stage));
-          for (int x = 0; x < MLA_R / 64; ++x)
-            tma_load_2d(dst + (MLA_C / 64 + x) * MT_KV_BOX, &map_r, 64 * x, row, kv_full(stage));
-        }
+        for (int i = 0; i < pc.n_units && ok; ++i) ok = fill(&map_c, &map_r, token0 + i * MT_POS);
         u += pc.n_units;
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (whole warp; one lane issues)
-    const uint32_t idesc_qk = idesc_bf16_f32(MT_ROWS, MT_POS, 0, 0);  // Q and K both K-major
+    const uint32_t idesc_qk = idesc_bf16_f32(MT_ROWS, MT_POS, 0, 0);  // Q from TMEM, K K-major
     const uint32_t idesc_pv = idesc_bf16_f32(MT_ROWS, 256, 0, 1);     // P from TMEM, the latents MN-major
-    long long in_wait = 0, p_wait = 0, fill_wait = -1, units = 0;
+    long long in_wait = 0, p_wait = 0, fill_wait = -1, units = 0, qk_cyc = 0, pv_cyc = 0;
     const long long t_first = prof != nullptr ? clock64() : 0;
     auto wait = [&](uint32_t bar, uint32_t parity, int err, long long& waited) {
       return __all_sync(0xFFFFFFFFu, mbar_wait_timed(bar, parity, abort_flag, p.status, err, waited, prof != nullptr)) != 0;
     };
-    auto issue_qk = [&](int g) {  // the scores of unit g (counted over the CTA's whole range)
-      const int stage = g % MT_STAGES;
-      const uint32_t kv = base + MT_KV_OFF + stage * MT_STAGE_BYTES;
-      const uint32_t d = tmem_base + MT_S_COL + (g & 1) * MT_POS;
+    // The scores of unit g (counted over the CTA's whole range), whose positions are in ring slot `slot`: columns
+    // 0-319 of Q and K into the lower lanes of the score buffer, 320-639 into the upper lanes.
+    auto issue_qk = [&](int g, int slot) {
+      const long long t0 = prof != nullptr ? clock64() : 0;
+      const uint32_t kv = base + (slot % MT_STAGES) * MT_STAGE_BYTES;
 #pragma unroll
-      for (int pair = 0; pair < MLA_BOXES / 2; ++pair) {  // two 64-column boxes = eight MMAs at a time
-        uint64_t qd[8], kd[8];
+      for (int half = 0; half < 2; ++half) {
+        const uint32_t tile = tmem_base + (static_cast<uint32_t>(16 * half) << 16);
+        const uint32_t d = tile + MT_S_COL + (g & 1) * MT_POS;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const int box = 2 * pair + (k >> 2);
-          qd[k] = smem_desc_sw128(base + box * MT_Q_BOX, 16, 1024) + (((k & 3) * 32) >> 4);
-          kd[k] = smem_desc_sw128(kv + box * MT_KV_BOX, 16, 1024) + (((k & 3) * 32) >> 4);
+        for (int bl = 0; bl < MLA_BOXES / 2; ++bl) {  // a 64-column box = four MMAs at a time
+          uint32_t qa[4];
+          uint64_t kd[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            qa[k] = tile + MT_Q_COL + (bl * 4 + k) * 8;
+            kd[k] = smem_desc_sw128(kv + (half * (MLA_BOXES / 2) + bl) * MT_KV_BOX, 16, 1024) + ((k * 32) >> 4);
+          }
+          mma_ts_x4(d, qa, kd, idesc_qk, bl != 0 ? 1u : 0u);
         }
-        mma_ss_x8(d, qd, kd, idesc_qk, pair != 0 ? 1u : 0u);
       }
       mma_commit_elected(s_full(g & 1));
+      if (prof != nullptr) qk_cyc += clock64() - t0;
     };
     int g0 = 0, done = 0;  // units and pieces issued so far
     bool ok = true;
     for (int u = u_begin; u < u_end && ok; ++done) {
       const MtPiece pc = piece_at(u);
       const int n = __shfl_sync(0xFFFFFFFFu, pc.n_units, 0);
-      ok = wait(q_full, done & 1, TJX_ERR_WAIT_FULL, in_wait) &&
-           wait(kv_full(g0 % MT_STAGES), (g0 / MT_STAGES) & 1, TJX_ERR_WAIT_FULL, in_wait);
+      const int slot0 = g0 + MT_Q_SLOTS * (done + 1);  // the ring slot of the piece's first unit
+      ok = wait(q_ready, done & 1, TJX_ERR_WAIT_FULL, in_wait) &&
+           wait(kv_full(slot0 % MT_STAGES), (slot0 / MT_STAGES) & 1, TJX_ERR_WAIT_FULL, in_wait);
       if (fill_wait < 0) fill_wait = in_wait;
       if (!ok) break;
       tc_fence_after_sync();
-      issue_qk(g0);
-      if (n == 1) mma_commit_elected(q_empty);
+      issue_qk(g0, slot0);
       for (int i = 0; i < n && ok; ++i) {
-        const int g = g0 + i;
-        const int stage = g % MT_STAGES;
+        const int g = g0 + i, slot = slot0 + i;
         if (i + 1 < n) {  // the next unit's scores run while this one's softmax does
-          ok = wait(kv_full((g + 1) % MT_STAGES), ((g + 1) / MT_STAGES) & 1, TJX_ERR_WAIT_FULL, in_wait);
+          ok = wait(kv_full((slot + 1) % MT_STAGES), ((slot + 1) / MT_STAGES) & 1, TJX_ERR_WAIT_FULL, in_wait);
           if (!ok) break;
           tc_fence_after_sync();
-          issue_qk(g + 1);
-          if (i + 2 == n) mma_commit_elected(q_empty);  // that was the piece's last Q K^T
+          issue_qk(g + 1, slot + 1);
         }
         ok = wait(p_ready(g & 1), (g >> 1) & 1, TJX_ERR_WAIT_OTHER, p_wait);
         if (!ok) break;
         tc_fence_after_sync();
-        const uint32_t kv = base + MT_KV_OFF + stage * MT_STAGE_BYTES;
+        const long long t_pv = prof != nullptr ? clock64() : 0;
+        const int stage = slot % MT_STAGES;
+        const uint32_t kv = base + stage * MT_STAGE_BYTES;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {  // latent columns 256 half .. 256 half + 255: the tile at lanes 16 half
           const uint32_t tile = static_cast<uint32_t>(16 * half) << 16;
@@ -579,13 +595,14 @@ __global__ void __launch_bounds__(MT_THREADS, 1)
         }
         mma_commit_elected(kv_empty(stage));
         mma_commit_elected(o_done);
+        if (prof != nullptr) pv_cyc += clock64() - t_pv;
       }
       g0 += n, units += n;
       u += n;
     }
     if (prof != nullptr && lane == 0) {
       prof[1] = t_first, prof[2] = clock64(), prof[3] = in_wait, prof[4] = max(fill_wait, 0ll), prof[5] = 0, prof[6] = units;
-      prof[8] = p_wait;
+      prof[8] = p_wait, prof[9] = qk_cyc, prof[10] = pv_cyc, prof[11] = done;
     }
   } else {
     // ------------------------------------------------------------------ softmax, correction, flush (warps 2..5)
@@ -602,9 +619,44 @@ __global__ void __launch_bounds__(MT_THREADS, 1)
           uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(b) * p.H + row) * MLA_C + 256 * half);
           for (int x = 0; x < 32; ++x) dst[x] = make_uint4(0u, 0u, 0u, 0u);
         }
-    int g0 = 0;  // units seen so far
-    bool ok = true;
-    for (int u = u_begin; u < u_end && ok;) {
+    // This row's queries, from the ring into TMEM as the A operand of Q K^T. `first_slot` is the first of the piece's
+    // two query slots: warps 0-1 find rows 0-31 there, warps 2-3 rows 32-63 in the next; a lane copies five 64-column
+    // boxes, 128 bytes of its row each (the 16-byte chunk c of row r of a swizzled box sits at chunk c ^ (r & 7)).
+    // Called when the previous piece's Q K^T have all completed: this warp has waited for each of their score buffers.
+    auto stage_queries = [&](int first_slot) {
+      const int q_slot = first_slot + (q >> 1);
+      const int stage = q_slot % MT_STAGES;
+      const bool got = mbar_wait(kv_full(stage), (q_slot / MT_STAGES) & 1, abort_flag, p.status, TJX_ERR_WAIT_FULL);
+      if (!__all_sync(0xFFFFFFFFu, got)) return false;
+      const int r_slot = 16 * (q & 1) + (lane & 15);
+      const uint8_t* src = base_ptr + stage * MT_STAGE_BYTES + half * (MLA_BOXES / 2) * MT_KV_BOX + r_slot * 128;
+#pragma unroll 1
+      for (int bl = 0; bl < MLA_BOXES / 2; ++bl) {
+        uint32_t w[32];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 x = *reinterpret_cast<const uint4*>(src + bl * MT_KV_BOX + ((c ^ (r_slot & 7)) << 4));
+          w[4 * c] = x.x, w[4 * c + 1] = x.y, w[4 * c + 2] = x.z, w[4 * c + 3] = x.w;
+        }
+        tmem_st32(tmem_base + quarter + MT_Q_COL + bl * 32, w);
+      }
+      tmem_wait_st();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(q_ready);
+        // The slot goes back to the producer when both of its warps have read it.
+        __threadfence_block();
+        if (atomicAdd(&q_release[q >> 1], 1) == 1) {
+          q_release[q >> 1] = 0;
+          mbar_arrive(kv_empty(stage));
+        }
+      }
+      return true;
+    };
+    int g0 = 0, done = 0;  // units and pieces seen so far
+    bool ok = u_begin >= u_end || stage_queries(0);
+    for (int u = u_begin; u < u_end && ok; ++done) {
       const MtPiece pc = piece_at(u);
       const int n = pc.n_units;
       const int j0 = pc.unit0 * MT_POS;
@@ -627,8 +679,9 @@ __global__ void __launch_bounds__(MT_THREADS, 1)
         float mx = MLA_MASK * MLA_LOG2E;
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-          // Lanes 16-31 take the scores of the lane 16 below: the same row.
-          const float sc = __shfl_sync(0xFFFFFFFFu, __uint_as_float(v[j]), lane & 15);
+          // The row's score is the sum over the two column halves, one in this lane, one in its partner.
+          const float part = __uint_as_float(v[j]);
+          const float sc = part + __shfl_xor_sync(0xFFFFFFFFu, part, 16);
           const float x = pos0 + j < limit ? sc * MLA_LOG2E : MLA_MASK * MLA_LOG2E;
           v[j] = __float_as_uint(x);
           mx = fmaxf(mx, x);
@@ -679,30 +732,36 @@ __global__ void __launch_bounds__(MT_THREADS, 1)
           const bool od = mbar_wait(o_done, (g - 1) & 1, abort_flag, p.status, TJX_ERR_WAIT_OTHER);
           ok = __all_sync(0xFFFFFFFFu, od) != 0;
         }
-        if (ok && i + 1 == n) {
-          const bool od = mbar_wait(o_done, g & 1, abort_flag, p.status, TJX_ERR_WAIT_OTHER);
-          ok = __all_sync(0xFFFFFFFFu, od) != 0;
-        }
         if (!ok) break;
         tc_fence_after_sync();
       }
       if (!ok) break;
-      // Flush this lane's 256 latent columns of its row: the output itself, or a partial for the merge.
-      if (row < p.H) {
-        const int c0 = 256 * half;
-        const float inv = 1.0f / fmaxf(l, 1e-30f);
-        const size_t part = pc.index * p.H + row;
-        if (pc.pieces > 1 && half == 0) {  // the partials keep the max in natural-log units
-          p.ws_m[part] = m_used * (1.0f / MLA_LOG2E);
-          p.ws_l[part] = l;
-        }
+      // The next piece's queries go in while the last P V runs: its first Q K^T then overlaps the flush below.
+      if (u + n < u_end && !stage_queries(g0 + n + MT_Q_SLOTS * (done + 1))) break;
+      {
+        const bool od = mbar_wait(o_done, (g0 + n - 1) & 1, abort_flag, p.status, TJX_ERR_WAIT_OTHER);
+        if (!__all_sync(0xFFFFFFFFu, od)) break;
+        tc_fence_after_sync();
+      }
+      // Flush this lane's 256 latent columns of its row: the output itself, or a partial for the merge. A partial is
+      // laid out the way the warps hold it — [warp q][32-column step c][16-byte chunk x][lane] — so that every store
+      // instruction of a warp writes 512 contiguous bytes; written by row, each lane's 16 bytes land in a line of
+      // their own and a flush costs ~10 000 cycles between two pieces. (Rows past the sequence's last are written too:
+      // the workspace holds whole 64-row groups, and the merge skips them.)
+      const float inv = 1.0f / fmaxf(l, 1e-30f);
+      const size_t block = pc.index * gridDim.y + blockIdx.y;  // this piece's 64 rows in the workspace
+      if (pc.pieces > 1 && half == 0) {  // the partials keep the max in natural-log units
+        p.ws_m[block * MT_ROWS + r] = m_used * (1.0f / MLA_LOG2E);
+        p.ws_l[block * MT_ROWS + r] = l;
+      }
 #pragma unroll 1
-        for (int c = 0; c < 8; ++c) {
-          uint32_t o[32];
-          tmem_ld32(o_tmem + c * 32, o);
-          tmem_wait_ld();
-          if (pc.pieces == 1) {
-            uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(pc.b) * p.H + row) * MLA_C + c0 + c * 32);
+      for (int c = 0; c < 8; ++c) {
+        uint32_t o[32];
+        tmem_ld32(o_tmem + c * 32, o);
+        tmem_wait_ld();
+        if (pc.pieces == 1) {
+          if (row < p.H) {
+            uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(pc.b) * p.H + row) * MLA_C + 256 * half + c * 32);
 #pragma unroll
             for (int x = 0; x < 4; ++x) {
               uint4 val;
@@ -712,11 +771,11 @@ __global__ void __launch_bounds__(MT_THREADS, 1)
               val.w = pack_bf16(__uint_as_float(o[8 * x + 6]) * inv, __uint_as_float(o[8 * x + 7]) * inv);
               dst[x] = val;
             }
-          } else {
-            uint4* dst = reinterpret_cast<uint4*>(p.ws_acc + part * MLA_C + c0 + c * 32);
-#pragma unroll
-            for (int x = 0; x < 8; ++x) dst[x] = make_uint4(o[4 * x], o[4 * x + 1], o[4 * x + 2], o[4 * x + 3]);
           }
+        } else {
+          uint4* dst = reinterpret_cast<uint4*>(p.ws_acc + block * (MT_ROWS * MLA_C)) + ((q * 8 + c) * 8) * 32 + lane;
+#pragma unroll
+          for (int x = 0; x < 8; ++x) dst[x * 32] = make_uint4(o[4 * x], o[4 * x + 1], o[4 * x + 2], o[4 * x + 3]);
         }
       }
       // The reads of O above are ordered before this warp's next arrival on p_ready, which is what the next piece's
@@ -737,15 +796,16 @@ __global__ void __launch_bounds__(MT_THREADS, 1)
   }
 }
 
-// Merges the partials mla_tc_kernel left: a CTA per (sequence, 8 rows), a warp per row, a lane 16 of the row's 512
-// latent columns. It works out the sequence's pieces as the main kernel did (units before the sequence, the share
-// of a CTA), returns at once for a sequence written directly, and otherwise reads the pieces' (max, sum,
-// accumulator) past L1, weights them by exp(max_i - max), and writes the normalised row in bf16. Launched with
-// programmatic stream serialisation: the prologue runs beside the main kernel's tail.
+// Merges the partials mla_tc_kernel left: a CTA per (sequence, 64-row group, 16 rows of it), a warp per step of 32
+// latent columns, a lane per (row, half of the columns) exactly as the main kernel's warps held them, so that its
+// reads are the 512-byte runs the main kernel wrote. It works out the sequence's pieces as the main kernel did
+// (units before the sequence, the share of a CTA), returns at once for a sequence written directly, and otherwise
+// reads the pieces' (max, sum, accumulator) past L1, weights them by exp(max_i - max), and writes the normalised
+// rows in bf16. Launched with programmatic stream serialisation: the prologue runs beside the main kernel's tail.
 constexpr int MG_WARPS = 8;
 
 __global__ void __launch_bounds__(MG_WARPS * 32)
-    mla_tc_merge_kernel(const MlaParams p, int main_ctas) {
+    mla_tc_merge_kernel(const MlaParams p, int main_ctas, int groups) {
   __shared__ int seq_units[3];  // units before sequence b, before b + 1, in total
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.x;
@@ -775,50 +835,52 @@ __global__ void __launch_bounds__(MG_WARPS * 32)
   const int first_cta = f / share;
   const int n = (l - 1) / share - first_cta + 1;
   if (n <= 1) return;  // written directly
-  const int row = blockIdx.y * MG_WARPS + warp;
-  if (row >= p.H) return;
+  const int group = blockIdx.y >> 2, q = blockIdx.y & 3, c = warp;
+  const int r = 16 * q + (lane & 15), half = lane >> 4;
+  const int row = group * MT_ROWS + r;
   asm volatile("griddepcontrol.wait;" ::: "memory");  // the partials are the main kernel's
-  const size_t base = (static_cast<size_t>(first_cta) + b) * p.H + row;  // piece i: base + i * p.H
+  const size_t block0 = (static_cast<size_t>(first_cta) + b) * groups + group;  // piece i: block0 + i * groups
   float mx = MLA_MASK;
-  for (int i = lane; i < n; i += 32) mx = fmaxf(mx, __ldcg(p.ws_m + base + static_cast<size_t>(i) * p.H));
-#pragma unroll
-  for (int d = 16; d >= 1; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, d));
+  for (int i = 0; i < n; ++i) mx = fmaxf(mx, __ldcg(p.ws_m + (block0 + static_cast<size_t>(i) * groups) * MT_ROWS + r));
   float lsum = 0.f;
-  float4 o[4];
+  float4 o[8];
 #pragma unroll
-  for (int k = 0; k < 4; ++k) o[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int i0 = 0; i0 < n; i0 += 32) {
-    float w_mine = 0.f;
-    if (i0 + lane < n) {
-      const size_t idx = base + static_cast<size_t>(i0 + lane) * p.H;
-      w_mine = __expf(__ldcg(p.ws_m + idx) - mx);
-      lsum += w_mine * __ldcg(p.ws_l + idx);
-    }
-    const int cnt = min(32, n - i0);
-#pragma unroll 4
-    for (int i = 0; i < cnt; ++i) {
-      const float w = __shfl_sync(0xFFFFFFFFu, w_mine, i);
-      const float4* src = reinterpret_cast<const float4*>(p.ws_acc + (base + static_cast<size_t>(i0 + i) * p.H) * MLA_C);
+  for (int x = 0; x < 8; ++x) o[x] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 2
+  for (int i = 0; i < n; ++i) {
+    const size_t block = block0 + static_cast<size_t>(i) * groups;
+    const float w = __expf(__ldcg(p.ws_m + block * MT_ROWS + r) - mx);
+    lsum += w * __ldcg(p.ws_l + block * MT_ROWS + r);
+    const float4* src = reinterpret_cast<const float4*>(p.ws_acc + block * (MT_ROWS * MLA_C)) + ((q * 8 + c) * 8) * 32 + lane;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float4 a = __ldcg(src + lane + 32 * k);
-        o[k].x = fmaf(w, a.x, o[k].x), o[k].y = fmaf(w, a.y, o[k].y);
-        o[k].z = fmaf(w, a.z, o[k].z), o[k].w = fmaf(w, a.w, o[k].w);
-      }
+    for (int x = 0; x < 8; ++x) {
+      const float4 a = __ldcg(src + x * 32);
+      o[x].x = fmaf(w, a.x, o[x].x), o[x].y = fmaf(w, a.y, o[x].y);
+      o[x].z = fmaf(w, a.z, o[x].z), o[x].w = fmaf(w, a.w, o[x].w);
     }
   }
-#pragma unroll
-  for (int d = 16; d >= 1; d >>= 1) lsum += __shfl_xor_sync(0xFFFFFFFFu, lsum, d);
+  if (row >= p.H) return;
   const float inv = 1.0f / fmaxf(lsum, 1e-30f);
-  uint2* dst = reinterpret_cast<uint2*>(p.out + (static_cast<size_t>(b) * p.H + row) * MLA_C);
+  uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(b) * p.H + row) * MLA_C + 256 * half + 32 * c);
 #pragma unroll
-  for (int k = 0; k < 4; ++k)
-    dst[lane + 32 * k] = make_uint2(pack_bf16(o[k].x * inv, o[k].y * inv), pack_bf16(o[k].z * inv, o[k].w * inv));
+  for (int x = 0; x < 4; ++x) {
+    uint4 val;
+    val.x = pack_bf16(o[2 * x].x * inv, o[2 * x].y * inv), val.y = pack_bf16(o[2 * x].z * inv, o[2 * x].w * inv);
+    val.z = pack_bf16(o[2 * x + 1].x * inv, o[2 * x + 1].y * inv), val.w = pack_bf16(o[2 * x + 1].z * inv, o[2 * x + 1].w * inv);
+    dst[x] = val;
+  }
 }
 
 int g_mla_mode = 1;  // 1: the tcgen05 kernel; 0: the warp-level MMA kernel (an A/B switch; values agree to rounding)
 
 static size_t mla_align256(size_t n) { return (n + 255) & ~static_cast<size_t>(255); }
+
+// Rows of partials the workspace holds, H rows a sequence: [sequence][block] for the warp-level kernel,
+// [CTA + sequence] whole 64-row groups for the tcgen05 kernel; the larger of the two.
+static size_t mla_partial_rows(int B, int H, int blocks) {
+  const size_t groups = (static_cast<size_t>(H) + MT_ROWS - 1) / MT_ROWS;
+  return std::max(static_cast<size_t>(B) * blocks * H, (static_cast<size_t>(MT_MAX_CTAS) + B) * groups * MT_ROWS);
+}
 
 }  // namespace tjx
 
@@ -833,7 +895,7 @@ int tjx_mla_set_mode(int mode) {
 size_t tjx_mla_decode_workspace_bytes(int B, int T, int H, int S, int block) {
   if (B <= 0 || T <= 0 || H <= 0 || S <= 0 || block <= 0 || S % block != 0) return 0;
   H *= T;  // rows per sequence
-  const size_t rows = std::max(static_cast<size_t>(B) * (S / block), static_cast<size_t>(tjx::MT_MAX_CTAS) + B) * H;
+  const size_t rows = tjx::mla_partial_rows(B, H, S / block);
   return 2 * tjx::mla_align256(rows * sizeof(float)) + tjx::mla_align256(rows * tjx::MLA_C * sizeof(float)) +
          tjx::mla_align256(static_cast<size_t>(B) * H * sizeof(int));
 }
@@ -872,9 +934,7 @@ int tjx_mla_decode_bf16(const void* q_c, const void* q_r, const void* c_kv, cons
   p.step_tile = step_tile, p.step_code = step_code, p.step_count = step_count, p.tile_first = tile_first;
   p.B = B, p.H = H, p.S = S, p.block = block, p.blocks = S / block;
   p.heads = heads, p.T = T;
-  // Partials: [sequence][block] for the warp-level kernel, [CTA + sequence] for the tcgen05 kernel; the workspace
-  // holds the larger of the two.
-  const size_t rows = std::max(static_cast<size_t>(B) * p.blocks, static_cast<size_t>(MT_MAX_CTAS) + B) * H;
+  const size_t rows = mla_partial_rows(B, H, p.blocks);
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   p.ws_m = reinterpret_cast<float*>(ws);
   p.ws_l = reinterpret_cast<float*>(ws + mla_align256(rows * sizeof(float)));
@@ -892,10 +952,10 @@ int tjx_mla_decode_bf16(const void* q_c, const void* q_r, const void* c_kv, cons
 
   if (tensor_path) {
     CUtensorMap mqc, mqr, mc, mr;
-    const uint32_t q_box[2] = {64, MT_ROWS}, kv_box[2] = {64, MT_POS};
+    const uint32_t kv_box[2] = {64, MT_POS};  // the queries travel in boxes of 32 rows too: two ring slots a piece
     const uint64_t q_rows = static_cast<uint64_t>(B) * H, kv_rows = static_cast<uint64_t>(B) * S;
     const struct { CUtensorMap* map; const void* ptr; uint64_t cols, rows; const uint32_t* box; } maps[4] = {
-        {&mqc, q_c, MLA_C, q_rows, q_box}, {&mqr, q_r, MLA_R, q_rows, q_box},
+        {&mqc, q_c, MLA_C, q_rows, kv_box}, {&mqr, q_r, MLA_R, q_rows, kv_box},
         {&mc, c_kv, MLA_C, kv_rows, kv_box}, {&mr, k_rope, MLA_R, kv_rows, kv_box}};
     for (const auto& m : maps) {
       const uint64_t dims[2] = {m.cols, m.rows};
@@ -923,10 +983,10 @@ int tjx_mla_decode_bf16(const void* q_c, const void* q_r, const void* c_kv, cons
     cfg.attrs = &attr, cfg.numAttrs = 1;
     TJX_CUDA(cudaLaunchKernelEx(&cfg, mla_tc_kernel, mqc, mqr, mc, mr, p));
     cudaLaunchConfig_t merge{};
-    merge.gridDim = dim3(B, (H + MG_WARPS - 1) / MG_WARPS), merge.blockDim = dim3(MG_WARPS * 32);
+    merge.gridDim = dim3(B, groups * 4), merge.blockDim = dim3(MG_WARPS * 32);
     merge.dynamicSmemBytes = 0, merge.stream = s;
     merge.attrs = &attr, merge.numAttrs = 1;
-    TJX_CUDA(cudaLaunchKernelEx(&merge, mla_tc_merge_kernel, p, ctas));
+    TJX_CUDA(cudaLaunchKernelEx(&merge, mla_tc_merge_kernel, p, ctas, groups));
     return 0;
   }
 
