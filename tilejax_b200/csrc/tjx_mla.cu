@@ -390,6 +390,10 @@ constexpr int MT_S_COL = 256;                                // first column of 
 constexpr int MT_Q_COL = 320;                                // first column of the queries (160 columns, both lane halves)
 constexpr int MT_MAX_CTAS = 256;                             // CTAs per 64-row group (the SMs of one GPU)
 constexpr int MT_MIN_SHARE = 2;                              // units a CTA takes at least
+// What starting a piece costs (its queries into TMEM, the pipeline filling, its flush), in units: measured 5 200
+// cycles against 1 340 a unit. The units are shared out with this much counted in front of every sequence, so that
+// a CTA whose range crosses into another sequence gets fewer units.
+constexpr int MT_PIECE_COST = 3;
 constexpr float MT_RESCALE_THRESHOLD = 8.0f;
 
 // The work of a launch is every sequence's cache in units of 32 positions, in sequence order; the CTAs of a 64-row
@@ -398,10 +402,12 @@ constexpr float MT_RESCALE_THRESHOLD = 8.0f;
 // `lengths` (a warp scan in its prologue); the step-table kernel runs beside it and only emits the caller's tables.
 // A piece = (sequence, range of its units) is one pass of the pipeline below; a piece that is its sequence's only
 // one is normalised and written at once, else its partial goes to the workspace at index (CTA + sequence) — unique,
-// and consecutive for the pieces of one sequence — and the last CTA to count itself on the sequence merges.
+// and consecutive for the pieces of one sequence — and mla_tc_merge_kernel, launched behind this kernel, merges.
 struct MtPiece {
   int b, unit0, n_units, len, pieces;
-  size_t index, first_index;  // this piece's partial, the sequence's first
+  int next;     // where the CTA's range continues (a position on the line of units with MT_PIECE_COST before each sequence)
+  bool more;    // the range holds units of a later sequence
+  size_t index;  // this piece's partial
 };
 
 __global__ void __launch_bounds__(MT_THREADS, 1)
@@ -430,7 +436,7 @@ __global__ void __launch_bounds__(MT_THREADS, 1)
   long long* prof = p.profile == nullptr
                         ? nullptr
                         : p.profile + (static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x) * PROFILE_WORDS;
-  if (prof != nullptr && threadIdx.x == 0) prof[0] = clock64();
+  if (prof != nullptr && threadIdx.x == 0) prof[0] = clock64(), prof[12] = static_cast<long long>(globaltimer_ns());
   if (threadIdx.x == 0) {
     for (int i = 0; i < N_BARS; ++i)
       mbar_init(bar_base + 8u * i, (i == 2 * MT_STAGES + 2 || i == 2 * MT_STAGES + 3 || i == 2 * MT_STAGES + 5) ? 4 : 1);
@@ -451,6 +457,7 @@ __global__ void __launch_bounds__(MT_THREADS, 1)
     for (int b0 = 0; b0 < p.B; b0 += 32) {
       const int b = b0 + lane;
       int x = b < p.B ? (min(max(p.lengths[b], 0), p.S) + MT_POS - 1) / MT_POS : 0;
+      if (x > 0) x += MT_PIECE_COST;
 #pragma unroll
       for (int d = 1; d < 32; d <<= 1) {
         const int y = __shfl_up_sync(0xFFFFFFFFu, x, d);
@@ -473,10 +480,13 @@ __global__ void __launch_bounds__(MT_THREADS, 1)
   // (Read from shared memory: the same in every lane, and said so to the compiler, so that the MMA warp's loops over
   // this CTA's range stay warp-uniform and its descriptors in uniform registers.)
   const int total_units = __shfl_sync(0xFFFFFFFFu, first_unit[p.B], 0);
-  const int share = max(MT_MIN_SHARE, (total_units + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x));
+  const int share = max(MT_MIN_SHARE + MT_PIECE_COST,
+                        (total_units + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x));
   const int cta = static_cast<int>(blockIdx.x);
   const int u_begin = min(cta * share, total_units), u_end = min(u_begin + share, total_units);
-  // The piece that starts at unit `u` of this CTA's range (u < u_end): the same in every thread.
+  // The piece at position `u` of this CTA's range (u < u_end): the same in every thread. Positions count units with
+  // MT_PIECE_COST more in front of every sequence that has any; a range that ends inside that margin holds no unit of
+  // the sequence (n_units == 0: every role skips it).
   auto piece_at = [&](int u) {
     int lo = 0, hi = p.B;  // the sequence with first_unit[b] <= u < first_unit[b + 1]
     while (hi - lo > 1) {
@@ -485,14 +495,17 @@ __global__ void __launch_bounds__(MT_THREADS, 1)
     }
     MtPiece pc;
     pc.b = lo;
-    const int f = first_unit[lo], l = first_unit[lo + 1];
-    pc.unit0 = u - f;
-    pc.n_units = min(u_end, l) - u;
+    const int l = first_unit[lo + 1];
+    const int real0 = first_unit[lo] + MT_PIECE_COST;  // the sequence's first unit
+    const int start = max(u, real0), end = min(u_end, l);
+    pc.unit0 = start - real0;
+    pc.n_units = max(end - start, 0);
+    pc.next = end;
+    pc.more = u_end > l + MT_PIECE_COST;
     pc.len = min(max(p.lengths[lo], 0), p.S);
-    const int first_cta = f / share;
+    const int first_cta = real0 / share;
     pc.pieces = (l - 1) / share - first_cta + 1;
     pc.index = static_cast<size_t>(cta) + lo;
-    pc.first_index = static_cast<size_t>(first_cta) + lo;
     return pc;
   };
 
@@ -516,11 +529,12 @@ __global__ void __launch_bounds__(MT_THREADS, 1)
       };
       for (int u = u_begin; u < u_end && ok;) {
         const MtPiece pc = piece_at(u);
+        u = pc.next;
+        if (pc.n_units == 0) continue;
         const int q_row = pc.b * p.H + row0;
         for (int h = 0; h < MT_Q_SLOTS && ok; ++h) ok = fill(&map_qc, &map_qr, q_row + h * MT_POS);
         const int token0 = pc.b * p.S + pc.unit0 * MT_POS;
         for (int i = 0; i < pc.n_units && ok; ++i) ok = fill(&map_c, &map_r, token0 + i * MT_POS);
-        u += pc.n_units;
       }
     }
     __syncwarp();
@@ -559,9 +573,11 @@ __global__ void __launch_bounds__(MT_THREADS, 1)
     };
     int g0 = 0, done = 0;  // units and pieces issued so far
     bool ok = true;
-    for (int u = u_begin; u < u_end && ok; ++done) {
+    for (int u = u_begin; u < u_end && ok;) {
       const MtPiece pc = piece_at(u);
       const int n = __shfl_sync(0xFFFFFFFFu, pc.n_units, 0);
+      u = __shfl_sync(0xFFFFFFFFu, pc.next, 0);
+      if (n == 0) continue;
       const int slot0 = g0 + MT_Q_SLOTS * (done + 1);  // the ring slot of the piece's first unit
       ok = wait(q_ready, done & 1, TJX_ERR_WAIT_FULL, in_wait) &&
            wait(kv_full(slot0 % MT_STAGES), (slot0 / MT_STAGES) & 1, TJX_ERR_WAIT_FULL, in_wait);
@@ -598,7 +614,7 @@ __global__ void __launch_bounds__(MT_THREADS, 1)
         if (prof != nullptr) pv_cyc += clock64() - t_pv;
       }
       g0 += n, units += n;
-      u += n;
+      ++done;
     }
     if (prof != nullptr && lane == 0) {
       prof[1] = t_first, prof[2] = clock64(), prof[3] = in_wait, prof[4] = max(fill_wait, 0ll), prof[5] = 0, prof[6] = units;
@@ -655,10 +671,13 @@ __global__ void __launch_bounds__(MT_THREADS, 1)
       return true;
     };
     int g0 = 0, done = 0;  // units and pieces seen so far
-    bool ok = u_begin >= u_end || stage_queries(0);
-    for (int u = u_begin; u < u_end && ok; ++done) {
+    bool ok = true, staged = false;  // staged: the coming piece's queries are in TMEM already
+    for (int u = u_begin; u < u_end && ok;) {
       const MtPiece pc = piece_at(u);
       const int n = pc.n_units;
+      u = pc.next;
+      if (n == 0) continue;
+      if (!staged && !stage_queries(g0 + MT_Q_SLOTS * done)) break;
       const int j0 = pc.unit0 * MT_POS;
       // New token `row / heads` sees the positions before lengths[b] - T + token + 1.
       const int limit = min(pc.len - p.T + row / p.heads + 1, pc.len);
@@ -737,7 +756,8 @@ __global__ void __launch_bounds__(MT_THREADS, 1)
       }
       if (!ok) break;
       // The next piece's queries go in while the last P V runs: its first Q K^T then overlaps the flush below.
-      if (u + n < u_end && !stage_queries(g0 + n + MT_Q_SLOTS * (done + 1))) break;
+      staged = pc.more;
+      if (staged && !stage_queries(g0 + n + MT_Q_SLOTS * (done + 1))) break;
       {
         const bool od = mbar_wait(o_done, (g0 + n - 1) & 1, abort_flag, p.status, TJX_ERR_WAIT_OTHER);
         if (!__all_sync(0xFFFFFFFFu, od)) break;
@@ -782,13 +802,13 @@ __global__ void __launch_bounds__(MT_THREADS, 1)
       // first P V waits for before it overwrites O. (Partials are merged by mla_tc_merge_kernel, launched behind this.)
       tc_fence_before_sync();
       g0 += n;
-      u += n;
+      ++done;
     }
   }
 
   tc_fence_before_sync();
   __syncthreads();
-  if (prof != nullptr && threadIdx.x == 0) prof[7] = clock64();
+  if (prof != nullptr && threadIdx.x == 0) prof[7] = clock64(), prof[13] = static_cast<long long>(globaltimer_ns());
   if (warp == 1) {
     if (*abort_flag) __nanosleep(100000);
     tc_fence_after_sync();
@@ -814,6 +834,7 @@ __global__ void __launch_bounds__(MG_WARPS * 32)
     for (int b0 = 0; b0 < p.B; b0 += 32) {
       const int i = b0 + lane;
       int x = i < p.B ? (min(max(p.lengths[i], 0), p.S) + MT_POS - 1) / MT_POS : 0;
+      if (x > 0) x += MT_PIECE_COST;
 #pragma unroll
       for (int d = 1; d < 32; d <<= 1) {
         const int y = __shfl_up_sync(0xFFFFFFFFu, x, d);
@@ -831,8 +852,8 @@ __global__ void __launch_bounds__(MG_WARPS * 32)
   __syncthreads();
   const int f = seq_units[0], l = seq_units[1], total = seq_units[2];
   if (l == f) return;  // no position: the main kernel wrote zeros
-  const int share = max(MT_MIN_SHARE, (total + main_ctas - 1) / main_ctas);
-  const int first_cta = f / share;
+  const int share = max(MT_MIN_SHARE + MT_PIECE_COST, (total + main_ctas - 1) / main_ctas);
+  const int first_cta = (f + MT_PIECE_COST) / share;
   const int n = (l - 1) / share - first_cta + 1;
   if (n <= 1) return;  // written directly
   const int group = blockIdx.y >> 2, q = blockIdx.y & 3, c = warp;
@@ -840,23 +861,43 @@ __global__ void __launch_bounds__(MG_WARPS * 32)
   const int row = group * MT_ROWS + r;
   asm volatile("griddepcontrol.wait;" ::: "memory");  // the partials are the main kernel's
   const size_t block0 = (static_cast<size_t>(first_cta) + b) * groups + group;  // piece i: block0 + i * groups
-  float mx = MLA_MASK;
-  for (int i = 0; i < n; ++i) mx = fmaxf(mx, __ldcg(p.ws_m + (block0 + static_cast<size_t>(i) * groups) * MT_ROWS + r));
-  float lsum = 0.f;
+  // Four pieces at a time, all their loads issued before the first is used (the kernel is a handful of dependent
+  // round trips to L2 long, nothing else), folded into a running (max, sum, accumulator) as the softmax itself is.
+  constexpr int MG_CHUNK = 4;
+  float mx = MLA_MASK, lsum = 0.f;
   float4 o[8];
 #pragma unroll
   for (int x = 0; x < 8; ++x) o[x] = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 2
-  for (int i = 0; i < n; ++i) {
-    const size_t block = block0 + static_cast<size_t>(i) * groups;
-    const float w = __expf(__ldcg(p.ws_m + block * MT_ROWS + r) - mx);
-    lsum += w * __ldcg(p.ws_l + block * MT_ROWS + r);
-    const float4* src = reinterpret_cast<const float4*>(p.ws_acc + block * (MT_ROWS * MLA_C)) + ((q * 8 + c) * 8) * 32 + lane;
+  for (int i0 = 0; i0 < n; i0 += MG_CHUNK) {
+    float m[MG_CHUNK], ls[MG_CHUNK];
+    float4 a[MG_CHUNK][8];
 #pragma unroll
-    for (int x = 0; x < 8; ++x) {
-      const float4 a = __ldcg(src + x * 32);
-      o[x].x = fmaf(w, a.x, o[x].x), o[x].y = fmaf(w, a.y, o[x].y);
-      o[x].z = fmaf(w, a.z, o[x].z), o[x].w = fmaf(w, a.w, o[x].w);
+    for (int k = 0; k < MG_CHUNK; ++k) {
+      const bool live = i0 + k < n;
+      const size_t block = block0 + static_cast<size_t>(live ? i0 + k : i0) * groups;
+      m[k] = live ? __ldcg(p.ws_m + block * MT_ROWS + r) : MLA_MASK;
+      ls[k] = live ? __ldcg(p.ws_l + block * MT_ROWS + r) : 0.f;
+      const float4* src = reinterpret_cast<const float4*>(p.ws_acc + block * (MT_ROWS * MLA_C)) + ((q * 8 + c) * 8) * 32 + lane;
+#pragma unroll
+      for (int x = 0; x < 8; ++x) a[k][x] = live ? __ldcg(src + x * 32) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float m_new = mx;
+#pragma unroll
+    for (int k = 0; k < MG_CHUNK; ++k) m_new = fmaxf(m_new, m[k]);
+    const float keep = __expf(mx - m_new);
+    mx = m_new;
+    lsum *= keep;
+#pragma unroll
+    for (int x = 0; x < 8; ++x) o[x].x *= keep, o[x].y *= keep, o[x].z *= keep, o[x].w *= keep;
+#pragma unroll
+    for (int k = 0; k < MG_CHUNK; ++k) {
+      const float w = i0 + k < n ? __expf(m[k] - mx) : 0.f;
+      lsum = fmaf(w, ls[k], lsum);
+#pragma unroll
+      for (int x = 0; x < 8; ++x) {
+        o[x].x = fmaf(w, a[k][x].x, o[x].x), o[x].y = fmaf(w, a[k][x].y, o[x].y);
+        o[x].z = fmaf(w, a[k][x].z, o[x].z), o[x].w = fmaf(w, a[k][x].w, o[x].w);
+      }
     }
   }
   if (row >= p.H) return;

@@ -124,7 +124,8 @@ __device__ __forceinline__ bool mbar_wait_timed(uint32_t bar, uint32_t parity, v
 //           slot A's first softmax warp: [12] cycles busy, [13] cycles waiting for scores, [14] blocks,
 //           [15] three 21-bit fields, high to low: cycles in the TMEM load, in the row max (and rescale), in the
 //           exponentials. MLA decode (tcgen05 kernel): [8] as attention's, [9] cycles issuing score MMAs, [10] cycles
-//           issuing output MMAs, [11] pieces; work items are units of 32 positions.
+//           issuing output MMAs, [11] pieces, [12] and [13] %globaltimer (ns) at CTA start and end; work items are units of
+//           32 positions.
 //           All-gather matmul: [10] cycles this CTA's producer waited for gathered rows to arrive, [11] clock when
 //           its copier warp had posted its last block
 constexpr int PROFILE_WORDS = 16;
