@@ -62,6 +62,24 @@ def test_several_new_tokens_each_see_the_positions_up_to_their_own(tokens, heads
     assert np.abs(f64(got[:, -1:]) - f64(single)).max() <= 2e-2
 
 
+@pytest.mark.parametrize(("batch", "heads", "longest", "seed"), [(200, 16, 96, 0), (333, 64, 40, 1), (150, 32, 700, 2)])
+def test_many_short_and_empty_sequences_share_the_ctas(batch, heads, longest, seed):
+    # More sequences than CTAs, a third of them empty, many of a single 32-position unit: a CTA's range then crosses
+    # several sequences, ends inside the margin the split counts in front of a sequence, or holds whole sequences
+    # that are written without a merge. Every row against float64; empty sequences are zeros.
+    rng = np.random.default_rng(seed)
+    S = 1024
+    lengths = rng.integers(1, longest + 1, batch).astype(np.int32)
+    lengths[rng.random(batch) < 0.33] = 0
+    lengths[-1] = S
+    q_c, q_r, c_kv, k_rope = mla_inputs(batch, heads, S, seed=20 + seed)
+    got = run(q_c, q_r, c_kv, k_rope, lengths, 256)
+    want = oracle.mla_decode_f64(q_c, q_r, c_kv, k_rope, lengths)
+    assert np.abs(f64(got) - want).max() <= 2e-2
+    assert not f64(got[lengths == 0]).any()
+    np.testing.assert_array_equal(f64(got), f64(run(q_c, q_r, c_kv, k_rope, lengths, 256)))
+
+
 def test_block_size_is_only_a_schedule():
     # The same cache walked in blocks of 64 or 512 positions agrees to rounding; two calls in a row agree exactly.
     q_c, q_r, c_kv, k_rope = mla_inputs(8, 16, 2048, seed=5)
@@ -81,3 +99,34 @@ def test_unsupported_shapes_are_errors():
     q_c, q_r, c_kv, k_rope = mla_inputs(2, 16, 128)
     with pytest.raises(NativeError, match="multiple of 16 positions"):
         run(q_c, q_r, c_kv, k_rope, lengths, 8)
+
+
+def test_the_kernel_shares_units_out_as_the_host_side_statement_says():
+    # The counters every CTA of the tcgen05 kernel leaves (units and pieces it ran) against schedule.mla_unit_ranges.
+    import ctypes
+
+    import torch
+
+    from tilejax_b200 import schedule
+    from tilejax_b200._lib import check, library
+
+    rng = np.random.default_rng(3)
+    batch, heads, S = 40, 64, 2048
+    lengths = rng.integers(0, S + 1, batch).astype(np.int32)
+    lengths[::7] = 0
+    q_c, q_r, c_kv, k_rope = mla_inputs(batch, heads, S, seed=30)
+    dev = [to_device(a) for a in (q_c, q_r, c_kv, k_rope, lengths)]
+    ctas = min(256, torch.cuda.get_device_properties(0).multi_processor_count)
+    buf = torch.zeros(ctas * 16, dtype=torch.int64, device="cuda")
+    check(library().tjx_set_profile_buffer(ctypes.c_void_p(buf.data_ptr()), buf.numel() * 8))
+    try:
+        got = to_host(ops.mla_decode(*dev, 512))
+        torch.cuda.synchronize()
+    finally:
+        check(library().tjx_set_profile_buffer(None, 0))
+    assert ops.device_status() == 0
+    records = buf.cpu().numpy().reshape(ctas, 16)
+    want = schedule.mla_unit_ranges(lengths, ctas)
+    np.testing.assert_array_equal(records[:, 6], [sum(n for _, _, n in pieces) for pieces in want])
+    np.testing.assert_array_equal(records[:, 11], [len(pieces) for pieces in want])
+    assert np.abs(f64(got) - oracle.mla_decode_f64(q_c, q_r, c_kv, k_rope, lengths)).max() <= 2e-2

@@ -392,7 +392,8 @@ constexpr int MT_MAX_CTAS = 256;                             // CTAs per 64-row 
 constexpr int MT_MIN_SHARE = 2;                              // units a CTA takes at least
 // What starting a piece costs (its queries into TMEM, the pipeline filling, its flush), in units: measured 5 200
 // cycles against 1 340 a unit. The units are shared out with this much counted in front of every sequence, so that
-// a CTA whose range crosses into another sequence gets fewer units.
+// a CTA whose range crosses into another sequence gets fewer units. (tilejax_b200/schedule.py states the same
+// arithmetic on the host, `mla_unit_ranges`, with these three constants; a test compares the two.)
 constexpr int MT_PIECE_COST = 3;
 constexpr float MT_RESCALE_THRESHOLD = 8.0f;
 

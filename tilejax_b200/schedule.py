@@ -280,3 +280,53 @@ def collective_row_blocks(me: int, chips: int, shard_blocks: int) -> np.ndarray:
     i_blk = np.arange(chips * shard_blocks)
     r, within = np.divmod(i_blk, shard_blocks)
     return (((me + chips - r) % chips) * shard_blocks + within).astype(np.int32)
+
+
+MLA_UNIT = 32        # positions per unit of the tcgen05 MLA decode kernel's work
+MLA_PIECE_COST = 3   # what starting on a sequence costs a CTA, in units
+MLA_MIN_SHARE = 2    # units a CTA takes at least
+
+
+def mla_unit_ranges(lengths: Sequence[int], ctas: int) -> list[list[tuple[int, int, int]]]:
+    """How the tcgen05 MLA decode kernel shares a launch's work out, as the kernel itself derives it from `lengths`
+    (every CTA runs the same arithmetic; there is no table): per CTA the list of its pieces (sequence, first unit,
+    units). A sequence's cache is cut into units of 32 positions; the units of all sequences lie on one line with
+    MLA_PIECE_COST more positions in front of every sequence that has any, and CTA c takes the positions
+    [c * share, (c + 1) * share) of that line, share = max(MLA_MIN_SHARE + MLA_PIECE_COST, ceil(line / ctas)): a CTA
+    whose range crosses into another sequence gets fewer units, by about what starting a piece costs it. The pieces of
+    a sequence come from consecutive CTAs, first = (start of its units) // share, so its partials sit at consecutive
+    workspace indices (CTA + sequence) and the merge kernel finds them with the same arithmetic."""
+    units = [(max(int(n), 0) + MLA_UNIT - 1) // MLA_UNIT for n in lengths]
+    before = [0]
+    for n in units:
+        before.append(before[-1] + (n + MLA_PIECE_COST if n else 0))
+    line = before[-1]
+    share = max(MLA_MIN_SHARE + MLA_PIECE_COST, -(-line // max(ctas, 1)))
+    out: list[list[tuple[int, int, int]]] = []
+    for c in range(ctas):
+        begin = min(c * share, line)
+        end = min(begin + share, line)
+        pieces = []
+        u = begin
+        while u < end:
+            b = max(i for i in range(len(units)) if before[i] <= u)
+            first_unit = before[b] + MLA_PIECE_COST
+            start, stop = max(u, first_unit), min(end, before[b + 1])
+            if stop > start:
+                pieces.append((b, start - first_unit, stop - start))
+            u = min(end, before[b + 1])
+        out.append(pieces)
+    return out
+
+
+def mla_pieces_of(lengths: Sequence[int], ctas: int, b: int) -> tuple[int, int]:
+    """(first CTA, number of pieces) of sequence `b` under `mla_unit_ranges`, by the merge kernel's closed form."""
+    units = [(max(int(n), 0) + MLA_UNIT - 1) // MLA_UNIT for n in lengths]
+    before = [0]
+    for n in units:
+        before.append(before[-1] + (n + MLA_PIECE_COST if n else 0))
+    if before[b + 1] == before[b]:
+        return 0, 0
+    share = max(MLA_MIN_SHARE + MLA_PIECE_COST, -(-before[-1] // max(ctas, 1)))
+    first = (before[b] + MLA_PIECE_COST) // share
+    return first, (before[b + 1] - 1) // share - first + 1
