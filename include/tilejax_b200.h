@@ -208,7 +208,7 @@ int tjx_rpa_write_bf16(void* kv_cache, const void* keys, const void* values, con
                        int S, int Hkv, int D, int page_size, int pages_per_seq, int num_pages, tjx_stream_t stream);
 
 /* Bytes of scratch tjx_rpa_decode_bf16 needs for these sizes. */
-size_t tjx_rpa_decode_workspace_bytes(int T, int S, int H, int D, int pages_per_seq);
+size_t tjx_rpa_decode_workspace_bytes(int T, int S, int H, int D, int page_size, int pages_per_seq);
 
 /* Ragged paged attention, the decode case (`rpa_decode`, examples/ragged_paged_attention.py:121-149): sequence
  * s < distribution[0] is token s; its query row q[s] [H, D] attends over the kv_lens[s] positions of its pages in the

@@ -80,6 +80,7 @@ struct DecodeParams {
   float score_scale;             // scores are multiplied by this before the base-2 exponential: log2(e), times the
                                  // softmax scale when the queries do not arrive pre-scaled (ragged paged attention)
   long long kv_head_stride, kv_token_stride;  // elements between KV heads / tokens in the page pools (0: packed)
+  int min_share;                 // steps a CTA takes at least (what bounds the partials a sequence can have)
   int* status;
   long long* profile;            // per-CTA counters (PROFILE_WORDS each) or null
 };
@@ -248,7 +249,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, WIDE ? (TJX_DEC_CTAS * 2 / 3) 
   bool ok = true;
   // A persistent CTA takes one contiguous share of the steps that run — the same number for every CTA, at least
   // DEC_CHUNK — so ragged lengths balance to within a step and a sequence is cut into as few pieces as possible.
-  const int per = max(DEC_CHUNK, (n_steps + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x));
+  const int per = max(p.min_share, (n_steps + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x));
   const int r_begin = min(n_steps, static_cast<int>(blockIdx.x) * per), r_end = min(n_steps, r_begin + per);
 
   uint32_t qa[8][2 * NR];  // A fragments of Q: k-step j = dims 16 j .. + 15; row x: [2x] = dims + 2t, + 1, [2x + 1] = + 8
@@ -537,7 +538,7 @@ static int launch_decode_chunks(DecodeParams& p, int group, cudaStream_t s) {
                                CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
   const long long capacity = static_cast<long long>(p.B) * p.pages_per_seq;
-  const int chunks = static_cast<int>((capacity + DEC_CHUNK - 1) / DEC_CHUNK);
+  const int chunks = static_cast<int>((capacity + p.min_share - 1) / p.min_share);
   const int groups = (p.Hkv + DEC_WARPS - 1) / DEC_WARPS;
   const bool wide = p.T * group > 8;  // more than 8 query rows per KV head: both halves of the MMA's 16 rows
   // As many CTAs as are resident at once (never more than there are chunks of DEC_CHUNK steps): each takes an equal
@@ -553,15 +554,25 @@ static int launch_decode_chunks(DecodeParams& p, int group, cudaStream_t s) {
   }
 }
 
-static int decode_slots(int pages_per_seq) { return (pages_per_seq + DEC_CHUNK - 1) / DEC_CHUNK + 1; }
+// Partials a sequence can have: the shares (of at least `min_share` steps) its pages_per_seq steps can fall in.
+static int decode_slots(int pages_per_seq, int min_share = DEC_CHUNK) {
+  return (pages_per_seq + min_share - 1) / min_share + 1;
+}
+
+// The least share for pages of `page_size` tokens: DEC_CHUNK pages of 16, as many tokens in larger pages. (With
+// pages of 128 a share of DEC_CHUNK steps is 1536 tokens: 32 sequences of ~2000 tokens then keep a quarter of the
+// resident warps busy and the kernel streams at 3 TB/s.)
+static int min_share_for_pages_of(int page_size) {
+  return std::max(1, (DEC_CHUNK * DEC_SUB + page_size - 1) / page_size);
+}
 
 static size_t align256(size_t n) { return (n + 255) & ~static_cast<size_t>(255); }
 
 // Scratch layout, with rows = T * H query rows per sequence: max [B, slots, rows] | sum [B, slots, rows] |
 // accumulators [B, slots, rows, D] | arrival counters [B, Hkv] (room for H per sequence). Nothing in it has to start at zero: the step-table kernel clears the
 // counters at the start of every call, and every partial that is read was written earlier in the same call.
-static size_t decode_scratch_bytes(int B, int T, int H, int D, int pages_per_seq) {
-  const size_t rows = static_cast<size_t>(B) * decode_slots(pages_per_seq) * T * H;
+static size_t decode_scratch_bytes(int B, int T, int H, int D, int pages_per_seq, int min_share = DEC_CHUNK) {
+  const size_t rows = static_cast<size_t>(B) * decode_slots(pages_per_seq, min_share) * T * H;
   return 2 * align256(rows * sizeof(float)) + align256(rows * D * sizeof(float)) +
          align256(static_cast<size_t>(B) * H * sizeof(int));
 }
@@ -597,8 +608,9 @@ static int run_decode(const void* q, const void* k_pages, const void* v_pages, c
                       const int32_t* lengths, void* out, int B, int T, int H, int Hkv, int page_size,
                       int pages_per_seq, int num_pages, int32_t* step_tile, int32_t* step_code, int32_t* step_count,
                       int32_t* tile_first, void* scratch, cudaStream_t s, float softmax_scale = 1.0f,
-                      long long kv_head_stride = 0, long long kv_token_stride = 0) {
+                      long long kv_head_stride = 0, long long kv_token_stride = 0, int min_share = DEC_CHUNK) {
   DecodeParams p{};
+  p.min_share = min_share;
   p.score_scale = DEC_LOG2E * softmax_scale;
   p.kv_head_stride = kv_head_stride, p.kv_token_stride = kv_token_stride;
   p.q = static_cast<const __nv_bfloat16*>(q);
@@ -609,7 +621,7 @@ static int run_decode(const void* q, const void* k_pages, const void* v_pages, c
   p.B = B, p.H = H, p.Hkv = Hkv, p.page_size = page_size, p.pages_per_seq = pages_per_seq, p.num_pages = num_pages;
   p.T = T, p.rows = T * H;
   p.self_steps = B <= DEC_SELF_MAX_B ? 1 : 0;
-  p.slots = decode_slots(pages_per_seq);
+  p.slots = decode_slots(pages_per_seq, min_share);
   const size_t rows = static_cast<size_t>(B) * p.slots * p.rows;
   uint8_t* ws = static_cast<uint8_t*>(scratch);
   p.ws_m = reinterpret_cast<float*>(ws);
@@ -721,7 +733,7 @@ struct RpaScratch {
   size_t bytes;
 };
 
-static RpaScratch rpa_scratch(void* workspace, int n, int H, int pages_per_seq) {
+static RpaScratch rpa_scratch(void* workspace, int n, int H, int page_size, int pages_per_seq) {
   uint8_t* w = static_cast<uint8_t*>(workspace);
   size_t at = 0;
   auto take = [&](size_t bytes) {
@@ -736,7 +748,7 @@ static RpaScratch rpa_scratch(void* workspace, int n, int H, int pages_per_seq) 
   r.step_count = reinterpret_cast<int32_t*>(take(4));
   r.tile_first = reinterpret_cast<int32_t*>(take(static_cast<size_t>(n + 1) * 4));
   r.result = reinterpret_cast<__nv_bfloat16*>(take(static_cast<size_t>(n) * H * DEC_D * 2));
-  r.decode = take(decode_scratch_bytes(n, 1, H, DEC_D, pages_per_seq));
+  r.decode = take(decode_scratch_bytes(n, 1, H, DEC_D, pages_per_seq, min_share_for_pages_of(page_size)));
   r.bytes = at;
   return r;
 }
@@ -767,9 +779,9 @@ int tjx_rpa_write_bf16(void* kv_cache, const void* keys, const void* values, con
   return 0;
 }
 
-size_t tjx_rpa_decode_workspace_bytes(int T, int S, int H, int D, int pages_per_seq) {
-  if (T <= 0 || S <= 0 || H <= 0 || D <= 0 || pages_per_seq <= 0) return 0;
-  return tjx::rpa_scratch(nullptr, std::min(S, T), H, pages_per_seq).bytes;
+size_t tjx_rpa_decode_workspace_bytes(int T, int S, int H, int D, int page_size, int pages_per_seq) {
+  if (T <= 0 || S <= 0 || H <= 0 || D <= 0 || page_size <= 0 || pages_per_seq <= 0) return 0;
+  return tjx::rpa_scratch(nullptr, std::min(S, T), H, page_size, pages_per_seq).bytes;
 }
 
 int tjx_rpa_decode_bf16(const void* q, void* out, const void* kv_cache, const int32_t* kv_lens,
@@ -780,12 +792,12 @@ int tjx_rpa_decode_bf16(const void* q, void* out, const void* kv_cache, const in
   if (int rc = check_device()) return rc;
   if (!kv_lens || !page_indices || !distribution) return fail(TJX_E_ARG, "an index array pointer is null");
   const int n = std::min(S, T);  // sequence s is token s
-  const size_t need = tjx_rpa_decode_workspace_bytes(T, S, H, D, pages_per_seq);
+  const size_t need = tjx_rpa_decode_workspace_bytes(T, S, H, D, page_size, pages_per_seq);
   if (T <= 0 || S <= 0 || need == 0) return fail(TJX_E_ARG, "sizes must be positive");
   if (workspace == nullptr || workspace_bytes < need)
     return fail(TJX_E_ARG, "workspace is null or smaller than tjx_rpa_decode_workspace_bytes");
   if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(TJX_E_ARG, "workspace must be 256-byte aligned");
-  const RpaScratch w = rpa_scratch(workspace, n, H, pages_per_seq);
+  const RpaScratch w = rpa_scratch(workspace, n, H, page_size, pages_per_seq);
   const __nv_bfloat16* cache = static_cast<const __nv_bfloat16*>(kv_cache);
   if (int rc = check_decode_args(q, cache, cache == nullptr ? nullptr : cache + DEC_D, page_indices, w.lengths, out, n, 1,
                                  H, Hkv, D, page_size, pages_per_seq, num_pages, w.step_tile, w.step_code, w.step_count,
@@ -799,7 +811,7 @@ int tjx_rpa_decode_bf16(const void* q, void* out, const void* kv_cache, const in
   TJX_CUDA(cudaGetLastError());
   if (int rc = run_decode(q, cache, cache + DEC_D, page_indices, w.lengths, w.result, n, 1, H, Hkv, page_size,
                           pages_per_seq, num_pages, w.step_tile, w.step_code, w.step_count, w.tile_first, w.decode, s,
-                          sm_scale, 2 * DEC_D, static_cast<long long>(Hkv) * 2 * DEC_D))
+                          sm_scale, 2 * DEC_D, static_cast<long long>(Hkv) * 2 * DEC_D, min_share_for_pages_of(page_size)))
     return rc;
   rpa_decode_scatter_kernel<<<n, 128, 0, s>>>(w.result, static_cast<__nv_bfloat16*>(out), distribution, H * DEC_D);
   TJX_CUDA(cudaGetLastError());

@@ -491,7 +491,7 @@ def rpa_decode(q: torch.Tensor, kv_cache: torch.Tensor, kv_lens: torch.Tensor, p
     elif out.shape != q.shape or out.dtype != q.dtype or not out.is_contiguous() or out.device != q.device:
         raise ValueError("out must look like q")
     with torch.cuda.device(device):
-        need = int(library().tjx_rpa_decode_workspace_bytes(T, S, H, D, pps))
+        need = int(library().tjx_rpa_decode_workspace_bytes(T, S, H, D, page_size, pps))
         key = (str(device), need)
         ws = _rpa_workspaces.get(key)
         if ws is None:
