@@ -443,6 +443,13 @@ constexpr int PAIR_STAGES = 3;
 constexpr int PAIR_KSUB = 2;
 constexpr int PAIR_STAGES_128 = 4;  // 128-wide pieces stage 8 KB less per K block: a fourth slot fits
 
+// A causal launch's work items are of two kinds — pieces that compute and pieces that are only written with zeros —
+// and item w, w + pairs, w + 2 pairs, ... can hold nine of the first kind for one pair of CTAs and seven for another.
+// Such a launch numbers the two kinds separately in its prologue (a warp scan over all items) and pair r takes the
+// r-th, (r + pairs)-th, ... of each: no pair computes more than one piece above the mean. The lists live in shared
+// memory, this many entries each; a launch whose share would not fit walks the items the plain way.
+constexpr int PAIR_LIST_CAP = 128;
+
 constexpr int GATHER_THREADS = GEMM_THREADS + 32;  // the pair kernel with its copier warp
 // 16-byte loads a copier lane keeps in flight: 148 warps x 32 lanes x 32 x 16 B = 2.4 MB on the wire, what a few
 // microseconds of NVLink latency need at several hundred GB/s.
@@ -483,7 +490,9 @@ struct PairSmem {
   static constexpr int RING_OFF = 0;
   static constexpr int C_OFF = STAGES * STAGE_BYTES;
   static constexpr int BAR_OFF = C_OFF + C_BYTES;
-  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+  static constexpr int LIST_OFF = BAR_OFF + 256;        // two lists of work items (see PAIR_LIST_CAP)
+  static constexpr int TOTAL = LIST_OFF + 2 * PAIR_LIST_CAP * 4 + 1024;
+  static_assert(TOTAL <= 227 * 1024, "the pair kernel's shared memory fits one CTA per SM");
 };
 
 // PBN = columns of a piece (the N of the pair's MMA): 256, or 128 as an A/B switch (half-size pieces; slower: more
@@ -533,15 +542,53 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
     tma_prefetch_desc(&map_c);
     if (GATHER) tma_prefetch_desc(&map_a_own);
   }
+  int* list_compute = reinterpret_cast<int*>(base_ptr + L::LIST_OFF);
+  int* list_zero = list_compute + PAIR_LIST_CAP;
+  volatile int* list_meta = abort_flag + 1;  // [0] lists in use, [1] computing items of this pair, [2] the others
   if (warp == 1) {
     tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_holder)), TMEM_COLS);
     tmem_relinquish_pair();
+  } else if (warp == 2) {
+    int use = 0, mine_c = 0, mine_z = 0;
+    if (!GATHER && p.causal) {
+      int seen_c = 0, seen_z = 0;
+      constexpr int SCAN = 8;  // items a lane decodes per pass: their table reads are in flight together
+      for (int w0 = 0; w0 < total_items; w0 += 32 * SCAN) {
+        bool in[SCAN], computes[SCAN];
+#pragma unroll
+        for (int u = 0; u < SCAN; ++u) {
+          const int w = w0 + u * 32 + lane;
+          in[u] = w < total_items;
+          computes[u] = in[u] && decode_item<PAIR_ROWS, BN>(p, w).compute;
+        }
+#pragma unroll
+        for (int u = 0; u < SCAN; ++u) {
+          const uint32_t mc = __ballot_sync(0xFFFFFFFFu, computes[u]), mz = __ballot_sync(0xFFFFFFFFu, in[u] && !computes[u]);
+          if (in[u]) {
+            const uint32_t below = (1u << lane) - 1u;
+            const int index = computes[u] ? seen_c + __popc(mc & below) : seen_z + __popc(mz & below);
+            if (index % n_pairs == pair && index / n_pairs < PAIR_LIST_CAP)
+              (computes[u] ? list_compute : list_zero)[index / n_pairs] = w0 + u * 32 + lane;
+          }
+          seen_c += __popc(mc), seen_z += __popc(mz);
+        }
+      }
+      mine_c = seen_c > pair ? (seen_c - pair + n_pairs - 1) / n_pairs : 0;
+      mine_z = seen_z > pair ? (seen_z - pair + n_pairs - 1) / n_pairs : 0;
+      use = mine_c <= PAIR_LIST_CAP && mine_z <= PAIR_LIST_CAP;
+    }
+    if (lane == 0) list_meta[0] = use, list_meta[1] = mine_c, list_meta[2] = mine_z;
   }
   tc_fence_before_sync();
   __syncthreads();
   cluster_sync_all();  // the peer's barriers are initialised before anything of ours can reach them
   tc_fence_after_sync();
   const uint32_t tmem_base = __shfl_sync(0xFFFFFFFFu, *tmem_holder, 0);
+  // This pair's walk: its list of computing items, or items pair, pair + pairs, ... of every kind.
+  const bool listed = __shfl_sync(0xFFFFFFFFu, list_meta[0], 0) != 0;
+  const int n_walk = __shfl_sync(0xFFFFFFFFu, listed ? list_meta[1]
+                                                     : (total_items > pair ? (total_items - pair + n_pairs - 1) / n_pairs : 0), 0);
+  auto item_of = [&](int idx) { return listed ? list_compute[idx] : pair + idx * n_pairs; };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer (one per CTA)
@@ -551,8 +598,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
       bool ok = true;
       long long gather_waited = 0;
       const int row_off = static_cast<int>(rank) * BM, col_off = static_cast<int>(rank) * (BN / 2);
-      for (int w = pair; w < total_items && ok; w += n_pairs) {
-        const Item it = decode_item<PAIR_ROWS, BN>(p, w);
+      for (int idx = 0; idx < n_walk && ok; ++idx) {
+        const Item it = decode_item<PAIR_ROWS, BN>(p, item_of(idx));
         if (!it.compute) continue;
         bool own = true;
         if (GATHER) {
@@ -616,8 +663,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
       auto wait = [&](uint32_t bar, uint32_t parity, int code, long long& waited) {
         return __all_sync(0xFFFFFFFFu, mbar_wait_timed(bar, parity, abort_flag, p.status, code, waited, prof != nullptr)) != 0;
       };
-      for (int w = pair; w < total_items && ok; w += n_pairs) {
-        const Item it = decode_item<PAIR_ROWS, BN>(p, w);
+      for (int idx = 0; idx < n_walk && ok; ++idx) {
+        const Item it = decode_item<PAIR_ROWS, BN>(p, item_of(idx));
         if (!__shfl_sync(0xFFFFFFFFu, static_cast<int>(it.compute), 0)) continue;
         if (items++ == 0) t_first = clock64();
         if (!wait(tempty_bar(acc), acc_phase ^ 1u, TJX_ERR_WAIT_TMEM_EMPTY, out_wait)) break;
@@ -703,8 +750,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
     const uint32_t c_smem = base + L::C_OFF + ew * (2 * 32 * 128);
     uint8_t* c_ptr = base_ptr + L::C_OFF + ew * (2 * 32 * 128);
     int c_buf = 0;
-    for (int w = pair; w < total_items; w += n_pairs) {
-      const Item it = decode_item<PAIR_ROWS, BN>(p, w);
+    // With lists: first the items that only write zeros (their stores run under the first pieces' loads).
+    for (int idx = 0, n_zero = listed ? list_meta[2] : 0; idx < n_zero; ++idx) {
+      const Item it = decode_item<PAIR_ROWS, BN>(p, list_zero[idx]);
+      if (!it.valid) {
+        if (lane == 0 && p.status != nullptr) atomicCAS(p.status, 0, TJX_ERR_BAD_TABLE);
+        continue;
+      }
+      zero_rows<BN>(p, it.m0 + static_cast<int>(rank) * BM + q * 32, it.n0, lane);
+    }
+    for (int idx = 0; idx < n_walk; ++idx) {
+      const Item it = decode_item<PAIR_ROWS, BN>(p, item_of(idx));
       if (!it.valid) {
         if (lane == 0 && p.status != nullptr) atomicCAS(p.status, 0, TJX_ERR_BAD_TABLE);
         continue;
