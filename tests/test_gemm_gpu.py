@@ -150,6 +150,11 @@ def test_dense_4096_against_sampled_float64_rows_and_linearity():
     ((1024, 8192, 512), (256, 256, 512), {}),                     # a long reduction: many trips round the ring
     ((2048, 256, 2048), (512, 256, 256), {"causal": True}),
     ((4096, 512, 4096), (512, 512, 512), {}),                     # more pieces than SM pairs: persistent loop
+    # A last round that keeps at most half the SM pairs busy is run on half pieces (N = 128), two pairs a piece:
+    ((2560, 256, 2560), (256, 256, 256), {}),                     # 100 pieces: 74 + 26
+    ((2560, 320, 2560), (512, 256, 64), {"out_f32": True}),
+    ((3584, 256, 3584), (512, 512, 256), {"causal": True}),       # 105 computing pieces: 74 + 31, dealt out from lists
+    ((3328, 128, 3328), (256, 256, 128), {"causal": True}),       # 91 = 74 + 17
 ])
 def test_sm_pairs_and_single_ctas_agree_bit_for_bit(shape, tiles, kw):
     # One MMA per pair of SMs (256 x 256 pieces) and one per SM (128 x 256) sum K in the same order.

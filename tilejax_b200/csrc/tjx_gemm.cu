@@ -46,6 +46,7 @@ struct GemmParams {
   const int32_t* fill_i;
   const int32_t* fill_j;
   int causal, out_f32, b_kmajor;
+  int tail_split;        // the pair kernel may halve the pieces of a short last round (see its header)
   int num_kb;
   void* out;
   int* status;
@@ -141,9 +142,9 @@ __device__ __forceinline__ void zero_rows(const GemmParams& p, int row0, int n0,
 template <int BN>
 __device__ __forceinline__ void store_accumulator(const GemmParams& p, const CUtensorMap* map_c, uint32_t t_row,
                                                   int row0, int n0, uint8_t* c_ptr, uint32_t c_smem, int& c_buf,
-                                                  int lane) {
+                                                  int lane, int columns = BN) {
   const int row = row0 + lane;
-  constexpr int CHUNKS = BN / 32;
+  const int CHUNKS = columns / 32;
   const float scale = p.row_scale != nullptr && row < p.M ? p.row_scale[row] : 1.0f;
 #pragma unroll 1
   for (int c = 0; c < CHUNKS; ++c) {
@@ -448,7 +449,16 @@ constexpr int PAIR_STAGES_128 = 4;  // 128-wide pieces stage 8 KB less per K blo
 // Such a launch numbers the two kinds separately in its prologue (a warp scan over all items) and pair r takes the
 // r-th, (r + pairs)-th, ... of each: no pair computes more than one piece above the mean. The lists live in shared
 // memory, this many entries each; a launch whose share would not fit walks the items the plain way.
+//
+// A short last round: with P computing pieces and n pairs, the last of ceil(P / n) rounds holds P mod n pieces and the
+// other pairs wait for it (10 of 74 for the causal 8192^2, 34 of 74 for 4096^3). When at most half the pairs would
+// be busy, each of those pieces is cut into its left and right 128 columns and two pairs take one each (an MMA with
+// N = 128, half of the B tile staged, half of the accumulator stored): the round lasts half as long. K is summed in
+// the same order, so the result is bit-identical. Pair r finds the piece of pair r / 2 in a third list.
 constexpr int PAIR_LIST_CAP = 128;
+#ifndef TJX_GEMM_TAIL_SPLIT
+#define TJX_GEMM_TAIL_SPLIT 1  // 0: never halve the pieces of a short last round (an A/B switch)
+#endif
 
 constexpr int GATHER_THREADS = GEMM_THREADS + 32;  // the pair kernel with its copier warp
 // 16-byte loads a copier lane keeps in flight: 148 warps x 32 lanes x 32 x 16 B = 2.4 MB on the wire, what a few
@@ -491,7 +501,7 @@ struct PairSmem {
   static constexpr int C_OFF = STAGES * STAGE_BYTES;
   static constexpr int BAR_OFF = C_OFF + C_BYTES;
   static constexpr int LIST_OFF = BAR_OFF + 256;        // two lists of work items (see PAIR_LIST_CAP)
-  static constexpr int TOTAL = LIST_OFF + 2 * PAIR_LIST_CAP * 4 + 1024;
+  static constexpr int TOTAL = LIST_OFF + 3 * PAIR_LIST_CAP * 4 + 1024;
   static_assert(TOTAL <= 227 * 1024, "the pair kernel's shared memory fits one CTA per SM");
 };
 
@@ -544,7 +554,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
   }
   int* list_compute = reinterpret_cast<int*>(base_ptr + L::LIST_OFF);
   int* list_zero = list_compute + PAIR_LIST_CAP;
-  volatile int* list_meta = abort_flag + 1;  // [0] lists in use, [1] computing items of this pair, [2] the others
+  int* list_donor = list_zero + PAIR_LIST_CAP;  // the computing items of pair `pair / 2`: where a halved piece comes from
+  volatile int* list_meta = abort_flag + 1;  // [0] lists in use, [1] computing items in all, [2] zero-only items of this pair
   if (warp == 1) {
     tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_holder)), TMEM_COLS);
     tmem_relinquish_pair();
@@ -569,13 +580,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
             const int index = computes[u] ? seen_c + __popc(mc & below) : seen_z + __popc(mz & below);
             if (index % n_pairs == pair && index / n_pairs < PAIR_LIST_CAP)
               (computes[u] ? list_compute : list_zero)[index / n_pairs] = w0 + u * 32 + lane;
+            if (computes[u] && index % n_pairs == (pair >> 1) && index / n_pairs < PAIR_LIST_CAP)
+              list_donor[index / n_pairs] = w0 + u * 32 + lane;
           }
           seen_c += __popc(mc), seen_z += __popc(mz);
         }
       }
-      mine_c = seen_c > pair ? (seen_c - pair + n_pairs - 1) / n_pairs : 0;
+      mine_c = seen_c;
       mine_z = seen_z > pair ? (seen_z - pair + n_pairs - 1) / n_pairs : 0;
-      use = mine_c <= PAIR_LIST_CAP && mine_z <= PAIR_LIST_CAP;
+      use = seen_c / n_pairs + 1 <= PAIR_LIST_CAP && mine_z <= PAIR_LIST_CAP;
     }
     if (lane == 0) list_meta[0] = use, list_meta[1] = mine_c, list_meta[2] = mine_z;
   }
@@ -584,11 +597,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
   cluster_sync_all();  // the peer's barriers are initialised before anything of ours can reach them
   tc_fence_after_sync();
   const uint32_t tmem_base = __shfl_sync(0xFFFFFFFFu, *tmem_holder, 0);
-  // This pair's walk: its list of computing items, or items pair, pair + pairs, ... of every kind.
+  // This pair's walk: its list of computing items, or items pair, pair + pairs, ... of every kind; `rounds` whole
+  // rounds and a last one of `tail` pieces, halved when that keeps twice as many pairs busy.
   const bool listed = __shfl_sync(0xFFFFFFFFu, list_meta[0], 0) != 0;
-  const int n_walk = __shfl_sync(0xFFFFFFFFu, listed ? list_meta[1]
-                                                     : (total_items > pair ? (total_items - pair + n_pairs - 1) / n_pairs : 0), 0);
-  auto item_of = [&](int idx) { return listed ? list_compute[idx] : pair + idx * n_pairs; };
+  const int n_pieces = __shfl_sync(0xFFFFFFFFu, listed ? list_meta[1] : total_items, 0);
+  const int rounds = n_pieces / n_pairs, tail = n_pieces - rounds * n_pairs;
+  const bool halved = PBN == 256 && !GATHER && p.tail_split != 0 && tail > 0 && 2 * tail <= n_pairs &&
+                      (listed || (p.causal == 0 && p.n_fills == 0));
+  const int n_walk = rounds + ((halved ? pair < 2 * tail : pair < tail) ? 1 : 0);
+  // Item idx of the walk and which part of it: 0 the whole piece, 1 / 2 its left / right 128 columns.
+  auto item_of = [&](int idx, int& part) {
+    part = 0;
+    if (idx < rounds || !halved) return listed ? list_compute[idx] : pair + idx * n_pairs;
+    part = 1 + (pair & 1);
+    return listed ? list_donor[rounds] : rounds * n_pairs + (pair >> 1);
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer (one per CTA)
@@ -597,10 +620,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
       uint32_t phase = 0;
       bool ok = true;
       long long gather_waited = 0;
-      const int row_off = static_cast<int>(rank) * BM, col_off = static_cast<int>(rank) * (BN / 2);
+      const int row_off = static_cast<int>(rank) * BM;
       for (int idx = 0; idx < n_walk && ok; ++idx) {
-        const Item it = decode_item<PAIR_ROWS, BN>(p, item_of(idx));
+        int part;
+        Item it = decode_item<PAIR_ROWS, BN>(p, item_of(idx, part));
         if (!it.compute) continue;
+        const int my_cols = part != 0 ? BN / 4 : BN / 2;  // columns of y this CTA stages
+        if (part != 0) it.n0 += (part - 1) * (BN / 2);
+        const int col_off = static_cast<int>(rank) * my_cols;
         bool own = true;
         if (GATHER) {
           own = it.m0 / p.gather_rows == p.gather_me;
@@ -623,7 +650,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
             break;
           }
           // Blocks past the end of K are loaded all the same: the TMA fills them with zeros, which add nothing.
-          if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * L::STAGE_BYTES);
+          if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * KSUB * (L::A_BYTES + my_cols * BK * 2));
           const uint32_t bar = cluster_map(full_bar(stage), 0);
 #pragma unroll
           for (int sub = 0; sub < KSUB; ++sub) {
@@ -639,7 +666,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
             } else {
 #pragma unroll
               for (int nb = 0; nb < BN / 2 / 64; ++nb)
-                tma_load_2d_pair(b_dst + nb * (64 * BK * 2), &map_b, it.n0 + col_off + nb * 64, kb * BK, bar);
+                if (nb * 64 < my_cols)
+                  tma_load_2d_pair(b_dst + nb * (64 * BK * 2), &map_b, it.n0 + col_off + nb * 64, kb * BK, bar);
             }
           }
           if (++stage == STAGES) {
@@ -655,7 +683,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
     // ------------------------------------------------------------------ MMA issuer (even CTA only)
     // The whole warp runs the loop (uniform registers for addresses and descriptors); one elected lane issues.
     if (rank == 0) {
-      const uint32_t idesc = idesc_bf16_f32(PAIR_ROWS, BN, 0, p.b_kmajor ? 0 : 1);
+      const uint32_t idesc_whole = idesc_bf16_f32(PAIR_ROWS, BN, 0, p.b_kmajor ? 0 : 1);
+      const uint32_t idesc_half = idesc_bf16_f32(PAIR_ROWS, BN / 2, 0, p.b_kmajor ? 0 : 1);
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
@@ -664,8 +693,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
         return __all_sync(0xFFFFFFFFu, mbar_wait_timed(bar, parity, abort_flag, p.status, code, waited, prof != nullptr)) != 0;
       };
       for (int idx = 0; idx < n_walk && ok; ++idx) {
-        const Item it = decode_item<PAIR_ROWS, BN>(p, item_of(idx));
+        int part;
+        const Item it = decode_item<PAIR_ROWS, BN>(p, item_of(idx, part));
         if (!__shfl_sync(0xFFFFFFFFu, static_cast<int>(it.compute), 0)) continue;
+        const uint32_t idesc = __shfl_sync(0xFFFFFFFFu, part, 0) != 0 ? idesc_half : idesc_whole;
         if (items++ == 0) t_first = clock64();
         if (!wait(tempty_bar(acc), acc_phase ^ 1u, TJX_ERR_WAIT_TMEM_EMPTY, out_wait)) break;
         tc_fence_after_sync();
@@ -760,7 +791,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
       zero_rows<BN>(p, it.m0 + static_cast<int>(rank) * BM + q * 32, it.n0, lane);
     }
     for (int idx = 0; idx < n_walk; ++idx) {
-      const Item it = decode_item<PAIR_ROWS, BN>(p, item_of(idx));
+      int part;
+      Item it = decode_item<PAIR_ROWS, BN>(p, item_of(idx, part));
+      if (part != 0) it.n0 += (part - 1) * (BN / 2);
       if (!it.valid) {
         if (lane == 0 && p.status != nullptr) atomicCAS(p.status, 0, TJX_ERR_BAD_TABLE);
         continue;
@@ -774,7 +807,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
       if (!__all_sync(0xFFFFFFFFu, got)) break;
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-      if (row0 < p.M) store_accumulator<BN>(p, &map_c, t_row, row0, it.n0, c_ptr, c_smem, c_buf, lane);
+      if (row0 < p.M) store_accumulator<BN>(p, &map_c, t_row, row0, it.n0, c_ptr, c_smem, c_buf, lane, part != 0 ? BN / 2 : BN);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(cluster_map(tempty_bar(acc), 0));
@@ -883,6 +916,7 @@ int gemm_launch(const void* x, const void* y, void* out, int M, int N, int K, in
   p.n_tiles = n_tiles, p.n_fills = n_fills;
   p.tile_i = tile_i, p.tile_j = tile_j, p.fill_i = fill_i, p.fill_j = fill_j;
   p.causal = causal ? 1 : 0, p.out_f32 = out_f32 ? 1 : 0, p.b_kmajor = y_transposed ? 1 : 0;
+  p.tail_split = y_transposed ? 0 : TJX_GEMM_TAIL_SPLIT;  // (x @ y.T stages y through a box of fixed height)
   p.num_kb = (K + BK - 1) / BK;
   p.out = out;
   p.row_scale = row_scale;
