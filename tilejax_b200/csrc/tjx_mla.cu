@@ -825,6 +825,8 @@ __global__ void __launch_bounds__(MT_THREADS, 1)
 // rows in bf16. Launched with programmatic stream serialisation: the prologue runs beside the main kernel's tail.
 constexpr int MG_WARPS = 8;
 
+// (Its 188 registers a thread keep a CTA of it off an SM that still holds one of the main kernel's; capped at 168 it
+// fits beside one, spills a little, and the call measured 2 us slower.)
 __global__ void __launch_bounds__(MG_WARPS * 32)
     mla_tc_merge_kernel(const MlaParams p, int main_ctas, int groups) {
   __shared__ int seq_units[3];  // units before sequence b, before b + 1, in total
