@@ -473,8 +473,9 @@ __global__ void __launch_bounds__(MT_THREADS, 1)
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = __shfl_sync(0xFFFFFFFFu, *tmem_holder, 0);
-  // The merge kernel may be scheduled from here on: its CTAs take no shared memory, work out their sequence's pieces,
-  // and then wait for this whole grid to complete before they read a partial.
+  // The merge kernel may be scheduled from here on: a CTA of it starts wherever an SM has room (in practice once
+  // that SM's CTA of this kernel has left), works out its sequence's pieces, and then waits for this whole grid to
+  // complete before it reads a partial.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   const int row0 = blockIdx.y * MT_ROWS;  // first of this CTA's rows among a sequence's p.H rows
