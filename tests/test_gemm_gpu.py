@@ -155,6 +155,7 @@ def test_dense_4096_against_sampled_float64_rows_and_linearity():
     ((2560, 320, 2560), (512, 256, 64), {"out_f32": True}),
     ((3584, 256, 3584), (512, 512, 256), {"causal": True}),       # 105 computing pieces: 74 + 31, dealt out from lists
     ((3328, 128, 3328), (256, 256, 128), {"causal": True}),       # 91 = 74 + 17
+    ((2560, 200, 2816), (256, 256, 64), {}),                      # K not a multiple of the K block: 110 pieces = 74 + 36
 ])
 def test_sm_pairs_and_single_ctas_agree_bit_for_bit(shape, tiles, kw):
     # One MMA per pair of SMs (256 x 256 pieces) and one per SM (128 x 256) sum K in the same order.
