@@ -103,7 +103,9 @@ def test_this_packages_nest_is_in_the_table():
     assert fingerprint.fingerprint(K.attention_block) in RECOGNISED["attention_block"]
 
 
-EXAMPLES = "/root/reference/examples"
+# The reference's examples, when its tree sits beside this repository (or where AUTOKERNEL_EXAMPLES points).
+EXAMPLES = os.environ.get("AUTOKERNEL_EXAMPLES") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference", "examples")
 
 
 @pytest.mark.skipif(not os.path.isdir(EXAMPLES), reason="the reference's tree is not on this machine")

@@ -140,7 +140,9 @@ def test_every_nest_of_this_package_is_in_the_table():
 
 # ----------------------------------------------------------------------------- the reference's own example sources
 
-EXAMPLES = "/root/reference/examples"
+# The reference's examples, when its tree sits beside this repository (or where AUTOKERNEL_EXAMPLES points).
+EXAMPLES = os.environ.get("AUTOKERNEL_EXAMPLES") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference", "examples")
 needs_reference = pytest.mark.skipif(not os.path.isdir(EXAMPLES), reason="the reference's tree is not on this machine")
 
 
