@@ -1,0 +1,142 @@
+"""Ragged paged attention's decode case through the front end (`@autokernel.kernel` on the loop nest of
+examples/ragged_paged_attention.py:121-149): a trip count read from an input as the kernel runs, an output that is
+an input updated, a cache read as paired words. On the CPU: what the nest means (`kernel.reference`) against the
+oracle bit for bit, what it lowers to, what is refused. The reference's own example is used unmodified when its tree
+is at hand."""
+
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+import tilejax_b200.autokernel as autokernel
+from tilejax_b200.autokernel import KernelError, fingerprint, jaxlike
+from tilejax_b200.autokernel import kernels as K
+from tilejax_b200.autokernel.recognised import RECOGNISED
+
+jax = jaxlike
+jnp = jaxlike.numpy
+MASK_VALUE = K.MASK_VALUE
+
+EXAMPLES = os.environ.get("AUTOKERNEL_EXAMPLES") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference", "examples")
+needs_reference = pytest.mark.skipif(not os.path.isdir(EXAMPLES), reason="the reference's tree is not on this machine")
+SCALE = 128**-0.5
+
+
+def step_inputs(**sizes):
+    """Three decode sequences (one token, one page and a bit, four full pages), a prefill sequence, padding."""
+    sizes = dict(dict(heads=8, kv_heads=2, head_dim=128, page_size=64, max_len=256, max_tokens=12, max_seqs=6, seed=3), **sizes)
+    inp = oracle.rpa_inputs([1, 1, 1, 5], [1, 130, 256, 200], **sizes)
+    cache = oracle.rpa_write_ref(inp["kv_cache"], inp["keys"], inp["values"], inp["kv_lens"], inp["page_indices"],
+                                 inp["cu_q_lens"], inp["distribution"])
+    return inp["q"], cache, inp["kv_lens"], inp["page_indices"], inp["distribution"]
+
+
+def test_the_nest_means_what_the_oracle_says_and_is_parsed_as_runtime_and_in_place():
+    kernel = K.make_rpa_decode(SCALE)
+    assert kernel.nest.inplace == {"out": "q"} and kernel.nest.runtime_ranges and not kernel.nest.runtime_masks
+    assert kernel.nest.range_reads == {"kv_lens", "distribution"}
+    args = step_inputs()
+    want = oracle.rpa_decode_ref(*args, SCALE)
+    got = kernel.reference(*args)
+    np.testing.assert_array_equal(got.view(np.uint16), want.view(np.uint16))
+    np.testing.assert_array_equal(got[3:].view(np.uint16), args[0][3:].view(np.uint16))  # non-decode rows: the query
+    assert fingerprint.fingerprint(kernel) in RECOGNISED["rpa_decode"]
+    assert fingerprint.fingerprint(K.make_rpa_decode(0.5)) == fingerprint.fingerprint(kernel)  # the scale is an argument
+
+
+def test_it_lowers_to_the_rpa_decode_entry_with_its_scale():
+    args = step_inputs()
+    lowered = K.make_rpa_decode(0.25).lower(*args)
+    p = lowered.plan.params
+    assert lowered.plan.family == "decode" and p["rpa"] and p["sm_scale"] == 0.25
+    assert (p["B"], p["H"], p["Hkv"], p["D"], p["page"], p["pages"]) == (6, 8, 2, 128, 64, 4)
+    assert lowered.tiles == 6 and lowered.steps == 24  # at most: a sequence walks cdiv(kv_lens[s], page_size) pages
+    assert "tjx_rpa_decode_bf16" in lowered.source and "softmax scale 0.25" in lowered.source
+
+
+def test_what_is_not_that_nest_is_refused():
+    args = step_inputs()
+
+    def other_mask_value(sm_scale):
+        @autokernel.kernel
+        def rpa_decode(q, kv_cache, kv_lens, page_indices, distribution):
+            T, H, Dh = q.shape
+            P, Hkv = kv_cache.shape[1], kv_cache.shape[2]
+            S = kv_lens.shape[0]
+            per_seq = page_indices.shape[0] // S
+            dtype = q.dtype
+            out = q
+            for s in range(min(S, T)):
+                qt = K.queries_by_kv_head(q[s : s + 1, :, :], Hkv)
+                row_max = jnp.full((Hkv, H // Hkv, 1), -1e9, jnp.float32)
+                row_sum = jnp.zeros((Hkv, H // Hkv, 1), jnp.float32)
+                acc = jnp.zeros((Hkv, H // Hkv, Dh), jnp.float32)
+                for p in range((kv_lens[s] + P - 1) // P if s < distribution[0] else 0):
+                    kt, vt = K.cache_page_by_kv_head(kv_cache[page_indices[s * per_seq + p], :, :, :, :])
+                    scores = jnp.dot(qt, kt.transpose(0, 2, 1), preferred_element_type=jnp.float32) * sm_scale
+                    ok = K.visible(P, p * P, kv_lens[s], 1, H // Hkv)
+                    row_max, row_sum, acc = K.online_softmax(scores, vt, ok, row_max, row_sum, acc)
+                attended = K.finish(acc, row_sum, (1, H, Dh), dtype)
+                out = out.at[s, :, :].set(jnp.where(s < distribution[0], attended[0, :, :], q[s, :, :]))
+            return out
+
+        return rpa_decode
+
+    with pytest.raises(KernelError, match="not a form of it"):
+        other_mask_value(SCALE).lower(*args)
+
+    def every_sequence_decodes(sm_scale):
+        @autokernel.kernel
+        def rpa_decode(q, kv_cache, kv_lens, page_indices, distribution):
+            T, H, Dh = q.shape
+            P, Hkv = kv_cache.shape[1], kv_cache.shape[2]
+            S = kv_lens.shape[0]
+            per_seq = page_indices.shape[0] // S
+            dtype = q.dtype
+            out = q
+            for s in range(min(S, T)):
+                qt = K.queries_by_kv_head(q[s : s + 1, :, :], Hkv)
+                row_max = jnp.full((Hkv, H // Hkv, 1), MASK_VALUE, jnp.float32)
+                row_sum = jnp.zeros((Hkv, H // Hkv, 1), jnp.float32)
+                acc = jnp.zeros((Hkv, H // Hkv, Dh), jnp.float32)
+                for p in range((kv_lens[s] + P - 1) // P):  # no distribution: not the decode case
+                    kt, vt = K.cache_page_by_kv_head(kv_cache[page_indices[s * per_seq + p], :, :, :, :])
+                    scores = jnp.dot(qt, kt.transpose(0, 2, 1), preferred_element_type=jnp.float32) * sm_scale
+                    ok = K.visible(P, p * P, kv_lens[s], 1, H // Hkv)
+                    row_max, row_sum, acc = K.online_softmax(scores, vt, ok, row_max, row_sum, acc)
+                out = out.at[s, :, :].set(K.finish(acc, row_sum, (1, H, Dh), dtype)[0, :, :])
+            return out
+
+        return rpa_decode
+
+    with pytest.raises(KernelError, match="read from kv_lens and distribution"):
+        every_sequence_decodes(SCALE).lower(*args)
+
+    # The kernel's shape rules are reported the same way: a head dimension the decode kernel does not take.
+    small = step_inputs(head_dim=64)
+    with pytest.raises(KernelError, match="head_dim 128"):
+        K.make_rpa_decode(SCALE).lower(*small)
+
+
+@needs_reference
+def test_the_references_own_decode_kernel_is_recognised_unmodified():
+    stand_ins = {"jax": jaxlike, "jnp": jaxlike.numpy, "autokernel": autokernel, "__name__": "example"}
+    ns = fingerprint.load_example(os.path.join(EXAMPLES, "ragged_paged_attention.py"), stand_ins)
+    kernel = ns["make_decode"](SCALE)  # paired words, shifts and bitcasts, lane-wide row statistics
+    assert fingerprint.fingerprint(kernel) in RECOGNISED["rpa_decode"]
+    # Its scores and P @ v are one matmul over every KV head's positions (the other heads' masked to zero weight):
+    # the same sums as the oracle's per-head ones in another order, so equal to f32 rounding, not bit for bit.
+    args = step_inputs()
+    got, want = kernel.reference(*args), oracle.rpa_decode_ref(*args, SCALE)
+    assert np.abs(got.astype(np.float64) - want.astype(np.float64)).max() <= 2e-2
+    np.testing.assert_array_equal(got[3:].view(np.uint16), args[0][3:].view(np.uint16))
+    lowered = kernel.lower(*args)
+    assert "tjx_rpa_decode_bf16" in lowered.source and lowered.plan.params["sm_scale"] == SCALE
+    # Llama-3-8B heads and pages of 128, as the example's own inputs (examples/ragged_paged_attention.py:22-24).
+    big = step_inputs(heads=32, kv_heads=8, page_size=128, max_len=512)
+    got, want = kernel.reference(*big), oracle.rpa_decode_ref(*big, SCALE)
+    assert np.abs(got.astype(np.float64) - want.astype(np.float64)).max() <= 2e-2
+    assert np.abs(got.astype(np.float64) - oracle.rpa_decode_f64(*big, SCALE)).max() <= 2e-2

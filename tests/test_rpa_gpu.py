@@ -126,3 +126,23 @@ def test_prefill_limits_are_errors():
     inp, dev = step([4], [4], heads=4, kv_heads=2, max_len=256, page_size=64)
     with pytest.raises(NativeError, match="pages of 128 positions"):
         ops.rpa_prefill(dev["q"], dev["kv_cache"], dev["kv_lens"], dev["page_indices"], dev["cu_q_lens"], dev["distribution"])
+
+
+def test_the_decode_nest_runs_through_the_front_end():
+    # `@autokernel.kernel` on the loop nest (a trip count read from kv_lens as the kernel runs, q updated): the same
+    # launch as ops.rpa_decode, found by recognising the nest; the caller's q is left alone (the reference donates it).
+    from tilejax_b200.autokernel import kernels
+
+    inp, dev = step([1, 1, 1, 1, 9], [1, 128, 129, 700, 64], max_len=1024, max_seqs=8)
+    cache = ops.rpa_write(*(dev[n] for n in NAMES))
+    scale = 128**-0.5
+    kernel = kernels.make_rpa_decode(scale)
+    q_before = dev["q"].clone()
+    args = (dev["q"], cache, dev["kv_lens"], dev["page_indices"], dev["distribution"])
+    got = kernel(*args)
+    assert ops.device_status() == 0 and torch.equal(dev["q"], q_before)
+    assert torch.equal(got, ops.rpa_decode(*args, scale))
+    want = oracle.rpa_decode_ref(inp["q"], to_host(cache), inp["kv_lens"], inp["page_indices"], inp["distribution"], scale)
+    assert np.abs(f64(to_host(got)) - f64(want)).max() <= 2e-2
+    assert kernel.verify(*args) <= 2e-2
+    assert "tjx_rpa_decode_bf16" in kernel.source(*args)

@@ -5,15 +5,17 @@
     jnp = jax.numpy
 
 Same names as the reference package (src/autokernel/__init__.py:32-50): `kernel`, `Kernel`, `Lowered`, `tunable`,
-`choice`, `Config`, `Pipeline`, `Trial`, `Tuning`, `KernelProfile`, `profile`, `KernelError`, `all_gather`.
+`choice`, `Config`, `Pipeline`, `Trial`, `Tuning`, `KernelProfile`, `profile`, `KernelError`, `all_gather`, `pairs`,
+`unpairs`, `rows`.
 """
 
 from .api import Kernel, Lowered, compare, kernel
 from .collective import all_gather
 from .errors import KernelError
 from .profiling import KernelProfile, profile
+from .ragged import pairs, rows, unpairs
 from .tunable import choice, tunable
 from .tune import Config, Pipeline, Trial, Tuning
 
 __all__ = ["Config", "Kernel", "KernelError", "KernelProfile", "Lowered", "Pipeline", "Trial", "Tuning", "all_gather",
-           "choice", "compare", "kernel", "profile", "tunable"]
+           "choice", "compare", "kernel", "pairs", "profile", "rows", "tunable", "unpairs"]

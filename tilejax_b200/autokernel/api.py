@@ -384,6 +384,8 @@ def launch_key(plan: Plan, config: Config) -> tuple:
         return ("attention_block",)
     if p.get("mla"):
         return ("mla_decode",)
+    if p.get("rpa"):
+        return ("rpa_decode",)
     if p.get("contiguous"):
         return ("decode", p["page"])
     return ("decode",)
@@ -482,6 +484,19 @@ def _lower(plan: Plan, config: Config) -> tuple[str, Callable[..., Any]]:
             f"steps       at most {sch.steps}: step_tile / step_code / step_count are built on the device from lengths "
             f"before the kernel\n")
         return text, lambda q_c, q_r, c_kv, k_rope, lengths: ops.mla_decode(q_c, q_r, c_kv, k_rope, lengths, p["page"])
+    if p.get("rpa"):
+        text = header + (
+            f"kernel      tjx_rpa_decode_bf16 (the paged decode kernel on the cache's own layout: two tensor maps over the "
+            f"one buffer, keys and values of a head side by side; lengths of the sequences outside [0, distribution[0]) "
+            f"set to zero on the device; only the decode tokens' rows are written)\n"
+            f"problem     {p['tokens']} token rows, {p['sequences']} sequences (sequence s is token s), {p['H']} / {p['Hkv']} "
+            f"heads, head_dim {p['D']}, pages of {p['page']}, {p['pages']} pages per sequence, pool of {p['num_pages']}, "
+            f"softmax scale {p['sm_scale']:.6g}\n"
+            f"steps       at most {sch.steps}: how many pages a sequence walks is read from kv_lens on the device "
+            f"(the reference's `for p in range(cdiv(kv_lens[s], page_size))`)\n"
+            f"in place    the reference donates q and updates it; this entry returns a new array holding q's other rows\n")
+        return text, lambda q, cache, kv_lens, page_indices, distribution: ops.rpa_decode(
+            q, cache, kv_lens, page_indices, distribution, p["sm_scale"])
     text = header + (
         f"kernel      tjx_paged_gqa_decode_bf16 (device step tables, per-warp TMA rings, warp-level MMA, partials "
         f"merged by the last warp to arrive)\n"

@@ -9,7 +9,8 @@ refused with a KernelError instead of being sent to a fixed kernel that computes
 
 Canonical form of a function: its body without the docstring, with
   * local names (parameters, assigned names, loop variables) numbered in order of first appearance;
-  * global names that hold numbers or strings replaced by their values (LANES -> 128, MASK_VALUE -> -1e30);
+  * global names that hold numbers or strings replaced by their values (LANES -> 128, MASK_VALUE -> -1e30); a
+    float the function closes over (the softmax scale of `make_decode(sm_scale)`) stays a name: it is an argument;
   * array modules and namespaces (`jnp`, `jax`, `jax.lax`, `autokernel`) collapsed, so that `jnp.where`,
     `jax.numpy.where` and `np.where` read alike;
   * helper functions replaced by a marker, their own canonical forms appended in order of first call.
@@ -54,6 +55,11 @@ def _is_namespace(value: Any) -> bool:
 class _Canonical(ast.NodeTransformer):
     def __init__(self, fn: Callable, function: ast.FunctionDef):
         self.ns = _namespace(fn)
+        # A float the function closes over is a parameter of the kernel (`make_decode(sm_scale)`,
+        # examples/ragged_paged_attention.py:110-149), not part of its form: every scale is the same code.
+        self.closed_floats = {n for n, c in zip(getattr(fn, "__code__", None).co_freevars if hasattr(fn, "__code__") else (),
+                                                getattr(fn, "__closure__", None) or ())
+                              if isinstance(c.cell_contents, float)}
         self.locals: dict[str, str] = {}
         self.helpers: list[Callable] = []
         assigned = {a.arg for a in function.args.args}
@@ -84,6 +90,8 @@ class _Canonical(ast.NodeTransformer):
     def visit_Name(self, node: ast.Name) -> ast.AST:
         if node.id in self.assigned:
             return ast.Name(self._local(node.id), ast.Load())
+        if node.id in self.closed_floats:
+            return ast.Name("closed_float", ast.Load())
         ok, value = self._resolve(node)
         if not ok:
             return ast.Name(f"?{node.id}", ast.Load())
@@ -170,8 +178,8 @@ def _write(path: str, found: dict[str, dict[str, str]]) -> None:
              "",
              "Written by `python -m tilejax_b200.autokernel.fingerprint [reference/examples]`: the forms in this package's",
              "kernels.py and, when the reference's example files are at hand, the forms in examples/causal_attention.py,",
-             'examples/decode.py, examples/rmsnorm_matmul.py and examples/attention_block.py (lane-replicated row',
-             'statistics, block-diagonal queries).',
+             'examples/decode.py, examples/rmsnorm_matmul.py, examples/attention_block.py and',
+             'examples/ragged_paged_attention.py (lane-replicated row statistics, block-diagonal queries, paired words).',
              'Do not edit by hand."""',
              "", "RECOGNISED: dict[str, dict[str, str]] = {"]
     for family in sorted(found):
@@ -191,10 +199,14 @@ def main(argv: list[str]) -> None:
 
     families = {"attention": ["causal_attention"], "decode": ["paged_gqa_decode", "gqa_decode"], "mla": ["mla_decode"],
                 "rmsnorm": ["rmsnorm_matmul"], "attention_block": ["attention_block"]}
-    found: dict[str, dict[str, str]] = {f: {} for f in families}
+    # Kernels made by a function of the softmax scale: (family, the maker's name here, the maker's name there, file).
+    makers = [("rpa_decode", "make_rpa_decode", "make_decode", "ragged_paged_attention.py")]
+    found: dict[str, dict[str, str]] = {f: {} for f in [*families, *(m[0] for m in makers)]}
     for family, names in families.items():
         for name in names:
             found[family][fingerprint(getattr(kernels, name))] = f"tilejax_b200/autokernel/kernels.py {name}"
+    for family, here, _, _ in makers:
+        found[family][fingerprint(getattr(kernels, here)(1.0))] = f"tilejax_b200/autokernel/kernels.py {here}"
     if len(argv) > 1:
         stand_ins = {"jax": jaxlike, "jnp": jaxlike.numpy, "autokernel": autokernel, "__name__": "example"}
         for file in ("causal_attention.py", "decode.py", "rmsnorm_matmul.py", "attention_block.py"):
@@ -203,6 +215,10 @@ def main(argv: list[str]) -> None:
                 for name in names:
                     if name in ns:
                         found[family][fingerprint(ns[name])] = f"examples/{file} {name}"
+        for family, _, there, file in makers:
+            ns = load_example(os.path.join(argv[1], file), stand_ins)
+            if there in ns:
+                found[family][fingerprint(ns[there](1.0))] = f"examples/{file} {there}"
     _write(os.path.join(os.path.dirname(__file__), "recognised.py"), found)
     for family, entries in found.items():
         for digest, label in entries.items():

@@ -166,7 +166,8 @@ def _weak(x, dtype):
 
 
 for _name, _op in (("add", np.add), ("sub", np.subtract), ("mul", np.multiply), ("truediv", np.divide),
-                   ("floordiv", np.floor_divide), ("mod", np.mod), ("and", np.bitwise_and), ("or", np.bitwise_or)):
+                   ("floordiv", np.floor_divide), ("mod", np.mod), ("and", np.bitwise_and), ("or", np.bitwise_or),
+                   ("lshift", np.left_shift), ("rshift", np.right_shift)):
     _binary(_name, _op)
 for _name, _op in (("lt", np.less), ("le", np.less_equal), ("gt", np.greater), ("ge", np.greater_equal),
                    ("eq", np.equal), ("ne", np.not_equal)):
@@ -222,6 +223,22 @@ def _full(shape, value, dtype=None):
     return Array(np.full(shape, _raw(value), dtype or np.float32))
 
 
+def _bitcast_convert_type(x, dtype):
+    """jax.lax.bitcast_convert_type: the same bits as another type. Equal widths keep the shape; to a type twice as
+    wide the last dimension (of two) goes away, first element in the low half; to one half as wide a last dimension
+    of two appears."""
+    x, dtype = np.ascontiguousarray(_raw(x)), np.dtype(dtype)
+    if x.dtype.itemsize == dtype.itemsize:
+        return Array(x.view(dtype))
+    if x.dtype.itemsize * 2 == dtype.itemsize:
+        if x.shape[-1] != 2:
+            raise ValueError("bitcast to a type twice as wide needs a last dimension of 2")
+        return Array(x.view(dtype)[..., 0])
+    if x.dtype.itemsize == dtype.itemsize * 2:
+        return Array(x[..., None].view(dtype))
+    raise ValueError(f"bitcast from {x.dtype} to {dtype}")
+
+
 def _broadcasted_iota(dtype, shape, dimension):
     index = np.arange(shape[dimension], dtype=dtype)
     view = [1] * len(shape)
@@ -242,10 +259,10 @@ numpy = types.SimpleNamespace(
     arange=_lift(np.arange), clip=_lift(np.clip), dot=_dot, matmul=_matmul, tril=_lift(np.tril),
     abs=_lift(np.abs), logical_not=_lift(np.logical_not), sqrt=_lift(np.sqrt), mean=_lift(np.mean),
     square=_lift(np.square), transpose=_lift(np.transpose), reshape=_lift(np.reshape), stack=_stack,
-    tanh=_lift(np.tanh),
+    tanh=_lift(np.tanh), swapaxes=_lift(np.swapaxes), uint16=np.uint16,
 )
 nn = types.SimpleNamespace(gelu=_gelu)
-lax = types.SimpleNamespace(broadcasted_iota=_broadcasted_iota,
+lax = types.SimpleNamespace(broadcasted_iota=_broadcasted_iota, bitcast_convert_type=_bitcast_convert_type,
                             rsqrt=_lift(lambda x: (1.0 / np.sqrt(np.asarray(x))).astype(np.asarray(x).dtype)))
 
 

@@ -3,7 +3,7 @@
 Each is the plain loop nest over tiles whose meaning the kernel must reproduce — `kernel.fn` runs it as written on
 the CPU — with the same structure as the reference's examples (examples/matmul.py, causal_matmul.py,
 causal_attention.py, rmsnorm_matmul.py, decode.py `gqa_decode`, `mla_decode` and `paged_gqa_decode`,
-collective_matmul.py). Row statistics are kept as (rows, 1)
+ragged_paged_attention.py `rpa_decode`, collective_matmul.py). Row statistics are kept as (rows, 1)
 columns here: the reference's lane-replicated (rows, 128) layout is a TPU register trick, not arithmetic.
 """
 
@@ -340,6 +340,44 @@ def paged_gqa_decode(q, k_pages, v_pages, block_tables, lengths):
             row_max, row_sum, acc = online_softmax(s, vt, ok, row_max, row_sum, acc)
         out = out.at[b, :, :, :].set(finish(acc, row_sum, (T, H, Dh), dtype))
     return out
+
+
+def cache_page_by_kv_head(page):
+    """A page of a cache that holds each head's key and value side by side, (P, Hkv, 2, Dh), as keys and values
+    (Hkv, P, Dh)."""
+    return page[:, :, 0, :].transpose(1, 0, 2), page[:, :, 1, :].transpose(1, 0, 2)
+
+
+def make_rpa_decode(sm_scale: float) -> autokernel.Kernel:
+    """Ragged paged attention's decode case for one softmax scale (examples/ragged_paged_attention.py:110-149): q
+    (T, H, Dh) holds every sequence's new tokens and sequence s < distribution[0] is token s; the cache (pages,
+    page_size, Hkv, 2, Dh) already holds the new tokens; kv_lens (S,) counts them in; sequence s's pages are
+    page_indices[s * pages_per_seq :]. The result is q with the decode tokens' rows replaced by their attention
+    outputs. How many pages a sequence walks is read from kv_lens as the kernel runs."""
+
+    @autokernel.kernel
+    def rpa_decode(q, kv_cache, kv_lens, page_indices, distribution):
+        T, H, Dh = q.shape
+        P, Hkv = kv_cache.shape[1], kv_cache.shape[2]
+        S = kv_lens.shape[0]
+        per_seq = page_indices.shape[0] // S
+        dtype = q.dtype
+        out = q
+        for s in range(min(S, T)):
+            qt = queries_by_kv_head(q[s : s + 1, :, :], Hkv)
+            row_max = jnp.full((Hkv, H // Hkv, 1), MASK_VALUE, jnp.float32)
+            row_sum = jnp.zeros((Hkv, H // Hkv, 1), jnp.float32)
+            acc = jnp.zeros((Hkv, H // Hkv, Dh), jnp.float32)
+            for p in range((kv_lens[s] + P - 1) // P if s < distribution[0] else 0):
+                kt, vt = cache_page_by_kv_head(kv_cache[page_indices[s * per_seq + p], :, :, :, :])
+                scores = jnp.dot(qt, kt.transpose(0, 2, 1), preferred_element_type=jnp.float32) * sm_scale
+                ok = visible(P, p * P, kv_lens[s], 1, H // Hkv)
+                row_max, row_sum, acc = online_softmax(scores, vt, ok, row_max, row_sum, acc)
+            attended = finish(acc, row_sum, (1, H, Dh), dtype)
+            out = out.at[s, :, :].set(jnp.where(s < distribution[0], attended[0, :, :], q[s, :, :]))
+        return out
+
+    return rpa_decode
 
 
 @autokernel.kernel

@@ -59,10 +59,18 @@ class Nest:
     stores: dict[str, Store]
     all_gathers: tuple[AllGather, ...] = ()
     index_reads: frozenset[str] = field(default_factory=frozenset)  # inputs read element-wise in masks
+    range_reads: frozenset[str] = field(default_factory=frozenset)  # inputs read element-wise in a reduction loop's range
+    inplace: dict[str, str] = field(default_factory=dict)           # output -> the input it starts as (`out = q`)
 
     @property
     def runtime_masks(self) -> bool:
         return bool(self.index_reads)
+
+    @property
+    def runtime_ranges(self) -> bool:
+        """A reduction loop runs a number of times read from an input as the kernel runs
+        (`for p in range(cdiv(kv_lens[s], page_size))`, examples/ragged_paged_attention.py:138)."""
+        return bool(self.range_reads)
 
     def error(self, message: str, node: ast.AST | None = None) -> KernelError:
         return KernelError(f"{self.name}: {message}", filename=self.filename, node=node)
@@ -116,15 +124,16 @@ class _Parser:
                              rest[0] if rest else nest_stmt)
         outputs = self._returned(rest[0])
         all_gathers = self._all_gathers(prologue, params)
-        allocations = self._allocations(prologue, outputs)
+        allocations, inplace = self._allocations(prologue, outputs, params)
 
         parallel, tile_body = self._parallel(nest_stmt)
         reductions, bodies, segments = self._tile(tile_body)
         stores = self._stores(segments, bodies, outputs)
         index_reads = self._index_reads(reductions, params)
+        range_reads = self._range_reads(reductions, params)
         return Nest(self.name, self.filename, f, tuple(params), tunable, tuple(prologue), allocations, outputs,
                     tuple(parallel), tuple(reductions), tuple(bodies), tuple(segments), stores, all_gathers,
-                    frozenset(index_reads))
+                    frozenset(index_reads), frozenset(range_reads), inplace)
 
     def _returned(self, ret: ast.Return) -> tuple[str, ...]:
         value = ret.value
@@ -156,8 +165,8 @@ class _Parser:
             raise self.error("a kernel gathers one input across chips", found[1].node)
         return tuple(found)
 
-    def _allocations(self, prologue, outputs):
-        allocations = {}
+    def _allocations(self, prologue, outputs, params):
+        allocations, inplace = {}, {}
         for s in prologue:
             targets = s.targets if isinstance(s, ast.Assign) else []
             for t in targets:
@@ -172,10 +181,13 @@ class _Parser:
                 raise self.error(f"output `{name}` must be allocated before the loops (jnp.zeros or jnp.full)",
                                  self.function)
             call = allocations[name].value
+            if isinstance(call, ast.Name) and call.id in params:
+                inplace[name] = call.id  # `out = q`: the output is the input updated (examples/ragged_paged_attention.py:131)
+                continue
             ok = isinstance(call, ast.Call) and isinstance(call.func, ast.Attribute) and call.func.attr in ("zeros", "full")
             if not ok:
                 raise self.error(f"allocate output `{name}` once, with jnp.zeros or jnp.full", allocations[name])
-        return allocations
+        return allocations, inplace
 
     def _loop(self, node: ast.For):
         if node.orelse:
@@ -252,6 +264,15 @@ class _Parser:
             if name not in stores:
                 raise self.error(f"output `{name}` is never stored: `{name} = {name}.at[index].set(value)`", self.function)
         return stores
+
+    def _range_reads(self, reductions, params):
+        reads = set()
+        for loop in reductions:
+            for arg in loop.args:
+                for n in ast.walk(arg):
+                    if isinstance(n, ast.Subscript) and isinstance(n.value, ast.Name) and n.value.id in params:
+                        reads.add(n.value.id)
+        return reads
 
     def _index_reads(self, reductions, params):
         reads = set()

@@ -131,6 +131,12 @@ def _run_prologue(nest: Nest, fn, specs: list[Spec], tunable: Any, chips: int = 
     def ranges(loops):
         out = []
         for loop in loops:
+            if any(isinstance(n, ast.Subscript) and isinstance(n.value, ast.Name) and n.value.id in nest.range_reads
+                   for a in loop.args for n in ast.walk(a)):
+                # A trip count read from an input as the kernel runs: no integer here; the recogniser of the family
+                # knows its bound (the pages a sequence may have).
+                out.append(Range(loop.var, 0, 0, 1))
+                continue
             try:
                 args = [int(eval(compile(ast.Expression(a), nest.filename, "eval"), ns)) for a in loop.args]
             except Exception as e:
@@ -250,6 +256,8 @@ def _require_known_form(nest: Nest, fn, family: str) -> None:
                 "attention_block": "an attention block: causal attention over all heads, RMSNorm of the heads side by "
                                    "side, then `gelu(n @ w_up) @ w_down`",
                 "decode": "GQA decode's online softmax over the cache blocks",
+                "rpa_decode": "ragged paged attention's decode case: the online softmax over a sequence's pages of a cache "
+                              "that holds keys and values side by side",
                 "mla": "absorbed MLA decode's online softmax over the latent cache"}[family]
         raise _unsupported(nest, f"the loops and masks are those of {what}, but the tile code is not a form of it this "
                                  f"backend's kernel is known to compute (fingerprint {digest[:12]})")
@@ -263,6 +271,10 @@ def _recognise(nest, fn, ns, specs, outputs, parallel, reductions, chips) -> Pla
         return plan
     if n_red != 1:
         raise _unsupported(nest, f"{n_red} reduction loops (one is supported, or the two phases of an attention block)")
+    if nest.runtime_ranges:
+        plan = _recognise_rpa_decode(nest, fn, ns, specs, outputs, parallel, reductions)
+        _require_known_form(nest, fn, "rpa_decode")
+        return plan
     if nest.runtime_masks:
         plan = _recognise_decode(nest, ns, specs, outputs, parallel, reductions)
         _require_known_form(nest, fn, "mla" if plan.params.get("mla") else "decode")
@@ -584,6 +596,44 @@ def _recognise_mla_decode(nest, ns, specs, outputs, parallel, reductions) -> Pla
                            nest.reductions[0].node)
     sch = _schedule.paged_decode_schedule(B, j.count)
     params = dict(B=B, T=T, H=H, C=C, R=R, S=S, page=block, pages=j.count, schedule=sch, mla=True)
+    return Plan(nest, "decode", specs, outputs, parallel, reductions, params, runtime=True)
+
+
+def _recognise_rpa_decode(nest, fn, ns, specs, outputs, parallel, reductions) -> Plan:
+    """`rpa_decode` (examples/ragged_paged_attention.py:121-149): (q, kv_cache, kv_lens, page_indices, distribution), a
+    tile per sequence, its pages counted from kv_lens as the kernel runs, the output q updated. What the tile code
+    computes is pinned by its fingerprint (the caller checks it); here the shapes, the loops and the scale."""
+    if len(parallel) != 1 or len(nest.inputs) != 5 or nest.inplace != {nest.outputs[0]: nest.inputs[0]} or len(nest.outputs) != 1:
+        raise _unsupported(nest, "a trip count read from an input other than ragged paged attention's decode case: "
+                                 "(q, kv_cache, kv_lens, page_indices, distribution) with q updated in place")
+    q, cache, kv_lens, page_indices, distribution = specs[:5]
+    int32 = np.dtype(np.int32)
+    if q.ndim != 3 or cache.ndim != 5 or cache.shape[3] != 2 or cache.shape[4] != q.shape[2] or kv_lens.ndim != 1 \
+            or page_indices.ndim != 1 or distribution.shape != (3,) or page_indices.shape[0] % kv_lens.shape[0] \
+            or any(np.dtype(x.dtype) != int32 for x in (kv_lens, page_indices, distribution)) \
+            or np.dtype(q.dtype) != np.dtype(cache.dtype):
+        raise _unsupported(nest, "ragged paged decode takes q (T, H, D), a cache (pages, page_size, Hkv, 2, D) of q's "
+                                 "dtype, kv_lens (S,), page_indices (S * pages_per_seq,) and distribution (3,), int32")
+    if nest.range_reads != {nest.inputs[2], nest.inputs[4]}:
+        raise _unsupported(nest, "the page loop's trip count must be read from kv_lens and distribution",
+                           nest.reductions[0].node)
+    T, H, D = q.shape
+    num_pages, page, Hkv = cache.shape[0], cache.shape[1], cache.shape[2]
+    S = kv_lens.shape[0]
+    pages = page_indices.shape[0] // S
+    (s_loop,) = parallel
+    if (s_loop.start, s_loop.stop, s_loop.step) != (0, min(S, T), 1):
+        raise _unsupported(nest, "the sequence loop must run over min(sequences, tokens): sequence s is token s",
+                           nest.parallel[0].node)
+    # The softmax scale: the one float the function closes over.
+    closed = [c.cell_contents for c in (fn.__closure__ or ()) if isinstance(c.cell_contents, float)]
+    if len(closed) != 1:
+        raise _unsupported(nest, "the kernel must close over its softmax scale, one float (`make_decode(sm_scale)`)")
+    n = min(S, T)
+    sch = _schedule.paged_decode_schedule(n, pages)
+    params = dict(B=n, T=1, H=H, Hkv=Hkv, D=D, page=page, pages=pages, num_pages=num_pages, schedule=sch, rpa=True,
+                  tokens=T, sequences=S, sm_scale=float(closed[0]))
+    reductions = (Range(reductions[0].var, 0, pages, 1),)
     return Plan(nest, "decode", specs, outputs, parallel, reductions, params, runtime=True)
 
 

@@ -2,8 +2,8 @@
 
 Written by `python -m tilejax_b200.autokernel.fingerprint [reference/examples]`: the forms in this package's
 kernels.py and, when the reference's example files are at hand, the forms in examples/causal_attention.py,
-examples/decode.py, examples/rmsnorm_matmul.py and examples/attention_block.py (lane-replicated row
-statistics, block-diagonal queries).
+examples/decode.py, examples/rmsnorm_matmul.py, examples/attention_block.py and
+examples/ragged_paged_attention.py (lane-replicated row statistics, block-diagonal queries, paired words).
 Do not edit by hand."""
 
 RECOGNISED: dict[str, dict[str, str]] = {
@@ -28,5 +28,9 @@ RECOGNISED: dict[str, dict[str, str]] = {
     "rmsnorm": {
         "ebbdf02fc35cd281f7cba2fdd95589e0d8717f3476647b2313b8393a40b81e26": "examples/rmsnorm_matmul.py rmsnorm_matmul",
         "bc7e5bbddff3f245c47e9cbeea906d10d142f2fe1e7f9fd7b4a7eeb32f1c031d": "tilejax_b200/autokernel/kernels.py rmsnorm_matmul",
+    },
+    "rpa_decode": {
+        "9c7c8eadbba15db816b68fdb97c1db23c79f3bd0271a905b33d9cc1f13b2ace2": "examples/ragged_paged_attention.py make_decode",
+        "696fd4feefd3a8683940cba797e0bab498b59e7d6d01532804293f16acfa9fe4": "tilejax_b200/autokernel/kernels.py make_rpa_decode",
     },
 }
