@@ -207,6 +207,15 @@ int tjx_rpa_write_bf16(void* kv_cache, const void* keys, const void* values, con
                        const int32_t* page_indices, const int32_t* cu_q_lens, const int32_t* distribution, int T,
                        int S, int Hkv, int D, int page_size, int pages_per_seq, int num_pages, tjx_stream_t stream);
 
+/* The same write from run tables, as the reference's `rpa_write` kernel takes them (examples/ragged_paged_attention.py:
+ * 33-47; its `writes`, :49-71, makes them in plain JAX): run w < n_writes[0] copies the tokens from write_rows[w] on to
+ * rows write_first[w] .. write_stop[w] - 1 of page page_indices[write_page[w]]. The table arrays are int32[max_runs],
+ * n_writes int32[1], page_indices int32[n_page_indices]; rows, tokens or runs out of range write nothing. In place. */
+int tjx_rpa_write_runs_bf16(void* kv_cache, const void* keys, const void* values, const int32_t* page_indices,
+                            const int32_t* write_page, const int32_t* write_rows, const int32_t* write_first,
+                            const int32_t* write_stop, const int32_t* n_writes, int T, int n_page_indices, int max_runs,
+                            int Hkv, int D, int page_size, int num_pages, tjx_stream_t stream);
+
 /* Bytes of scratch tjx_rpa_decode_bf16 needs for these sizes. */
 size_t tjx_rpa_decode_workspace_bytes(int T, int S, int H, int D, int page_size, int pages_per_seq);
 

@@ -48,6 +48,28 @@ def rpa_inputs(q_lens, kv_lens, *, heads=32, kv_heads=8, head_dim=128, page_size
                 cu_q_lens=cu, distribution=np.array([decodes, decodes, S], np.int32))
 
 
+def rpa_write_runs(kv_lens, page_indices, cu_q_lens, distribution, page_size: int, max_tokens: int) -> dict:
+    """`writes` (examples/ragged_paged_attention.py:49-71) in NumPy: sequence s's new tokens, at positions
+    [kv_len - q_len, kv_len), cut at page boundaries; int32 arrays of the run count's bound, cdiv(T, page_size) + S,
+    in the order of `rpa_write`'s parameters, n_writes of shape (1,)."""
+    S = kv_lens.shape[0]
+    pps = page_indices.shape[0] // S
+    seqs = np.arange(S)
+    q_len = np.where(seqs < distribution[2], cu_q_lens[1:] - cu_q_lens[:-1], 0)
+    first = kv_lens - q_len
+    n_runs = np.where(q_len > 0, (kv_lens - 1) // page_size - first // page_size + 1, 0)
+    ends = np.cumsum(n_runs)
+    w = np.arange(-(-max_tokens // page_size) + S)
+    seq = np.minimum((ends[None, :] <= w[:, None]).sum(axis=1), S - 1)
+    page = first[seq] // page_size + w - (ends[seq] - n_runs[seq])
+    start = np.maximum(first[seq], page * page_size)
+    i32 = lambda a: np.asarray(a, np.int32)  # noqa: E731
+    return dict(write_page=i32(seq * pps + page), write_rows=i32(cu_q_lens[seq] + start - first[seq]),
+                write_first=i32(start - page * page_size),
+                write_stop=i32(np.minimum(kv_lens[seq], (page + 1) * page_size) - page * page_size),
+                n_writes=i32(ends[-1:]))
+
+
 def rpa_write_ref(kv_cache, keys, values, kv_lens, page_indices, cu_q_lens, distribution) -> np.ndarray:
     """examples/ragged_paged_attention.py:33-79 token by token: sequence s < distribution[2] has q_len =
     cu_q_lens[s + 1] - cu_q_lens[s] new tokens at positions [kv_len - q_len, kv_len) (:56-58); position p lives in page

@@ -1,5 +1,5 @@
 """Ragged paged attention's cache write and decode case on the CPU side (examples/ragged_paged_attention.py): the
-oracle's token-by-token write against the reference's run arithmetic (`writes`, :49-71) restated here, and its decode
+oracle's token-by-token write against the reference's run arithmetic (`writes`, :49-71; `oracle.rpa_write_runs`), and its decode
 against float64."""
 
 import numpy as np
@@ -7,33 +7,14 @@ import numpy as np
 import oracle
 
 
-def runs(kv_lens, page_indices, cu_q_lens, distribution, page_size, max_tokens):
-    """`writes` (examples/ragged_paged_attention.py:49-71) in NumPy: sequence s's new tokens, at positions
-    [kv_len - q_len, kv_len), cut at page boundaries; arrays of the run count's bound."""
-    S = kv_lens.shape[0]
-    pps = page_indices.shape[0] // S
-    seqs = np.arange(S)
-    q_len = np.where(seqs < distribution[2], cu_q_lens[1:] - cu_q_lens[:-1], 0)
-    first = kv_lens - q_len
-    n_runs = np.where(q_len > 0, (kv_lens - 1) // page_size - first // page_size + 1, 0)
-    ends = np.cumsum(n_runs)
-    w = np.arange(-(-max_tokens // page_size) + S)
-    seq = np.minimum((ends[None, :] <= w[:, None]).sum(axis=1), S - 1)
-    page = first[seq] // page_size + w - (ends[seq] - n_runs[seq])
-    start = np.maximum(first[seq], page * page_size)
-    return dict(write_page=seq * pps + page, write_rows=cu_q_lens[seq] + start - first[seq],
-                write_first=start - page * page_size,
-                write_stop=np.minimum(kv_lens[seq], (page + 1) * page_size) - page * page_size, n_writes=int(ends[-1]))
-
-
 def test_the_token_by_token_write_is_the_references_run_by_run_write():
     inp = oracle.rpa_inputs([1, 1, 1, 300, 7, 130], [513, 1, 128, 300, 135, 400], max_len=1024, max_tokens=448,
                             max_seqs=8, seed=3)
     got = oracle.rpa_write_ref(inp["kv_cache"], inp["keys"], inp["values"], inp["kv_lens"], inp["page_indices"],
                                inp["cu_q_lens"], inp["distribution"])
-    r = runs(inp["kv_lens"], inp["page_indices"], inp["cu_q_lens"], inp["distribution"], 128, 448)
+    r = oracle.rpa_write_runs(inp["kv_lens"], inp["page_indices"], inp["cu_q_lens"], inp["distribution"], 128, 448)
     want = inp["kv_cache"].copy()
-    for w in range(r["n_writes"]):  # rpa_write (:33-46): a run lands in one page
+    for w in range(int(r["n_writes"][0])):  # rpa_write (:33-46): a run lands in one page
         page = inp["page_indices"][r["write_page"][w]]
         n = r["write_stop"][w] - r["write_first"][w]
         rows = slice(r["write_rows"][w], r["write_rows"][w] + n)

@@ -1,6 +1,6 @@
-"""Ragged paged attention's decode case through the front end (`@autokernel.kernel` on the loop nest of
-examples/ragged_paged_attention.py:121-149): a trip count read from an input as the kernel runs, an output that is
-an input updated, a cache read as paired words. On the CPU: what the nest means (`kernel.reference`) against the
+"""Ragged paged attention's cache write and decode case through the front end (`@autokernel.kernel` on the loop nests
+of examples/ragged_paged_attention.py:33-47 and :121-149): trip counts read from inputs as the kernel runs, outputs
+that are inputs updated, rows chosen as the kernel runs (`rows`), a cache read and written as paired words. On the CPU: what the nest means (`kernel.reference`) against the
 oracle bit for bit, what it lowers to, what is refused. The reference's own example is used unmodified when its tree
 is at hand."""
 
@@ -140,3 +140,62 @@ def test_the_references_own_decode_kernel_is_recognised_unmodified():
     got, want = kernel.reference(*big), oracle.rpa_decode_ref(*big, SCALE)
     assert np.abs(got.astype(np.float64) - want.astype(np.float64)).max() <= 2e-2
     assert np.abs(got.astype(np.float64) - oracle.rpa_decode_f64(*big, SCALE)).max() <= 2e-2
+
+
+# ----------------------------------------------------------------------------- the cache write
+
+
+def write_inputs():
+    inp = oracle.rpa_inputs([1, 1, 1, 300, 7, 130], [513, 1, 128, 300, 135, 400], max_len=1024, max_tokens=448,
+                            max_seqs=8, seed=3)
+    runs = oracle.rpa_write_runs(inp["kv_lens"], inp["page_indices"], inp["cu_q_lens"], inp["distribution"], 128, 448)
+    want = oracle.rpa_write_ref(inp["kv_cache"], inp["keys"], inp["values"], inp["kv_lens"], inp["page_indices"],
+                                inp["cu_q_lens"], inp["distribution"])
+    return (inp["kv_cache"], inp["keys"], inp["values"], inp["page_indices"], *runs.values()), want
+
+
+def test_the_write_nest_means_the_token_by_token_write_and_lowers_to_the_run_kernel():
+    args, want = write_inputs()
+    kernel = K.rpa_write
+    assert kernel.nest.inplace == {"out": "kv_cache"} and kernel.nest.range_reads == {"n_writes"}
+    assert len(kernel.nest.parallel) == 1 and not kernel.nest.reductions
+    np.testing.assert_array_equal(kernel.reference(*args).view(np.uint16), want.view(np.uint16))
+    assert fingerprint.fingerprint(kernel) in RECOGNISED["rpa_write"]
+    lowered = kernel.lower(*args)
+    assert lowered.plan.family == "rpa_write" and "tjx_rpa_write_runs_bf16" in lowered.source
+    assert lowered.tiles == args[4].shape[0]  # at most: the run count is read on the device
+    # Another store is another kernel: keys where the values go.
+    @autokernel.kernel
+    def swapped(kv_cache, keys, values, page_indices, write_page, write_rows, write_first, write_stop, n_writes):
+        P = kv_cache.shape[1]
+        out = kv_cache
+        for w in range(n_writes[0]):
+            tokens = autokernel.rows(write_rows[w], write_rows[w] + write_stop[w] - write_first[w], P)
+            side_by_side = jnp.stack([values[tokens, :, :], keys[tokens, :, :]], axis=2)
+            out = out.at[page_indices[write_page[w]], autokernel.rows(write_first[w], write_stop[w], P), :, :, :].set(side_by_side)
+        return out
+
+    with pytest.raises(KernelError, match="not a form of it"):
+        swapped.lower(*args)
+
+
+def test_rows_reads_clamp_and_stores_past_the_stop_are_dropped():
+    # `rows(start, stop, n)` (src/autokernel/ragged.py:23-28): n indices from start, those at or past stop out of range.
+    index = jaxlike.to_numpy(autokernel.rows(3, 5, 4))
+    assert index[:2].tolist() == [3, 4] and (index[2:] > 10**9).all()
+    x = jaxlike.Array(np.arange(12, dtype=np.float32).reshape(6, 2))
+    read = jaxlike.to_numpy(x[autokernel.rows(4, 6, 4), :])
+    assert read.tolist() == [[8, 9], [10, 11], [10, 11], [10, 11]]        # a read out of range clamps
+    stored = jaxlike.to_numpy(x.at[autokernel.rows(1, 3, 4), :].set(jnp.full((4, 2), -1.0)))
+    assert stored[:, 0].tolist() == [0, -1, -1, 6, 8, 10]                  # a store out of range is dropped
+
+
+@needs_reference
+def test_the_references_own_write_kernel_is_recognised_unmodified():
+    stand_ins = {"jax": jaxlike, "jnp": jaxlike.numpy, "autokernel": autokernel, "__name__": "example"}
+    ns = fingerprint.load_example(os.path.join(EXAMPLES, "ragged_paged_attention.py"), stand_ins)
+    kernel = ns["rpa_write"]  # keys and values packed into words, stored with `unpairs`
+    assert fingerprint.fingerprint(kernel) in RECOGNISED["rpa_write"]
+    args, want = write_inputs()
+    np.testing.assert_array_equal(kernel.reference(*args).view(np.uint16), want.view(np.uint16))
+    assert "tjx_rpa_write_runs_bf16" in kernel.lower(*args).source

@@ -146,3 +146,19 @@ def test_the_decode_nest_runs_through_the_front_end():
     assert np.abs(f64(to_host(got)) - f64(want)).max() <= 2e-2
     assert kernel.verify(*args) <= 2e-2
     assert "tjx_rpa_decode_bf16" in kernel.source(*args)
+
+
+def test_the_write_nest_runs_through_the_front_end_and_the_run_kernel_writes_in_place():
+    from tilejax_b200.autokernel import kernels
+
+    inp, dev = step([1, 1, 1, 300, 7, 130], [513, 1, 128, 300, 135, 400], max_len=1024, max_tokens=448, max_seqs=8)
+    runs = oracle.rpa_write_runs(inp["kv_lens"], inp["page_indices"], inp["cu_q_lens"], inp["distribution"], 128, 448)
+    tables = [to_device(v) for v in runs.values()]
+    want = oracle.rpa_write_ref(*(inp[n] for n in NAMES))
+    before = dev["kv_cache"].clone()
+    got = kernels.rpa_write(dev["kv_cache"], dev["keys"], dev["values"], dev["page_indices"], *tables)
+    assert ops.device_status() == 0 and torch.equal(dev["kv_cache"], before)  # the caller's cache is left alone
+    np.testing.assert_array_equal(to_host(got).view(np.uint16), want.view(np.uint16))
+    same = ops.rpa_write_runs(dev["kv_cache"], dev["keys"], dev["values"], dev["page_indices"], *tables)
+    assert same.data_ptr() == dev["kv_cache"].data_ptr() and torch.equal(same, got)     # the C entry: in place
+    assert torch.equal(ops.rpa_write(*(dev[n] for n in NAMES)), got)                    # writing again changes nothing

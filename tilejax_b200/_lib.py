@@ -39,6 +39,7 @@ SYMBOLS: dict[str, tuple] = {
     "tjx_paged_gqa_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "tjx_paged_gqa_decode_bf16": (c_int, [_P] * 6 + [c_int] * 8 + [_P] * 5 + [c_size_t, _P]),
     "tjx_rpa_write_bf16": (c_int, [_P] * 7 + [c_int] * 7 + [_P]),
+    "tjx_rpa_write_runs_bf16": (c_int, [_P] * 9 + [c_int] * 7 + [_P]),
     "tjx_rpa_decode_workspace_bytes": (c_size_t, [c_int] * 6),
     "tjx_rpa_decode_bf16": (c_int, [_P] * 6 + [c_int] * 8 + [ctypes.c_float, _P, c_size_t, _P]),
     "tjx_rpa_prefill_workspace_bytes": (c_size_t, [c_int, c_int]),

@@ -340,6 +340,9 @@ def _check_kernel_rules(plan: Plan) -> None:
             raise nest.error("the attention kernel takes head_dim 128 and blocks that are multiples of 128")
         if any(np.dtype(s.dtype) != bf16 for s in plan.specs[:3]):
             raise nest.error("the attention kernel takes bfloat16 q, k, v")
+    elif plan.family == "rpa_write":
+        if p["D"] != 128 or any(np.dtype(s.dtype) != bf16 for s in plan.specs[:3]):
+            raise nest.error("the cache write kernel takes a bfloat16 cache, keys and values of head_dim 128")
     elif p.get("mla"):
         if p["C"] != 512 or p["R"] != 128 or p["H"] % 16 or p["page"] % 16:
             raise nest.error("the MLA decode kernel takes 512 latent and 128 RoPE columns, heads in multiples of 16 and "
@@ -382,6 +385,8 @@ def launch_key(plan: Plan, config: Config) -> tuple:
         return ("attention",)
     if plan.family == "attention_block":
         return ("attention_block",)
+    if plan.family == "rpa_write":
+        return ("rpa_write",)
     if p.get("mla"):
         return ("mla_decode",)
     if p.get("rpa"):
@@ -484,6 +489,20 @@ def _lower(plan: Plan, config: Config) -> tuple[str, Callable[..., Any]]:
             f"steps       at most {sch.steps}: step_tile / step_code / step_count are built on the device from lengths "
             f"before the kernel\n")
         return text, lambda q_c, q_r, c_kv, k_rope, lengths: ops.mla_decode(q_c, q_r, c_kv, k_rope, lengths, p["page"])
+    if plan.family == "rpa_write":
+        text = header + (
+            f"kernel      tjx_rpa_write_runs_bf16 (a CTA per (row of a page, run): the run's tokens' keys and values copied "
+            f"side by side into their page, 16 bytes per thread)\n"
+            f"problem     {p['T']} new tokens, {p['Hkv']} KV heads of {p['D']}, pages of {p['page']}, pool of "
+            f"{p['num_pages']}, at most {p['max_runs']} runs: how many there are is read from n_writes on the device\n"
+            f"in place    the reference donates the cache and updates it; this entry copies it first (ops.rpa_write_runs "
+            f"and the C entry point write in place)\n")
+
+        def write(cache, keys, values, page_indices, write_page, write_rows, write_first, write_stop, n_writes):
+            return ops.rpa_write_runs(cache.clone(), keys, values, page_indices, write_page, write_rows, write_first,
+                                      write_stop, n_writes)
+
+        return text, write
     if p.get("rpa"):
         text = header + (
             f"kernel      tjx_rpa_decode_bf16 (the paged decode kernel on the cache's own layout: two tensor maps over the "

@@ -198,7 +198,7 @@ def main(argv: list[str]) -> None:
     from tilejax_b200.autokernel import jaxlike, kernels
 
     families = {"attention": ["causal_attention"], "decode": ["paged_gqa_decode", "gqa_decode"], "mla": ["mla_decode"],
-                "rmsnorm": ["rmsnorm_matmul"], "attention_block": ["attention_block"]}
+                "rmsnorm": ["rmsnorm_matmul"], "attention_block": ["attention_block"], "rpa_write": ["rpa_write"]}
     # Kernels made by a function of the softmax scale: (family, the maker's name here, the maker's name there, file).
     makers = [("rpa_decode", "make_rpa_decode", "make_decode", "ragged_paged_attention.py")]
     found: dict[str, dict[str, str]] = {f: {} for f in [*families, *(m[0] for m in makers)]}
@@ -209,7 +209,8 @@ def main(argv: list[str]) -> None:
         found[family][fingerprint(getattr(kernels, here)(1.0))] = f"tilejax_b200/autokernel/kernels.py {here}"
     if len(argv) > 1:
         stand_ins = {"jax": jaxlike, "jnp": jaxlike.numpy, "autokernel": autokernel, "__name__": "example"}
-        for file in ("causal_attention.py", "decode.py", "rmsnorm_matmul.py", "attention_block.py"):
+        for file in ("causal_attention.py", "decode.py", "rmsnorm_matmul.py", "attention_block.py",
+                     "ragged_paged_attention.py"):
             ns = load_example(os.path.join(argv[1], file), stand_ins)
             for family, names in families.items():
                 for name in names:

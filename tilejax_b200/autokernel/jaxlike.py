@@ -72,18 +72,54 @@ class _Setter:
 
     def set(self, value):
         out = self.array.value.copy()
-        out[_index(self.idx, out.shape)] = np.asarray(_raw(value)).astype(out.dtype)
+        value = np.asarray(_raw(value))
+        items = self.idx if isinstance(self.idx, tuple) else (self.idx,)
+        vectors = [n for n, item in enumerate(items) if _is_index_vector(item)]
+        if vectors:
+            # A vector of row indices (`autokernel.rows`): a store at an index out of range is dropped, as JAX drops
+            # it. The vector's entries run along the value's axis that its place in the index selects.
+            if len(vectors) != 1:
+                raise NotImplementedError("one vector of indices per store")
+            at = vectors[0]
+            rows = np.asarray(_raw(items[at])).astype(np.int64)
+            keep = (rows >= 0) & (rows < out.shape[at])
+            axis = sum(1 for item in items[:at] if isinstance(item, slice))
+            value = np.broadcast_to(value, _stored_shape(items, out.shape, rows.shape[0]))
+            value = np.compress(keep, value, axis=axis)
+            items = (*items[:at], rows[keep], *items[at + 1:])
+        out[_index(tuple(items), out.shape)] = value.astype(out.dtype)
         return Array(out)
 
 
+def _is_index_vector(item) -> bool:
+    return isinstance(item, (Array, np.ndarray)) and np.asarray(_raw(item)).ndim == 1
+
+
+def _stored_shape(items, shape, n):
+    """The shape a store's value takes: slices keep their dimension, scalars drop it, the index vector gives n."""
+    dims = []
+    for dim, item in enumerate(items):
+        if isinstance(item, slice):
+            dims.append(len(range(*item.indices(shape[dim]))))
+        elif _is_index_vector(item):
+            dims.append(n)
+    return tuple(dims) + tuple(shape[len(items):])
+
+
 def _index(idx, shape):
-    """Indices with array scalars turned into clamped ints (JAX clamps gathers into range)."""
+    """Indices with array scalars turned into clamped ints, and index vectors clamped into range (JAX clamps
+    gathers into range)."""
     items = idx if isinstance(idx, tuple) else (idx,)
     out = []
     for dim, item in enumerate(items):
         if isinstance(item, (Array, np.generic)) or (isinstance(item, np.ndarray) and item.ndim == 0):
+            if np.asarray(_raw(item)).ndim == 1:
+                out.append(np.clip(np.asarray(_raw(item)).astype(np.int64), 0, shape[dim] - 1))
+                continue
             value = int(np.asarray(_raw(item)))
             out.append(int(np.clip(value, 0, shape[dim] - 1)))
+        elif isinstance(item, np.ndarray) and item.ndim == 1:
+            out.append(np.clip(item.astype(np.int64), 0, shape[dim] - 1))
         else:
             out.append(item)
     return tuple(out)

@@ -3,7 +3,7 @@
 Each is the plain loop nest over tiles whose meaning the kernel must reproduce — `kernel.fn` runs it as written on
 the CPU — with the same structure as the reference's examples (examples/matmul.py, causal_matmul.py,
 causal_attention.py, rmsnorm_matmul.py, decode.py `gqa_decode`, `mla_decode` and `paged_gqa_decode`,
-ragged_paged_attention.py `rpa_decode`, collective_matmul.py). Row statistics are kept as (rows, 1)
+ragged_paged_attention.py `rpa_write` and `rpa_decode`, collective_matmul.py). Row statistics are kept as (rows, 1)
 columns here: the reference's lane-replicated (rows, 128) layout is a TPU register trick, not arithmetic.
 """
 
@@ -339,6 +339,21 @@ def paged_gqa_decode(q, k_pages, v_pages, block_tables, lengths):
             vt = page_by_kv_head(v_pages[block_tables[b, p], :, :], Hkv)
             row_max, row_sum, acc = online_softmax(s, vt, ok, row_max, row_sum, acc)
         out = out.at[b, :, :, :].set(finish(acc, row_sum, (T, H, Dh), dtype))
+    return out
+
+
+@autokernel.kernel
+def rpa_write(kv_cache, keys, values, page_indices, write_page, write_rows, write_first, write_stop, n_writes):
+    """Ragged paged attention's cache write (examples/ragged_paged_attention.py:33-47): the cache (pages, page_size,
+    Hkv, 2, Dh) with the step's new keys and values (T, Hkv, Dh) in it. Run w < n_writes[0] is a stretch of one
+    sequence's new tokens that lands in one page: the tokens from write_rows[w] on go to rows write_first[w] ..
+    write_stop[w] - 1 of page page_indices[write_page[w]]. How many runs there are is read as the kernel runs."""
+    P = kv_cache.shape[1]
+    out = kv_cache
+    for w in range(n_writes[0]):
+        tokens = autokernel.rows(write_rows[w], write_rows[w] + write_stop[w] - write_first[w], P)
+        side_by_side = jnp.stack([keys[tokens, :, :], values[tokens, :, :]], axis=2)
+        out = out.at[page_indices[write_page[w]], autokernel.rows(write_first[w], write_stop[w], P), :, :, :].set(side_by_side)
     return out
 
 

@@ -59,7 +59,7 @@ class Nest:
     stores: dict[str, Store]
     all_gathers: tuple[AllGather, ...] = ()
     index_reads: frozenset[str] = field(default_factory=frozenset)  # inputs read element-wise in masks
-    range_reads: frozenset[str] = field(default_factory=frozenset)  # inputs read element-wise in a reduction loop's range
+    range_reads: frozenset[str] = field(default_factory=frozenset)  # inputs read element-wise in a loop's range
     inplace: dict[str, str] = field(default_factory=dict)           # output -> the input it starts as (`out = q`)
 
     @property
@@ -68,8 +68,8 @@ class Nest:
 
     @property
     def runtime_ranges(self) -> bool:
-        """A reduction loop runs a number of times read from an input as the kernel runs
-        (`for p in range(cdiv(kv_lens[s], page_size))`, examples/ragged_paged_attention.py:138)."""
+        """A loop runs a number of times read from an input as the kernel runs (`for w in range(n_writes[0])`,
+        `for p in range(cdiv(kv_lens[s], page_size))`: examples/ragged_paged_attention.py:39, :138)."""
         return bool(self.range_reads)
 
     def error(self, message: str, node: ast.AST | None = None) -> KernelError:
@@ -130,7 +130,7 @@ class _Parser:
         reductions, bodies, segments = self._tile(tile_body)
         stores = self._stores(segments, bodies, outputs)
         index_reads = self._index_reads(reductions, params)
-        range_reads = self._range_reads(reductions, params)
+        range_reads = self._range_reads([*parallel, *reductions], params)
         return Nest(self.name, self.filename, f, tuple(params), tunable, tuple(prologue), allocations, outputs,
                     tuple(parallel), tuple(reductions), tuple(bodies), tuple(segments), stores, all_gathers,
                     frozenset(index_reads), frozenset(range_reads), inplace)

@@ -256,6 +256,7 @@ def _require_known_form(nest: Nest, fn, family: str) -> None:
                 "attention_block": "an attention block: causal attention over all heads, RMSNorm of the heads side by "
                                    "side, then `gelu(n @ w_up) @ w_down`",
                 "decode": "GQA decode's online softmax over the cache blocks",
+                "rpa_write": "ragged paged attention's cache write: runs of new tokens copied into their pages",
                 "rpa_decode": "ragged paged attention's decode case: the online softmax over a sequence's pages of a cache "
                               "that holds keys and values side by side",
                 "mla": "absorbed MLA decode's online softmax over the latent cache"}[family]
@@ -268,6 +269,10 @@ def _recognise(nest, fn, ns, specs, outputs, parallel, reductions, chips) -> Pla
     if n_red == 2 and n_par == 2 and len(nest.inputs) == 6 and not nest.runtime_masks and not nest.all_gathers:
         plan = _recognise_attention_block(nest, ns, specs, outputs, parallel, reductions)
         _require_known_form(nest, fn, "attention_block")
+        return plan
+    if n_red == 0 and nest.runtime_ranges:
+        plan = _recognise_rpa_write(nest, ns, specs, outputs, parallel)
+        _require_known_form(nest, fn, "rpa_write")
         return plan
     if n_red != 1:
         raise _unsupported(nest, f"{n_red} reduction loops (one is supported, or the two phases of an attention block)")
@@ -597,6 +602,31 @@ def _recognise_mla_decode(nest, ns, specs, outputs, parallel, reductions) -> Pla
     sch = _schedule.paged_decode_schedule(B, j.count)
     params = dict(B=B, T=T, H=H, C=C, R=R, S=S, page=block, pages=j.count, schedule=sch, mla=True)
     return Plan(nest, "decode", specs, outputs, parallel, reductions, params, runtime=True)
+
+
+def _recognise_rpa_write(nest, ns, specs, outputs, parallel) -> Plan:
+    """`rpa_write` (examples/ragged_paged_attention.py:33-47): (kv_cache, keys, values, page_indices, write_page,
+    write_rows, write_first, write_stop, n_writes), a tile per run, the run count read as the kernel runs, the output
+    the cache updated. What a tile stores is pinned by the fingerprint (the caller checks it); here the shapes."""
+    if len(parallel) != 1 or len(nest.inputs) != 9 or len(nest.outputs) != 1 \
+            or nest.inplace != {nest.outputs[0]: nest.inputs[0]} or nest.range_reads != {nest.inputs[8]}:
+        raise _unsupported(nest, "a run count read from an input other than ragged paged attention's cache write: "
+                                 "(kv_cache, keys, values, page_indices, write_page, write_rows, write_first, write_stop, "
+                                 "n_writes) with the cache updated in place")
+    cache, keys, values, page_indices, *tables, n_writes = specs[:9]
+    int32 = np.dtype(np.int32)
+    if cache.ndim != 5 or cache.shape[3] != 2 or keys.shape != values.shape or keys.ndim != 3 \
+            or keys.shape[1:] != (cache.shape[2], cache.shape[4]) or page_indices.ndim != 1 \
+            or any(t.ndim != 1 or t.shape != tables[0].shape for t in tables) or n_writes.shape != (1,) \
+            or any(np.dtype(x.dtype) != int32 for x in (page_indices, *tables, n_writes)) \
+            or len({np.dtype(x.dtype) for x in (cache, keys, values)}) != 1:
+        raise _unsupported(nest, "the cache write takes a cache (pages, page_size, Hkv, 2, D), keys and values (T, Hkv, D) "
+                                 "of its dtype, page_indices, four run tables of one length and n_writes (1,), int32")
+    max_runs = tables[0].shape[0]
+    sch = _schedule.runtime_schedule([Range(parallel[0].var, 0, max_runs, 1)], [Range("row", 0, 1, 1)])
+    params = dict(rpa_write=True, T=keys.shape[0], Hkv=cache.shape[2], D=cache.shape[4], page=cache.shape[1],
+                  num_pages=cache.shape[0], max_runs=max_runs, schedule=sch)
+    return Plan(nest, "rpa_write", specs, outputs, (Range(parallel[0].var, 0, max_runs, 1),), (), params, runtime=True)
 
 
 def _recognise_rpa_decode(nest, fn, ns, specs, outputs, parallel, reductions) -> Plan:

@@ -33,4 +33,8 @@ RECOGNISED: dict[str, dict[str, str]] = {
         "9c7c8eadbba15db816b68fdb97c1db23c79f3bd0271a905b33d9cc1f13b2ace2": "examples/ragged_paged_attention.py make_decode",
         "696fd4feefd3a8683940cba797e0bab498b59e7d6d01532804293f16acfa9fe4": "tilejax_b200/autokernel/kernels.py make_rpa_decode",
     },
+    "rpa_write": {
+        "def963b42a5c366a39776b84afb2a63038a660fb73310acbfba03d1e39d81308": "examples/ragged_paged_attention.py rpa_write",
+        "3fee2d20ba0172da09fb01183ac7ab746c160528b82cd1c3bd876fd6046eba06": "tilejax_b200/autokernel/kernels.py rpa_write",
+    },
 }

@@ -708,6 +708,35 @@ __global__ void __launch_bounds__(128)
   }
 }
 
+// The same write from the run tables the reference's `rpa_write` kernel takes (examples/ragged_paged_attention.py:33-47):
+// run w < n_writes[0] copies the tokens from write_rows[w] on to rows write_first[w] .. write_stop[w] - 1 of page
+// page_indices[write_page[w]]. One CTA per (row of a page, run); rows past the run, runs past the count, tokens or
+// rows out of range write nothing (the reference's out-of-bounds stores are dropped), indices into page_indices and
+// page numbers are clamped as its gathers are.
+__global__ void __launch_bounds__(128)
+    rpa_write_runs_kernel(__nv_bfloat16* __restrict__ cache, const __nv_bfloat16* __restrict__ keys,
+                          const __nv_bfloat16* __restrict__ values, const int32_t* __restrict__ page_indices,
+                          const int32_t* __restrict__ write_page, const int32_t* __restrict__ write_rows,
+                          const int32_t* __restrict__ write_first, const int32_t* __restrict__ write_stop,
+                          const int32_t* __restrict__ n_writes, int T, int n_page_indices, int Hkv, int page_size,
+                          int num_pages) {
+  const int w = blockIdx.y, r = blockIdx.x;
+  if (w >= n_writes[0]) return;
+  const int first = write_first[w], stop = write_stop[w];
+  const int row = first + r, t = write_rows[w] + r;
+  if (row >= stop || row < 0 || row >= page_size || t < 0 || t >= T) return;
+  const int entry = min(max(write_page[w], 0), n_page_indices - 1);
+  const int page = min(max(page_indices[entry], 0), num_pages - 1);
+  __nv_bfloat16* dst = cache + (static_cast<size_t>(page) * page_size + row) * Hkv * 2 * DEC_D;
+  const uint4* k = reinterpret_cast<const uint4*>(keys + static_cast<size_t>(t) * Hkv * DEC_D);
+  const uint4* v = reinterpret_cast<const uint4*>(values + static_cast<size_t>(t) * Hkv * DEC_D);
+  for (int u = threadIdx.x; u < Hkv * DEC_D / 8; u += blockDim.x) {
+    const int h = u / (DEC_D / 8), d = (u % (DEC_D / 8)) * 8;
+    *reinterpret_cast<uint4*>(dst + h * 2 * DEC_D + d) = k[u];
+    *reinterpret_cast<uint4*>(dst + h * 2 * DEC_D + DEC_D + d) = v[u];
+  }
+}
+
 // lengths[s] = kv_lens[s] for the decode sequences, 0 for the others (which then take one empty step).
 __global__ void rpa_decode_lengths_kernel(const int32_t* __restrict__ kv_lens, const int32_t* __restrict__ distribution,
                                           int32_t* __restrict__ lengths, int n, int max_len) {
@@ -775,6 +804,31 @@ int tjx_rpa_write_bf16(void* kv_cache, const void* keys, const void* values, con
       static_cast<__nv_bfloat16*>(kv_cache), static_cast<const __nv_bfloat16*>(keys),
       static_cast<const __nv_bfloat16*>(values), kv_lens, page_indices, cu_q_lens, distribution, S, Hkv, page_size,
       pages_per_seq, num_pages);
+  TJX_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int tjx_rpa_write_runs_bf16(void* kv_cache, const void* keys, const void* values, const int32_t* page_indices,
+                            const int32_t* write_page, const int32_t* write_rows, const int32_t* write_first,
+                            const int32_t* write_stop, const int32_t* n_writes, int T, int n_page_indices, int max_runs,
+                            int Hkv, int D, int page_size, int num_pages, tjx_stream_t stream) {
+  using namespace tjx;
+  if (int rc = check_device()) return rc;
+  if (!kv_cache || !keys || !values || !page_indices || !write_page || !write_rows || !write_first || !write_stop ||
+      !n_writes)
+    return fail(TJX_E_ARG, "an input pointer is null");
+  if (T <= 0 || n_page_indices <= 0 || max_runs <= 0 || Hkv <= 0 || page_size <= 0 || num_pages <= 0)
+    return fail(TJX_E_ARG, "sizes must be positive");
+  if (max_runs > 65535) return fail(TJX_E_LIMIT, "more than 65535 runs");
+  if (D != DEC_D) return fail(TJX_E_ARG, "head dimension must be 128");
+  const uintptr_t ptrs[] = {reinterpret_cast<uintptr_t>(kv_cache), reinterpret_cast<uintptr_t>(keys),
+                            reinterpret_cast<uintptr_t>(values)};
+  for (uintptr_t a : ptrs)
+    if (a & 15u) return fail(TJX_E_ARG, "kv_cache, keys and values must be 16-byte aligned");
+  rpa_write_runs_kernel<<<dim3(page_size, max_runs), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(kv_cache), static_cast<const __nv_bfloat16*>(keys),
+      static_cast<const __nv_bfloat16*>(values), page_indices, write_page, write_rows, write_first, write_stop, n_writes,
+      T, n_page_indices, Hkv, page_size, num_pages);
   TJX_CUDA(cudaGetLastError());
   return 0;
 }

@@ -471,6 +471,32 @@ def rpa_write(kv_cache: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, 
     return kv_cache
 
 
+def rpa_write_runs(kv_cache: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, page_indices: torch.Tensor,
+                   write_page: torch.Tensor, write_rows: torch.Tensor, write_first: torch.Tensor,
+                   write_stop: torch.Tensor, n_writes: torch.Tensor) -> torch.Tensor:
+    """The reference's `rpa_write` kernel (examples/ragged_paged_attention.py:33-47) on its own run tables: run
+    w < n_writes[0] copies the tokens from write_rows[w] on to rows write_first[w] .. write_stop[w] - 1 of page
+    page_indices[write_page[w]] of the cache (pages, page_size, Hkv, 2, D), IN PLACE; returns the cache."""
+    device = _need_cuda(kv_cache, keys, values, page_indices, write_page, write_rows, write_first, write_stop, n_writes)
+    if kv_cache.dim() != 5 or kv_cache.shape[3] != 2 or kv_cache.dtype != torch.bfloat16 or not kv_cache.is_contiguous():
+        raise ValueError("kv_cache is a contiguous (pages, page_size, Hkv, 2, D) bfloat16 tensor")
+    num_pages, page_size, Hkv, _, D = kv_cache.shape
+    if keys.shape != values.shape or keys.dim() != 3 or keys.shape[1:] != (Hkv, D) or keys.dtype != torch.bfloat16 \
+            or values.dtype != torch.bfloat16:
+        raise ValueError("keys and values are (T, Hkv, D) bfloat16")
+    tables = (write_page, write_rows, write_first, write_stop)
+    if any(t.dtype != torch.int32 or t.dim() != 1 or t.shape != write_page.shape for t in tables) \
+            or page_indices.dtype != torch.int32 or page_indices.dim() != 1 or n_writes.dtype != torch.int32 \
+            or n_writes.numel() < 1:
+        raise ValueError("the run tables are int32 vectors of one length, page_indices an int32 vector, n_writes int32 (1,)")
+    with torch.cuda.device(device):
+        check(library().tjx_rpa_write_runs_bf16(_ptr(kv_cache), _ptr(keys), _ptr(values), _ptr(page_indices),
+                                                _ptr(write_page), _ptr(write_rows), _ptr(write_first), _ptr(write_stop),
+                                                _ptr(n_writes), keys.shape[0], page_indices.numel(), write_page.numel(),
+                                                Hkv, D, page_size, num_pages, _stream()))
+    return kv_cache
+
+
 _rpa_workspaces: dict[tuple, torch.Tensor] = {}
 
 
