@@ -248,6 +248,21 @@ int tjx_rpa_prefill_bf16(const void* q, void* out, const void* kv_cache, const i
                          int S, int H, int Hkv, int D, int page_size, int pages_per_seq, int num_pages, float sm_scale,
                          void* workspace, size_t workspace_bytes, tjx_stream_t stream);
 
+/* Bytes of scratch tjx_rpa_prefill_tiles_bf16 needs for T token rows and tile tables of max_tiles entries. */
+size_t tjx_rpa_prefill_tiles_workspace_bytes(int T, int max_tiles);
+
+/* The same attention on the tile tables the reference's `rpa_prefill` kernel takes (examples/ragged_paged_attention.py:
+ * 204-243; its `prefill_tiles`, :252-275, makes them in plain JAX): tile k < n_tiles[0] is the query rows tile_rows[k] ..
+ * tile_rows[k + 1] - 1 of q (up to 256), the first at cache position tile_pos[k], of the sequence whose pages start at
+ * page_indices[tile_page[k]]; a row at position p attends to the positions up to p. tile_page and tile_pos are
+ * int32[max_tiles], tile_rows int32[max_tiles + 1], n_tiles int32[1]. A small kernel cuts the tiles into this kernel's
+ * 128 queries; rows no tile covers keep q (out may be q). Constraints as tjx_rpa_prefill_bf16. */
+int tjx_rpa_prefill_tiles_bf16(const void* q, void* out, const void* kv_cache, const int32_t* page_indices,
+                               const int32_t* tile_page, const int32_t* tile_rows, const int32_t* tile_pos,
+                               const int32_t* n_tiles, int T, int max_tiles, int n_page_indices, int H, int Hkv, int D,
+                               int page_size, int num_pages, float sm_scale, void* workspace, size_t workspace_bytes,
+                               tjx_stream_t stream);
+
 /* Which kernel tjx_mla_decode_bf16 launches from now on: 1 (the default) the tcgen05 kernel, 64 rows per CTA with
  * scores and output in TMEM; 0 the warp-level MMA kernel, 16 rows per CTA. An A/B switch for measurements: the two
  * agree to rounding. No counterpart in the reference. */

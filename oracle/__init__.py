@@ -28,8 +28,8 @@ from .decode import (
 )
 from .matmul import causal_matmul_ref, collective_row_order, matmul_ref
 from .rmsnorm import rmsnorm_matmul_f64, rmsnorm_matmul_ref
-from .rpa import (rpa_decode_f64, rpa_decode_ref, rpa_inputs, rpa_prefill_f64, rpa_prefill_ref, rpa_write_ref,
-                  rpa_write_runs)
+from .rpa import (rpa_decode_f64, rpa_decode_ref, rpa_inputs, rpa_prefill_f64, rpa_prefill_ref, rpa_prefill_tiles,
+                  rpa_write_ref, rpa_write_runs)
 from .steps import (
     attention_step_tables,
     causal_tile_tables,
@@ -61,6 +61,7 @@ __all__ = [
     "rpa_inputs",
     "rpa_prefill_f64",
     "rpa_prefill_ref",
+    "rpa_prefill_tiles",
     "rpa_write_ref",
     "rpa_write_runs",
     "to_pages",

@@ -157,6 +157,28 @@ def rpa_decode_f64(q, kv_cache, kv_lens, page_indices, distribution, sm_scale: f
 BLOCK_Q = 256  # examples/ragged_paged_attention.py:154
 
 
+def rpa_prefill_tiles(kv_lens, page_indices, cu_q_lens, distribution, max_tokens: int, block_q: int = BLOCK_Q) -> dict:
+    """`prefill_tiles` (examples/ragged_paged_attention.py:252-275) in NumPy: a tile per block of block_q queries of
+    each sequence in [distribution[0], distribution[2]); int32 arrays of the tile count's bound, cdiv(T, block_q) + S
+    (tile_rows one longer), in the order of `rpa_prefill`'s parameters, n_tiles of shape (1,)."""
+    S = kv_lens.shape[0]
+    pps = page_indices.shape[0] // S
+    seqs = np.arange(S)
+    q_len = cu_q_lens[1:] - cu_q_lens[:-1]
+    mixed = (seqs >= distribution[0]) & (seqs < distribution[2])
+    blocks = np.where(mixed, (q_len + block_q - 1) // block_q, 0)
+    ends = np.cumsum(blocks)
+    k = np.arange(-(-max_tokens // block_q) + S)
+    seq = np.minimum((ends[None, :] <= k[:, None]).sum(axis=1), S - 1)
+    b = k - (ends[seq] - blocks[seq])
+    rows = cu_q_lens[seq] + b * block_q
+    stop = np.minimum(rows + block_q, cu_q_lens[seq + 1])
+    pos = kv_lens[seq] - q_len[seq] + b * block_q
+    i32 = lambda a: np.asarray(a, np.int32)  # noqa: E731
+    return dict(tile_page=i32(seq * pps), tile_rows=i32(np.concatenate([rows[:1], stop])), tile_pos=i32(pos),
+                tile_stop=i32(pos + (stop - rows)), n_tiles=i32(ends[-1:]))
+
+
 def rpa_prefill_ref(q, kv_cache, kv_lens, page_indices, cu_q_lens, distribution, sm_scale: float, pages_per_step: int = 4):
     """examples/ragged_paged_attention.py:196-275, tile by tile and step by step: a tile is a block of up to 256 new
     tokens of a sequence in [distribution[0], distribution[2]) (`prefill_tiles`, :252-275), its first token at cache

@@ -1,5 +1,5 @@
-"""Ragged paged attention's cache write and decode case through the front end (`@autokernel.kernel` on the loop nests
-of examples/ragged_paged_attention.py:33-47 and :121-149): trip counts read from inputs as the kernel runs, outputs
+"""Ragged paged attention's cache write, decode case and prefill case through the front end (`@autokernel.kernel` on the
+loop nests of examples/ragged_paged_attention.py:33-47, :121-149 and :204-243): trip counts read from inputs as the kernel runs, outputs
 that are inputs updated, rows chosen as the kernel runs (`rows`), a cache read and written as paired words. On the CPU: what the nest means (`kernel.reference`) against the
 oracle bit for bit, what it lowers to, what is refused. The reference's own example is used unmodified when its tree
 is at hand."""
@@ -199,3 +199,59 @@ def test_the_references_own_write_kernel_is_recognised_unmodified():
     args, want = write_inputs()
     np.testing.assert_array_equal(kernel.reference(*args).view(np.uint16), want.view(np.uint16))
     assert "tjx_rpa_write_runs_bf16" in kernel.lower(*args).source
+
+
+# ----------------------------------------------------------------------------- the prefill / mixed case
+
+
+def prefill_inputs(**sizes):
+    """Two decode sequences, then three with 300, 7 and 130 new tokens on prefixes of 0, 128 and 270 positions."""
+    sizes = dict(dict(heads=8, kv_heads=2, max_len=1024, max_tokens=448, max_seqs=8, seed=3), **sizes)
+    inp = oracle.rpa_inputs([1, 1, 300, 7, 130], [513, 1, 300, 135, 400], **sizes)
+    cache = oracle.rpa_write_ref(inp["kv_cache"], inp["keys"], inp["values"], inp["kv_lens"], inp["page_indices"],
+                                 inp["cu_q_lens"], inp["distribution"])
+    tiles = oracle.rpa_prefill_tiles(inp["kv_lens"], inp["page_indices"], inp["cu_q_lens"], inp["distribution"], 448)
+    return inp, cache, (inp["q"], cache, inp["page_indices"], *tiles.values())
+
+
+def test_the_prefill_nest_means_what_the_oracle_says_and_lowers_to_the_tile_kernel():
+    inp, cache, args = prefill_inputs()
+    kernel = K.make_rpa_prefill(SCALE)
+    assert kernel.nest.inplace == {"out": "q"} and kernel.nest.range_reads == {"n_tiles", "tile_stop"}
+    want = oracle.rpa_prefill_ref(inp["q"], cache, inp["kv_lens"], inp["page_indices"], inp["cu_q_lens"],
+                                  inp["distribution"], SCALE, pages_per_step=1)
+    got = kernel.reference(*args)
+    np.testing.assert_array_equal(got.view(np.uint16), want.view(np.uint16))
+    np.testing.assert_array_equal(got[:2].view(np.uint16), inp["q"][:2].view(np.uint16))  # the decode tokens' rows stay
+    exact = oracle.rpa_prefill_f64(inp["q"], cache, inp["kv_lens"], inp["page_indices"], inp["cu_q_lens"],
+                                   inp["distribution"], SCALE)
+    assert np.abs(got.astype(np.float64) - exact).max() <= 2e-2
+    assert fingerprint.fingerprint(kernel) in RECOGNISED["rpa_prefill"]
+    lowered = kernel.lower(*args)
+    p = lowered.plan.params
+    assert lowered.plan.family == "rpa_prefill" and p["sm_scale"] == SCALE and p["max_tiles"] == args[3].shape[0]
+    assert "tjx_rpa_prefill_tiles_bf16" in lowered.source
+    # The kernel's own limits are KernelErrors before anything runs: pages of 64, an odd group of query heads.
+    _, _, small_pages = prefill_inputs(page_size=64)
+    with pytest.raises(KernelError, match="pages of 128"):
+        kernel.lower(*small_pages)
+    _, _, odd = prefill_inputs(heads=6, kv_heads=2)
+    with pytest.raises(KernelError, match="even number of query heads"):
+        kernel.lower(*odd)
+
+
+@needs_reference
+def test_the_references_own_prefill_kernel_is_recognised_unmodified():
+    stand_ins = {"jax": jaxlike, "jnp": jaxlike.numpy, "autokernel": autokernel, "__name__": "example"}
+    ns = fingerprint.load_example(os.path.join(EXAMPLES, "ragged_paged_attention.py"), stand_ins)
+    kernel = ns["make_prefill"](SCALE)  # head_rows / token_heads, dot_general over every KV head, four pages a step
+    assert fingerprint.fingerprint(kernel) in RECOGNISED["rpa_prefill"]
+    inp, cache, args = prefill_inputs()
+    tiles = ns["PrefillTiles"](pages=2)
+    want = oracle.rpa_prefill_ref(inp["q"], cache, inp["kv_lens"], inp["page_indices"], inp["cu_q_lens"],
+                                  inp["distribution"], SCALE, pages_per_step=2)
+    got = kernel.reference(*args, tiles)
+    assert np.abs(got.astype(np.float64) - want.astype(np.float64)).max() <= 2e-2  # the same sums in another order
+    lowered = kernel.lower(*args, tiles)
+    assert "tjx_rpa_prefill_tiles_bf16" in lowered.source and lowered.plan.params["sm_scale"] == SCALE
+    assert kernel.lower(*args, ns["PrefillTiles"](pages=8)).entry is not None  # pages per step: not the kernel's business

@@ -162,3 +162,26 @@ def test_the_write_nest_runs_through_the_front_end_and_the_run_kernel_writes_in_
     same = ops.rpa_write_runs(dev["kv_cache"], dev["keys"], dev["values"], dev["page_indices"], *tables)
     assert same.data_ptr() == dev["kv_cache"].data_ptr() and torch.equal(same, got)     # the C entry: in place
     assert torch.equal(ops.rpa_write(*(dev[n] for n in NAMES)), got)                    # writing again changes nothing
+
+
+def test_the_prefill_nest_runs_through_the_front_end():
+    from tilejax_b200.autokernel import kernels
+
+    inp, dev = step([1, 1, 300, 7, 130], [513, 1, 300, 135, 400], max_len=1024, max_tokens=448, max_seqs=8)
+    cache = ops.rpa_write(*(dev[n] for n in NAMES))
+    tiles = oracle.rpa_prefill_tiles(inp["kv_lens"], inp["page_indices"], inp["cu_q_lens"], inp["distribution"], 448)
+    tables = [to_device(v) for v in tiles.values()]
+    scale = 128**-0.5
+    kernel = kernels.make_rpa_prefill(scale)
+    q_before = dev["q"].clone()
+    args = (dev["q"], cache, dev["page_indices"], *tables)
+    got = kernel(*args)
+    assert ops.device_status() == 0 and torch.equal(dev["q"], q_before)
+    # The tiles of 256 cut in two are the tiles of 128 the other entry point builds itself: the same launch.
+    assert torch.equal(got, ops.rpa_prefill(dev["q"], cache, dev["kv_lens"], dev["page_indices"], dev["cu_q_lens"],
+                                            dev["distribution"], scale))
+    host_cache = to_host(cache)
+    exact = oracle.rpa_prefill_f64(inp["q"], host_cache, inp["kv_lens"], inp["page_indices"], inp["cu_q_lens"],
+                                   inp["distribution"], scale)
+    assert np.abs(f64(to_host(got)) - exact).max() <= 2e-2
+    assert kernel.verify(*args) <= 2e-2

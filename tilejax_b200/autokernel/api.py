@@ -340,6 +340,11 @@ def _check_kernel_rules(plan: Plan) -> None:
             raise nest.error("the attention kernel takes head_dim 128 and blocks that are multiples of 128")
         if any(np.dtype(s.dtype) != bf16 for s in plan.specs[:3]):
             raise nest.error("the attention kernel takes bfloat16 q, k, v")
+    elif plan.family == "rpa_prefill":
+        if p["D"] != 128 or p["page"] != 128 or p["H"] % p["Hkv"] or (p["H"] // p["Hkv"]) % 2 \
+                or any(np.dtype(s.dtype) != bf16 for s in plan.specs[:2]):
+            raise nest.error("the paged prefill kernel takes bfloat16 q and cache, head_dim 128, pages of 128 positions and "
+                             "an even number of query heads per KV head")
     elif plan.family == "rpa_write":
         if p["D"] != 128 or any(np.dtype(s.dtype) != bf16 for s in plan.specs[:3]):
             raise nest.error("the cache write kernel takes a bfloat16 cache, keys and values of head_dim 128")
@@ -387,6 +392,8 @@ def launch_key(plan: Plan, config: Config) -> tuple:
         return ("attention_block",)
     if plan.family == "rpa_write":
         return ("rpa_write",)
+    if plan.family == "rpa_prefill":
+        return ("rpa_prefill",)
     if p.get("mla"):
         return ("mla_decode",)
     if p.get("rpa"):
@@ -503,6 +510,21 @@ def _lower(plan: Plan, config: Config) -> tuple[str, Callable[..., Any]]:
                                       write_stop, n_writes)
 
         return text, write
+    if plan.family == "rpa_prefill":
+        text = header + (
+            f"kernel      tjx_rpa_prefill_tiles_bf16 (the causal attention kernel's paged instantiation: a small kernel cuts "
+            f"the tiles into 128 queries; a unit = (tile, KV head, two of its query heads), a block = one page through "
+            f"page_indices by 3-D TMA; outputs replace the queries' rows)\n"
+            f"problem     {p['T']} token rows, {p['H']} / {p['Hkv']} heads, head_dim {p['D']}, pages of {p['page']}, pool of "
+            f"{p['num_pages']}, at most {p['max_tiles']} tiles of up to 256 queries, softmax scale {p['sm_scale']:.6g}\n"
+            f"steps       how many tiles there are and how many pages each walks is read from n_tiles and tile_pos / "
+            f"tile_rows on the device; a tunable's pages per step only shapes the reference's own steps\n"
+            f"in place    the reference donates q and updates it; this entry returns a new array holding q's other rows\n")
+
+        def prefill(q, cache, page_indices, tile_page, tile_rows, tile_pos, tile_stop, n_tiles):
+            return ops.rpa_prefill_tiles(q, cache, page_indices, tile_page, tile_rows, tile_pos, n_tiles, p["sm_scale"])
+
+        return text, prefill
     if p.get("rpa"):
         text = header + (
             f"kernel      tjx_rpa_decode_bf16 (the paged decode kernel on the cache's own layout: two tensor maps over the "

@@ -200,7 +200,8 @@ def main(argv: list[str]) -> None:
     families = {"attention": ["causal_attention"], "decode": ["paged_gqa_decode", "gqa_decode"], "mla": ["mla_decode"],
                 "rmsnorm": ["rmsnorm_matmul"], "attention_block": ["attention_block"], "rpa_write": ["rpa_write"]}
     # Kernels made by a function of the softmax scale: (family, the maker's name here, the maker's name there, file).
-    makers = [("rpa_decode", "make_rpa_decode", "make_decode", "ragged_paged_attention.py")]
+    makers = [("rpa_decode", "make_rpa_decode", "make_decode", "ragged_paged_attention.py"),
+              ("rpa_prefill", "make_rpa_prefill", "make_prefill", "ragged_paged_attention.py")]
     found: dict[str, dict[str, str]] = {f: {} for f in [*families, *(m[0] for m in makers)]}
     for family, names in families.items():
         for name in names:

@@ -237,6 +237,33 @@ def _dot(a, b, preferred_element_type=None, precision=None):
     return Array(np.matmul(a.astype(acc), b.astype(acc)))
 
 
+def _dot_general(a, b, dimension_numbers, preferred_element_type=None, precision=None):
+    """jax.lax.dot_general: contract and batch the listed dimensions; the result is (batch..., a's free..., b's
+    free...), accumulated in `preferred_element_type` (else as `@` would)."""
+    (ca, cb), (ba, bb) = dimension_numbers
+    a, b = np.asarray(_raw(a)), np.asarray(_raw(b))
+    acc = np.dtype(preferred_element_type) if preferred_element_type is not None else None
+    letters = iter("abcdefghijklmnopqrstuvwxyz")
+    ia, ib = [None] * a.ndim, [None] * b.ndim
+    for x, y in zip(ba, bb):
+        ia[x] = ib[y] = next(letters)
+    for x, y in zip(ca, cb):
+        ia[x] = ib[y] = next(letters)
+    for names in (ia, ib):
+        for n, name in enumerate(names):
+            if name is None:
+                names[n] = next(letters)
+    free_a = [ia[n] for n in range(a.ndim) if n not in ba and n not in ca]
+    free_b = [ib[n] for n in range(b.ndim) if n not in bb and n not in cb]
+    spec = f"{''.join(ia)},{''.join(ib)}->{''.join(ia[x] for x in ba)}{''.join(free_a)}{''.join(free_b)}"
+    if acc is None:
+        integer = np.issubdtype(a.dtype, np.integer)
+        wide = np.int32 if integer else np.float32
+        out = np.einsum(spec, a.astype(wide), b.astype(wide))
+        return Array(out if getattr(_state, "mxu", False) else out.astype(np.promote_types(a.dtype, b.dtype)))
+    return Array(np.einsum(spec, a.astype(acc), b.astype(acc)))
+
+
 def _concatenate(arrays, axis=0):
     return Array(np.concatenate([np.asarray(_raw(a)) for a in arrays], axis=axis))
 
@@ -299,6 +326,7 @@ numpy = types.SimpleNamespace(
 )
 nn = types.SimpleNamespace(gelu=_gelu)
 lax = types.SimpleNamespace(broadcasted_iota=_broadcasted_iota, bitcast_convert_type=_bitcast_convert_type,
+                            dot_general=_dot_general,
                             rsqrt=_lift(lambda x: (1.0 / np.sqrt(np.asarray(x))).astype(np.asarray(x).dtype)))
 
 

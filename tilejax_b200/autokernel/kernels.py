@@ -3,7 +3,7 @@
 Each is the plain loop nest over tiles whose meaning the kernel must reproduce — `kernel.fn` runs it as written on
 the CPU — with the same structure as the reference's examples (examples/matmul.py, causal_matmul.py,
 causal_attention.py, rmsnorm_matmul.py, decode.py `gqa_decode`, `mla_decode` and `paged_gqa_decode`,
-ragged_paged_attention.py `rpa_write` and `rpa_decode`, collective_matmul.py). Row statistics are kept as (rows, 1)
+ragged_paged_attention.py `rpa_write`, `rpa_decode` and `rpa_prefill`, collective_matmul.py). Row statistics are kept as (rows, 1)
 columns here: the reference's lane-replicated (rows, 128) layout is a TPU register trick, not arithmetic.
 """
 
@@ -393,6 +393,40 @@ def make_rpa_decode(sm_scale: float) -> autokernel.Kernel:
         return out
 
     return rpa_decode
+
+
+PREFILL_QUERIES = 256  # query rows per prefill tile (examples/ragged_paged_attention.py:154)
+
+
+def make_rpa_prefill(sm_scale: float) -> autokernel.Kernel:
+    """Ragged paged attention's prefill / mixed case for one softmax scale (examples/ragged_paged_attention.py:196-243):
+    tile k < n_tiles[0] is the rows tile_rows[k] .. tile_rows[k + 1] - 1 of q (at most 256), the new tokens of a
+    sequence whose pages start at page_indices[tile_page[k]]; the first sits at cache position tile_pos[k], and a row
+    at position p attends to the positions up to p, all before tile_stop[k]. The result is q with those rows replaced.
+    How many tiles there are, and how many pages a tile walks, is read as the kernel runs."""
+
+    @autokernel.kernel
+    def rpa_prefill(q, kv_cache, page_indices, tile_page, tile_rows, tile_pos, tile_stop, n_tiles):
+        _, H, Dh = q.shape
+        P, Hkv = kv_cache.shape[1], kv_cache.shape[2]
+        rows = PREFILL_QUERIES * (H // Hkv)
+        dtype = q.dtype
+        out = q
+        for k in range(n_tiles[0]):
+            tokens = autokernel.rows(tile_rows[k], tile_rows[k + 1], PREFILL_QUERIES)
+            qt = queries_by_kv_head(q[tokens, :, :], Hkv)
+            row_max = jnp.full((Hkv, rows, 1), MASK_VALUE, jnp.float32)
+            row_sum = jnp.zeros((Hkv, rows, 1), jnp.float32)
+            acc = jnp.zeros((Hkv, rows, Dh), jnp.float32)
+            for j in range(0, tile_stop[k], P):
+                kt, vt = cache_page_by_kv_head(kv_cache[page_indices[tile_page[k] + j // P], :, :, :, :])
+                scores = jnp.dot(qt, kt.transpose(0, 2, 1), preferred_element_type=jnp.float32) * sm_scale
+                ok = visible(P, j, tile_pos[k] + PREFILL_QUERIES, PREFILL_QUERIES, H // Hkv)
+                row_max, row_sum, acc = online_softmax(scores, vt, ok, row_max, row_sum, acc)
+            out = out.at[tokens, :, :].set(finish(acc, row_sum, (PREFILL_QUERIES, H, Dh), dtype))
+        return out
+
+    return rpa_prefill
 
 
 @autokernel.kernel

@@ -257,6 +257,8 @@ def _require_known_form(nest: Nest, fn, family: str) -> None:
                                    "side, then `gelu(n @ w_up) @ w_down`",
                 "decode": "GQA decode's online softmax over the cache blocks",
                 "rpa_write": "ragged paged attention's cache write: runs of new tokens copied into their pages",
+                "rpa_prefill": "ragged paged attention's prefill case: causal attention of a tile of a sequence's new tokens "
+                               "over its pages",
                 "rpa_decode": "ragged paged attention's decode case: the online softmax over a sequence's pages of a cache "
                               "that holds keys and values side by side",
                 "mla": "absorbed MLA decode's online softmax over the latent cache"}[family]
@@ -276,6 +278,10 @@ def _recognise(nest, fn, ns, specs, outputs, parallel, reductions, chips) -> Pla
         return plan
     if n_red != 1:
         raise _unsupported(nest, f"{n_red} reduction loops (one is supported, or the two phases of an attention block)")
+    if nest.runtime_ranges and len(nest.inputs) == 8:
+        plan = _recognise_rpa_prefill(nest, fn, ns, specs, outputs, parallel, reductions)
+        _require_known_form(nest, fn, "rpa_prefill")
+        return plan
     if nest.runtime_ranges:
         plan = _recognise_rpa_decode(nest, fn, ns, specs, outputs, parallel, reductions)
         _require_known_form(nest, fn, "rpa_decode")
@@ -629,6 +635,43 @@ def _recognise_rpa_write(nest, ns, specs, outputs, parallel) -> Plan:
     return Plan(nest, "rpa_write", specs, outputs, (Range(parallel[0].var, 0, max_runs, 1),), (), params, runtime=True)
 
 
+def _closed_scale(nest, fn) -> float:
+    """The softmax scale of a kernel made by `make_...(sm_scale)`: the one float the function closes over."""
+    closed = [c.cell_contents for c in (fn.__closure__ or ()) if isinstance(c.cell_contents, float)]
+    if len(closed) != 1:
+        raise _unsupported(nest, "the kernel must close over its softmax scale, one float (`make_decode(sm_scale)`)")
+    return float(closed[0])
+
+
+def _recognise_rpa_prefill(nest, fn, ns, specs, outputs, parallel, reductions) -> Plan:
+    """`rpa_prefill` (examples/ragged_paged_attention.py:204-243): (q, kv_cache, page_indices, tile_page, tile_rows,
+    tile_pos, tile_stop, n_tiles), a tile per block of a sequence's new tokens, the tile count and each tile's pages
+    read as the kernel runs, the output q updated. What the tile code computes is pinned by its fingerprint (the
+    caller checks it); here the shapes and the loops."""
+    if len(parallel) != 1 or len(nest.outputs) != 1 or nest.inplace != {nest.outputs[0]: nest.inputs[0]} \
+            or nest.range_reads != {nest.inputs[6], nest.inputs[7]}:
+        raise _unsupported(nest, "trip counts read from inputs other than ragged paged attention's prefill case: (q, "
+                                 "kv_cache, page_indices, tile_page, tile_rows, tile_pos, tile_stop, n_tiles) with q "
+                                 "updated in place, tiles counted by n_tiles and their pages by tile_stop")
+    q, cache, page_indices, tile_page, tile_rows, tile_pos, tile_stop, n_tiles = specs[:8]
+    int32 = np.dtype(np.int32)
+    tiles = tile_page.shape[0] if tile_page.ndim == 1 else -1
+    if q.ndim != 3 or cache.ndim != 5 or cache.shape[3] != 2 or cache.shape[4] != q.shape[2] or page_indices.ndim != 1 \
+            or any(t.shape != (tiles,) for t in (tile_pos, tile_stop)) or tile_rows.shape != (tiles + 1,) \
+            or n_tiles.shape != (1,) or np.dtype(q.dtype) != np.dtype(cache.dtype) \
+            or any(np.dtype(x.dtype) != int32 for x in (page_indices, tile_page, tile_rows, tile_pos, tile_stop, n_tiles)):
+        raise _unsupported(nest, "ragged paged prefill takes q (T, H, D), a cache (pages, page_size, Hkv, 2, D) of q's "
+                                 "dtype, page_indices, tile tables (tile_rows one longer) and n_tiles (1,), int32")
+    T, H, D = q.shape
+    num_pages, page, Hkv = cache.shape[0], cache.shape[1], cache.shape[2]
+    max_pages = -(-page_indices.shape[0] // 1)  # a tile walks at most every listed page
+    sch = _schedule.runtime_schedule([Range(parallel[0].var, 0, tiles, 1)], [Range(reductions[0].var, 0, max_pages, 1)])
+    params = dict(rpa_prefill=True, T=T, H=H, Hkv=Hkv, D=D, page=page, num_pages=num_pages, max_tiles=tiles,
+                  sm_scale=_closed_scale(nest, fn), schedule=sch)
+    return Plan(nest, "rpa_prefill", specs, outputs, (Range(parallel[0].var, 0, tiles, 1),),
+                (Range(reductions[0].var, 0, max_pages, 1),), params, runtime=True)
+
+
 def _recognise_rpa_decode(nest, fn, ns, specs, outputs, parallel, reductions) -> Plan:
     """`rpa_decode` (examples/ragged_paged_attention.py:121-149): (q, kv_cache, kv_lens, page_indices, distribution), a
     tile per sequence, its pages counted from kv_lens as the kernel runs, the output q updated. What the tile code
@@ -655,14 +698,10 @@ def _recognise_rpa_decode(nest, fn, ns, specs, outputs, parallel, reductions) ->
     if (s_loop.start, s_loop.stop, s_loop.step) != (0, min(S, T), 1):
         raise _unsupported(nest, "the sequence loop must run over min(sequences, tokens): sequence s is token s",
                            nest.parallel[0].node)
-    # The softmax scale: the one float the function closes over.
-    closed = [c.cell_contents for c in (fn.__closure__ or ()) if isinstance(c.cell_contents, float)]
-    if len(closed) != 1:
-        raise _unsupported(nest, "the kernel must close over its softmax scale, one float (`make_decode(sm_scale)`)")
     n = min(S, T)
     sch = _schedule.paged_decode_schedule(n, pages)
     params = dict(B=n, T=1, H=H, Hkv=Hkv, D=D, page=page, pages=pages, num_pages=num_pages, schedule=sch, rpa=True,
-                  tokens=T, sequences=S, sm_scale=float(closed[0]))
+                  tokens=T, sequences=S, sm_scale=_closed_scale(nest, fn))
     reductions = (Range(reductions[0].var, 0, pages, 1),)
     return Plan(nest, "decode", specs, outputs, parallel, reductions, params, runtime=True)
 

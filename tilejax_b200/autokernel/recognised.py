@@ -33,6 +33,10 @@ RECOGNISED: dict[str, dict[str, str]] = {
         "9c7c8eadbba15db816b68fdb97c1db23c79f3bd0271a905b33d9cc1f13b2ace2": "examples/ragged_paged_attention.py make_decode",
         "696fd4feefd3a8683940cba797e0bab498b59e7d6d01532804293f16acfa9fe4": "tilejax_b200/autokernel/kernels.py make_rpa_decode",
     },
+    "rpa_prefill": {
+        "cbaa8046c2a0deb3deedebe1db8dad7806c5cd06e62a0ed9662d5a627fc5f8d0": "examples/ragged_paged_attention.py make_prefill",
+        "0fce51cce7ad19b9991a5e8051ac449fa8804e234a5e9cee9a155610c3621781": "tilejax_b200/autokernel/kernels.py make_rpa_prefill",
+    },
     "rpa_write": {
         "def963b42a5c366a39776b84afb2a63038a660fb73310acbfba03d1e39d81308": "examples/ragged_paged_attention.py rpa_write",
         "3fee2d20ba0172da09fb01183ac7ab746c160528b82cd1c3bd876fd6046eba06": "tilejax_b200/autokernel/kernels.py rpa_write",

@@ -68,6 +68,7 @@ struct AttnParams {
   const int32_t* n_tiles;        // [1]
   const int32_t* page_indices;
   int Hkv, group, num_pages;     // KV heads, query heads per KV head (even), pages in the pool
+  int n_page_indices;            // entries of page_indices
   float scale_log2e;             // log2(e) times the softmax scale (the queries do not arrive pre-scaled)
   __nv_bfloat16* out_tokens;     // (T, H, D): row (token, head)
 };
@@ -281,7 +282,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
           const uint32_t kd = base + L::K_OFF + stage * L::TILE_BYTES;
           // Paged: block n is page page_indices[page0 + n] of the cache seen as (D, Hkv * 2, pages * 128), the key
           // of KV head g at index 2 g of the middle dimension, its value at 2 g + 1.
-          const int page_row = PAGED ? min(max(p.page_indices[u.page0 + n], 0), p.num_pages - 1) * AT_BKV : 0;
+          const int page_row = PAGED ? min(max(p.page_indices[min(max(u.page0 + n, 0), p.n_page_indices - 1)], 0),
+                                               p.num_pages - 1) * AT_BKV : 0;  // index and page clamped, as a gather's are
           mbar_expect_tx(k_full(stage), L::TILE_BYTES);
           if (PAGED) {
             tma_load_3d(kd, &map_k, 0, 2 * u.kv_head, page_row, k_full(stage));
@@ -761,54 +763,84 @@ __global__ void __launch_bounds__(256)
   if (threadIdx.x == 0) n_tiles[0] = min(carry_sh, max_tiles);
 }
 
-static size_t attn_align256(size_t n) { return (n + 255) & ~static_cast<size_t>(255); }
-
-}  // namespace tjx
-
-extern "C" size_t tjx_rpa_prefill_workspace_bytes(int T, int S) {
-  if (T <= 0 || S <= 0) return 0;
-  const size_t max_tiles = static_cast<size_t>((T + tjx::AT_BQ - 1) / tjx::AT_BQ) + S;
-  return 4 * tjx::attn_align256(max_tiles * 4) + 256;
+// The tiles of the reference's `rpa_prefill` kernel (examples/ragged_paged_attention.py:204-243: tile k is the query
+// rows tile_rows[k] .. tile_rows[k + 1] - 1, up to 256 of them, the first at cache position tile_pos[k], of the
+// sequence whose pages start at page_indices[tile_page[k]]) cut into this kernel's tiles of 128 queries. One CTA;
+// thread t handles tiles t, t + 256, ...; an exclusive scan of their piece counts gives each its first piece.
+__global__ void __launch_bounds__(256)
+    rpa_split_tiles_kernel(const int32_t* __restrict__ in_page, const int32_t* __restrict__ in_rows,
+                           const int32_t* __restrict__ in_pos, const int32_t* __restrict__ in_count, int max_in,
+                           int max_tiles, int T, int32_t* __restrict__ tile_row0, int32_t* __restrict__ tile_rows,
+                           int32_t* __restrict__ tile_pos, int32_t* __restrict__ tile_page,
+                           int32_t* __restrict__ n_tiles) {
+  __shared__ int carry_sh, scan_sh[256];
+  if (threadIdx.x == 0) carry_sh = 0;
+  __syncthreads();
+  const int count = min(max(in_count[0], 0), max_in);
+  for (int k0 = 0; k0 < count; k0 += 256) {
+    const int k = k0 + threadIdx.x;
+    int first_row = 0, rows = 0;
+    if (k < count) {
+      first_row = in_rows[k];
+      rows = in_rows[k + 1] - first_row;
+      if (first_row < 0 || rows < 0 || first_row + rows > T) rows = 0;  // not a range of q's rows: nothing to do
+    }
+    const int mine = (rows + AT_BQ - 1) / AT_BQ;
+    scan_sh[threadIdx.x] = mine;
+    __syncthreads();
+    for (int d = 1; d < 256; d <<= 1) {  // inclusive scan
+      const int y = threadIdx.x >= d ? scan_sh[threadIdx.x - d] : 0;
+      __syncthreads();
+      scan_sh[threadIdx.x] += y;
+      __syncthreads();
+    }
+    const int first = carry_sh + scan_sh[threadIdx.x] - mine;
+    for (int b = 0; b < mine; ++b) {
+      const int out = first + b;
+      if (out >= max_tiles) break;
+      tile_row0[out] = first_row + b * AT_BQ;
+      tile_rows[out] = min(AT_BQ, rows - b * AT_BQ);
+      tile_pos[out] = in_pos[k] + b * AT_BQ;
+      tile_page[out] = in_page[k];
+    }
+    __syncthreads();
+    if (threadIdx.x == 255) carry_sh += scan_sh[255];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) n_tiles[0] = min(carry_sh, max_tiles);
 }
 
-extern "C" int tjx_rpa_prefill_bf16(const void* q, void* out, const void* kv_cache, const int32_t* kv_lens,
-                                    const int32_t* page_indices, const int32_t* cu_q_lens,
-                                    const int32_t* distribution, int T, int S, int H, int Hkv, int D, int page_size,
-                                    int pages_per_seq, int num_pages, float sm_scale, void* workspace,
-                                    size_t workspace_bytes, tjx_stream_t stream) {
-  using namespace tjx;
-  if (int rc = check_device()) return rc;
-  if (!q || !out || !kv_cache || !kv_lens || !page_indices || !cu_q_lens || !distribution)
-    return fail(TJX_E_ARG, "an input or output pointer is null");
-  if (T <= 0 || S <= 0 || H <= 0 || Hkv <= 0 || pages_per_seq <= 0 || num_pages <= 0)
-    return fail(TJX_E_ARG, "sizes must be positive");
+static size_t attn_align256(size_t n) { return (n + 255) & ~static_cast<size_t>(255); }
+
+// The workspace's tile arrays (max_tiles entries each, then the count) as the kernel's parameters.
+static void rpa_tile_arrays(AttnParams& p, void* workspace, int max_tiles) {
+  uint8_t* w = static_cast<uint8_t*>(workspace);
+  const size_t stride = attn_align256(static_cast<size_t>(max_tiles) * 4);
+  p.tile_row0 = reinterpret_cast<int32_t*>(w), p.tile_rows = reinterpret_cast<int32_t*>(w + stride);
+  p.tile_pos = reinterpret_cast<int32_t*>(w + 2 * stride), p.tile_page = reinterpret_cast<int32_t*>(w + 3 * stride);
+  p.n_tiles = reinterpret_cast<int32_t*>(w + 4 * stride);
+}
+
+static int rpa_prefill_check(const void* q, const void* out, const void* kv_cache, const void* page_indices, int T,
+                             int H, int Hkv, int D, int page_size, int num_pages) {
+  if (!q || !out || !kv_cache || !page_indices) return fail(TJX_E_ARG, "an input or output pointer is null");
+  if (T <= 0 || H <= 0 || Hkv <= 0 || num_pages <= 0) return fail(TJX_E_ARG, "sizes must be positive");
   if (D != AT_D) return fail(TJX_E_ARG, "head dimension must be 128");
   if (page_size != AT_BKV) return fail(TJX_E_ARG, "the prefill kernel takes pages of 128 positions");
   if (H % Hkv != 0 || (H / Hkv) % 2 != 0)
     return fail(TJX_E_ARG, "the prefill kernel takes an even number of query heads per KV head (two share each K / V block)");
   if (static_cast<long long>(num_pages) * page_size >= (1ll << 31) || static_cast<long long>(T) * H >= (1ll << 31))
     return fail(TJX_E_LIMIT, "num_pages * page_size and T * H must fit in int32");
-  const size_t need = tjx_rpa_prefill_workspace_bytes(T, S);
-  if (workspace == nullptr || workspace_bytes < need)
-    return fail(TJX_E_ARG, "workspace is null or smaller than tjx_rpa_prefill_workspace_bytes");
-  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(TJX_E_ARG, "workspace must be 256-byte aligned");
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (out != q)  // rows no tile covers keep what q holds (the decode case's outputs among them)
-    TJX_CUDA(cudaMemcpyAsync(out, q, static_cast<size_t>(T) * H * AT_D * 2, cudaMemcpyDeviceToDevice, s));
-  const int max_tiles = (T + AT_BQ - 1) / AT_BQ + S;
-  uint8_t* w = static_cast<uint8_t*>(workspace);
-  const size_t stride = attn_align256(static_cast<size_t>(max_tiles) * 4);
-  AttnParams p{};
-  p.tile_row0 = reinterpret_cast<int32_t*>(w), p.tile_rows = reinterpret_cast<int32_t*>(w + stride);
-  p.tile_pos = reinterpret_cast<int32_t*>(w + 2 * stride), p.tile_page = reinterpret_cast<int32_t*>(w + 3 * stride);
-  p.n_tiles = reinterpret_cast<int32_t*>(w + 4 * stride);
-  rpa_prefill_tiles_kernel<<<1, 256, 0, s>>>(kv_lens, cu_q_lens, distribution, S, pages_per_seq, max_tiles,
-                                             const_cast<int32_t*>(p.tile_row0), const_cast<int32_t*>(p.tile_rows),
-                                             const_cast<int32_t*>(p.tile_pos), const_cast<int32_t*>(p.tile_page),
-                                             const_cast<int32_t*>(p.n_tiles));
-  TJX_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// The paged attention launch over the tiles `p` lists (at most max_tiles of them, counted in p.n_tiles on the device).
+static int rpa_prefill_launch(AttnParams& p, void* out, const void* kv_cache, const int32_t* page_indices,
+                              int n_page_indices, int T, int H, int Hkv, int num_pages, float sm_scale, int max_tiles,
+                              cudaStream_t s) {
   p.B = 1, p.H = H, p.S = 0, p.bq = p.bk = AT_BQ;
   p.page_indices = page_indices, p.Hkv = Hkv, p.group = H / Hkv, p.num_pages = num_pages;
+  p.n_page_indices = n_page_indices;
   p.scale_log2e = AT_LOG2E * sm_scale;
   p.out_tokens = static_cast<__nv_bfloat16*>(out);
   p.status = device_status_word();
@@ -842,6 +874,75 @@ extern "C" int tjx_rpa_prefill_bf16(const void* q, void* out, const void* kv_cac
   attention_kernel<false, true><<<grid, AT_THREADS, AttnSmem::TOTAL, s>>>(mq, mkv, mkv, p);
   TJX_CUDA(cudaGetLastError());
   return 0;
+}
+
+}  // namespace tjx
+
+extern "C" size_t tjx_rpa_prefill_workspace_bytes(int T, int S) {
+  if (T <= 0 || S <= 0) return 0;
+  const size_t max_tiles = static_cast<size_t>((T + tjx::AT_BQ - 1) / tjx::AT_BQ) + S;
+  return 4 * tjx::attn_align256(max_tiles * 4) + 256;
+}
+
+extern "C" int tjx_rpa_prefill_bf16(const void* q, void* out, const void* kv_cache, const int32_t* kv_lens,
+                                    const int32_t* page_indices, const int32_t* cu_q_lens,
+                                    const int32_t* distribution, int T, int S, int H, int Hkv, int D, int page_size,
+                                    int pages_per_seq, int num_pages, float sm_scale, void* workspace,
+                                    size_t workspace_bytes, tjx_stream_t stream) {
+  using namespace tjx;
+  if (int rc = check_device()) return rc;
+  if (!kv_lens || !cu_q_lens || !distribution) return fail(TJX_E_ARG, "an input or output pointer is null");
+  if (S <= 0 || pages_per_seq <= 0) return fail(TJX_E_ARG, "sizes must be positive");
+  if (int rc = rpa_prefill_check(q, out, kv_cache, page_indices, T, H, Hkv, D, page_size, num_pages)) return rc;
+  const size_t need = tjx_rpa_prefill_workspace_bytes(T, S);
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(TJX_E_ARG, "workspace is null or smaller than tjx_rpa_prefill_workspace_bytes");
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(TJX_E_ARG, "workspace must be 256-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (out != q)  // rows no tile covers keep what q holds (the decode case's outputs among them)
+    TJX_CUDA(cudaMemcpyAsync(out, q, static_cast<size_t>(T) * H * AT_D * 2, cudaMemcpyDeviceToDevice, s));
+  const int max_tiles = (T + AT_BQ - 1) / AT_BQ + S;
+  AttnParams p{};
+  rpa_tile_arrays(p, workspace, max_tiles);
+  rpa_prefill_tiles_kernel<<<1, 256, 0, s>>>(kv_lens, cu_q_lens, distribution, S, pages_per_seq, max_tiles,
+                                             const_cast<int32_t*>(p.tile_row0), const_cast<int32_t*>(p.tile_rows),
+                                             const_cast<int32_t*>(p.tile_pos), const_cast<int32_t*>(p.tile_page),
+                                             const_cast<int32_t*>(p.n_tiles));
+  TJX_CUDA(cudaGetLastError());
+  return rpa_prefill_launch(p, out, kv_cache, page_indices, S * pages_per_seq, T, H, Hkv, num_pages, sm_scale, max_tiles, s);
+}
+
+extern "C" size_t tjx_rpa_prefill_tiles_workspace_bytes(int T, int max_tiles) {
+  if (T <= 0 || max_tiles <= 0) return 0;
+  const size_t pieces = static_cast<size_t>((T + tjx::AT_BQ - 1) / tjx::AT_BQ) + max_tiles;
+  return 4 * tjx::attn_align256(pieces * 4) + 256;
+}
+
+extern "C" int tjx_rpa_prefill_tiles_bf16(const void* q, void* out, const void* kv_cache, const int32_t* page_indices,
+                                          const int32_t* tile_page, const int32_t* tile_rows, const int32_t* tile_pos,
+                                          const int32_t* n_tiles, int T, int max_tiles, int n_page_indices, int H,
+                                          int Hkv, int D, int page_size, int num_pages, float sm_scale, void* workspace,
+                                          size_t workspace_bytes, tjx_stream_t stream) {
+  using namespace tjx;
+  if (int rc = check_device()) return rc;
+  if (!tile_page || !tile_rows || !tile_pos || !n_tiles) return fail(TJX_E_ARG, "a tile table pointer is null");
+  if (max_tiles <= 0 || n_page_indices <= 0) return fail(TJX_E_ARG, "sizes must be positive");
+  if (int rc = rpa_prefill_check(q, out, kv_cache, page_indices, T, H, Hkv, D, page_size, num_pages)) return rc;
+  const size_t need = tjx_rpa_prefill_tiles_workspace_bytes(T, max_tiles);
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(TJX_E_ARG, "workspace is null or smaller than tjx_rpa_prefill_tiles_workspace_bytes");
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(TJX_E_ARG, "workspace must be 256-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (out != q) TJX_CUDA(cudaMemcpyAsync(out, q, static_cast<size_t>(T) * H * AT_D * 2, cudaMemcpyDeviceToDevice, s));
+  const int pieces = (T + AT_BQ - 1) / AT_BQ + max_tiles;
+  AttnParams p{};
+  rpa_tile_arrays(p, workspace, pieces);
+  rpa_split_tiles_kernel<<<1, 256, 0, s>>>(tile_page, tile_rows, tile_pos, n_tiles, max_tiles, pieces, T,
+                                           const_cast<int32_t*>(p.tile_row0), const_cast<int32_t*>(p.tile_rows),
+                                           const_cast<int32_t*>(p.tile_pos), const_cast<int32_t*>(p.tile_page),
+                                           const_cast<int32_t*>(p.n_tiles));
+  TJX_CUDA(cudaGetLastError());
+  return rpa_prefill_launch(p, out, kv_cache, page_indices, n_page_indices, T, H, Hkv, num_pages, sm_scale, pieces, s);
 }
 
 extern "C" int tjx_causal_attention_bf16(const void* q, const void* k, const void* v, void* out, int B, int H, int S,

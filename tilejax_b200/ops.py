@@ -559,6 +559,40 @@ def rpa_prefill(q: torch.Tensor, kv_cache: torch.Tensor, kv_lens: torch.Tensor, 
     return out
 
 
+def rpa_prefill_tiles(q: torch.Tensor, kv_cache: torch.Tensor, page_indices: torch.Tensor, tile_page: torch.Tensor,
+                      tile_rows: torch.Tensor, tile_pos: torch.Tensor, n_tiles: torch.Tensor, sm_scale: float = 1.0,
+                      out: torch.Tensor | None = None) -> torch.Tensor:
+    """The reference's `rpa_prefill` kernel (examples/ragged_paged_attention.py:204-243) on its own tile tables: tile
+    k < n_tiles[0] is the rows tile_rows[k] .. tile_rows[k + 1] - 1 of q (T, H, D), the first at cache position
+    tile_pos[k], of the sequence whose pages start at page_indices[tile_page[k]]; those rows become their causal
+    attention outputs, every other row stays. `out=q` updates in place."""
+    device = _need_cuda(q, kv_cache, page_indices, tile_page, tile_rows, tile_pos, n_tiles)
+    if kv_cache.dim() != 5 or kv_cache.shape[3] != 2 or kv_cache.dtype != torch.bfloat16 or not kv_cache.is_contiguous():
+        raise ValueError("kv_cache is a contiguous (pages, page_size, Hkv, 2, D) bfloat16 tensor")
+    num_pages, page_size, Hkv, _, D = kv_cache.shape
+    if q.dim() != 3 or q.shape[2] != D or q.dtype != torch.bfloat16:
+        raise ValueError("q is (T, H, D) bfloat16")
+    max_tiles = tile_page.numel()
+    if any(t.dtype != torch.int32 or t.dim() != 1 for t in (page_indices, tile_page, tile_rows, tile_pos, n_tiles)) \
+            or tile_pos.numel() != max_tiles or tile_rows.numel() != max_tiles + 1 or n_tiles.numel() < 1:
+        raise ValueError("tile_page and tile_pos are int32 (tiles,), tile_rows int32 (tiles + 1,), n_tiles int32 (1,)")
+    T, H, _ = q.shape
+    if out is None:
+        out = torch.empty_like(q)
+    elif out.shape != q.shape or out.dtype != q.dtype or not out.is_contiguous() or out.device != q.device:
+        raise ValueError("out must look like q")
+    with torch.cuda.device(device):
+        need = int(library().tjx_rpa_prefill_tiles_workspace_bytes(T, max_tiles))
+        ws = torch.empty(need + 256, dtype=torch.uint8, device=device)
+        ws_ptr = (ws.data_ptr() + 255) & ~255
+        check(library().tjx_rpa_prefill_tiles_bf16(_ptr(q), _ptr(out), _ptr(kv_cache), _ptr(page_indices), _ptr(tile_page),
+                                                   _ptr(tile_rows), _ptr(tile_pos), _ptr(n_tiles), T, max_tiles,
+                                                   page_indices.numel(), H, Hkv, D, page_size, num_pages, float(sm_scale),
+                                                   ctypes.c_void_p(ws_ptr), need, _stream()))
+        ws.record_stream(torch.cuda.current_stream(device))
+    return out
+
+
 def ragged_paged_attention(q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, kv_cache: torch.Tensor,
                            kv_lens: torch.Tensor, page_indices: torch.Tensor, cu_q_lens: torch.Tensor,
                            distribution: torch.Tensor, sm_scale: float = 1.0) -> tuple[torch.Tensor, torch.Tensor]:
