@@ -800,7 +800,7 @@ __global__ void __launch_bounds__(256)
       if (out >= max_tiles) break;
       tile_row0[out] = first_row + b * AT_BQ;
       tile_rows[out] = min(AT_BQ, rows - b * AT_BQ);
-      tile_pos[out] = in_pos[k] + b * AT_BQ;
+      tile_pos[out] = max(in_pos[k], 0) + b * AT_BQ;  // (a position before the cache's start is not one)
       tile_page[out] = in_page[k];
     }
     __syncthreads();
