@@ -664,7 +664,7 @@ def _recognise_rpa_prefill(nest, fn, ns, specs, outputs, parallel, reductions) -
                                  "dtype, page_indices, tile tables (tile_rows one longer) and n_tiles (1,), int32")
     T, H, D = q.shape
     num_pages, page, Hkv = cache.shape[0], cache.shape[1], cache.shape[2]
-    max_pages = -(-page_indices.shape[0] // 1)  # a tile walks at most every listed page
+    max_pages = page_indices.shape[0]  # a tile walks at most every listed page
     sch = _schedule.runtime_schedule([Range(parallel[0].var, 0, tiles, 1)], [Range(reductions[0].var, 0, max_pages, 1)])
     params = dict(rpa_prefill=True, T=T, H=H, Hkv=Hkv, D=D, page=page, num_pages=num_pages, max_tiles=tiles,
                   sm_scale=_closed_scale(nest, fn), schedule=sch)
