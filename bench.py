@@ -744,8 +744,9 @@ def main() -> None:
 
     def e2e_step():
         # Host shard and weights in, host result out: copies, GEMMs and copies back pipelined on three streams. With
-        # several GPUs every rank computes the whole (replicated) result and hands the host its own rows of it.
-        op.from_host(x_host, y_host, out_host, copy_back="own" if own_rows_only else "all")
+        # several GPUs every rank computes the whole (replicated) result and hands the host its own rows of it, and
+        # reads its 1 / N of the replicated y from the host (the ranks all-gather the parts over NVLink).
+        op.from_host(x_host, y_host, out_host, copy_back="own" if own_rows_only else "all", w_replicated=world > 1)
         torch.cuda.current_stream().wait_event(op.host_done)
 
     for _ in range(2):
@@ -788,11 +789,12 @@ def main() -> None:
         "parity": parity,
         "clocks": clocks,
         "e2e": {"value": world * flops_per_gpu / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": x_host.numel() * 2 + y_host.numel() * 2,
+                "h2d_bytes_per_step": x_host.numel() * 2 + y_host.numel() * 2 // world,
                 "d2h_bytes_per_step": (m if own_rows_only else M_TOTAL) * N_DIM * 2,
                 "bytes_are": "per rank",
                 "api": "tilejax_b200.collective.AllGatherMatmul.from_host with pinned host x, y and out"
-                       + ("; each rank returns its own rows of the replicated result" if own_rows_only else "")},
+                       + ("; each rank reads 1 / N of the replicated y from its host (all-gathered over NVLink) and returns "
+                          "its own rows of the replicated result" if own_rows_only else "")},
         # Kernels of this library launched inside the timed region of `value`: GEMM launches per step x steps.
         "gpu_launches": args.steps * (1 if world == 1 or op.transport == "fused" else len(op.groups)),
         "roofline": tensor_roofline(

@@ -50,6 +50,12 @@ for transport in ("fused", "peer", "nccl"):
         op.from_host(x_host, w_host, out_host, chunks=4)
         op.host_done.synchronize()
         assert torch.equal(out_host, want.cpu()), (transport, "from_host", call)
+    # The same with w read a part per rank and all-gathered over NVLink (w is the same on every rank here), own rows back.
+    out_host.fill_(float("nan"))
+    op.from_host(x_host, w_host, out_host, chunks=4, copy_back="own", w_replicated=True)
+    op.host_done.synchronize()
+    assert torch.equal(out_host[rank * m : (rank + 1) * m], want[rank * m : (rank + 1) * m].cpu()), (transport, "shared w")
+    assert torch.equal(op.out, want), (transport, "shared w, device result")
 dist.barrier()
 dist.destroy_process_group()
 sys.stdout.write("rank %d ok\\n" % rank)

@@ -172,6 +172,7 @@ class AllGatherMatmul:
         else:
             self.exchange = ShardExchange(m, K, torch.bfloat16, device, group)
         self.ranks, self.me = self.exchange.ranks, self.exchange.me
+        self.group = group
         self.m, self.K, self.N = m, K, N
         self.tm, self.tn, self.tk = min(tm, m), min(tn, N), min(tk, K)
         if m % self.tm:
@@ -303,7 +304,7 @@ class AllGatherMatmul:
                 after_group(self.groups[n + 1])
 
     def from_host(self, x_host: torch.Tensor, w_host: torch.Tensor, out_host: torch.Tensor, chunks: int = 8,
-                  copy_back: str = "all") -> None:
+                  copy_back: str = "all", w_replicated: bool = False) -> None:
         """The same product for operands in pinned host memory, result into pinned host memory: the host-to-device
         copies, the GEMMs and the device-to-host copies run as a pipeline on three streams, so a step costs about
         its slower copy direction instead of the sum of both copies and the compute. w goes first (every tile needs
@@ -311,7 +312,10 @@ class AllGatherMatmul:
         the result copied back while the next piece is still arriving; the other ranks' shards follow as in
         `__call__`. With `copy_back="own"` only this rank's m rows of the result are copied to `out_host` (where w is
         the same on every rank the result is too, and the ranks together hand the host every row once); the whole
-        result stays in `self.out`. Enqueues only: `out_host` is complete once `host_done` has been synchronised."""
+        result stays in `self.out`. With `w_replicated=True` the caller states that w_host holds the same values on
+        every rank (as `all_gather_matmul`'s replicated w does): each rank then reads only its 1 / ranks of w's rows from
+        its host and the ranks all-gather the parts over NVLink, instead of every rank pulling all of w over PCIe.
+        Enqueues only: `out_host` is complete once `host_done` has been synchronised."""
         if copy_back not in ("all", "own"):
             raise ValueError("copy_back is 'all' or 'own'")
         ops = self._ops
@@ -354,7 +358,13 @@ class AllGatherMatmul:
         if peer_memory:
             h2d.wait_event(self.barrier_done)  # peers finished reading this half of the send buffer two calls ago
         with torch.cuda.stream(h2d):
-            w_dev.copy_(w_host, non_blocking=True)
+            if w_replicated and self.ranks > 1 and self.K % self.ranks == 0:
+                part = self.K // self.ranks
+                mine = w_dev[self.me * part : (self.me + 1) * part]
+                mine.copy_(w_host[self.me * part : (self.me + 1) * part], non_blocking=True)
+                dist.all_gather_into_tensor(w_dev, mine, group=self.group)  # in place: each part lands where it belongs
+            else:
+                w_dev.copy_(w_host, non_blocking=True)
             self._w_ready.record(h2d)
         compute.wait_event(self._w_ready)
         try:
