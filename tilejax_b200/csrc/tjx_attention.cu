@@ -71,6 +71,7 @@ struct AttnParams {
   int n_page_indices;            // entries of page_indices
   float scale_log2e;             // log2(e) times the softmax scale (the queries do not arrive pre-scaled)
   __nv_bfloat16* out_tokens;     // (T, H, D): row (token, head)
+  int chain;                     // CHAIN_RELEASES: the kernel launched behind this one may be scheduled early
 };
 
 constexpr int AT_MAX_TILES = 1024;  // user query tiles per (b, h) whose last key block is cached in shared memory
@@ -214,6 +215,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = __shfl_sync(0xFFFFFFFFu, *tmem_holder, 0);
+  if (p.chain & CHAIN_RELEASES) chain_release();
 
   // What every role derives for a unit, identically.
   struct Unit {
@@ -691,6 +693,7 @@ int attention_launch(const void* q, const void* k, const void* v, void* out, flo
   if (pattern_tiles > AT_MAX_TILES) return fail(TJX_E_LIMIT, "more than 1024 query tiles per (batch, head)");
   p.status = device_status_word();
   if (p.status == nullptr) return fail(TJX_E_CUDA, "could not locate the device status word");
+  p.chain = launch_chain();
 
   const uint64_t dims[2] = {static_cast<uint64_t>(D), static_cast<uint64_t>(B) * H * S};
   const uint64_t strides[1] = {static_cast<uint64_t>(D) * 2};

@@ -39,6 +39,7 @@ __global__ void __launch_bounds__(ROWS_WARPS * 32)
                         __nv_bfloat16* __restrict__ n, int M, int D, float eps) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * ROWS_WARPS + warp;
+  chain_wait();  // launched behind the attention kernel, whose rows it reads
   if (row >= M) return;
   const float4* src = reinterpret_cast<const float4*>(a + static_cast<size_t>(row) * D);
   float sum = 0.f;
@@ -57,6 +58,7 @@ __global__ void __launch_bounds__(ROWS_WARPS * 32)
     dst[u] = make_uint2(pack_bf16(x.x * scale * bf16_lo(gv.x), x.y * scale * bf16_hi(gv.x)),
                         pack_bf16(x.z * scale * bf16_lo(gv.y), x.w * scale * bf16_hi(gv.y)));
   }
+  chain_release();  // (a CTA that has written its rows: the matmul behind is scheduled when every CTA is here or gone)
 }
 
 static size_t block_align256(size_t n) { return (n + 255) & ~static_cast<size_t>(255); }
@@ -97,16 +99,37 @@ int tjx_attention_block_bf16(const void* q, const void* k, const void* v, const 
   __nv_bfloat16* normed = reinterpret_cast<__nv_bfloat16*>(ws + block_align256(static_cast<size_t>(M) * D * 4));
   __nv_bfloat16* hidden = reinterpret_cast<__nv_bfloat16*>(ws + block_align256(static_cast<size_t>(M) * D * 4) +
                                                            block_align256(static_cast<size_t>(M) * D * 2));
-  if (int rc = attention_launch(q, k, v, nullptr, a, B, H, S, Dh, block_q, block_kv, step_tile, step_code, pattern_steps,
-                                pattern_tiles, stream))
-    return rc;
-  rmsnorm_rows_kernel<<<(M + ROWS_WARPS - 1) / ROWS_WARPS, ROWS_WARPS * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-      a, static_cast<const __nv_bfloat16*>(gamma), normed, M, D, eps);
-  TJX_CUDA(cudaGetLastError());
+  // The four launches are chained: each may be scheduled while the one in front of it still runs, sets itself up
+  // (barriers, tensor memory, descriptors) beside that kernel's tail and waits for its results on the device.
+  struct Chain {
+    explicit Chain(int how) { launch_chain() = how; }
+    ~Chain() { launch_chain() = 0; }
+  };
+  {
+    Chain chain(CHAIN_RELEASES);
+    if (int rc = attention_launch(q, k, v, nullptr, a, B, H, S, Dh, block_q, block_kv, step_tile, step_code,
+                                  pattern_steps, pattern_tiles, stream))
+      return rc;
+  }
+  {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((M + ROWS_WARPS - 1) / ROWS_WARPS), cfg.blockDim = dim3(ROWS_WARPS * 32);
+    cfg.dynamicSmemBytes = 0, cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr, cfg.numAttrs = 1;
+    TJX_CUDA(cudaLaunchKernelEx(&cfg, rmsnorm_rows_kernel, static_cast<const float*>(a),
+                                static_cast<const __nv_bfloat16*>(gamma), normed, M, D, eps));
+  }
   const int tm = tile_edge(M);
-  if (int rc = gemm_launch(normed, w_up, hidden, M, F, D, 0, tm, tile_edge(F), 512, 0, 0, 0, nullptr, nullptr, 0, nullptr,
-                           nullptr, 0, nullptr, 1, stream))
-    return rc;
+  {
+    Chain chain(CHAIN_WAITS | CHAIN_RELEASES);
+    if (int rc = gemm_launch(normed, w_up, hidden, M, F, D, 0, tm, tile_edge(F), 512, 0, 0, 0, nullptr, nullptr, 0,
+                             nullptr, nullptr, 0, nullptr, 1, stream))
+      return rc;
+  }
+  Chain chain(CHAIN_WAITS);
   return gemm_launch(hidden, w_down, out, M, D, F, 0, tm, tile_edge(D), 512, 0, 0, 0, nullptr, nullptr, 0, nullptr, nullptr,
                      0, nullptr, 0, stream);
 }

@@ -47,6 +47,7 @@ struct GemmParams {
   const int32_t* fill_j;
   int causal, out_f32, b_kmajor;
   int tail_split;        // the pair kernel may halve the pieces of a short last round (see its header)
+  int chain;             // CHAIN_WAITS / CHAIN_RELEASES: how the pair kernel's launch is chained on the stream
   int num_kb;
   void* out;
   int* status;
@@ -608,6 +609,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? GATHER_THRE
   cluster_sync_all();  // the peer's barriers are initialised before anything of ours can reach them
   tc_fence_after_sync();
   const uint32_t tmem_base = __shfl_sync(0xFFFFFFFFu, *tmem_holder, 0);
+  // A chained launch: everything above ran beside the tail of the kernel in front; its results are needed from here.
+  if (p.chain & CHAIN_WAITS) chain_wait();
+  if (p.chain & CHAIN_RELEASES) chain_release();
   // This pair's walk: its list of computing items, or items pair, pair + pairs, ... of every kind; `rounds` whole
   // rounds and a last one of `tail` pieces, halved when that keeps twice as many pairs busy.
   const bool listed = __shfl_sync(0xFFFFFFFFu, list_meta[0], 0) != 0;
@@ -855,6 +859,17 @@ static int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const 
     TJX_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
     configured[dev & 63] = true;
   }
+  if (p.chain & CHAIN_WAITS) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid), cfg.blockDim = dim3(GATHER ? GATHER_THREADS : GEMM_THREADS);
+    cfg.dynamicSmemBytes = L::TOTAL, cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr, cfg.numAttrs = 1;
+    TJX_CUDA(cudaLaunchKernelEx(&cfg, kernel, ma, mb, mc, ma_own, p));
+    return 0;
+  }
   kernel<<<grid, GATHER ? GATHER_THREADS : GEMM_THREADS, L::TOTAL, stream>>>(ma, mb, mc, ma_own, p);
   TJX_CUDA(cudaGetLastError());
   return 0;
@@ -928,6 +943,7 @@ int gemm_launch(const void* x, const void* y, void* out, int M, int N, int K, in
   p.tile_i = tile_i, p.tile_j = tile_j, p.fill_i = fill_i, p.fill_j = fill_j;
   p.causal = causal ? 1 : 0, p.out_f32 = out_f32 ? 1 : 0, p.b_kmajor = y_transposed ? 1 : 0;
   p.tail_split = y_transposed ? 0 : TJX_GEMM_TAIL_SPLIT;  // (x @ y.T stages y through a box of fixed height)
+  p.chain = launch_chain();  // (only the pair kernel looks at it: an ordinary launch is always right)
   p.num_kb = (K + BK - 1) / BK;
   p.out = out;
   p.row_scale = row_scale;

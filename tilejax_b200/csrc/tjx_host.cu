@@ -60,6 +60,11 @@ int check_device() {
   return 0;
 }
 
+int& launch_chain() {
+  static thread_local int chain = 0;
+  return chain;
+}
+
 int sm_count() {
   int dev;
   if (current_device(&dev)) return 0;

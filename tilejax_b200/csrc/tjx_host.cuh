@@ -26,6 +26,14 @@ int cuda_fail(cudaError_t e, const char* what);
 int check_device();
 int sm_count();
 
+// How the calling thread's next launches are chained to their neighbours on the stream (programmatic dependent
+// launch): CHAIN_WAITS = launched so that it may start before the kernel in front of it has finished, and waits for
+// that kernel's results itself (griddepcontrol.wait) before it reads or writes anything; CHAIN_RELEASES = lets the
+// kernel behind it be scheduled as soon as its own CTAs have started. 0 = an ordinary launch. Set by an entry point
+// that issues several dependent kernels (the attention block), around each of them.
+enum : int { CHAIN_WAITS = 1, CHAIN_RELEASES = 2 };
+int& launch_chain();
+
 // Per-device status word the kernels write error codes to: a fixed device variable inside the library (no
 // allocation); the address is looked up once per device.
 int* device_status_word();

@@ -199,6 +199,14 @@ __device__ __forceinline__ void tma_store_wait_all() {
   asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 
+// ---------------------------------------------------------------------------------------------- launch chains
+
+// Programmatic dependent launch: wait until the kernels this one was chained behind have completed and their
+// writes are visible (nothing happens in a kernel launched the ordinary way); let the kernel chained behind this
+// one be scheduled.
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------------------------------------- TMEM
 
 // Allocate `cols` (power of two, 32..512) TMEM columns; the base address lands in shared memory at `dst`.
