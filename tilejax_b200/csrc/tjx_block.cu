@@ -101,12 +101,8 @@ int tjx_attention_block_bf16(const void* q, const void* k, const void* v, const 
                                                            block_align256(static_cast<size_t>(M) * D * 2));
   // The four launches are chained: each may be scheduled while the one in front of it still runs, sets itself up
   // (barriers, tensor memory, descriptors) beside that kernel's tail and waits for its results on the device.
-  struct Chain {
-    explicit Chain(int how) { launch_chain() = how; }
-    ~Chain() { launch_chain() = 0; }
-  };
   {
-    Chain chain(CHAIN_RELEASES);
+    LaunchChain chain(CHAIN_RELEASES);
     if (int rc = attention_launch(q, k, v, nullptr, a, B, H, S, Dh, block_q, block_kv, step_tile, step_code,
                                   pattern_steps, pattern_tiles, stream))
       return rc;
@@ -124,12 +120,12 @@ int tjx_attention_block_bf16(const void* q, const void* k, const void* v, const 
   }
   const int tm = tile_edge(M);
   {
-    Chain chain(CHAIN_WAITS | CHAIN_RELEASES);
+    LaunchChain chain(CHAIN_WAITS | CHAIN_RELEASES);
     if (int rc = gemm_launch(normed, w_up, hidden, M, F, D, 0, tm, tile_edge(F), 512, 0, 0, 0, nullptr, nullptr, 0,
                              nullptr, nullptr, 0, nullptr, 1, stream))
       return rc;
   }
-  Chain chain(CHAIN_WAITS);
+  LaunchChain chain(CHAIN_WAITS);
   return gemm_launch(hidden, w_down, out, M, D, F, 0, tm, tile_edge(D), 512, 0, 0, 0, nullptr, nullptr, 0, nullptr, nullptr,
                      0, nullptr, 0, stream);
 }

@@ -33,6 +33,13 @@ int sm_count();
 // that issues several dependent kernels (the attention block), around each of them.
 enum : int { CHAIN_WAITS = 1, CHAIN_RELEASES = 2 };
 int& launch_chain();
+// Sets the calling thread's chain for the launches made while it lives.
+struct LaunchChain {
+  explicit LaunchChain(int how) { launch_chain() = how; }
+  ~LaunchChain() { launch_chain() = 0; }
+  LaunchChain(const LaunchChain&) = delete;
+  LaunchChain& operator=(const LaunchChain&) = delete;
+};
 
 // Per-device status word the kernels write error codes to: a fixed device variable inside the library (no
 // allocation); the address is looked up once per device.

@@ -52,6 +52,8 @@ __global__ void __launch_bounds__(RMS_WARPS * 32)
 #pragma unroll
   for (int d = 16; d >= 1; d >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, d);
   if (lane == 0) scale[row] = rsqrtf(sum / static_cast<float>(D) + eps);
+  chain_release();  // the matmul chained behind may be scheduled once every CTA is here (or gone): it sets itself up
+                    // beside this kernel's tail and waits for the rows on the device
 }
 
 static size_t rms_align256(size_t n) { return (n + 255) & ~static_cast<size_t>(255); }
@@ -86,6 +88,7 @@ int tjx_rmsnorm_gemm_bf16(const void* x, const void* gamma, const void* w, void*
   rmsnorm_prepare_kernel<<<grid, RMS_WARPS * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(gamma), xg, scale, M, D, eps);
   TJX_CUDA(cudaGetLastError());
+  LaunchChain chain(CHAIN_WAITS);
   return gemm_launch(xg, w, out, M, N, D, 0, tm, tn, tk, 0, out_f32, 0, nullptr, nullptr, 0, nullptr, nullptr, 0, scale, 0,
                      stream);
 }
