@@ -633,6 +633,61 @@ def check_parity(op, x, y, world: int, rank: int, device) -> dict:
             "device_status": int(flags[2].item()), "ranks_checked": world, "ok": ok}
 
 
+PEER_COPY_GBS = 770.0  # measured peer copy bandwidth per direction per GPU on this pool's NVLink 5 / NVSwitch
+
+
+def reference_layout(world: int, rank: int, device, x, y, m: int, steps: int, warmup: int, pk: dict, barrier) -> dict:
+    """The collective matmul as the reference's own example shards it (examples/collective_matmul.py:64, in_specs
+    P("x", None) and P(None, "x")): w split by columns, so a rank computes all_gather(x) @ its N / G columns, 2 * G *
+    m * K * n flops (benchmarks/collective_matmul.py:44) — 1 / G of the headline's — behind the same gathered bytes.
+    With eight ranks the gather no longer hides: the bound is the slower of the tensor pipe and NVLink. Both
+    transports are timed: the one-launch kernel, whose copier warps pull at about 400 GB/s, and the copy-engine one
+    ("peer": a GEMM launch per group of shards behind copies on a second stream)."""
+    import torch
+    import torch.distributed as dist
+
+    from tilejax_b200.collective import AllGatherMatmul
+
+    n = N_DIM // world
+    w = y[:, rank * n : (rank + 1) * n].contiguous()
+    flops = 2.0 * M_TOTAL * K_DIM * n
+    gathered = (world - 1) * m * K_DIM * 2
+    tensor_ms = flops / (pk["bf16_tflops"] * 1e9)
+    link_ms = gathered / (PEER_COPY_GBS * 1e6)
+    by_transport, parity_ok = {}, True
+    for transport in ("fused", "peer"):
+        op = AllGatherMatmul(m, K_DIM, n, *TILES, transport=transport)
+        for _ in range(warmup):
+            op(x, w)
+        barrier()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            op(x, w)
+        end.record()
+        barrier()
+        elapsed = torch.tensor([start.elapsed_time(end)], device=device)
+        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+        ms = elapsed.item() / steps
+        parity = check_parity(op, x, w, world, rank, device)
+        barrier()
+        parity_ok = parity_ok and parity["ok"]
+        by_transport[op.transport] = {"ms_per_step": ms, "gather_gbs_per_gpu": gathered / ms / 1e6,
+                                      "frac": max(tensor_ms, link_ms) / ms, "parity": parity}
+        del op
+    best = min(by_transport, key=lambda t: by_transport[t]["ms_per_step"])
+    ms = by_transport[best]["ms_per_step"]
+    return {"ms_per_step": ms, "steps": steps, "value": world * flops / ms / 1e9, "unit": "TFLOP/s",
+            "per_gpu_tflops": flops / ms / 1e9, "columns_per_gpu": n, "transport": best,
+            "gathered_bytes_per_gpu": gathered, "by_transport": by_transport,
+            "roofline": {"bound": "tensor" if tensor_ms >= link_ms else "nvlink", "tensor_ms": tensor_ms,
+                         "nvlink_ms": link_ms, "target_ms": max(tensor_ms, link_ms),
+                         "frac": max(tensor_ms, link_ms) / ms,
+                         "peaks": f"measured cuBLAS bf16 burst {pk['bf16_tflops']} TFLOP/s; measured peer copy "
+                                  f"{PEER_COPY_GBS} GB/s per direction"},
+            "parity": {"ok": parity_ok}}
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -775,6 +830,9 @@ def main() -> None:
     gemm_sustained_ms = time_sustained(alone, 1.2, gemm_ms)
     ops.device_status()
     barrier()
+    column_sharded = None
+    if world > 1 and not args.no_extras:
+        column_sharded = reference_layout(world, rank, device, x, y, m, min(args.steps, 20), args.warmup, pk, barrier)
     clocks = sampler.stop() if sampler else None  # sampled over every timed region of this run
 
     value = world * flops_per_gpu / ms_per_step / 1e9
@@ -806,6 +864,9 @@ def main() -> None:
             NCU_TRAFFIC_BYTES["gemm_16384x8192x8192"], kernel="gemm_pair_kernel<256,3,2>", ms_per_launch=gemm_ms,
             ms_per_launch_sustained=gemm_sustained_ms, flops_per_launch=flops_per_gpu),
     }
+    if column_sharded is not None:
+        line["workloads"] = {f"collective_matmul_w_column_sharded_{world}gpus": column_sharded}
+        parity = {**parity, "ok": parity["ok"] and column_sharded["parity"]["ok"]}
     if workloads is not None:
         line["workloads"] = workloads
         tflops, sec, threads, sample = cpu_port_tflops(CPU_SAMPLE_ROWS, 3, 1)
