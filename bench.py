@@ -832,7 +832,10 @@ def main() -> None:
     barrier()
     column_sharded = None
     if world > 1 and not args.no_extras:
-        column_sharded = reference_layout(world, rank, device, x, y, m, min(args.steps, 20), args.warmup, pk, barrier)
+        try:
+            column_sharded = reference_layout(world, rank, device, x, y, m, min(args.steps, 20), args.warmup, pk, barrier)
+        except Exception as exc:  # the headline line is still printed; the failure is in it
+            column_sharded = {"error": f"{type(exc).__name__}: {exc}", "parity": {"ok": False}}
     clocks = sampler.stop() if sampler else None  # sampled over every timed region of this run
 
     value = world * flops_per_gpu / ms_per_step / 1e9
