@@ -520,7 +520,7 @@ def extra_workloads(device, pk: dict, pk_kind: str, only: str | None = None, ite
             tensor_entry(name, ms, 4.0 * H * D * seen, extra={
                 "algorithmic_flops": "the prefill tokens' 4*H*D*(positions seen); the decode part reads "
                                      f"{sum(kv_lens[:32]) * Hkv * 2 * D * 2 / 1e6:.0f} MB of cache",
-                "launches": "rpa_write, decode lengths + step tables + decode + scatter, prefill tiles + attention (paged)",
+                "launches": "one call (tjx_ragged_paged_attention_bf16): rpa_write with decode lengths and prefill tiles beside it, step tables + decode, decode rows, attention (paged)",
                 "new_tokens": T})
         except Exception as e:
             out[name] = {"error": str(e)[:200]}

@@ -263,6 +263,24 @@ int tjx_rpa_prefill_tiles_bf16(const void* q, void* out, const void* kv_cache, c
                                int page_size, int num_pages, float sm_scale, void* workspace, size_t workspace_bytes,
                                tjx_stream_t stream);
 
+/* Bytes of scratch tjx_ragged_paged_attention_bf16 needs for these sizes. */
+size_t tjx_ragged_paged_attention_workspace_bytes(int T, int S, int H, int D, int page_size, int pages_per_seq);
+
+/* One whole ragged paged attention step, the reference's `autokernel_rpa` (examples/ragged_paged_attention.py:279-290:
+ * rpa_write, then rpa_decode, then rpa_prefill on its result) in one call: the new keys and values written into
+ * kv_cache in place, then out [T, H, D] = the decode sequences' outputs in their rows, the prefill and mixed sequences'
+ * outputs in theirs, and q's rows everywhere else (out may be q). Same results as tjx_rpa_write_bf16,
+ * tjx_rpa_decode_bf16 and tjx_rpa_prefill_bf16 called in that order, for inputs whose decode tokens and prefill tokens
+ * are different rows; it spares their copy of q into out (the prefill queries are read from q itself), and its small
+ * kernels are chained to run beside their neighbours on the stream.
+ *   workspace: at least tjx_ragged_paged_attention_workspace_bytes(...) bytes, 256-byte aligned
+ * Constraints: those of the three entry points together (D == 128; page_size == 128; H / Hkv in {2, 4, 8}). */
+int tjx_ragged_paged_attention_bf16(const void* q, const void* keys, const void* values, void* kv_cache,
+                                    const int32_t* kv_lens, const int32_t* page_indices, const int32_t* cu_q_lens,
+                                    const int32_t* distribution, void* out, int T, int S, int H, int Hkv, int D,
+                                    int page_size, int pages_per_seq, int num_pages, float sm_scale, void* workspace,
+                                    size_t workspace_bytes, tjx_stream_t stream);
+
 /* Which kernel tjx_mla_decode_bf16 launches from now on: 1 (the default) the tcgen05 kernel, 64 rows per CTA with
  * scores and output in TMEM; 0 the warp-level MMA kernel, 16 rows per CTA. An A/B switch for measurements: the two
  * agree to rounding. No counterpart in the reference. */

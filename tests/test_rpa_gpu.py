@@ -119,6 +119,35 @@ def test_the_whole_step_is_write_then_decode_then_prefill():
     np.testing.assert_array_equal(to_host(dev["q"]).view(np.uint16), inp["q"].view(np.uint16))  # q itself is left alone
 
 
+@pytest.mark.parametrize(("q_lens", "kv_lens", "sizes"), [
+    ([1, 1, 1, 200, 64], [900, 1, 257, 200, 700], dict(max_len=1024, max_tokens=320, max_seqs=8, seed=9)),  # padding rows
+    ([1] * 8 + [256, 130], [40 * i + 1 for i in range(8)] + [512, 130], dict(max_len=1024, seed=3)),        # every row used
+    ([1] * 16, list(range(1, 1025, 64)), dict(max_len=1024, max_tokens=64)),                                # decode only
+    ([129, 5], [1000, 5], dict(max_len=1024, max_tokens=256, seed=4)),                                      # no decode sequence
+])
+def test_the_one_call_step_equals_the_three_calls_bit_for_bit(q_lens, kv_lens, sizes):
+    # tjx_ragged_paged_attention_bf16 against tjx_rpa_write_bf16, tjx_rpa_decode_bf16 and tjx_rpa_prefill_bf16 in that
+    # order: the same cache and the same out, rows that no case writes (padding tokens) holding the query; q itself
+    # untouched; three calls on one workspace.
+    inp, dev = step(q_lens, kv_lens, **sizes)
+    inp["q"][int(sum(q_lens)):] = 3.0  # the padding rows: something a fresh buffer does not hold by chance
+    dev["q"] = to_device(inp["q"])
+    scale = 128**-0.5
+    index = [dev[n] for n in ("kv_lens", "page_indices")]
+    cache3 = ops.rpa_write(dev["kv_cache"].clone(), dev["keys"], dev["values"], *index, dev["cu_q_lens"], dev["distribution"])
+    out3 = ops.rpa_decode(dev["q"], cache3, *index, dev["distribution"], scale)
+    out3 = ops.rpa_prefill(out3, cache3, *index, dev["cu_q_lens"], dev["distribution"], scale, out=out3)
+    for _ in range(3):
+        cache1 = dev["kv_cache"].clone()
+        out1, same_cache = ops.ragged_paged_attention(dev["q"], dev["keys"], dev["values"], cache1, *index,
+                                                      dev["cu_q_lens"], dev["distribution"], scale)
+        assert ops.device_status() == 0
+        assert same_cache is cache1
+        assert torch.equal(cache1.view(torch.int16), cache3.view(torch.int16))
+        assert torch.equal(out1.view(torch.int16), out3.view(torch.int16))
+    np.testing.assert_array_equal(to_host(dev["q"]).view(np.uint16), inp["q"].view(np.uint16))
+
+
 def test_prefill_limits_are_errors():
     inp, dev = step([4], [4], heads=4, kv_heads=4, max_len=256)  # one query head per KV head
     with pytest.raises(NativeError, match="even number of query heads per KV head"):

@@ -46,6 +46,8 @@ SYMBOLS: dict[str, tuple] = {
     "tjx_rpa_prefill_bf16": (c_int, [_P] * 7 + [c_int] * 8 + [ctypes.c_float, _P, c_size_t, _P]),
     "tjx_rpa_prefill_tiles_workspace_bytes": (c_size_t, [c_int, c_int]),
     "tjx_rpa_prefill_tiles_bf16": (c_int, [_P] * 8 + [c_int] * 8 + [ctypes.c_float, _P, c_size_t, _P]),
+    "tjx_ragged_paged_attention_workspace_bytes": (c_size_t, [c_int] * 6),
+    "tjx_ragged_paged_attention_bf16": (c_int, [_P] * 9 + [c_int] * 8 + [ctypes.c_float, _P, c_size_t, _P]),
     "tjx_mla_set_mode": (c_int, [c_int]),
     "tjx_mla_decode_workspace_bytes": (c_size_t, [c_int] * 5),
     "tjx_mla_decode_bf16": (c_int, [_P] * 6 + [c_int] * 7 + [_P] * 5 + [c_size_t, _P]),

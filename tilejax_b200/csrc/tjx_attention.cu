@@ -71,7 +71,8 @@ struct AttnParams {
   int n_page_indices;            // entries of page_indices
   float scale_log2e;             // log2(e) times the softmax scale (the queries do not arrive pre-scaled)
   __nv_bfloat16* out_tokens;     // (T, H, D): row (token, head)
-  int chain;                     // CHAIN_RELEASES: the kernel launched behind this one may be scheduled early
+  int chain;                     // CHAIN_RELEASES: the kernel launched behind this one may be scheduled early;
+                                 // CHAIN_WAITS: launched early itself, orders itself behind the kernel in front
 };
 
 constexpr int AT_MAX_TILES = 1024;  // user query tiles per (b, h) whose last key block is cached in shared memory
@@ -215,6 +216,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = __shfl_sync(0xFFFFFFFFu, *tmem_holder, 0);
+  if (p.chain & CHAIN_WAITS) chain_wait();
   if (p.chain & CHAIN_RELEASES) chain_release();
 
   // What every role derives for a unit, identically.
@@ -735,6 +737,7 @@ __global__ void __launch_bounds__(256)
                              int32_t* __restrict__ tile_pos, int32_t* __restrict__ tile_page,
                              int32_t* __restrict__ n_tiles) {
   __shared__ int carry_sh, scan_sh[256];
+  chain_release();  // (reads only the call's inputs: when chained it runs beside the kernel in front of it)
   if (threadIdx.x == 0) carry_sh = 0;
   __syncthreads();
   const int d0 = distribution[0], d2 = min(distribution[2], S);
@@ -764,6 +767,7 @@ __global__ void __launch_bounds__(256)
     __syncthreads();
   }
   if (threadIdx.x == 0) n_tiles[0] = min(carry_sh, max_tiles);
+  chain_wait();  // ends after the kernel it was chained behind: what follows this one follows that one too
 }
 
 // The tiles of the reference's `rpa_prefill` kernel (examples/ragged_paged_attention.py:204-243: tile k is the query
@@ -840,7 +844,8 @@ static int rpa_prefill_check(const void* q, const void* out, const void* kv_cach
 // The paged attention launch over the tiles `p` lists (at most max_tiles of them, counted in p.n_tiles on the device).
 static int rpa_prefill_launch(AttnParams& p, void* out, const void* kv_cache, const int32_t* page_indices,
                               int n_page_indices, int T, int H, int Hkv, int num_pages, float sm_scale, int max_tiles,
-                              cudaStream_t s) {
+                              cudaStream_t s, const void* queries = nullptr) {
+  if (queries == nullptr) queries = out;
   p.B = 1, p.H = H, p.S = 0, p.bq = p.bk = AT_BQ;
   p.page_indices = page_indices, p.Hkv = Hkv, p.group = H / Hkv, p.num_pages = num_pages;
   p.n_page_indices = n_page_indices;
@@ -848,14 +853,15 @@ static int rpa_prefill_launch(AttnParams& p, void* out, const void* kv_cache, co
   p.out_tokens = static_cast<__nv_bfloat16*>(out);
   p.status = device_status_word();
   if (p.status == nullptr) return fail(TJX_E_CUDA, "could not locate the device status word");
-  // q (T, H, D) as (D, H, T); the cache (pages, 128, Hkv, 2, D) as (D, Hkv * 2, pages * 128). The queries are read from
-  // `out`: the rows the decode case has already replaced are not query tiles of this case.
+  // q (T, H, D) as (D, H, T); the cache (pages, 128, Hkv, 2, D) as (D, Hkv * 2, pages * 128). Unless the caller names
+  // another buffer the queries are read from `out`: the rows the decode case has already replaced are not query
+  // tiles of this case.
   CUtensorMap mq, mkv;
   {
     const uint64_t dims[3] = {AT_D, static_cast<uint64_t>(H), static_cast<uint64_t>(T)};
     const uint64_t strides[2] = {AT_D * 2, static_cast<uint64_t>(H) * AT_D * 2};
     const uint32_t box[3] = {64, 1, AT_BQ};
-    if (int rc = make_tensor_map(&mq, out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+    if (int rc = make_tensor_map(&mq, queries, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
       return rc;
   }
   {
@@ -874,9 +880,48 @@ static int rpa_prefill_launch(AttnParams& p, void* out, const void* kv_cache, co
   }
   const long long bound = static_cast<long long>(max_tiles) * Hkv * (p.group / 2);
   const int grid = static_cast<int>(std::min<long long>(bound, sm_count()));
-  attention_kernel<false, true><<<grid, AT_THREADS, AttnSmem::TOTAL, s>>>(mq, mkv, mkv, p);
-  TJX_CUDA(cudaGetLastError());
+  p.chain = launch_chain();
+  if (p.chain & CHAIN_WAITS) {
+    TJX_CUDA(launch_chained(attention_kernel<false, true>, dim3(grid), dim3(AT_THREADS), AttnSmem::TOTAL, s, mq, mkv, mkv, p));
+  } else {
+    attention_kernel<false, true><<<grid, AT_THREADS, AttnSmem::TOTAL, s>>>(mq, mkv, mkv, p);
+    TJX_CUDA(cudaGetLastError());
+  }
   return 0;
+}
+
+size_t rpa_prefill_part_bytes(int T, int S) {
+  const size_t max_tiles = static_cast<size_t>((T + AT_BQ - 1) / AT_BQ) + S;
+  return 4 * attn_align256(max_tiles * 4) + 256;
+}
+
+int rpa_prefill_part_check(const void* q, const void* out, const void* kv_cache, const void* page_indices, int T, int S,
+                           int H, int Hkv, int D, int page_size, int pages_per_seq, int num_pages) {
+  if (S <= 0 || pages_per_seq <= 0) return fail(TJX_E_ARG, "sizes must be positive");
+  return rpa_prefill_check(q, out, kv_cache, page_indices, T, H, Hkv, D, page_size, num_pages);
+}
+
+int rpa_prefill_tiles_part(const int32_t* kv_lens, const int32_t* cu_q_lens, const int32_t* distribution, int T, int S,
+                           int pages_per_seq, void* workspace, cudaStream_t stream, RpaTiles* tiles) {
+  const int max_tiles = (T + AT_BQ - 1) / AT_BQ + S;
+  AttnParams p{};
+  rpa_tile_arrays(p, workspace, max_tiles);
+  TJX_CUDA(launch_chained(rpa_prefill_tiles_kernel, dim3(1), dim3(256), 0, stream, kv_lens, cu_q_lens, distribution, S,
+                          pages_per_seq, max_tiles, const_cast<int32_t*>(p.tile_row0), const_cast<int32_t*>(p.tile_rows),
+                          const_cast<int32_t*>(p.tile_pos), const_cast<int32_t*>(p.tile_page),
+                          const_cast<int32_t*>(p.n_tiles)));
+  tiles->row0 = p.tile_row0, tiles->rows = p.tile_rows, tiles->count = p.n_tiles, tiles->max_tiles = max_tiles;
+  return 0;
+}
+
+int rpa_prefill_attention_part(const void* q, void* out, const void* kv_cache, const int32_t* page_indices, int T, int S,
+                               int H, int Hkv, int pages_per_seq, int num_pages, float sm_scale, void* workspace,
+                               cudaStream_t stream) {
+  const int max_tiles = (T + AT_BQ - 1) / AT_BQ + S;
+  AttnParams p{};
+  rpa_tile_arrays(p, workspace, max_tiles);
+  return rpa_prefill_launch(p, out, kv_cache, page_indices, S * pages_per_seq, T, H, Hkv, num_pages, sm_scale, max_tiles,
+                            stream, q);
 }
 
 }  // namespace tjx

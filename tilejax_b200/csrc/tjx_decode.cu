@@ -685,6 +685,7 @@ __global__ void __launch_bounds__(128)
                      const int32_t* __restrict__ page_indices, const int32_t* __restrict__ cu_q_lens,
                      const int32_t* __restrict__ distribution, int S, int Hkv, int page_size, int pages_per_seq,
                      int num_pages) {
+  chain_release();  // (a kernel chained behind this one may run beside it: see tjx_ragged_paged_attention_bf16)
   const int t = blockIdx.x;
   int lo = 0, hi = S;  // the sequence with cu_q_lens[s] <= t < cu_q_lens[s + 1]
   if (t >= cu_q_lens[S]) return;  // a padding token
@@ -740,8 +741,10 @@ __global__ void __launch_bounds__(128)
 // lengths[s] = kv_lens[s] for the decode sequences, 0 for the others (which then take one empty step).
 __global__ void rpa_decode_lengths_kernel(const int32_t* __restrict__ kv_lens, const int32_t* __restrict__ distribution,
                                           int32_t* __restrict__ lengths, int n, int max_len) {
+  chain_release();  // (reads only the call's inputs: when chained it runs beside the kernel in front of it)
   const int s = blockIdx.x * blockDim.x + threadIdx.x;
   if (s < n) lengths[s] = s < distribution[0] ? min(max(kv_lens[s], 0), max_len) : 0;
+  chain_wait();  // ends after the kernel it was chained behind: what follows this one follows that one too
 }
 
 // out[s] = result[s] for the decode tokens (one CTA per token, 16 bytes per thread per pass); other rows keep q.
@@ -752,6 +755,39 @@ __global__ void __launch_bounds__(128)
   if (s >= distribution[0]) return;
   const uint4* src = reinterpret_cast<const uint4*>(result + static_cast<size_t>(s) * row_elements);
   uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(s) * row_elements);
+  for (int u = threadIdx.x; u < row_elements / 8; u += blockDim.x) dst[u] = src[u];
+}
+
+// The whole step's rows other than the prefill tiles': row r of out becomes the decode result of token r < decode
+// sequences, or, where `keep` is set, stays the query unless a prefill tile covers it (those rows are the attention
+// kernel's to write). One CTA per row; the tile list is short (a tile per 128 new tokens).
+__global__ void __launch_bounds__(128)
+    rpa_finish_rows_kernel(const __nv_bfloat16* __restrict__ result, const __nv_bfloat16* __restrict__ q,
+                           __nv_bfloat16* __restrict__ out, const int32_t* __restrict__ distribution, int n,
+                           int row_elements, const int32_t* __restrict__ tile_row0,
+                           const int32_t* __restrict__ tile_rows, const int32_t* __restrict__ n_tiles, int max_tiles,
+                           int keep) {
+  __shared__ int covered;
+  chain_release();
+  const int r = blockIdx.x;
+  const __nv_bfloat16* from;
+  if (r < n && r < distribution[0]) {
+    from = result;
+  } else {
+    if (!keep) return;
+    if (threadIdx.x == 0) covered = 0;
+    __syncthreads();
+    const int count = min(max(n_tiles[0], 0), max_tiles);
+    for (int k = threadIdx.x; k < count; k += blockDim.x) {
+      const int first = tile_row0[k];
+      if (r >= first && r < first + tile_rows[k]) covered = 1;
+    }
+    __syncthreads();
+    if (covered) return;
+    from = q;
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(from + static_cast<size_t>(r) * row_elements);
+  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * row_elements);
   for (int u = threadIdx.x; u < row_elements / 8; u += blockDim.x) dst[u] = src[u];
 }
 
@@ -870,6 +906,63 @@ int tjx_rpa_decode_bf16(const void* q, void* out, const void* kv_cache, const in
   rpa_decode_scatter_kernel<<<n, 128, 0, s>>>(w.result, static_cast<__nv_bfloat16*>(out), distribution, H * DEC_D);
   TJX_CUDA(cudaGetLastError());
   return 0;
+}
+
+size_t tjx_ragged_paged_attention_workspace_bytes(int T, int S, int H, int D, int page_size, int pages_per_seq) {
+  const size_t decode = tjx_rpa_decode_workspace_bytes(T, S, H, D, page_size, pages_per_seq);
+  if (decode == 0) return 0;
+  return tjx::align256(decode) + tjx::rpa_prefill_part_bytes(T, S);
+}
+
+int tjx_ragged_paged_attention_bf16(const void* q, const void* keys, const void* values, void* kv_cache,
+                                    const int32_t* kv_lens, const int32_t* page_indices, const int32_t* cu_q_lens,
+                                    const int32_t* distribution, void* out, int T, int S, int H, int Hkv, int D,
+                                    int page_size, int pages_per_seq, int num_pages, float sm_scale, void* workspace,
+                                    size_t workspace_bytes, tjx_stream_t stream) {
+  using namespace tjx;
+  if (int rc = check_device()) return rc;
+  if (!q || !out || !keys || !values || !kv_cache || !kv_lens || !page_indices || !cu_q_lens || !distribution)
+    return fail(TJX_E_ARG, "an input or output pointer is null");
+  const size_t need = tjx_ragged_paged_attention_workspace_bytes(T, S, H, D, page_size, pages_per_seq);
+  if (T <= 0 || S <= 0 || need == 0) return fail(TJX_E_ARG, "sizes must be positive");
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(TJX_E_ARG, "workspace is null or smaller than tjx_ragged_paged_attention_workspace_bytes");
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(TJX_E_ARG, "workspace must be 256-byte aligned");
+  // Every refusal comes before the first launch.
+  const int n = std::min(S, T);  // sequence s is token s
+  const RpaScratch w = rpa_scratch(workspace, n, H, page_size, pages_per_seq);
+  void* prefill_ws = static_cast<uint8_t*>(workspace) + align256(w.bytes);
+  const __nv_bfloat16* cache = static_cast<const __nv_bfloat16*>(kv_cache);
+  if (int rc = check_decode_args(q, cache, cache + DEC_D, page_indices, w.lengths, out, n, 1, H, Hkv, D, page_size,
+                                 pages_per_seq, num_pages, w.step_tile, w.step_code, w.step_count, w.tile_first))
+    return rc;
+  if (int rc = rpa_prefill_part_check(q, out, kv_cache, page_indices, T, S, H, Hkv, D, page_size, pages_per_seq, num_pages))
+    return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // 1. The new tokens into the cache; beside it (chained, reading only index arrays) the decode lengths and the
+  //    prefill tiles.
+  if (int rc = tjx_rpa_write_bf16(kv_cache, keys, values, kv_lens, page_indices, cu_q_lens, distribution, T, S, Hkv, D,
+                                  page_size, pages_per_seq, num_pages, stream))
+    return rc;
+  TJX_CUDA(launch_chained(rpa_decode_lengths_kernel, dim3((n + 127) / 128), dim3(128), 0, s, kv_lens, distribution,
+                          w.lengths, n, pages_per_seq * page_size));
+  RpaTiles tiles{};
+  if (int rc = rpa_prefill_tiles_part(kv_lens, cu_q_lens, distribution, T, S, pages_per_seq, prefill_ws, s, &tiles))
+    return rc;
+  // 2. The decode sequences over the updated cache (ordinary launches: they follow everything above), into scratch.
+  if (int rc = run_decode(q, cache, cache + DEC_D, page_indices, w.lengths, w.result, n, 1, H, Hkv, page_size,
+                          pages_per_seq, num_pages, w.step_tile, w.step_code, w.step_count, w.tile_first, w.decode, s,
+                          sm_scale, 2 * DEC_D, static_cast<long long>(Hkv) * 2 * DEC_D, min_share_for_pages_of(page_size)))
+    return rc;
+  // 3. Their rows of out, and q's rows that no case writes; 4. the prefill tiles' rows, queries straight from q, its
+  //    set-up under kernel 3.
+  rpa_finish_rows_kernel<<<T, 128, 0, s>>>(w.result, static_cast<const __nv_bfloat16*>(q),
+                                           static_cast<__nv_bfloat16*>(out), distribution, n, H * DEC_D, tiles.row0,
+                                           tiles.rows, tiles.count, tiles.max_tiles, out != q ? 1 : 0);
+  TJX_CUDA(cudaGetLastError());
+  LaunchChain chain(CHAIN_WAITS);
+  return rpa_prefill_attention_part(q, out, kv_cache, page_indices, T, S, H, Hkv, pages_per_seq, num_pages, sm_scale,
+                                    prefill_ws, s);
 }
 
 }  // extern "C"

@@ -41,6 +41,39 @@ struct LaunchChain {
   LaunchChain& operator=(const LaunchChain&) = delete;
 };
 
+// A launch with programmatic stream serialization allowed: the kernel may be scheduled once the kernel in front of it
+// on the stream has released (chain_release) or ended, and orders itself behind that kernel with chain_wait.
+template <typename... Params, typename... Args>
+cudaError_t launch_chained(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                           Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = stream;
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr, cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
+
+// The prefill half of a ragged paged attention step, for the entry point that runs the whole step
+// (tjx_ragged_paged_attention_bf16; defined beside the attention kernel). The tile arrays live in `workspace`
+// (rpa_prefill_part_bytes, 256-byte aligned).
+struct RpaTiles {
+  const int32_t *row0, *rows, *count;  // tile k covers rows row0[k] .. row0[k] + rows[k] - 1 of q; count[0] tiles
+  int max_tiles;
+};
+size_t rpa_prefill_part_bytes(int T, int S);
+int rpa_prefill_part_check(const void* q, const void* out, const void* kv_cache, const void* page_indices, int T, int S,
+                           int H, int Hkv, int D, int page_size, int pages_per_seq, int num_pages);
+// Enqueues the kernel that lists the step's prefill tiles, chained behind the kernel in front of it.
+int rpa_prefill_tiles_part(const int32_t* kv_lens, const int32_t* cu_q_lens, const int32_t* distribution, int T, int S,
+                           int pages_per_seq, void* workspace, cudaStream_t stream, RpaTiles* tiles);
+// Enqueues the paged attention over those tiles: queries from q, outputs to the tiles' rows of out; chained behind
+// the kernel in front of it as launch_chain() says.
+int rpa_prefill_attention_part(const void* q, void* out, const void* kv_cache, const int32_t* page_indices, int T, int S,
+                               int H, int Hkv, int pages_per_seq, int num_pages, float sm_scale, void* workspace,
+                               cudaStream_t stream);
+
 // Per-device status word the kernels write error codes to: a fixed device variable inside the library (no
 // allocation); the address is looked up once per device.
 int* device_status_word();

@@ -598,11 +598,33 @@ def ragged_paged_attention(q: torch.Tensor, keys: torch.Tensor, values: torch.Te
                            distribution: torch.Tensor, sm_scale: float = 1.0) -> tuple[torch.Tensor, torch.Tensor]:
     """RPA v3's step (`autokernel_rpa`, examples/ragged_paged_attention.py:279-290): the new tokens' keys and values
     written into the cache in place, the decode sequences' attention, then the others'. Returns (out (T, H, D), the
-    cache); q is left as it was."""
-    cache = rpa_write(kv_cache, keys, values, kv_lens, page_indices, cu_q_lens, distribution)
-    out = rpa_decode(q, cache, kv_lens, page_indices, distribution, sm_scale)
-    out = rpa_prefill(out, cache, kv_lens, page_indices, cu_q_lens, distribution, sm_scale, out=out)
-    return out, cache
+    cache); q is left as it was. One call into the library (tjx_ragged_paged_attention_bf16): the same results as
+    rpa_write, rpa_decode and rpa_prefill one after the other, without their copy of q into out."""
+    num_pages, page_size, Hkv, D, S, pps = _rpa_sizes(kv_cache, kv_lens, page_indices)
+    device = _need_cuda(q, keys, values, kv_cache, kv_lens, page_indices, cu_q_lens, distribution)
+    if q.dim() != 3 or q.shape[2] != D or q.dtype != torch.bfloat16 or not q.is_contiguous():
+        raise ValueError("q is a contiguous (T, H, D) bfloat16 tensor")
+    T, H, _ = q.shape
+    if keys.shape != (T, Hkv, D) or values.shape != (T, Hkv, D) or keys.dtype != torch.bfloat16 \
+            or values.dtype != torch.bfloat16:
+        raise ValueError("keys and values are (T, Hkv, D) bfloat16")
+    if cu_q_lens.shape != (S + 1,) or distribution.shape != (3,) or cu_q_lens.dtype != torch.int32 \
+            or distribution.dtype != torch.int32:
+        raise ValueError("cu_q_lens is int32 (S + 1,), distribution int32 (3,)")
+    out = torch.empty_like(q)
+    with torch.cuda.device(device):
+        need = int(library().tjx_ragged_paged_attention_workspace_bytes(T, S, H, D, page_size, pps))
+        key = ("step", str(device), need)
+        ws = _rpa_workspaces.get(key)
+        if ws is None:
+            _rpa_workspaces.clear()
+            ws = _rpa_workspaces[key] = torch.empty(need + 256, dtype=torch.uint8, device=device)
+        ws_ptr = (ws.data_ptr() + 255) & ~255
+        check(library().tjx_ragged_paged_attention_bf16(
+            _ptr(q), _ptr(keys), _ptr(values), _ptr(kv_cache), _ptr(kv_lens), _ptr(page_indices), _ptr(cu_q_lens),
+            _ptr(distribution), _ptr(out), T, S, H, Hkv, D, page_size, pps, num_pages, float(sm_scale),
+            ctypes.c_void_p(ws_ptr), need, _stream()))
+    return out, kv_cache
 
 
 def paged_gqa_decode_static(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_tables: torch.Tensor,
