@@ -146,6 +146,11 @@ def test_the_one_call_step_equals_the_three_calls_bit_for_bit(q_lens, kv_lens, s
         assert torch.equal(cache1.view(torch.int16), cache3.view(torch.int16))
         assert torch.equal(out1.view(torch.int16), out3.view(torch.int16))
     np.testing.assert_array_equal(to_host(dev["q"]).view(np.uint16), inp["q"].view(np.uint16))
+    # The update in place, as the reference's donated q gets it.
+    in_place = dev["q"].clone()
+    same, _ = ops.ragged_paged_attention(in_place, dev["keys"], dev["values"], dev["kv_cache"].clone(), *index,
+                                         dev["cu_q_lens"], dev["distribution"], scale, out=in_place)
+    assert same is in_place and torch.equal(in_place.view(torch.int16), out3.view(torch.int16))
 
 
 def test_prefill_limits_are_errors():

@@ -595,10 +595,11 @@ def rpa_prefill_tiles(q: torch.Tensor, kv_cache: torch.Tensor, page_indices: tor
 
 def ragged_paged_attention(q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, kv_cache: torch.Tensor,
                            kv_lens: torch.Tensor, page_indices: torch.Tensor, cu_q_lens: torch.Tensor,
-                           distribution: torch.Tensor, sm_scale: float = 1.0) -> tuple[torch.Tensor, torch.Tensor]:
+                           distribution: torch.Tensor, sm_scale: float = 1.0,
+                           out: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
     """RPA v3's step (`autokernel_rpa`, examples/ragged_paged_attention.py:279-290): the new tokens' keys and values
     written into the cache in place, the decode sequences' attention, then the others'. Returns (out (T, H, D), the
-    cache); q is left as it was. One call into the library (tjx_ragged_paged_attention_bf16): the same results as
+    cache); q is left as it was unless `out=q` asks for the update in place. One call into the library (tjx_ragged_paged_attention_bf16): the same results as
     rpa_write, rpa_decode and rpa_prefill one after the other, without their copy of q into out."""
     num_pages, page_size, Hkv, D, S, pps = _rpa_sizes(kv_cache, kv_lens, page_indices)
     device = _need_cuda(q, keys, values, kv_cache, kv_lens, page_indices, cu_q_lens, distribution)
@@ -611,7 +612,10 @@ def ragged_paged_attention(q: torch.Tensor, keys: torch.Tensor, values: torch.Te
     if cu_q_lens.shape != (S + 1,) or distribution.shape != (3,) or cu_q_lens.dtype != torch.int32 \
             or distribution.dtype != torch.int32:
         raise ValueError("cu_q_lens is int32 (S + 1,), distribution int32 (3,)")
-    out = torch.empty_like(q)
+    if out is None:
+        out = torch.empty_like(q)
+    elif out.shape != q.shape or out.dtype != q.dtype or not out.is_contiguous() or out.device != q.device:
+        raise ValueError("out must look like q")
     with torch.cuda.device(device):
         need = int(library().tjx_ragged_paged_attention_workspace_bytes(T, S, H, D, page_size, pps))
         key = ("step", str(device), need)
