@@ -726,47 +726,76 @@ int attention_launch(const void* q, const void* k, const void* v, void* out, flo
 
 namespace tjx {
 
+// Buckets of the tile kernels' counting sort: a tile's key is the number of 128-key blocks it attends to.
+constexpr int RPA_SORT_KEYS = 1024;
+
+// Exclusive scan of hist[RPA_SORT_KEYS] in place by a CTA of 256 threads (four buckets a thread).
+__device__ __forceinline__ void rpa_scan_buckets(int* hist, int* scan_sh) {
+  const int t = threadIdx.x;
+  int v[4], sum = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) v[j] = hist[4 * t + j], sum += v[j];
+  scan_sh[t] = sum;
+  __syncthreads();
+  for (int d = 1; d < 256; d <<= 1) {  // inclusive scan of the threads' sums
+    const int y = t >= d ? scan_sh[t - d] : 0;
+    __syncthreads();
+    scan_sh[t] += y;
+    __syncthreads();
+  }
+  int at = scan_sh[t] - sum;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) hist[4 * t + j] = at, at += v[j];
+  __syncthreads();
+}
+
+// Bucket of a tile whose first row sits at cache position pos: longest first.
+__device__ __forceinline__ int rpa_bucket(int pos, int rows) {
+  const int blocks = (max(pos, 0) + rows + AT_BKV - 1) / AT_BKV;
+  return RPA_SORT_KEYS - 1 - min(blocks, RPA_SORT_KEYS - 1);
+}
+
 // The prefill tiles of one step, on the device (what `prefill_tiles` computes in plain JAX,
 // examples/ragged_paged_attention.py:252-275, for blocks of 128 queries): a tile per block of 128 new tokens of each
-// sequence in [distribution[0], distribution[2]). One CTA; thread s handles sequences s, s + 256, ...; an exclusive
-// scan of the sequences' tile counts gives each its first tile.
+// sequence in [distribution[0], distribution[2]), listed longest first (by the key blocks a tile attends to: the
+// attention kernel deals its units out in list order, and a short last round should hold the lightest). One CTA;
+// thread s handles sequences s, s + 256, ...; a counting sort: one pass counts the tiles of every length, a scan
+// gives each length its first slot, a second pass writes every tile to the next slot of its length.
 __global__ void __launch_bounds__(256)
     rpa_prefill_tiles_kernel(const int32_t* __restrict__ kv_lens, const int32_t* __restrict__ cu_q_lens,
                              const int32_t* __restrict__ distribution, int S, int pages_per_seq, int max_tiles,
                              int32_t* __restrict__ tile_row0, int32_t* __restrict__ tile_rows,
                              int32_t* __restrict__ tile_pos, int32_t* __restrict__ tile_page,
                              int32_t* __restrict__ n_tiles) {
-  __shared__ int carry_sh, scan_sh[256];
+  __shared__ int hist[RPA_SORT_KEYS], scan_sh[256], total_sh;
   chain_release();  // (reads only the call's inputs: when chained it runs beside the kernel in front of it)
-  if (threadIdx.x == 0) carry_sh = 0;
+  for (int i = threadIdx.x; i < RPA_SORT_KEYS; i += 256) hist[i] = 0;
+  if (threadIdx.x == 0) total_sh = 0;
   __syncthreads();
   const int d0 = distribution[0], d2 = min(distribution[2], S);
-  for (int s0 = 0; s0 < S; s0 += 256) {
-    const int s = s0 + threadIdx.x;
-    const int q_len = s < S ? cu_q_lens[s + 1] - cu_q_lens[s] : 0;
-    const int mine = (s >= d0 && s < d2 && q_len > 0) ? (q_len + AT_BQ - 1) / AT_BQ : 0;
-    scan_sh[threadIdx.x] = mine;
-    __syncthreads();
-    for (int d = 1; d < 256; d <<= 1) {  // inclusive scan
-      const int y = threadIdx.x >= d ? scan_sh[threadIdx.x - d] : 0;
-      __syncthreads();
-      scan_sh[threadIdx.x] += y;
-      __syncthreads();
-    }
-    const int first = carry_sh + scan_sh[threadIdx.x] - mine;
-    for (int b = 0; b < mine; ++b) {
-      const int k = first + b;
-      if (k >= max_tiles) break;
-      tile_row0[k] = cu_q_lens[s] + b * AT_BQ;
-      tile_rows[k] = min(AT_BQ, q_len - b * AT_BQ);
-      tile_pos[k] = kv_lens[s] - q_len + b * AT_BQ;
-      tile_page[k] = s * pages_per_seq;
+  for (int pass = 0; pass < 2; ++pass) {
+    for (int s = threadIdx.x; s < S; s += 256) {
+      const int q_len = cu_q_lens[s + 1] - cu_q_lens[s];
+      const int mine = (s >= d0 && s < d2 && q_len > 0) ? (q_len + AT_BQ - 1) / AT_BQ : 0;
+      for (int b = 0; b < mine; ++b) {
+        const int pos = kv_lens[s] - q_len + b * AT_BQ, rows = min(AT_BQ, q_len - b * AT_BQ);
+        if (pass == 0) {
+          atomicAdd(&hist[rpa_bucket(pos, rows)], 1);
+        } else {
+          const int k = atomicAdd(&hist[rpa_bucket(pos, rows)], 1);
+          if (k >= max_tiles) continue;
+          tile_row0[k] = cu_q_lens[s] + b * AT_BQ;
+          tile_rows[k] = rows;
+          tile_pos[k] = pos;
+          tile_page[k] = s * pages_per_seq;
+        }
+      }
+      if (pass == 0 && mine > 0) atomicAdd(&total_sh, mine);
     }
     __syncthreads();
-    if (threadIdx.x == 255) carry_sh += scan_sh[255];
-    __syncthreads();
+    if (pass == 0) rpa_scan_buckets(hist, scan_sh);
   }
-  if (threadIdx.x == 0) n_tiles[0] = min(carry_sh, max_tiles);
+  if (threadIdx.x == 0) n_tiles[0] = min(total_sh, max_tiles);
   chain_wait();  // ends after the kernel it was chained behind: what follows this one follows that one too
 }
 
