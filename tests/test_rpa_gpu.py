@@ -153,6 +153,22 @@ def test_the_one_call_step_equals_the_three_calls_bit_for_bit(q_lens, kv_lens, s
     assert same is in_place and torch.equal(in_place.view(torch.int16), out3.view(torch.int16))
 
 
+def test_the_one_call_step_refuses_before_it_writes_the_cache():
+    # More sequences than a device step table holds: refused by the call as a whole, the cache as it was.
+    T = S = 8193
+    zeros = lambda *shape: torch.zeros(shape, dtype=torch.int32, device="cuda")  # noqa: E731
+    q = torch.zeros((T, 4, 128), dtype=torch.bfloat16, device="cuda")
+    kv = torch.ones((T, 2, 128), dtype=torch.bfloat16, device="cuda")
+    cache = torch.zeros((2, 128, 2, 2, 128), dtype=torch.bfloat16, device="cuda")
+    lens = torch.ones(S, dtype=torch.int32, device="cuda")
+    cu = torch.arange(S + 1, dtype=torch.int32, device="cuda")
+    dist = torch.tensor([S, S, S], dtype=torch.int32, device="cuda")
+    with pytest.raises(NativeError, match="more than 8192 tiles"):
+        ops.ragged_paged_attention(q, kv, kv, cache, lens, zeros(S), cu, dist)
+    torch.cuda.synchronize()
+    assert not cache.any()
+
+
 def test_prefill_limits_are_errors():
     inp, dev = step([4], [4], heads=4, kv_heads=4, max_len=256)  # one query head per KV head
     with pytest.raises(NativeError, match="even number of query heads per KV head"):

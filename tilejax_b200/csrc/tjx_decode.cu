@@ -29,6 +29,7 @@
 
 namespace tjx {
 
+int check_step_table_sizes(int tiles, int blocks);
 int launch_build_steps_lengths(const int32_t* lengths, int n_lengths, const int32_t* tile_values, int tiles,
                                int blocks, int value0, int value_step, int32_t* step_tile, int32_t* step_code,
                                int32_t* step_count, int32_t* tile_first, int32_t* zero_words, int n_zero,
@@ -928,8 +929,9 @@ int tjx_ragged_paged_attention_bf16(const void* q, const void* keys, const void*
   if (workspace == nullptr || workspace_bytes < need)
     return fail(TJX_E_ARG, "workspace is null or smaller than tjx_ragged_paged_attention_workspace_bytes");
   if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(TJX_E_ARG, "workspace must be 256-byte aligned");
-  // Every refusal comes before the first launch.
+  // Every refusal of a size or a pointer comes before the first launch: the cache is not written by a call that fails.
   const int n = std::min(S, T);  // sequence s is token s
+  if (int rc = check_step_table_sizes(n, pages_per_seq)) return rc;
   const RpaScratch w = rpa_scratch(workspace, n, H, page_size, pages_per_seq);
   void* prefill_ws = static_cast<uint8_t*>(workspace) + align256(w.bytes);
   const __nv_bfloat16* cache = static_cast<const __nv_bfloat16*>(kv_cache);

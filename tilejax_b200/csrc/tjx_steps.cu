@@ -152,6 +152,12 @@ static int check_common(int tiles, int blocks, const void* a, const void* b, con
   return 0;
 }
 
+// The size limits alone, for an entry point that must refuse before its first launch.
+int check_step_table_sizes(int tiles, int blocks) {
+  static const int placeholder = 0;
+  return check_common(tiles, blocks, &placeholder, &placeholder, &placeholder);
+}
+
 int launch_build_steps_lengths(const int32_t* lengths, int n_lengths, const int32_t* tile_values, int tiles,
                                int blocks, int value0, int value_step, int32_t* step_tile, int32_t* step_code,
                                int32_t* step_count, int32_t* tile_first, int32_t* zero_words, int n_zero,
