@@ -274,7 +274,9 @@ size_t tjx_ragged_paged_attention_workspace_bytes(int T, int S, int H, int D, in
  * are different rows; it spares their copy of q into out (the prefill queries are read from q itself), and its small
  * kernels are chained to run beside their neighbours on the stream.
  *   workspace: at least tjx_ragged_paged_attention_workspace_bytes(...) bytes, 256-byte aligned
- * Constraints: those of the three entry points together (D == 128; page_size == 128; H / Hkv in {2, 4, 8}). */
+ * Constraints: those of the three entry points together (D == 128; page_size == 128; H / Hkv in {2, 4, 8}; at most
+ * 8192 sequences, the device step table's limit). Sizes and pointers are checked before the first launch: a call
+ * that returns an error for them has not touched the cache. */
 int tjx_ragged_paged_attention_bf16(const void* q, const void* keys, const void* values, void* kv_cache,
                                     const int32_t* kv_lens, const int32_t* page_indices, const int32_t* cu_q_lens,
                                     const int32_t* distribution, void* out, int T, int S, int H, int Hkv, int D,
