@@ -19,7 +19,8 @@ def test_every_registered_target_has_a_handler_symbol():
     defined = set(re.findall(r"XLA_FFI_DEFINE_HANDLER_SYMBOL\((\w+),", text))
     assert defined == set(xla_ffi.TARGETS.values())
     for entry in ("tjx_build_steps", "tjx_gemm_bf16", "tjx_causal_attention_bf16", "tjx_paged_gqa_decode_bf16",
-                  "tjx_rmsnorm_gemm_bf16", "tjx_attention_block_bf16", "tjx_mla_decode_bf16"):
+                  "tjx_rmsnorm_gemm_bf16", "tjx_attention_block_bf16", "tjx_mla_decode_bf16",
+                  "tjx_ragged_paged_attention_bf16"):
         assert f"{entry}(" in text  # each handler ends in the C ABI call it wraps
     assert "cudaMalloc" not in text and "cudaDeviceSynchronize" not in text  # enqueue only, no allocation
 

@@ -202,6 +202,46 @@ ffi::Error MlaDecodeImpl(cudaStream_t stream, ffi::AnyBuffer q_c, ffi::AnyBuffer
   return rc == 0 ? ffi::Error::Success() : Failed(rc);
 }
 
+// ------------------------------------------------------------------------------------ ragged paged attention
+
+// The whole step (`autokernel_rpa`, examples/ragged_paged_attention.py:279-290). The cache is updated in place: the
+// caller aliases the cache operand to the cache result (input_output_aliases), as the reference donates it; where XLA
+// hands over two different buffers the old cache is copied into the result first, on the same stream.
+ffi::Error RaggedPagedAttentionImpl(cudaStream_t stream, ffi::AnyBuffer q, ffi::AnyBuffer keys, ffi::AnyBuffer values,
+                                    ffi::AnyBuffer kv_cache, ffi::AnyBuffer kv_lens, ffi::AnyBuffer page_indices,
+                                    ffi::AnyBuffer cu_q_lens, ffi::AnyBuffer distribution,
+                                    ffi::Result<ffi::AnyBuffer> out, ffi::Result<ffi::AnyBuffer> cache_out,
+                                    ffi::Result<ffi::AnyBuffer> workspace, float sm_scale) {
+  for (const ffi::AnyBuffer* b : {&q, &keys, &values, &kv_cache})
+    if (b->element_type() != ffi::BF16) return Bad("q, keys, values and kv_cache must be bfloat16");
+  for (const ffi::AnyBuffer* b : {&kv_lens, &page_indices, &cu_q_lens, &distribution})
+    if (b->element_type() != ffi::S32) return Bad("kv_lens, page_indices, cu_q_lens and distribution must be int32");
+  if (q.dimensions().size() != 3 || keys.dimensions().size() != 3 || kv_cache.dimensions().size() != 5)
+    return Bad("q [T, H, D], keys and values [T, Hkv, D], kv_cache [pages, page_size, Hkv, 2, D]");
+  const int T = Dim(q, 0), H = Dim(q, 1), D = Dim(q, 2), Hkv = Dim(kv_cache, 2);
+  const int num_pages = Dim(kv_cache, 0), page_size = Dim(kv_cache, 1);
+  const int S = static_cast<int>(kv_lens.element_count());
+  if (S <= 0 || page_indices.element_count() % static_cast<size_t>(S) != 0 ||
+      cu_q_lens.element_count() != static_cast<size_t>(S) + 1 || distribution.element_count() != 3)
+    return Bad("page_indices holds S * pages_per_seq entries, cu_q_lens S + 1, distribution 3");
+  const int pages_per_seq = static_cast<int>(page_indices.element_count() / static_cast<size_t>(S));
+  if (cache_out->size_bytes() != kv_cache.size_bytes()) return Bad("the cache result must have the cache's size");
+  const size_t need = tjx_ragged_paged_attention_workspace_bytes(T, S, H, D, page_size, pages_per_seq);
+  void* ws = need == 0 ? nullptr : Aligned(workspace, need);
+  if (ws == nullptr) return Bad("the workspace result is too small");
+  if (cache_out->untyped_data() != kv_cache.untyped_data()) {
+    const cudaError_t e = cudaMemcpyAsync(cache_out->untyped_data(), kv_cache.untyped_data(), kv_cache.size_bytes(),
+                                          cudaMemcpyDeviceToDevice, stream);
+    if (e != cudaSuccess) return ffi::Error(ffi::ErrorCode::kInternal, cudaGetErrorString(e));
+  }
+  const int rc = tjx_ragged_paged_attention_bf16(
+      q.untyped_data(), keys.untyped_data(), values.untyped_data(), cache_out->untyped_data(),
+      static_cast<const int32_t*>(kv_lens.untyped_data()), static_cast<const int32_t*>(page_indices.untyped_data()),
+      static_cast<const int32_t*>(cu_q_lens.untyped_data()), static_cast<const int32_t*>(distribution.untyped_data()),
+      out->untyped_data(), T, S, H, Hkv, D, page_size, pages_per_seq, num_pages, sm_scale, ws, need, stream);
+  return rc == 0 ? ffi::Error::Success() : Failed(rc);
+}
+
 }  // namespace
 
 XLA_FFI_DEFINE_HANDLER_SYMBOL(TjxBuildSteps, BuildStepsImpl,
@@ -308,3 +348,19 @@ XLA_FFI_DEFINE_HANDLER_SYMBOL(TjxMlaDecode, MlaDecodeImpl,
                                   .Ret<ffi::AnyBuffer>()   // tile_first
                                   .Ret<ffi::AnyBuffer>()   // workspace (uint8)
                                   .Attr<int32_t>("block"));
+
+XLA_FFI_DEFINE_HANDLER_SYMBOL(TjxRaggedPagedAttention, RaggedPagedAttentionImpl,
+                              ffi::Ffi::Bind()
+                                  .Ctx<ffi::PlatformStream<cudaStream_t>>()
+                                  .Arg<ffi::AnyBuffer>()   // q
+                                  .Arg<ffi::AnyBuffer>()   // keys
+                                  .Arg<ffi::AnyBuffer>()   // values
+                                  .Arg<ffi::AnyBuffer>()   // kv_cache (aliased to the cache result)
+                                  .Arg<ffi::AnyBuffer>()   // kv_lens
+                                  .Arg<ffi::AnyBuffer>()   // page_indices
+                                  .Arg<ffi::AnyBuffer>()   // cu_q_lens
+                                  .Arg<ffi::AnyBuffer>()   // distribution
+                                  .Ret<ffi::AnyBuffer>()   // out
+                                  .Ret<ffi::AnyBuffer>()   // kv_cache, updated
+                                  .Ret<ffi::AnyBuffer>()   // workspace (uint8)
+                                  .Attr<float>("sm_scale"));

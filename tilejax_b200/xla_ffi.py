@@ -20,7 +20,8 @@ from ._lib import LIBRARY
 FFI_LIBRARY = Path(__file__).resolve().parent / "libtilejax_b200_ffi.so"
 TARGETS = {"tjx_build_steps": "TjxBuildSteps", "tjx_gemm": "TjxGemm", "tjx_causal_attention": "TjxCausalAttention",
            "tjx_paged_gqa_decode": "TjxPagedGqaDecode", "tjx_rmsnorm_gemm": "TjxRmsnormGemm",
-           "tjx_attention_block": "TjxAttentionBlock", "tjx_mla_decode": "TjxMlaDecode"}
+           "tjx_attention_block": "TjxAttentionBlock", "tjx_mla_decode": "TjxMlaDecode",
+           "tjx_ragged_paged_attention": "TjxRaggedPagedAttention"}
 _registered = False
 
 
@@ -178,3 +179,23 @@ def mla_decode(q_c, q_r, c_kv, k_rope, lengths, block_kv: int = 512):
     out, tile, code, count, _, _ = jax.ffi.ffi_call("tjx_mla_decode", results)(q_c, q_r, c_kv, k_rope, lengths,
                                                                                block=np.int32(block))
     return out, tile, code, count
+
+
+def ragged_paged_attention(q, keys, values, kv_cache, kv_lens, page_indices, cu_q_lens, distribution,
+                           sm_scale: float = 1.0):
+    """One ragged paged attention step through `tjx_ragged_paged_attention` (`autokernel_rpa`,
+    examples/ragged_paged_attention.py:279-290): (out, the updated cache). The cache operand is aliased to the cache
+    result, so under `jax.jit` with the cache donated the update is in place, as the reference's is."""
+    import jax
+    import jax.numpy as jnp
+
+    register()
+    T, H, D = q.shape
+    S = kv_lens.shape[0]
+    page_size = kv_cache.shape[1]
+    scratch = _scratch("tjx_ragged_paged_attention_workspace_bytes", T, S, H, D, page_size, page_indices.shape[0] // S)
+    results = (jax.ShapeDtypeStruct(q.shape, q.dtype), jax.ShapeDtypeStruct(kv_cache.shape, kv_cache.dtype),
+               jax.ShapeDtypeStruct((scratch,), jnp.uint8))
+    out, cache, _ = jax.ffi.ffi_call("tjx_ragged_paged_attention", results, input_output_aliases={3: 1})(
+        q, keys, values, kv_cache, kv_lens, page_indices, cu_q_lens, distribution, sm_scale=np.float32(sm_scale))
+    return out, cache
