@@ -151,6 +151,12 @@ def test_the_one_call_step_equals_the_three_calls_bit_for_bit(q_lens, kv_lens, s
     same, _ = ops.ragged_paged_attention(in_place, dev["keys"], dev["values"], dev["kv_cache"].clone(), *index,
                                          dev["cu_q_lens"], dev["distribution"], scale, out=in_place)
     assert same is in_place and torch.equal(in_place.view(torch.int16), out3.view(torch.int16))
+    # Under the reference's name and signature (examples/ragged_paged_attention.py:279-290).
+    from tilejax_b200.autokernel.kernels import autokernel_rpa
+
+    named, _ = autokernel_rpa(dev["q"], dev["keys"], dev["values"], dev["kv_cache"].clone(), *index, dev["cu_q_lens"],
+                              dev["distribution"], sm_scale=scale)
+    assert torch.equal(named.view(torch.int16), out3.view(torch.int16))
 
 
 def test_the_one_call_step_refuses_before_it_writes_the_cache():

@@ -3,7 +3,8 @@
 Each is the plain loop nest over tiles whose meaning the kernel must reproduce — `kernel.fn` runs it as written on
 the CPU — with the same structure as the reference's examples (examples/matmul.py, causal_matmul.py,
 causal_attention.py, rmsnorm_matmul.py, decode.py `gqa_decode`, `mla_decode` and `paged_gqa_decode`,
-ragged_paged_attention.py `rpa_write`, `rpa_decode` and `rpa_prefill`, collective_matmul.py). Row statistics are kept as (rows, 1)
+ragged_paged_attention.py `rpa_write`, `rpa_decode`, `rpa_prefill` and the step `autokernel_rpa`,
+collective_matmul.py). Row statistics are kept as (rows, 1)
 columns here: the reference's lane-replicated (rows, 128) layout is a TPU register trick, not arithmetic.
 """
 
@@ -427,6 +428,18 @@ def make_rpa_prefill(sm_scale: float) -> autokernel.Kernel:
         return out
 
     return rpa_prefill
+
+
+def autokernel_rpa(queries, keys, values, kv_cache, kv_lens, page_indices, cu_q_lens, distribution, *, sm_scale=1.0):
+    """RPA v3's `ragged_paged_attention` as the reference composes it (examples/ragged_paged_attention.py:279-290: the
+    new tokens written into the cache, the decode sequences' attention, then the others'): (out (T, H, D), the
+    updated cache) for CUDA tensors. The reference runs three kernels with plain-JAX index arithmetic between them
+    and donates the queries and the cache; here the whole step, index arithmetic included, is one call into the
+    library (tilejax_b200.ops.ragged_paged_attention), the cache updated in place and the queries left alone."""
+    from tilejax_b200 import ops
+
+    return ops.ragged_paged_attention(queries, keys, values, kv_cache, kv_lens, page_indices, cu_q_lens, distribution,
+                                      float(sm_scale))
 
 
 @autokernel.kernel
